@@ -1,0 +1,188 @@
+/*
+ * ksearch_cuda.h -- C ABI of libksearch_cuda.so, a B200 (sm_100a) backend for
+ * the single-token decode path of ksearch.
+ *
+ * Each entry point names the reference interface it stands in for.  Paths are
+ * relative to the reference project root; K = crates/ksearch_kernels/src/lib.rs
+ * (the `Eng` op interface), M = crates/ksearch_metal/src/lib.rs (the device
+ * runtime), GG = crates/ksearch_gguf/src/gguf_impl.rs, GP =
+ * crates/ksearch_gemma/src/gemma_prim.rs, KV = crates/ksearch_gemma/src/kv_pool.rs,
+ * CG = crates/ksearch_codegen/src/lib.rs.
+ *
+ * Conventions (the reference's, K:137-146, M:269-374):
+ *   - every op only ENQUEUES work on the context's stream, in program order;
+ *     nothing inside an op allocates or synchronises;
+ *   - static dims first, then dtype tags, then (buffer, offset) pairs; offsets
+ *     are in ELEMENTS for f32/f16 operands and in BYTES for packed operands;
+ *   - outputs may alias inputs where the reference allows it (residual in/out);
+ *   - return 0 on success, a negative ks_status otherwise; ks_last_error() gives
+ *     the message.  Nothing aborts.  There is no CPU fallback: every op needs
+ *     a CUDA device of compute capability 10.x.
+ *   - one context per GPU, used from one thread at a time (M:20-22).
+ */
+#ifndef KSEARCH_CUDA_H
+#define KSEARCH_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ks_ctx ks_ctx;
+typedef struct ks_buf ks_buf;
+
+/* crates/ksearch_ir/src/lib.rs:17-74 (DType and packed byte sizes) */
+typedef enum { KS_F32 = 0, KS_F16 = 1, KS_Q4K = 2, KS_Q6K = 3, KS_Q40 = 4 } ks_dtype;
+
+typedef enum {
+  KS_OK = 0,
+  KS_ERR_INVALID = -1,     /* bad shape / alignment / range (anyhow::bail! in the reference) */
+  KS_ERR_CUDA = -2,        /* a CUDA call failed */
+  KS_ERR_OOM = -3,         /* allocation failed */
+  KS_ERR_UNSUPPORTED = -4, /* dtype or device not supported */
+  KS_ERR_STATE = -5,       /* e.g. max_seq exceeded (GP:882-884), slot pool full (KV:136-145) */
+  KS_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up */
+} ks_status;
+
+#define KS_Q4K_BLOCK_BYTES 144
+#define KS_Q6K_BLOCK_BYTES 210
+#define KS_Q40_BLOCK_BYTES 18
+#define KS_SDPA_MAX_SPLITS 64
+
+/* ---- runtime: MetalContext (M:16-218) ----------------------------------- */
+ks_ctx* ks_ctx_create(int device, uint64_t flags);          /* M:31-41  MetalContext::new */
+void ks_ctx_destroy(ks_ctx* ctx);
+const char* ks_last_error(const ks_ctx* ctx);               /* anyhow::Error text */
+const char* ks_chip_name(const ks_ctx* ctx);                /* M device_name(); KSEARCH_CHIP overrides (CG:63-66) */
+int ks_ctx_device(const ks_ctx* ctx);
+int ks_ctx_sm_count(const ks_ctx* ctx);
+void* ks_ctx_stream(const ks_ctx* ctx);                     /* the cudaStream_t ops are enqueued on */
+/* Number of kernels this context has launched since creation (bench bookkeeping). */
+uint64_t ks_ctx_launch_count(const ks_ctx* ctx);
+
+ks_buf* ks_buf_alloc(ks_ctx* ctx, size_t bytes);            /* M:63-91  buffer_empty_* (zero-filled) */
+void ks_buf_free(ks_ctx* ctx, ks_buf* buf);
+size_t ks_buf_size(const ks_buf* buf);
+void* ks_buf_device_ptr(const ks_buf* buf);
+/* Wrap device memory owned by the caller (e.g. a torch tensor); never freed by the library. */
+ks_buf* ks_buf_wrap(ks_ctx* ctx, void* device_ptr, size_t bytes);
+int ks_buf_upload(ks_ctx* ctx, ks_buf* dst, size_t dst_off, const void* host, size_t bytes);   /* M:93-113 write_buffer (blocking) */
+int ks_buf_download(ks_ctx* ctx, const ks_buf* src, size_t src_off, void* host, size_t bytes); /* M:115-135 read_* (synchronises first) */
+int ks_buf_upload_async(ks_ctx* ctx, ks_buf* dst, size_t dst_off, const void* host, size_t bytes);   /* write_buffer_nosync */
+int ks_buf_download_async(ks_ctx* ctx, const ks_buf* src, size_t src_off, void* host, size_t bytes); /* read_f32_nosync */
+int ks_buf_zero(ks_ctx* ctx, ks_buf* buf, size_t off, size_t bytes);
+void* ks_host_alloc_pinned(size_t bytes);
+void ks_host_free_pinned(void* p);
+
+int ks_flush(ks_ctx* ctx);                                  /* M:162   flush_async: mark a commit point */
+int ks_wait_inflight_at_most(ks_ctx* ctx, int n);           /* M:173   wait until <= n commit points are pending */
+int ks_synchronize(ks_ctx* ctx);                            /* M:205   synchronize */
+int ks_has_gpu_work(ks_ctx* ctx);                           /* M:157   has_gpu_work */
+
+/* Device-side stopwatch on the context's stream (the timed `run` of M:377-456 measures with
+ * the host clock around commit+wait; CUDA events time the device itself). */
+int ks_timer_begin(ks_ctx* ctx);
+int ks_timer_end_ms(ks_ctx* ctx, float* ms);               /* synchronises, returns elapsed milliseconds */
+
+/* Record the ops enqueued between begin and end into a replayable CUDA graph: the B200
+ * counterpart of keeping one open encoder per token (M:137-155, M:308-312) -- one submission
+ * replays a whole token.  Ops are capturable because none allocates or synchronises. */
+typedef struct ks_graph ks_graph;
+int ks_graph_begin(ks_ctx* ctx);
+ks_graph* ks_graph_end(ks_ctx* ctx);                       /* NULL on failure (see ks_last_error) */
+int ks_graph_launch(ks_ctx* ctx, ks_graph* g);
+void ks_graph_free(ks_ctx* ctx, ks_graph* g);
+
+/* ---- launch plans: OptSchedule {tg, vec, unroll, nsg, nr0} + ms of
+ * crates/ksearch_ir/src/kernel.rs:11-54, retargeted to the knobs of the hand-written matvec
+ * kernels.  A zero field means "kernel default". */
+typedef struct {
+  int variant;      /* kernel family member (0 = default) */
+  int nr;           /* rows kept in flight per lane group (nr0) */
+  int nwarps;       /* warps per block (nsg) */
+  int ctas_per_sm;  /* grid = min(tiles, SMs * ctas_per_sm) */
+  float ms;         /* measured time of the winning candidate, 0 if untimed */
+} ks_plan;
+/* Force every matvec launch of this context to use *plan (NULL clears): how the search times
+ * a candidate through the ordinary op path (K:2015-2031). */
+int ks_plan_override(ks_ctx* ctx, const ks_plan* plan);
+
+/* ---- dequant test hook: GG:577-794 dequant_blocks (Q4_0 / Q4_K / Q6_K) --- */
+int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_off, size_t nelem,
+               ks_buf* dst_f32, size_t dst_off);
+
+/* ---- matvec family ------------------------------------------------------- */
+/* y[t, r] = sum_c deq(W)[r, c] * x[t, c], t < n_tok (1..8).  x is [n_tok, cols],
+ * y is [n_tok, rows].  K:137 matvec_wd, K:1446 matvec_wd_at (offsets),
+ * K:1414 matvec_batch for 2 <= n_tok <= 8.  The weight matrix is streamed once
+ * for all n_tok tokens. */
+int ks_matvec(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* W, size_t w_byte_off,
+              ks_dtype act, const ks_buf* x, size_t x_off, ks_buf* y, size_t y_off, int n_tok);
+/* K:227 matvec_qkv_wds: three outputs in one launch. */
+int ks_matvec_qkv(ks_ctx* ctx, size_t q_rows, size_t kv_rows, size_t cols, ks_dtype dq, ks_dtype dk, ks_dtype dv,
+                  const ks_buf* Wq, const ks_buf* Wk, const ks_buf* Wv, ks_dtype act, const ks_buf* x,
+                  ks_buf* q, ks_buf* k, ks_buf* v);
+/* K:953 matvec_gate_up_gelu_wd: out[i] = gelu_tanh(clamp(Wg[i].x, +-20)) * (Wu[i].x). */
+int ks_matvec_gate_up_gelu(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* Wg,
+                           const ks_buf* Wu, ks_dtype act, const ks_buf* x, ks_buf* y);
+/* Blocking convenience for callers that hold HOST memory: copies x up, runs
+ * ks_matvec, copies y back.  W must already be resident (a ks_buf). */
+int ks_matvec_host(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* W, size_t w_byte_off,
+                   const float* x_host, float* y_host, int n_tok);
+
+/* ---- RMSNorm family ------------------------------------------------------ */
+/* K:456-535 rmsnorm / rmsnorm_at / rmsnorm_add / rmsnorm_add_scale and the
+ * *_rows forms K:1478-1560: y = (x*rsqrt(mean(x^2)+eps))*w [+ res] [* scale].
+ * res may be NULL; scale is applied only when has_scale != 0.  w: [n] in `act`. */
+int ks_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const ks_buf* x, size_t x_off,
+               const ks_buf* w, const ks_buf* res, size_t res_off, int has_scale, float scale, ks_buf* y,
+               size_t y_off);
+/* K:539 rmsnorm_add_then_rmsnorm: out_x = res + rms(y)*w_post; out_x2 = rms(out_x)*w_ffn. */
+int ks_rmsnorm_add_then_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const ks_buf* y,
+                                const ks_buf* w_post, const ks_buf* res, const ks_buf* w_ffn, ks_buf* out_x,
+                                ks_buf* out_x2);
+/* K:1257 rmsnorm_per_head_qkv_q40_off (n_tok == 1) and K:1750 .._batch:
+ * Q: per-head RMS*w then RoPE -> q_out; K: RMS*w, RoPE, Q4_0 pack; V: RMS (no
+ * weight), Q4_0 pack.  rope is f32 [*, hd] = cos[hd/2] || sin[hd/2] per position,
+ * rope_off in elements.  Token t writes its KV rows at kv_byte_off +
+ * t*n_kv*(hd/32*18). */
+int ks_rmsnorm_per_head_qkv_q40(ks_ctx* ctx, size_t n_q, size_t n_kv, size_t hd, size_t n_tok, float eps,
+                                ks_dtype act, const ks_buf* q, const ks_buf* qw, const ks_buf* rope,
+                                size_t rope_off, const ks_buf* k, const ks_buf* kw, const ks_buf* v,
+                                ks_buf* q_out, ks_buf* kv_k, ks_buf* kv_v, size_t kv_byte_off);
+
+/* ---- decode attention over a Q4_0 cache ---------------------------------- */
+/* K:1157 sdpa_hybrid_kv (one slot) and the slot-batched form used by serving.
+ * q/out: [n_slots, n_q*hd].  K, V: slot s starts at kv_byte_off + s*slot_stride_bytes,
+ * logical layout [max_t, n_kv, hd] in Q4_0.  meta: f32 [n_slots, 4] = (tlen, start, -, -)
+ * read ON THE DEVICE (GP:636-644), so one captured launch serves every length.
+ * Scores are scale*(q.k); the reference uses scale = 1.  n_splits partitions of
+ * the context per KV head (1..KS_SDPA_MAX_SPLITS; 0 = pick from max_t); tmp must
+ * hold ks_sdpa_tmp_floats() f32 when n_splits != 1 (K:1117 `tmp`). */
+size_t ks_sdpa_tmp_floats(size_t n_slots, size_t n_q, size_t hd, int n_splits);
+int ks_sdpa_pick_splits(const ks_ctx* ctx, size_t n_slots, size_t n_kv, size_t max_t);
+int ks_sdpa_decode(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t hd, size_t max_t,
+                   ks_dtype kv_dtype, float scale, ks_dtype act, const ks_buf* q, const ks_buf* K,
+                   const ks_buf* V, size_t kv_byte_off, size_t slot_stride_bytes, const ks_buf* meta,
+                   ks_buf* tmp, ks_buf* out, int n_splits);
+
+/* ---- small ops ------------------------------------------------------------ */
+/* K:1181 quantize_q40: n values (n % 32 == 0) -> Q4_0 at dst + dst_byte_off. */
+int ks_quantize_q40(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* src, size_t src_off, ks_buf* dst,
+                    size_t dst_byte_off);
+/* K:1364 copy_scale_indexed_wd / K:1387 .._batch_wd: dst[b, i] = scale * deq(src)[uint(idx[b])*n + i];
+ * idx holds token ids as f32.  src dtype: F32, F16, Q4K or Q6K. */
+int ks_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype, const ks_buf* src,
+                          const ks_buf* idx, size_t idx_off, ks_dtype act, ks_buf* dst);
+/* K:1966 softcap_argmax: index of max cap*tanh(x/cap), ties to the lower index, written as one f32. */
+int ks_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const ks_buf* logits, ks_buf* out_idx,
+                      size_t out_off);
+/* K:695 gelu_mul: y = gelu_tanh(clamp(g)) * u (the unfused fallback of the gate/up path). */
+int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_buf* u, ks_buf* y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KSEARCH_CUDA_H */

@@ -1,0 +1,106 @@
+// Internal declarations shared by the translation units of libksearch_cuda.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <deque>
+#include <string>
+
+#include "../../include/ksearch_cuda.h"
+
+struct ks_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t smem_optin = 0;
+  cudaStream_t stream = nullptr;
+  bool pdl = false;  // launch kernels with programmatic stream serialization
+  std::string err;
+  std::string chip;
+  std::deque<cudaEvent_t> inflight;  // commit points not yet known complete
+  uint64_t launches = 0;
+  cudaEvent_t t0 = nullptr, t1 = nullptr;  // stopwatch
+  bool has_override = false;
+  ks_plan override_plan{};
+  void* ws = nullptr;  // small zero-initialised device workspace (cross-block reductions)
+  // pinned staging for the *_host convenience calls
+  void* stage_h = nullptr;
+  size_t stage_h_bytes = 0;
+  ks_buf* stage_x = nullptr;
+  ks_buf* stage_y = nullptr;
+};
+
+struct ks_buf {
+  void* dptr = nullptr;
+  size_t bytes = 0;
+  bool owned = true;
+};
+
+int ks_fail(ks_ctx* ctx, int code, const char* fmt, ...);
+
+#define KS_REQUIRE(ctx, cond, ...)                              \
+  do {                                                          \
+    if (!(cond)) return ks_fail((ctx), KS_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define KS_CUDA(ctx, call)                                                                     \
+  do {                                                                                         \
+    cudaError_t e__ = (call);                                                                  \
+    if (e__ != cudaSuccess)                                                                    \
+      return ks_fail((ctx), KS_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__));     \
+  } while (0)
+
+// Checks the last launch and counts it.
+int ks_after_launch(ks_ctx* ctx, const char* what);
+
+static inline size_t ks_act_bytes(ks_dtype a) { return a == KS_F16 ? 2 : 4; }
+static inline bool ks_is_act(ks_dtype a) { return a == KS_F32 || a == KS_F16; }
+static inline size_t ks_block_bytes(ks_dtype d) {
+  return d == KS_Q4K ? KS_Q4K_BLOCK_BYTES : d == KS_Q6K ? KS_Q6K_BLOCK_BYTES : d == KS_Q40 ? KS_Q40_BLOCK_BYTES : 0;
+}
+static inline size_t ks_block_elems(ks_dtype d) { return d == KS_Q40 ? 32 : 256; }
+// bytes of n elements of dtype d (n a multiple of the block size for packed types)
+static inline size_t ks_nbytes(ks_dtype d, size_t n) {
+  if (d == KS_F32) return n * 4;
+  if (d == KS_F16) return n * 2;
+  return n / ks_block_elems(d) * ks_block_bytes(d);
+}
+
+// Range check of (buffer, byte offset, byte extent).
+static inline bool ks_fits(const ks_buf* b, size_t off, size_t extent) {
+  return b && b->dptr && off <= b->bytes && extent <= b->bytes - off;
+}
+
+// ---- launchers on raw device pointers (used by the C ABI and by the decoder) --
+struct ks_mv_seg {   // one weight matrix of a fused matvec launch
+  const uint8_t* W;  // packed rows
+  void* y;           // output vector base ([n_tok, rows])
+  unsigned rows;
+};
+
+enum ks_mv_epilogue { KS_EPI_PLAIN = 0, KS_EPI_GATE_UP = 1 };
+
+// Launch tuning knobs of the matvec kernels (the planner's vocabulary, after
+// OptSchedule in crates/ksearch_ir/src/kernel.rs:11-54).  Zero = default.
+typedef ks_plan ks_mv_plan;
+
+int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi,
+                     size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan);
+
+int ks_launch_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const void* x, const void* w,
+                      const void* res, int has_scale, float scale, void* y);
+int ks_launch_rmsnorm_add_then_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const void* y,
+                                       const void* w_post, const void* res, const void* w_ffn, void* out_x,
+                                       void* out_x2);
+int ks_launch_per_head_qkv_q40(ks_ctx* ctx, size_t n_q, size_t n_kv, size_t hd, size_t n_tok, float eps,
+                               ks_dtype act, const void* q, const void* qw, const float* rope, const void* k,
+                               const void* kw, const void* v, void* q_out, uint8_t* kv_k, uint8_t* kv_v,
+                               const int* pos_dev, size_t slot_stride_bytes);
+int ks_launch_sdpa(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t hd, float scale, ks_dtype act,
+                   const void* q, const uint8_t* K, const uint8_t* V, size_t slot_stride_bytes, const float* meta,
+                   float* tmp, void* out, int n_splits);
+int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype,
+                                 const void* src, const float* idx, ks_dtype act, void* dst);
+int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);

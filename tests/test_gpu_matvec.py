@@ -1,0 +1,201 @@
+"""GPU parity tests of the dequant-fused matvec family, through the C ABI.
+
+Tolerance (the path's contract): |y - ref| <= 1e-4 + 1e-3*|ref| element-wise against the
+f64-accumulated CPU result, plus a norm-wise bound against the reference-style f32
+sequential sum (whose own rounding noise exceeds the element-wise bound on rows that
+cancel to ~0, so it cannot be the element-wise yardstick)."""
+import numpy as np
+import pytest
+
+from ksearch_b200 import F16, F32, Q4K, Q6K, Eng, KsError, synth
+from tests.conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _gen(dtype, seed, name, rows, cols, **kw):
+    return (synth.q4k_matrix if dtype == Q4K else synth.q6k_matrix)(seed, name, rows, cols, **kw)
+
+
+def _check(y, y32, y64, what):
+    assert_close(y, y64, what=what)
+    scale = np.abs(y64).max()
+    assert np.abs(y - y32).max() <= 1e-5 * scale + 1e-4, what
+
+
+@pytest.mark.parametrize("name", ["q4k_64x512", "q4k_24x1536", "q6k_32x1536"])
+def test_matvec_golden_cases(ctx, golden_cases, name):
+    W, x = golden_cases[name + ".W"], golden_cases[name + ".x"]
+    dtype = Q4K if name.startswith("q4k") else Q6K
+    rows, cols = (int(v) for v in name.split("_")[1].split("x"))
+    y = ctx.buffer_empty_f32(rows)
+    Eng().matvec_wd(ctx, rows, cols, dtype, ctx.buffer_bytes(W), ctx.buffer_bytes(x), y)
+    _check(ctx.read_f32(y, rows), golden_cases[name + ".y32"], golden_cases[name + ".y64"], name)
+
+
+@pytest.mark.parametrize("dtype,rows,cols", [
+    (Q4K, 256, 4096),    # config 0 columns
+    (Q4K, 128, 1536), (Q4K, 96, 6144), (Q4K, 64, 10240), (Q4K, 130, 2048), (Q4K, 33, 2560),
+    (Q4K, 1, 256), (Q4K, 7, 768), (Q4K, 5, 512), (Q4K, 3, 1280),
+    (Q6K, 512, 1536), (Q6K, 100, 2560), (Q6K, 1, 256), (Q6K, 9, 768), (Q6K, 31, 4096),
+])
+def test_matvec_vs_oracle(ctx, oracle, dtype, rows, cols):
+    W = _gen(dtype, 61, f"W{rows}x{cols}", rows, cols)
+    x = synth.normals(61, "x", cols)
+    y = ctx.buffer_empty_f32(rows + 8)
+    Eng().matvec_wd_at(ctx, rows, cols, dtype, ctx.buffer_bytes(W), ctx.buffer_bytes(np.concatenate([np.zeros(3, np.float32), x])), 3, y, 4)
+    got = ctx.read_f32(y, rows + 8)
+    assert not got[:4].any() and not got[rows + 4:].any()      # nothing written outside [y_off, y_off+rows)
+    y32, y64 = oracle.matvec(dtype, W, rows, cols, x)
+    _check(got[4:rows + 4], y32, y64, f"matvec {dtype} {rows}x{cols}")
+
+
+def test_matvec_q6k_signed_scales(ctx, oracle):
+    W = synth.q6k_matrix(62, "W", 200, 1536, signed_scales=True)
+    x = synth.normals(62, "x", 1536)
+    y = ctx.buffer_empty_f32(200)
+    Eng().matvec_wd(ctx, 200, 1536, Q6K, ctx.buffer_bytes(W), ctx.buffer_bytes(x), y)
+    y32, y64 = oracle.matvec(Q6K, W, 200, 1536, x)
+    _check(ctx.read_f32(y, 200), y32, y64, "q6k signed scales")
+
+
+def test_matvec_reference_patterns(ctx, oracle):
+    """check_mul_mm.rs:47-109 inputs: integer-pattern W quantised by the reference quantizer,
+    pattern x; GEMV vs CPU dequant + f32 dot.  The reference prints max|err| against a 0.05
+    threshold; here the path's own tolerance applies."""
+    for rows, cols, batch in ((64, 256, 8), (128, 256, 8), (512, 1536, 4)):
+        r, c, t = np.arange(rows)[:, None], np.arange(cols)[None, :], np.arange(batch)[:, None]
+        w = ((((r * 17 + c * 13) % 200).astype(np.float32) - 100.0) * np.float32(0.02)).astype(np.float32)
+        x = ((((t * 11 + c * 7) % 50).astype(np.float32) - 25.0) * np.float32(0.04)).astype(np.float32)
+        wq = oracle.quantize_q4k(w.ravel())
+        y32, y64 = oracle.matvec(Q4K, wq, rows, cols, x)
+        by = ctx.buffer_empty_f32(batch * rows)
+        Eng().matvec_batch(ctx, rows, cols, batch, Q4K, ctx.buffer_bytes(wq), ctx.buffer_bytes(x), by)
+        got = ctx.read_f32(by, batch * rows).reshape(batch, rows)
+        _check(got, y32, y64, f"pattern {rows}x{cols}x{batch}")
+        assert np.abs(got - x.astype(np.float64) @ w.astype(np.float64).T).max() < 0.05 * np.sqrt(cols)
+
+
+@pytest.mark.parametrize("dtype", [Q4K, Q6K])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 8])
+def test_matvec_batch(ctx, oracle, dtype, batch):
+    rows, cols = 96, 1536
+    W = _gen(dtype, 63, "W", rows, cols)
+    x = synth.normals(63, "x", batch * cols).reshape(batch, cols)
+    y = ctx.buffer_empty_f32(batch * rows)
+    Eng().matvec_batch(ctx, rows, cols, batch, dtype, ctx.buffer_bytes(W), ctx.buffer_bytes(x), y)
+    y32, y64 = oracle.matvec(dtype, W, rows, cols, x)
+    _check(ctx.read_f32(y, batch * rows).reshape(batch, rows), np.atleast_2d(y32), np.atleast_2d(y64), f"batch {batch}")
+
+
+@pytest.mark.parametrize("q_rows,kv_rows,cols", [(2048, 256, 1536), (2048, 512, 2560), (40, 8, 512)])
+def test_matvec_qkv(ctx, oracle, q_rows, kv_rows, cols):
+    Wq, Wk, Wv = (_gen(Q4K, 64, n, r, cols) for n, r in (("q", q_rows), ("k", kv_rows), ("v", kv_rows)))
+    x = synth.normals(64, "x", cols)
+    q, k, v = ctx.buffer_empty_f32(q_rows), ctx.buffer_empty_f32(kv_rows), ctx.buffer_empty_f32(kv_rows)
+    Eng().matvec_qkv_wd(ctx, q_rows, kv_rows, cols, Q4K, *map(ctx.buffer_bytes, (Wq, Wk, Wv)), ctx.buffer_bytes(x), q, k, v)
+    for buf, W, r, nm in ((q, Wq, q_rows, "q"), (k, Wk, kv_rows, "k"), (v, Wv, kv_rows, "v")):
+        y32, y64 = oracle.matvec(Q4K, W, r, cols, x)
+        _check(ctx.read_f32(buf, r), y32, y64, "qkv " + nm)
+
+
+def test_matvec_qkv_mixed_dtypes(ctx, oracle):
+    """Q4K / Q4K / Q6K packings in one call (K:226 'per-buffer weight dtypes')."""
+    cols = 1536
+    Wq, Wk, Wv = _gen(Q4K, 65, "q", 64, cols), _gen(Q4K, 65, "k", 16, cols), _gen(Q6K, 65, "v", 16, cols)
+    x = synth.normals(65, "x", cols)
+    q, k, v = ctx.buffer_empty_f32(64), ctx.buffer_empty_f32(16), ctx.buffer_empty_f32(16)
+    Eng().matvec_qkv_wds(ctx, 64, 16, cols, Q4K, Q4K, Q6K, *map(ctx.buffer_bytes, (Wq, Wk, Wv)), ctx.buffer_bytes(x), q, k, v)
+    y32, y64 = oracle.matvec(Q6K, Wv, 16, cols, x)
+    _check(ctx.read_f32(v, 16), y32, y64, "mixed v")
+    y32, y64 = oracle.matvec(Q4K, Wq, 64, cols, x)
+    _check(ctx.read_f32(q, 64), y32, y64, "mixed q")
+
+
+@pytest.mark.parametrize("rows,cols", [(6144, 1536), (1000, 2560), (6, 512)])
+def test_matvec_gate_up_gelu(ctx, oracle, rows, cols):
+    # d scaled down so the gate lands in GELU's curved range rather than saturating
+    Wg, Wu = _gen(Q4K, 66, "g", rows, cols, sigma=0.0005), _gen(Q4K, 66, "u", rows, cols, sigma=0.0005)
+    x = synth.normals(66, "x", cols)
+    y = ctx.buffer_empty_f32(rows)
+    Eng().matvec_gate_up_gelu_wd(ctx, rows, cols, Q4K, ctx.buffer_bytes(Wg), ctx.buffer_bytes(Wu), ctx.buffer_bytes(x), y)
+    _, g64 = oracle.matvec(Q4K, Wg, rows, cols, x)
+    _, u64 = oracle.matvec(Q4K, Wu, rows, cols, x)
+    want = oracle.gelu_mul(g64.astype(np.float32), u64.astype(np.float32))
+    # the product of two rounded dot products: allow each factor its own tolerance
+    got = ctx.read_f32(y, rows)
+    tol = 1e-4 + 2e-3 * np.abs(want) + 1e-4 * (np.abs(g64) + np.abs(u64))
+    assert np.all(np.abs(got - want) <= tol)
+
+
+def test_matvec_f16_activations(ctx, oracle):
+    """The reference's own mode: f16 x in, f16 y out, f32 accumulation (RE:2263-2274)."""
+    rows, cols = 256, 1536
+    W = _gen(Q4K, 67, "W", rows, cols, sigma=0.001)
+    x = synth.normals(67, "x", cols).astype(np.float16)
+    y = ctx.buffer_empty_f16(rows)
+    Eng(F16).matvec_wd(ctx, rows, cols, Q4K, ctx.buffer_bytes(W), ctx.buffer_bytes(x), y)
+    _, y64 = oracle.matvec(Q4K, W, rows, cols, x.astype(np.float32))
+    got = ctx.read_f16(y, rows).astype(np.float64)
+    assert np.all(np.abs(got - y64) <= 1e-3 + 1.5e-3 * np.abs(y64))
+
+
+def test_matvec_linearity_full_size(ctx):
+    """Size-independent property at the full 4096x4096 shape: W(a*x1 + x2) = a*W x1 + W x2."""
+    rows = cols = 4096
+    W = ctx.buffer_bytes(synth.q4k_matrix(68, "W", rows, cols))
+    x1, x2 = synth.normals(68, "x1", cols), synth.normals(68, "x2", cols)
+    e = Eng()
+    ys = []
+    for x in (x1, x2, (np.float32(0.5) * x1 + x2).astype(np.float32)):
+        y = ctx.buffer_empty_f32(rows)
+        e.matvec_wd(ctx, rows, cols, Q4K, W, ctx.buffer_bytes(x), y)
+        ys.append(ctx.read_f32(y, rows).astype(np.float64))
+    scale = np.abs(ys[2]).max()
+    assert np.abs(0.5 * ys[0] + ys[1] - ys[2]).max() <= 2e-5 * scale
+
+
+def test_matvec_full_config_shapes_row_checksums(ctx, oracle):
+    """Full-size shapes of the sweep; the oracle checks a strided sample of rows exactly and the
+    rest through the sum of outputs (y . 1 = (W^T 1) . x is linear in the rows)."""
+    for dtype, rows, cols in ((Q4K, 4096, 4096), (Q4K, 6144, 1536), (Q4K, 1536, 6144), (Q4K, 2560, 10240), (Q6K, 32768, 1536)):
+        W = _gen(dtype, 69, f"W{rows}x{cols}", rows, cols)
+        x = synth.normals(69, "x", cols)
+        y = ctx.buffer_empty_f32(rows)
+        Eng().matvec_wd(ctx, rows, cols, dtype, ctx.buffer_bytes(W), ctx.buffer_bytes(x), y)
+        got = ctx.read_f32(y, rows)
+        rb = cols // 256 * (144 if dtype == Q4K else 210)
+        sel = np.arange(0, rows, max(1, rows // 256))
+        Wsel = np.concatenate([W[r * rb:(r + 1) * rb] for r in sel])
+        y32, y64 = oracle.matvec(dtype, Wsel, sel.size, cols, x)
+        _check(got[sel], y32, y64, f"sample {rows}x{cols}")
+        assert np.isfinite(got).all()
+
+
+def test_matvec_host_entry(ctx, oracle):
+    rows, cols = 512, 1536
+    W = _gen(Q4K, 70, "W", rows, cols)
+    x = synth.normals(70, "x", 2 * cols)
+    y = np.empty(2 * rows, np.float32)
+    bw = ctx.buffer_bytes(W)
+    ctx.check(ctx.lib.ks_matvec_host(ctx.h, rows, cols, Q4K, bw.h, 0, x.ctypes.data, y.ctypes.data, 2))
+    y32, y64 = oracle.matvec(Q4K, W, rows, cols, x.reshape(2, cols))
+    _check(y.reshape(2, rows), y32, y64, "matvec_host")
+
+
+def test_matvec_errors(ctx):
+    e = Eng()
+    W = ctx.buffer_bytes(synth.q4k_matrix(71, "W", 8, 512))
+    x, y = ctx.buffer_empty_f32(512), ctx.buffer_empty_f32(8)
+    with pytest.raises(KsError, match="multiple of 256"):
+        e.matvec_wd(ctx, 8, 500, Q4K, W, x, y)
+    with pytest.raises(KsError, match="too small"):
+        e.matvec_wd(ctx, 16, 512, Q4K, W, x, y)
+    with pytest.raises(KsError, match="not supported"):
+        e.matvec_wd(ctx, 8, 512, F16, W, x, y)
+    with pytest.raises(KsError, match="n_tok"):
+        e.matvec_batch(ctx, 8, 512, 9, Q4K, W, x, y)
+    with pytest.raises(KsError, match="y buffer"):
+        e.matvec_wd_at(ctx, 8, 512, Q4K, W, x, 0, y, 4)
+    with pytest.raises(KsError):
+        e.matvec_gate_up_gelu_wd(ctx, 8, 512, Q6K, W, W, x, y)
