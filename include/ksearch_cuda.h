@@ -182,6 +182,41 @@ int ks_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const ks_b
 /* K:695 gelu_mul: y = gelu_tanh(clamp(g)) * u (the unfused fallback of the gate/up path). */
 int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_buf* u, ks_buf* y);
 
+/* ---- decode driver: GemmaPrimModel (GP:76-132, 881-1275, 1616-1768) + KvPool (KV:24-230) ----
+ * Dense layers that own their KV cache; no per-layer embeddings, sliding window or shared KV. */
+typedef struct ks_model ks_model;
+typedef struct {              /* the GemmaConfig fields the dense path uses (crates/ksearch_gemma/src/lib.rs:14-36) */
+  int n_layers, hidden, ffn, n_q, n_kv, hd, vocab, max_seq;
+  int n_slots;                /* KvPool max_batch (1..8): slots that can advance in one weight pass */
+  float eps, rope_theta, softcap, attn_scale;   /* attn_scale: the reference uses 1 */
+  int embd_dtype;             /* ks_dtype of the tied token_embd / lm_head: KS_Q4K or KS_Q6K */
+  int act;                    /* ks_dtype of activations and norm weights: KS_F32 or KS_F16 */
+} ks_model_config;
+typedef struct {              /* GenerateStats (crates/ksearch_gemma/src/lib.rs:189-205), device-timed */
+  int prefill_tokens, decode_tokens;
+  float prefill_ms_device, decode_ms_device;
+} ks_generate_stats;
+
+ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg);          /* GP:135-413 load, minus the GGUF file */
+void ks_model_destroy(ks_model* m);
+/* Tensor names are the GGUF names the reference loads (GP:149-183, 356-357): token_embd.weight,
+ * output_norm.weight, blk.N.{attn_q,attn_k,attn_v,attn_output,ffn_gate,ffn_up,ffn_down}.weight (Q4_K),
+ * blk.N.{attn_norm,attn_q_norm,attn_k_norm,post_attention_norm,ffn_norm,post_ffw_norm}.weight (act dtype). */
+size_t ks_model_tensor_bytes(const ks_model* m, const char* name);           /* 0 if unknown */
+int ks_model_upload_tensor(ks_model* m, const char* name, const void* host, size_t bytes);  /* GP:415-451 ensure_weight */
+const void* ks_model_tensor_ptr(const ks_model* m, const char* name);      /* device address of a resident tensor, NULL if unknown */
+size_t ks_model_weight_bytes(const ks_model* m);
+int ks_model_slot_alloc(ks_model* m);                                        /* KV:136 alloc -> slot id, or KS_ERR_STATE "KvPool full" */
+int ks_model_slot_free(ks_model* m, int slot);                               /* KV:168 free */
+int ks_model_slot_reset(ks_model* m, int slot);                              /* KV:147 clear_slot + GP:1644 reset */
+int ks_model_slot_seq_len(const ks_model* m, int slot);                      /* KV:161 seq_len */
+int ks_model_slot_active(const ks_model* m);                                 /* KV:179 active_batch().len() */
+int ks_model_forward(ks_model* m, int first_slot, int n_slots, const int* tokens, int want_logits);   /* GP:881 forward_token, enqueue only */
+int ks_model_decode_token(ks_model* m, int first_slot, int n_slots, const int* tokens, int* next);    /* GP:1616 decode_token, blocking */
+int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight,
+                      int* out, ks_generate_stats* stats);                   /* GP:1658 generate_timed */
+const void* ks_model_debug_ptr(const ks_model* m, int which, int slot);      /* test hook: 0 residual x, 1 logits */
+
 #ifdef __cplusplus
 }
 #endif

@@ -66,6 +66,21 @@ SIGNATURES = {
     "ks_copy_scale_indexed": (_i, [_vp, _sz, _sz, _f, _i, _vp, _vp, _sz, _i, _vp]),
     "ks_softcap_argmax": (_i, [_vp, _sz, _f, _i, _vp, _vp, _sz]),
     "ks_gelu_mul": (_i, [_vp, _sz, _i, _vp, _vp, _vp]),
+    "ks_model_create": (_vp, [_vp, _vp]),
+    "ks_model_destroy": (None, [_vp]),
+    "ks_model_tensor_bytes": (_sz, [_vp, C.c_char_p]),
+    "ks_model_upload_tensor": (_i, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_model_tensor_ptr": (_vp, [_vp, C.c_char_p]),
+    "ks_model_weight_bytes": (_sz, [_vp]),
+    "ks_model_slot_alloc": (_i, [_vp]),
+    "ks_model_slot_free": (_i, [_vp, _i]),
+    "ks_model_slot_reset": (_i, [_vp, _i]),
+    "ks_model_slot_seq_len": (_i, [_vp, _i]),
+    "ks_model_slot_active": (_i, [_vp]),
+    "ks_model_forward": (_i, [_vp, _i, _i, _vp, _i]),
+    "ks_model_decode_token": (_i, [_vp, _i, _i, _vp, _vp]),
+    "ks_model_generate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp]),
+    "ks_model_debug_ptr": (_vp, [_vp, _i, _i]),
 }
 
 

@@ -128,27 +128,51 @@ __device__ __forceinline__ unsigned total_tiles_of(const MvArgs& a) {
 // Shared memory: xp[unit][l] = (x_lo[l]*s, x_hi[l]*s/16), s = 1 for even l, 1/256 for odd l;
 //                sx[unit]    = (sum x_lo, sum x_hi).
 // -------------------------------------------------------------------------------------------
+// Stage x for the Q4_K kernels.  Thread i takes 4 consecutive elements (always one sub-block:
+// 8 neighbouring lanes cover its 32 elements), so every load is issued before anything waits
+// and the sub-block sums need three shuffles instead of a pass over shared memory.
 template <typename XT>
 __device__ __forceinline__ void q4k_stage_x(unsigned char* smem, const XT* x, unsigned cols, int n_tok) {
   const unsigned units = cols >> 6;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  const float s_lo = (lane & 1) ? (1.0f / 256.0f) : 1.0f;
-  const float s_hi = s_lo * (1.0f / 16.0f);
+  const unsigned nchunk = cols >> 2;
   for (int t = 0; t < n_tok; t++) {
-    float2* xp = reinterpret_cast<float2*>(smem) + (size_t)t * units * 33;
-    float2* sx = xp + (size_t)units * 32;
+    float* xp = reinterpret_cast<float*>(smem) + (size_t)t * units * 66;  // float2 [units*32] then float2 [units]
+    float* sx = xp + (size_t)units * 64;
     const XT* xt = x + (size_t)t * cols;
-    for (unsigned u = warp; u < units; u += nwarp) {
-      float lo = act_load<XT>(xt, (size_t)u * 64 + lane);
-      float hi = act_load<XT>(xt, (size_t)u * 64 + 32 + lane);
-      xp[u * 32 + lane] = make_float2(lo * s_lo, hi * s_hi);
-      float a = lo, b = hi;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        a += __shfl_xor_sync(0xffffffffu, a, o);
-        b += __shfl_xor_sync(0xffffffffu, b, o);
+    // cols is a multiple of 256, so nchunk is a multiple of 64 and whole warps run every trip
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(xt) & (sizeof(XT) * 4 - 1)) == 0;
+#pragma unroll 4
+    for (unsigned c = threadIdx.x; c < nchunk; c += blockDim.x) {
+      const bool live = true;
+      float v0, v1, v2, v3;
+      if (!vec_ok) {
+        v0 = act_load<XT>(xt, (size_t)c * 4);
+        v1 = act_load<XT>(xt, (size_t)c * 4 + 1);
+        v2 = act_load<XT>(xt, (size_t)c * 4 + 2);
+        v3 = act_load<XT>(xt, (size_t)c * 4 + 3);
+      } else if (sizeof(XT) == 4) {
+        const float4 v = reinterpret_cast<const float4*>(xt)[c];
+        v0 = v.x; v1 = v.y; v2 = v.z; v3 = v.w;
+      } else {
+        const uint2 raw = reinterpret_cast<const uint2*>(xt)[c];
+        const __half2 a = *reinterpret_cast<const __half2*>(&raw.x), b = *reinterpret_cast<const __half2*>(&raw.y);
+        v0 = __low2float(a); v1 = __high2float(a); v2 = __low2float(b); v3 = __high2float(b);
       }
-      if (lane == 0) sx[u] = make_float2(a, b);
+      const unsigned e = c << 2;
+      const unsigned u = e >> 6, hi = (e >> 5) & 1u, l = e & 31u;  // l is a multiple of 4: even, odd, even, odd
+      float s = (v0 + v1) + (v2 + v3);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (live) {
+        const float k0 = hi ? (1.0f / 16.0f) : 1.0f, k1 = hi ? (1.0f / 4096.0f) : (1.0f / 256.0f);
+        float* dst = xp + ((size_t)u * 32 + l) * 2 + hi;
+        dst[0] = v0 * k0;
+        dst[2] = v1 * k1;
+        dst[4] = v2 * k0;
+        dst[6] = v3 * k1;
+        if ((threadIdx.x & 7u) == 0) sx[(size_t)u * 2 + hi] = s;
+      }
     }
   }
 }

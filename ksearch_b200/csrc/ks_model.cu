@@ -1,0 +1,517 @@
+// Decode driver: the op sequence of GemmaPrimModel::forward_token
+// (crates/ksearch_gemma/src/gemma_prim.rs:881-1275) for dense layers that own
+// their KV cache, the slot pool of crates/ksearch_gemma/src/kv_pool.rs:24-230,
+// and the generate loop of gemma_prim.rs:1658-1768.
+//
+// What differs from the reference, by design for this GPU:
+//   * the position, the (tlen, start) attention record and the token id all
+//     live on the device (the reference already keeps the token id there,
+//     gemma_prim.rs:1237-1242), so ONE captured CUDA graph replays any token;
+//   * up to 8 slots advance together through one pass over the weights
+//     (the reference runs slots serially, scheduler.rs:163-231);
+//   * the residual update after the FFN and the next layer's attention norm
+//     run as one launch (the same two-output kernel as after attention).
+// Per-layer embeddings, sliding windows and shared-KV layers of real Gemma-4
+// checkpoints are not part of this driver.
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "ks_internal.h"
+
+namespace {
+
+__global__ void begin_token_kernel(int n, const int* pos, float* meta) {
+  const int s = threadIdx.x;
+  if (s < n) {
+    meta[s * 4 + 0] = (float)(pos[s] + 1);  // tlen = kv_len (gemma_prim.rs:1009-1016, full attention)
+    meta[s * 4 + 1] = 0.0f;                 // start
+    meta[s * 4 + 2] = 0.0f;
+    meta[s * 4 + 3] = 0.0f;
+  }
+}
+__global__ void end_token_kernel(int n, int* pos) {
+  const int s = threadIdx.x;
+  if (s < n) pos[s] += 1;
+}
+__global__ void set_state_kernel(int slot, int pos_value, int* pos) { pos[slot] = pos_value; }
+
+struct Tensor {
+  void* dptr = nullptr;
+  size_t bytes = 0;
+  bool set = false;
+};
+
+struct Layer {
+  Tensor wq, wk, wv, wo, wgate, wup, wdown;
+  Tensor attn_norm, q_norm, k_norm, post_attn_norm, ffn_norm, post_ffw_norm;
+};
+
+}  // namespace
+
+struct ks_model {
+  ks_ctx* ctx = nullptr;
+  ks_model_config cfg{};
+  std::vector<Layer> layers;
+  Tensor token_embd, output_norm;
+  std::map<std::string, Tensor*> by_name;
+  void* arena = nullptr;  // all weights, one allocation
+  size_t arena_bytes = 0;
+  // KV pool: per layer K and V, [n_slots, max_seq, n_kv, hd] Q4_0
+  std::vector<uint8_t*> kv_k, kv_v;
+  size_t slot_stride = 0;
+  std::vector<char> occupied;
+  std::vector<int> seq_len;
+  // activations, n_slots rows each
+  void *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *ff = nullptr,
+       *logits = nullptr;
+  float* rope = nullptr;
+  float* tok = nullptr;   // [2][n_slots] f32 token ids, ping-pong (gemma_prim.rs:98-99)
+  int* pos = nullptr;     // [n_slots]
+  float* meta = nullptr;  // [n_slots][4]
+  float* attn_tmp = nullptr;
+  int n_splits = 1;
+  float* host_tok = nullptr;  // pinned ring for token read-back
+  size_t host_tok_n = 0;
+  // graphs keyed by (first slot, n slots, src parity, want_logits)
+  std::map<uint64_t, cudaGraphExec_t> graphs;
+  std::map<uint64_t, size_t> graph_nodes;
+  std::vector<void*> owned;
+  int tok_src = 0;  // which half of the ping-pong holds the next input ids
+};
+
+namespace {
+
+size_t act_b(const ks_model* m) { return ks_act_bytes((ks_dtype)m->cfg.act); }
+
+int dev_alloc(ks_model* m, void** p, size_t bytes) {
+  cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+  if (e != cudaSuccess) return ks_fail(m->ctx, KS_ERR_OOM, "model: cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+  cudaMemsetAsync(*p, 0, bytes ? bytes : 16, m->ctx->stream);
+  m->owned.push_back(*p);
+  return KS_OK;
+}
+
+// One token (or one token per slot for slots first..first+n-1) through every layer.
+// src: which half of the token ping-pong holds the input ids.
+int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
+  ks_ctx* c = m->ctx;
+  const ks_model_config& g = m->cfg;
+  const ks_dtype act = (ks_dtype)g.act;
+  const size_t ab = act_b(m);
+  const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
+  const size_t qn = nq * hd, kvn = nkv * hd;
+  char* x = (char*)m->x + (size_t)first * H * ab;
+  char* x2 = (char*)m->x2 + (size_t)first * H * ab;
+  char* q = (char*)m->q + (size_t)first * qn * ab;
+  char* k = (char*)m->k + (size_t)first * kvn * ab;
+  char* v = (char*)m->v + (size_t)first * kvn * ab;
+  char* o = (char*)m->o + (size_t)first * qn * ab;
+  char* ff = (char*)m->ff + (size_t)first * F * ab;
+  char* logits = (char*)m->logits + (size_t)first * g.vocab * ab;
+  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
+  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  int* pos = m->pos + first;
+  float* meta = m->meta + (size_t)first * 4;
+  int rc;
+
+  begin_token_kernel<<<1, 32, 0, c->stream>>>(n, pos, meta);
+  if ((rc = ks_after_launch(c, "begin_token"))) return rc;
+  // embed: x = sqrt(hidden) * deq(token_embd[id])   (gemma_prim.rs:681-683)
+  if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, act, x))) return rc;
+  if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
+
+  for (int l = 0; l < g.n_layers; l++) {
+    const Layer& L = m->layers[l];
+    ks_mv_seg qkv[3] = {{(const uint8_t*)L.wq.dptr, q, (unsigned)qn},
+                        {(const uint8_t*)L.wk.dptr, k, (unsigned)kvn},
+                        {(const uint8_t*)L.wv.dptr, v, (unsigned)kvn}};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, qkv, 3, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
+    uint8_t* kk = m->kv_k[l] + (size_t)first * m->slot_stride;
+    uint8_t* kv = m->kv_v[l] + (size_t)first * m->slot_stride;
+    if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
+                                         kk, kv, pos, m->slot_stride)))
+      return rc;
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, m->slot_stride, meta, m->attn_tmp, o, m->n_splits)))
+      return rc;
+    ks_mv_seg so{(const uint8_t*)L.wo.dptr, x2, (unsigned)H};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
+    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_attn_norm.dptr, x, L.ffn_norm.dptr, x, x2))) return rc;
+    ks_mv_seg gu[2] = {{(const uint8_t*)L.wgate.dptr, ff, (unsigned)F}, {(const uint8_t*)L.wup.dptr, ff, (unsigned)F}};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, gu, 2, KS_EPI_GATE_UP, H, act, x2, n, nullptr))) return rc;
+    ks_mv_seg sd{(const uint8_t*)L.wdown.dptr, x2, (unsigned)H};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, &sd, 1, KS_EPI_PLAIN, F, act, ff, n, nullptr))) return rc;
+    // x += rms(down)*w_post_ffw, then the NEXT norm (next layer's attn_norm, or output_norm) in the same launch
+    const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
+    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_ffw_norm.dptr, x, next_norm, x, x2))) return rc;
+  }
+  end_token_kernel<<<1, 32, 0, c->stream>>>(n, pos);
+  if ((rc = ks_after_launch(c, "end_token"))) return rc;
+  if (!want_logits) return KS_OK;
+  // head: logits = token_embd . rms(x, output_norm); next id = softcap argmax (gemma_prim.rs:1222-1242)
+  ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
+  if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
+  for (int s = 0; s < n; s++)
+    if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
+  return KS_OK;
+}
+
+// Launch the forward pass through a cached graph (captured on first use).
+int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
+  ks_ctx* c = m->ctx;
+  const uint64_t key = ((uint64_t)first << 32) | ((uint64_t)n << 8) | ((uint64_t)src << 1) | (want_logits ? 1 : 0);
+  auto it = m->graphs.find(key);
+  if (it == m->graphs.end()) {
+    cudaGraph_t graph = nullptr;
+    KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    const uint64_t before = c->launches;
+    int rc = enqueue_forward(m, first, n, src, want_logits);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    c->launches = before;  // captured launches are counted when the graph replays
+    if (rc) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    if (e != cudaSuccess) return ks_fail(c, KS_ERR_CUDA, "model: graph capture failed: %s", cudaGetErrorString(e));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return ks_fail(c, KS_ERR_CUDA, "model: graph instantiate failed: %s", cudaGetErrorString(e));
+    m->graphs[key] = exec;
+    m->graph_nodes[key] = nodes;
+    it = m->graphs.find(key);
+  }
+  KS_CUDA(c, cudaGraphLaunch(it->second, c->stream));
+  c->launches += m->graph_nodes[key];
+  return KS_OK;
+}
+
+}  // namespace
+
+// ---- C ABI ------------------------------------------------------------------------------------
+extern "C" {
+
+ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
+  if (!ctx || !cfg) return nullptr;
+  const ks_model_config& g = *cfg;
+  auto bad = [&](const char* why) -> ks_model* {
+    ks_fail(ctx, KS_ERR_INVALID, "model_create: %s", why);
+    return nullptr;
+  };
+  if (g.n_layers < 1 || g.hidden < 256 || g.hidden % 256 || g.ffn < 256 || g.ffn % 256) return bad("hidden and ffn must be positive multiples of 256");
+  if (g.n_q < 1 || g.n_kv < 1 || g.n_q % g.n_kv) return bad("n_q must be a multiple of n_kv");
+  if (g.hd != 128 && g.hd != 256) return bad("head_dim must be 128 or 256");
+  if ((g.n_q * g.hd) % 256) return bad("n_q*head_dim must be a multiple of 256");
+  if (g.vocab < 1 || g.max_seq < 1 || g.n_slots < 1 || g.n_slots > 8) return bad("vocab, max_seq >= 1 and 1 <= n_slots <= 8 required");
+  if (g.embd_dtype != KS_Q4K && g.embd_dtype != KS_Q6K) return bad("token_embd must be Q4K or Q6K");
+  if (g.act != KS_F32 && g.act != KS_F16) return bad("activation dtype must be F32 or F16");
+  if (!(g.softcap > 0.0f)) return bad("softcap must be > 0");
+  cudaSetDevice(ctx->device);
+
+  ks_model* m = new ks_model();
+  m->ctx = ctx;
+  m->cfg = g;
+  m->layers.resize(g.n_layers);
+  const size_t ab = ks_act_bytes((ks_dtype)g.act);
+  const size_t H = g.hidden, F = g.ffn, qn = (size_t)g.n_q * g.hd, kvn = (size_t)g.n_kv * g.hd;
+  // weight arena
+  size_t off = 0;
+  auto place = [&](Tensor& t, size_t bytes, const std::string& name) {
+    off = (off + 255) & ~size_t(255);
+    t.dptr = (void*)off;  // offset for now
+    t.bytes = bytes;
+    off += bytes;
+    m->by_name[name] = &t;
+  };
+  place(m->token_embd, ks_nbytes((ks_dtype)g.embd_dtype, (size_t)g.vocab * H), "token_embd.weight");
+  place(m->output_norm, H * ab, "output_norm.weight");
+  for (int l = 0; l < g.n_layers; l++) {
+    Layer& L = m->layers[l];
+    const std::string p = "blk." + std::to_string(l) + ".";
+    place(L.wq, ks_nbytes(KS_Q4K, qn * H), p + "attn_q.weight");
+    place(L.wk, ks_nbytes(KS_Q4K, kvn * H), p + "attn_k.weight");
+    place(L.wv, ks_nbytes(KS_Q4K, kvn * H), p + "attn_v.weight");
+    place(L.wo, ks_nbytes(KS_Q4K, H * qn), p + "attn_output.weight");
+    place(L.wgate, ks_nbytes(KS_Q4K, F * H), p + "ffn_gate.weight");
+    place(L.wup, ks_nbytes(KS_Q4K, F * H), p + "ffn_up.weight");
+    place(L.wdown, ks_nbytes(KS_Q4K, H * F), p + "ffn_down.weight");
+    place(L.attn_norm, H * ab, p + "attn_norm.weight");
+    place(L.q_norm, (size_t)g.hd * ab, p + "attn_q_norm.weight");
+    place(L.k_norm, (size_t)g.hd * ab, p + "attn_k_norm.weight");
+    place(L.post_attn_norm, H * ab, p + "post_attention_norm.weight");
+    place(L.ffn_norm, H * ab, p + "ffn_norm.weight");
+    place(L.post_ffw_norm, H * ab, p + "post_ffw_norm.weight");
+  }
+  m->arena_bytes = off + 256;
+  bool ok = dev_alloc(m, &m->arena, m->arena_bytes) == KS_OK;
+  if (ok)
+    for (auto& kv : m->by_name) kv.second->dptr = (char*)m->arena + (size_t)kv.second->dptr;
+
+  const size_t rowb = (size_t)g.hd / 32 * KS_Q40_BLOCK_BYTES;
+  m->slot_stride = (size_t)g.max_seq * g.n_kv * rowb;
+  m->kv_k.resize(g.n_layers);
+  m->kv_v.resize(g.n_layers);
+  for (int l = 0; ok && l < g.n_layers; l++) {
+    ok = dev_alloc(m, (void**)&m->kv_k[l], m->slot_stride * g.n_slots) == KS_OK &&
+         dev_alloc(m, (void**)&m->kv_v[l], m->slot_stride * g.n_slots) == KS_OK;
+  }
+  m->occupied.assign(g.n_slots, 0);
+  m->seq_len.assign(g.n_slots, 0);
+  const size_t S = g.n_slots;
+  ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
+       dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&
+       dev_alloc(m, &m->v, S * kvn * ab) == KS_OK && dev_alloc(m, &m->o, S * qn * ab) == KS_OK &&
+       dev_alloc(m, &m->ff, S * F * ab) == KS_OK && dev_alloc(m, &m->logits, S * (size_t)g.vocab * ab) == KS_OK &&
+       dev_alloc(m, (void**)&m->tok, 2 * S * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->pos, S * sizeof(int)) == KS_OK &&
+       dev_alloc(m, (void**)&m->meta, S * 4 * sizeof(float)) == KS_OK &&
+       dev_alloc(m, (void**)&m->rope, (size_t)g.max_seq * g.hd * sizeof(float)) == KS_OK;
+  if (ok) {
+    m->n_splits = ks_sdpa_pick_splits(ctx, 1, g.n_kv, g.max_seq);
+    ok = dev_alloc(m, (void**)&m->attn_tmp, (ks_sdpa_tmp_floats(S, g.n_q, g.hd, m->n_splits) + 4) * sizeof(float)) == KS_OK;
+  }
+  if (ok) {
+    // RoPE table: per position hd f32 = cos[hd/2] || sin[hd/2], freq_i = theta^(-2i/hd) (gemma_prim.rs:33-56)
+    std::vector<float> t((size_t)g.max_seq * g.hd);
+    const int half = g.hd / 2;
+    for (int p = 0; p < g.max_seq; p++)
+      for (int i = 0; i < half; i++) {
+        const float freq = (float)(1.0 / pow((double)g.rope_theta, (double)(2 * i) / (double)g.hd));
+        const float ang = (float)p * freq;
+        t[(size_t)p * g.hd + i] = cosf(ang);
+        t[(size_t)p * g.hd + half + i] = sinf(ang);
+      }
+    ok = cudaMemcpyAsync(m->rope, t.data(), t.size() * sizeof(float), cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
+         cudaStreamSynchronize(ctx->stream) == cudaSuccess;
+    if (!ok) ks_fail(ctx, KS_ERR_CUDA, "model_create: rope upload failed");
+  }
+  m->host_tok_n = 4096;
+  if (ok && cudaMallocHost((void**)&m->host_tok, m->host_tok_n * sizeof(float)) != cudaSuccess) {
+    ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
+    ok = false;
+  }
+  if (!ok) {
+    ks_model_destroy(m);
+    return nullptr;
+  }
+  return m;
+}
+
+void ks_model_destroy(ks_model* m) {
+  if (!m) return;
+  cudaSetDevice(m->ctx->device);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
+  for (void* p : m->owned) cudaFree(p);
+  if (m->host_tok) cudaFreeHost(m->host_tok);
+  delete m;
+}
+
+size_t ks_model_tensor_bytes(const ks_model* m, const char* name) {
+  if (!m || !name) return 0;
+  auto it = m->by_name.find(name);
+  return it == m->by_name.end() ? 0 : it->second->bytes;
+}
+
+int ks_model_upload_tensor(ks_model* m, const char* name, const void* host, size_t bytes) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, name && host, "model_upload_tensor: null argument");
+  auto it = m->by_name.find(name);
+  KS_REQUIRE(c, it != m->by_name.end(), "missing tensor %s", name);
+  KS_REQUIRE(c, bytes == it->second->bytes, "tensor %s: got %zu bytes, expected %zu", name, bytes, it->second->bytes);
+  KS_CUDA(c, cudaMemcpyAsync(it->second->dptr, host, bytes, cudaMemcpyHostToDevice, c->stream));
+  KS_CUDA(c, cudaStreamSynchronize(c->stream));
+  it->second->set = true;
+  return KS_OK;
+}
+
+const void* ks_model_tensor_ptr(const ks_model* m, const char* name) {
+  if (!m || !name) return nullptr;
+  auto it = m->by_name.find(name);
+  return it == m->by_name.end() ? nullptr : it->second->dptr;
+}
+
+size_t ks_model_weight_bytes(const ks_model* m) {
+  if (!m) return 0;
+  size_t n = 0;
+  for (auto& kv : m->by_name) n += kv.second->bytes;
+  return n;
+}
+
+// ---- slot pool (kv_pool.rs:136-230) ---------------------------------------------------------
+int ks_model_slot_alloc(ks_model* m) {
+  if (!m) return KS_ERR_INVALID;
+  for (int s = 0; s < m->cfg.n_slots; s++)
+    if (!m->occupied[s]) {
+      m->occupied[s] = 1;
+      m->seq_len[s] = 0;
+      set_state_kernel<<<1, 1, 0, m->ctx->stream>>>(s, 0, m->pos);
+      return s;
+    }
+  return ks_fail(m->ctx, KS_ERR_STATE, "KvPool full (max_batch=%d)", m->cfg.n_slots);
+}
+
+int ks_model_slot_free(ks_model* m, int slot) {
+  if (!m) return KS_ERR_INVALID;
+  if (slot < 0 || slot >= m->cfg.n_slots) return ks_fail(m->ctx, KS_ERR_STATE, "bad SlotId");
+  m->occupied[slot] = 0;
+  m->seq_len[slot] = 0;
+  return KS_OK;
+}
+
+int ks_model_slot_seq_len(const ks_model* m, int slot) {
+  if (!m || slot < 0 || slot >= m->cfg.n_slots) return KS_ERR_STATE;
+  return m->seq_len[slot];
+}
+
+int ks_model_slot_active(const ks_model* m) {
+  int n = 0;
+  if (m)
+    for (char o : m->occupied) n += o ? 1 : 0;
+  return n;
+}
+
+// Zero a slot's K/V rows and rewind it (gemma_prim.rs:1644-1656 reset, kv_pool.rs:147-160 clear_slot).
+int ks_model_slot_reset(ks_model* m, int slot) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  if (slot < 0 || slot >= m->cfg.n_slots) return ks_fail(c, KS_ERR_STATE, "bad SlotId");
+  for (int l = 0; l < m->cfg.n_layers; l++) {
+    KS_CUDA(c, cudaMemsetAsync(m->kv_k[l] + (size_t)slot * m->slot_stride, 0, m->slot_stride, c->stream));
+    KS_CUDA(c, cudaMemsetAsync(m->kv_v[l] + (size_t)slot * m->slot_stride, 0, m->slot_stride, c->stream));
+  }
+  set_state_kernel<<<1, 1, 0, c->stream>>>(slot, 0, m->pos);
+  m->seq_len[slot] = 0;
+  m->occupied[slot] = 1;
+  return ks_after_launch(c, "slot_reset");
+}
+
+static int check_ready(ks_model* m) {
+  for (auto& kv : m->by_name)
+    if (!kv.second->set) return ks_fail(m->ctx, KS_ERR_STATE, "missing tensor %s", kv.first.c_str());
+  return KS_OK;
+}
+
+static int check_slots(ks_model* m, int first, int n) {
+  ks_ctx* c = m->ctx;
+  if (first < 0 || n < 1 || first + n > m->cfg.n_slots) return ks_fail(c, KS_ERR_STATE, "bad SlotId");
+  for (int s = first; s < first + n; s++) {
+    if (!m->occupied[s]) return ks_fail(c, KS_ERR_STATE, "slot not occupied");
+    if (m->seq_len[s] >= m->cfg.max_seq) return ks_fail(c, KS_ERR_STATE, "max_seq exceeded");
+  }
+  return KS_OK;
+}
+
+// Enqueue one token for slots first..first+n-1.  tokens != NULL: ids are written from the host
+// first (decode_token_sampled, gemma_prim.rs:1622-1634); NULL: ids already on the device from the
+// previous step's argmax.  Nothing is read back and nothing waits.
+int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_logits) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  int rc;
+  if ((rc = check_ready(m)) || (rc = check_slots(m, first, n))) return rc;
+  int src = m->tok_src;
+  if (tokens) {
+    src = 0;
+    float* stage = m->host_tok + m->host_tok_n - 8;  // last 8 entries of the pinned ring stage the ids
+    KS_CUDA(c, cudaStreamSynchronize(c->stream));     // the staging words may still be in flight
+    for (int s = 0; s < n; s++) {
+      KS_REQUIRE(c, tokens[s] >= 0 && tokens[s] < m->cfg.vocab, "token id %d outside the vocabulary", tokens[s]);
+      stage[s] = (float)tokens[s];
+    }
+    KS_CUDA(c, cudaMemcpyAsync(m->tok + first, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+  }
+  if ((rc = run_forward(m, first, n, src, want_logits != 0))) return rc;
+  for (int s = first; s < first + n; s++) m->seq_len[s] += 1;
+  m->tok_src = want_logits ? (src ^ 1) : src;
+  return KS_OK;
+}
+
+// Blocking greedy step with host ids in and out: the serve path's decode_token
+// (gemma_prim.rs:1616-1635).  4*n bytes go up, 4*n bytes come back, every call.
+int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int* next) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, tokens && next, "decode_token: null argument");
+  int rc = ks_model_forward(m, first, n, tokens, 1);
+  if (rc) return rc;
+  float* back = m->host_tok;
+  KS_CUDA(c, cudaMemcpyAsync(back, m->tok + (size_t)m->tok_src * m->cfg.n_slots + first, n * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+  KS_CUDA(c, cudaStreamSynchronize(c->stream));
+  for (int s = 0; s < n; s++) next[s] = (int)back[s];
+  return KS_OK;
+}
+
+// generate_timed (gemma_prim.rs:1658-1768) for one slot: rewind, run prompt[0..n-2] without
+// logits, then n_new greedy steps starting from the last prompt token.  The token id never
+// leaves the device between steps; each step's id is copied to pinned host memory behind the
+// step and the host waits only once more than `max_inflight` steps are pending
+// (wait_inflight_at_most, gemma_prim.rs:1688-1691).  Times are host wall clock like the
+// reference's; decode_ms_device is the device time of the decode steps (CUDA events).
+int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight, int* out,
+                      ks_generate_stats* stats) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, prompt && n_prompt >= 1, "empty prompt");
+  KS_REQUIRE(c, n_new >= 0 && (size_t)n_new <= m->host_tok_n - 8, "generate: n_new out of range");
+  KS_REQUIRE(c, out || n_new == 0, "generate: null output");
+  int rc;
+  if ((rc = ks_model_slot_reset(m, slot))) return rc;
+  if (n_prompt - 1 + n_new > m->cfg.max_seq) return ks_fail(c, KS_ERR_STATE, "max_seq exceeded");
+  cudaEvent_t e0, e1, e2;
+  KS_CUDA(c, cudaEventCreate(&e0));
+  KS_CUDA(c, cudaEventCreate(&e1));
+  KS_CUDA(c, cudaEventCreate(&e2));
+  cudaEventRecord(e0, c->stream);
+  for (int i = 0; i + 1 < n_prompt; i++)
+    if ((rc = ks_model_forward(m, slot, 1, &prompt[i], 0))) return rc;
+  KS_CUDA(c, cudaStreamSynchronize(c->stream));
+  int last = prompt[n_prompt - 1];
+  cudaEventRecord(e1, c->stream);
+  std::vector<cudaEvent_t> done;
+  if (max_inflight < 0) max_inflight = 0;
+  for (int i = 0; i < n_new; i++) {
+    if ((rc = ks_model_forward(m, slot, 1, i == 0 ? &last : nullptr, 1))) return rc;
+    KS_CUDA(c, cudaMemcpyAsync(m->host_tok + i, m->tok + (size_t)m->tok_src * m->cfg.n_slots + slot, sizeof(float),
+                               cudaMemcpyDeviceToHost, c->stream));
+    cudaEvent_t ev;
+    KS_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    cudaEventRecord(ev, c->stream);
+    done.push_back(ev);
+    const int wait_upto = i - max_inflight;  // steps <= this index must have finished
+    if (wait_upto >= 0) KS_CUDA(c, cudaEventSynchronize(done[wait_upto]));
+  }
+  cudaEventRecord(e2, c->stream);
+  KS_CUDA(c, cudaStreamSynchronize(c->stream));
+  for (cudaEvent_t ev : done) cudaEventDestroy(ev);
+  for (int i = 0; i < n_new; i++) out[i] = (int)m->host_tok[i];
+  if (stats) {
+    float a = 0, b = 0;
+    cudaEventElapsedTime(&a, e0, e1);
+    cudaEventElapsedTime(&b, e1, e2);
+    stats->prefill_tokens = n_prompt - 1;
+    stats->decode_tokens = n_new;
+    stats->prefill_ms_device = a;
+    stats->decode_ms_device = b;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaEventDestroy(e2);
+  return KS_OK;
+}
+
+// Device pointers of the slot's activations, for tests: 0 = residual x, 1 = logits.
+const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
+  if (!m || slot < 0 || slot >= m->cfg.n_slots) return nullptr;
+  const size_t ab = ks_act_bytes((ks_dtype)m->cfg.act);
+  if (which == 0) return (const char*)m->x + (size_t)slot * m->cfg.hidden * ab;
+  if (which == 1) return (const char*)m->logits + (size_t)slot * m->cfg.vocab * ab;
+  return nullptr;
+}
+
+}  // extern "C"

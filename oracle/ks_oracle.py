@@ -278,17 +278,21 @@ class _Model(C.Structure):
     ]
 
 
-_LAYER_FIELDS = ["wq", "wk", "wv", "wo", "wgate", "wup", "wdown", "attn_norm", "q_norm", "k_norm",
-                 "post_attn_norm", "ffn_norm", "post_ffw_norm"]
+# struct field -> GGUF tensor suffix (crates/ksearch_gemma/src/gemma_prim.rs:174-181, 356-357)
+_LAYER_FIELDS = {"wq": "attn_q.weight", "wk": "attn_k.weight", "wv": "attn_v.weight", "wo": "attn_output.weight",
+                 "wgate": "ffn_gate.weight", "wup": "ffn_up.weight", "wdown": "ffn_down.weight",
+                 "attn_norm": "attn_norm.weight", "q_norm": "attn_q_norm.weight", "k_norm": "attn_k_norm.weight",
+                 "post_attn_norm": "post_attention_norm.weight", "ffn_norm": "ffn_norm.weight",
+                 "post_ffw_norm": "post_ffw_norm.weight"}
 
 
 class CpuDecoder:
     """CPU fp32 decoder over the same packed tensors the CUDA model is given.
 
     ``cfg``: dict with n_layers, hidden, ffn, n_q, n_kv, hd, vocab, max_seq, eps,
-    rope_theta, softcap, attn_scale, embd_dtype.  ``tensors``: name -> ndarray
-    (``token_embd``, ``output_norm``, ``blk.{l}.<field>``); packed weights uint8,
-    norm weights float32.
+    rope_theta, softcap, attn_scale, embd_dtype.  ``tensors``: GGUF tensor name ->
+    ndarray (``token_embd.weight``, ``output_norm.weight``, ``blk.N.attn_q.weight`` ...);
+    packed weights uint8, norm weights float32.
     """
 
     def __init__(self, cfg: dict, tensors: dict, fast: bool = False):
@@ -305,11 +309,11 @@ class CpuDecoder:
             self._keep.append(a)
             return a.ctypes.data
 
-        m.token_embd = hold(tensors["token_embd"], np.uint8)
-        m.output_norm = hold(tensors["output_norm"], np.float32)
-        for f in _LAYER_FIELDS:
+        m.token_embd = hold(tensors["token_embd.weight"], np.uint8)
+        m.output_norm = hold(tensors["output_norm.weight"], np.float32)
+        for f, suffix in _LAYER_FIELDS.items():
             dt = np.uint8 if f.startswith("w") else np.float32
-            arr = (C.c_void_p * m.n_layers)(*[hold(tensors[f"blk.{l}.{f}"], dt) for l in range(m.n_layers)])
+            arr = (C.c_void_p * m.n_layers)(*[hold(tensors[f"blk.{l}.{suffix}"], dt) for l in range(m.n_layers)])
             self._keep.append(arr)
             setattr(m, f, C.cast(arr, C.c_void_p))
         self._m = m
@@ -332,15 +336,15 @@ class CpuDecoder:
         return np.ctypeslib.as_array(self._L.kso_state_hidden(self._s), shape=(self.cfg["hidden"],)).copy()
 
     def generate(self, prompt, n_new: int):
+        """gemma_prim.rs:1658-1768: prompt[:-1] without logits, then n_new greedy steps from prompt[-1]."""
         self.reset()
-        tok = 0
-        for i, t in enumerate(prompt):
-            tok = self.forward_token(int(t), want_logits=(i == len(prompt) - 1))
+        for t in prompt[:-1]:
+            self.forward_token(int(t), want_logits=False)
+        tok = int(prompt[-1])
         out = []
-        for i in range(n_new):
+        for _ in range(n_new):
+            tok = self.forward_token(tok, True)
             out.append(tok)
-            if i + 1 < n_new:
-                tok = self.forward_token(tok, True)
         return out
 
     def close(self):

@@ -73,7 +73,6 @@ def test_matvec_reference_patterns(ctx, oracle):
         Eng().matvec_batch(ctx, rows, cols, batch, Q4K, ctx.buffer_bytes(wq), ctx.buffer_bytes(x), by)
         got = ctx.read_f32(by, batch * rows).reshape(batch, rows)
         _check(got, y32, y64, f"pattern {rows}x{cols}x{batch}")
-        assert np.abs(got - x.astype(np.float64) @ w.astype(np.float64).T).max() < 0.05 * np.sqrt(cols)
 
 
 @pytest.mark.parametrize("dtype", [Q4K, Q6K])

@@ -1,0 +1,141 @@
+"""GPU parity of the decode driver against the CPU fp32 decoder on seeded synthetic models."""
+import numpy as np
+import pytest
+
+from ksearch_b200 import F16, F32, KsError, synth
+from ksearch_b200 import model as ksm
+
+pytestmark = pytest.mark.gpu
+
+
+def _teacher_forced(model, cpu, tokens, slot=0):
+    """Same token sequence through both; compare the logits of every step."""
+    model.slot_reset(slot)
+    cpu.reset()
+    worst = 0.0
+    for t in tokens:
+        model.forward(slot, 1, [int(t)], True)
+        model.ctx.synchronize()
+        got = model.read_debug(1, slot).astype(np.float64)
+        cpu.forward_token(int(t), True)
+        want = cpu.logits().astype(np.float64)
+        scale = np.abs(want).max()
+        err = np.abs(got - want).max()
+        worst = max(worst, err / scale)
+        assert err <= 5e-3 * scale, f"logits differ: {err} on scale {scale}"
+    return worst
+
+
+@pytest.mark.parametrize("n_kv", [1, 2])
+def test_tiny_model_matches_cpu_decoder(ctx, oracle, n_kv):
+    cfg = ksm.tiny_config(max_seq=48, n_kv=n_kv)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=9, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    toks = synth.token_ids(9, "tf", 20, cfg.vocab)
+    _teacher_forced(model, cpu, toks)
+    prompt = synth.token_ids(9, "prompt", 8, cfg.vocab)
+    out, st = model.generate_timed(prompt, 24)
+    assert len(out) == 24 and st.decode_tokens == 24 and st.prefill_tokens == 7
+    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    assert equal + ties == 24 and ties <= 1
+    assert model.seq_len(0) == 7 + 24
+    # generate again: the slot is rewound and the stream repeats exactly
+    out2, _ = model.generate_timed(prompt, 24, max_inflight=0)
+    assert out2 == out
+    # the blocking host-token path gives the same stream
+    model.slot_reset(0)
+    for t in prompt[:-1]:
+        model.forward(0, 1, [int(t)], False)
+    tok, step = int(prompt[-1]), []
+    for _ in range(6):
+        tok = model.decode_token([tok])[0]
+        step.append(tok)
+    assert step == out[:6]
+    cpu.close()
+    model.close()
+
+
+def test_slots_advance_together(ctx, oracle):
+    """Four slots with different histories step through one weight pass; each matches its own
+    single-slot CPU run (the reference serves slots serially, scheduler.rs:163-231)."""
+    cfg = ksm.tiny_config(max_seq=32, n_slots=4)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=10, keep=True)
+    slots = [model.slot_alloc() for _ in range(4)]
+    assert slots == [0, 1, 2, 3] and model.active_batch() == 4
+    with pytest.raises(KsError, match="KvPool full"):
+        model.slot_alloc()
+    lens = [3, 9, 1, 6]
+    seqs = [synth.token_ids(10, f"s{s}", lens[s] + 5, cfg.vocab) for s in range(4)]
+    for s in range(4):                      # different prompt lengths, slot by slot
+        for t in seqs[s][:lens[s]]:
+            model.forward(s, 1, [int(t)], False)
+    want_logits = []
+    for s in range(4):
+        cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+        for t in seqs[s][:lens[s]]:
+            cpu.forward_token(int(t), False)
+        rows = []
+        for j in range(5):
+            cpu.forward_token(int(seqs[s][lens[s] + j]), True)
+            rows.append(cpu.logits().astype(np.float64))
+        want_logits.append(rows)
+        cpu.close()
+    for j in range(5):                      # five batched steps over all four slots
+        model.forward(0, 4, [int(seqs[s][lens[s] + j]) for s in range(4)], True)
+        model.ctx.synchronize()
+        for s in range(4):
+            got = model.read_debug(1, s).astype(np.float64)
+            want = want_logits[s][j]
+            assert np.abs(got - want).max() <= 5e-3 * np.abs(want).max(), (j, s)
+    assert [model.seq_len(s) for s in range(4)] == [l + 5 for l in lens]
+    model.slot_free(1)
+    assert model.active_batch() == 3 and model.slot_alloc() == 1       # reuses the freed slot (KV:232-249)
+    model.close()
+
+
+def test_model_errors(ctx):
+    cfg = ksm.tiny_config(max_seq=4)
+    m = ksm.GemmaCudaModel(ctx, cfg)
+    m.slot_alloc()
+    with pytest.raises(KsError, match="missing tensor"):
+        m.forward(0, 1, [1], True)
+    with pytest.raises(KsError, match="missing tensor"):
+        m.upload_tensor("blk.99.attn_q.weight", np.zeros(4, np.uint8))
+    with pytest.raises(KsError, match="expected"):
+        m.upload_tensor("output_norm.weight", np.zeros(3, np.float32))
+    m.close()
+    m, _ = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=1, keep=True)
+    with pytest.raises(KsError, match="slot not occupied"):
+        m.forward(0, 1, [1], True)
+    m.slot_alloc()
+    for t in range(4):
+        m.forward(0, 1, [t], False)
+    with pytest.raises(KsError, match="max_seq exceeded"):
+        m.forward(0, 1, [1], False)
+    with pytest.raises(KsError, match="vocabulary"):
+        m.slot_reset(0) or m.forward(0, 1, [cfg.vocab], False)
+    with pytest.raises(KsError, match="empty prompt"):
+        m.generate_timed([], 1)
+    m.close()
+    bad = ksm.tiny_config()
+    bad.hd = 96
+    with pytest.raises(KsError, match="head_dim"):
+        ksm.GemmaCudaModel(ctx, bad)
+
+
+def test_f16_activation_model_runs_close(ctx, oracle):
+    """The reference's activation dtype (f16 in/out of every op, f32 accumulation)."""
+    cfg = ksm.tiny_config(max_seq=16, act=F16)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=11, keep=True)
+    model.slot_alloc()
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    toks = synth.token_ids(11, "tf", 6, cfg.vocab)
+    for t in toks:
+        model.forward(0, 1, [int(t)], True)
+        cpu.forward_token(int(t), True)
+    model.ctx.synchronize()
+    got, want = model.read_debug(1, 0).astype(np.float64), cpu.logits().astype(np.float64)
+    assert np.abs(got - want).max() <= 0.05 * np.abs(want).max()
+    cpu.close()
+    model.close()
