@@ -119,7 +119,7 @@ def run_reference(args, rank, world):
     # scales with streamed bytes, so tok/s(full) = tok/s(sample) * bytes(sample) / bytes(full).
     budget_s = 150.0
     ls = 2
-    cfg = ksm.e2b_config(max_seq=PROMPT_LEN + 8)
+    cfg = ksm.e2b_config(max_seq=args.steps + args.warmup + 8)
     cfg.n_layers = ls
     cfg.vocab = max(256, full.vocab * ls // full.n_layers // 256 * 256)
     T = ksm.synth_tensors(cfg, SEED)
@@ -245,7 +245,7 @@ def cpu_baseline(cfg_full):
     """Oracle CPU decoder on a bounded sample of the same workload."""
     from ksearch_b200 import model as ksm
     from oracle import ks_oracle
-    cfg = ksm.e2b_config(max_seq=16)
+    cfg = ksm.e2b_config(max_seq=80)
     ls = 2
     cfg.n_layers = ls
     cfg.vocab = cfg_full.vocab * ls // cfg_full.n_layers // 256 * 256

@@ -166,11 +166,8 @@ __device__ __forceinline__ void pack_q40_warp(float v, uint8_t* blk, int lane) {
   q = q < 0 ? 0 : q > 15 ? 15 : q;
   const int qhi = __shfl_down_sync(0xffffffffu, q, 16);
   if (lane < 16) blk[2 + lane] = (uint8_t)(q | (qhi << 4));
-  if (lane == 0) {
-    const unsigned short hs = __half_as_ushort(__float2half_rn(scale));
-    blk[0] = (uint8_t)(hs & 0xFF);
-    blk[1] = (uint8_t)(hs >> 8);
-  }
+  // Q4_0 blocks are 18 bytes on an even base, so the fp16 scale is one aligned 16-bit store
+  if (lane == 0) *reinterpret_cast<__half*>(blk) = __float2half_rn(scale);
 }
 
 template <typename T>
@@ -489,6 +486,7 @@ int ks_quantize_q40(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* src, size
   const size_t ab = ks_act_bytes(act);
   KS_REQUIRE(ctx, ks_fits(src, src_off * ab, n * ab), "quantize_q40: source buffer too small");
   KS_REQUIRE(ctx, ks_fits(dst, dst_byte_off, n / 32 * KS_Q40_BLOCK_BYTES), "quantize_q40: destination buffer too small");
+  KS_REQUIRE(ctx, dst_byte_off % 2 == 0, "quantize_q40: odd destination byte offset");
   if (n == 0) return KS_OK;
   const size_t nblocks = n / 32;
   size_t grid = (nblocks + 7) / 8;
