@@ -214,6 +214,13 @@ int ks_synchronize(ks_ctx* c) {
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
   for (cudaEvent_t ev : c->inflight) cudaEventDestroy(ev);
   c->inflight.clear();
+  // a kernel whose bounded wait gave up leaves a mark instead of hanging
+  unsigned flag = 0;
+  KS_CUDA(c, cudaMemcpy(&flag, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof flag, cudaMemcpyDeviceToHost));
+  if (flag) {
+    cudaMemset((unsigned*)c->ws + KS_WS_ERR_WORD, 0, sizeof flag);
+    return ks_fail(c, KS_ERR_TIMEOUT, "a device-side wait gave up (status word 0x%x)", flag);
+  }
   return KS_OK;
 }
 

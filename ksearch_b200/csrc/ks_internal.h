@@ -89,6 +89,14 @@ typedef ks_plan ks_mv_plan;
 int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi,
                      size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan);
 
+// variant (plan->variant & 0xFF): 0 = streamed through the bulk-copy engine, 1 = direct register loads
+int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi, size_t cols,
+                                ks_dtype act, const void* x, int n_tok, const ks_plan* plan);
+int ks_launch_matvec_stream_q6k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x,
+                                int n_tok, const ks_plan* plan);   // returns 1 when the shape must use the direct kernel
+// Device error word raised by a kernel whose bounded wait gave up (index into ctx->ws, in words).
+#define KS_WS_ERR_WORD 4000
+
 int ks_launch_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const void* x, const void* w,
                       const void* res, int has_scale, float scale, void* y);
 int ks_launch_rmsnorm_add_then_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const void* y,

@@ -1,0 +1,83 @@
+"""Runs one op of the decode path a few times on seeded inputs: the small, self-ending case that
+profiler captures are taken on.
+
+    python -m ksearch_b200.profile_case matvec --dtype q4k --rows 4096 --cols 4096 --copies 16 --iters 2
+    python -m ksearch_b200.profile_case gate_up --rows 6144 --cols 1536 --copies 16 --iters 2
+    python -m ksearch_b200.profile_case decode --layers 4 --tokens 4
+
+`--copies` distinct weight copies are cycled so that a launch never finds its weights in L2
+(copies * matrix bytes should exceed the 126 MB L2).  Prints the CUDA-event time per launch.
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+from . import Q4K, Q6K, CudaContext, Eng, synth
+from . import model as ksm
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["matvec", "gate_up", "decode"])
+    ap.add_argument("--dtype", default="q4k", choices=["q4k", "q6k"])
+    ap.add_argument("--rows", type=int, default=4096)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--copies", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--tokens", type=int, default=4)
+    ap.add_argument("--pdl", type=int, default=0)
+    args = ap.parse_args()
+    ctx = CudaContext(0, flags=args.pdl)
+    eng = Eng()
+    if args.op == "decode":
+        cfg = ksm.e2b_config(max_seq=64)
+        cfg.n_layers = args.layers
+        cfg.vocab = 32768
+        m = ksm.GemmaCudaModel.synthetic(ctx, cfg, 7)
+        m.slot_alloc()
+        m.forward(0, 1, [3], True)
+        ctx.synchronize()
+        ctx.timer_begin()
+        for _ in range(args.tokens):
+            m.forward(0, 1, None, True)
+        ms = ctx.timer_end_ms()
+        print(f"decode: {ms / args.tokens * 1e3:.1f} us/token over {args.tokens} tokens ({args.layers} layers, vocab {cfg.vocab})")
+        return
+    dt = Q4K if args.dtype == "q4k" else Q6K
+    gen = synth.q4k_matrix if dt == Q4K else synth.q6k_matrix
+    one = gen(1, "w", args.rows, args.cols)
+    n_mat = 2 if args.op == "gate_up" else 1
+    big = ctx.buffer_empty_bytes(one.nbytes * args.copies * n_mat)
+    for c in range(args.copies * n_mat):
+        ctx.write_buffer(big, one, c * one.nbytes)
+    x = ctx.buffer_bytes(synth.normals(1, "x", args.cols))
+    y = ctx.buffer_empty_f32(args.rows)
+    lib = ctx.lib
+    bufs = [lib.ks_buf_wrap(ctx.h, big.ptr + c * one.nbytes, one.nbytes) for c in range(args.copies * n_mat)]
+
+    def launch(c):
+        if args.op == "gate_up":
+            ctx.check(lib.ks_matvec_gate_up_gelu(ctx.h, args.rows, args.cols, dt, bufs[2 * c], bufs[2 * c + 1], 0, x.h, y.h))
+        else:
+            ctx.check(lib.ks_matvec(ctx.h, args.rows, args.cols, dt, bufs[c], 0, 0, x.h, 0, y.h, 0, 1))
+
+    for c in range(args.copies):   # first touch
+        launch(c)
+    ctx.synchronize()
+    ctx.timer_begin()
+    n = 0
+    for _ in range(args.iters):
+        for c in range(args.copies):
+            launch(c)
+            n += 1
+    ms = ctx.timer_end_ms()
+    nbytes = one.nbytes * n_mat + 4 * (args.rows + args.cols)
+    print(f"{args.op} {args.dtype} {args.rows}x{args.cols}: {ms / n * 1e3:.2f} us/launch (host-paced), "
+          f"{nbytes / (ms / n) / 1e6:.0f} GB/s algorithmic")
+
+
+if __name__ == "__main__":
+    main()
