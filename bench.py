@@ -291,10 +291,11 @@ def main():
     from ksearch_b200 import model as ksm
     from ksearch_b200 import synth
     peak, peak_kind = measured_peak()
-    ctx = CudaContext(local)
+    ctx = CudaContext(local, flags=1)  # bit 0: programmatic dependent launch
     lib = ctx.lib
     cfg = ksm.e2b_config(max_seq=PROMPT_LEN + args.steps * 2 + args.warmup * 2 + 16)
     model = ksm.GemmaCudaModel.synthetic(ctx, cfg, SEED + rank)
+    plans_found = model.warm_plans(1)   # load-time plan search / per-chip cache, outside every timed region
     slot = model.slot_alloc()
     prompt = synth.token_ids(SEED + rank, "prompt", PROMPT_LEN, cfg.vocab)
 

@@ -99,7 +99,7 @@ void ks_graph_free(ks_ctx* ctx, ks_graph* g);
  * crates/ksearch_ir/src/kernel.rs:11-54, retargeted to the knobs of the hand-written matvec
  * kernels.  A zero field means "kernel default". */
 typedef struct {
-  int variant;      /* kernel family member (0 = default) */
+  int variant;      /* bits 0-7 kernel family (0 streamed, 1 direct loads), 8-15 pipeline stages, 16-23 blocks per column segment (0 = auto) */
   int nr;           /* rows kept in flight per lane group (nr0) */
   int nwarps;       /* warps per block (nsg) */
   int ctas_per_sm;  /* grid = min(tiles, SMs * ctas_per_sm) */
@@ -108,6 +108,20 @@ typedef struct {
 /* Force every matvec launch of this context to use *plan (NULL clears): how the search times
  * a candidate through the ordinary op path (K:2015-2031). */
 int ks_plan_override(ks_ctx* ctx, const ks_plan* plan);
+/* Plan table of the context, keyed by (op, rows, cols, n_tok); op is "mv_q4k", "mv_q6k", "gu_q4k"
+ * (gate||up, rows of one matrix) or "qkv_q4k" (rows = q_rows + 2*kv_rows).  plan_plan == NULL erases. */
+int ks_plan_set(ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok, const ks_plan* plan);
+int ks_plan_get(const ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok, ks_plan* out);
+/* CG:178-246 beam_search_matvec + K:1985 Eng::beam_matvec: use the cached plan of this chip if there is
+ * one, else time every candidate (beam.rs:26-65) on synthetic weights, keep and cache the fastest.
+ * Allocates scratch: call at load time, not on the decode path.  kv_rows only for "qkv_*". */
+int ks_plan_search(ks_ctx* ctx, const char* op, size_t rows, size_t kv_rows, size_t cols, int n_tok, ks_plan* best);
+int ks_plan_candidates(const char* op, ks_plan* out, int max_out);     /* beam.rs:26-65 */
+/* The on-disk plan cache (beam.rs:67-139, plan_cache.rs:9-38): <dir>/<key>_<hash(key,chip)>.txt holding
+ * k=v lines.  dir == NULL: $KSEARCH_BEAM_CACHE or ~/.cache/ksearch/beam.  No GPU needed. */
+int ks_plan_file_name(const char* key, const char* chip, char* out, size_t out_len);
+int ks_plan_file_save(const char* dir, const char* key, const char* chip, const ks_plan* plan);
+int ks_plan_file_load(const char* dir, const char* key, const char* chip, ks_plan* plan);
 
 /* ---- dequant test hook: GG:577-794 dequant_blocks (Q4_0 / Q4_K / Q6_K) --- */
 int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_off, size_t nelem,
@@ -127,6 +141,22 @@ int ks_matvec_qkv(ks_ctx* ctx, size_t q_rows, size_t kv_rows, size_t cols, ks_dt
 /* K:953 matvec_gate_up_gelu_wd: out[i] = gelu_tanh(clamp(Wg[i].x, +-20)) * (Wu[i].x). */
 int ks_matvec_gate_up_gelu(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* Wg,
                            const ks_buf* Wu, ks_dtype act, const ks_buf* x, ks_buf* y);
+/* RMSNorm fused into the matvec that follows it: K:278 rmsnorm_matvec_wd, K:379 rmsnorm_matvec_qkv_wds,
+ * K:1004 rmsnorm_matvec_gate_up_gelu_wd.  The matvec applies x2 = (x*rsqrt(mean(x^2)+eps))*w_norm while
+ * it stages its input (Q4K weights, cols <= 4096).  When y_prev != NULL the residual update of K:539 is
+ * fused in front as well: x' = x + rms(y_prev)*w_post is written to out_x (which must not alias x) and
+ * the norm is taken of x'.  y_prev, w_post, out_x are NULL together. */
+int ks_rmsnorm_matvec(ks_ctx* ctx, size_t rows, size_t cols, float eps, ks_dtype wdtype, ks_dtype act, const ks_buf* x,
+                      const ks_buf* w_norm, const ks_buf* W, ks_buf* y, const ks_buf* y_prev, const ks_buf* w_post,
+                      ks_buf* out_x);
+int ks_rmsnorm_matvec_qkv(ks_ctx* ctx, size_t q_rows, size_t kv_rows, size_t cols, float eps, ks_dtype wdtype,
+                          ks_dtype act, const ks_buf* x, const ks_buf* w_norm, const ks_buf* Wq, const ks_buf* Wk,
+                          const ks_buf* Wv, ks_buf* q, ks_buf* k, ks_buf* v, const ks_buf* y_prev,
+                          const ks_buf* w_post, ks_buf* out_x);
+int ks_rmsnorm_matvec_gate_up_gelu(ks_ctx* ctx, size_t rows, size_t cols, float eps, ks_dtype wdtype, ks_dtype act,
+                                   const ks_buf* x, const ks_buf* w_norm, const ks_buf* Wg, const ks_buf* Wu, ks_buf* y,
+                                   const ks_buf* y_prev, const ks_buf* w_post, ks_buf* out_x);
+
 /* Blocking convenience for callers that hold HOST memory: copies x up, runs
  * ks_matvec, copies y back.  W must already be resident (a ks_buf). */
 int ks_matvec_host(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* W, size_t w_byte_off,
@@ -199,6 +229,7 @@ typedef struct {              /* GenerateStats (crates/ksearch_gemma/src/lib.rs:
 
 ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg);          /* GP:135-413 load, minus the GGUF file */
 void ks_model_destroy(ks_model* m);
+int ks_model_warm_plans(ks_model* m, int n_tok);                             /* GP:254-290 BEAM warm at load; returns plans found */
 /* Tensor names are the GGUF names the reference loads (GP:149-183, 356-357): token_embd.weight,
  * output_norm.weight, blk.N.{attn_q,attn_k,attn_v,attn_output,ffn_gate,ffn_up,ffn_down}.weight (Q4_K),
  * blk.N.{attn_norm,attn_q_norm,attn_k_norm,post_attention_norm,ffn_norm,post_ffw_norm}.weight (act dtype). */

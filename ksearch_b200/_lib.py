@@ -51,10 +51,20 @@ SIGNATURES = {
     "ks_graph_launch": (_i, [_vp, _vp]),
     "ks_graph_free": (None, [_vp, _vp]),
     "ks_plan_override": (_i, [_vp, _vp]),
+    "ks_plan_set": (_i, [_vp, C.c_char_p, _sz, _sz, _i, _vp]),
+    "ks_plan_get": (_i, [_vp, C.c_char_p, _sz, _sz, _i, _vp]),
+    "ks_plan_search": (_i, [_vp, C.c_char_p, _sz, _sz, _sz, _i, _vp]),
+    "ks_plan_candidates": (_i, [C.c_char_p, _vp, _i]),
+    "ks_plan_file_name": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _sz]),
+    "ks_plan_file_save": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _vp]),
+    "ks_plan_file_load": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _vp]),
     "ks_dequant": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _sz]),
     "ks_matvec": (_i, [_vp, _sz, _sz, _i, _vp, _sz, _i, _vp, _sz, _vp, _sz, _i]),
     "ks_matvec_qkv": (_i, [_vp, _sz, _sz, _sz, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "ks_matvec_gate_up_gelu": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _vp, _vp]),
+    "ks_rmsnorm_matvec": (_i, [_vp, _sz, _sz, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ks_rmsnorm_matvec_qkv": (_i, [_vp, _sz, _sz, _sz, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ks_rmsnorm_matvec_gate_up_gelu": (_i, [_vp, _sz, _sz, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ks_matvec_host": (_i, [_vp, _sz, _sz, _i, _vp, _sz, _vp, _vp, _i]),
     "ks_rmsnorm": (_i, [_vp, _sz, _sz, _f, _i, _vp, _sz, _vp, _vp, _sz, _i, _f, _vp, _sz]),
     "ks_rmsnorm_add_then_rmsnorm": (_i, [_vp, _sz, _sz, _f, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -68,6 +78,7 @@ SIGNATURES = {
     "ks_gelu_mul": (_i, [_vp, _sz, _i, _vp, _vp, _vp]),
     "ks_model_create": (_vp, [_vp, _vp]),
     "ks_model_destroy": (None, [_vp]),
+    "ks_model_warm_plans": (_i, [_vp, _i]),
     "ks_model_tensor_bytes": (_sz, [_vp, C.c_char_p]),
     "ks_model_upload_tensor": (_i, [_vp, C.c_char_p, _vp, _sz]),
     "ks_model_tensor_ptr": (_vp, [_vp, C.c_char_p]),

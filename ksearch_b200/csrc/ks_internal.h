@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <deque>
+#include <map>
 #include <string>
 
 #include "../../include/ksearch_cuda.h"
@@ -24,6 +25,7 @@ struct ks_ctx {
   cudaEvent_t t0 = nullptr, t1 = nullptr;  // stopwatch
   bool has_override = false;
   ks_plan override_plan{};
+  std::map<std::string, ks_plan> plans;  // op_rowsxcols[_bN] -> plan (searched, loaded or set)
   void* ws = nullptr;  // small zero-initialised device workspace (cross-block reductions)
   // pinned staging for the *_host convenience calls
   void* stage_h = nullptr;
@@ -82,16 +84,33 @@ struct ks_mv_seg {   // one weight matrix of a fused matvec launch
 
 enum ks_mv_epilogue { KS_EPI_PLAIN = 0, KS_EPI_GATE_UP = 1 };
 
+// Input prologue fused into a matvec (see ks_mv_common.cuh): none, RMSNorm, or
+// residual-add-then-RMSNorm.  out_x must not alias the residual input.
+enum { KS_PRO_NONE = 0, KS_PRO_NORM = 1, KS_PRO_ADD_NORM = 2 };
+struct ks_mv_pro {
+  int mode;
+  float eps;
+  const void* w;       // norm weight applied last (w or w_next)
+  const void* y;       // ADD_NORM: the vector that is normed and added
+  const void* w_post;  // ADD_NORM: its weight
+  void* out_x;         // ADD_NORM: new residual stream (written by block 0)
+};
+
 // Launch tuning knobs of the matvec kernels (the planner's vocabulary, after
 // OptSchedule in crates/ksearch_ir/src/kernel.rs:11-54).  Zero = default.
 typedef ks_plan ks_mv_plan;
 
 int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi,
-                     size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan);
+                     size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan,
+                     const ks_mv_pro* pro = nullptr);
+std::string ks_plan_key(const char* op, size_t rows, size_t cols, int n_tok);
+const ks_plan* ks_plan_lookup(const ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok);
+// True when a prologue can be fused for this shape (streamed Q4_K kernel, cols <= 4096, even block count).
+bool ks_matvec_can_fuse_pro(ks_dtype wdtype, size_t cols);
 
 // variant (plan->variant & 0xFF): 0 = streamed through the bulk-copy engine, 1 = direct register loads
 int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi, size_t cols,
-                                ks_dtype act, const void* x, int n_tok, const ks_plan* plan);
+                                ks_dtype act, const void* x, int n_tok, const ks_plan* plan, const ks_mv_pro* pro);
 int ks_launch_matvec_stream_q6k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x,
                                 int n_tok, const ks_plan* plan);   // returns 1 when the shape must use the direct kernel
 // Device error word raised by a kernel whose bounded wait gave up (index into ctx->ws, in words).
@@ -112,3 +131,34 @@ int ks_launch_sdpa(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t 
 int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype,
                                  const void* src, const float* idx, ks_dtype act, void* dst);
 int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);
+
+// ---- programmatic dependent launch --------------------------------------------------------------
+// Every kernel of the library is launched through ks_launch_k.  When the context was created with
+// flag bit 0, the launch carries the programmatic-stream-serialization attribute: the kernel may
+// start while its predecessor in the stream still runs.  Each kernel therefore calls
+// ks_pdl_entry() (or, for the streamed matvec, issues its weight copies first) before it touches
+// anything a predecessor writes; griddepcontrol.wait returns at once when the launch carried no
+// such attribute.
+#ifdef __CUDACC__
+#include <utility>
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ks_launch_k(ks_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+#define KS_LAUNCH(ctx, kern, grid, block, smem, ...) (void)ks_launch_k((ctx), kern, dim3(grid), dim3(block), (smem), __VA_ARGS__)
+// Let the next kernel in the stream start, then wait until everything before this kernel is done.
+static __device__ __forceinline__ void ks_pdl_entry() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif

@@ -308,8 +308,10 @@ int launch_q6k_nt(ks_ctx* ctx, const MvArgs& a, int grid, int threads, size_t sm
 
 }  // namespace
 
+bool ks_matvec_can_fuse_pro(ks_dtype wdtype, size_t cols) { return wdtype == KS_Q4K && cols % 256 == 0 && cols <= 4096; }
+
 int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi,
-                     size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan) {
+                     size_t cols, ks_dtype act, const void* x, int n_tok, const ks_mv_plan* plan, const ks_mv_pro* pro) {
   KS_REQUIRE(ctx, wdtype == KS_Q4K || wdtype == KS_Q6K, "matvec: weight dtype %d not supported (Q4K, Q6K)", (int)wdtype);
   KS_REQUIRE(ctx, ks_is_act(act), "matvec: activation dtype must be F32 or F16");
   KS_REQUIRE(ctx, n_seg >= 1 && n_seg <= 3, "matvec: 1..3 weight segments");
@@ -323,9 +325,22 @@ int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_
     KS_REQUIRE(ctx, ((uintptr_t)segs[s].W & (wdtype == KS_Q4K ? 15 : 1)) == 0, "matvec: weight pointer misaligned");
   }
 
-  if (ctx->has_override) plan = &ctx->override_plan;
+  if (ctx->has_override) {
+    plan = &ctx->override_plan;
+  } else if (!plan && !ctx->plans.empty()) {
+    // the planner's table: op_rowsxcols[_bN]
+    size_t total = 0;
+    for (int s = 0; s < n_seg; s++) total += segs[s].rows;
+    const char* op = epi == KS_EPI_GATE_UP ? "gu_q4k" : n_seg == 3 ? (wdtype == KS_Q4K ? "qkv_q4k" : "qkv_q6k")
+                                                                  : (wdtype == KS_Q4K ? "mv_q4k" : "mv_q6k");
+    plan = ks_plan_lookup(ctx, op, epi == KS_EPI_GATE_UP ? segs[0].rows : total, cols, n_tok);
+  }
+  if (pro && pro->mode != KS_PRO_NONE) {
+    KS_REQUIRE(ctx, ks_matvec_can_fuse_pro(wdtype, cols), "matvec: no fused norm prologue for dtype %d, cols=%zu", (int)wdtype, cols);
+    return ks_launch_matvec_stream_q4k(ctx, segs, n_seg, epi, cols, act, x, n_tok, plan, pro);
+  }
   if (wdtype == KS_Q4K && (!plan || (plan->variant & 0xFF) == 0))
-    return ks_launch_matvec_stream_q4k(ctx, segs, n_seg, epi, cols, act, x, n_tok, plan);
+    return ks_launch_matvec_stream_q4k(ctx, segs, n_seg, epi, cols, act, x, n_tok, plan, nullptr);
   if (wdtype == KS_Q6K && (!plan || (plan->variant & 0xFF) == 0)) {
     const int rc = ks_launch_matvec_stream_q6k(ctx, segs, n_seg, cols, act, x, n_tok, plan);
     if (rc != 1) return rc;
@@ -482,6 +497,76 @@ int ks_matvec_gate_up_gelu(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtyp
   KS_REQUIRE(ctx, ks_fits(y, 0, rows * ab), "matvec_gate_up_gelu: y buffer too small");
   ks_mv_seg segs[2] = {{(const uint8_t*)Wg->dptr, y->dptr, (unsigned)rows}, {(const uint8_t*)Wu->dptr, y->dptr, (unsigned)rows}};
   return ks_launch_matvec(ctx, wdtype, segs, 2, KS_EPI_GATE_UP, cols, act, x->dptr, 1, nullptr);
+}
+
+// Validates the fused-norm operands and fills the prologue descriptor.
+static int make_pro(ks_ctx* ctx, const char* what, size_t cols, float eps, ks_dtype wdtype, ks_dtype act, const ks_buf* x,
+                    const ks_buf* w_norm, const ks_buf* y_prev, const ks_buf* w_post, ks_buf* out_x, ks_mv_pro* pro) {
+  KS_REQUIRE(ctx, ks_is_act(act), "%s: activation dtype must be F32 or F16", what);
+  KS_REQUIRE(ctx, ks_matvec_can_fuse_pro(wdtype, cols), "%s: the norm can be fused only for Q4K weights with cols <= 4096", what);
+  const size_t ab = ks_act_bytes(act);
+  KS_REQUIRE(ctx, ks_fits(x, 0, cols * ab) && ks_fits(w_norm, 0, cols * ab), "%s: x or norm weight buffer too small", what);
+  const bool add = y_prev || w_post || out_x;
+  if (add) {
+    KS_REQUIRE(ctx, y_prev && w_post && out_x, "%s: y_prev, w_post and out_x go together", what);
+    KS_REQUIRE(ctx, ks_fits(y_prev, 0, cols * ab) && ks_fits(w_post, 0, cols * ab) && ks_fits(out_x, 0, cols * ab),
+               "%s: residual-update buffer too small", what);
+    KS_REQUIRE(ctx, out_x->dptr != x->dptr, "%s: out_x must not alias x", what);
+  }
+  pro->mode = add ? KS_PRO_ADD_NORM : KS_PRO_NORM;
+  pro->eps = eps;
+  pro->w = w_norm->dptr;
+  pro->y = add ? y_prev->dptr : nullptr;
+  pro->w_post = add ? w_post->dptr : nullptr;
+  pro->out_x = add ? out_x->dptr : nullptr;
+  return KS_OK;
+}
+
+int ks_rmsnorm_matvec(ks_ctx* ctx, size_t rows, size_t cols, float eps, ks_dtype wdtype, ks_dtype act, const ks_buf* x,
+                      const ks_buf* w_norm, const ks_buf* W, ks_buf* y, const ks_buf* y_prev, const ks_buf* w_post,
+                      ks_buf* out_x) {
+  if (!ctx) return KS_ERR_INVALID;
+  int rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec", wdtype, W, 0, rows, cols))) return rc;
+  ks_mv_pro pro{};
+  if ((rc = make_pro(ctx, "rmsnorm_matvec", cols, eps, wdtype, act, x, w_norm, y_prev, w_post, out_x, &pro))) return rc;
+  KS_REQUIRE(ctx, ks_fits(y, 0, rows * ks_act_bytes(act)), "rmsnorm_matvec: y buffer too small");
+  ks_mv_seg seg{(const uint8_t*)W->dptr, y->dptr, (unsigned)rows};
+  return ks_launch_matvec(ctx, wdtype, &seg, 1, KS_EPI_PLAIN, cols, act, x->dptr, 1, nullptr, &pro);
+}
+
+int ks_rmsnorm_matvec_qkv(ks_ctx* ctx, size_t q_rows, size_t kv_rows, size_t cols, float eps, ks_dtype wdtype,
+                          ks_dtype act, const ks_buf* x, const ks_buf* w_norm, const ks_buf* Wq, const ks_buf* Wk,
+                          const ks_buf* Wv, ks_buf* q, ks_buf* k, ks_buf* v, const ks_buf* y_prev, const ks_buf* w_post,
+                          ks_buf* out_x) {
+  if (!ctx) return KS_ERR_INVALID;
+  int rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec_qkv(q)", wdtype, Wq, 0, q_rows, cols))) return rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec_qkv(k)", wdtype, Wk, 0, kv_rows, cols))) return rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec_qkv(v)", wdtype, Wv, 0, kv_rows, cols))) return rc;
+  ks_mv_pro pro{};
+  if ((rc = make_pro(ctx, "rmsnorm_matvec_qkv", cols, eps, wdtype, act, x, w_norm, y_prev, w_post, out_x, &pro))) return rc;
+  const size_t ab = ks_act_bytes(act);
+  KS_REQUIRE(ctx, ks_fits(q, 0, q_rows * ab) && ks_fits(k, 0, kv_rows * ab) && ks_fits(v, 0, kv_rows * ab),
+             "rmsnorm_matvec_qkv: output buffer too small");
+  ks_mv_seg segs[3] = {{(const uint8_t*)Wq->dptr, q->dptr, (unsigned)q_rows},
+                       {(const uint8_t*)Wk->dptr, k->dptr, (unsigned)kv_rows},
+                       {(const uint8_t*)Wv->dptr, v->dptr, (unsigned)kv_rows}};
+  return ks_launch_matvec(ctx, wdtype, segs, 3, KS_EPI_PLAIN, cols, act, x->dptr, 1, nullptr, &pro);
+}
+
+int ks_rmsnorm_matvec_gate_up_gelu(ks_ctx* ctx, size_t rows, size_t cols, float eps, ks_dtype wdtype, ks_dtype act,
+                                   const ks_buf* x, const ks_buf* w_norm, const ks_buf* Wg, const ks_buf* Wu, ks_buf* y,
+                                   const ks_buf* y_prev, const ks_buf* w_post, ks_buf* out_x) {
+  if (!ctx) return KS_ERR_INVALID;
+  int rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec_gate_up_gelu(gate)", wdtype, Wg, 0, rows, cols))) return rc;
+  if ((rc = check_w(ctx, "rmsnorm_matvec_gate_up_gelu(up)", wdtype, Wu, 0, rows, cols))) return rc;
+  ks_mv_pro pro{};
+  if ((rc = make_pro(ctx, "rmsnorm_matvec_gate_up_gelu", cols, eps, wdtype, act, x, w_norm, y_prev, w_post, out_x, &pro))) return rc;
+  KS_REQUIRE(ctx, ks_fits(y, 0, rows * ks_act_bytes(act)), "rmsnorm_matvec_gate_up_gelu: y buffer too small");
+  ks_mv_seg segs[2] = {{(const uint8_t*)Wg->dptr, y->dptr, (unsigned)rows}, {(const uint8_t*)Wu->dptr, y->dptr, (unsigned)rows}};
+  return ks_launch_matvec(ctx, wdtype, segs, 2, KS_EPI_GATE_UP, cols, act, x->dptr, 1, nullptr, &pro);
 }
 
 int ks_matvec_host(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* W, size_t w_byte_off,

@@ -14,6 +14,8 @@
 // Per-layer embeddings, sliding windows and shared-KV layers of real Gemma-4
 // checkpoints are not part of this driver.
 #include <cmath>
+#include <cstdlib>
+#include <utility>
 #include <cstring>
 #include <map>
 #include <string>
@@ -24,6 +26,7 @@
 namespace {
 
 __global__ void begin_token_kernel(int n, const int* pos, float* meta) {
+  ks_pdl_entry();
   const int s = threadIdx.x;
   if (s < n) {
     meta[s * 4 + 0] = (float)(pos[s] + 1);  // tlen = kv_len (gemma_prim.rs:1009-1016, full attention)
@@ -33,10 +36,11 @@ __global__ void begin_token_kernel(int n, const int* pos, float* meta) {
   }
 }
 __global__ void end_token_kernel(int n, int* pos) {
+  ks_pdl_entry();
   const int s = threadIdx.x;
   if (s < n) pos[s] += 1;
 }
-__global__ void set_state_kernel(int slot, int pos_value, int* pos) { pos[slot] = pos_value; }
+__global__ void set_state_kernel(int slot, int pos_value, int* pos) { ks_pdl_entry(); pos[slot] = pos_value; }
 
 struct Tensor {
   void* dptr = nullptr;
@@ -65,6 +69,8 @@ struct ks_model {
   std::vector<char> occupied;
   std::vector<int> seq_len;
   // activations, n_slots rows each
+  void *xb = nullptr, *xn = nullptr;  // second residual buffer (fused chain ping-pong), normed x for the head
+  bool fused = false;                 // norms folded into the matvec prologues
   void *x = nullptr, *x2 = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *ff = nullptr,
        *logits = nullptr;
   float* rope = nullptr;
@@ -117,7 +123,7 @@ int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
   float* meta = m->meta + (size_t)first * 4;
   int rc;
 
-  begin_token_kernel<<<1, 32, 0, c->stream>>>(n, pos, meta);
+  KS_LAUNCH(c, (begin_token_kernel), 1, 32, 0, n, pos, meta);
   if ((rc = ks_after_launch(c, "begin_token"))) return rc;
   // embed: x = sqrt(hidden) * deq(token_embd[id])   (gemma_prim.rs:681-683)
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, act, x))) return rc;
@@ -147,12 +153,96 @@ int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
     const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
     if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_ffw_norm.dptr, x, next_norm, x, x2))) return rc;
   }
-  end_token_kernel<<<1, 32, 0, c->stream>>>(n, pos);
+  KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, n, pos);
   if ((rc = ks_after_launch(c, "end_token"))) return rc;
   if (!want_logits) return KS_OK;
   // head: logits = token_embd . rms(x, output_norm); next id = softcap argmax (gemma_prim.rs:1222-1242)
   ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
+  for (int s = 0; s < n; s++)
+    if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
+  return KS_OK;
+}
+
+// The same token with the norms folded into the matvecs that consume them: five launches per layer
+// (qkv, per-head norm/rope/KV, attention, o-proj, gate/up, down -> six with the attention pair).
+// The residual stream alternates between two buffers because the block that writes the updated
+// stream must not overwrite what the other blocks of the same launch still read.
+int enqueue_forward_fused(ks_model* m, int first, int n, int src, bool want_logits) {
+  ks_ctx* c = m->ctx;
+  const ks_model_config& g = m->cfg;
+  const ks_dtype act = (ks_dtype)g.act;
+  const size_t ab = act_b(m);
+  const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
+  const size_t qn = nq * hd, kvn = nkv * hd;
+  char* cur = (char*)m->x + (size_t)first * H * ab;
+  char* oth = (char*)m->xb + (size_t)first * H * ab;
+  char* yb = (char*)m->x2 + (size_t)first * H * ab;
+  char* xn = (char*)m->xn + (size_t)first * H * ab;
+  char* q = (char*)m->q + (size_t)first * qn * ab;
+  char* k = (char*)m->k + (size_t)first * kvn * ab;
+  char* v = (char*)m->v + (size_t)first * kvn * ab;
+  char* o = (char*)m->o + (size_t)first * qn * ab;
+  char* ff = (char*)m->ff + (size_t)first * F * ab;
+  char* logits = (char*)m->logits + (size_t)first * g.vocab * ab;
+  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
+  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  int* pos = m->pos + first;
+  float* meta = m->meta + (size_t)first * 4;
+  int rc;
+
+  KS_LAUNCH(c, (begin_token_kernel), 1, 32, 0, n, pos, meta);
+  if ((rc = ks_after_launch(c, "begin_token"))) return rc;
+  if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, act, cur))) return rc;
+  for (int l = 0; l < g.n_layers; l++) {
+    const Layer& L = m->layers[l];
+    ks_mv_pro pro{};
+    pro.eps = g.eps;
+    pro.w = L.attn_norm.dptr;
+    if (l == 0) {
+      pro.mode = KS_PRO_NORM;
+    } else {
+      pro.mode = KS_PRO_ADD_NORM;  // x += rms(down)*w_post_ffw of the previous layer, then this layer's attn norm
+      pro.y = yb;
+      pro.w_post = m->layers[l - 1].post_ffw_norm.dptr;
+      pro.out_x = oth;
+    }
+    ks_mv_seg qkv[3] = {{(const uint8_t*)L.wq.dptr, q, (unsigned)qn},
+                        {(const uint8_t*)L.wk.dptr, k, (unsigned)kvn},
+                        {(const uint8_t*)L.wv.dptr, v, (unsigned)kvn}};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, qkv, 3, KS_EPI_PLAIN, H, act, cur, n, nullptr, &pro))) return rc;
+    if (l > 0) std::swap(cur, oth);
+    uint8_t* kk = m->kv_k[l] + (size_t)first * m->slot_stride;
+    uint8_t* kv = m->kv_v[l] + (size_t)first * m->slot_stride;
+    if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
+                                         kk, kv, pos, m->slot_stride)))
+      return rc;
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, m->slot_stride, meta, m->attn_tmp, o, m->n_splits)))
+      return rc;
+    ks_mv_seg so{(const uint8_t*)L.wo.dptr, yb, (unsigned)H};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
+    ks_mv_pro p2{};
+    p2.mode = KS_PRO_ADD_NORM;  // x += rms(attn)*w_post_attn, then the FFN norm (K:539)
+    p2.eps = g.eps;
+    p2.w = L.ffn_norm.dptr;
+    p2.y = yb;
+    p2.w_post = L.post_attn_norm.dptr;
+    p2.out_x = oth;
+    ks_mv_seg gu[2] = {{(const uint8_t*)L.wgate.dptr, ff, (unsigned)F}, {(const uint8_t*)L.wup.dptr, ff, (unsigned)F}};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, gu, 2, KS_EPI_GATE_UP, H, act, cur, n, nullptr, &p2))) return rc;
+    std::swap(cur, oth);
+    ks_mv_seg sd{(const uint8_t*)L.wdown.dptr, yb, (unsigned)H};
+    if ((rc = ks_launch_matvec(c, KS_Q4K, &sd, 1, KS_EPI_PLAIN, F, act, ff, n, nullptr))) return rc;
+  }
+  KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, n, pos);
+  if ((rc = ks_after_launch(c, "end_token"))) return rc;
+  if (!want_logits) return KS_OK;
+  // last residual update and the output norm, then the head (gemma_prim.rs:1222-1242)
+  if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, yb, m->layers[g.n_layers - 1].post_ffw_norm.dptr, cur,
+                                               m->output_norm.dptr, cur, xn)))
+    return rc;
+  ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
+  if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, xn, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
   return KS_OK;
@@ -167,7 +257,7 @@ int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
     cudaGraph_t graph = nullptr;
     KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     const uint64_t before = c->launches;
-    int rc = enqueue_forward(m, first, n, src, want_logits);
+    int rc = m->fused ? enqueue_forward_fused(m, first, n, src, want_logits) : enqueue_forward(m, first, n, src, want_logits);
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
     c->launches = before;  // captured launches are counted when the graph replays
     if (rc) {
@@ -262,6 +352,8 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   m->occupied.assign(g.n_slots, 0);
   m->seq_len.assign(g.n_slots, 0);
   const size_t S = g.n_slots;
+  m->fused = ks_matvec_can_fuse_pro(KS_Q4K, H) && !getenv("KSEARCH_UNFUSED");
+  ok = ok && dev_alloc(m, &m->xb, S * H * ab) == KS_OK && dev_alloc(m, &m->xn, S * H * ab) == KS_OK;
   ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
        dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&
        dev_alloc(m, &m->v, S * kvn * ab) == KS_OK && dev_alloc(m, &m->o, S * qn * ab) == KS_OK &&
@@ -298,6 +390,28 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
     return nullptr;
   }
   return m;
+}
+
+// Search (or load from the per-chip cache) the launch plan of every matvec shape of this model:
+// the load-time BEAM warm of gemma_prim.rs:254-290.  Honours KSEARCH_SKIP_BEAM.
+int ks_model_warm_plans(ks_model* m, int n_tok) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  const ks_model_config& g = m->cfg;
+  const size_t H = g.hidden, F = g.ffn, qn = (size_t)g.n_q * g.hd, kvn = (size_t)g.n_kv * g.hd;
+  if (n_tok < 1) n_tok = 1;
+  int found = 0;
+  found += ks_plan_search(c, "qkv_q4k", qn, kvn, H, n_tok, nullptr) == KS_OK;
+  found += ks_plan_search(c, "mv_q4k", H, 0, qn, n_tok, nullptr) == KS_OK;
+  found += ks_plan_search(c, "gu_q4k", F, 0, H, n_tok, nullptr) == KS_OK;
+  found += ks_plan_search(c, "mv_q4k", H, 0, F, n_tok, nullptr) == KS_OK;
+  found += ks_plan_search(c, g.embd_dtype == KS_Q6K ? "mv_q6k" : "mv_q4k", (size_t)g.vocab, 0, H, n_tok, nullptr) == KS_OK;
+  // plans change the captured launches: drop graphs recorded before
+  cudaStreamSynchronize(c->stream);
+  for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
+  m->graphs.clear();
+  m->graph_nodes.clear();
+  return found;
 }
 
 void ks_model_destroy(ks_model* m) {
@@ -349,7 +463,7 @@ int ks_model_slot_alloc(ks_model* m) {
     if (!m->occupied[s]) {
       m->occupied[s] = 1;
       m->seq_len[s] = 0;
-      set_state_kernel<<<1, 1, 0, m->ctx->stream>>>(s, 0, m->pos);
+      KS_LAUNCH(m->ctx, (set_state_kernel), 1, 1, 0, s, 0, m->pos);
       return s;
     }
   return ks_fail(m->ctx, KS_ERR_STATE, "KvPool full (max_batch=%d)", m->cfg.n_slots);
@@ -384,7 +498,7 @@ int ks_model_slot_reset(ks_model* m, int slot) {
     KS_CUDA(c, cudaMemsetAsync(m->kv_k[l] + (size_t)slot * m->slot_stride, 0, m->slot_stride, c->stream));
     KS_CUDA(c, cudaMemsetAsync(m->kv_v[l] + (size_t)slot * m->slot_stride, 0, m->slot_stride, c->stream));
   }
-  set_state_kernel<<<1, 1, 0, c->stream>>>(slot, 0, m->pos);
+  KS_LAUNCH(c, (set_state_kernel), 1, 1, 0, slot, 0, m->pos);
   m->seq_len[slot] = 0;
   m->occupied[slot] = 1;
   return ks_after_launch(c, "slot_reset");

@@ -34,6 +34,7 @@ struct MvsArgs {
   unsigned n_cseg;      // column segments per row
   int stages;
   unsigned* err;
+  MvPro pro;
 };
 
 __device__ __forceinline__ const uint8_t* s_w(const MvsArgs& a, int s) { return s == 0 ? a.W[0] : s == 1 ? a.W[1] : a.W[2]; }
@@ -79,7 +80,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 // Shared memory map (bytes): [x staging | pad to 128 | stage rings of all warps | mbarriers]
 struct Layout {
-  unsigned x_bytes, ring_off, stage_bytes, bar_off, total;
+  unsigned x_bytes, ring_off, stage_bytes, bar_off, red_off, total;
 };
 __host__ __device__ inline Layout make_layout(unsigned x_bytes, unsigned stage_bytes, int nwarps, int stages) {
   Layout L;
@@ -87,7 +88,8 @@ __host__ __device__ inline Layout make_layout(unsigned x_bytes, unsigned stage_b
   L.ring_off = (x_bytes + 127u) & ~127u;
   L.stage_bytes = stage_bytes;
   L.bar_off = L.ring_off + stage_bytes * (unsigned)(nwarps * stages);
-  L.total = L.bar_off + 8u * (unsigned)(nwarps * stages);
+  L.red_off = (L.bar_off + 8u * (unsigned)(nwarps * stages) + 15u) & ~15u;  // 32 floats for block reductions
+  L.total = L.red_off + 128u;
   return L;
 }
 
@@ -131,7 +133,14 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
     const unsigned st = i % (unsigned)S;
     const uint32_t bar = bars + st * 8u;
     if (lane == 0) mbar_expect_tx(bar, valid * MATS * seg_bytes);
-    if (lane < NCOPY) {
+    if (a.n_cseg == 1 && (EPI == KS_EPI_PLAIN || R == 1)) {
+      // whole rows: the rows of a group are contiguous in memory, one copy per matrix
+      if (lane < MATS) {
+        const uint8_t* base = (EPI == KS_EPI_GATE_UP) ? (lane ? a.W[1] : a.W[0]) : s_w(a, seg);
+        bulk_g2s(smem_u32(ring + (size_t)st * L.stage_bytes + (size_t)lane * RL * seg_bytes),
+                 base + (size_t)row0 * a.row_bytes, valid * seg_bytes, bar);
+      }
+    } else if (lane < NCOPY) {
       const int slot = lane / RL, rr = lane % RL;
       const unsigned j = (unsigned)(EPI == KS_EPI_GATE_UP ? (slot >> 1) : slot) * RL + rr;  // logical row in group
       if (j < valid) {
@@ -142,6 +151,7 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
     }
   };
 
+  pdl_launch_dependents();  // successors may start (and prefetch their own weights) right away
   if (lane == 0) {
     for (int s = 0; s < S; s++) mbar_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -150,16 +160,20 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
   __syncwarp();
   for (unsigned i = 0; i < (unsigned)S && i < n_items; i++) issue(i);
 
-  pdl_wait();  // x is written by the kernel before this one
-  q4k_stage_x<XT>(smem, reinterpret_cast<const XT*>(a.x), a.cols, a.n_tok);
+  if (a.pro.mode == KS_PRO_NONE) {
+    pdl_wait();  // x is written by the kernel before this one
+    q4k_stage_x<XT>(smem, reinterpret_cast<const XT*>(a.x), a.cols, a.n_tok);
+  } else
+    q4k_stage_x_pro<XT>(smem, reinterpret_cast<float*>(smem + L.red_off), a.pro, reinterpret_cast<const XT*>(a.x), a.cols, a.n_tok);
   __syncthreads();
-  pdl_launch_dependents();
 
   float yacc[SLOTS][NT];
 #pragma unroll
   for (int r = 0; r < SLOTS; r++)
 #pragma unroll
     for (int t = 0; t < NT; t++) yacc[r][t] = 0.0f;
+  const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(smem);
+  const uint32_t tok_stride = units * Q4K_XTOK * 4u;
 
   bool ok = true;
   unsigned i = 0;
@@ -170,48 +184,62 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
       ok = false;
       break;
     }
-    const unsigned char* stage = ring + (size_t)st * L.stage_bytes;
+    // 32-bit shared addresses that advance by constants per unit: this lane's first unit of the
+    // segment in every row slot, and the matching x fragment / sums.
+    uint32_t waddr = ring_s + st * L.stage_bytes + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES +
+                     (uint32_t)g * 32u;
+    uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * (Q4K_XS * 4u);
+    uint32_t saddr = xs_s + units * (Q4K_XS * 4u) + (cs * seg_units + (unsigned)cl) * 8u;
     for (unsigned it = 0; it < upl; it++) {
-      const unsigned ul = cl + LPR * it;  // unit within the segment
-      const unsigned u = cs * seg_units + ul;
-      const unsigned boff = (ul >> 2) * KS_Q4K_BLOCK_BYTES;
 #pragma unroll
       for (int t = 0; t < NT; t++) {
         if (t < a.n_tok) {
-          const float* xp = reinterpret_cast<const float*>(smem) + (size_t)t * units * Q4K_XTOK;
-          const float2 sx = lds_f2(xp + (size_t)units * Q4K_XS + (size_t)u * 2);
-          const float* xv = xp + (size_t)u * Q4K_XS;
-          float2 acc[SLOTS][2];
+          const uint32_t xt = xaddr + (uint32_t)t * tok_stride;
+          const float2 sx = lds_f2a(saddr + (uint32_t)t * tok_stride);
+          u64 acc[SLOTS][2];
 #pragma unroll
-          for (int r = 0; r < SLOTS; r++) acc[r][0] = acc[r][1] = make_float2(0.0f, 0.0f);
-#pragma unroll
-          for (int half = 0; half < 2; half++) {
-            float4 xf[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) xf[q] = lds_f4(xv + (half * 8 + q) * 4);
+          for (int r = 0; r < SLOTS; r++) acc[r][0] = acc[r][1] = 0ull;
+          {
+            u64 xf[16];  // 16 packed (lo, hi) pairs: l = 0..15
+            lds_p2o<0>(xt, xf[0], xf[1]);     lds_p2o<16>(xt, xf[2], xf[3]);
+            lds_p2o<32>(xt, xf[4], xf[5]);    lds_p2o<48>(xt, xf[6], xf[7]);
+            lds_p2o<64>(xt, xf[8], xf[9]);    lds_p2o<80>(xt, xf[10], xf[11]);
+            lds_p2o<96>(xt, xf[12], xf[13]);  lds_p2o<112>(xt, xf[14], xf[15]);
 #pragma unroll
             for (int r = 0; r < SLOTS; r++) {
-              const unsigned char* rowp = stage + (size_t)(r * RL + rl) * seg_bytes + boff;
-              const uint4 q = lds_u4(rowp + 16 + g * 32 + half * 16);
-              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+              const uint4 q = lds_u4o<16>(waddr + (uint32_t)(r * RL) * seg_bytes);
+              q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
+              q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
+              q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
+              q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
+            }
+          }
+          {
+            u64 xf[16];  // l = 16..31
+            lds_p2o<128>(xt, xf[0], xf[1]);    lds_p2o<144>(xt, xf[2], xf[3]);
+            lds_p2o<160>(xt, xf[4], xf[5]);    lds_p2o<176>(xt, xf[6], xf[7]);
+            lds_p2o<192>(xt, xf[8], xf[9]);    lds_p2o<208>(xt, xf[10], xf[11]);
+            lds_p2o<224>(xt, xf[12], xf[13]);  lds_p2o<240>(xt, xf[14], xf[15]);
 #pragma unroll
-              for (int j = 0; j < 4; j++)
-                q4_word(w[j], make_float2(xf[2 * j].x, xf[2 * j].y), make_float2(xf[2 * j].z, xf[2 * j].w),
-                        make_float2(xf[2 * j + 1].x, xf[2 * j + 1].y), make_float2(xf[2 * j + 1].z, xf[2 * j + 1].w),
-                        acc[r][0], acc[r][1]);
+            for (int r = 0; r < SLOTS; r++) {
+              const uint4 q = lds_u4o<32>(waddr + (uint32_t)(r * RL) * seg_bytes);
+              q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
+              q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
+              q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
+              q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
             }
           }
 #pragma unroll
           for (int r = 0; r < SLOTS; r++) {
-            const uint4 hdr = lds_u4(stage + (size_t)(r * RL + rl) * seg_bytes + boff);
-            float dsc_lo, dsc_hi, dm_lo, dm_hi;
-            q4k_group_scales(hdr, g, dsc_lo, dsc_hi, dm_lo, dm_hi);
-            const float s_lo = acc[r][0].x + acc[r][1].x;
-            const float s_hi = acc[r][0].y + acc[r][1].y;
-            yacc[r][t] += (dsc_lo * s_lo + dsc_hi * s_hi) - (dm_lo * sx.x + dm_hi * sx.y);
+            const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)(r * RL) * seg_bytes - (uint32_t)g * 32u);
+            const float2 a01 = unpack2(padd2(acc[r][0], acc[r][1]));
+            yacc[r][t] = q4k_apply_scales(hdr, g, a01.x, a01.y, sx.x, sx.y, yacc[r][t]);
           }
         }
       }
+      waddr += (LPR / 4) * KS_Q4K_BLOCK_BYTES;
+      xaddr += LPR * Q4K_XS * 4u;
+      saddr += LPR * 8u;
     }
     __syncwarp();
     if (i + (unsigned)S < n_items) {
@@ -276,6 +304,13 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
 template <int LPR, int R, int NT, int EPI, typename XT>
 int launch_q4k(ks_ctx* ctx, const MvsArgs& a, unsigned grid, int nwarps, size_t smem) {
   auto kern = mvs_q4k_kernel<LPR, R, NT, EPI, XT>;
+  static bool carve_set[16] = {false};
+  if (!carve_set[ctx->device & 15]) {
+    // Ask for the largest shared-memory carve-out, so that the blocks of two consecutive kernels can
+    // be resident together (the next kernel prefetches its weights while this one computes).
+    carve_set[ctx->device & 15] = true;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  }
   static size_t smem_set[16] = {0};  // per device: largest opt-in size already granted to this kernel
   if (smem > 48 * 1024 && smem > smem_set[ctx->device & 15]) {
     smem_set[ctx->device & 15] = smem;
@@ -361,6 +396,7 @@ __global__ void __launch_bounds__(256) mvs_q6k_kernel(const MvsArgs a) {
     }
   };
 
+  pdl_launch_dependents();  // successors may start (and prefetch their own weights) right away
   if (lane == 0) {
     for (int s = 0; s < S; s++) mbar_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -372,7 +408,6 @@ __global__ void __launch_bounds__(256) mvs_q6k_kernel(const MvsArgs a) {
   pdl_wait();
   q6k_stage_x<XT>(smem, reinterpret_cast<const XT*>(a.x), a.cols, a.n_tok);
   __syncthreads();
-  pdl_launch_dependents();
 
   bool ok = true;
   unsigned i = 0;
@@ -411,10 +446,15 @@ __global__ void __launch_bounds__(256) mvs_q6k_kernel(const MvsArgs a) {
         if (t < a.n_tok) {
           const float4* xq = reinterpret_cast<const float4*>(smem) + (size_t)t * units * 5;
           const float4 sx = lds_f4(xq + (size_t)4 * units + u);
-          float p = s1 * (q6_word(v1, lds_f4(xq + u)) - 32.0f * sx.x);
-          p += s2 * (q6_word(v2, lds_f4(xq + (size_t)units + u)) - 32.0f * sx.y);
-          p += s3 * (q6_word(v3, lds_f4(xq + (size_t)2 * units + u)) - 32.0f * sx.z);
-          p += s4 * (q6_word(v4, lds_f4(xq + (size_t)3 * units + u)) - 32.0f * sx.w);
+          u64 xa, xb;
+          lds_p2(xq + u, xa, xb);
+          float p = s1 * (q6_word_p(v1, xa, xb) - 32.0f * sx.x);
+          lds_p2(xq + (size_t)units + u, xa, xb);
+          p += s2 * (q6_word_p(v2, xa, xb) - 32.0f * sx.y);
+          lds_p2(xq + (size_t)2 * units + u, xa, xb);
+          p += s3 * (q6_word_p(v3, xa, xb) - 32.0f * sx.z);
+          lds_p2(xq + (size_t)3 * units + u, xa, xb);
+          p += s4 * (q6_word_p(v4, xa, xb) - 32.0f * sx.w);
           yacc[t] += d * p;
         }
       }
@@ -447,6 +487,13 @@ __global__ void __launch_bounds__(256) mvs_q6k_kernel(const MvsArgs a) {
 template <int NT, typename XT>
 int launch_q6k(ks_ctx* ctx, const MvsArgs& a, unsigned grid, int nwarps, size_t smem) {
   auto kern = mvs_q6k_kernel<NT, XT>;
+  static bool carve_set[16] = {false};
+  if (!carve_set[ctx->device & 15]) {
+    // Ask for the largest shared-memory carve-out, so that the blocks of two consecutive kernels can
+    // be resident together (the next kernel prefetches its weights while this one computes).
+    carve_set[ctx->device & 15] = true;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  }
   static size_t smem_set[16] = {0};  // per device: largest opt-in size already granted to this kernel
   if (smem > 48 * 1024 && smem > smem_set[ctx->device & 15]) {
     smem_set[ctx->device & 15] = smem;
@@ -473,7 +520,7 @@ int launch_q6k(ks_ctx* ctx, const MvsArgs& a, unsigned grid, int nwarps, size_t 
 // Streamed Q4_K launch; plan fields: nr = rows per lane (1 or 2), nwarps, ctas_per_sm,
 // variant bits 8..15 = stages (0 = default 3), bits 16..23 = blocks per column segment (0 = auto).
 int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi, size_t cols,
-                                ks_dtype act, const void* x, int n_tok, const ks_plan* plan) {
+                                ks_dtype act, const void* x, int n_tok, const ks_plan* plan, const ks_mv_pro* pro) {
   const unsigned nb = (unsigned)(cols / 256);
   const int LPR = (nb % 2 == 0) ? 8 : 4;
   const int RL = 32 / LPR;
@@ -484,6 +531,7 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   int nwarps = (plan && plan->nwarps > 0) ? plan->nwarps : 8;
   if (nwarps > 8) nwarps = 8;
   int stages = plan ? (plan->variant >> 8) & 0xFF : 0;
+  const bool auto_stages = stages <= 0;
   if (stages <= 0) stages = 3;
   unsigned seg_blocks = plan ? (unsigned)((plan->variant >> 16) & 0xFF) : 0;
   const unsigned step = LPR == 8 ? 2 : 1;  // segment units must divide among LPR lanes
@@ -501,6 +549,15 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   a.seg_blocks = seg_blocks;
   a.n_cseg = nb / seg_blocks;
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
+  if (pro) a.pro = *pro;
+  if (a.pro.mode != KS_PRO_NONE) {
+    KS_REQUIRE(ctx, cols <= 16u * (unsigned)nwarps * 32u, "matvec: fused norm needs cols <= %u", 16u * (unsigned)nwarps * 32u);
+    const uintptr_t al = act == KS_F32 ? 15 : 7;
+    KS_REQUIRE(ctx, (((uintptr_t)x | (uintptr_t)a.pro.w) & al) == 0, "matvec: fused norm needs aligned vectors");
+    if (a.pro.mode == KS_PRO_ADD_NORM)
+      KS_REQUIRE(ctx, a.pro.out_x != x && (((uintptr_t)a.pro.y | (uintptr_t)a.pro.w_post | (uintptr_t)a.pro.out_x) & al) == 0,
+                 "matvec: fused residual update must not alias its input and needs aligned vectors");
+  }
   const unsigned grows = (unsigned)(RL * R);
   unsigned g0 = 0;
   for (int s = 0; s < n_seg; s++) {
@@ -515,6 +572,23 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   a.grp_start[a.n_seg] = g0;
   const unsigned x_bytes = (unsigned)n_tok * (unsigned)(cols / 64) * Q4K_XTOK * 4u;
   const unsigned stage_bytes = (unsigned)(RL * R * mats) * seg_blocks * KS_Q4K_BLOCK_BYTES;
+  const int cps = (plan && plan->ctas_per_sm > 0) ? plan->ctas_per_sm : 1;
+  if (auto_stages) {
+    // Enough stages for a warp to start ALL of its copies before it waits for its input (the whole
+    // weight stream of a decode-sized matrix is then in flight while the previous kernel still
+    // runs), inside HALF of an SM's shared memory so that the blocks of two consecutive kernels fit
+    // side by side: fewer stages first, then fewer warps (not below 4).
+    const unsigned half = 108u * 1024u;
+    const bool pick_warps = !(plan && plan->nwarps > 0);
+    for (;;) {
+      const unsigned gw_total = (unsigned)(ctx->sm_count * cps * nwarps);
+      const unsigned items = ((g0 + gw_total - 1) / gw_total) * a.n_cseg;
+      stages = (int)(items < 2 ? 2 : items > 8 ? 8 : items);
+      while (stages > 2 && make_layout(x_bytes, stage_bytes, nwarps, stages).total > half) stages--;
+      if (make_layout(x_bytes, stage_bytes, nwarps, stages).total <= half || !pick_warps || nwarps <= 4) break;
+      nwarps -= 1;
+    }
+  }
   // fit the rings into the shared memory budget: fewer stages first, then fewer warps
   Layout L = make_layout(x_bytes, stage_bytes, nwarps, stages);
   const unsigned budget = (unsigned)ctx->smem_optin;
@@ -522,7 +596,6 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   while (L.total > budget && nwarps > 1) L = make_layout(x_bytes, stage_bytes, --nwarps, stages);
   KS_REQUIRE(ctx, L.total <= budget, "matvec: needs %u B of shared memory (limit %u)", L.total, budget);
   a.stages = stages;
-  const int cps = (plan && plan->ctas_per_sm > 0) ? plan->ctas_per_sm : 1;
   unsigned grid = (g0 + nwarps - 1) / nwarps;
   const unsigned cap = (unsigned)(ctx->sm_count * cps);
   if (grid > cap) grid = cap;

@@ -82,6 +82,7 @@ __device__ __forceinline__ float deq_any(int dtype, const void* base, size_t idx
 }
 
 __global__ void dequant_kernel(int dtype, const uint8_t* src, size_t n, float* dst) {
+  ks_pdl_entry();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     dst[i] = deq_any(dtype, src, i);
 }
@@ -112,6 +113,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename T>
 __global__ void rmsnorm_kernel(unsigned n, float eps, const T* x, const T* w, const T* res, int has_scale,
                                float scale, T* y) {
+  ks_pdl_entry();
   __shared__ float red[32];
   const size_t off = (size_t)blockIdx.x * n;
   float ss = 0.0f;
@@ -133,6 +135,7 @@ __global__ void rmsnorm_kernel(unsigned n, float eps, const T* x, const T* w, co
 template <typename T>
 __global__ void rmsnorm_add_then_rmsnorm_kernel(unsigned n, float eps, const T* y, const T* w_post, const T* res,
                                                 const T* w_ffn, T* out_x, T* out_x2) {
+  ks_pdl_entry();
   extern __shared__ float xs[];  // n floats: the new residual stream
   __shared__ float red[32];
   const size_t off = (size_t)blockIdx.x * n;
@@ -172,6 +175,7 @@ __device__ __forceinline__ void pack_q40_warp(float v, uint8_t* blk, int lane) {
 
 template <typename T>
 __global__ void quantize_q40_kernel(size_t nblocks, const T* src, uint8_t* dst) {
+  ks_pdl_entry();
   const int lane = threadIdx.x & 31;
   const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -187,6 +191,7 @@ template <typename T>
 __global__ void per_head_qkv_q40_kernel(unsigned n_q, unsigned n_kv, unsigned hd, float eps, const T* q, const T* qw,
                                         const float* rope, const T* k, const T* kw, const T* v, T* q_out,
                                         uint8_t* kv_k, uint8_t* kv_v, const int* pos, size_t slot_stride) {
+  ks_pdl_entry();
   extern __shared__ float tmp[];  // hd floats
   const int lane = threadIdx.x;
   const unsigned jobs = n_q + 2 * n_kv;
@@ -248,6 +253,7 @@ __global__ void per_head_qkv_q40_kernel(unsigned n_q, unsigned n_kv, unsigned hd
 // ---- embedding gather (lower.rs:3899-3924): dst[b, i] = scale * deq(src)[uint(idx[b])*n + i] --
 template <typename T>
 __global__ void copy_scale_indexed_kernel(unsigned n, float scale, int dtype, const void* src, const float* idx, T* dst) {
+  ks_pdl_entry();
   const size_t id = (size_t)(unsigned)idx[blockIdx.y];
   size_t row_elems = (size_t)id * n;
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
@@ -266,6 +272,7 @@ __device__ __forceinline__ void argmax_merge(float& bv, unsigned& bi, float ov, 
 template <typename T>
 __global__ void softcap_argmax_kernel(unsigned n, float cap, const T* x, float* out_idx, float* ws_val,
                                       unsigned* ws_idx, unsigned* counter) {
+  ks_pdl_entry();
   __shared__ float sv[32];
   __shared__ unsigned si[32];
   __shared__ bool last;
@@ -321,6 +328,7 @@ __global__ void softcap_argmax_kernel(unsigned n, float cap, const T* x, float* 
 
 template <typename T>
 __global__ void gelu_mul_kernel(size_t n, const T* g, const T* u, T* y) {
+  ks_pdl_entry();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float ax = fminf(20.0f, fmaxf(-20.0f, ld_act<T>(g, i)));
     const float t = 0.79788456f * (ax + 0.044715f * ((ax * ax) * ax));
@@ -338,10 +346,10 @@ int ks_launch_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype ac
                       const void* res, int has_scale, float scale, void* y) {
   const int th = norm_threads(n);
   if (act == KS_F32)
-    rmsnorm_kernel<float><<<(unsigned)rows, th, 0, ctx->stream>>>((unsigned)n, eps, (const float*)x, (const float*)w,
+    KS_LAUNCH(ctx, (rmsnorm_kernel<float>), (unsigned)rows, th, 0, (unsigned)n, eps, (const float*)x, (const float*)w,
                                                                  (const float*)res, has_scale, scale, (float*)y);
   else
-    rmsnorm_kernel<__half><<<(unsigned)rows, th, 0, ctx->stream>>>((unsigned)n, eps, (const __half*)x, (const __half*)w,
+    KS_LAUNCH(ctx, (rmsnorm_kernel<__half>), (unsigned)rows, th, 0, (unsigned)n, eps, (const __half*)x, (const __half*)w,
                                                                   (const __half*)res, has_scale, scale, (__half*)y);
   return ks_after_launch(ctx, "rmsnorm");
 }
@@ -352,11 +360,11 @@ int ks_launch_rmsnorm_add_then_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float
   const int th = norm_threads(n);
   const size_t smem = n * sizeof(float);
   if (act == KS_F32)
-    rmsnorm_add_then_rmsnorm_kernel<float><<<(unsigned)rows, th, smem, ctx->stream>>>(
+    KS_LAUNCH(ctx, (rmsnorm_add_then_rmsnorm_kernel<float>), (unsigned)rows, th, smem, 
         (unsigned)n, eps, (const float*)y, (const float*)w_post, (const float*)res, (const float*)w_ffn, (float*)out_x,
         (float*)out_x2);
   else
-    rmsnorm_add_then_rmsnorm_kernel<__half><<<(unsigned)rows, th, smem, ctx->stream>>>(
+    KS_LAUNCH(ctx, (rmsnorm_add_then_rmsnorm_kernel<__half>), (unsigned)rows, th, smem, 
         (unsigned)n, eps, (const __half*)y, (const __half*)w_post, (const __half*)res, (const __half*)w_ffn,
         (__half*)out_x, (__half*)out_x2);
   return ks_after_launch(ctx, "rmsnorm_add_then_rmsnorm");
@@ -369,11 +377,11 @@ int ks_launch_per_head_qkv_q40(ks_ctx* ctx, size_t n_q, size_t n_kv, size_t hd, 
   const unsigned grid = (unsigned)(n_tok * (n_q + 2 * n_kv));
   const size_t smem = hd * sizeof(float);
   if (act == KS_F32)
-    per_head_qkv_q40_kernel<float><<<grid, 32, smem, ctx->stream>>>(
+    KS_LAUNCH(ctx, (per_head_qkv_q40_kernel<float>), grid, 32, smem, 
         (unsigned)n_q, (unsigned)n_kv, (unsigned)hd, eps, (const float*)q, (const float*)qw, rope, (const float*)k,
         (const float*)kw, (const float*)v, (float*)q_out, kv_k, kv_v, pos_dev, slot_stride_bytes);
   else
-    per_head_qkv_q40_kernel<__half><<<grid, 32, smem, ctx->stream>>>(
+    KS_LAUNCH(ctx, (per_head_qkv_q40_kernel<__half>), grid, 32, smem, 
         (unsigned)n_q, (unsigned)n_kv, (unsigned)hd, eps, (const __half*)q, (const __half*)qw, rope, (const __half*)k,
         (const __half*)kw, (const __half*)v, (__half*)q_out, kv_k, kv_v, pos_dev, slot_stride_bytes);
   return ks_after_launch(ctx, "rmsnorm_per_head_qkv_q40");
@@ -383,9 +391,9 @@ int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scal
                                  const float* idx, ks_dtype act, void* dst) {
   dim3 grid((unsigned)((n + 255) / 256), (unsigned)batch);
   if (act == KS_F32)
-    copy_scale_indexed_kernel<float><<<grid, 256, 0, ctx->stream>>>((unsigned)n, scale, (int)src_dtype, src, idx, (float*)dst);
+    KS_LAUNCH(ctx, (copy_scale_indexed_kernel<float>), grid, 256, 0, (unsigned)n, scale, (int)src_dtype, src, idx, (float*)dst);
   else
-    copy_scale_indexed_kernel<__half><<<grid, 256, 0, ctx->stream>>>((unsigned)n, scale, (int)src_dtype, src, idx, (__half*)dst);
+    KS_LAUNCH(ctx, (copy_scale_indexed_kernel<__half>), grid, 256, 0, (unsigned)n, scale, (int)src_dtype, src, idx, (__half*)dst);
   return ks_after_launch(ctx, "copy_scale_indexed");
 }
 
@@ -399,9 +407,9 @@ int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, con
   if (grid > cap_grid) grid = cap_grid;
   if (grid == 0) grid = 1;
   if (act == KS_F32)
-    softcap_argmax_kernel<float><<<grid, 256, 0, ctx->stream>>>((unsigned)n, cap, (const float*)logits, out_idx, ws_val, ws_idx, counter);
+    KS_LAUNCH(ctx, (softcap_argmax_kernel<float>), grid, 256, 0, (unsigned)n, cap, (const float*)logits, out_idx, ws_val, ws_idx, counter);
   else
-    softcap_argmax_kernel<__half><<<grid, 256, 0, ctx->stream>>>((unsigned)n, cap, (const __half*)logits, out_idx, ws_val, ws_idx, counter);
+    KS_LAUNCH(ctx, (softcap_argmax_kernel<__half>), grid, 256, 0, (unsigned)n, cap, (const __half*)logits, out_idx, ws_val, ws_idx, counter);
   return ks_after_launch(ctx, "softcap_argmax");
 }
 
@@ -419,7 +427,7 @@ int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_o
   if (nelem == 0) return KS_OK;
   size_t blocks = (nelem + 255) / 256;
   if (blocks > (size_t)ctx->sm_count * 32) blocks = (size_t)ctx->sm_count * 32;
-  dequant_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>((int)dtype, (const uint8_t*)src->dptr + src_byte_off, nelem,
+  KS_LAUNCH(ctx, (dequant_kernel), (unsigned)blocks, 256, 0, (int)dtype, (const uint8_t*)src->dptr + src_byte_off, nelem,
                                                             (float*)dst->dptr + dst_off);
   return ks_after_launch(ctx, "dequant");
 }
@@ -492,10 +500,10 @@ int ks_quantize_q40(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* src, size
   size_t grid = (nblocks + 7) / 8;
   if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
   if (act == KS_F32)
-    quantize_q40_kernel<float><<<(unsigned)grid, 256, 0, ctx->stream>>>(nblocks, (const float*)src->dptr + src_off,
+    KS_LAUNCH(ctx, (quantize_q40_kernel<float>), (unsigned)grid, 256, 0, nblocks, (const float*)src->dptr + src_off,
                                                                         (uint8_t*)dst->dptr + dst_byte_off);
   else
-    quantize_q40_kernel<__half><<<(unsigned)grid, 256, 0, ctx->stream>>>(nblocks, (const __half*)src->dptr + src_off,
+    KS_LAUNCH(ctx, (quantize_q40_kernel<__half>), (unsigned)grid, 256, 0, nblocks, (const __half*)src->dptr + src_off,
                                                                          (uint8_t*)dst->dptr + dst_byte_off);
   return ks_after_launch(ctx, "quantize_q40");
 }
@@ -535,9 +543,9 @@ int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_b
   size_t grid = (n + 255) / 256;
   if (grid > (size_t)ctx->sm_count * 8) grid = (size_t)ctx->sm_count * 8;
   if (act == KS_F32)
-    gelu_mul_kernel<float><<<(unsigned)grid, 256, 0, ctx->stream>>>(n, (const float*)g->dptr, (const float*)u->dptr, (float*)y->dptr);
+    KS_LAUNCH(ctx, (gelu_mul_kernel<float>), (unsigned)grid, 256, 0, n, (const float*)g->dptr, (const float*)u->dptr, (float*)y->dptr);
   else
-    gelu_mul_kernel<__half><<<(unsigned)grid, 256, 0, ctx->stream>>>(n, (const __half*)g->dptr, (const __half*)u->dptr, (__half*)y->dptr);
+    KS_LAUNCH(ctx, (gelu_mul_kernel<__half>), (unsigned)grid, 256, 0, n, (const __half*)g->dptr, (const __half*)u->dptr, (__half*)y->dptr);
   return ks_after_launch(ctx, "gelu_mul");
 }
 

@@ -1,0 +1,263 @@
+// Launch planner for the matvec kernels: the reference's BEAM search and plan cache
+// (crates/ksearch_codegen/src/lib.rs:178-246 beam_search_matvec, beam.rs:26-139 candidates and
+// the on-disk cache, plan_cache.rs:9-38, Eng::beam_matvec crates/ksearch_kernels/src/lib.rs:1985-2043),
+// retargeted from "tile sizes of generated code" to "which hand-written variant with which launch
+// shape".  A plan is {variant, stages, nr, nwarps, ctas_per_sm}; plans live in the context, keyed by
+// (op, rows, cols, n_tok), and on disk per chip:  <dir>/<op>_<rows>x<cols>_<hash>.txt  with k=v
+// lines, <dir> = $KSEARCH_BEAM_CACHE or ~/.cache/ksearch/beam.  KSEARCH_SKIP_BEAM skips the timing
+// search (cached or default plans are used), KSEARCH_BEAM_FORCE ignores cached files, KSEARCH_CHIP
+// overrides the chip name that enters the key.
+#include <sys/stat.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+#include <vector>
+
+#include "ks_internal.h"
+
+namespace {
+
+uint64_t fnv1a(const std::string& s) {
+  uint64_t h = 0xcbf29ce484222325ull;
+  for (unsigned char c : s) h = (h ^ c) * 0x100000001b3ull;
+  return h;
+}
+
+std::string cache_dir() {
+  if (const char* p = getenv("KSEARCH_BEAM_CACHE")) return p;
+  if (const char* h = getenv("HOME")) return std::string(h) + "/.cache/ksearch/beam";
+  return ".ksearch_beam_cache";
+}
+
+void mkdirs(const std::string& path) {
+  std::string cur;
+  for (size_t i = 0; i <= path.size(); i++) {
+    if (i == path.size() || path[i] == '/') {
+      if (!cur.empty()) mkdir(cur.c_str(), 0755);
+    }
+    if (i < path.size()) cur += path[i];
+  }
+}
+
+}  // namespace
+
+std::string ks_plan_key(const char* op, size_t rows, size_t cols, int n_tok) {
+  std::ostringstream o;
+  o << op << "_" << rows << "x" << cols;
+  if (n_tok > 1) o << "_b" << n_tok;
+  return o.str();
+}
+
+const ks_plan* ks_plan_lookup(const ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok) {
+  auto it = ctx->plans.find(ks_plan_key(op, rows, cols, n_tok));
+  return it == ctx->plans.end() ? nullptr : &it->second;
+}
+
+extern "C" {
+
+// File name of a plan: "<key>_<hash(key, chip)>.txt" (beam.rs:81-88 beam_cache_key).
+int ks_plan_file_name(const char* key, const char* chip, char* out, size_t out_len) {
+  if (!key || !chip || !out) return KS_ERR_INVALID;
+  char buf[512];
+  snprintf(buf, sizeof buf, "%s_%016llx.txt", key, (unsigned long long)fnv1a(std::string(key) + "|" + chip));
+  if (strlen(buf) + 1 > out_len) return KS_ERR_INVALID;
+  strcpy(out, buf);
+  return KS_OK;
+}
+
+// beam.rs:125-139 save_beam_cache.  dir == NULL: the default cache directory.
+int ks_plan_file_save(const char* dir, const char* key, const char* chip, const ks_plan* plan) {
+  if (!key || !chip || !plan) return KS_ERR_INVALID;
+  const std::string d = dir ? dir : cache_dir();
+  mkdirs(d);
+  char name[512];
+  if (ks_plan_file_name(key, chip, name, sizeof name)) return KS_ERR_INVALID;
+  std::ofstream f(d + "/" + name);
+  if (!f) return KS_ERR_STATE;
+  char ms[64];
+  snprintf(ms, sizeof ms, "%.6f", plan->ms);
+  f << "variant=" << (plan->variant & 0xFF) << "\nstages=" << ((plan->variant >> 8) & 0xFF) << "\nseg_blocks="
+    << ((plan->variant >> 16) & 0xFF) << "\nnr0=" << plan->nr << "\nnsg=" << plan->nwarps << "\nctas_per_sm="
+    << plan->ctas_per_sm << "\nms=" << ms << "\nchip=" << chip << "\n";
+  return f.good() ? KS_OK : KS_ERR_STATE;
+}
+
+// beam.rs:90-123 load_beam_cache.  Returns KS_ERR_STATE when there is no (complete) file.
+int ks_plan_file_load(const char* dir, const char* key, const char* chip, ks_plan* plan) {
+  if (!key || !chip || !plan) return KS_ERR_INVALID;
+  const std::string d = dir ? dir : cache_dir();
+  char name[512];
+  if (ks_plan_file_name(key, chip, name, sizeof name)) return KS_ERR_INVALID;
+  std::ifstream f(d + "/" + name);
+  if (!f) return KS_ERR_STATE;
+  int variant = -1, stages = 0, seg = 0, nr = -1, nsg = -1, cps = -1;
+  double ms = -1;
+  std::string line;
+  while (std::getline(f, line)) {
+    const size_t eq = line.find('=');
+    if (eq == std::string::npos) continue;
+    const std::string k = line.substr(0, eq), v = line.substr(eq + 1);
+    if (k == "variant") variant = atoi(v.c_str());
+    else if (k == "stages") stages = atoi(v.c_str());
+    else if (k == "seg_blocks") seg = atoi(v.c_str());
+    else if (k == "nr0") nr = atoi(v.c_str());
+    else if (k == "nsg") nsg = atoi(v.c_str());
+    else if (k == "ctas_per_sm") cps = atoi(v.c_str());
+    else if (k == "ms") ms = atof(v.c_str());
+  }
+  if (variant < 0 || nr < 0 || nsg < 0 || cps < 0 || ms < 0) return KS_ERR_STATE;
+  plan->variant = (variant & 0xFF) | ((stages & 0xFF) << 8) | ((seg & 0xFF) << 16);
+  plan->nr = nr;
+  plan->nwarps = nsg;
+  plan->ctas_per_sm = cps;
+  plan->ms = (float)ms;
+  return KS_OK;
+}
+
+int ks_plan_set(ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok, const ks_plan* plan) {
+  if (!ctx || !op) return KS_ERR_INVALID;
+  const std::string key = ks_plan_key(op, rows, cols, n_tok);
+  if (plan) ctx->plans[key] = *plan;
+  else ctx->plans.erase(key);
+  return KS_OK;
+}
+
+int ks_plan_get(const ks_ctx* ctx, const char* op, size_t rows, size_t cols, int n_tok, ks_plan* out) {
+  if (!ctx || !op || !out) return KS_ERR_INVALID;
+  const ks_plan* p = ks_plan_lookup(ctx, op, rows, cols, n_tok);
+  if (!p) return KS_ERR_STATE;
+  *out = *p;
+  return KS_OK;
+}
+
+// Candidate plans of one op (beam.rs:26-65 keeps the grid "modest so load-time warm stays practical").
+int ks_plan_candidates(const char* op, ks_plan* out, int max_out) {
+  if (!op || !out) return 0;
+  const bool q6 = strstr(op, "q6k") != nullptr;
+  const bool gu = strncmp(op, "gu_", 3) == 0;
+  std::vector<ks_plan> c;
+  for (int nw : {4, 6, 8})
+    for (int cps : {1, 2})
+      for (int st : {0, 2})
+        for (int nr : {1, 2}) {
+          if ((q6 || gu) && nr != 1) continue;
+          c.push_back(ks_plan{st << 8, nr, nw, cps, 0.f});
+        }
+  for (int nr : {2, 4})  // the direct-load kernels
+    for (int cps : {2, 4}) c.push_back(ks_plan{1, nr, 8, cps, 0.f});
+  const int n = std::min<int>((int)c.size(), max_out);
+  for (int i = 0; i < n; i++) out[i] = c[i];
+  return n;
+}
+
+// Times every candidate on synthetic weights of the op's shape and keeps the fastest
+// (CG:178-246; K:2015-2031 times warm-up + median of 3 -- here: a CUDA graph of `reps` launches
+// over rotating weight copies, best of 3 replays, device time from CUDA events).
+// op: "mv_q4k", "mv_q6k", "gu_q4k" (gate||up), "qkv_q4k" (rows = q rows, kv_rows given).
+int ks_plan_search(ks_ctx* ctx, const char* op, size_t rows, size_t kv_rows, size_t cols, int n_tok, ks_plan* best_out) {
+  if (!ctx || !op) return KS_ERR_INVALID;
+  const bool q6 = strstr(op, "q6k") != nullptr;
+  const bool gu = strncmp(op, "gu_", 3) == 0, qkv = strncmp(op, "qkv_", 4) == 0;
+  const ks_dtype wd = q6 ? KS_Q6K : KS_Q4K;
+  KS_REQUIRE(ctx, cols % 256 == 0 && rows > 0 && n_tok >= 1 && n_tok <= 8, "plan_search: bad shape");
+  const std::string key = ks_plan_key(op, qkv ? rows + 2 * kv_rows : rows, cols, n_tok);
+  const bool force = getenv("KSEARCH_BEAM_FORCE") != nullptr;
+  ks_plan cached{};
+  if (!force && ks_plan_file_load(nullptr, key.c_str(), ctx->chip.c_str(), &cached) == KS_OK) {
+    ctx->plans[key] = cached;
+    if (best_out) *best_out = cached;
+    return KS_OK;
+  }
+  if (getenv("KSEARCH_SKIP_BEAM")) return KS_ERR_STATE;  // nothing cached and no search wanted: defaults apply
+
+  // synthetic operands: enough distinct weight copies that no launch finds its matrix in L2
+  const size_t total_rows = qkv ? rows + 2 * kv_rows : (gu ? 2 * rows : rows);
+  const size_t mat_bytes = total_rows * (cols / 256) * ks_block_bytes(wd);
+  int copies = (int)std::min<size_t>(24, std::max<size_t>(2, (size_t)(192u << 20) / mat_bytes + 1));
+  void *W = nullptr, *x = nullptr, *y = nullptr;
+  cudaError_t e = cudaMalloc(&W, mat_bytes * copies);
+  if (e == cudaSuccess) e = cudaMalloc(&x, (size_t)n_tok * cols * 4);
+  if (e == cudaSuccess) e = cudaMalloc(&y, (size_t)n_tok * total_rows * 4);
+  if (e != cudaSuccess) {
+    cudaFree(W); cudaFree(x); cudaFree(y);
+    return ks_fail(ctx, KS_ERR_OOM, "plan_search: %s", cudaGetErrorString(e));
+  }
+  // byte pattern 0x11..: small finite scales and weights (fp16 0x1111 ~ 1e-4), so nothing overflows
+  cudaMemsetAsync(W, 0x11, mat_bytes * copies, ctx->stream);
+  cudaMemsetAsync(x, 0, (size_t)n_tok * cols * 4, ctx->stream);
+
+  ks_plan cand[64];
+  const int nc = ks_plan_candidates(op, cand, 64);
+  const bool had_override = ctx->has_override;
+  const ks_plan saved = ctx->override_plan;
+  const uint64_t launches0 = ctx->launches;
+  ks_plan best{};
+  best.ms = 1e30f;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  for (int i = 0; i < nc; i++) {
+    ctx->has_override = true;
+    ctx->override_plan = cand[i];
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) break;
+    int rc = KS_OK;
+    for (int c = 0; c < copies && rc == KS_OK; c++) {
+      const uint8_t* w = (const uint8_t*)W + (size_t)c * mat_bytes;
+      const size_t rb = (cols / 256) * ks_block_bytes(wd);
+      if (gu) {
+        ks_mv_seg s[2] = {{w, y, (unsigned)rows}, {w + rows * rb, y, (unsigned)rows}};
+        rc = ks_launch_matvec(ctx, wd, s, 2, KS_EPI_GATE_UP, cols, KS_F32, x, n_tok, nullptr);
+      } else if (qkv) {
+        ks_mv_seg s[3] = {{w, y, (unsigned)rows},
+                          {w + rows * rb, (float*)y + rows, (unsigned)kv_rows},
+                          {w + (rows + kv_rows) * rb, (float*)y + rows + kv_rows, (unsigned)kv_rows}};
+        rc = ks_launch_matvec(ctx, wd, s, 3, KS_EPI_PLAIN, cols, KS_F32, x, n_tok, nullptr);
+      } else {
+        ks_mv_seg s{w, y, (unsigned)rows};
+        rc = ks_launch_matvec(ctx, wd, &s, 1, KS_EPI_PLAIN, cols, KS_F32, x, n_tok, nullptr);
+      }
+    }
+    cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+    if (rc != KS_OK || ce != cudaSuccess || cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+      if (graph) cudaGraphDestroy(graph);
+      cudaGetLastError();
+      continue;  // a candidate that does not fit this shape is simply skipped
+    }
+    cudaGraphLaunch(exec, ctx->stream);  // warm-up
+    float best_ms = 1e30f;
+    for (int rep = 0; rep < 3; rep++) {
+      cudaEventRecord(e0, ctx->stream);
+      cudaGraphLaunch(exec, ctx->stream);
+      cudaEventRecord(e1, ctx->stream);
+      cudaEventSynchronize(e1);
+      float ms = 0;
+      cudaEventElapsedTime(&ms, e0, e1);
+      best_ms = std::min(best_ms, ms / copies);
+    }
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    if (best_ms < best.ms) {
+      best = cand[i];
+      best.ms = best_ms;
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  ctx->has_override = had_override;
+  ctx->override_plan = saved;
+  ctx->launches = launches0;
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(W); cudaFree(x); cudaFree(y);
+  if (best.ms >= 1e29f) return ks_fail(ctx, KS_ERR_STATE, "plan_search: no candidate ran for %s", key.c_str());
+  ctx->plans[key] = best;
+  ks_plan_file_save(nullptr, key.c_str(), ctx->chip.c_str(), &best);
+  if (best_out) *best_out = best;
+  return KS_OK;
+}
+
+}  // extern "C"

@@ -65,6 +65,7 @@ template <int G, int DPL, typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uint8_t* K, const uint8_t* V,
                  size_t slot_stride, const float* meta, float* tmp, T* out, int n_splits) {
+  ks_pdl_entry();
   constexpr int HD = DPL * 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split = blockIdx.x, kvh = blockIdx.y, slot = blockIdx.z;
@@ -167,6 +168,7 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
 // Merge the per-split records of one (slot, head): lower.rs:5897-6088.
 template <typename T>
 __global__ void sdpa_reduce_kernel(unsigned hd, const float* tmp, T* out, int n_splits) {
+  ks_pdl_entry();
   const size_t sh = blockIdx.x;  // slot * n_q + head
   const float* rec0 = tmp + sh * n_splits * (hd + 2);
   for (unsigned d = threadIdx.x; d < hd; d += blockDim.x) {
@@ -187,7 +189,7 @@ __global__ void sdpa_reduce_kernel(unsigned hd, const float* tmp, T* out, int n_
 template <int G, int DPL, typename T>
 int launch_part(ks_ctx* ctx, dim3 grid, unsigned n_q, unsigned n_kv, float scale, const void* q, const uint8_t* K,
                 const uint8_t* V, size_t slot_stride, const float* meta, float* tmp, void* out, int n_splits) {
-  sdpa_part_kernel<G, DPL, T><<<grid, kWarps * 32, 0, ctx->stream>>>(n_q, n_kv, scale, (const T*)q, K, V, slot_stride, meta,
+  KS_LAUNCH(ctx, (sdpa_part_kernel<G, DPL, T>), grid, kWarps * 32, 0, n_q, n_kv, scale, (const T*)q, K, V, slot_stride, meta,
                                                                    tmp, (T*)out, n_splits);
   return ks_after_launch(ctx, "sdpa_part");
 }
@@ -224,9 +226,9 @@ int ks_launch_sdpa(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t 
   if (rc || n_splits == 1) return rc;
   const unsigned blocks = (unsigned)(n_slots * n_q);
   if (act == KS_F32)
-    sdpa_reduce_kernel<float><<<blocks, 128, 0, ctx->stream>>>((unsigned)hd, tmp, (float*)out, n_splits);
+    KS_LAUNCH(ctx, (sdpa_reduce_kernel<float>), blocks, 128, 0, (unsigned)hd, tmp, (float*)out, n_splits);
   else
-    sdpa_reduce_kernel<__half><<<blocks, 128, 0, ctx->stream>>>((unsigned)hd, tmp, (__half*)out, n_splits);
+    KS_LAUNCH(ctx, (sdpa_reduce_kernel<__half>), blocks, 128, 0, (unsigned)hd, tmp, (__half*)out, n_splits);
   return ks_after_launch(ctx, "sdpa_reduce");
 }
 

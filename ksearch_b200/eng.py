@@ -228,6 +228,30 @@ class Eng:
         """K:953"""
         ctx.check(ctx.lib.ks_matvec_gate_up_gelu(ctx.h, rows, cols, weight_dtype, w_gate.h, w_up.h, self.act, x.h, y.h))
 
+    # ---- RMSNorm fused into the following matvec (optionally with the residual update in front)
+    @staticmethod
+    def _h(b):
+        return None if b is None else b.h
+
+    def rmsnorm_matvec_wd(self, ctx, rows, cols, eps, weight_dtype, x, w_norm, a, y, y_prev=None, w_post=None, out_x=None):
+        """K:278"""
+        ctx.check(ctx.lib.ks_rmsnorm_matvec(ctx.h, rows, cols, eps, weight_dtype, self.act, x.h, w_norm.h, a.h, y.h,
+                                            self._h(y_prev), self._h(w_post), self._h(out_x)))
+
+    def rmsnorm_matvec_qkv_wd(self, ctx, q_rows, kv_rows, cols, eps, weight_dtype, x, w_norm, wq, wk, wv, q, k, v,
+                              y_prev=None, w_post=None, out_x=None):
+        """K:341"""
+        ctx.check(ctx.lib.ks_rmsnorm_matvec_qkv(ctx.h, q_rows, kv_rows, cols, eps, weight_dtype, self.act, x.h, w_norm.h,
+                                                wq.h, wk.h, wv.h, q.h, k.h, v.h, self._h(y_prev), self._h(w_post),
+                                                self._h(out_x)))
+
+    def rmsnorm_matvec_gate_up_gelu_wd(self, ctx, rows, cols, eps, weight_dtype, x, w_norm, w_gate, w_up, y,
+                                       y_prev=None, w_post=None, out_x=None):
+        """K:1004"""
+        ctx.check(ctx.lib.ks_rmsnorm_matvec_gate_up_gelu(ctx.h, rows, cols, eps, weight_dtype, self.act, x.h, w_norm.h,
+                                                         w_gate.h, w_up.h, y.h, self._h(y_prev), self._h(w_post),
+                                                         self._h(out_x)))
+
     # ---- RMSNorm family ---------------------------------------------------
     def rmsnorm(self, ctx, n, eps, x, w, y):
         """K:456"""

@@ -143,6 +143,10 @@ class GemmaCudaModel:
             a = a.astype(np.float16)
         self.ctx.check(self.lib.ks_model_upload_tensor(self.h, name.encode(), a.ctypes.data, a.nbytes))
 
+    def warm_plans(self, n_tok: int = 1) -> int:
+        """Load-time BEAM warm (gemma_prim.rs:254-290): search or load the launch plan of every matvec shape."""
+        return self.lib.ks_model_warm_plans(self.h, n_tok)
+
     def weight_bytes(self) -> int:
         return self.lib.ks_model_weight_bytes(self.h)
 

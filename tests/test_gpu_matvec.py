@@ -198,3 +198,60 @@ def test_matvec_errors(ctx):
         e.matvec_wd_at(ctx, 8, 512, Q4K, W, x, 0, y, 4)
     with pytest.raises(KsError):
         e.matvec_gate_up_gelu_wd(ctx, 8, 512, Q6K, W, W, x, y)
+
+
+@pytest.mark.parametrize("act", [F32, F16])
+def test_rmsnorm_fused_into_matvec(ctx, oracle, act):
+    """K:278 / K:379 / K:1004 and the fused residual update: same numbers as norm kernel + matvec."""
+    e = Eng(act)
+    npdt = np.float32 if act == F32 else np.float16
+    cols, rows, kv_rows, eps = 1536, 512, 256, 1e-6
+    sig = 0.01 if act == F32 else 0.0005
+    W, Wk, Wv = (_gen(Q4K, 72, n, r, cols, sigma=sig) for n, r in (("q", rows), ("k", kv_rows), ("v", kv_rows)))
+    x = (synth.normals(72, "x", cols) * 2).astype(npdt)
+    yp = synth.normals(72, "yp", cols).astype(npdt)
+    wn = synth.norm_weight(72, "wn", cols).astype(npdt)
+    wp = synth.norm_weight(72, "wp", cols).astype(npdt)
+    bx, byp, bwn, bwp = map(ctx.buffer_bytes, (x, yp, wn, wp))
+    f = lambda a: a.astype(np.float32)
+    tol = dict(rtol=1e-3, atol=1e-4) if act == F32 else dict(rtol=4e-3, atol=4e-3)
+
+    # plain norm + matvec
+    x2 = oracle.rmsnorm(f(x), f(wn), eps)
+    if act == F16:
+        x2 = x2.astype(np.float16).astype(np.float32)
+    y = ctx.buffer_empty_bytes(rows * x.itemsize)
+    e.rmsnorm_matvec_wd(ctx, rows, cols, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y)
+    _, y64 = oracle.matvec(Q4K, W, rows, cols, x2)
+    assert_close(ctx.read_act(y, rows, act), y64, what="rmsnorm_matvec", **tol)
+
+    # residual update + norm + fused QKV
+    ox, ox2 = oracle.rmsnorm_add_then_rmsnorm(f(yp), f(wp), f(x), f(wn), eps)
+    if act == F16:
+        ox2 = oracle.rmsnorm(ox.astype(np.float16).astype(np.float32), f(wn), eps).astype(np.float16).astype(np.float32)
+    q, k, v = (ctx.buffer_empty_bytes(r * x.itemsize) for r in (rows, kv_rows, kv_rows))
+    out_x = ctx.buffer_empty_bytes(x.nbytes)
+    e.rmsnorm_matvec_qkv_wd(ctx, rows, kv_rows, cols, eps, Q4K, bx, bwn, *map(ctx.buffer_bytes, (W, Wk, Wv)), q, k, v,
+                            y_prev=byp, w_post=bwp, out_x=out_x)
+    assert_close(ctx.read_act(out_x, cols, act), ox, what="out_x", **(dict(rtol=1e-3, atol=1e-4) if act == F32 else dict(rtol=2e-3, atol=2e-3)))
+    for buf, Wm, r in ((q, W, rows), (k, Wk, kv_rows), (v, Wv, kv_rows)):
+        _, y64 = oracle.matvec(Q4K, Wm, r, cols, ox2)
+        assert_close(ctx.read_act(buf, r, act), y64, what="fused qkv", **tol)
+
+    # gate/up with the norm fused
+    Wg, Wu = _gen(Q4K, 72, "g", rows, cols, sigma=0.0005), _gen(Q4K, 72, "u", rows, cols, sigma=0.0005)
+    yy = ctx.buffer_empty_bytes(rows * x.itemsize)
+    e.rmsnorm_matvec_gate_up_gelu_wd(ctx, rows, cols, eps, Q4K, bx, bwn, ctx.buffer_bytes(Wg), ctx.buffer_bytes(Wu), yy)
+    _, g64 = oracle.matvec(Q4K, Wg, rows, cols, x2)
+    _, u64 = oracle.matvec(Q4K, Wu, rows, cols, x2)
+    want = oracle.gelu_mul(g64.astype(np.float32), u64.astype(np.float32))
+    got = ctx.read_act(yy, rows, act)
+    k_ = 1.0 if act == F32 else 4.0
+    assert np.all(np.abs(got - want) <= k_ * (1e-4 + 2e-3 * np.abs(want) + 1e-4 * (np.abs(g64) + np.abs(u64))))
+
+    with pytest.raises(KsError, match="alias"):
+        e.rmsnorm_matvec_wd(ctx, rows, cols, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y, y_prev=byp, w_post=bwp, out_x=bx)
+    with pytest.raises(KsError, match="go together"):
+        e.rmsnorm_matvec_wd(ctx, rows, cols, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y, y_prev=byp)
+    with pytest.raises(KsError):   # 6144 columns: no fused norm
+        e.rmsnorm_matvec_wd(ctx, 8, 6144, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y)

@@ -128,6 +128,26 @@ def test_model_errors(ctx):
         ksm.GemmaCudaModel(ctx, bad)
 
 
+def test_model_with_dependent_launch_matches(oracle):
+    """Context flag bit 0: kernels start before their predecessor ends (weights prefetched early).
+    The token stream must not change."""
+    from ksearch_b200 import CudaContext
+    cfg = ksm.tiny_config(max_seq=48)
+    prompt = synth.token_ids(12, "prompt", 8, cfg.vocab)
+    outs = []
+    for flags in (0, 1):
+        c = CudaContext(0, flags=flags)
+        model = ksm.GemmaCudaModel.synthetic(c, cfg, seed=12)
+        model.slot_alloc()
+        toks, _ = model.generate_timed(prompt, 24)
+        outs.append(toks)
+        model.forward(0, 1, [3], True)
+        c.synchronize()
+        model.close()
+        c.close()
+    assert outs[0] == outs[1]
+
+
 def test_f16_activation_model_runs_close(ctx, oracle):
     """The reference's activation dtype (f16 in/out of every op, f32 accumulation)."""
     cfg = ksm.tiny_config(max_seq=16, act=F16)
