@@ -209,6 +209,19 @@ int ks_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_d
 /* K:1966 softcap_argmax: index of max cap*tanh(x/cap), ties to the lower index, written as one f32. */
 int ks_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const ks_buf* logits, ks_buf* out_idx,
                       size_t out_off);
+/* No counterpart in the reference.  The same arg-max as ks_softcap_argmax (f32 logits) for callers that
+ * cannot allocate device memory and so cannot own a ks_ctx (whose creation allocates): a host runtime
+ * that pre-carved all device memory into its own arena, a plugin under a fixed memory budget, code that
+ * must not trigger the implicit synchronisation of cudaMalloc.  It takes raw device pointers and a
+ * stream (NULL = the default stream) and allocates nothing: the cross-block scratch is a fixed array
+ * inside the library image (about 4 KB; every GPU that loads the library holds it until exit).
+ *  - n <= 4,194,304 (KS_ERR_INVALID beyond; message via ks_last_error(NULL)).
+ *  - The first call on a device looks up the array's device address; make that first call outside
+ *    any stream capture.
+ *  - All calls share the array: two calls that may overlap on the GPU (different streams) race.
+ *    Calls on one stream are safe; the arrival counter is cleared on the stream before each launch. */
+int ks_softcap_argmax_noalloc(int device, void* stream, size_t n, float cap, const float* logits_dev,
+                              float* out_idx_dev);
 /* K:695 gelu_mul: y = gelu_tanh(clamp(g)) * u (the unfused fallback of the gate/up path). */
 int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_buf* u, ks_buf* y);
 

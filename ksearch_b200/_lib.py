@@ -75,6 +75,7 @@ SIGNATURES = {
     "ks_quantize_q40": (_i, [_vp, _sz, _i, _vp, _sz, _vp, _sz]),
     "ks_copy_scale_indexed": (_i, [_vp, _sz, _sz, _f, _i, _vp, _vp, _sz, _i, _vp]),
     "ks_softcap_argmax": (_i, [_vp, _sz, _f, _i, _vp, _vp, _sz]),
+    "ks_softcap_argmax_noalloc": (_i, [_i, _vp, _sz, _f, _vp, _vp]),
     "ks_gelu_mul": (_i, [_vp, _sz, _i, _vp, _vp, _vp]),
     "ks_model_create": (_vp, [_vp, _vp]),
     "ks_model_destroy": (None, [_vp]),

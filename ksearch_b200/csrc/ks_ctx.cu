@@ -24,6 +24,9 @@ int ks_after_launch(ks_ctx* ctx, const char* what) {
 
 static thread_local std::string g_create_err;
 
+// Message for calls that have no context to hang an error on; read back with ks_last_error(NULL).
+void ks_set_global_error(const char* msg) { g_create_err = msg ? msg : ""; }
+
 extern "C" {
 
 ks_ctx* ks_ctx_create(int device, uint64_t flags) {

@@ -41,6 +41,7 @@ struct ks_buf {
 };
 
 int ks_fail(ks_ctx* ctx, int code, const char* fmt, ...);
+void ks_set_global_error(const char* msg);
 
 #define KS_REQUIRE(ctx, cond, ...)                              \
   do {                                                          \

@@ -550,3 +550,66 @@ int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_b
 }
 
 }  // extern "C"
+
+// ---- arg-max for callers that must not allocate ---------------------------------------------------
+// Some hosts hand this library device pointers but may not create device allocations themselves:
+// a runtime that carved all of HBM into its own arena up front, a plugin loaded into a process
+// whose memory budget is fixed, code running where cudaMalloc would synchronise a device it does
+// not own.  ks_softcap_argmax needs a little global scratch for its cross-block reduction and takes
+// it from the context, which cudaMalloc'ed it; this variant needs no context at all and keeps that
+// scratch in a fixed array inside the library image instead.
+#define KS_NOALLOC_MAX_N (1u << 22)   /* largest logits vector accepted */
+#define KS_NOALLOC_MAX_BLOCKS 512
+// [0, 512) f32 block maxima | [512, 1024) u32 block indices | [1024] u32 arrival counter
+static __device__ __align__(256) unsigned ks_noalloc_scratch[KS_NOALLOC_MAX_BLOCKS * 2 + 64];
+
+extern "C" int ks_softcap_argmax_noalloc(int device, void* stream, size_t n, float cap, const float* logits,
+                                         float* out_idx) {
+  static void* scratch_addr[64] = {nullptr};  // device address of the array, per device
+  char msg[256];
+  if (!logits || !out_idx || n == 0 || !(cap > 0.0f) || device < 0 || device >= 64) {
+    ks_set_global_error("softcap_argmax_noalloc: null pointer, n == 0, cap <= 0 or bad device index");
+    return KS_ERR_INVALID;
+  }
+  if (n > KS_NOALLOC_MAX_N) {
+    snprintf(msg, sizeof msg, "softcap_argmax_noalloc: n=%zu exceeds the fixed-scratch limit of %u elements", n, KS_NOALLOC_MAX_N);
+    ks_set_global_error(msg);
+    return KS_ERR_INVALID;
+  }
+  int prev = -1;
+  cudaGetDevice(&prev);
+  cudaError_t e = cudaSetDevice(device);
+  if (e == cudaSuccess && !scratch_addr[device]) {
+    // In host code the array's name is only a handle; the kernel needs the device-side address,
+    // looked up once per device with that device current.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, ks_noalloc_scratch);
+    if (e == cudaSuccess) scratch_addr[device] = p;
+  }
+  if (e != cudaSuccess) {
+    snprintf(msg, sizeof msg, "softcap_argmax_noalloc: set-up on device %d failed: %s", device, cudaGetErrorString(e));
+    ks_set_global_error(msg);
+    if (prev >= 0) cudaSetDevice(prev);
+    return KS_ERR_CUDA;
+  }
+  unsigned* base = (unsigned*)scratch_addr[device];
+  float* ws_val = (float*)base;
+  unsigned* ws_idx = base + KS_NOALLOC_MAX_BLOCKS;
+  unsigned* counter = base + 2 * KS_NOALLOC_MAX_BLOCKS;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps whatever the last call left: the arrival counter has to start at zero
+  e = cudaMemsetAsync(counter, 0, sizeof(unsigned), st);
+  unsigned grid = (unsigned)((n + 1023) / 1024);
+  if (grid > KS_NOALLOC_MAX_BLOCKS) grid = KS_NOALLOC_MAX_BLOCKS;
+  if (e == cudaSuccess) {
+    softcap_argmax_kernel<float><<<grid, 256, 0, st>>>((unsigned)n, cap, logits, out_idx, ws_val, ws_idx, counter);
+    e = cudaGetLastError();
+  }
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    snprintf(msg, sizeof msg, "softcap_argmax_noalloc: launch failed: %s", cudaGetErrorString(e));
+    ks_set_global_error(msg);
+    return KS_ERR_CUDA;
+  }
+  return KS_OK;
+}
