@@ -133,6 +133,31 @@ int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scal
                                  const void* src, const float* idx, ks_dtype act, void* dst);
 int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);
 
+// ---- all layers of one token as ONE persistent kernel (ks_mega.cu) --------------------------------
+struct ks_mega_layer {
+  const void *wq, *wk, *wv, *wo, *wgate, *wup, *wdown;  // Q4_K
+  const void *attn_norm, *q_norm, *k_norm, *post_attn_norm, *ffn_norm, *post_ffw_norm;  // f32
+  uint8_t *kv_k, *kv_v;  // this slot's cache rows [max_seq, n_kv, hd] Q4_0
+};
+struct ks_mega_desc {
+  int n_layers;
+  unsigned hidden, ffn, n_q, n_kv, hd;
+  float eps, attn_scale;
+  const float* rope;  // [max_seq, hd]
+  const int* pos;     // device: position of the token being processed
+  float *x_a, *x_b;   // residual stream ping-pong; the token's embedding is in x_a on entry
+  float *yb, *q, *k, *v, *o, *ff;
+  float* att_tmp;     // n_q * n_splits * (hd + 2) floats
+  int n_splits;
+};
+struct ks_mega;
+// *out == nullptr with KS_OK: shape not covered, keep the launch-per-op path.
+int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* layers, ks_mega** out);
+int ks_mega_launch(ks_ctx* ctx, ks_mega* mg);
+float* ks_mega_residual(const ks_mega* mg);  // where the residual stream is when the kernel ends (yb holds the last down-proj)
+const long long* ks_mega_prof(const ks_mega* mg);  // [2][phases][4] clock stamps of the last token (first, last block)
+void ks_mega_destroy(ks_mega* mg);
+
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Every kernel of the library is launched through ks_launch_k.  When the context was created with
 // flag bit 0, the launch carries the programmatic-stream-serialization attribute: the kernel may

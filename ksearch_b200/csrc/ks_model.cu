@@ -86,6 +86,9 @@ struct ks_model {
   std::map<uint64_t, size_t> graph_nodes;
   std::vector<void*> owned;
   int tok_src = 0;  // which half of the ping-pong holds the next input ids
+  // one persistent decode kernel per slot (nullptr entry: shape not covered, tried once)
+  std::map<int, ks_mega*> mega;
+  bool use_mega = false;
 };
 
 namespace {
@@ -248,16 +251,96 @@ int enqueue_forward_fused(ks_model* m, int first, int n, int src, bool want_logi
   return KS_OK;
 }
 
+// One slot's token with every layer inside one persistent kernel; embedding before, head after.
+int enqueue_forward_mega(ks_model* m, ks_mega* mg, int first, int src, bool want_logits) {
+  ks_ctx* c = m->ctx;
+  const ks_model_config& g = m->cfg;
+  const size_t H = g.hidden;
+  float* cur = (float*)m->x + (size_t)first * H;
+  float* yb = (float*)m->x2 + (size_t)first * H;
+  float* xn = (float*)m->xn + (size_t)first * H;
+  float* logits = (float*)m->logits + (size_t)first * g.vocab;
+  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
+  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  int* pos = m->pos + first;
+  int rc;
+  if ((rc = ks_launch_copy_scale_indexed(c, H, 1, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, KS_F32, cur))) return rc;
+  if ((rc = ks_mega_launch(c, mg))) return rc;
+  KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, 1, pos);
+  if ((rc = ks_after_launch(c, "end_token"))) return rc;
+  if (!want_logits) return KS_OK;
+  float* res = ks_mega_residual(mg);
+  if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, 1, g.eps, KS_F32, yb, m->layers[g.n_layers - 1].post_ffw_norm.dptr, res,
+                                               m->output_norm.dptr, res, xn)))
+    return rc;
+  ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
+  if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, KS_F32, xn, 1, nullptr))) return rc;
+  return ks_launch_softcap_argmax(c, g.vocab, g.softcap, KS_F32, logits, tok_out);
+}
+
+// The persistent kernel of slot `first`, built on first use (outside any stream capture).
+int get_mega(ks_model* m, int first, ks_mega** out) {
+  *out = nullptr;
+  if (!m->use_mega) return KS_OK;
+  auto it = m->mega.find(first);
+  if (it != m->mega.end()) {
+    *out = it->second;
+    return KS_OK;
+  }
+  const ks_model_config& g = m->cfg;
+  const size_t H = g.hidden, F = g.ffn, qn = (size_t)g.n_q * g.hd, kvn = (size_t)g.n_kv * g.hd;
+  ks_mega_desc d{};
+  d.n_layers = g.n_layers;
+  d.hidden = (unsigned)H; d.ffn = (unsigned)F; d.n_q = (unsigned)g.n_q; d.n_kv = (unsigned)g.n_kv; d.hd = (unsigned)g.hd;
+  d.eps = g.eps; d.attn_scale = g.attn_scale;
+  d.rope = m->rope;
+  d.pos = m->pos + first;
+  d.x_a = (float*)m->x + (size_t)first * H;
+  d.x_b = (float*)m->xb + (size_t)first * H;
+  d.yb = (float*)m->x2 + (size_t)first * H;
+  d.q = (float*)m->q + (size_t)first * qn;
+  d.k = (float*)m->k + (size_t)first * kvn;
+  d.v = (float*)m->v + (size_t)first * kvn;
+  d.o = (float*)m->o + (size_t)first * qn;
+  d.ff = (float*)m->ff + (size_t)first * F;
+  d.att_tmp = m->attn_tmp + (size_t)first * g.n_q * m->n_splits * (g.hd + 2);
+  d.n_splits = m->n_splits;
+  std::vector<ks_mega_layer> ls(g.n_layers);
+  for (int l = 0; l < g.n_layers; l++) {
+    const Layer& L = m->layers[l];
+    ks_mega_layer& o = ls[l];
+    o.wq = L.wq.dptr; o.wk = L.wk.dptr; o.wv = L.wv.dptr; o.wo = L.wo.dptr;
+    o.wgate = L.wgate.dptr; o.wup = L.wup.dptr; o.wdown = L.wdown.dptr;
+    o.attn_norm = L.attn_norm.dptr; o.q_norm = L.q_norm.dptr; o.k_norm = L.k_norm.dptr;
+    o.post_attn_norm = L.post_attn_norm.dptr; o.ffn_norm = L.ffn_norm.dptr; o.post_ffw_norm = L.post_ffw_norm.dptr;
+    o.kv_k = m->kv_k[l] + (size_t)first * m->slot_stride;
+    o.kv_v = m->kv_v[l] + (size_t)first * m->slot_stride;
+  }
+  ks_mega* mg = nullptr;
+  int rc = ks_mega_create(m->ctx, &d, ls.data(), &mg);
+  if (rc) return rc;
+  m->mega[first] = mg;
+  *out = mg;
+  return KS_OK;
+}
+
 // Launch the forward pass through a cached graph (captured on first use).
 int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
   ks_ctx* c = m->ctx;
   const uint64_t key = ((uint64_t)first << 32) | ((uint64_t)n << 8) | ((uint64_t)src << 1) | (want_logits ? 1 : 0);
   auto it = m->graphs.find(key);
   if (it == m->graphs.end()) {
+    ks_mega* mg = nullptr;
+    if (n == 1) {
+      int rcm = get_mega(m, first, &mg);
+      if (rcm) return rcm;
+    }
     cudaGraph_t graph = nullptr;
     KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     const uint64_t before = c->launches;
-    int rc = m->fused ? enqueue_forward_fused(m, first, n, src, want_logits) : enqueue_forward(m, first, n, src, want_logits);
+    int rc = mg ? enqueue_forward_mega(m, mg, first, src, want_logits)
+             : m->fused ? enqueue_forward_fused(m, first, n, src, want_logits)
+                        : enqueue_forward(m, first, n, src, want_logits);
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
     c->launches = before;  // captured launches are counted when the graph replays
     if (rc) {
@@ -353,6 +436,9 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   m->seq_len.assign(g.n_slots, 0);
   const size_t S = g.n_slots;
   m->fused = ks_matvec_can_fuse_pro(KS_Q4K, H) && !getenv("KSEARCH_UNFUSED");
+  // KSEARCH_DECODE_KERNEL=1: single-slot steps run all layers inside one persistent kernel
+  const char* dk = getenv("KSEARCH_DECODE_KERNEL");
+  m->use_mega = m->fused && g.act == KS_F32 && dk && dk[0] == '1';
   ok = ok && dev_alloc(m, &m->xb, S * H * ab) == KS_OK && dev_alloc(m, &m->xn, S * H * ab) == KS_OK;
   ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
        dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&
@@ -363,7 +449,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
        dev_alloc(m, (void**)&m->rope, (size_t)g.max_seq * g.hd * sizeof(float)) == KS_OK;
   if (ok) {
     m->n_splits = ks_sdpa_pick_splits(ctx, 1, g.n_kv, g.max_seq);
-    ok = dev_alloc(m, (void**)&m->attn_tmp, (ks_sdpa_tmp_floats(S, g.n_q, g.hd, m->n_splits) + 4) * sizeof(float)) == KS_OK;
+    ok = dev_alloc(m, (void**)&m->attn_tmp, (S * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
   }
   if (ok) {
     // RoPE table: per position hd f32 = cos[hd/2] || sin[hd/2], freq_i = theta^(-2i/hd) (gemma_prim.rs:33-56)
@@ -419,6 +505,7 @@ void ks_model_destroy(ks_model* m) {
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
   for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : m->mega) ks_mega_destroy(kv.second);
   for (void* p : m->owned) cudaFree(p);
   if (m->host_tok) cudaFreeHost(m->host_tok);
   delete m;
@@ -619,12 +706,16 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
   return KS_OK;
 }
 
-// Device pointers of the slot's activations, for tests: 0 = residual x, 1 = logits.
+// Device pointers of the slot's state, for tests and profiling: 0 = residual x, 1 = logits, 2 = phase clocks.
 const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
   if (!m || slot < 0 || slot >= m->cfg.n_slots) return nullptr;
   const size_t ab = ks_act_bytes((ks_dtype)m->cfg.act);
   if (which == 0) return (const char*)m->x + (size_t)slot * m->cfg.hidden * ab;
   if (which == 1) return (const char*)m->logits + (size_t)slot * m->cfg.vocab * ab;
+  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][5 * n_layers][4] int64
+    auto it = m->mega.find(slot);
+    return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof(it->second);
+  }
   return nullptr;
 }
 

@@ -148,6 +148,31 @@ def test_model_with_dependent_launch_matches(oracle):
     assert outs[0] == outs[1]
 
 
+@pytest.mark.parametrize("n_kv", [1, 2])
+def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv):
+    """KSEARCH_DECODE_KERNEL=1: every layer of a single-slot step runs inside one persistent kernel
+    (grid barriers between phases).  Same parity bar as the launch-per-op path."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", "1")
+    c = CudaContext(0, flags=1)
+    cfg = ksm.tiny_config(max_seq=80, n_kv=n_kv)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=21, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is None      # not built before the first step
+    _teacher_forced(model, cpu, synth.token_ids(21, "tf", 70, cfg.vocab))   # crosses several attention split counts
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None  # the persistent kernel did run
+    prompt = synth.token_ids(21, "prompt", 8, cfg.vocab)
+    out, _ = model.generate_timed(prompt, 24)
+    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    assert equal + ties == 24 and ties <= 1
+    out2, _ = model.generate_timed(prompt, 24, max_inflight=0)
+    assert out2 == out
+    cpu.close()
+    model.close()
+    c.close()
+
+
 def test_f16_activation_model_runs_close(ctx, oracle):
     """The reference's activation dtype (f16 in/out of every op, f32 accumulation)."""
     cfg = ksm.tiny_config(max_seq=16, act=F16)
