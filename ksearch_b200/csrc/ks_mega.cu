@@ -10,53 +10,59 @@
 //     the copies of the next phases are already in flight while the block waits at a barrier;
 //   * phases (qkv | attention | o-proj | gate-up | down, per layer) are separated by a grid barrier
 //     on one global counter; activations cross it through global memory (L2), read with ld.cg;
-//   * the norms are applied while x is staged (same code path as the stand-alone fused matvec);
+//   * the norms are applied while x is staged; their weights are fetched BEFORE the barrier wait,
+//     because the acquire that ends the wait drops the SM's L1 and every later plain load of a
+//     constant would be a full round trip to L2;
+//   * for the same reason nothing on the critical path reads a descriptor from global memory: the
+//     five phase shapes and the per-layer pointers are copied to shared memory once;
 //   * attention: per-head RMS + RoPE + Q4_0 pack of the new K/V row, split-context online softmax
 //     and the merge of the splits (last arriving block) happen inside one phase.
 // Every spin (barrier, mbarrier) is bounded; on expiry the block raises the context's status word,
 // drains its copies and leaves, and the other blocks time out the same way.
-#include <vector>
 #include <utility>
+#include <vector>
 
 #include "ks_mv_common.cuh"
 
 namespace {
 
 enum { MG_MATVEC = 0, MG_GATE_UP = 1, MG_ATTN = 2 };
+enum { PH_QKV = 0, PH_ATTN = 1, PH_OPROJ = 2, PH_GATEUP = 3, PH_DOWN = 4, PH_PER_LAYER = 5 };
 
-struct MegaPhase {
+struct MegaShape {          // one of the five phases of a layer; the same for every layer
   int type;
   int n_seg;                // matvec: 1 or 3 (q, k, v)
-  const uint8_t* W[3];
-  float* y[3];
   unsigned rows[3];
-  unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups
+  unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups (0 for attention)
   unsigned cols, row_bytes, seg_blocks, n_cseg;
-  const float* x;           // input vector, or the residual stream for ADD_NORM
-  ks_mv_pro pro;
-  // attention only: this layer's KV cache (Q4_0 rows [max_seq, n_kv, hd]) and per-head norm weights
-  uint8_t *kv_k, *kv_v;
-  const float *q_norm, *k_norm;
+};
+
+struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
+  const uint8_t* W[7];      // wq, wk, wv, wo, wgate, wup, wdown (Q4_K)
+  const float* norm[6];     // attn_norm, q_norm, k_norm, post_attn_norm, ffn_norm, post_ffw_norm
+  uint8_t *kv_k, *kv_v;     // this slot's cache rows [max_seq, n_kv, hd] Q4_0
 };
 
 struct MegaArgs {
-  const MegaPhase* phases;
-  int n_phases;
+  const void* tables;       // MegaShape[5] then MegaLayer[n_layers], 16-byte aligned; copied to shared memory at start
+  unsigned tables_bytes;    // multiple of 16
+  int n_layers;
   int stages;               // ring slots per warp
   unsigned slot_bytes;      // bytes per ring slot
-  unsigned x_bytes;         // staging area for x
-  // attention
+  unsigned x_bytes;         // staging area for x (also the attention scratch)
   unsigned n_q, n_kv, hd, n_splits;
   float eps, attn_scale;
   const float* rope;        // [max_seq, hd]
   const int* pos;           // [1]
-  const float *q, *k, *v;   // outputs of the qkv phase
-  float* o;                 // attention output [n_q * hd]
+  float *x_a, *x_b;         // residual stream: layers read x_a / write x_b at the FFN, the reverse at the next qkv
+  float *yb, *q, *k, *v, *o, *ff;
   float* att_tmp;           // [n_q * n_splits * (hd + 2)]
-  unsigned* att_cnt;        // arrival counter of the attention blocks
+  float4* nsum;             // [grid] per-block sums of the last o-proj / down phase: (sum y^2, sum x*y*wp, sum (y*wp)^2, sum x^2)
+  unsigned* att_cnt;        // [n_q] arrival counters of the attention blocks, per head
   unsigned* bar;            // [0] running barrier counter, [1] its value when the previous token ended
   unsigned* err;
-  long long* prof;          // [2][n_phases][4] SM clock stamps of the first and last block (start, staged, computed, released)
+  long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released,
+                            // then warp 0's copy-wait cycles, compute cycles, items
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -92,12 +98,28 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 }
 __device__ __forceinline__ float4 ldcg4(const float* p, unsigned c) { return __ldcg(reinterpret_cast<const float4*>(p) + c); }
 
-// Grid-wide barrier on a monotonically increasing counter.  Returns false when the wait gave up.
-__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, unsigned* err, int* sflag) {
-  __syncthreads();
+// Grid-wide barrier on a monotonically increasing counter, in two halves so that loads which do not
+// depend on other blocks can be issued in between.
+// wsum != nullptr: the eight warps left their partial norm sums there; thread 0 folds them (fixed order) into nsum[block].
+__device__ __forceinline__ void grid_arrive(unsigned* counter, const float4* wsum, float4* nsum) {
+  __syncthreads();  // every store of this block is issued
   if (threadIdx.x == 0) {
+    if (wsum) {
+      float4 t = wsum[0];
+#pragma unroll
+      for (int w = 1; w < 8; w++) {
+        const float4 u = wsum[w];
+        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+      }
+      nsum[blockIdx.x] = t;
+    }
     __threadfence();
     atomicAdd(counter, 1u);
+  }
+}
+// Returns false when the wait gave up.
+__device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, unsigned* err, int* sflag) {
+  if (threadIdx.x == 0) {
     int ok = 0;
     for (unsigned i = 0; i < (1u << 21); i++) {  // a second or two of polling at most
       if ((int)(ld_acquire_u32(counter) - target) >= 0) {
@@ -114,46 +136,83 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
 }
 
 // ---- staging of x (with the fused norm prologues), reads through L2 ---------------------------
-__device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, const MegaPhase& ph) {
-  const unsigned cols = ph.cols, units = cols >> 6, nchunk = cols >> 2;
+// Norm weights of the next matvec phase, fetched into registers before the barrier wait.
+struct NormPre {
+  float4 w[KS_PRO_MAXC], wp[KS_PRO_MAXC];
+};
+__device__ __forceinline__ void mg_prefetch_norm(NormPre& n, int mode, const float* w, const float* wp, unsigned cols) {
+  const unsigned nchunk = cols >> 2;
+  if (mode == KS_PRO_NONE) return;
+#pragma unroll
+  for (int k = 0; k < KS_PRO_MAXC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      n.w[k] = reinterpret_cast<const float4*>(w)[c];
+      if (mode == KS_PRO_ADD_NORM) n.wp[k] = reinterpret_cast<const float4*>(wp)[c];
+    }
+  }
+}
+
+constexpr int MG_XMAX = 8;  // plain staging keeps up to 8 chunks per thread in flight (cols <= 8192), loops beyond
+
+// mode NONE: x' = x.  NORM: x' = rms(x)*w.  ADD_NORM: r = x + rms(y)*wp (block 0 stores r to out_x); x' = rms(r)*w.
+__device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mode, unsigned cols, const float* x,
+                                           const float* y, float* out_x, float eps, const NormPre& n, long long* pf = nullptr) {
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
   float* xp = reinterpret_cast<float*>(xs);
   float* sx = xp + (size_t)units * Q4K_XS;
-  if (ph.pro.mode == KS_PRO_NONE) {
-#pragma unroll 4
-    for (unsigned c = threadIdx.x; c < nchunk; c += blockDim.x) q4k_put_chunk(xp, sx, c, ldcg4(ph.x, c));
+  if (mode == KS_PRO_NONE) {
+    for (unsigned base = 0; base < nchunk; base += MG_XMAX * blockDim.x) {
+      float4 v[MG_XMAX];
+#pragma unroll
+      for (int k = 0; k < MG_XMAX; k++) {
+        const unsigned c = base + threadIdx.x + k * blockDim.x;
+        if (c < nchunk) v[k] = ldcg4(x, c);
+      }
+#pragma unroll
+      for (int k = 0; k < MG_XMAX; k++) {
+        const unsigned c = base + threadIdx.x + k * blockDim.x;
+        if (c < nchunk) q4k_put_chunk(xp, sx, c, v[k]);
+      }
+    }
     return;
   }
   const float invn = 1.0f / (float)cols;
   float4 v[KS_PRO_MAXC], yv[KS_PRO_MAXC];
   float ss = 0.0f;
-  const float* w = reinterpret_cast<const float*>(ph.pro.w);
-  if (ph.pro.mode == KS_PRO_ADD_NORM) {
-    const float* y = reinterpret_cast<const float*>(ph.pro.y);
-    const float* wp = reinterpret_cast<const float*>(ph.pro.w_post);
+  if (mode == KS_PRO_ADD_NORM) {
 #pragma unroll
     for (int k = 0; k < KS_PRO_MAXC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
         yv[k] = ldcg4(y, c);
-        v[k] = ldcg4(ph.x, c);
+        v[k] = ldcg4(x, c);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < KS_PRO_MAXC; k++) {
+      const unsigned c = threadIdx.x + k * blockDim.x;
+      if (c < nchunk) {
         ss = fmaf(yv[k].x, yv[k].x, ss); ss = fmaf(yv[k].y, yv[k].y, ss);
         ss = fmaf(yv[k].z, yv[k].z, ss); ss = fmaf(yv[k].w, yv[k].w, ss);
       }
     }
+    if (pf) pf[4] = clock64();
     ss = block_sum_f(ss, red);
-    const float inv = 1.0f / sqrtf(ss * invn + ph.pro.eps);
+    if (pf) pf[5] = clock64();
+    const float inv = 1.0f / sqrtf(ss * invn + eps);
     ss = 0.0f;
 #pragma unroll
     for (int k = 0; k < KS_PRO_MAXC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
-        const float4 p4 = reinterpret_cast<const float4*>(wp)[c];
+        const float4 p4 = n.wp[k];
         float4 r = v[k];
         r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
         r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
         r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
         r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
-        if (blockIdx.x == 0) reinterpret_cast<float4*>(ph.pro.out_x)[c] = r;
+        if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
         v[k] = r;
       }
     }
@@ -161,7 +220,7 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, const 
 #pragma unroll
     for (int k = 0; k < KS_PRO_MAXC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
-      if (c < nchunk) v[k] = ldcg4(ph.x, c);
+      if (c < nchunk) v[k] = ldcg4(x, c);
     }
   }
 #pragma unroll
@@ -172,13 +231,15 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, const 
       ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
     }
   }
+  if (pf) pf[6] = clock64();
   ss = block_sum_f(ss, red);
-  const float inv2 = 1.0f / sqrtf(ss * invn + ph.pro.eps);
+  if (pf) pf[7] = clock64();
+  const float inv2 = 1.0f / sqrtf(ss * invn + eps);
 #pragma unroll
   for (int k = 0; k < KS_PRO_MAXC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
-      const float4 w4 = reinterpret_cast<const float4*>(w)[c];
+      const float4 w4 = n.w[k];
       float4 r;
       r.x = __fmul_rn(__fmul_rn(v[k].x, inv2), w4.x);
       r.y = __fmul_rn(__fmul_rn(v[k].y, inv2), w4.y);
@@ -189,57 +250,121 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, const 
   }
 }
 
+// ADD_NORM without any block-wide reduction: the blocks that produced y left the four sums that both
+// norms need (K:539 expands to  sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2,  r = x + inv y wp).
+__device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned cols, const float* x, const float* y, float* out_x,
+                                                 float eps, const NormPre& n, const float4* nsum, unsigned nblocks, long long* pf = nullptr) {
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
+  const int lane = threadIdx.x & 31;
+  float* xp = reinterpret_cast<float*>(xs);
+  float* sx = xp + (size_t)units * Q4K_XS;
+  float4 v[KS_PRO_MAXC], yv[KS_PRO_MAXC], ps[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const unsigned i = (unsigned)lane + 32u * j;
+    ps[j] = i < nblocks ? __ldcg(nsum + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < KS_PRO_MAXC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      yv[k] = ldcg4(y, c);
+      v[k] = ldcg4(x, c);
+    }
+  }
+  float4 t = ps[0];
+  if (pf) pf[4] = clock64();
+#pragma unroll
+  for (int j = 1; j < 8; j++) {
+    t.x += ps[j].x; t.y += ps[j].y; t.z += ps[j].z; t.w += ps[j].w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
+    t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
+    t.z += __shfl_xor_sync(0xffffffffu, t.z, o);
+    t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
+  }
+  if (pf) pf[5] = clock64() + (long long)(t.x > 1e30f);
+  const float invn = 1.0f / (float)cols;
+  const float inv = 1.0f / sqrtf(t.x * invn + eps);
+  const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
+  const float inv2 = 1.0f / sqrtf(fmaxf(rr, 0.0f) * invn + eps);
+  if (pf) pf[6] = clock64() + (long long)(inv2 > 1e30f);
+#pragma unroll
+  for (int k = 0; k < KS_PRO_MAXC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      const float4 p4 = n.wp[k], w4 = n.w[k];
+      float4 r = v[k];
+      r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
+      r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
+      r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
+      r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
+      if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
+      float4 q;
+      q.x = __fmul_rn(__fmul_rn(r.x, inv2), w4.x);
+      q.y = __fmul_rn(__fmul_rn(r.y, inv2), w4.y);
+      q.z = __fmul_rn(__fmul_rn(r.z, inv2), w4.z);
+      q.w = __fmul_rn(__fmul_rn(r.w, inv2), w4.w);
+      q4k_put_chunk(xp, sx, c, q);
+    }
+  }
+}
+
 // ---- the per-warp item list of a whole token -----------------------------------------------------
 // Item = (phase, row group, column segment).  Warp gw owns groups gw, gw+GW, ... of every matvec
-// phase.  Two cursors walk the same list: one issues copies, one consumes them.
+// phase.  Two cursors walk the same list: one issues copies, one consumes them.  `sh` is the
+// shared-memory copy of the five shapes.
 struct Cursor {
-  int p;
+  int p;        // phase index = layer * 5 + kind
+  int kind;     // p % 5
   unsigned g, cs;
 };
-__device__ __forceinline__ void cur_settle(Cursor& c, const MegaArgs& a, unsigned gw) {
-  while (c.p < a.n_phases) {
-    const MegaPhase& ph = a.phases[c.p];
-    const unsigned total = ph.type == MG_ATTN ? 0u : ph.grp_start[ph.n_seg];
-    if (c.g < total) return;
+__device__ __forceinline__ unsigned shape_groups(const MegaShape& s) { return s.type == MG_ATTN ? 0u : s.grp_start[s.n_seg]; }
+__device__ __forceinline__ void cur_settle(Cursor& c, const MegaShape* sh, unsigned gw, int n_phases) {
+  while (c.p < n_phases && c.g >= shape_groups(sh[c.kind])) {
     c.p++;
+    c.kind = c.kind == PH_PER_LAYER - 1 ? 0 : c.kind + 1;
     c.g = gw;
     c.cs = 0;
   }
 }
-__device__ __forceinline__ void cur_next(Cursor& c, const MegaArgs& a, unsigned gw, unsigned GW) {
-  const MegaPhase& ph = a.phases[c.p];
-  if (++c.cs >= ph.n_cseg) {
+__device__ __forceinline__ void cur_next(Cursor& c, const MegaShape* sh, unsigned gw, unsigned GW, int n_phases) {
+  if (++c.cs >= sh[c.kind].n_cseg) {
     c.cs = 0;
     c.g += GW;
   }
-  cur_settle(c, a, gw);
+  cur_settle(c, sh, gw, n_phases);
 }
 
 constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
 
-// Start the copies of the item under the cursor into ring slot `slot` (all lanes call).
-__device__ __forceinline__ void mg_issue(const MegaArgs& a, const Cursor& c, uint32_t slot_addr, uint32_t bar, int lane) {
-  const MegaPhase& ph = a.phases[c.p];
+// Start the copies of the item under the cursor into a ring slot (all lanes call).
+__device__ __forceinline__ void mg_issue(const MegaShape* shapes, const MegaLayer* layers, const Cursor& c, uint32_t slot_addr,
+                                         uint32_t bar, int lane) {
+  const MegaShape& sh = shapes[c.kind];
+  const MegaLayer& L = layers[c.p / PH_PER_LAYER];
   int seg = 0;
-  if (ph.n_seg > 1 && c.g >= ph.grp_start[1]) seg = 1;
-  if (ph.n_seg > 2 && c.g >= ph.grp_start[2]) seg = 2;
-  const unsigned seg_rows = seg == 0 ? ph.rows[0] : seg == 1 ? ph.rows[1] : ph.rows[2];
-  const unsigned g0 = seg == 0 ? ph.grp_start[0] : seg == 1 ? ph.grp_start[1] : ph.grp_start[2];
-  const unsigned row0 = (c.g - g0) * MG_RL;
-  const unsigned valid = min((unsigned)MG_RL, seg_rows - row0);
-  const unsigned seg_bytes = ph.seg_blocks * KS_Q4K_BLOCK_BYTES;
-  const int mats = ph.type == MG_GATE_UP ? 2 : 1;
+  if (sh.n_seg > 1 && c.g >= sh.grp_start[1]) seg = 1;
+  if (sh.n_seg > 2 && c.g >= sh.grp_start[2]) seg = 2;
+  const unsigned row0 = (c.g - sh.grp_start[seg]) * MG_RL;
+  const unsigned valid = min((unsigned)MG_RL, sh.rows[seg] - row0);
+  const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
+  const int mats = sh.type == MG_GATE_UP ? 2 : 1;
+  // first weight matrix of the phase inside MegaLayer::W
+  const int w0 = c.kind == PH_QKV ? 0 : c.kind == PH_OPROJ ? 3 : c.kind == PH_GATEUP ? 4 : 6;
   if (lane == 0) mb_expect(bar, valid * mats * seg_bytes);
-  if (ph.n_cseg == 1) {
+  if (sh.n_cseg == 1) {
     if (lane < mats) {
-      const uint8_t* base = ph.type == MG_GATE_UP ? (lane ? ph.W[1] : ph.W[0]) : (seg == 0 ? ph.W[0] : seg == 1 ? ph.W[1] : ph.W[2]);
-      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, base + (size_t)row0 * ph.row_bytes, valid * seg_bytes, bar);
+      const uint8_t* base = L.W[w0 + (mats == 2 ? lane : seg)];
+      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, base + (size_t)row0 * sh.row_bytes, valid * seg_bytes, bar);
     }
   } else if (lane < MG_RL * mats) {
     const int m = lane / MG_RL, rr = lane % MG_RL;
     if ((unsigned)rr < valid) {
-      const uint8_t* base = ph.type == MG_GATE_UP ? (m ? ph.W[1] : ph.W[0]) : (seg == 0 ? ph.W[0] : seg == 1 ? ph.W[1] : ph.W[2]);
-      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, base + (size_t)(row0 + rr) * ph.row_bytes + (size_t)c.cs * seg_bytes,
+      const uint8_t* base = L.W[w0 + (mats == 2 ? m : seg)];
+      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, base + (size_t)(row0 + rr) * sh.row_bytes + (size_t)c.cs * seg_bytes,
               seg_bytes, bar);
     }
   }
@@ -361,338 +486,485 @@ __device__ __forceinline__ int mg_lane_dim(int lane, int j) {
   return j < BPL ? base + j : base + 16 + (j - BPL);
 }
 
+constexpr int MG_MAX_SPLITS = 16;  // context splits per head (the final merge keeps one record per split in registers)
+
 // Shared memory the attention phase needs (it reuses the x staging area).
-__host__ __device__ inline unsigned mg_att_bytes(unsigned G, unsigned hd) {
-  const unsigned area = 4u * G * (hd + 2u) > 8u * hd ? 4u * G * (hd + 2u) : 8u * hd;
-  return (G * hd + area) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 32u;
+__host__ __device__ inline unsigned mg_att_bytes(unsigned hd) {
+  return 8u * (hd + 2u) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 32u;
 }
 
-template <int G, int DPL>
-__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaPhase& ph, unsigned char* sm, int* sflag) {
-  constexpr int HD = DPL * 32, HALF = HD / 2;
-  constexpr unsigned ROWB = (HD / 32) * KS_Q40_BLOCK_BYTES;
-  constexpr unsigned AREA = (4u * G * (HD + 2u) > 8u * HD) ? 4u * G * (HD + 2u) : 8u * HD;
+// Splits in use for a context of tlen positions: one row per warp (8 per block) until every split is
+// in use, more rows per warp beyond that.
+__host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits) {
+  unsigned ns = (tlen + 7u) / 8u;
+  return ns < 1u ? 1u : ns > max_splits ? max_splits : ns;
+}
+
+// One block per (query head, context split): the work of a short context is tiny, so it is spread
+// as widely as the grid allows and every serial step stays short.
+//   1. every warp builds the roped, normed, scaled q of the head in registers (no exchange needed);
+//      in the blocks of the split that holds the newest position, warps 0.. pack the new K row and
+//      warps 4.. the new V row to Q4_0 in shared memory (lower.rs:4231-4702), block pairs (b, b+NB/2)
+//      per warp because RoPE pairs those halves; the block of the KV group's first head stores them;
+//   2. warps take the positions of the split round-robin, online softmax per warp;
+//   3. the eight warps' (m, l, O) meet in shared memory, thread d folds dimension d;
+//   4. the block leaves a (m, l, O[hd]) record; the last block of a head to arrive merges the
+//      head's records (lower.rs:5897-6088).
+template <int DPL>
+__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, unsigned char* sm, int* sflag, long long* pf) {
+  constexpr int HD = DPL * 32, HALF = HD / 2, NB = HD / 32;
+  constexpr unsigned ROWB = NB * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned NS = a.n_splits, n_att = a.n_kv * NS;
-  if (blockIdx.x >= n_att) return;
-  const unsigned kvh = blockIdx.x / NS, split = blockIdx.x % NS;
+  const unsigned NSMAX = a.n_splits;
+  if (blockIdx.x >= a.n_q * NSMAX) return;
+  const unsigned head = blockIdx.x / NSMAX, split = blockIdx.x % NSMAX;
+  const unsigned G = a.n_q / a.n_kv, kvh = head / G;
   const unsigned pos = (unsigned)a.pos[0], tlen = pos + 1;
+  const unsigned NS = mg_active_splits(tlen, NSMAX);
+  if (split >= NS) return;
   const unsigned chunk = (tlen + NS - 1) / NS;
   const unsigned p0 = split * chunk, p1 = min(p0 + chunk, tlen);
-  float* sq = reinterpret_cast<float*>(sm);       // [G][HD] roped, scaled q
-  float* area = sq + G * HD;                      // warp scratch, then the merge tree
-  uint8_t* skrow = reinterpret_cast<uint8_t*>(area + AREA);
+  const bool owner = pos >= p0 && pos < p1;  // the split that holds the newest position
+  float* part = reinterpret_cast<float*>(sm);     // [8][HD + 2]
+  uint8_t* skrow = reinterpret_cast<uint8_t*>(part + 8 * (HD + 2));
   uint8_t* svrow = skrow + ROWB + 16u;
   const float* cs = a.rope + (size_t)pos * HD;
 
-  // per-head RMS + RoPE of q, and the new K / V row (lower.rs:4231-4702), one warp per job
-  for (int t = warp; t < G + 2; t += 8) {
-    const int kind = t < G ? 0 : t == G ? 1 : 2;
-    const float* src = kind == 0 ? a.q + ((size_t)kvh * G + t) * HD : kind == 1 ? a.k + (size_t)kvh * HD : a.v + (size_t)kvh * HD;
-    const float* w = kind == 0 ? ph.q_norm : ph.k_norm;
-    float xv[DPL];
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      xv[j] = __ldcg(src + lane + 32 * j);
-      ss = fmaf(xv[j], xv[j], ss);
-    }
-    ss = mg_warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
-    float* tmp = area + warp * HD;
-    if (kind == 2) {
-#pragma unroll
-      for (int j = 0; j < DPL; j++) tmp[lane + 32 * j] = __fmul_rn(xv[j], inv);
-    } else {
-#pragma unroll
-      for (int j = 0; j < DPL / 2; j++) {
-        const int i = lane + 32 * j;
-        const float u = __fmul_rn(__fmul_rn(xv[j], inv), w[i]);
-        const float vv = __fmul_rn(__fmul_rn(xv[j + DPL / 2], inv), w[HALF + i]);
-        const float c = cs[i], s = cs[HALF + i];
-        const float lo = __fsub_rn(__fmul_rn(u, c), __fmul_rn(vv, s));
-        const float hi = __fadd_rn(__fmul_rn(u, s), __fmul_rn(vv, c));
-        if (kind == 0) {
-          sq[t * HD + i] = lo * a.attn_scale;
-          sq[t * HD + HALF + i] = hi * a.attn_scale;
-        } else {
-          tmp[i] = lo;
-          tmp[HALF + i] = hi;
-        }
-      }
-    }
-    if (kind != 0) {
-      __syncwarp();
-      uint8_t* dst = kind == 1 ? skrow : svrow;
-#pragma unroll
-      for (int b = 0; b < HD / 32; b++) {
-        const float val = __half2float(__float2half_rn(tmp[b * 32 + lane]));  // through f16 (render.rs:1046)
-        mg_pack_q40(val, dst + b * KS_Q40_BLOCK_BYTES, lane);
-      }
-    }
-  }
-  __syncthreads();
-  const size_t rowstride = (size_t)a.n_kv * ROWB;
-  uint8_t* Kc = ph.kv_k + (size_t)kvh * ROWB;
-  uint8_t* Vc = ph.kv_v + (size_t)kvh * ROWB;
-  if (pos >= p0 && pos < p1) {  // the split that holds the newest position stores the new row
-    const unsigned n16 = ROWB / 2;
-    if (threadIdx.x < n16)
-      reinterpret_cast<unsigned short*>(Kc + (size_t)pos * rowstride)[threadIdx.x] = reinterpret_cast<const unsigned short*>(skrow)[threadIdx.x];
-    else if (threadIdx.x < 2 * n16)
-      reinterpret_cast<unsigned short*>(Vc + (size_t)pos * rowstride)[threadIdx.x - n16] =
-          reinterpret_cast<const unsigned short*>(svrow)[threadIdx.x - n16];
-  }
-
-  float qr[G][DPL], o[G][DPL], m[G], l[G];
-#pragma unroll
-  for (int g = 0; g < G; g++) {
-#pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      qr[g][j] = sq[g * HD + mg_lane_dim<DPL>(lane, j)];
-      o[g][j] = 0.0f;
-    }
-    m[g] = kNegInit;
-    l[g] = 0.0f;
-  }
-  auto fetch = [&](unsigned t, RawRow<DPL>& kr, RawRow<DPL>& vr) {
-    if (t < p1) {
-      const uint8_t* kp = t == pos ? skrow : Kc + (size_t)t * rowstride;
-      const uint8_t* vp = t == pos ? svrow : Vc + (size_t)t * rowstride;
-      raw_load<DPL>(kp, lane, kr);
-      raw_load<DPL>(vp, lane, vr);
-    }
-  };
-  auto process = [&](const RawRow<DPL>& kr, const RawRow<DPL>& vr) {
-    float kv[DPL];
-    raw_decode<DPL>(kr, kv);
-    float s[G];
-#pragma unroll
-    for (int g = 0; g < G; g++) {
-      float acc = 0.0f;
-#pragma unroll
-      for (int j = 0; j < DPL; j++) acc = fmaf(qr[g][j], kv[j], acc);
-      s[g] = acc;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-      for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
-    raw_decode<DPL>(vr, kv);
-#pragma unroll
-    for (int g = 0; g < G; g++) {
-      const float m2 = fmaxf(m[g], s[g]);
-      const float alpha = __expf(m[g] - m2);
-      const float e = __expf(s[g] - m2);
-      l[g] = l[g] * alpha + e;
-      m[g] = m2;
-#pragma unroll
-      for (int j = 0; j < DPL; j++) o[g][j] = fmaf(e, kv[j], o[g][j] * alpha);
-    }
-  };
+  float qr[DPL];
   {
-    RawRow<DPL> kA, vA, kB, vB;
-    unsigned t = p0 + warp;
-    fetch(t, kA, vA);
-    fetch(t + 8, kB, vB);
-    while (t < p1) {
-      const RawRow<DPL> k0 = kA, v0 = vA, k1 = kB, v1 = vB;
-      fetch(t + 16, kA, vA);
-      fetch(t + 24, kB, vB);
-      process(k0, v0);
-      if (t + 8 < p1) process(k1, v1);
-      t += 16;
-    }
-  }
-  __syncthreads();  // every warp is done with sq / its scratch: the area becomes the merge tree
-  // fold the 8 warps pairwise: (4..7 -> 0..3), (2,3 -> 0,1), (1 -> 0)
-#pragma unroll 1
-  for (int half = 4; half >= 1; half >>= 1) {
-    if (warp >= half && warp < 2 * half) {
-      float* dst = area + (size_t)(warp - half) * G * (HD + 2);
+    const int pb = warp & 3;  // block pair of the K / V job
+    const bool kjob = owner && warp < 4 && pb < NB / 2, vjob = owner && warp >= 4 && pb < NB / 2;
+    float qv[DPL], qw[DPL], qc[DPL], qs[DPL], rv[DPL], r_w0 = 0.f, r_w1 = 0.f, r_c = 0.f, r_s = 0.f;
+    const float* qsrc = a.q + (size_t)head * HD;
+    const float* qnw = L.norm[1];
 #pragma unroll
-      for (int g = 0; g < G; g++) {
-        if (lane == 0) {
-          dst[g * (HD + 2)] = m[g];
-          dst[g * (HD + 2) + 1] = l[g];
+    for (int j = 0; j < DPL; j++) {
+      const int d = mg_lane_dim<DPL>(lane, j);
+      qv[j] = __ldcg(qsrc + d);
+      qw[j] = qnw[d];
+      qc[j] = cs[d & (HALF - 1)];
+      qs[j] = cs[HALF + (d & (HALF - 1))];
+    }
+    if (kjob || vjob) {
+      const float* src = (kjob ? a.k : a.v) + (size_t)kvh * HD;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) rv[j] = __ldcg(src + lane + 32 * j);
+      if (kjob) {
+        const float* w = L.norm[2];
+        r_w0 = w[32 * pb + lane];
+        r_w1 = w[HALF + 32 * pb + lane];
+        r_c = cs[32 * pb + lane];
+        r_s = cs[HALF + 32 * pb + lane];
+      }
+    }
+    {
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) ss = fmaf(qv[j], qv[j], ss);
+      ss = mg_warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+      // lanes 0..15 hold dims of the first half, lanes 16..31 their RoPE partners (dim + HD/2)
+#pragma unroll
+      for (int j = 0; j < DPL; j++) {
+        const float u = __fmul_rn(__fmul_rn(qv[j], inv), qw[j]);
+        const float pu = __shfl_xor_sync(0xffffffffu, u, 16);
+        const float r = lane < 16 ? __fsub_rn(__fmul_rn(u, qc[j]), __fmul_rn(pu, qs[j]))
+                                  : __fadd_rn(__fmul_rn(pu, qs[j]), __fmul_rn(u, qc[j]));
+        qr[j] = r * a.attn_scale;
+      }
+    }
+    if (kjob || vjob) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) ss = fmaf(rv[j], rv[j], ss);
+      ss = mg_warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+      float x0 = 0.f, x1 = 0.f;  // this lane's element of block pb and of block pb + NB/2
+#pragma unroll
+      for (int j = 0; j < DPL / 2; j++)
+        if (j == pb) {
+          x0 = rv[j];
+          x1 = rv[j + DPL / 2];
         }
-#pragma unroll
-        for (int j = 0; j < DPL; j++) dst[g * (HD + 2) + 2 + j * 32 + lane] = o[g][j];
+      float lo, hi;
+      if (kjob) {
+        const float u = __fmul_rn(__fmul_rn(x0, inv), r_w0), vv = __fmul_rn(__fmul_rn(x1, inv), r_w1);
+        lo = __fsub_rn(__fmul_rn(u, r_c), __fmul_rn(vv, r_s));
+        hi = __fadd_rn(__fmul_rn(u, r_s), __fmul_rn(vv, r_c));
+      } else {
+        lo = __fmul_rn(x0, inv);
+        hi = __fmul_rn(x1, inv);
       }
+      uint8_t* dst = kjob ? skrow : svrow;
+      // values pass through f16 before packing (render.rs:1046)
+      mg_pack_q40(__half2float(__float2half_rn(lo)), dst + pb * KS_Q40_BLOCK_BYTES, lane);
+      mg_pack_q40(__half2float(__float2half_rn(hi)), dst + (pb + NB / 2) * KS_Q40_BLOCK_BYTES, lane);
     }
-    __syncthreads();
-    if (warp < half) {
-      const float* srcm = area + (size_t)warp * G * (HD + 2);
-#pragma unroll
-      for (int g = 0; g < G; g++) {
-        const float mp = srcm[g * (HD + 2)], lp = srcm[g * (HD + 2) + 1];
-        const float m2 = fmaxf(m[g], mp);
-        const float alpha = __expf(m[g] - m2), beta = __expf(mp - m2);
-        l[g] = l[g] * alpha + lp * beta;
-        m[g] = m2;
-#pragma unroll
-        for (int j = 0; j < DPL; j++) o[g][j] = o[g][j] * alpha + srcm[g * (HD + 2) + 2 + j * 32 + lane] * beta;
-      }
-    }
-    __syncthreads();
   }
-  if (warp == 0) {
+  const size_t rowstride = (size_t)a.n_kv * ROWB;
+  uint8_t* Kc = L.kv_k + (size_t)kvh * ROWB;
+  uint8_t* Vc = L.kv_v + (size_t)kvh * ROWB;
+  if (owner) {
+    __syncthreads();
+    if (head == kvh * G) {
+      const unsigned n16 = ROWB / 2;
+      if (threadIdx.x < n16)
+        reinterpret_cast<unsigned short*>(Kc + (size_t)pos * rowstride)[threadIdx.x] = reinterpret_cast<const unsigned short*>(skrow)[threadIdx.x];
+      else if (threadIdx.x < 2 * n16)
+        reinterpret_cast<unsigned short*>(Vc + (size_t)pos * rowstride)[threadIdx.x - n16] =
+            reinterpret_cast<const unsigned short*>(svrow)[threadIdx.x - n16];
+    }
+  }
+  if (pf) pf[4] = clock64();
+
+  float o[DPL], m = kNegInit, l = 0.0f;
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-      const unsigned head = kvh * G + g;
-      float* rec = a.att_tmp + ((size_t)head * NS + split) * (HD + 2);
-      if (lane == 0) {
-        rec[0] = m[g];
-        rec[1] = l[g];
+  for (int j = 0; j < DPL; j++) o[j] = 0.0f;
+  {
+    RawRow<DPL> kn, vn;  // next row, in flight while the current one is processed
+    unsigned t = p0 + warp;
+    if (t < p1) {
+      raw_load<DPL>(t == pos ? skrow : Kc + (size_t)t * rowstride, lane, kn);
+      raw_load<DPL>(t == pos ? svrow : Vc + (size_t)t * rowstride, lane, vn);
+    }
+#pragma unroll 1
+    for (; t < p1; t += 8) {
+      const RawRow<DPL> kr = kn, vr = vn;
+      const unsigned t2 = t + 8;
+      if (t2 < p1) {
+        raw_load<DPL>(t2 == pos ? skrow : Kc + (size_t)t2 * rowstride, lane, kn);
+        raw_load<DPL>(t2 == pos ? svrow : Vc + (size_t)t2 * rowstride, lane, vn);
       }
+      float kv[DPL];
+      raw_decode<DPL>(kr, kv);
+      float sc = 0.0f;
 #pragma unroll
-      for (int j = 0; j < DPL; j++) rec[2 + mg_lane_dim<DPL>(lane, j)] = o[g][j];
+      for (int j = 0; j < DPL; j++) sc = fmaf(qr[j], kv[j], sc);
+      sc = mg_warp_sum(sc);
+      raw_decode<DPL>(vr, kv);
+      const float m2 = fmaxf(m, sc);
+      const float alpha = __expf(m - m2);
+      const float e = __expf(sc - m2);
+      l = l * alpha + e;
+      m = m2;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) o[j] = fmaf(e, kv[j], o[j] * alpha);
+    }
+  }
+  {
+    float* dst = part + warp * (HD + 2);
+    if (lane == 0) {
+      dst[0] = m;
+      dst[1] = l;
+    }
+#pragma unroll
+    for (int j = 0; j < DPL; j++) dst[2 + j * 32 + lane] = o[j];
+  }
+  __syncthreads();
+  if (pf) pf[5] = clock64();
+  // thread d folds slot d (= j * 32 + lane of the warps' layout) over the eight warps
+  const int d = threadIdx.x;
+  const int ddim = mg_lane_dim<DPL>(d & 31, d >> 5);  // the head dimension that slot holds
+  float M = kNegInit, Lsum = 0.0f, O = 0.0f;
+  if (d < HD) {
+    float mw[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      mw[w] = part[w * (HD + 2)];
+      M = fmaxf(M, mw[w]);
+    }
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      const float f = __expf(mw[w] - M);
+      Lsum = fmaf(part[w * (HD + 2) + 1], f, Lsum);
+      O = fmaf(part[w * (HD + 2) + 2 + d], f, O);
+    }
+  }
+  if (pf) pf[6] = clock64();
+  if (NS == 1) {  // one split: this block's result is final
+    if (d < HD) a.o[(size_t)head * HD + ddim] = O / Lsum;
+    return;
+  }
+  float* rec = a.att_tmp + ((size_t)head * NSMAX + split) * (HD + 2);
+  if (d < HD) {
+    rec[2 + d] = O;
+    if (d == 0) {
+      rec[0] = M;
+      rec[1] = Lsum;
     }
     __threadfence();
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned old = atomicAdd(a.att_cnt, 1u);
-    *sflag = (old == n_att - 1) ? 1 : 0;
-  }
+  if (threadIdx.x == 0) *sflag = (atomicAdd(a.att_cnt + head, 1u) == NS - 1) ? 1 : 0;
   __syncthreads();
+  if (pf) pf[7] = clock64();
   if (*sflag) {
-    // last block to arrive: merge the splits of every head (lower.rs:5897-6088)
+    // last block of this head to arrive: merge the head's records, every load first
     __threadfence();
-    const unsigned total = a.n_q * HD;
-    for (unsigned idx = threadIdx.x; idx < total; idx += blockDim.x) {
-      const unsigned head = idx / HD, d = idx % HD;
-      const float* rec0 = a.att_tmp + (size_t)head * NS * (HD + 2);
-      float mm = kNegInit, ll = 0.0f, oo = 0.0f;
-      for (unsigned p = 0; p < NS; p++) {
-        const float* rec = rec0 + (size_t)p * (HD + 2);
-        const float mp = __ldcg(rec), lp = __ldcg(rec + 1);
-        const float m2 = fmaxf(mm, mp);
-        const float alpha = __expf(mm - m2), beta = __expf(mp - m2);
-        ll = ll * alpha + lp * beta;
-        mm = m2;
-        oo = oo * alpha + __ldcg(rec + 2 + d) * beta;
+    if (d < HD) {
+      const float* rec0 = a.att_tmp + (size_t)head * NSMAX * (HD + 2);
+      float mp[MG_MAX_SPLITS], lp[MG_MAX_SPLITS], ov[MG_MAX_SPLITS];
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) {
+        if ((unsigned)p < NS) {
+          const float* r = rec0 + (size_t)p * (HD + 2);
+          mp[p] = __ldcg(r);
+          lp[p] = __ldcg(r + 1);
+          ov[p] = __ldcg(r + 2 + d);
+        } else {
+          mp[p] = kNegInit;
+          lp[p] = 0.0f;
+          ov[p] = 0.0f;
+        }
       }
-      a.o[idx] = oo * (1.0f / ll);
+      float MM = kNegInit;
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) MM = fmaxf(MM, mp[p]);
+      float LL = 0.0f, OO = 0.0f;
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) {
+        const float f = __expf(mp[p] - MM);
+        LL = fmaf(lp[p], f, LL);
+        OO = fmaf(ov[p], f, OO);
+      }
+      a.o[(size_t)head * HD + ddim] = OO / LL;
     }
-    if (threadIdx.x == 0) *a.att_cnt = 0u;
+    if (threadIdx.x == 0) a.att_cnt[head] = 0u;
   }
 }
 
 // ---- the kernel -------------------------------------------------------------------------------------
 struct MegaSmem {
-  unsigned ring_off, bar_off, red_off, flag_off, total;
+  unsigned ring_off, bar_off, red_off, flag_off, tab_off, total;
 };
-__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int stages) {
+__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int stages, unsigned tables_bytes) {
   MegaSmem L;
   L.ring_off = (x_bytes + 127u) & ~127u;
   L.bar_off = L.ring_off + 8u * (unsigned)stages * slot_bytes;
   L.red_off = (L.bar_off + 8u * 8u * (unsigned)stages + 15u) & ~15u;
-  L.flag_off = L.red_off + 128u;
-  L.total = L.flag_off + 16u;
+  L.flag_off = L.red_off + 256u;  // 32 floats for block sums, then 8 float4 of per-warp norm sums
+  L.tab_off = L.flag_off + 16u;
+  L.total = L.tab_off + tables_bytes;
   return L;
 }
 
-template <int G, int DPL>
+template <int DPL>
 __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cl = lane % MG_LPR, rl = lane / MG_LPR;
   const int S = a.stages;
-  const MegaSmem L = mg_smem(a.x_bytes, a.slot_bytes, S);
-  const uint32_t ring_s = sm32(smem + L.ring_off) + (uint32_t)(warp * S) * a.slot_bytes;
-  const uint32_t bars = sm32(smem + L.bar_off) + (uint32_t)(warp * S) * 8u;
-  float* red = reinterpret_cast<float*>(smem + L.red_off);
-  int* sflag = reinterpret_cast<int*>(smem + L.flag_off);
+  const MegaSmem SL = mg_smem(a.x_bytes, a.slot_bytes, S, a.tables_bytes);
+  const uint32_t ring_s = sm32(smem + SL.ring_off) + (uint32_t)(warp * S) * a.slot_bytes;
+  const uint32_t bars = sm32(smem + SL.bar_off) + (uint32_t)(warp * S) * 8u;
+  float* red = reinterpret_cast<float*>(smem + SL.red_off);
+  float4* wsum = reinterpret_cast<float4*>(smem + SL.red_off + 128u);
+  int* sflag = reinterpret_cast<int*>(smem + SL.flag_off);
+  const MegaShape* shapes = reinterpret_cast<const MegaShape*>(smem + SL.tab_off);
+  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u));
   const uint32_t xs_s = sm32(smem);
   // consecutive groups go to different blocks, so a phase with few groups still uses every SM
   const unsigned gw = (unsigned)warp * gridDim.x + blockIdx.x, GW = gridDim.x * 8u;
   const unsigned bar_base = a.bar[1];
+  const int n_phases = a.n_layers * PH_PER_LAYER;
 
+  for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
+    reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
   if (lane == 0) {
     for (int s = 0; s < S; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  __syncwarp();
-  Cursor ic{0, gw, 0}, cc{0, gw, 0};
-  cur_settle(ic, a, gw);
-  cur_settle(cc, a, gw);
+  __syncthreads();
+  const unsigned H = shapes[PH_QKV].cols;
+
+  Cursor ic{0, 0, gw, 0}, cc{0, 0, gw, 0};
+  cur_settle(ic, shapes, gw, n_phases);
+  cur_settle(cc, shapes, gw, n_phases);
   unsigned issued = 0, consumed = 0;
-  while (issued < (unsigned)S && ic.p < a.n_phases) {
-    mg_issue(a, ic, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
+  while (issued < (unsigned)S && ic.p < n_phases) {
+    mg_issue(shapes, layers, ic, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
     issued++;
-    cur_next(ic, a, gw, GW);
+    cur_next(ic, shapes, gw, GW, n_phases);
   }
 
   long long* prof = nullptr;
   if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * a.n_phases * 4;
+    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * n_phases * 8;
   bool dead = false;  // this warp gave up on a copy: it keeps the block-level steps, skips its items
-  int p = 0;
-  for (; p < a.n_phases; p++) {
-    const MegaPhase& ph = a.phases[p];
-    if (prof) prof[p * 4 + 0] = clock64();
-    if (ph.type == MG_ATTN) {
-      mg_attention<G, DPL>(a, ph, smem, sflag);
+  int p = 0, layer = 0, kind = 0;
+  for (; p < n_phases; p++) {
+    const MegaLayer& L = layers[layer];
+    // constants of this phase, fetched while the other blocks arrive at the barrier before it
+    NormPre npre;
+    if (kind == PH_QKV)
+      mg_prefetch_norm(npre, layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM, L.norm[0], layers[layer > 0 ? layer - 1 : 0].norm[5], H);
+    else if (kind == PH_GATEUP)
+      mg_prefetch_norm(npre, KS_PRO_ADD_NORM, L.norm[4], L.norm[3], H);
+    if (p > 0) {
+      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x, a.err, sflag)) break;
+      if (prof) prof[(p - 1) * 8 + 3] = clock64();
+    }
+    if (prof) prof[p * 8 + 0] = clock64();
+#ifdef KS_MEGA_LATENCY_PROBE
+    if (kind == PH_ATTN && blockIdx.x == gridDim.x - 1) {  // idle block in this phase: time known instruction chains
+      float f = (float)p;
+      const long long c0 = clock64();
+#pragma unroll
+      for (int i = 0; i < 64; i++) f = fmaf(f, 1.0001f, 0.5f);
+      const long long c1 = clock64() + (long long)(f > 1e30f);
+#pragma unroll
+      for (int i = 0; i < 16; i++) f += __shfl_xor_sync(0xffffffffu, f, 1 + (i & 15));
+      const long long c2 = clock64() + (long long)(f > 1e30f);
+      float sacc = f;
+#pragma unroll
+      for (int i = 0; i < 16; i++) sacc += red[(i * 7 + (int)sacc) & 31];
+      const long long c3 = clock64() + (long long)(sacc > 1e30f);
+      if (prof) {
+        prof[p * 8 + 4] = c1 - c0;
+        prof[p * 8 + 5] = c2 - c1;
+        prof[p * 8 + 6] = c3 - c2;
+      }
+    }
+#endif
+    if (kind == PH_ATTN) {
+      mg_attention<DPL>(a, L, smem, sflag, prof ? prof + p * 8 : nullptr);
     } else {
-      mg_stage_x(smem, red, ph);
+      const MegaShape& sh = shapes[kind];
+      // input, prologue and outputs of this phase
+      int mode = KS_PRO_NONE;
+      const float* x;
+      const float* yin = a.yb;
+      float* out_x = nullptr;
+      if (kind == PH_QKV) {
+        mode = layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM;
+        x = layer == 0 ? a.x_a : a.x_b;
+        out_x = a.x_a;
+      } else if (kind == PH_OPROJ) {
+        x = a.o;
+      } else if (kind == PH_GATEUP) {
+        mode = KS_PRO_ADD_NORM;
+        x = a.x_a;
+        out_x = a.x_b;
+      } else {
+        x = a.ff;
+      }
+      if (mode == KS_PRO_ADD_NORM)
+        mg_stage_addnorm(smem, sh.cols, x, yin, out_x, a.eps, npre, a.nsum, gridDim.x);
+      else
+        mg_stage_x(smem, red, mode, sh.cols, x, yin, out_x, a.eps, npre);
       __syncthreads();
-      if (prof) prof[p * 4 + 1] = clock64();
-      const unsigned units = ph.cols >> 6;
+      if (prof) prof[p * 8 + 1] = clock64();
+      const unsigned units = sh.cols >> 6;
+      // o-proj and down feed a residual-add + norm: their rows also leave the sums that norm needs
+      const bool sums = kind == PH_OPROJ || kind == PH_DOWN;
+      const float* xres = kind == PH_OPROJ ? a.x_a : a.x_b;
+      const float* wpost = kind == PH_OPROJ ? L.norm[3] : L.norm[5];
+      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f;
       float yacc[2] = {0.0f, 0.0f};
+      long long t_wait = 0, t_comp = 0, n_it = 0;
       while (cc.p == p && !dead) {
         const unsigned st = consumed % (unsigned)S;
+        const unsigned g = cc.g, cs = cc.cs;
+        const bool last_cs = cs + 1 == sh.n_cseg;
+        int seg = 0;
+        if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
+        if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
+        const unsigned row = (g - sh.grp_start[seg]) * MG_RL + (unsigned)rl;
+        const bool writer = cl == 0 && row < sh.rows[seg];
+        float xr = 0.0f, wpr = 0.0f;
+        if (sums && last_cs && writer) {  // in flight while the item is multiplied
+          xr = __ldcg(xres + row);
+          wpr = wpost[row];
+        }
+        const long long tq0 = prof ? clock64() : 0;
         if (!mb_wait(bars + st * 8u, (consumed / (unsigned)S) & 1u)) {
           dead = true;
           if (lane == 0) atomicOr(a.err, 1u);
           break;
         }
         const uint32_t slot = ring_s + st * a.slot_bytes;
-        if (ph.type == MG_GATE_UP)
-          mg_item_compute<2>(slot, xs_s, units, ph.seg_blocks, cc.cs, cl, rl, yacc);
+        const long long tq1 = prof ? clock64() : 0;
+        if (sh.type == MG_GATE_UP)
+          mg_item_compute<2>(slot, xs_s, units, sh.seg_blocks, cs, cl, rl, yacc);
         else
-          mg_item_compute<1>(slot, xs_s, units, ph.seg_blocks, cc.cs, cl, rl, yacc);
-        __syncwarp();
-        consumed++;
-        const unsigned g = cc.g, cs = cc.cs;
-        cur_next(cc, a, gw, GW);
-        if (ic.p < a.n_phases) {
-          if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
-          __syncwarp();
-          mg_issue(a, ic, slot, bars + st * 8u, lane);
-          issued++;
-          cur_next(ic, a, gw, GW);
+          mg_item_compute<1>(slot, xs_s, units, sh.seg_blocks, cs, cl, rl, yacc);
+        if (prof) {
+          t_wait += tq1 - tq0;
+          t_comp += clock64() - tq1;
+          n_it++;
         }
-        if (cs + 1 == ph.n_cseg) {
-          int seg = 0;
-          if (ph.n_seg > 1 && g >= ph.grp_start[1]) seg = 1;
-          if (ph.n_seg > 2 && g >= ph.grp_start[2]) seg = 2;
-          const unsigned seg_rows = seg == 0 ? ph.rows[0] : seg == 1 ? ph.rows[1] : ph.rows[2];
-          const unsigned g0 = seg == 0 ? ph.grp_start[0] : seg == 1 ? ph.grp_start[1] : ph.grp_start[2];
-          const unsigned row = (g - g0) * MG_RL + (unsigned)rl;
+        consumed++;
+        if (last_cs) {
           float v0 = yacc[0], v1 = yacc[1];
 #pragma unroll
           for (int o = MG_LPR / 2; o > 0; o >>= 1) {
             v0 += __shfl_xor_sync(0xffffffffu, v0, o);
             v1 += __shfl_xor_sync(0xffffffffu, v1, o);
           }
-          if (cl == 0 && row < seg_rows) {
-            float* y = seg == 0 ? ph.y[0] : seg == 1 ? ph.y[1] : ph.y[2];
-            y[row] = ph.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
+          if (writer) {
+            float* y = kind == PH_QKV ? (seg == 0 ? a.q : seg == 1 ? a.k : a.v) : kind == PH_GATEUP ? a.ff : a.yb;
+            const float val = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
+            y[row] = val;
+            if (sums) {
+              const float t = val * wpr;
+              ns0 = fmaf(val, val, ns0);
+              ns1 = fmaf(xr, t, ns1);
+              ns2 = fmaf(t, t, ns2);
+              ns3 = fmaf(xr, xr, ns3);
+            }
           }
           yacc[0] = yacc[1] = 0.0f;
         }
+        cur_next(cc, shapes, gw, GW, n_phases);
+        // Refill now only when the next item of THIS phase is not in flight yet; everything else is
+        // refilled after the barrier arrival below, off the critical path.
+        if (ic.p == p) {
+          __syncwarp();
+          if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
+          __syncwarp();
+          mg_issue(shapes, layers, ic, slot, bars + st * 8u, lane);
+          issued++;
+          cur_next(ic, shapes, gw, GW, n_phases);
+        }
+      }
+      if (sums) {
+        // only the four writer lanes (0, 8, 16, 24) hold anything
+        ns0 += __shfl_xor_sync(0xffffffffu, ns0, 8);  ns1 += __shfl_xor_sync(0xffffffffu, ns1, 8);
+        ns2 += __shfl_xor_sync(0xffffffffu, ns2, 8);  ns3 += __shfl_xor_sync(0xffffffffu, ns3, 8);
+        ns0 += __shfl_xor_sync(0xffffffffu, ns0, 16); ns1 += __shfl_xor_sync(0xffffffffu, ns1, 16);
+        ns2 += __shfl_xor_sync(0xffffffffu, ns2, 16); ns3 += __shfl_xor_sync(0xffffffffu, ns3, 16);
+        if (lane == 0) wsum[warp] = make_float4(ns0, ns1, ns2, ns3);
+      }
+      if (prof) {
+        prof[p * 8 + 4] = t_wait;
+        prof[p * 8 + 5] = t_comp;
+        prof[p * 8 + 6] = n_it;
       }
     }
-    if (prof) prof[p * 4 + 2] = clock64();
-    if (!grid_barrier(a.bar, bar_base + (unsigned)(p + 1) * gridDim.x, a.err, sflag)) break;
-    if (prof) prof[p * 4 + 3] = clock64();
+    if (prof) prof[p * 8 + 2] = clock64();
+    if (p + 1 == n_phases) {  // the end of the kernel orders the last phase before whatever follows
+      p++;
+      break;
+    }
+    grid_arrive(a.bar, (kind == PH_OPROJ || kind == PH_DOWN) ? wsum : nullptr, a.nsum);
+    // refill the ring while the other blocks arrive
+    if (!dead && issued - consumed < (unsigned)S && ic.p < n_phases) {
+      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      while (issued - consumed < (unsigned)S && ic.p < n_phases) {
+        const unsigned st = issued % (unsigned)S;
+        mg_issue(shapes, layers, ic, ring_s + st * a.slot_bytes, bars + st * 8u, lane);
+        issued++;
+        cur_next(ic, shapes, gw, GW, n_phases);
+      }
+    }
+    if (++kind == PH_PER_LAYER) {
+      kind = 0;
+      layer++;
+    }
   }
-  if (p == a.n_phases) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) a.bar[1] = bar_base + (unsigned)a.n_phases * gridDim.x;
-  }
+  if (p == n_phases && blockIdx.x == 0 && threadIdx.x == 0) a.bar[1] = bar_base + (unsigned)(n_phases - 1) * gridDim.x;
   // copies still in flight must land before this block's shared memory goes away (bounded)
   for (unsigned j = consumed; j < issued; j++) mb_wait(bars + (j % (unsigned)S) * 8u, (j / (unsigned)S) & 1u);
 }
@@ -702,8 +974,8 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
 // ---- host side --------------------------------------------------------------------------------------
 struct ks_mega {
   MegaArgs args{};
-  MegaPhase* d_phases = nullptr;
-  unsigned* d_sync = nullptr;  // [0..1] barrier words, [2] attention arrival counter
+  void* d_tables = nullptr;
+  unsigned* d_sync = nullptr;  // words 0..1 barrier, 8..63 per-head attention arrival counters, from byte 256: per-block norm sums
   long long* d_prof = nullptr;
   unsigned grid = 0;
   size_t smem = 0;
@@ -712,9 +984,9 @@ struct ks_mega {
 };
 
 namespace {
-template <int G, int DPL>
+template <int DPL>
 int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
-  auto kern = mega_kernel<G, DPL>;
+  auto kern = mega_kernel<DPL>;
   static size_t smem_set[16] = {0};
   if (mg->smem > smem_set[ctx->device & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg->smem);
@@ -738,12 +1010,9 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
 }  // namespace
 
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
-#define KS_MG(G_, D_) \
-  if (mg->G == G_ && mg->dpl == D_) return mega_launch_t<G_, D_>(ctx, mg)
-  KS_MG(1, 4); KS_MG(2, 4); KS_MG(4, 4); KS_MG(8, 4);
-  KS_MG(1, 8); KS_MG(2, 8); KS_MG(4, 8); KS_MG(8, 8);
-#undef KS_MG
-  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head grouping not supported");
+  if (mg->dpl == 4) return mega_launch_t<4>(ctx, mg);
+  if (mg->dpl == 8) return mega_launch_t<8>(ctx, mg);
+  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size not supported");
 }
 
 float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
@@ -751,7 +1020,7 @@ const long long* ks_mega_prof(const ks_mega* mg) { return mg->d_prof; }
 
 void ks_mega_destroy(ks_mega* mg) {
   if (!mg) return;
-  if (mg->d_phases) cudaFree(mg->d_phases);
+  if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
   if (mg->d_prof) cudaFree(mg->d_prof);
   delete mg;
@@ -767,17 +1036,24 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   auto even_blocks = [](unsigned cols) { return cols % 512 == 0; };
   if (!even_blocks(H) || !even_blocks(F) || !even_blocks(qn)) return KS_OK;
   if (H > 16u * 256u) return KS_OK;  // the fused norms hold the vector in registers
-  if (!(G == 1 || G == 2 || G == 4 || G == 8) || !(hd == 128 || hd == 256)) return KS_OK;
-  if (d->n_splits < 1 || nkv * (unsigned)d->n_splits > (unsigned)ctx->sm_count) return KS_OK;
+  if (G < 1 || nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
+  // one block per (query head, split): fewer splits than the caller's record layout allows if the grid is small
+  unsigned n_splits = (unsigned)d->n_splits;
+  if (n_splits > (unsigned)ctx->sm_count / nq) n_splits = (unsigned)ctx->sm_count / nq;
+  if (n_splits > (unsigned)MG_MAX_SPLITS) n_splits = MG_MAX_SPLITS;
+  if (n_splits < 1 || nq > 48) return KS_OK;
+  if (d->n_layers < 1 || d->n_layers > 128) return KS_OK;
 
   const int stages = 3;
+  const unsigned shapes_bytes = (unsigned)((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u);
+  const unsigned tables_bytes = (unsigned)((shapes_bytes + d->n_layers * sizeof(MegaLayer) + 15u) & ~15u);
   unsigned maxcols = H > F ? H : F;
   if (qn > maxcols) maxcols = qn;
   unsigned x_bytes = (maxcols / 64u) * Q4K_XTOK * 4u;
-  const unsigned att = mg_att_bytes(G, hd);
+  const unsigned att = mg_att_bytes(hd);
   if (att > x_bytes) x_bytes = att;
   const unsigned budget = (unsigned)ctx->smem_optin;
-  const MegaSmem fixed = mg_smem(x_bytes, 0, stages);
+  const MegaSmem fixed = mg_smem(x_bytes, 0, stages, tables_bytes);
   if (fixed.total + 8u * stages * 4u * KS_Q4K_BLOCK_BYTES * 2u > budget) return KS_OK;
   unsigned slot_cap = (budget - fixed.total) / (8u * stages);
   slot_cap &= ~15u;
@@ -799,10 +1075,10 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   };
   upd(sb_h, 1); upd(sb_h2, 2); upd(sb_q, 1); upd(sb_f, 1);
 
-  std::vector<MegaPhase> ph;
-  float* cur = d->x_a;
-  float* oth = d->x_b;
-  auto set_rows = [](MegaPhase& p, unsigned cols, unsigned sb) {
+  std::vector<unsigned char> tab(tables_bytes, 0);
+  MegaShape* sh = reinterpret_cast<MegaShape*>(tab.data());
+  MegaLayer* ly = reinterpret_cast<MegaLayer*>(tab.data() + shapes_bytes);
+  auto set_rows = [](MegaShape& p, unsigned cols, unsigned sb) {
     p.cols = cols;
     p.row_bytes = cols / 256u * KS_Q4K_BLOCK_BYTES;
     p.seg_blocks = sb;
@@ -814,108 +1090,65 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
     }
     p.grp_start[p.n_seg] = g0;
   };
+  sh[PH_QKV].type = MG_MATVEC; sh[PH_QKV].n_seg = 3;
+  sh[PH_QKV].rows[0] = qn; sh[PH_QKV].rows[1] = kvn; sh[PH_QKV].rows[2] = kvn;
+  set_rows(sh[PH_QKV], H, sb_h);
+  sh[PH_ATTN].type = MG_ATTN; sh[PH_ATTN].n_seg = 1; sh[PH_ATTN].n_cseg = 1;
+  sh[PH_OPROJ].type = MG_MATVEC; sh[PH_OPROJ].n_seg = 1; sh[PH_OPROJ].rows[0] = H;
+  set_rows(sh[PH_OPROJ], qn, sb_q);
+  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F;
+  set_rows(sh[PH_GATEUP], H, sb_h2);
+  sh[PH_DOWN].type = MG_MATVEC; sh[PH_DOWN].n_seg = 1; sh[PH_DOWN].rows[0] = H;
+  set_rows(sh[PH_DOWN], F, sb_f);
   for (int l = 0; l < d->n_layers; l++) {
     const ks_mega_layer& L = layers[l];
-    MegaPhase a{};
-    a.type = MG_MATVEC;
-    a.n_seg = 3;
-    a.W[0] = (const uint8_t*)L.wq; a.W[1] = (const uint8_t*)L.wk; a.W[2] = (const uint8_t*)L.wv;
-    a.y[0] = d->q; a.y[1] = d->k; a.y[2] = d->v;
-    a.rows[0] = qn; a.rows[1] = kvn; a.rows[2] = kvn;
-    set_rows(a, H, sb_h);
-    a.x = cur;
-    a.pro.eps = d->eps;
-    a.pro.w = L.attn_norm;
-    if (l == 0) {
-      a.pro.mode = KS_PRO_NORM;
-    } else {
-      a.pro.mode = KS_PRO_ADD_NORM;
-      a.pro.y = d->yb;
-      a.pro.w_post = layers[l - 1].post_ffw_norm;
-      a.pro.out_x = oth;
-    }
-    ph.push_back(a);
-    if (l > 0) std::swap(cur, oth);
-
-    MegaPhase t{};
-    t.type = MG_ATTN;
-    t.kv_k = L.kv_k; t.kv_v = L.kv_v;
-    t.q_norm = (const float*)L.q_norm; t.k_norm = (const float*)L.k_norm;
-    ph.push_back(t);
-
-    MegaPhase o{};
-    o.type = MG_MATVEC;
-    o.n_seg = 1;
-    o.W[0] = (const uint8_t*)L.wo;
-    o.y[0] = d->yb;
-    o.rows[0] = H;
-    set_rows(o, qn, sb_q);
-    o.x = d->o;
-    ph.push_back(o);
-
-    MegaPhase gu{};
-    gu.type = MG_GATE_UP;
-    gu.n_seg = 1;
-    gu.W[0] = (const uint8_t*)L.wgate; gu.W[1] = (const uint8_t*)L.wup;
-    gu.y[0] = d->ff;
-    gu.rows[0] = F;
-    set_rows(gu, H, sb_h2);
-    gu.x = cur;
-    gu.pro.mode = KS_PRO_ADD_NORM;
-    gu.pro.eps = d->eps;
-    gu.pro.w = L.ffn_norm;
-    gu.pro.y = d->yb;
-    gu.pro.w_post = L.post_attn_norm;
-    gu.pro.out_x = oth;
-    ph.push_back(gu);
-    std::swap(cur, oth);
-
-    MegaPhase dn{};
-    dn.type = MG_MATVEC;
-    dn.n_seg = 1;
-    dn.W[0] = (const uint8_t*)L.wdown;
-    dn.y[0] = d->yb;
-    dn.rows[0] = H;
-    set_rows(dn, F, sb_f);
-    dn.x = d->ff;
-    ph.push_back(dn);
+    MegaLayer& o = ly[l];
+    o.W[0] = (const uint8_t*)L.wq; o.W[1] = (const uint8_t*)L.wk; o.W[2] = (const uint8_t*)L.wv; o.W[3] = (const uint8_t*)L.wo;
+    o.W[4] = (const uint8_t*)L.wgate; o.W[5] = (const uint8_t*)L.wup; o.W[6] = (const uint8_t*)L.wdown;
+    o.norm[0] = (const float*)L.attn_norm; o.norm[1] = (const float*)L.q_norm; o.norm[2] = (const float*)L.k_norm;
+    o.norm[3] = (const float*)L.post_attn_norm; o.norm[4] = (const float*)L.ffn_norm; o.norm[5] = (const float*)L.post_ffw_norm;
+    o.kv_k = L.kv_k; o.kv_v = L.kv_v;
   }
 
   ks_mega* mg = new ks_mega();
   cudaSetDevice(ctx->device);
-  if (cudaMalloc((void**)&mg->d_phases, ph.size() * sizeof(MegaPhase)) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_sync, 64) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_prof, ph.size() * 8 * sizeof(long long)) != cudaSuccess) {
+  const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
+  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess) {
     ks_mega_destroy(mg);
-    return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate the phase table");
+    return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
-  cudaError_t e = cudaMemcpyAsync(mg->d_phases, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 64, ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // ph is a local
+  cudaError_t e = cudaMemcpyAsync(mg->d_tables, tab.data(), tables_bytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 256 + 16 * (size_t)ctx->sm_count, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
   if (e != cudaSuccess) {
     ks_mega_destroy(mg);
-    return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: phase table upload failed: %s", cudaGetErrorString(e));
+    return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: table upload failed: %s", cudaGetErrorString(e));
   }
   MegaArgs& a = mg->args;
-  a.phases = mg->d_phases;
-  a.n_phases = (int)ph.size();
+  a.tables = mg->d_tables;
+  a.tables_bytes = tables_bytes;
+  a.n_layers = d->n_layers;
   a.stages = stages;
   a.slot_bytes = slot_bytes;
   a.x_bytes = x_bytes;
-  a.n_q = nq; a.n_kv = nkv; a.hd = hd; a.n_splits = (unsigned)d->n_splits;
+  a.n_q = nq; a.n_kv = nkv; a.hd = hd; a.n_splits = n_splits;
   a.eps = d->eps; a.attn_scale = d->attn_scale;
   a.rope = d->rope; a.pos = d->pos;
-  a.q = d->q; a.k = d->k; a.v = d->v; a.o = d->o;
+  a.x_a = d->x_a; a.x_b = d->x_b;
+  a.yb = d->yb; a.q = d->q; a.k = d->k; a.v = d->v; a.o = d->o; a.ff = d->ff;
   a.att_tmp = d->att_tmp;
   a.bar = mg->d_sync;
-  a.att_cnt = mg->d_sync + 2;
+  a.att_cnt = mg->d_sync + 8;
+  a.nsum = reinterpret_cast<float4*>(mg->d_sync + 64);
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
   a.prof = mg->d_prof;
   mg->grid = (unsigned)ctx->sm_count;
-  mg->smem = mg_smem(x_bytes, slot_bytes, stages).total;
+  mg->smem = mg_smem(x_bytes, slot_bytes, stages, tables_bytes).total;
   mg->G = (int)G;
   mg->dpl = (int)(hd / 32);
-  mg->residual = cur;
+  mg->residual = d->x_b;
   *out = mg;
   return KS_OK;
 }
