@@ -113,8 +113,9 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter, const float4* wsu
       }
       nsum[blockIdx.x] = t;
     }
-    __threadfence();
-    atomicAdd(counter, 1u);
+    // release: everything this block wrote (ordered before by the barrier above) is visible to whoever
+    // acquires the counter; nothing comes back, so the thread does not wait for a round trip
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
   }
 }
 // Returns false when the wait gave up.
@@ -128,7 +129,6 @@ __device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, un
       }
     }
     if (!ok) atomicOr(err, 2u);
-    __threadfence();
     *sflag = ok;
   }
   __syncthreads();
@@ -313,60 +313,85 @@ __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned col
 }
 
 // ---- the per-warp item list of a whole token -----------------------------------------------------
-// Item = (phase, row group, column segment).  Warp gw owns groups gw, gw+GW, ... of every matvec
-// phase.  Two cursors walk the same list: one issues copies, one consumes them.  `sh` is the
-// shared-memory copy of the five shapes.
-struct Cursor {
-  int p;        // phase index = layer * 5 + kind
-  int kind;     // p % 5
-  unsigned g, cs;
-};
-__device__ __forceinline__ unsigned shape_groups(const MegaShape& s) { return s.type == MG_ATTN ? 0u : s.grp_start[s.n_seg]; }
-__device__ __forceinline__ void cur_settle(Cursor& c, const MegaShape* sh, unsigned gw, int n_phases) {
-  while (c.p < n_phases && c.g >= shape_groups(sh[c.kind])) {
-    c.p++;
-    c.kind = c.kind == PH_PER_LAYER - 1 ? 0 : c.kind + 1;
-    c.g = gw;
-    c.cs = 0;
-  }
-}
-__device__ __forceinline__ void cur_next(Cursor& c, const MegaShape* sh, unsigned gw, unsigned GW, int n_phases) {
-  if (++c.cs >= sh[c.kind].n_cseg) {
-    c.cs = 0;
-    c.g += GW;
-  }
-  cur_settle(c, sh, gw, n_phases);
-}
-
+// Item = (phase, row group, column segment).
 constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
 
-// Start the copies of the item under the cursor into a ring slot (all lanes call).
-__device__ __forceinline__ void mg_issue(const MegaShape* shapes, const MegaLayer* layers, const Cursor& c, uint32_t slot_addr,
-                                         uint32_t bar, int lane) {
-  const MegaShape& sh = shapes[c.kind];
-  const MegaLayer& L = layers[c.p / PH_PER_LAYER];
-  int seg = 0;
-  if (sh.n_seg > 1 && c.g >= sh.grp_start[1]) seg = 1;
-  if (sh.n_seg > 2 && c.g >= sh.grp_start[2]) seg = 2;
-  const unsigned row0 = (c.g - sh.grp_start[seg]) * MG_RL;
-  const unsigned valid = min((unsigned)MG_RL, sh.rows[seg] - row0);
-  const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
-  const int mats = sh.type == MG_GATE_UP ? 2 : 1;
-  // first weight matrix of the phase inside MegaLayer::W
-  const int w0 = c.kind == PH_QKV ? 0 : c.kind == PH_OPROJ ? 3 : c.kind == PH_GATEUP ? 4 : 6;
-  if (lane == 0) mb_expect(bar, valid * mats * seg_bytes);
-  if (sh.n_cseg == 1) {
-    if (lane < mats) {
-      const uint8_t* base = L.W[w0 + (mats == 2 ? lane : seg)];
-      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, base + (size_t)row0 * sh.row_bytes, valid * seg_bytes, bar);
+// The items of a warp repeat layer after layer (same shapes, other pointers), so the walk over the
+// shapes is done once per kernel: each warp records its items of ONE layer, in phase order, and the
+// issue and consume positions are (layer, entry) pairs.
+constexpr int MG_MAX_ENT = 16;
+struct ItemEnt {
+  uint32_t src_off;  // byte offset of the first copy inside its weight matrix
+  uint32_t pslot;    // index of this item among the block's items of the phase (where its partial sums go)
+  uint16_t seg16;    // bytes of one row segment / 16
+  uint8_t kind, seg, cs, valid;
+  uint8_t widx;      // MegaLayer::W index of the first matrix
+  uint8_t flags;     // bit 0: two matrices (gate, up); bit 1: whole rows (one copy per matrix)
+};
+struct ItemPos {
+  int layer, e;
+};
+__device__ __forceinline__ void pos_next(ItemPos& c, int n_ent) {
+  if (++c.e >= n_ent) {
+    c.e = 0;
+    c.layer++;
+  }
+}
+// Groups of a phase go to blocks round-robin (block c owns groups c, c + grid, ...); the block's items
+// -- its groups x the column segments -- go to its warps round-robin.  A row's column segments may
+// therefore be multiplied by different warps; the partial sums meet in shared memory (slot pslot).
+constexpr int MG_MAX_P = 64;  // items of one block in one phase
+__device__ __forceinline__ unsigned block_groups(const MegaShape& sh) {
+  const unsigned total = sh.type == MG_ATTN ? 0u : sh.grp_start[sh.n_seg];
+  return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+}
+// lane 0 of each warp fills its table; returns the entry count (0 when the warp owns nothing, -1 on overflow)
+__device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes, int warp) {
+  int n = 0;
+  for (int kind = 0; kind < PH_PER_LAYER; kind++) {
+    const MegaShape& sh = shapes[kind];
+    const unsigned C = sh.n_cseg, n_items = block_groups(sh) * C;
+    if (n_items > (unsigned)MG_MAX_P) return -1;
+    const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
+    const int mats = sh.type == MG_GATE_UP ? 2 : 1;
+    const int w0 = kind == PH_QKV ? 0 : kind == PH_OPROJ ? 3 : kind == PH_GATEUP ? 4 : 6;
+    for (unsigned j = (unsigned)warp; j < n_items; j += 8u) {
+      if (n >= MG_MAX_ENT) return -1;
+      const unsigned k = j / C, cs = j - k * C;
+      const unsigned g = blockIdx.x + k * gridDim.x;
+      int seg = 0;
+      if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
+      if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
+      const unsigned row0 = (g - sh.grp_start[seg]) * MG_RL;
+      ItemEnt e;
+      e.src_off = row0 * sh.row_bytes + cs * seg_bytes;
+      e.pslot = j;
+      e.seg16 = (uint16_t)(seg_bytes / 16u);
+      e.kind = (uint8_t)kind;
+      e.seg = (uint8_t)seg;
+      e.cs = (uint8_t)cs;
+      e.valid = (uint8_t)min((unsigned)MG_RL, sh.rows[seg] - row0);
+      e.widx = (uint8_t)(w0 + (mats == 2 ? 0 : seg));
+      e.flags = (uint8_t)((mats == 2 ? 1 : 0) | (C == 1 ? 2 : 0));
+      ent[n++] = e;
     }
+  }
+  return n;
+}
+
+// Start the copies of one item into a ring slot (all lanes call).
+__device__ __forceinline__ void mg_issue_ent(const ItemEnt& e, const MegaLayer& L, unsigned row_bytes, uint32_t slot_addr,
+                                             uint32_t bar, int lane) {
+  const unsigned seg_bytes = (unsigned)e.seg16 * 16u, valid = e.valid;
+  const int mats = (e.flags & 1) ? 2 : 1;
+  if (lane == 0) mb_expect(bar, valid * mats * seg_bytes);
+  if (e.flags & 2) {
+    if (lane < mats)
+      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, L.W[e.widx + lane] + e.src_off, valid * seg_bytes, bar);
   } else if (lane < MG_RL * mats) {
     const int m = lane / MG_RL, rr = lane % MG_RL;
-    if ((unsigned)rr < valid) {
-      const uint8_t* base = L.W[w0 + (mats == 2 ? m : seg)];
-      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, base + (size_t)(row0 + rr) * sh.row_bytes + (size_t)c.cs * seg_bytes,
-              seg_bytes, bar);
-    }
+    if ((unsigned)rr < valid)
+      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, L.W[e.widx + m] + e.src_off + (size_t)rr * row_bytes, seg_bytes, bar);
   }
 }
 
@@ -735,16 +760,17 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
 
 // ---- the kernel -------------------------------------------------------------------------------------
 struct MegaSmem {
-  unsigned ring_off, bar_off, red_off, flag_off, tab_off, total;
+  unsigned ring_off, bar_off, red_off, flag_off, tab_off, ent_off, total;
 };
 __host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int stages, unsigned tables_bytes) {
   MegaSmem L;
   L.ring_off = (x_bytes + 127u) & ~127u;
   L.bar_off = L.ring_off + 8u * (unsigned)stages * slot_bytes;
   L.red_off = (L.bar_off + 8u * 8u * (unsigned)stages + 15u) & ~15u;
-  L.flag_off = L.red_off + 256u;  // 32 floats for block sums, then 8 float4 of per-warp norm sums
+  L.flag_off = L.red_off + 256u + MG_MAX_P * 32u;  // 32 floats for block sums, 8 float4 of per-warp norm sums, partial sums [MG_MAX_P][2][4]
   L.tab_off = L.flag_off + 16u;
-  L.total = L.tab_off + tables_bytes;
+  L.ent_off = L.tab_off + tables_bytes;
+  L.total = L.ent_off + 8u * MG_MAX_ENT * (unsigned)sizeof(ItemEnt);
   return L;
 }
 
@@ -759,12 +785,11 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   const uint32_t bars = sm32(smem + SL.bar_off) + (uint32_t)(warp * S) * 8u;
   float* red = reinterpret_cast<float*>(smem + SL.red_off);
   float4* wsum = reinterpret_cast<float4*>(smem + SL.red_off + 128u);
+  float* psum = reinterpret_cast<float*>(smem + SL.red_off + 256u);
   int* sflag = reinterpret_cast<int*>(smem + SL.flag_off);
   const MegaShape* shapes = reinterpret_cast<const MegaShape*>(smem + SL.tab_off);
   const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u));
   const uint32_t xs_s = sm32(smem);
-  // consecutive groups go to different blocks, so a phase with few groups still uses every SM
-  const unsigned gw = (unsigned)warp * gridDim.x + blockIdx.x, GW = gridDim.x * 8u;
   const unsigned bar_base = a.bar[1];
   const int n_phases = a.n_layers * PH_PER_LAYER;
 
@@ -778,20 +803,29 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   __syncthreads();
   const unsigned H = shapes[PH_QKV].cols;
 
-  Cursor ic{0, 0, gw, 0}, cc{0, 0, gw, 0};
-  cur_settle(ic, shapes, gw, n_phases);
-  cur_settle(cc, shapes, gw, n_phases);
+  ItemEnt* ent = reinterpret_cast<ItemEnt*>(smem + SL.ent_off) + warp * MG_MAX_ENT;
+  int n_ent = 0;
+  if (lane == 0) n_ent = build_items(ent, shapes, warp);
+  n_ent = __shfl_sync(0xffffffffu, n_ent, 0);
+  bool dead = false;  // this warp gave up (a copy never landed, or its item table overflowed): it keeps the block-level steps only
+  if (n_ent < 0) {
+    dead = true;
+    if (lane == 0) atomicOr(a.err, 4u);
+    n_ent = 0;
+  }
+  __syncwarp();
+  ItemPos ic{n_ent > 0 ? 0 : a.n_layers, 0}, cc = ic;
   unsigned issued = 0, consumed = 0;
-  while (issued < (unsigned)S && ic.p < n_phases) {
-    mg_issue(shapes, layers, ic, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
+  while (issued < (unsigned)S && ic.layer < a.n_layers) {
+    const ItemEnt e = ent[ic.e];
+    mg_issue_ent(e, layers[ic.layer], shapes[e.kind].row_bytes, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
     issued++;
-    cur_next(ic, shapes, gw, GW, n_phases);
+    pos_next(ic, n_ent);
   }
 
   long long* prof = nullptr;
   if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
     prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * n_phases * 8;
-  bool dead = false;  // this warp gave up on a copy: it keeps the block-level steps, skips its items
   int p = 0, layer = 0, kind = 0;
   for (; p < n_phases; p++) {
     const MegaLayer& L = layers[layer];
@@ -858,25 +892,29 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
       const unsigned units = sh.cols >> 6;
       // o-proj and down feed a residual-add + norm: their rows also leave the sums that norm needs
       const bool sums = kind == PH_OPROJ || kind == PH_DOWN;
-      const float* xres = kind == PH_OPROJ ? a.x_a : a.x_b;
-      const float* wpost = kind == PH_OPROJ ? L.norm[3] : L.norm[5];
-      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f;
-      float yacc[2] = {0.0f, 0.0f};
-      long long t_wait = 0, t_comp = 0, n_it = 0;
-      while (cc.p == p && !dead) {
-        const unsigned st = consumed % (unsigned)S;
-        const unsigned g = cc.g, cs = cc.cs;
-        const bool last_cs = cs + 1 == sh.n_cseg;
-        int seg = 0;
-        if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
-        if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
-        const unsigned row = (g - sh.grp_start[seg]) * MG_RL + (unsigned)rl;
-        const bool writer = cl == 0 && row < sh.rows[seg];
-        float xr = 0.0f, wpr = 0.0f;
-        if (sums && last_cs && writer) {  // in flight while the item is multiplied
-          xr = __ldcg(xres + row);
-          wpr = wpost[row];
+      // Thread f finishes row (f & 3) of this block's group (f >> 2): it adds the column segments'
+      // partial sums in order, applies the epilogue and stores the row.
+      const unsigned n_g = block_groups(sh), C = sh.n_cseg;
+      unsigned frow = 0;
+      int fseg = 0;
+      bool fin = false;
+      float xr = 0.0f, wpr = 0.0f;
+      if ((threadIdx.x >> 2) < n_g) {
+        const unsigned g = blockIdx.x + (threadIdx.x >> 2) * gridDim.x;
+        if (sh.n_seg > 1 && g >= sh.grp_start[1]) fseg = 1;
+        if (sh.n_seg > 2 && g >= sh.grp_start[2]) fseg = 2;
+        frow = (g - sh.grp_start[fseg]) * MG_RL + (threadIdx.x & 3u);
+        fin = frow < sh.rows[fseg];
+        if (fin && sums) {  // in flight while the items are multiplied
+          xr = __ldcg((kind == PH_OPROJ ? a.x_a : a.x_b) + frow);
+          wpr = (kind == PH_OPROJ ? L.norm[3] : L.norm[5])[frow];
         }
+      }
+      long long t_wait = 0, t_comp = 0, n_it = 0;
+      while (cc.layer == layer && !dead) {
+        const ItemEnt e = ent[cc.e];
+        if (e.kind != kind) break;
+        const unsigned st = consumed % (unsigned)S;
         const long long tq0 = prof ? clock64() : 0;
         if (!mb_wait(bars + st * 8u, (consumed / (unsigned)S) & 1u)) {
           dead = true;
@@ -885,55 +923,68 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         }
         const uint32_t slot = ring_s + st * a.slot_bytes;
         const long long tq1 = prof ? clock64() : 0;
+        float yacc[2] = {0.0f, 0.0f};
         if (sh.type == MG_GATE_UP)
-          mg_item_compute<2>(slot, xs_s, units, sh.seg_blocks, cs, cl, rl, yacc);
+          mg_item_compute<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         else
-          mg_item_compute<1>(slot, xs_s, units, sh.seg_blocks, cs, cl, rl, yacc);
+          mg_item_compute<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         if (prof) {
           t_wait += tq1 - tq0;
           t_comp += clock64() - tq1;
           n_it++;
         }
         consumed++;
-        if (last_cs) {
-          float v0 = yacc[0], v1 = yacc[1];
+        float v0 = yacc[0], v1 = yacc[1];
 #pragma unroll
-          for (int o = MG_LPR / 2; o > 0; o >>= 1) {
-            v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-            v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-          }
-          if (writer) {
-            float* y = kind == PH_QKV ? (seg == 0 ? a.q : seg == 1 ? a.k : a.v) : kind == PH_GATEUP ? a.ff : a.yb;
-            const float val = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
-            y[row] = val;
-            if (sums) {
-              const float t = val * wpr;
-              ns0 = fmaf(val, val, ns0);
-              ns1 = fmaf(xr, t, ns1);
-              ns2 = fmaf(t, t, ns2);
-              ns3 = fmaf(xr, xr, ns3);
-            }
-          }
-          yacc[0] = yacc[1] = 0.0f;
+        for (int o = MG_LPR / 2; o > 0; o >>= 1) {
+          v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+          v1 += __shfl_xor_sync(0xffffffffu, v1, o);
         }
-        cur_next(cc, shapes, gw, GW, n_phases);
+        if (cl == 0) {
+          psum[e.pslot * 8u + (unsigned)rl] = v0;
+          psum[e.pslot * 8u + 4u + (unsigned)rl] = v1;
+        }
+        pos_next(cc, n_ent);
         // Refill now only when the next item of THIS phase is not in flight yet; everything else is
         // refilled after the barrier arrival below, off the critical path.
-        if (ic.p == p) {
+        if (ic.layer == layer && ent[ic.e].kind == kind) {
           __syncwarp();
           if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
           __syncwarp();
-          mg_issue(shapes, layers, ic, slot, bars + st * 8u, lane);
+          const ItemEnt ne = ent[ic.e];
+          mg_issue_ent(ne, layers[ic.layer], sh.row_bytes, slot, bars + st * 8u, lane);
           issued++;
-          cur_next(ic, shapes, gw, GW, n_phases);
+          pos_next(ic, n_ent);
+        }
+      }
+      __syncthreads();  // the partial sums of every item of this block are in shared memory
+      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f;
+      if (fin) {
+        const float* ps = psum + (size_t)(threadIdx.x >> 2) * C * 8u + (threadIdx.x & 3u);
+        float v0 = 0.0f, v1 = 0.0f;
+        for (unsigned cs = 0; cs < C; cs++) {
+          v0 += ps[cs * 8u];
+          v1 += ps[cs * 8u + 4u];
+        }
+        float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : kind == PH_GATEUP ? a.ff : a.yb;
+        const float val = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
+        y[frow] = val;
+        if (sums) {
+          const float t = val * wpr;
+          ns0 = val * val;
+          ns1 = xr * t;
+          ns2 = t * t;
+          ns3 = xr * xr;
         }
       }
       if (sums) {
-        // only the four writer lanes (0, 8, 16, 24) hold anything
-        ns0 += __shfl_xor_sync(0xffffffffu, ns0, 8);  ns1 += __shfl_xor_sync(0xffffffffu, ns1, 8);
-        ns2 += __shfl_xor_sync(0xffffffffu, ns2, 8);  ns3 += __shfl_xor_sync(0xffffffffu, ns3, 8);
-        ns0 += __shfl_xor_sync(0xffffffffu, ns0, 16); ns1 += __shfl_xor_sync(0xffffffffu, ns1, 16);
-        ns2 += __shfl_xor_sync(0xffffffffu, ns2, 16); ns3 += __shfl_xor_sync(0xffffffffu, ns3, 16);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          ns0 += __shfl_xor_sync(0xffffffffu, ns0, o);
+          ns1 += __shfl_xor_sync(0xffffffffu, ns1, o);
+          ns2 += __shfl_xor_sync(0xffffffffu, ns2, o);
+          ns3 += __shfl_xor_sync(0xffffffffu, ns3, o);
+        }
         if (lane == 0) wsum[warp] = make_float4(ns0, ns1, ns2, ns3);
       }
       if (prof) {
@@ -949,14 +1000,15 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
     }
     grid_arrive(a.bar, (kind == PH_OPROJ || kind == PH_DOWN) ? wsum : nullptr, a.nsum);
     // refill the ring while the other blocks arrive
-    if (!dead && issued - consumed < (unsigned)S && ic.p < n_phases) {
+    if (!dead && issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
       if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      while (issued - consumed < (unsigned)S && ic.p < n_phases) {
+      while (issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
         const unsigned st = issued % (unsigned)S;
-        mg_issue(shapes, layers, ic, ring_s + st * a.slot_bytes, bars + st * 8u, lane);
+        const ItemEnt ne = ent[ic.e];
+        mg_issue_ent(ne, layers[ic.layer], shapes[ne.kind].row_bytes, ring_s + st * a.slot_bytes, bars + st * 8u, lane);
         issued++;
-        cur_next(ic, shapes, gw, GW, n_phases);
+        pos_next(ic, n_ent);
       }
     }
     if (++kind == PH_PER_LAYER) {
@@ -1058,15 +1110,30 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   unsigned slot_cap = (budget - fixed.total) / (8u * stages);
   slot_cap &= ~15u;
   if (slot_cap > 8192u) slot_cap = 8192u;
-  // blocks per column segment: the largest even divisor of the row's block count that fits a slot
-  auto pick_seg = [&](unsigned cols, unsigned mats) {
+  // Blocks per column segment.  A block's items (its groups x column segments) are shared by its 8
+  // warps, so more segments shorten the longest warp until the per-item overhead (measured: a little more
+  // than one unit's worth of time) wins; segments hold an even number of blocks (8 lanes per row) and must fit a ring slot.
+  const unsigned grid = (unsigned)ctx->sm_count;
+  auto pick_seg = [&](unsigned cols, unsigned mats, unsigned total_groups) {
     const unsigned nb = cols / 256u;
+    const unsigned n_g = (total_groups + grid - 1) / grid;
     unsigned best = 0;
-    for (unsigned c = 2; c <= nb; c += 2)
-      if (nb % c == 0 && 4u * mats * c * KS_Q4K_BLOCK_BYTES <= slot_cap) best = c;
+    float best_cost = 0.f;
+    for (unsigned C = 1; C <= nb; C++) {
+      if (nb % C) continue;
+      const unsigned sb = nb / C;
+      if (sb % 2 || 4u * mats * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
+      const float cost = (float)((n_g * C + 7u) / 8u) * ((float)(sb * mats) * 0.5f + 1.2f);
+      if (!best || cost < best_cost) {
+        best = sb;
+        best_cost = cost;
+      }
+    }
     return best;
   };
-  const unsigned sb_h = pick_seg(H, 1), sb_h2 = pick_seg(H, 2), sb_q = pick_seg(qn, 1), sb_f = pick_seg(F, 1);
+  const unsigned g_qkv = (qn + 3) / 4 + 2 * ((kvn + 3) / 4), g_h = (H + 3) / 4, g_f = (F + 3) / 4;
+  if (g_qkv > 64u * grid || g_f > 64u * grid || g_h > 64u * grid) return KS_OK;  // a block finishes at most 64 groups per phase
+  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_h2 = pick_seg(H, 2, g_f), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
   if (!sb_h || !sb_h2 || !sb_q || !sb_f) return KS_OK;
   unsigned slot_bytes = 0;
   auto upd = [&](unsigned sb, unsigned mats) {
@@ -1075,6 +1142,12 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   };
   upd(sb_h, 1); upd(sb_h2, 2); upd(sb_q, 1); upd(sb_f, 1);
 
+  {  // every warp's items of one layer must fit its table
+    auto per_warp = [&](unsigned total_groups, unsigned ncs) { return ((total_groups + grid - 1) / grid * ncs + 7u) / 8u; };
+    const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) + per_warp(g_f, H / 256 / sb_h2) +
+                           per_warp(g_h, F / 256 / sb_f);
+    if (worst > (unsigned)MG_MAX_ENT) return KS_OK;
+  }
   std::vector<unsigned char> tab(tables_bytes, 0);
   MegaShape* sh = reinterpret_cast<MegaShape*>(tab.data());
   MegaLayer* ly = reinterpret_cast<MegaLayer*>(tab.data() + shapes_bytes);
@@ -1144,7 +1217,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.nsum = reinterpret_cast<float4*>(mg->d_sync + 64);
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
   a.prof = mg->d_prof;
-  mg->grid = (unsigned)ctx->sm_count;
+  mg->grid = grid;
   mg->smem = mg_smem(x_bytes, slot_bytes, stages, tables_bytes).total;
   mg->G = (int)G;
   mg->dpl = (int)(hd / 32);
