@@ -135,6 +135,117 @@ __device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, un
   return *sflag != 0;
 }
 
+// ---- x as 24-bit block fixed point, weights x x as byte dot products ----------------------------
+// Each 32-element sub-block of the staged vector shares a scale s; element i is the integer
+// X_i = round(x_i / s), |X_i| <= 8e6, kept as three byte planes (X = l2*65536 + l1*256 + l0, l2
+// signed).  Four neighbouring nibbles of a weight word, masked in place, are the other operand of a
+// dp4a, so 4 weights cost 3 integer dot-product instructions instead of ~9 f32 instructions, and the
+// shared-memory traffic for x drops from 4 bytes to 3/4 byte per weight.  Integer accumulation is
+// exact; the only approximation is x to 24 bits of its sub-block's largest element (f32 has 24 bits
+// per element), far inside the parity tolerance.
+// Shared-memory layout: plane k (k = 0..2) at k * units * 80 bytes, unit u at u * 80 inside it (64
+// used: words 0..7 = elements 0..31 of the low-nibble sub-block, 8..15 = the high-nibble one; the pad
+// keeps the 8 lanes of a row on different banks), then units * 16 bytes of (sum_lo, sum_hi, s_lo, s_hi).
+constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
+constexpr unsigned MG_XU = 80;  // bytes per unit and plane
+__device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, unsigned c, float4 v) {
+  const unsigned e = c << 2;
+  const unsigned u = e >> 6, hi = (e >> 5) & 1u, l = e & 31u;
+  float s = (v.x + v.y) + (v.z + v.w);
+  float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+  for (int o = 1; o <= 4; o <<= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  }
+  const float inv = am > 0.0f ? __fdividef(8.0e6f, am) : 0.0f;
+  const float sc = am > 0.0f ? am * (1.0f / 8.0e6f) : 1.0f;
+  const int X0 = __float2int_rn(v.x * inv), X1 = __float2int_rn(v.y * inv), X2 = __float2int_rn(v.z * inv),
+            X3 = __float2int_rn(v.w * inv);
+  const unsigned wi = hi * 8u + (l >> 2);
+  unsigned char* base = xs + (size_t)u * MG_XU + wi * 4u;
+  const size_t plane = (size_t)units * MG_XU;
+  *reinterpret_cast<uint32_t*>(base) = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+  *reinterpret_cast<uint32_t*>(base + plane) = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
+  *reinterpret_cast<uint32_t*>(base + 2 * plane) = __byte_perm(__byte_perm(X0, X1, 0x0062), __byte_perm(X2, X3, 0x0062), 0x5410);
+  if ((threadIdx.x & 7u) == 0) {
+    float* mt = reinterpret_cast<float*>(xs + 3 * plane + (size_t)u * 16u);
+    mt[hi] = s;
+    mt[2 + hi] = sc;
+  }
+}
+__device__ __forceinline__ unsigned dp4a_uu(unsigned a, unsigned b, unsigned c) {
+  unsigned d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {  // a: unsigned bytes, b: signed bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds_f4o(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFF));
+  return v;
+}
+// One weight word (8 nibbles: elements j..j+3 of the low and of the high sub-block) against the
+// matching x words of the three planes.
+__device__ __forceinline__ void fx_word(uint32_t w, unsigned xl0, unsigned xl1, unsigned xl2, unsigned xh0, unsigned xh1,
+                                        unsigned xh2, unsigned (&alo)[2], int& alo2, unsigned (&ahi)[2], int& ahi2) {
+  const unsigned lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+  alo[0] = dp4a_uu(lo, xl0, alo[0]);
+  alo[1] = dp4a_uu(lo, xl1, alo[1]);
+  alo2 = dp4a_us(lo, xl2, alo2);
+  ahi[0] = dp4a_uu(hi, xh0, ahi[0]);
+  ahi[1] = dp4a_uu(hi, xh1, ahi[1]);
+  ahi2 = dp4a_us(hi, xh2, ahi2);
+}
+// Multiply-accumulate one item against the fixed-point x: MATS row slots per lane.
+template <int MATS>
+__device__ __forceinline__ void mg_item_compute_fx(uint32_t slot_addr, uint32_t xs_s, unsigned units, unsigned seg_blocks,
+                                                   unsigned cs, int cl, int rl, float (&yacc)[2]) {
+  const int g = cl & 3;
+  const unsigned seg_bytes = seg_blocks * KS_Q4K_BLOCK_BYTES, seg_units = seg_blocks * 4, upl = seg_units / MG_LPR;
+  const uint32_t plane = units * MG_XU;
+  uint32_t waddr = slot_addr + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
+  uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * MG_XU;
+  uint32_t maddr = xs_s + 3u * plane + (cs * seg_units + (unsigned)cl) * 16u;
+  for (unsigned it = 0; it < upl; it++) {
+    const float4 mt = lds_f4o<0>(maddr);
+    // 16 words per plane: [0..7] low sub-block, [8..15] high sub-block
+    const uint4 a0 = lds_u4o<0>(xaddr), a1 = lds_u4o<16>(xaddr), a2 = lds_u4o<32>(xaddr), a3 = lds_u4o<48>(xaddr);
+    const uint4 b0 = lds_u4o<0>(xaddr + plane), b1 = lds_u4o<16>(xaddr + plane), b2 = lds_u4o<32>(xaddr + plane),
+                b3 = lds_u4o<48>(xaddr + plane);
+    const uint4 c0 = lds_u4o<0>(xaddr + 2 * plane), c1 = lds_u4o<16>(xaddr + 2 * plane), c2 = lds_u4o<32>(xaddr + 2 * plane),
+                c3 = lds_u4o<48>(xaddr + 2 * plane);
+#pragma unroll
+    for (int r = 0; r < MATS; r++) {
+      const uint32_t wa = waddr + (uint32_t)(r * MG_RL) * seg_bytes;
+      const uint4 q0 = lds_u4o<16>(wa), q1 = lds_u4o<32>(wa);
+      const uint4 hdr = lds_u4o<0>(wa - (uint32_t)g * 32u);
+      unsigned alo[2] = {0u, 0u}, ahi[2] = {0u, 0u};
+      int alo2 = 0, ahi2 = 0;
+      fx_word(q0.x, a0.x, b0.x, c0.x, a2.x, b2.x, c2.x, alo, alo2, ahi, ahi2);
+      fx_word(q0.y, a0.y, b0.y, c0.y, a2.y, b2.y, c2.y, alo, alo2, ahi, ahi2);
+      fx_word(q0.z, a0.z, b0.z, c0.z, a2.z, b2.z, c2.z, alo, alo2, ahi, ahi2);
+      fx_word(q0.w, a0.w, b0.w, c0.w, a2.w, b2.w, c2.w, alo, alo2, ahi, ahi2);
+      fx_word(q1.x, a1.x, b1.x, c1.x, a3.x, b3.x, c3.x, alo, alo2, ahi, ahi2);
+      fx_word(q1.y, a1.y, b1.y, c1.y, a3.y, b3.y, c3.y, alo, alo2, ahi, ahi2);
+      fx_word(q1.z, a1.z, b1.z, c1.z, a3.z, b3.z, c3.z, alo, alo2, ahi, ahi2);
+      fx_word(q1.w, a1.w, b1.w, c1.w, a3.w, b3.w, c3.w, alo, alo2, ahi, ahi2);
+      const float flo = fmaf((float)alo2, 65536.0f, fmaf((float)alo[1], 256.0f, (float)alo[0])) * mt.z;
+      const float fhi = fmaf((float)ahi2, 65536.0f, fmaf((float)ahi[1], 256.0f, (float)ahi[0])) * mt.w;
+      yacc[r] = q4k_apply_scales(hdr, g, flo, fhi, mt.x, mt.y, yacc[r]);
+    }
+    waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
+    xaddr += MG_LPR * MG_XU;
+    maddr += MG_LPR * 16u;
+  }
+}
+
+
 // ---- staging of x (with the fused norm prologues), reads through L2 ---------------------------
 // Norm weights of the next matvec phase, fetched into registers before the barrier wait.
 struct NormPre {
@@ -172,7 +283,7 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
 #pragma unroll
       for (int k = 0; k < MG_XMAX; k++) {
         const unsigned c = base + threadIdx.x + k * blockDim.x;
-        if (c < nchunk) q4k_put_chunk(xp, sx, c, v[k]);
+        if (c < nchunk) fx_put_chunk(xs, units, c, v[k]);
       }
     }
     return;
@@ -245,7 +356,7 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
       r.y = __fmul_rn(__fmul_rn(v[k].y, inv2), w4.y);
       r.z = __fmul_rn(__fmul_rn(v[k].z, inv2), w4.z);
       r.w = __fmul_rn(__fmul_rn(v[k].w, inv2), w4.w);
-      q4k_put_chunk(xp, sx, c, r);
+      fx_put_chunk(xs, units, c, r);
     }
   }
 }
@@ -307,14 +418,13 @@ __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned col
       q.y = __fmul_rn(__fmul_rn(r.y, inv2), w4.y);
       q.z = __fmul_rn(__fmul_rn(r.z, inv2), w4.z);
       q.w = __fmul_rn(__fmul_rn(r.w, inv2), w4.w);
-      q4k_put_chunk(xp, sx, c, q);
+      fx_put_chunk(xs, units, c, q);
     }
   }
 }
 
 // ---- the per-warp item list of a whole token -----------------------------------------------------
 // Item = (phase, row group, column segment).
-constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
 
 // The items of a warp repeat layer after layer (same shapes, other pointers), so the walk over the
 // shapes is done once per kernel: each warp records its items of ONE layer, in phase order, and the
@@ -925,9 +1035,9 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         const long long tq1 = prof ? clock64() : 0;
         float yacc[2] = {0.0f, 0.0f};
         if (sh.type == MG_GATE_UP)
-          mg_item_compute<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
+          mg_item_compute_fx<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         else
-          mg_item_compute<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
+          mg_item_compute_fx<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         if (prof) {
           t_wait += tq1 - tq0;
           t_comp += clock64() - tq1;

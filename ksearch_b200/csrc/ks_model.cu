@@ -436,9 +436,10 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   m->seq_len.assign(g.n_slots, 0);
   const size_t S = g.n_slots;
   m->fused = ks_matvec_can_fuse_pro(KS_Q4K, H) && !getenv("KSEARCH_UNFUSED");
-  // KSEARCH_DECODE_KERNEL=1: single-slot steps run all layers inside one persistent kernel
+  // Single-slot steps run all layers inside one persistent kernel; KSEARCH_DECODE_KERNEL=0 keeps one
+  // launch per op (the path every multi-slot step takes anyway).
   const char* dk = getenv("KSEARCH_DECODE_KERNEL");
-  m->use_mega = m->fused && g.act == KS_F32 && dk && dk[0] == '1';
+  m->use_mega = m->fused && g.act == KS_F32 && !(dk && dk[0] == '0');
   ok = ok && dev_alloc(m, &m->xb, S * H * ab) == KS_OK && dev_alloc(m, &m->xn, S * H * ab) == KS_OK;
   ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
        dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&

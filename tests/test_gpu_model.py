@@ -150,10 +150,10 @@ def test_model_with_dependent_launch_matches(oracle):
 
 @pytest.mark.parametrize("n_kv", [1, 2])
 def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv):
-    """KSEARCH_DECODE_KERNEL=1: every layer of a single-slot step runs inside one persistent kernel
-    (grid barriers between phases).  Same parity bar as the launch-per-op path."""
+    """Every layer of a single-slot step runs inside one persistent kernel (grid barriers between
+    phases) unless KSEARCH_DECODE_KERNEL=0.  Same parity bar as the launch-per-op path."""
     from ksearch_b200 import CudaContext
-    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", "1")
+    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=80, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=21, keep=True)
@@ -168,6 +168,26 @@ def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv)
     assert equal + ties == 24 and ties <= 1
     out2, _ = model.generate_timed(prompt, 24, max_inflight=0)
     assert out2 == out
+    cpu.close()
+    model.close()
+    c.close()
+
+
+def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
+    """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", "0")
+    c = CudaContext(0, flags=1)
+    cfg = ksm.tiny_config(max_seq=48)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=22, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    _teacher_forced(model, cpu, synth.token_ids(22, "tf", 20, cfg.vocab))
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is None      # the persistent kernel was never built
+    prompt = synth.token_ids(22, "prompt", 8, cfg.vocab)
+    out, _ = model.generate_timed(prompt, 24)
+    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    assert equal + ties == 24 and ties <= 1
     cpu.close()
     model.close()
     c.close()
