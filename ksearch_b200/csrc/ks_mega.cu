@@ -35,6 +35,8 @@ struct MegaShape {          // one of the five phases of a layer; the same for e
   unsigned rows[3];
   unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups (0 for attention)
   unsigned cols, row_bytes, seg_blocks, n_cseg;
+  int oct;                  // 1: a block owns runs of 8 consecutive groups (32 rows = one sub-block of the next phase's x)
+  int pad_;
 };
 
 struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
@@ -55,14 +57,15 @@ struct MegaArgs {
   const float* rope;        // [max_seq, hd]
   const int* pos;           // [1]
   float *x_a, *x_b;         // residual stream: layers read x_a / write x_b at the FFN, the reverse at the next qkv
-  float *yb, *q, *k, *v, *o, *ff;
+  float *yb, *q, *k, *v;
+  unsigned char *ox, *ffx;  // attention output and GeGLU output, written by their producers in the staged fixed-point layout
   float* att_tmp;           // [n_q * n_splits * (hd + 2)]
   float4* nsum;             // [grid] per-block sums of the last o-proj / down phase: (sum y^2, sum x*y*wp, sum (y*wp)^2, sum x^2)
   unsigned* att_cnt;        // [n_q] arrival counters of the attention blocks, per head
   unsigned* bar;            // [0] running barrier counter, [1] its value when the previous token ended
   unsigned* err;
-  long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released,
-                            // then warp 0's copy-wait cycles, compute cycles, items
+  long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released
+                            // (attention rows: 4..7 = q/k/v ready, positions done, folded, arrived)
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -119,20 +122,36 @@ __device__ __forceinline__ void grid_arrive(unsigned* counter, const float4* wsu
   }
 }
 // Returns false when the wait gave up.
-__device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, unsigned* err, int* sflag) {
-  if (threadIdx.x == 0) {
-    int ok = 0;
+// Lane 0 of four warps polls: their loads drift apart in time, so the arrival of the last block is
+// seen sooner than one poller's round trip allows.  sflag: 0 = waiting, 1 = released, 2 = gave up.
+// Two flag words alternate between consecutive barriers, so a word is cleared a whole phase after its last reader.
+__device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, unsigned* err, int* flags, int parity) {
+  int* sflag = flags + parity;
+  if (threadIdx.x == 0) flags[parity ^ 1] = 0;
+  if ((threadIdx.x & 31) == 0 && threadIdx.x < 128) {
+    volatile int* vf = sflag;
+    int state = 0;
     for (unsigned i = 0; i < (1u << 21); i++) {  // a second or two of polling at most
       if ((int)(ld_acquire_u32(counter) - target) >= 0) {
-        ok = 1;
+        state = 1;
         break;
       }
+      if (*vf == 1) {  // another poller saw it; take the acquire ourselves before reading what other blocks wrote
+        if ((int)(ld_acquire_u32(counter) - target) >= 0) {
+          state = 1;
+          break;
+        }
+      }
     }
-    if (!ok) atomicOr(err, 2u);
-    *sflag = ok;
+    if (state == 1) {
+      *vf = 1;
+    } else {
+      atomicOr(err, 2u);
+      *vf = 2;
+    }
   }
   __syncthreads();
-  return *sflag != 0;
+  return *sflag == 1;
 }
 
 // ---- x as 24-bit block fixed point, weights x x as byte dot products ----------------------------
@@ -172,6 +191,47 @@ __device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, 
     float* mt = reinterpret_cast<float*>(xs + 3 * plane + (size_t)u * 16u);
     mt[hi] = s;
     mt[2 + hi] = sc;
+  }
+}
+// The same layout written to GLOBAL memory by a producer: the warp holds the 32 consecutive elements
+// e0 .. e0+31 of one sub-block, one per lane (e0 a multiple of 32).
+__device__ __forceinline__ void fx_store_subblock(unsigned char* dst, unsigned units, unsigned e0, float val, int lane) {
+  float s = val, am = fabsf(val);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  }
+  const float inv = am > 0.0f ? __fdividef(8.0e6f, am) : 0.0f;
+  const float sc = am > 0.0f ? am * (1.0f / 8.0e6f) : 1.0f;
+  const int X = __float2int_rn(val * inv);
+  const unsigned u = e0 >> 6, hi = (e0 >> 5) & 1u;
+  const size_t plane = (size_t)units * MG_XU;
+  unsigned char* base = dst + (size_t)u * MG_XU + hi * 32u + (unsigned)lane;
+  base[0] = (unsigned char)(X & 0xFF);
+  base[plane] = (unsigned char)((X >> 8) & 0xFF);
+  base[2 * plane] = (unsigned char)((X >> 16) & 0xFF);
+  if (lane == 0) {
+    float* mt = reinterpret_cast<float*>(dst + 3 * plane + (size_t)u * 16u);
+    mt[hi] = s;
+    mt[2 + hi] = sc;
+  }
+}
+// Bring a vector a producer left in that layout into shared memory (units * 256 bytes; the pad words travel too).
+__device__ __forceinline__ void fx_copy_in(unsigned char* xs, const unsigned char* src, unsigned units) {
+  const unsigned n16 = units * 16u;  // 3 planes of 80 bytes + 16 bytes of sums and scales per unit
+  for (unsigned base = 0; base < n16; base += 6u * blockDim.x) {
+    uint4 v[6];
+#pragma unroll
+    for (int k = 0; k < 6; k++) {
+      const unsigned i = base + threadIdx.x + k * blockDim.x;
+      if (i < n16) v[k] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
+    }
+#pragma unroll
+    for (int k = 0; k < 6; k++) {
+      const unsigned i = base + threadIdx.x + k * blockDim.x;
+      if (i < n16) reinterpret_cast<uint4*>(xs)[i] = v[k];
+    }
   }
 }
 __device__ __forceinline__ unsigned dp4a_uu(unsigned a, unsigned b, unsigned c) {
@@ -248,14 +308,16 @@ __device__ __forceinline__ void mg_item_compute_fx(uint32_t slot_addr, uint32_t 
 
 // ---- staging of x (with the fused norm prologues), reads through L2 ---------------------------
 // Norm weights of the next matvec phase, fetched into registers before the barrier wait.
-struct NormPre {
-  float4 w[KS_PRO_MAXC], wp[KS_PRO_MAXC];
+template <int PC>
+struct NormPre {  // PC chunks of 4 elements per thread: cols <= PC * 4 * blockDim
+  float4 w[PC], wp[PC];
 };
-__device__ __forceinline__ void mg_prefetch_norm(NormPre& n, int mode, const float* w, const float* wp, unsigned cols) {
+template <int PC>
+__device__ __forceinline__ void mg_prefetch_norm(NormPre<PC>& n, int mode, const float* w, const float* wp, unsigned cols) {
   const unsigned nchunk = cols >> 2;
   if (mode == KS_PRO_NONE) return;
 #pragma unroll
-  for (int k = 0; k < KS_PRO_MAXC; k++) {
+  for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
       n.w[k] = reinterpret_cast<const float4*>(w)[c];
@@ -267,11 +329,10 @@ __device__ __forceinline__ void mg_prefetch_norm(NormPre& n, int mode, const flo
 constexpr int MG_XMAX = 8;  // plain staging keeps up to 8 chunks per thread in flight (cols <= 8192), loops beyond
 
 // mode NONE: x' = x.  NORM: x' = rms(x)*w.  ADD_NORM: r = x + rms(y)*wp (block 0 stores r to out_x); x' = rms(r)*w.
+template <int PC>
 __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mode, unsigned cols, const float* x,
-                                           const float* y, float* out_x, float eps, const NormPre& n, long long* pf = nullptr) {
+                                           const float* y, float* out_x, float eps, const NormPre<PC>& n) {
   const unsigned units = cols >> 6, nchunk = cols >> 2;
-  float* xp = reinterpret_cast<float*>(xs);
-  float* sx = xp + (size_t)units * Q4K_XS;
   if (mode == KS_PRO_NONE) {
     for (unsigned base = 0; base < nchunk; base += MG_XMAX * blockDim.x) {
       float4 v[MG_XMAX];
@@ -289,11 +350,11 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
     return;
   }
   const float invn = 1.0f / (float)cols;
-  float4 v[KS_PRO_MAXC], yv[KS_PRO_MAXC];
+  float4 v[PC], yv[PC];
   float ss = 0.0f;
   if (mode == KS_PRO_ADD_NORM) {
 #pragma unroll
-    for (int k = 0; k < KS_PRO_MAXC; k++) {
+    for (int k = 0; k < PC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
         yv[k] = ldcg4(y, c);
@@ -301,20 +362,18 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
       }
     }
 #pragma unroll
-    for (int k = 0; k < KS_PRO_MAXC; k++) {
+    for (int k = 0; k < PC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
         ss = fmaf(yv[k].x, yv[k].x, ss); ss = fmaf(yv[k].y, yv[k].y, ss);
         ss = fmaf(yv[k].z, yv[k].z, ss); ss = fmaf(yv[k].w, yv[k].w, ss);
       }
     }
-    if (pf) pf[4] = clock64();
     ss = block_sum_f(ss, red);
-    if (pf) pf[5] = clock64();
     const float inv = 1.0f / sqrtf(ss * invn + eps);
     ss = 0.0f;
 #pragma unroll
-    for (int k = 0; k < KS_PRO_MAXC; k++) {
+    for (int k = 0; k < PC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) {
         const float4 p4 = n.wp[k];
@@ -329,25 +388,23 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
     }
   } else {
 #pragma unroll
-    for (int k = 0; k < KS_PRO_MAXC; k++) {
+    for (int k = 0; k < PC; k++) {
       const unsigned c = threadIdx.x + k * blockDim.x;
       if (c < nchunk) v[k] = ldcg4(x, c);
     }
   }
 #pragma unroll
-  for (int k = 0; k < KS_PRO_MAXC; k++) {
+  for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
       ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
       ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
     }
   }
-  if (pf) pf[6] = clock64();
   ss = block_sum_f(ss, red);
-  if (pf) pf[7] = clock64();
   const float inv2 = 1.0f / sqrtf(ss * invn + eps);
 #pragma unroll
-  for (int k = 0; k < KS_PRO_MAXC; k++) {
+  for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
       const float4 w4 = n.w[k];
@@ -363,20 +420,19 @@ __device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mo
 
 // ADD_NORM without any block-wide reduction: the blocks that produced y left the four sums that both
 // norms need (K:539 expands to  sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2,  r = x + inv y wp).
+template <int PC>
 __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned cols, const float* x, const float* y, float* out_x,
-                                                 float eps, const NormPre& n, const float4* nsum, unsigned nblocks, long long* pf = nullptr) {
+                                                 float eps, const NormPre<PC>& n, const float4* nsum, unsigned nblocks) {
   const unsigned units = cols >> 6, nchunk = cols >> 2;
   const int lane = threadIdx.x & 31;
-  float* xp = reinterpret_cast<float*>(xs);
-  float* sx = xp + (size_t)units * Q4K_XS;
-  float4 v[KS_PRO_MAXC], yv[KS_PRO_MAXC], ps[8];
+  float4 v[PC], yv[PC], ps[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) {
     const unsigned i = (unsigned)lane + 32u * j;
     ps[j] = i < nblocks ? __ldcg(nsum + i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 #pragma unroll
-  for (int k = 0; k < KS_PRO_MAXC; k++) {
+  for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
       yv[k] = ldcg4(y, c);
@@ -384,7 +440,6 @@ __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned col
     }
   }
   float4 t = ps[0];
-  if (pf) pf[4] = clock64();
 #pragma unroll
   for (int j = 1; j < 8; j++) {
     t.x += ps[j].x; t.y += ps[j].y; t.z += ps[j].z; t.w += ps[j].w;
@@ -396,14 +451,12 @@ __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned col
     t.z += __shfl_xor_sync(0xffffffffu, t.z, o);
     t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
   }
-  if (pf) pf[5] = clock64() + (long long)(t.x > 1e30f);
   const float invn = 1.0f / (float)cols;
   const float inv = 1.0f / sqrtf(t.x * invn + eps);
   const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
   const float inv2 = 1.0f / sqrtf(fmaxf(rr, 0.0f) * invn + eps);
-  if (pf) pf[6] = clock64() + (long long)(inv2 > 1e30f);
 #pragma unroll
-  for (int k = 0; k < KS_PRO_MAXC; k++) {
+  for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
     if (c < nchunk) {
       const float4 p4 = n.wp[k], w4 = n.w[k];
@@ -453,7 +506,15 @@ __device__ __forceinline__ void pos_next(ItemPos& c, int n_ent) {
 constexpr int MG_MAX_P = 64;  // items of one block in one phase
 __device__ __forceinline__ unsigned block_groups(const MegaShape& sh) {
   const unsigned total = sh.type == MG_ATTN ? 0u : sh.grp_start[sh.n_seg];
+  if (sh.oct) {
+    const unsigned octs = (total + 7u) / 8u;
+    return octs > blockIdx.x ? (octs - blockIdx.x + gridDim.x - 1) / gridDim.x * 8u : 0u;
+  }
   return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+}
+// global group index of this block's k-th group
+__device__ __forceinline__ unsigned block_group_id(const MegaShape& sh, unsigned k) {
+  return sh.oct ? (blockIdx.x + (k >> 3) * gridDim.x) * 8u + (k & 7u) : blockIdx.x + k * gridDim.x;
 }
 // lane 0 of each warp fills its table; returns the entry count (0 when the warp owns nothing, -1 on overflow)
 __device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes, int warp) {
@@ -468,7 +529,8 @@ __device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes
     for (unsigned j = (unsigned)warp; j < n_items; j += 8u) {
       if (n >= MG_MAX_ENT) return -1;
       const unsigned k = j / C, cs = j - k * C;
-      const unsigned g = blockIdx.x + k * gridDim.x;
+      const unsigned g = block_group_id(sh, k);
+      if (g >= sh.grp_start[sh.n_seg]) continue;
       int seg = 0;
       if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
       if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
@@ -797,9 +859,15 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
   }
   __syncthreads();
   if (pf) pf[5] = clock64();
-  // thread d folds slot d (= j * 32 + lane of the warps' layout) over the eight warps
+  // thread d folds head dimension d over the eight warps; it sits in slot j * 32 + lane of the warps' layout
   const int d = threadIdx.x;
-  const int ddim = mg_lane_dim<DPL>(d & 31, d >> 5);  // the head dimension that slot holds
+  int dslot;
+  {
+    constexpr int BPL = DPL / 2, LPB = 16 / BPL;
+    const int within = d & 31, hh = within >> 4, w16 = within & 15;
+    dslot = (hh * BPL + (w16 % BPL)) * 32 + ((d >> 5) * LPB + w16 / BPL);
+  }
+  const unsigned ounits = (a.n_q * HD) >> 6;
   float M = kNegInit, Lsum = 0.0f, O = 0.0f;
   if (d < HD) {
     float mw[8];
@@ -812,17 +880,17 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
     for (int w = 0; w < 8; w++) {
       const float f = __expf(mw[w] - M);
       Lsum = fmaf(part[w * (HD + 2) + 1], f, Lsum);
-      O = fmaf(part[w * (HD + 2) + 2 + d], f, O);
+      O = fmaf(part[w * (HD + 2) + 2 + dslot], f, O);
     }
   }
   if (pf) pf[6] = clock64();
   if (NS == 1) {  // one split: this block's result is final
-    if (d < HD) a.o[(size_t)head * HD + ddim] = O / Lsum;
+    if (d < HD) fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), O / Lsum, lane);
     return;
   }
   float* rec = a.att_tmp + ((size_t)head * NSMAX + split) * (HD + 2);
   if (d < HD) {
-    rec[2 + d] = O;
+    rec[2 + d] = O;  // records are kept in dimension order
     if (d == 0) {
       rec[0] = M;
       rec[1] = Lsum;
@@ -862,7 +930,7 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
         LL = fmaf(lp[p], f, LL);
         OO = fmaf(ov[p], f, OO);
       }
-      a.o[(size_t)head * HD + ddim] = OO / LL;
+      fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), OO / LL, lane);
     }
     if (threadIdx.x == 0) a.att_cnt[head] = 0u;
   }
@@ -884,7 +952,7 @@ __host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_byte
   return L;
 }
 
-template <int DPL>
+template <int DPL, int PC>
 __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -905,6 +973,7 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
 
   for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
     reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
+  if (threadIdx.x == 0) sflag[2] = sflag[3] = 0;  // barrier flag words ([0] belongs to the attention phase)
   if (lane == 0) {
     for (int s = 0; s < S; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -940,13 +1009,13 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   for (; p < n_phases; p++) {
     const MegaLayer& L = layers[layer];
     // constants of this phase, fetched while the other blocks arrive at the barrier before it
-    NormPre npre;
+    NormPre<PC> npre;
     if (kind == PH_QKV)
       mg_prefetch_norm(npre, layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM, L.norm[0], layers[layer > 0 ? layer - 1 : 0].norm[5], H);
     else if (kind == PH_GATEUP)
       mg_prefetch_norm(npre, KS_PRO_ADD_NORM, L.norm[4], L.norm[3], H);
     if (p > 0) {
-      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x, a.err, sflag)) break;
+      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x, a.err, sflag + 2, p & 1)) break;
       if (prof) prof[(p - 1) * 8 + 3] = clock64();
     }
     if (prof) prof[p * 8 + 0] = clock64();
@@ -985,15 +1054,17 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         x = layer == 0 ? a.x_a : a.x_b;
         out_x = a.x_a;
       } else if (kind == PH_OPROJ) {
-        x = a.o;
+        x = nullptr;
       } else if (kind == PH_GATEUP) {
         mode = KS_PRO_ADD_NORM;
         x = a.x_a;
         out_x = a.x_b;
       } else {
-        x = a.ff;
+        x = nullptr;
       }
-      if (mode == KS_PRO_ADD_NORM)
+      if (kind == PH_OPROJ || kind == PH_DOWN)
+        fx_copy_in(smem, kind == PH_OPROJ ? a.ox : a.ffx, sh.cols >> 6);
+      else if (mode == KS_PRO_ADD_NORM)
         mg_stage_addnorm(smem, sh.cols, x, yin, out_x, a.eps, npre, a.nsum, gridDim.x);
       else
         mg_stage_x(smem, red, mode, sh.cols, x, yin, out_x, a.eps, npre);
@@ -1010,39 +1081,31 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
       bool fin = false;
       float xr = 0.0f, wpr = 0.0f;
       if ((threadIdx.x >> 2) < n_g) {
-        const unsigned g = blockIdx.x + (threadIdx.x >> 2) * gridDim.x;
+        const unsigned g = block_group_id(sh, threadIdx.x >> 2);
         if (sh.n_seg > 1 && g >= sh.grp_start[1]) fseg = 1;
         if (sh.n_seg > 2 && g >= sh.grp_start[2]) fseg = 2;
         frow = (g - sh.grp_start[fseg]) * MG_RL + (threadIdx.x & 3u);
-        fin = frow < sh.rows[fseg];
+        fin = g < sh.grp_start[sh.n_seg] && frow < sh.rows[fseg];
         if (fin && sums) {  // in flight while the items are multiplied
           xr = __ldcg((kind == PH_OPROJ ? a.x_a : a.x_b) + frow);
           wpr = (kind == PH_OPROJ ? L.norm[3] : L.norm[5])[frow];
         }
       }
-      long long t_wait = 0, t_comp = 0, n_it = 0;
       while (cc.layer == layer && !dead) {
         const ItemEnt e = ent[cc.e];
         if (e.kind != kind) break;
         const unsigned st = consumed % (unsigned)S;
-        const long long tq0 = prof ? clock64() : 0;
         if (!mb_wait(bars + st * 8u, (consumed / (unsigned)S) & 1u)) {
           dead = true;
           if (lane == 0) atomicOr(a.err, 1u);
           break;
         }
         const uint32_t slot = ring_s + st * a.slot_bytes;
-        const long long tq1 = prof ? clock64() : 0;
         float yacc[2] = {0.0f, 0.0f};
         if (sh.type == MG_GATE_UP)
           mg_item_compute_fx<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         else
           mg_item_compute_fx<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
-        if (prof) {
-          t_wait += tq1 - tq0;
-          t_comp += clock64() - tq1;
-          n_it++;
-        }
         consumed++;
         float v0 = yacc[0], v1 = yacc[1];
 #pragma unroll
@@ -1068,7 +1131,7 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         }
       }
       __syncthreads();  // the partial sums of every item of this block are in shared memory
-      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f;
+      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f, fval = 0.0f;
       if (fin) {
         const float* ps = psum + (size_t)(threadIdx.x >> 2) * C * 8u + (threadIdx.x & 3u);
         float v0 = 0.0f, v1 = 0.0f;
@@ -1076,9 +1139,12 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
           v0 += ps[cs * 8u];
           v1 += ps[cs * 8u + 4u];
         }
-        float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : kind == PH_GATEUP ? a.ff : a.yb;
-        const float val = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
-        y[frow] = val;
+        fval = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
+        const float val = fval;
+        if (kind != PH_GATEUP) {
+          float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : a.yb;
+          y[frow] = val;
+        }
         if (sums) {
           const float t = val * wpr;
           ns0 = val * val;
@@ -1086,6 +1152,11 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
           ns2 = t * t;
           ns3 = xr * xr;
         }
+      }
+      if (kind == PH_GATEUP && (threadIdx.x >> 2) < n_g) {
+        // this warp's 32 threads hold 32 consecutive rows (a run of 8 groups): one sub-block of the next phase's x
+        const unsigned g0 = block_group_id(sh, (threadIdx.x >> 2) & ~7u);
+        if (g0 < sh.grp_start[1]) fx_store_subblock(a.ffx, sh.rows[0] >> 6, g0 * MG_RL, fval, lane);
       }
       if (sums) {
 #pragma unroll
@@ -1096,11 +1167,6 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
           ns3 += __shfl_xor_sync(0xffffffffu, ns3, o);
         }
         if (lane == 0) wsum[warp] = make_float4(ns0, ns1, ns2, ns3);
-      }
-      if (prof) {
-        prof[p * 8 + 4] = t_wait;
-        prof[p * 8 + 5] = t_comp;
-        prof[p * 8 + 6] = n_it;
       }
     }
     if (prof) prof[p * 8 + 2] = clock64();
@@ -1139,16 +1205,17 @@ struct ks_mega {
   void* d_tables = nullptr;
   unsigned* d_sync = nullptr;  // words 0..1 barrier, 8..63 per-head attention arrival counters, from byte 256: per-block norm sums
   long long* d_prof = nullptr;
+  unsigned char* d_fx = nullptr;  // attention output and GeGLU output in the staged layout
   unsigned grid = 0;
   size_t smem = 0;
-  int G = 0, dpl = 0;
+  int G = 0, dpl = 0, pc = 4;  // pc: 4-element chunks of the hidden vector per thread (2 up to 2048 columns)
   float* residual = nullptr;  // buffer that holds the residual stream when the kernel ends
 };
 
 namespace {
-template <int DPL>
+template <int DPL, int PC>
 int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
-  auto kern = mega_kernel<DPL>;
+  auto kern = mega_kernel<DPL, PC>;
   static size_t smem_set[16] = {0};
   if (mg->smem > smem_set[ctx->device & 15]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mg->smem);
@@ -1172,8 +1239,8 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
 }  // namespace
 
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
-  if (mg->dpl == 4) return mega_launch_t<4>(ctx, mg);
-  if (mg->dpl == 8) return mega_launch_t<8>(ctx, mg);
+  if (mg->dpl == 4) return mg->pc == 2 ? mega_launch_t<4, 2>(ctx, mg) : mega_launch_t<4, 4>(ctx, mg);
+  if (mg->dpl == 8) return mg->pc == 2 ? mega_launch_t<8, 2>(ctx, mg) : mega_launch_t<8, 4>(ctx, mg);
   return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size not supported");
 }
 
@@ -1185,6 +1252,7 @@ void ks_mega_destroy(ks_mega* mg) {
   if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
   if (mg->d_prof) cudaFree(mg->d_prof);
+  if (mg->d_fx) cudaFree(mg->d_fx);
   delete mg;
 }
 
@@ -1224,9 +1292,9 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   // warps, so more segments shorten the longest warp until the per-item overhead (measured: a little more
   // than one unit's worth of time) wins; segments hold an even number of blocks (8 lanes per row) and must fit a ring slot.
   const unsigned grid = (unsigned)ctx->sm_count;
-  auto pick_seg = [&](unsigned cols, unsigned mats, unsigned total_groups) {
+  auto pick_seg = [&](unsigned cols, unsigned mats, unsigned total_groups, bool oct = false) {
     const unsigned nb = cols / 256u;
-    const unsigned n_g = (total_groups + grid - 1) / grid;
+    const unsigned n_g = oct ? ((total_groups + 7) / 8 + grid - 1) / grid * 8 : (total_groups + grid - 1) / grid;
     unsigned best = 0;
     float best_cost = 0.f;
     for (unsigned C = 1; C <= nb; C++) {
@@ -1243,7 +1311,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   };
   const unsigned g_qkv = (qn + 3) / 4 + 2 * ((kvn + 3) / 4), g_h = (H + 3) / 4, g_f = (F + 3) / 4;
   if (g_qkv > 64u * grid || g_f > 64u * grid || g_h > 64u * grid) return KS_OK;  // a block finishes at most 64 groups per phase
-  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_h2 = pick_seg(H, 2, g_f), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
+  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_h2 = pick_seg(H, 2, g_f, true), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
   if (!sb_h || !sb_h2 || !sb_q || !sb_f) return KS_OK;
   unsigned slot_bytes = 0;
   auto upd = [&](unsigned sb, unsigned mats) {
@@ -1254,7 +1322,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
 
   {  // every warp's items of one layer must fit its table
     auto per_warp = [&](unsigned total_groups, unsigned ncs) { return ((total_groups + grid - 1) / grid * ncs + 7u) / 8u; };
-    const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) + per_warp(g_f, H / 256 / sb_h2) +
+    const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) +
+                           (((g_f + 7) / 8 + grid - 1) / grid * 8 * (H / 256 / sb_h2) + 7u) / 8u +
                            per_warp(g_h, F / 256 / sb_f);
     if (worst > (unsigned)MG_MAX_ENT) return KS_OK;
   }
@@ -1279,7 +1348,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   sh[PH_ATTN].type = MG_ATTN; sh[PH_ATTN].n_seg = 1; sh[PH_ATTN].n_cseg = 1;
   sh[PH_OPROJ].type = MG_MATVEC; sh[PH_OPROJ].n_seg = 1; sh[PH_OPROJ].rows[0] = H;
   set_rows(sh[PH_OPROJ], qn, sb_q);
-  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F;
+  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F; sh[PH_GATEUP].oct = 1;
   set_rows(sh[PH_GATEUP], H, sb_h2);
   sh[PH_DOWN].type = MG_MATVEC; sh[PH_DOWN].n_seg = 1; sh[PH_DOWN].rows[0] = H;
   set_rows(sh[PH_DOWN], F, sb_f);
@@ -1297,12 +1366,14 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   cudaSetDevice(ctx->device);
   const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
   if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess) {
+      cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
   cudaError_t e = cudaMemcpyAsync(mg->d_tables, tab.data(), tables_bytes, cudaMemcpyHostToDevice, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 256 + 16 * (size_t)ctx->sm_count, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_fx, 0, ((size_t)qn / 64 + (size_t)F / 64) * 256, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
   if (e != cudaSuccess) {
@@ -1320,7 +1391,9 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.eps = d->eps; a.attn_scale = d->attn_scale;
   a.rope = d->rope; a.pos = d->pos;
   a.x_a = d->x_a; a.x_b = d->x_b;
-  a.yb = d->yb; a.q = d->q; a.k = d->k; a.v = d->v; a.o = d->o; a.ff = d->ff;
+  a.yb = d->yb; a.q = d->q; a.k = d->k; a.v = d->v;
+  a.ox = mg->d_fx;
+  a.ffx = mg->d_fx + (size_t)qn / 64 * 256;
   a.att_tmp = d->att_tmp;
   a.bar = mg->d_sync;
   a.att_cnt = mg->d_sync + 8;
@@ -1331,6 +1404,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   mg->smem = mg_smem(x_bytes, slot_bytes, stages, tables_bytes).total;
   mg->G = (int)G;
   mg->dpl = (int)(hd / 32);
+  mg->pc = H <= 2048 ? 2 : 4;
   mg->residual = d->x_b;
   *out = mg;
   return KS_OK;
