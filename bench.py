@@ -164,12 +164,30 @@ def workload_config(cfg, n_gpus):
             "l2": "weights (1.03 GB/token) are 8x the 126 MB L2, so every step streams them from HBM"}
 
 
-def time_kernel_alone(ctx, model_h, lib, cfg, peak):
-    """CUDA-event timing of the two heavy matvec kernels alone, over the model's own weights."""
-    import ctypes as C
-    from ksearch_b200 import Q4K, Q6K, Eng
-    eng = Eng()
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the persistent decode kernel on this
+# workload (697.9 MB read + 1.0 MB written), from the ncu capture summarised in profiles/decode_layers_e2b.md.
+DECODE_KERNEL_DRAM_TRAFFIC = 698972160
+
+
+def time_kernel_alone(ctx, model, slot, lib, cfg, peak, steps):
+    """CUDA-event timing of the heavy kernels alone, over the model's own weights."""
+    from ksearch_b200 import Q4K, Q6K
+    from ksearch_b200 import model as ksm
+    model_h = model.h
     out = {}
+    # The persistent decode kernel: steps without the head are embed + that kernel + a one-thread
+    # position update, so their device time is the kernel's (the two small launches add ~2 us).
+    n = max(4, min(steps, 32))
+    for rep in range(2):
+        ctx.timer_begin()
+        for i in range(n):
+            model.forward(slot, 1, [1 + i], False)
+        ms = ctx.timer_end_ms() / n
+    head = cfg.vocab * cfg.hidden // 256 * (210 if cfg.embd_dtype == Q6K else 144)
+    nbytes = ksm.weight_bytes_per_token(cfg) - head
+    out["decode_layers"] = {"kernel": "mega_kernel (all 35 layers of a token in one persistent launch: qkv | attention | "
+                                      "o-proj | gate-up+GELU | down per layer, grid barriers between)",
+                            "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "launches_per_token": 1}
     x = ctx.buffer_bytes(np.random.default_rng(0).standard_normal(cfg.hidden).astype(np.float32))
     # gate/up: 35 distinct layer pairs, 10.6 MB each
     y = ctx.buffer_empty_f32(cfg.ffn)
@@ -189,8 +207,8 @@ def time_kernel_alone(ctx, model_h, lib, cfg, peak):
         ms = ctx.timer_end_ms() / len(bufs)
     ctx.graph_free(gr)
     nbytes = 2 * cfg.ffn * cfg.hidden // 256 * 144 + 4 * cfg.hidden + 4 * cfg.ffn
-    out["q4k_gate_up"] = {"kernel": "mv_q4k_kernel (gate||up+GELU, 2x6144x1536)", "us": ms * 1e3, "bytes": nbytes,
-                          "gbs": nbytes / ms / 1e6, "launches_per_token": cfg.n_layers}
+    out["q4k_gate_up"] = {"kernel": "mvs_q4k_kernel (stand-alone gate||up+GELU, 2x6144x1536; the multi-slot path)",
+                          "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "launches_per_token": 0}
     for g, u in bufs:
         lib.ks_buf_free(ctx.h, g)
         lib.ks_buf_free(ctx.h, u)
@@ -203,7 +221,7 @@ def time_kernel_alone(ctx, model_h, lib, cfg, peak):
             ctx.check(lib.ks_matvec(ctx.h, cfg.vocab, cfg.hidden, Q6K, e, 0, 0, x.h, 0, lg.h, 0, 1))
         ms = ctx.timer_end_ms() / 4
     nbytes = cfg.vocab * cfg.hidden // 256 * 210 + 4 * cfg.hidden + 4 * cfg.vocab
-    out["q6k_lm_head"] = {"kernel": "mv_q6k_kernel (lm_head 262144x1536)", "us": ms * 1e3, "bytes": nbytes,
+    out["q6k_lm_head"] = {"kernel": "mv_q6k_kernel (lm_head 262144x1536, planner-chosen variant)", "us": ms * 1e3, "bytes": nbytes,
                           "gbs": nbytes / ms / 1e6, "launches_per_token": 1}
     lib.ks_buf_free(ctx.h, e)
     return out
@@ -293,7 +311,7 @@ def main():
     peak, peak_kind = measured_peak()
     ctx = CudaContext(local, flags=1)  # bit 0: programmatic dependent launch
     lib = ctx.lib
-    cfg = ksm.e2b_config(max_seq=PROMPT_LEN + args.steps * 2 + args.warmup * 2 + 16)
+    cfg = ksm.e2b_config(max_seq=PROMPT_LEN + args.steps * 2 + args.warmup * 2 + 16 + 64)
     model = ksm.GemmaCudaModel.synthetic(ctx, cfg, SEED + rank)
     plans_found = model.warm_plans(1)   # load-time plan search / per-chip cache, outside every timed region
     slot = model.slot_alloc()
@@ -361,12 +379,13 @@ def main():
                               "frac_of_peak": wb / (ms / args.steps) / 1e6 / peak, "peak_gbs": peak, "peak_kind": peak_kind},
         }
         if world == 1:
-            alone = time_kernel_alone(ctx, model.h, lib, cfg, peak)
+            alone = time_kernel_alone(ctx, model, slot, lib, cfg, peak, args.steps)
             share = {k: v["us"] * v["launches_per_token"] for k, v in alone.items()}
             dom = max(share, key=share.get)
             d = alone[dom]
             line["roofline"] = {"bound": "hbm", "kernel": d["kernel"], "achieved": d["gbs"], "peak": peak, "unit": "GB/s",
-                                "frac": d["gbs"] / peak, "of": peak_kind, "traffic": None, "us_per_launch": d["us"],
+                                "frac": d["gbs"] / peak, "of": peak_kind,
+                                "traffic": DECODE_KERNEL_DRAM_TRAFFIC if dom == "decode_layers" else None, "us_per_launch": d["us"],
                                 "bytes_per_launch": d["bytes"]}
             line["kernels_alone"] = alone
             line["gemv_config0"] = gemv_config0(ctx, peak)
