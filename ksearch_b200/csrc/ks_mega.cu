@@ -452,9 +452,9 @@ __device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned col
     t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
   }
   const float invn = 1.0f / (float)cols;
-  const float inv = 1.0f / sqrtf(t.x * invn + eps);
+  const float inv = __frsqrt_rn(t.x * invn + eps);
   const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
-  const float inv2 = 1.0f / sqrtf(fmaxf(rr, 0.0f) * invn + eps);
+  const float inv2 = __frsqrt_rn(fmaxf(rr, 0.0f) * invn + eps);
 #pragma unroll
   for (int k = 0; k < PC; k++) {
     const unsigned c = threadIdx.x + k * blockDim.x;
@@ -946,7 +946,7 @@ __host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_byte
   L.bar_off = L.ring_off + 8u * (unsigned)stages * slot_bytes;
   L.red_off = (L.bar_off + 8u * 8u * (unsigned)stages + 15u) & ~15u;
   L.flag_off = L.red_off + 256u + MG_MAX_P * 32u;  // 32 floats for block sums, 8 float4 of per-warp norm sums, partial sums [MG_MAX_P][2][4]
-  L.tab_off = L.flag_off + 16u;
+  L.tab_off = L.flag_off + 48u;  // 4 flag words, then 8 words of per-kind group counts
   L.ent_off = L.tab_off + tables_bytes;
   L.total = L.ent_off + 8u * MG_MAX_ENT * (unsigned)sizeof(ItemEnt);
   return L;
@@ -974,12 +974,15 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
     reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
   if (threadIdx.x == 0) sflag[2] = sflag[3] = 0;  // barrier flag words ([0] belongs to the attention phase)
+  unsigned* ngrp = reinterpret_cast<unsigned*>(smem + SL.flag_off + 16u);  // this block's group count per phase kind
+  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = 0;
   if (lane == 0) {
     for (int s = 0; s < S; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = block_groups(shapes[threadIdx.x]);
   const unsigned H = shapes[PH_QKV].cols;
 
   ItemEnt* ent = reinterpret_cast<ItemEnt*>(smem + SL.ent_off) + warp * MG_MAX_ENT;
@@ -1075,7 +1078,7 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
       const bool sums = kind == PH_OPROJ || kind == PH_DOWN;
       // Thread f finishes row (f & 3) of this block's group (f >> 2): it adds the column segments'
       // partial sums in order, applies the epilogue and stores the row.
-      const unsigned n_g = block_groups(sh), C = sh.n_cseg;
+      const unsigned n_g = ngrp[kind], C = sh.n_cseg;
       unsigned frow = 0;
       int fseg = 0;
       bool fin = false;
