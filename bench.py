@@ -221,7 +221,7 @@ def time_kernel_alone(ctx, model, slot, lib, cfg, peak, steps):
             ctx.check(lib.ks_matvec(ctx.h, cfg.vocab, cfg.hidden, Q6K, e, 0, 0, x.h, 0, lg.h, 0, 1))
         ms = ctx.timer_end_ms() / 4
     nbytes = cfg.vocab * cfg.hidden // 256 * 210 + 4 * cfg.hidden + 4 * cfg.vocab
-    out["q6k_lm_head"] = {"kernel": "mv_q6k_kernel (lm_head 262144x1536, planner-chosen variant)", "us": ms * 1e3, "bytes": nbytes,
+    out["q6k_lm_head"] = {"kernel": "mv_q6k_fx_kernel (lm_head 262144x1536, planner-chosen variant)", "us": ms * 1e3, "bytes": nbytes,
                           "gbs": nbytes / ms / 1e6, "launches_per_token": 1}
     lib.ks_buf_free(ctx.h, e)
     return out

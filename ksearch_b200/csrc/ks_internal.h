@@ -114,6 +114,9 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
                                 ks_dtype act, const void* x, int n_tok, const ks_plan* plan, const ks_mv_pro* pro);
 int ks_launch_matvec_stream_q6k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x,
                                 int n_tok, const ks_plan* plan);   // returns 1 when the shape must use the direct kernel
+// variant 2 (Q6_K only): x as block fixed point, byte dot products; returns 1 when the call must use another variant
+int ks_launch_matvec_q6k_fx(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x, int n_tok,
+                            const ks_plan* plan);
 // Device error word raised by a kernel whose bounded wait gave up (index into ctx->ws, in words).
 #define KS_WS_ERR_WORD 4000
 

@@ -148,6 +148,10 @@ int ks_plan_candidates(const char* op, ks_plan* out, int max_out) {
         }
   for (int nr : {2, 4})  // the direct-load kernels
     for (int cps : {2, 4}) c.push_back(ks_plan{1, nr, 8, cps, 0.f});
+  if (q6)  // block fixed-point x, byte dot products
+    for (int nr : {1, 2})
+      for (int nw : {4, 8})
+        for (int cps : {4, 6, 8}) c.push_back(ks_plan{2, nr, nw, cps, 0.f});
   const int n = std::min<int>((int)c.size(), max_out);
   for (int i = 0; i < n; i++) out[i] = c[i];
   return n;

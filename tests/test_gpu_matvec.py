@@ -59,6 +59,27 @@ def test_matvec_q6k_signed_scales(ctx, oracle):
     _check(ctx.read_f32(y, 200), y32, y64, "q6k signed scales")
 
 
+@pytest.mark.parametrize("rows,cols,nr", [(512, 1536, 1), (203, 1536, 2), (100, 2560, 2), (9, 768, 1), (31, 4096, 2), (1, 256, 1)])
+def test_matvec_q6k_fixed_point_variant(ctx, oracle, rows, cols, nr):
+    """Plan variant 2: x as 24-bit block fixed point, 6-bit weights x x as byte dot products (the lm_head kernel).
+    Odd row counts and odd block counts per row put blocks on both 2-byte alignments."""
+    from ksearch_b200 import _lib
+    W = synth.q6k_matrix(63, f"W{rows}x{cols}", rows, cols, signed_scales=True)
+    x = synth.normals(63, "x", cols)
+    y = ctx.buffer_empty_f32(rows + 8)
+    ctx.plan_override(_lib.Plan(2, nr, 8, 4, 0.0))
+    try:
+        launches = ctx.launch_count()
+        Eng().matvec_wd_at(ctx, rows, cols, Q6K, ctx.buffer_bytes(W), ctx.buffer_bytes(x), 0, y, 4)
+        assert ctx.launch_count() == launches + 1
+    finally:
+        ctx.plan_override(None)
+    got = ctx.read_f32(y, rows + 8)
+    assert not got[:4].any() and not got[rows + 4:].any()
+    y32, y64 = oracle.matvec(Q6K, W, rows, cols, x)
+    _check(got[4:rows + 4], y32, y64, f"q6k fixed-point {rows}x{cols}")
+
+
 def test_matvec_reference_patterns(ctx, oracle):
     """check_mul_mm.rs:47-109 inputs: integer-pattern W quantised by the reference quantizer,
     pattern x; GEMV vs CPU dequant + f32 dot.  The reference prints max|err| against a 0.05
