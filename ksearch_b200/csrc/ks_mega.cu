@@ -36,7 +36,7 @@ struct MegaShape {          // one of the five phases of a layer; the same for e
   unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups (0 for attention)
   unsigned cols, row_bytes, seg_blocks, n_cseg;
   int oct;                  // 1: a block owns runs of 8 consecutive groups (32 rows = one sub-block of the next phase's x)
-  int pad_;
+  int split;                // gate-up only, 1: the gate rows and the up rows of a group are two items (rows too long for one slot)
 };
 
 struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
@@ -489,7 +489,8 @@ struct ItemEnt {
   uint16_t seg16;    // bytes of one row segment / 16
   uint8_t kind, seg, cs, valid;
   uint8_t widx;      // MegaLayer::W index of the first matrix
-  uint8_t flags;     // bit 0: two matrices (gate, up); bit 1: whole rows (one copy per matrix)
+  uint8_t flags;     // bit 0: two matrices (gate, up) in one item; bit 1: whole rows (one copy per matrix);
+                     // bit 2: this item is the second matrix (up) of a split gate-up group
 };
 struct ItemPos {
   int layer, e;
@@ -521,13 +522,16 @@ __device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes
   int n = 0;
   for (int kind = 0; kind < PH_PER_LAYER; kind++) {
     const MegaShape& sh = shapes[kind];
-    const unsigned C = sh.n_cseg, n_items = block_groups(sh) * C;
-    if (n_items > (unsigned)MG_MAX_P) return -1;
+    const unsigned C = sh.n_cseg, n_slots = block_groups(sh) * C;
+    if (n_slots > (unsigned)MG_MAX_P) return -1;
     const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
-    const int mats = sh.type == MG_GATE_UP ? 2 : 1;
+    const bool split = sh.type == MG_GATE_UP && sh.split;
+    const int mats = (sh.type == MG_GATE_UP && !split) ? 2 : 1;
     const int w0 = kind == PH_QKV ? 0 : kind == PH_OPROJ ? 3 : kind == PH_GATEUP ? 4 : 6;
-    for (unsigned j = (unsigned)warp; j < n_items; j += 8u) {
+    const unsigned n_items = split ? n_slots * 2u : n_slots;
+    for (unsigned jj = (unsigned)warp; jj < n_items; jj += 8u) {
       if (n >= MG_MAX_ENT) return -1;
+      const unsigned j = split ? jj >> 1 : jj, second = split ? jj & 1u : 0u;
       const unsigned k = j / C, cs = j - k * C;
       const unsigned g = block_group_id(sh, k);
       if (g >= sh.grp_start[sh.n_seg]) continue;
@@ -543,8 +547,8 @@ __device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes
       e.seg = (uint8_t)seg;
       e.cs = (uint8_t)cs;
       e.valid = (uint8_t)min((unsigned)MG_RL, sh.rows[seg] - row0);
-      e.widx = (uint8_t)(w0 + (mats == 2 ? 0 : seg));
-      e.flags = (uint8_t)((mats == 2 ? 1 : 0) | (C == 1 ? 2 : 0));
+      e.widx = (uint8_t)(w0 + (mats == 2 ? 0 : split ? second : seg));
+      e.flags = (uint8_t)((mats == 2 ? 1 : 0) | (C == 1 ? 2 : 0) | (second ? 4 : 0));
       ent[n++] = e;
     }
   }
@@ -1105,7 +1109,7 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         }
         const uint32_t slot = ring_s + st * a.slot_bytes;
         float yacc[2] = {0.0f, 0.0f};
-        if (sh.type == MG_GATE_UP)
+        if (e.flags & 1)
           mg_item_compute_fx<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
         else
           mg_item_compute_fx<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
@@ -1117,8 +1121,12 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
           v1 += __shfl_xor_sync(0xffffffffu, v1, o);
         }
         if (cl == 0) {
-          psum[e.pslot * 8u + (unsigned)rl] = v0;
-          psum[e.pslot * 8u + 4u + (unsigned)rl] = v1;
+          if (e.flags & 4) {
+            psum[e.pslot * 8u + 4u + (unsigned)rl] = v0;  // the up rows of a split gate-up group
+          } else {
+            psum[e.pslot * 8u + (unsigned)rl] = v0;
+            if (e.flags & 1) psum[e.pslot * 8u + 4u + (unsigned)rl] = v1;
+          }
         }
         pos_next(cc, n_ent);
         // Refill now only when the next item of THIS phase is not in flight yet; everything else is
@@ -1314,19 +1322,37 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   };
   const unsigned g_qkv = (qn + 3) / 4 + 2 * ((kvn + 3) / 4), g_h = (H + 3) / 4, g_f = (F + 3) / 4;
   if (g_qkv > 64u * grid || g_f > 64u * grid || g_h > 64u * grid) return KS_OK;  // a block finishes at most 64 groups per phase
-  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_h2 = pick_seg(H, 2, g_f, true), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
+  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
+  // gate-up: gate and up rows of a group in one item (x read once for both) when they fit a slot, else as two items
+  unsigned sb_h2 = pick_seg(H, 2, g_f, true);
+  bool gu_split = false;
+  if (!sb_h2) {
+    gu_split = true;
+    const unsigned n_g = ((g_f + 7) / 8 + grid - 1) / grid * 8, nb = H / 256u;
+    float best_cost = 0.f;
+    for (unsigned C = 1; C <= nb; C++) {
+      if (nb % C) continue;
+      const unsigned sb = nb / C;
+      if (sb % 2 || 4u * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
+      const float cost = (float)((n_g * C * 2u + 7u) / 8u) * ((float)sb * 0.5f + 1.2f);
+      if (!sb_h2 || cost < best_cost) {
+        sb_h2 = sb;
+        best_cost = cost;
+      }
+    }
+  }
   if (!sb_h || !sb_h2 || !sb_q || !sb_f) return KS_OK;
   unsigned slot_bytes = 0;
   auto upd = [&](unsigned sb, unsigned mats) {
     const unsigned b = 4u * mats * sb * KS_Q4K_BLOCK_BYTES;
     if (b > slot_bytes) slot_bytes = b;
   };
-  upd(sb_h, 1); upd(sb_h2, 2); upd(sb_q, 1); upd(sb_f, 1);
+  upd(sb_h, 1); upd(sb_h2, gu_split ? 1 : 2); upd(sb_q, 1); upd(sb_f, 1);
 
   {  // every warp's items of one layer must fit its table
     auto per_warp = [&](unsigned total_groups, unsigned ncs) { return ((total_groups + grid - 1) / grid * ncs + 7u) / 8u; };
     const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) +
-                           (((g_f + 7) / 8 + grid - 1) / grid * 8 * (H / 256 / sb_h2) + 7u) / 8u +
+                           (((g_f + 7) / 8 + grid - 1) / grid * 8 * (H / 256 / sb_h2) * (gu_split ? 2u : 1u) + 7u) / 8u +
                            per_warp(g_h, F / 256 / sb_f);
     if (worst > (unsigned)MG_MAX_ENT) return KS_OK;
   }
@@ -1351,7 +1377,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   sh[PH_ATTN].type = MG_ATTN; sh[PH_ATTN].n_seg = 1; sh[PH_ATTN].n_cseg = 1;
   sh[PH_OPROJ].type = MG_MATVEC; sh[PH_OPROJ].n_seg = 1; sh[PH_OPROJ].rows[0] = H;
   set_rows(sh[PH_OPROJ], qn, sb_q);
-  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F; sh[PH_GATEUP].oct = 1;
+  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F; sh[PH_GATEUP].oct = 1; sh[PH_GATEUP].split = gu_split ? 1 : 0;
   set_rows(sh[PH_GATEUP], H, sb_h2);
   sh[PH_DOWN].type = MG_MATVEC; sh[PH_DOWN].n_seg = 1; sh[PH_DOWN].rows[0] = H;
   set_rows(sh[PH_DOWN], F, sb_f);

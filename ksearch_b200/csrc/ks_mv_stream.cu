@@ -551,13 +551,16 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
   if (pro) a.pro = *pro;
   if (a.pro.mode != KS_PRO_NONE) {
-    KS_REQUIRE(ctx, cols <= 16u * (unsigned)nwarps * 32u, "matvec: fused norm needs cols <= %u", 16u * (unsigned)nwarps * 32u);
+    if (nwarps < (int)((cols + 511) / 512)) nwarps = (int)((cols + 511) / 512);  // 16 elements per thread
+    KS_REQUIRE(ctx, nwarps <= 8, "matvec: fused norm needs cols <= 4096");
     const uintptr_t al = act == KS_F32 ? 15 : 7;
     KS_REQUIRE(ctx, (((uintptr_t)x | (uintptr_t)a.pro.w) & al) == 0, "matvec: fused norm needs aligned vectors");
     if (a.pro.mode == KS_PRO_ADD_NORM)
       KS_REQUIRE(ctx, a.pro.out_x != x && (((uintptr_t)a.pro.y | (uintptr_t)a.pro.w_post | (uintptr_t)a.pro.out_x) & al) == 0,
                  "matvec: fused residual update must not alias its input and needs aligned vectors");
   }
+  // a fused norm holds the input vector in registers, 16 elements per thread: never run it with fewer warps
+  const int min_warps = a.pro.mode != KS_PRO_NONE ? (int)((cols + 511) / 512) : 1;
   const unsigned grows = (unsigned)(RL * R);
   unsigned g0 = 0;
   for (int s = 0; s < n_seg; s++) {
@@ -585,7 +588,7 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
       const unsigned items = ((g0 + gw_total - 1) / gw_total) * a.n_cseg;
       stages = (int)(items < 2 ? 2 : items > 8 ? 8 : items);
       while (stages > 2 && make_layout(x_bytes, stage_bytes, nwarps, stages).total > half) stages--;
-      if (make_layout(x_bytes, stage_bytes, nwarps, stages).total <= half || !pick_warps || nwarps <= 4) break;
+      if (make_layout(x_bytes, stage_bytes, nwarps, stages).total <= half || !pick_warps || nwarps <= 4 || nwarps <= min_warps) break;
       nwarps -= 1;
     }
   }
@@ -593,7 +596,7 @@ int ks_launch_matvec_stream_q4k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, k
   Layout L = make_layout(x_bytes, stage_bytes, nwarps, stages);
   const unsigned budget = (unsigned)ctx->smem_optin;
   while (L.total > budget && stages > 2) L = make_layout(x_bytes, stage_bytes, nwarps, --stages);
-  while (L.total > budget && nwarps > 1) L = make_layout(x_bytes, stage_bytes, --nwarps, stages);
+  while (L.total > budget && nwarps > min_warps) L = make_layout(x_bytes, stage_bytes, --nwarps, stages);
   KS_REQUIRE(ctx, L.total <= budget, "matvec: needs %u B of shared memory (limit %u)", L.total, budget);
   a.stages = stages;
   unsigned grid = (g0 + nwarps - 1) / nwarps;

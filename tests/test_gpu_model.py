@@ -173,6 +173,45 @@ def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv)
     c.close()
 
 
+def test_persistent_kernel_long_context(oracle, monkeypatch):
+    """300 positions: every attention split in use, several positions per warp, the newest position
+    moving through the splits."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    c = CudaContext(0, flags=1)
+    cfg = ksm.tiny_config(max_seq=320, n_kv=2)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=23, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    model.slot_alloc()
+    _teacher_forced(model, cpu, synth.token_ids(23, "tf", 300, cfg.vocab))
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
+    cpu.close()
+    model.close()
+    c.close()
+
+
+def test_persistent_kernel_e4b_like_shapes(oracle, monkeypatch):
+    """Two layers with the E4B row and column counts (hidden 2560, GeGLU 10240, 8 q / 2 kv heads of
+    256): ten blocks per row (column segments of 2 and 10 blocks), four 4-element chunks per thread in
+    the fused norms, two KV heads."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    c = CudaContext(0, flags=1)
+    cfg = ksm.ModelConfig(2, 2560, 10240, 8, 2, 256, 4096, 64, 1, sigma_w=0.01, sigma_embd=5e-5)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=24, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    model.slot_alloc()
+    _teacher_forced(model, cpu, synth.token_ids(24, "tf", 40, cfg.vocab))
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
+    prompt = synth.token_ids(24, "prompt", 6, cfg.vocab)
+    out, _ = model.generate_timed(prompt, 12)
+    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    assert equal + ties == 12 and ties <= 1
+    cpu.close()
+    model.close()
+    c.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
