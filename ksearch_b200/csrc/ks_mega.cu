@@ -1214,7 +1214,8 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
 struct ks_mega {
   MegaArgs args{};
   void* d_tables = nullptr;
-  unsigned* d_sync = nullptr;  // words 0..1 barrier, 8..63 per-head attention arrival counters, from byte 256: per-block norm sums
+  unsigned* d_sync = nullptr;  // words 0..1 barrier (a 128-byte line of its own: every block polls it), 64..111 per-head
+                               // attention arrival counters, from byte 512: per-block norm sums
   long long* d_prof = nullptr;
   unsigned char* d_fx = nullptr;  // attention output and GeGLU output in the staged layout
   unsigned grid = 0;
@@ -1394,14 +1395,14 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   ks_mega* mg = new ks_mega();
   cudaSetDevice(ctx->device);
   const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
-  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
+  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 512 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
       cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess ||
       cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
   cudaError_t e = cudaMemcpyAsync(mg->d_tables, tab.data(), tables_bytes, cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 256 + 16 * (size_t)ctx->sm_count, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 512 + 16 * (size_t)ctx->sm_count, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_fx, 0, ((size_t)qn / 64 + (size_t)F / 64) * 256, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
@@ -1425,8 +1426,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.ffx = mg->d_fx + (size_t)qn / 64 * 256;
   a.att_tmp = d->att_tmp;
   a.bar = mg->d_sync;
-  a.att_cnt = mg->d_sync + 8;
-  a.nsum = reinterpret_cast<float4*>(mg->d_sync + 64);
+  a.att_cnt = mg->d_sync + 64;
+  a.nsum = reinterpret_cast<float4*>(mg->d_sync + 128);
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
   a.prof = mg->d_prof;
   mg->grid = grid;

@@ -190,19 +190,20 @@ def test_persistent_kernel_long_context(oracle, monkeypatch):
     c.close()
 
 
-def test_persistent_kernel_e4b_like_shapes(oracle, monkeypatch):
+@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     """Two layers with the E4B row and column counts (hidden 2560, GeGLU 10240, 8 q / 2 kv heads of
-    256): ten blocks per row (column segments of 2 and 10 blocks), four 4-element chunks per thread in
-    the fused norms, two KV heads."""
+    256): ten blocks per row, gate and up rows too long for one ring slot, four 4-element chunks per
+    thread in the fused norms, two KV heads.  Both the persistent kernel and the launch-per-op path."""
     from ksearch_b200 import CudaContext
-    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
     c = CudaContext(0, flags=1)
     cfg = ksm.ModelConfig(2, 2560, 10240, 8, 2, 256, 4096, 64, 1, sigma_w=0.01, sigma_embd=5e-5)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=24, keep=True)
     cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
     model.slot_alloc()
     _teacher_forced(model, cpu, synth.token_ids(24, "tf", 40, cfg.vocab))
-    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
     prompt = synth.token_ids(24, "prompt", 6, cfg.vocab)
     out, _ = model.generate_timed(prompt, 12)
     equal, ties = ksm.compare_streams(out, cpu, prompt)
