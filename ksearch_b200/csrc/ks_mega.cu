@@ -1257,6 +1257,14 @@ int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
 }
 
 float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
+
+// Zero the barrier words and arrival counters (stream-ordered).  They only leave their rest state when
+// a bounded wait gave up; a slot reset puts the kernel back in working order.
+int ks_mega_reset(ks_ctx* ctx, ks_mega* mg) {
+  cudaError_t e = cudaMemsetAsync(mg->d_sync, 0, 512, ctx->stream);
+  if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: reset failed: %s", cudaGetErrorString(e));
+  return KS_OK;
+}
 const long long* ks_mega_prof(const ks_mega* mg) { return mg->d_prof; }
 
 void ks_mega_destroy(ks_mega* mg) {

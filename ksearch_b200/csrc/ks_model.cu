@@ -589,6 +589,11 @@ int ks_model_slot_reset(ks_model* m, int slot) {
   KS_LAUNCH(c, (set_state_kernel), 1, 1, 0, slot, 0, m->pos);
   m->seq_len[slot] = 0;
   m->occupied[slot] = 1;
+  auto it = m->mega.find(slot);
+  if (it != m->mega.end() && it->second) {
+    const int rc = ks_mega_reset(c, it->second);
+    if (rc) return rc;
+  }
   return ks_after_launch(c, "slot_reset");
 }
 
