@@ -161,7 +161,10 @@ def workload_config(cfg, n_gpus):
                         "one slot per GPU",
             "weight_bytes_per_token": 1027031040, "prompt_len": PROMPT_LEN, "slots_per_gpu": 1,
             "parallelism": f"replicas x{n_gpus}, no collective on the data path",
-            "l2": "weights (1.03 GB/token) are 8x the 126 MB L2, so every step streams them from HBM"}
+            "l2": "weights (1.03 GB/token) are 8x the 126 MB L2, so every step streams them from HBM",
+            "arithmetic": "f32 activations and accumulation; inside the persistent decode kernel and the lm_head the input vector "
+                          "is 24-bit block fixed point (three int8 planes per 32 elements) and weight x input products are exact "
+                          "dp4a integer sums, scaled back in f32"}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the persistent decode kernel on this
