@@ -256,6 +256,11 @@ int ks_model_slot_reset(ks_model* m, int slot);                              /* 
 int ks_model_slot_seq_len(const ks_model* m, int slot);                      /* KV:161 seq_len */
 int ks_model_slot_active(const ks_model* m);                                 /* KV:179 active_batch().len() */
 int ks_model_forward(ks_model* m, int first_slot, int n_slots, const int* tokens, int want_logits);   /* GP:881 forward_token, enqueue only */
+/* Prompt tokens of one slot without logits, eight per pass over the weights (the rows of a chunk attend
+ * causally inside the chunk).  Stands in for GemmaPrimModel::prefill_chunk
+ * (crates/ksearch_gemma/src/gemma_prim.rs:1305-1315) with the batch GEMV (crates/ksearch_kernels/src/lib.rs:1414)
+ * in place of the mul_mm GEMM.  The slot advances by n_tokens; enqueues only. */
+int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens);
 int ks_model_decode_token(ks_model* m, int first_slot, int n_slots, const int* tokens, int* next);    /* GP:1616 decode_token, blocking */
 int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight,
                       int* out, ks_generate_stats* stats);                   /* GP:1658 generate_timed */

@@ -90,6 +90,7 @@ SIGNATURES = {
     "ks_model_slot_seq_len": (_i, [_vp, _i]),
     "ks_model_slot_active": (_i, [_vp]),
     "ks_model_forward": (_i, [_vp, _i, _i, _vp, _i]),
+    "ks_model_prefill": (_i, [_vp, _i, _vp, _i]),
     "ks_model_decode_token": (_i, [_vp, _i, _i, _vp, _vp]),
     "ks_model_generate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp]),
     "ks_model_debug_ptr": (_vp, [_vp, _i, _i]),

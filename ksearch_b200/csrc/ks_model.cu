@@ -41,6 +41,22 @@ __global__ void end_token_kernel(int n, int* pos) {
   if (s < n) pos[s] += 1;
 }
 __global__ void set_state_kernel(int slot, int pos_value, int* pos) { ks_pdl_entry(); pos[slot] = pos_value; }
+// A prompt chunk: row t of the chunk sits at position base + t of ONE slot (causal: it sees base + t + 1 positions).
+__global__ void begin_chunk_kernel(int n, const int* base, int* cpos, float* meta) {
+  ks_pdl_entry();
+  const int t = threadIdx.x;
+  if (t < n) {
+    cpos[t] = base[0] + t;
+    meta[t * 4 + 0] = (float)(base[0] + t + 1);
+    meta[t * 4 + 1] = 0.0f;
+    meta[t * 4 + 2] = 0.0f;
+    meta[t * 4 + 3] = 0.0f;
+  }
+}
+__global__ void end_chunk_kernel(int n, int* base) {
+  ks_pdl_entry();
+  if (threadIdx.x == 0) base[0] += n;
+}
 
 struct Tensor {
   void* dptr = nullptr;
@@ -89,6 +105,13 @@ struct ks_model {
   // one persistent decode kernel per slot (nullptr entry: shape not covered, tried once)
   std::map<int, ks_mega*> mega;
   bool use_mega = false;
+  // prompt chunks (ks_model_prefill): KS_PREFILL_CHUNK rows of activations of their own
+  void *cx = nullptr, *cxb = nullptr, *cx2 = nullptr, *cq = nullptr, *ck = nullptr, *cv = nullptr, *co = nullptr, *cff = nullptr;
+  float* ctok = nullptr;
+  int* cpos = nullptr;
+  float* cmeta = nullptr;
+  float* cattn_tmp = nullptr;
+  int chunk = 1;  // tokens per prompt chunk: as many as the matvec kernels can stage side by side (<= KS_PREFILL_CHUNK)
 };
 
 namespace {
@@ -103,31 +126,94 @@ int dev_alloc(ks_model* m, void** p, size_t bytes) {
   return KS_OK;
 }
 
-// One token (or one token per slot for slots first..first+n-1) through every layer.
-// src: which half of the token ping-pong holds the input ids.
-int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
+constexpr int KS_PREFILL_CHUNK = 8;  // tokens per pass over the weights (the matvec kernels take up to 8)
+
+// Where a forward pass reads and writes: n rows of activations, their positions, and the KV caches
+// behind them.  Decode steps map row s to slot first + s (one cache per row); a prompt chunk maps
+// row t to position base + t of ONE slot (every row shares that slot's cache, kv_stride = 0).
+struct Lane {
+  char *x, *xb, *x2, *xn, *q, *k, *v, *o, *ff, *logits;
+  const float* tok_in;
+  float* tok_out;
+  int* pos;          // device, one per row
+  float* meta;       // device, (tlen, start, -, -) per row
+  float* attn_tmp;
+  size_t kv_off;     // byte offset of row 0's cache inside every layer's K / V allocation
+  size_t kv_stride;  // bytes between the caches of consecutive rows
+  int* chunk_base;   // prompt chunk: the slot's position word (rows take base, base + 1, ...); else nullptr
+};
+
+Lane slot_lane(ks_model* m, int first, int src) {
+  const ks_model_config& g = m->cfg;
+  const size_t ab = act_b(m), H = g.hidden, F = g.ffn, qn = (size_t)g.n_q * g.hd, kvn = (size_t)g.n_kv * g.hd;
+  Lane L{};
+  L.x = (char*)m->x + (size_t)first * H * ab;
+  L.xb = (char*)m->xb + (size_t)first * H * ab;
+  L.x2 = (char*)m->x2 + (size_t)first * H * ab;
+  L.xn = (char*)m->xn + (size_t)first * H * ab;
+  L.q = (char*)m->q + (size_t)first * qn * ab;
+  L.k = (char*)m->k + (size_t)first * kvn * ab;
+  L.v = (char*)m->v + (size_t)first * kvn * ab;
+  L.o = (char*)m->o + (size_t)first * qn * ab;
+  L.ff = (char*)m->ff + (size_t)first * F * ab;
+  L.logits = (char*)m->logits + (size_t)first * g.vocab * ab;
+  L.tok_in = m->tok + (size_t)src * g.n_slots + first;
+  L.tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  L.pos = m->pos + first;
+  L.meta = m->meta + (size_t)first * 4;
+  L.attn_tmp = m->attn_tmp;
+  L.kv_off = (size_t)first * m->slot_stride;
+  L.kv_stride = m->slot_stride;
+  return L;
+}
+
+Lane chunk_lane(ks_model* m, int slot) {
+  Lane L{};
+  L.x = (char*)m->cx; L.xb = (char*)m->cxb; L.x2 = (char*)m->cx2; L.xn = nullptr;
+  L.q = (char*)m->cq; L.k = (char*)m->ck; L.v = (char*)m->cv; L.o = (char*)m->co; L.ff = (char*)m->cff;
+  L.logits = nullptr;
+  L.tok_in = m->ctok;
+  L.tok_out = nullptr;
+  L.pos = m->cpos;
+  L.meta = m->cmeta;
+  L.attn_tmp = m->cattn_tmp;
+  L.kv_off = (size_t)slot * m->slot_stride;
+  L.kv_stride = 0;
+  L.chunk_base = m->pos + slot;
+  return L;
+}
+
+int lane_begin(ks_model* m, const Lane& L, int n) {
+  if (L.chunk_base)
+    KS_LAUNCH(m->ctx, (begin_chunk_kernel), 1, 32, 0, n, (const int*)L.chunk_base, L.pos, L.meta);
+  else
+    KS_LAUNCH(m->ctx, (begin_token_kernel), 1, 32, 0, n, (const int*)L.pos, L.meta);
+  return ks_after_launch(m->ctx, "begin_token");
+}
+int lane_end(ks_model* m, const Lane& L, int n) {
+  if (L.chunk_base)
+    KS_LAUNCH(m->ctx, (end_chunk_kernel), 1, 32, 0, n, L.chunk_base);
+  else
+    KS_LAUNCH(m->ctx, (end_token_kernel), 1, 32, 0, n, L.pos);
+  return ks_after_launch(m->ctx, "end_token");
+}
+
+// One token per row through every layer.
+int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   ks_ctx* c = m->ctx;
   const ks_model_config& g = m->cfg;
   const ks_dtype act = (ks_dtype)g.act;
   const size_t ab = act_b(m);
   const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
   const size_t qn = nq * hd, kvn = nkv * hd;
-  char* x = (char*)m->x + (size_t)first * H * ab;
-  char* x2 = (char*)m->x2 + (size_t)first * H * ab;
-  char* q = (char*)m->q + (size_t)first * qn * ab;
-  char* k = (char*)m->k + (size_t)first * kvn * ab;
-  char* v = (char*)m->v + (size_t)first * kvn * ab;
-  char* o = (char*)m->o + (size_t)first * qn * ab;
-  char* ff = (char*)m->ff + (size_t)first * F * ab;
-  char* logits = (char*)m->logits + (size_t)first * g.vocab * ab;
-  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
-  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
-  int* pos = m->pos + first;
-  float* meta = m->meta + (size_t)first * 4;
+  char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff, *logits = L_.logits;
+  const float* tok_in = L_.tok_in;
+  float* tok_out = L_.tok_out;
+  int* pos = L_.pos;
+  float* meta = L_.meta;
   int rc;
 
-  KS_LAUNCH(c, (begin_token_kernel), 1, 32, 0, n, pos, meta);
-  if ((rc = ks_after_launch(c, "begin_token"))) return rc;
+  if ((rc = lane_begin(m, L_, n))) return rc;
   // embed: x = sqrt(hidden) * deq(token_embd[id])   (gemma_prim.rs:681-683)
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, act, x))) return rc;
   if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
@@ -138,12 +224,12 @@ int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
                         {(const uint8_t*)L.wk.dptr, k, (unsigned)kvn},
                         {(const uint8_t*)L.wv.dptr, v, (unsigned)kvn}};
     if ((rc = ks_launch_matvec(c, KS_Q4K, qkv, 3, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
-    uint8_t* kk = m->kv_k[l] + (size_t)first * m->slot_stride;
-    uint8_t* kv = m->kv_v[l] + (size_t)first * m->slot_stride;
+    uint8_t* kk = m->kv_k[l] + L_.kv_off;
+    uint8_t* kv = m->kv_v[l] + L_.kv_off;
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
-                                         kk, kv, pos, m->slot_stride)))
+                                         kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, m->slot_stride, meta, m->attn_tmp, o, m->n_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, m->n_splits)))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, x2, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
@@ -156,8 +242,7 @@ int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
     const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
     if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_ffw_norm.dptr, x, next_norm, x, x2))) return rc;
   }
-  KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, n, pos);
-  if ((rc = ks_after_launch(c, "end_token"))) return rc;
+  if ((rc = lane_end(m, L_, n))) return rc;
   if (!want_logits) return KS_OK;
   // head: logits = token_embd . rms(x, output_norm); next id = softcap argmax (gemma_prim.rs:1222-1242)
   ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
@@ -171,31 +256,22 @@ int enqueue_forward(ks_model* m, int first, int n, int src, bool want_logits) {
 // (qkv, per-head norm/rope/KV, attention, o-proj, gate/up, down -> six with the attention pair).
 // The residual stream alternates between two buffers because the block that writes the updated
 // stream must not overwrite what the other blocks of the same launch still read.
-int enqueue_forward_fused(ks_model* m, int first, int n, int src, bool want_logits) {
+int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) {
   ks_ctx* c = m->ctx;
   const ks_model_config& g = m->cfg;
   const ks_dtype act = (ks_dtype)g.act;
   const size_t ab = act_b(m);
   const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
   const size_t qn = nq * hd, kvn = nkv * hd;
-  char* cur = (char*)m->x + (size_t)first * H * ab;
-  char* oth = (char*)m->xb + (size_t)first * H * ab;
-  char* yb = (char*)m->x2 + (size_t)first * H * ab;
-  char* xn = (char*)m->xn + (size_t)first * H * ab;
-  char* q = (char*)m->q + (size_t)first * qn * ab;
-  char* k = (char*)m->k + (size_t)first * kvn * ab;
-  char* v = (char*)m->v + (size_t)first * kvn * ab;
-  char* o = (char*)m->o + (size_t)first * qn * ab;
-  char* ff = (char*)m->ff + (size_t)first * F * ab;
-  char* logits = (char*)m->logits + (size_t)first * g.vocab * ab;
-  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
-  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
-  int* pos = m->pos + first;
-  float* meta = m->meta + (size_t)first * 4;
+  char *cur = L_.x, *oth = L_.xb, *yb = L_.x2, *xn = L_.xn, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff,
+       *logits = L_.logits;
+  const float* tok_in = L_.tok_in;
+  float* tok_out = L_.tok_out;
+  int* pos = L_.pos;
+  float* meta = L_.meta;
   int rc;
 
-  KS_LAUNCH(c, (begin_token_kernel), 1, 32, 0, n, pos, meta);
-  if ((rc = ks_after_launch(c, "begin_token"))) return rc;
+  if ((rc = lane_begin(m, L_, n))) return rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, act, cur))) return rc;
   for (int l = 0; l < g.n_layers; l++) {
     const Layer& L = m->layers[l];
@@ -215,12 +291,12 @@ int enqueue_forward_fused(ks_model* m, int first, int n, int src, bool want_logi
                         {(const uint8_t*)L.wv.dptr, v, (unsigned)kvn}};
     if ((rc = ks_launch_matvec(c, KS_Q4K, qkv, 3, KS_EPI_PLAIN, H, act, cur, n, nullptr, &pro))) return rc;
     if (l > 0) std::swap(cur, oth);
-    uint8_t* kk = m->kv_k[l] + (size_t)first * m->slot_stride;
-    uint8_t* kv = m->kv_v[l] + (size_t)first * m->slot_stride;
+    uint8_t* kk = m->kv_k[l] + L_.kv_off;
+    uint8_t* kv = m->kv_v[l] + L_.kv_off;
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
-                                         kk, kv, pos, m->slot_stride)))
+                                         kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, m->slot_stride, meta, m->attn_tmp, o, m->n_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, m->n_splits)))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, yb, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
@@ -237,8 +313,7 @@ int enqueue_forward_fused(ks_model* m, int first, int n, int src, bool want_logi
     ks_mv_seg sd{(const uint8_t*)L.wdown.dptr, yb, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &sd, 1, KS_EPI_PLAIN, F, act, ff, n, nullptr))) return rc;
   }
-  KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, n, pos);
-  if ((rc = ks_after_launch(c, "end_token"))) return rc;
+  if ((rc = lane_end(m, L_, n))) return rc;
   if (!want_logits) return KS_OK;
   // last residual update and the output norm, then the head (gemma_prim.rs:1222-1242)
   if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, yb, m->layers[g.n_layers - 1].post_ffw_norm.dptr, cur,
@@ -338,11 +413,45 @@ int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
     cudaGraph_t graph = nullptr;
     KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     const uint64_t before = c->launches;
+    const Lane lane = slot_lane(m, first, src);
     int rc = mg ? enqueue_forward_mega(m, mg, first, src, want_logits)
-             : m->fused ? enqueue_forward_fused(m, first, n, src, want_logits)
-                        : enqueue_forward(m, first, n, src, want_logits);
+             : m->fused ? enqueue_forward_fused(m, lane, n, want_logits)
+                        : enqueue_forward(m, lane, n, want_logits);
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
     c->launches = before;  // captured launches are counted when the graph replays
+    if (rc) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc;
+    }
+    if (e != cudaSuccess) return ks_fail(c, KS_ERR_CUDA, "model: graph capture failed: %s", cudaGetErrorString(e));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return ks_fail(c, KS_ERR_CUDA, "model: graph instantiate failed: %s", cudaGetErrorString(e));
+    m->graphs[key] = exec;
+    m->graph_nodes[key] = nodes;
+    it = m->graphs.find(key);
+  }
+  KS_CUDA(c, cudaGraphLaunch(it->second, c->stream));
+  c->launches += m->graph_nodes[key];
+  return KS_OK;
+}
+
+// A chunk of n prompt tokens of one slot (ids already in m->ctok) through every layer, no head.
+int run_prefill_chunk(ks_model* m, int slot, int n) {
+  ks_ctx* c = m->ctx;
+  const uint64_t key = (1ull << 63) | ((uint64_t)slot << 32) | ((uint64_t)n << 8);
+  auto it = m->graphs.find(key);
+  if (it == m->graphs.end()) {
+    cudaGraph_t graph = nullptr;
+    KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    const uint64_t before = c->launches;
+    const Lane lane = chunk_lane(m, slot);
+    int rc = m->fused ? enqueue_forward_fused(m, lane, n, false) : enqueue_forward(m, lane, n, false);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    c->launches = before;
     if (rc) {
       if (graph) cudaGraphDestroy(graph);
       return rc;
@@ -448,8 +557,26 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
        dev_alloc(m, (void**)&m->tok, 2 * S * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->pos, S * sizeof(int)) == KS_OK &&
        dev_alloc(m, (void**)&m->meta, S * 4 * sizeof(float)) == KS_OK &&
        dev_alloc(m, (void**)&m->rope, (size_t)g.max_seq * g.hd * sizeof(float)) == KS_OK;
+  {
+    // every token of a chunk keeps its staged input vector in shared memory (280 bytes per 64 columns);
+    // leave 64 KB for the weight stages
+    size_t maxcols = H > F ? H : F;
+    if (qn > maxcols) maxcols = qn;
+    m->chunk = KS_PREFILL_CHUNK;
+    while (m->chunk > 1 && (size_t)m->chunk * (maxcols / 64) * 280 + (64u << 10) > ctx->smem_optin) m->chunk--;
+    const size_t C = KS_PREFILL_CHUNK;
+    ok = ok && dev_alloc(m, &m->cx, C * H * ab) == KS_OK && dev_alloc(m, &m->cxb, C * H * ab) == KS_OK &&
+         dev_alloc(m, &m->cx2, C * H * ab) == KS_OK && dev_alloc(m, &m->cq, C * qn * ab) == KS_OK &&
+         dev_alloc(m, &m->ck, C * kvn * ab) == KS_OK && dev_alloc(m, &m->cv, C * kvn * ab) == KS_OK &&
+         dev_alloc(m, &m->co, C * qn * ab) == KS_OK && dev_alloc(m, &m->cff, C * F * ab) == KS_OK &&
+         dev_alloc(m, (void**)&m->ctok, C * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->cpos, C * sizeof(int)) == KS_OK &&
+         dev_alloc(m, (void**)&m->cmeta, C * 4 * sizeof(float)) == KS_OK;
+  }
   if (ok) {
     m->n_splits = ks_sdpa_pick_splits(ctx, 1, g.n_kv, g.max_seq);
+    ok = dev_alloc(m, (void**)&m->cattn_tmp, ((size_t)KS_PREFILL_CHUNK * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
+  }
+  if (ok) {
     ok = dev_alloc(m, (void**)&m->attn_tmp, (S * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
   }
   if (ok) {
@@ -638,6 +765,34 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
   return KS_OK;
 }
 
+// Prompt tokens of one slot, KS_PREFILL_CHUNK at a time: the rows of a chunk share one pass over the
+// weights (the batch form of the matvec kernels, K:1414) and attend causally inside the chunk.  This is
+// the reference's GEMV fallback for prompts (forward_prefill_chunk, gemma_prim.rs:1317-1607, runs its
+// mul_mm GEMM instead); no logits are produced.  Enqueues only, apart from the wait for the pinned
+// staging words between chunks.
+int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, tokens || n_tokens == 0, "prefill: null tokens");
+  KS_REQUIRE(c, n_tokens >= 0, "prefill: negative token count");
+  int rc;
+  if ((rc = check_ready(m)) || (rc = check_slots(m, slot, 1))) return rc;
+  if (m->seq_len[slot] + n_tokens > m->cfg.max_seq) return ks_fail(c, KS_ERR_STATE, "max_seq exceeded");
+  float* stage = m->host_tok + m->host_tok_n - 8;
+  for (int t0 = 0; t0 < n_tokens; t0 += m->chunk) {
+    const int n = n_tokens - t0 < m->chunk ? n_tokens - t0 : m->chunk;
+    KS_CUDA(c, cudaStreamSynchronize(c->stream));  // the staging words may still be in flight
+    for (int t = 0; t < n; t++) {
+      KS_REQUIRE(c, tokens[t0 + t] >= 0 && tokens[t0 + t] < m->cfg.vocab, "token id %d outside the vocabulary", tokens[t0 + t]);
+      stage[t] = (float)tokens[t0 + t];
+    }
+    KS_CUDA(c, cudaMemcpyAsync(m->ctok, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if ((rc = run_prefill_chunk(m, slot, n))) return rc;
+    m->seq_len[slot] += n;
+  }
+  return KS_OK;
+}
+
 // Blocking greedy step with host ids in and out: the serve path's decode_token
 // (gemma_prim.rs:1616-1635).  4*n bytes go up, 4*n bytes come back, every call.
 int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int* next) {
@@ -654,7 +809,7 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   return KS_OK;
 }
 
-// generate_timed (gemma_prim.rs:1658-1768) for one slot: rewind, run prompt[0..n-2] without
+// generate_timed (gemma_prim.rs:1658-1768) for one slot: rewind, run prompt[0..n-2] in chunks without
 // logits, then n_new greedy steps starting from the last prompt token.  The token id never
 // leaves the device between steps; each step's id is copied to pinned host memory behind the
 // step and the host waits only once more than `max_inflight` steps are pending
@@ -675,8 +830,7 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
   KS_CUDA(c, cudaEventCreate(&e1));
   KS_CUDA(c, cudaEventCreate(&e2));
   cudaEventRecord(e0, c->stream);
-  for (int i = 0; i + 1 < n_prompt; i++)
-    if ((rc = ks_model_forward(m, slot, 1, &prompt[i], 0))) return rc;
+  if ((rc = ks_model_prefill(m, slot, prompt, n_prompt - 1))) return rc;
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
   int last = prompt[n_prompt - 1];
   cudaEventRecord(e1, c->stream);

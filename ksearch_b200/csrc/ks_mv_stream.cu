@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
     uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * (Q4K_XS * 4u);
     uint32_t saddr = xs_s + units * (Q4K_XS * 4u) + (cs * seg_units + (unsigned)cl) * 8u;
     for (unsigned it = 0; it < upl; it++) {
+      if constexpr (NT == 1) {
 #pragma unroll
       for (int t = 0; t < NT; t++) {
         if (t < a.n_tok) {
@@ -234,6 +235,66 @@ __global__ void __launch_bounds__(256) mvs_q4k_kernel(const MvsArgs a) {
             const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)(r * RL) * seg_bytes - (uint32_t)g * 32u);
             const float2 a01 = unpack2(padd2(acc[r][0], acc[r][1]));
             yacc[r][t] = q4k_apply_scales(hdr, g, a01.x, a01.y, sx.x, sx.y, yacc[r][t]);
+          }
+        }
+      }
+      } else {
+        // Several tokens: every nibble is turned into an f32 ONCE and then meets each token's x
+        // (the conversion is two thirds of the single-token instruction count).
+        u64 acc[SLOTS][NT][2];
+#pragma unroll
+        for (int r = 0; r < SLOTS; r++)
+#pragma unroll
+          for (int t = 0; t < NT; t++) acc[r][t][0] = acc[r][t][1] = 0ull;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          constexpr u64 M2 = ((u64)kMagicBits << 32) | kMagicBits;
+          u64 f[SLOTS][16];
+#pragma unroll
+          for (int r = 0; r < SLOTS; r++) {
+            const uint4 q = half ? lds_u4o<32>(waddr + (uint32_t)(r * RL) * seg_bytes) : lds_u4o<16>(waddr + (uint32_t)(r * RL) * seg_bytes);
+            const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+              const u64 ww = pack2(qw[w], qw[w]), hh = pack2(qw[w] >> 16, qw[w] >> 16);
+              f[r][4 * w + 0] = padd2((ww & 0x000000F00000000Full) | M2, kNegMagic2);
+              f[r][4 * w + 1] = padd2((ww & 0x0000F00000000F00ull) | M2, kNegMagic2);
+              f[r][4 * w + 2] = padd2((hh & 0x000000F00000000Full) | M2, kNegMagic2);
+              f[r][4 * w + 3] = padd2((hh & 0x0000F00000000F00ull) | M2, kNegMagic2);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            if (t < a.n_tok) {
+              const uint32_t xt = xaddr + (uint32_t)t * tok_stride + (uint32_t)half * 128u;
+              u64 xf[16];
+              lds_p2o<0>(xt, xf[0], xf[1]);     lds_p2o<16>(xt, xf[2], xf[3]);
+              lds_p2o<32>(xt, xf[4], xf[5]);    lds_p2o<48>(xt, xf[6], xf[7]);
+              lds_p2o<64>(xt, xf[8], xf[9]);    lds_p2o<80>(xt, xf[10], xf[11]);
+              lds_p2o<96>(xt, xf[12], xf[13]);  lds_p2o<112>(xt, xf[14], xf[15]);
+#pragma unroll
+              for (int r = 0; r < SLOTS; r++)
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc[r][t][j & 1] = pfma2(f[r][j], xf[j], acc[r][t][j & 1]);
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < SLOTS; r++) {
+          const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)(r * RL) * seg_bytes - (uint32_t)g * 32u);
+          float dsc_lo, dsc_hi, dm_lo, dm_hi;
+          q4k_group_scales(hdr, g, dsc_lo, dsc_hi, dm_lo, dm_hi);
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            if (t < a.n_tok) {
+              const float2 sx = lds_f2a(saddr + (uint32_t)t * tok_stride);
+              const float2 a01 = unpack2(padd2(acc[r][t][0], acc[r][t][1]));
+              float y = yacc[r][t];
+              y = fmaf(dsc_lo, a01.x, y);
+              y = fmaf(dsc_hi, a01.y, y);
+              y = fmaf(-dm_lo, sx.x, y);
+              yacc[r][t] = fmaf(-dm_hi, sx.y, y);
+            }
           }
         }
       }

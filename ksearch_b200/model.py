@@ -177,6 +177,12 @@ class GemmaCudaModel:
         arr = None if tokens is None else (C.c_int * n)(*[int(t) for t in tokens])
         self.ctx.check(self.lib.ks_model_forward(self.h, first, n, arr, int(want_logits)))
 
+    def prefill(self, slot: int, tokens):
+        """Prompt tokens without logits, eight per pass over the weights (prefill_chunk, gemma_prim.rs:1305-1315)."""
+        toks = [int(t) for t in tokens]
+        arr = (C.c_int * max(1, len(toks)))(*toks)
+        self.ctx.check(self.lib.ks_model_prefill(self.h, slot, arr, len(toks)))
+
     def decode_token(self, tokens, first: int = 0):
         toks = [int(t) for t in np.atleast_1d(tokens)]
         n = len(toks)

@@ -213,6 +213,38 @@ def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     c.close()
 
 
+@pytest.mark.parametrize("n_kv", [1, 2])
+def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
+    """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk.
+    After the prompt, the next-token logits must match the CPU decoder, and the KV rows it wrote must
+    serve later decode steps (teacher-forced continuation)."""
+    cfg = ksm.tiny_config(max_seq=96, n_kv=n_kv)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=31, keep=True)
+    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    model.slot_alloc()
+    for n_prompt in (1, 7, 8, 9, 21):          # below, at and above the chunk size; ragged last chunk
+        toks = synth.token_ids(31, f"p{n_prompt}", n_prompt + 6, cfg.vocab)
+        model.slot_reset(0)
+        cpu.reset()
+        model.prefill(0, toks[:n_prompt])
+        assert model.seq_len(0) == n_prompt
+        for t in toks[:n_prompt]:
+            cpu.forward_token(int(t), False)
+        for t in toks[n_prompt:]:               # decode steps on top of the prefilled cache
+            model.forward(0, 1, [int(t)], True)
+            ctx.synchronize()
+            got = model.read_debug(1, 0).astype(np.float64)
+            cpu.forward_token(int(t), True)
+            want = cpu.logits().astype(np.float64)
+            scale = np.abs(want).max()
+            err = np.abs(got - want)
+            assert err.max() <= 2e-2 * scale and np.sqrt((err ** 2).mean()) <= 2e-3 * scale
+    with pytest.raises(KsError, match="max_seq exceeded"):
+        model.prefill(0, [1] * 200)
+    cpu.close()
+    model.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
