@@ -243,6 +243,7 @@ def gemv_config0(ctx, peak):
     x = ctx.buffer_bytes(synth.normals(SEED, "cfg0/x", cols))
     y = ctx.buffer_empty_f32(rows)
     lib = ctx.lib
+    lib.ks_plan_search(ctx.h, b"mv_q4k", rows, 0, cols, 1, None)   # load-time plan search for this shape, untimed
     ctx.graph_begin()
     for c in range(ncopy):
         ctx.check(lib.ks_matvec(ctx.h, rows, cols, Q4K, big.h, c * one.nbytes, 0, x.h, 0, y.h, 0, 1))
