@@ -123,7 +123,7 @@ def run_reference(args, rank, world):
     cfg.n_layers = ls
     cfg.vocab = max(256, full.vocab * ls // full.n_layers // 256 * 256)
     T = ksm.synth_tensors(cfg, SEED)
-    dec = ks_oracle.CpuDecoder(ksm.oracle_cfg(cfg), T, fast=True)
+    dec = ks_oracle.CpuDecoder(ks_oracle.decoder_cfg(cfg), T, fast=True)
     tok = 17
     t0 = time.perf_counter()
     tok = dec.forward_token(tok, True)
@@ -272,7 +272,7 @@ def cpu_baseline(cfg_full):
     cfg.n_layers = ls
     cfg.vocab = cfg_full.vocab * ls // cfg_full.n_layers // 256 * 256
     T = ksm.synth_tensors(cfg, SEED)
-    dec = ks_oracle.CpuDecoder(ksm.oracle_cfg(cfg), T, fast=True)
+    dec = ks_oracle.CpuDecoder(ks_oracle.decoder_cfg(cfg), T, fast=True)
     frac = ksm.weight_bytes_per_token(cfg) / ksm.weight_bytes_per_token(cfg_full)
     tok = dec.forward_token(3, True)
     n, t0 = 0, time.perf_counter()

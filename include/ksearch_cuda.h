@@ -206,7 +206,8 @@ int ks_quantize_q40(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* src, size
  * idx holds token ids as f32.  src dtype: F32, F16, Q4K or Q6K. */
 int ks_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype, const ks_buf* src,
                           const ks_buf* idx, size_t idx_off, ks_dtype act, ks_buf* dst);
-/* K:1966 softcap_argmax: index of max cap*tanh(x/cap), ties to the lower index, written as one f32. */
+/* K:1966 softcap_argmax: index of max cap*tanh(x/cap), ties to the lower index, written as one f32
+ * (like the reference, so the index is exact only below 2^24 = 16,777,216).  1 <= n <= 2^31. */
 int ks_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const ks_buf* logits, ks_buf* out_idx,
                       size_t out_off);
 /* No counterpart in the reference.  The same arg-max as ks_softcap_argmax (f32 logits) for callers that
@@ -265,6 +266,10 @@ int ks_model_decode_token(ks_model* m, int first_slot, int n_slots, const int* t
 int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight,
                       int* out, ks_generate_stats* stats);                   /* GP:1658 generate_timed */
 const void* ks_model_debug_ptr(const ks_model* m, int which, int slot);      /* test hook: 0 residual x, 1 logits */
+/* One slot's rows of a layer's KV cache on the device, [max_seq, n_kv, hd] in Q4_0 (KV:24-60 holds one such
+ * buffer per owning layer); which: 0 = K, 1 = V.  For tests and for hosts that snapshot or restore a slot. */
+void* ks_model_kv_ptr(const ks_model* m, int layer, int which, int slot);
+size_t ks_model_kv_slot_bytes(const ks_model* m);                            /* bytes of one slot in one layer's K (or V) */
 
 #ifdef __cplusplus
 }

@@ -101,7 +101,7 @@ struct ks_model {
   std::map<uint64_t, cudaGraphExec_t> graphs;
   std::map<uint64_t, size_t> graph_nodes;
   std::vector<void*> owned;
-  int tok_src = 0;  // which half of the ping-pong holds the next input ids
+  std::vector<char> tok_src;  // per slot: which half of the ping-pong holds its next input id
   // one persistent decode kernel per slot (nullptr entry: shape not covered, tried once)
   std::map<int, ks_mega*> mega;
   bool use_mega = false;
@@ -543,6 +543,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   }
   m->occupied.assign(g.n_slots, 0);
   m->seq_len.assign(g.n_slots, 0);
+  m->tok_src.assign(g.n_slots, 0);
   const size_t S = g.n_slots;
   m->fused = ks_matvec_can_fuse_pro(KS_Q4K, H) && !getenv("KSEARCH_UNFUSED");
   // Single-slot steps run all layers inside one persistent kernel; KSEARCH_DECODE_KERNEL=0 keeps one
@@ -748,7 +749,13 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
   ks_ctx* c = m->ctx;
   int rc;
   if ((rc = check_ready(m)) || (rc = check_slots(m, first, n))) return rc;
-  int src = m->tok_src;
+  // Ids chained on the device sit in the half of the ping-pong each slot's last head wrote; slots that
+  // step together must agree on it (they do when they always step together, or when ids come from the host).
+  int src = m->tok_src[first];
+  if (!tokens)
+    for (int s = first + 1; s < first + n; s++)
+      if (m->tok_src[s] != src)
+        return ks_fail(c, KS_ERR_STATE, "slots %d..%d hold their device-side token ids in different buffers; pass host ids", first, first + n - 1);
   if (tokens) {
     src = 0;
     float* stage = m->host_tok + m->host_tok_n - 8;  // last 8 entries of the pinned ring stage the ids
@@ -760,9 +767,31 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
     KS_CUDA(c, cudaMemcpyAsync(m->tok + first, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
   }
   if ((rc = run_forward(m, first, n, src, want_logits != 0))) return rc;
-  for (int s = first; s < first + n; s++) m->seq_len[s] += 1;
-  m->tok_src = want_logits ? (src ^ 1) : src;
+  for (int s = first; s < first + n; s++) {
+    m->seq_len[s] += 1;
+    m->tok_src[s] = (char)(want_logits ? (src ^ 1) : src);
+  }
   return KS_OK;
+}
+
+// After a blocking wait: did a bounded device-side wait give up during the steps just run?  `status`
+// is the pinned word the context's status word was copied to behind them.  When it is set, the token
+// ids that came back are meaningless: the status word is cleared, the persistent kernel's barrier
+// words are put back to rest, the slots are rewound by `steps` positions and KS_ERR_TIMEOUT is returned,
+// so the context stays usable.
+static int check_device_status(ks_model* m, const unsigned* status, int first, int n, int steps) {
+  if (!*status) return KS_OK;
+  ks_ctx* c = m->ctx;
+  const unsigned flag = *status;
+  cudaMemsetAsync((unsigned*)c->ws + KS_WS_ERR_WORD, 0, sizeof(unsigned), c->stream);
+  for (int s = first; s < first + n; s++) {
+    m->seq_len[s] = m->seq_len[s] >= steps ? m->seq_len[s] - steps : 0;
+    KS_LAUNCH(c, (set_state_kernel), 1, 1, 0, s, m->seq_len[s], m->pos);
+    auto it = m->mega.find(s);
+    if (it != m->mega.end() && it->second) ks_mega_reset(c, it->second);
+  }
+  cudaStreamSynchronize(c->stream);
+  return ks_fail(c, KS_ERR_TIMEOUT, "a device-side wait gave up during decode (status word 0x%x); the slots were rewound", flag);
 }
 
 // Prompt tokens of one slot, KS_PREFILL_CHUNK at a time: the rows of a chunk share one pass over the
@@ -802,9 +831,12 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
   float* back = m->host_tok;
-  KS_CUDA(c, cudaMemcpyAsync(back, m->tok + (size_t)m->tok_src * m->cfg.n_slots + first, n * sizeof(float),
+  unsigned* status = reinterpret_cast<unsigned*>(m->host_tok + m->host_tok_n - 9);  // pinned word next to the id staging
+  KS_CUDA(c, cudaMemcpyAsync(back, m->tok + (size_t)m->tok_src[first] * m->cfg.n_slots + first, n * sizeof(float),
                              cudaMemcpyDeviceToHost, c->stream));
+  KS_CUDA(c, cudaMemcpyAsync(status, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream));
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
+  if ((rc = check_device_status(m, status, first, n, 1))) return rc;
   for (int s = 0; s < n; s++) next[s] = (int)back[s];
   return KS_OK;
 }
@@ -820,7 +852,7 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
   if (!m) return KS_ERR_INVALID;
   ks_ctx* c = m->ctx;
   KS_REQUIRE(c, prompt && n_prompt >= 1, "empty prompt");
-  KS_REQUIRE(c, n_new >= 0 && (size_t)n_new <= m->host_tok_n - 8, "generate: n_new out of range");
+  KS_REQUIRE(c, n_new >= 0 && (size_t)n_new <= m->host_tok_n - 16, "generate: n_new out of range");
   KS_REQUIRE(c, out || n_new == 0, "generate: null output");
   int rc;
   if ((rc = ks_model_slot_reset(m, slot))) return rc;
@@ -838,7 +870,7 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
   if (max_inflight < 0) max_inflight = 0;
   for (int i = 0; i < n_new; i++) {
     if ((rc = ks_model_forward(m, slot, 1, i == 0 ? &last : nullptr, 1))) return rc;
-    KS_CUDA(c, cudaMemcpyAsync(m->host_tok + i, m->tok + (size_t)m->tok_src * m->cfg.n_slots + slot, sizeof(float),
+    KS_CUDA(c, cudaMemcpyAsync(m->host_tok + i, m->tok + (size_t)m->tok_src[slot] * m->cfg.n_slots + slot, sizeof(float),
                                cudaMemcpyDeviceToHost, c->stream));
     cudaEvent_t ev;
     KS_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
@@ -848,8 +880,16 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
     if (wait_upto >= 0) KS_CUDA(c, cudaEventSynchronize(done[wait_upto]));
   }
   cudaEventRecord(e2, c->stream);
+  unsigned* status = reinterpret_cast<unsigned*>(m->host_tok + m->host_tok_n - 9);
+  KS_CUDA(c, cudaMemcpyAsync(status, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream));
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
   for (cudaEvent_t ev : done) cudaEventDestroy(ev);
+  if ((rc = check_device_status(m, status, slot, 1, n_new))) {
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaEventDestroy(e2);
+    return rc;
+  }
   for (int i = 0; i < n_new; i++) out[i] = (int)m->host_tok[i];
   if (stats) {
     float a = 0, b = 0;
@@ -878,5 +918,12 @@ const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
   }
   return nullptr;
 }
+
+// Device address of one slot's rows of a layer's cache ([max_seq, n_kv, hd] Q4_0); which: 0 = K, 1 = V.
+void* ks_model_kv_ptr(const ks_model* m, int layer, int which, int slot) {
+  if (!m || layer < 0 || layer >= m->cfg.n_layers || slot < 0 || slot >= m->cfg.n_slots || which < 0 || which > 1) return nullptr;
+  return (which ? m->kv_v[layer] : m->kv_k[layer]) + (size_t)slot * m->slot_stride;
+}
+size_t ks_model_kv_slot_bytes(const ks_model* m) { return m ? m->slot_stride : 0; }
 
 }  // extern "C"

@@ -527,7 +527,8 @@ int ks_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_d
 int ks_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const ks_buf* logits, ks_buf* out_idx, size_t out_off) {
   if (!ctx) return KS_ERR_INVALID;
   KS_REQUIRE(ctx, ks_is_act(act), "softcap_argmax: logits dtype must be F32 or F16");
-  KS_REQUIRE(ctx, n > 0 && n < (1ull << 32), "softcap_argmax: n=%zu out of range", n);
+  // 32-bit indices inside the kernel: n + one grid stride must not wrap; the index comes back as f32 (exact below 2^24)
+  KS_REQUIRE(ctx, n > 0 && n <= (1ull << 31), "softcap_argmax: n=%zu out of range (1 .. 2^31)", n);
   KS_REQUIRE(ctx, cap > 0.0f, "softcap_argmax: cap must be > 0");
   KS_REQUIRE(ctx, ks_fits(logits, 0, n * ks_act_bytes(act)), "softcap_argmax: logits buffer too small");
   KS_REQUIRE(ctx, ks_fits(out_idx, out_off * 4, 4), "softcap_argmax: output buffer too small");
@@ -565,7 +566,10 @@ static __device__ __align__(256) unsigned ks_noalloc_scratch[KS_NOALLOC_MAX_BLOC
 
 extern "C" int ks_softcap_argmax_noalloc(int device, void* stream, size_t n, float cap, const float* logits,
                                          float* out_idx) {
-  static void* scratch_addr[64] = {nullptr};  // device address of the array, per device
+  // Device address of the array, per device.  The cache is not synchronised: like every entry point of
+  // this library it expects one calling thread at a time (two racing first calls would both look the
+  // address up and store the same value, but nothing here promises more than that).
+  static void* scratch_addr[64] = {nullptr};
   char msg[256];
   if (!logits || !out_idx || n == 0 || !(cap > 0.0f) || device < 0 || device >= 64) {
     ks_set_global_error("softcap_argmax_noalloc: null pointer, n == 0, cap <= 0 or bad device index");

@@ -689,6 +689,8 @@ void kso_state_free(kso_state* s) {
 void kso_state_reset(kso_state* s) { s->pos = 0; }
 const float* kso_state_logits(const kso_state* s) { return s->logits; }
 const float* kso_state_hidden(const kso_state* s) { return s->x; }
+/* the decoder's cache rows of one layer, [max_seq, n_kv, hd] Q4_0; which: 0 = K, 1 = V */
+uint8_t* kso_state_kv(const kso_state* s, int layer, int which) { return which ? s->kv_v[layer] : s->kv_k[layer]; }
 
 /* One token through all layers; returns the greedy next token (softcap argmax),
  * or -1 when pos >= max_seq ("max_seq exceeded", gemma_prim.rs:882-884).

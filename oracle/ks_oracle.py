@@ -104,6 +104,8 @@ def lib(fast: bool = False) -> C.CDLL:
         L.kso_state_logits.argtypes = [C.c_void_p]
         L.kso_state_hidden.restype = _f32p
         L.kso_state_hidden.argtypes = [C.c_void_p]
+        L.kso_state_kv.restype = _u8p
+        L.kso_state_kv.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.kso_forward_token.restype = C.c_int
         L.kso_forward_token.argtypes = [C.c_void_p, C.c_int, C.c_int]
         _libs[fast] = L
@@ -335,6 +337,12 @@ class CpuDecoder:
     def hidden(self) -> np.ndarray:
         return np.ctypeslib.as_array(self._L.kso_state_hidden(self._s), shape=(self.cfg["hidden"],)).copy()
 
+    def kv(self, layer: int, which: int) -> np.ndarray:
+        """A view (not a copy) of one layer's cache rows, [max_seq * n_kv * hd/32 * 18] bytes; which: 0 = K, 1 = V."""
+        c = self.cfg
+        n = c["max_seq"] * c["n_kv"] * (c["hd"] // 32) * 18
+        return np.ctypeslib.as_array(self._L.kso_state_kv(self._s, layer, which), shape=(n,))
+
     def generate(self, prompt, n_new: int):
         """gemma_prim.rs:1658-1768: prompt[:-1] without logits, then n_new greedy steps from prompt[-1]."""
         self.reset()
@@ -357,3 +365,36 @@ class CpuDecoder:
             self.close()
         except Exception:
             pass
+
+
+_CFG_KEYS = ("n_layers", "hidden", "ffn", "n_q", "n_kv", "hd", "vocab", "max_seq", "eps", "rope_theta",
+             "softcap", "attn_scale", "embd_dtype")
+
+
+def decoder_cfg(cfg) -> dict:
+    """The CpuDecoder's config dict from a model-config object (attributes of the same names)."""
+    return {k: getattr(cfg, k) for k in _CFG_KEYS}
+
+
+def compare_streams(cuda_tokens, cpu_decoder, prompt, logit_tol: float = 2e-3):
+    """Greedy streams must be identical; the one allowed exception is a near-tie: where the CUDA
+    token differs, the CPU logits of the two candidates must differ by less than logit_tol
+    (relative to the logit scale), and the comparison continues on the CUDA token.
+    Returns (n_equal, n_near_tie)."""
+    cpu_decoder.reset()
+    for t in prompt[:-1]:
+        cpu_decoder.forward_token(int(t), False)
+    tok = int(prompt[-1])
+    equal = ties = 0
+    for got in cuda_tokens:
+        want = cpu_decoder.forward_token(tok, True)
+        if want == got:
+            equal += 1
+        else:
+            lg = cpu_decoder.logits()
+            gap = abs(float(lg[want]) - float(lg[got]))
+            if gap > logit_tol * max(1.0, float(np.abs(lg).max())):
+                raise AssertionError(f"token stream diverged: cuda {got} vs cpu {want}, logit gap {gap}")
+            ties += 1
+        tok = got
+    return equal, ties

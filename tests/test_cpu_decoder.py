@@ -58,7 +58,7 @@ def test_cpu_decoder_matches_numpy_and_is_deterministic(oracle):
     cfg = ksm.tiny_config(max_seq=8)
     cfg.n_layers = 2
     T = ksm.synth_tensors(cfg, 3)
-    dec = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    dec = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     toks = [5, 77, 1024]
     for i, t in enumerate(toks):
         nxt = dec.forward_token(t, i == len(toks) - 1)
@@ -77,7 +77,7 @@ def test_cpu_decoder_matches_numpy_and_is_deterministic(oracle):
 def test_cpu_decoder_max_seq(oracle):
     cfg = ksm.tiny_config(max_seq=3)
     cfg.n_layers = 1
-    dec = oracle.CpuDecoder(ksm.oracle_cfg(cfg), ksm.synth_tensors(cfg, 4))
+    dec = oracle.CpuDecoder(oracle.decoder_cfg(cfg), ksm.synth_tensors(cfg, 4))
     for t in (1, 2, 3):
         dec.forward_token(t, False)
     with pytest.raises(RuntimeError, match="max_seq exceeded"):

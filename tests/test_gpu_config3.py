@@ -1,0 +1,65 @@
+"""The benchmarked model at its full size: 35 layers, hidden 1536, GeGLU 6144, 8 q / 1 kv heads of 256,
+vocab 262144, Q4_K layers, Q6_K tied lm_head, Q4_0 KV -- teacher-forced logits and the greedy stream of a
+64-token prompt + 128 decoded tokens against the CPU decoder, through the persistent decode kernel and
+through the launch-per-op path."""
+import numpy as np
+import pytest
+
+from ksearch_b200 import CudaContext, synth
+from ksearch_b200 import model as ksm
+
+pytestmark = pytest.mark.gpu
+
+SEED = 1234          # the benchmark's seed: the same weights bench.py times
+N_TF, N_PROMPT, N_NEW = 16, 64, 128
+
+
+@pytest.fixture(scope="module")
+def full_model(oracle):
+    cfg = ksm.e2b_config(max_seq=N_PROMPT + N_NEW + 8)
+    T = ksm.synth_tensors(cfg, SEED)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    tf_tokens = synth.token_ids(SEED, "tf", N_TF, cfg.vocab)
+    tf_logits = []
+    for t in tf_tokens:
+        cpu.forward_token(int(t), True)
+        tf_logits.append(cpu.logits().astype(np.float64))
+    state = {"cfg": cfg, "T": T, "cpu": cpu, "tf_tokens": tf_tokens, "tf_logits": tf_logits, "streams": {}}
+    yield state
+    cpu.close()
+
+
+@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+def test_full_e2b_model_matches_cpu_decoder(full_model, oracle, monkeypatch, decode_kernel):
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
+    cfg, T, cpu = full_model["cfg"], full_model["T"], full_model["cpu"]
+    c = CudaContext(0, flags=1)
+    model = ksm.GemmaCudaModel(c, cfg)
+    for name, arr in T.items():
+        model.upload_tensor(name, arr)
+    model.slot_alloc()
+    worst_max = worst_rms = 0.0
+    for t, want in zip(full_model["tf_tokens"], full_model["tf_logits"]):
+        model.forward(0, 1, [int(t)], True)
+        c.synchronize()
+        got = model.read_debug(1, 0).astype(np.float64)
+        scale = np.abs(want).max()
+        err = np.abs(got - want)
+        worst_max = max(worst_max, err.max() / scale)
+        worst_rms = max(worst_rms, float(np.sqrt((err ** 2).mean())) / scale)
+        assert int(np.argmax(got)) == int(np.argmax(want)) or np.sort(want)[-1] - np.sort(want)[-2] < 2e-3 * scale
+    print(f"[config 3, kernel={decode_kernel}] teacher-forced logits over {N_TF} tokens: worst max error "
+          f"{worst_max:.2e}, worst rms error {worst_rms:.2e} (relative to the largest logit)")
+    assert worst_max <= 2e-2 and worst_rms <= 2e-3
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
+    prompt = synth.token_ids(SEED, "prompt", N_PROMPT, cfg.vocab)
+    out, st = model.generate_timed(prompt, N_NEW)
+    assert st.prefill_tokens == N_PROMPT - 1 and st.decode_tokens == N_NEW
+    key = tuple(out)
+    if key not in full_model["streams"]:       # the CPU pass follows the CUDA stream; identical streams share it
+        full_model["streams"][key] = oracle.compare_streams(out, cpu, prompt)
+    equal, ties = full_model["streams"][key]
+    print(f"[config 3, kernel={decode_kernel}] greedy stream: {equal} identical, {ties} near-ties of {N_NEW}")
+    assert equal + ties == N_NEW and ties <= 2
+    model.close()
+    c.close()

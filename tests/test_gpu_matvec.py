@@ -192,6 +192,22 @@ def test_matvec_full_config_shapes_row_checksums(ctx, oracle):
         assert np.isfinite(got).all()
 
 
+def test_q6k_lm_head_all_rows(ctx, oracle):
+    """The tied lm_head at its full size, 262144 x 1536 Q6_K with signed scales: every row against the oracle."""
+    from ksearch_b200 import model as ksm
+    rows, cols = 262144, 1536
+    cfg = ksm.e2b_config()
+    W = ksm.synth_tensor(cfg, 77, "token_embd.weight", "embd", rows, cols)
+    x = synth.normals(77, "x", cols)
+    y = ctx.buffer_empty_f32(rows)
+    bw = ctx.buffer_bytes(W)
+    Eng().matvec_wd(ctx, rows, cols, Q6K, bw, ctx.buffer_bytes(x), y)
+    got = ctx.read_f32(y, rows)
+    y32, y64 = oracle.matvec(Q6K, W, rows, cols, x)
+    _check(got, y32, y64, "lm_head 262144x1536")
+    bw.free()
+
+
 def test_matvec_host_entry(ctx, oracle):
     rows, cols = 512, 1536
     W = _gen(Q4K, 70, "W", rows, cols)

@@ -34,14 +34,14 @@ def _teacher_forced(model, cpu, tokens, slot=0):
 def test_tiny_model_matches_cpu_decoder(ctx, oracle, n_kv):
     cfg = ksm.tiny_config(max_seq=48, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=9, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     assert model.slot_alloc() == 0
     toks = synth.token_ids(9, "tf", 20, cfg.vocab)
     _teacher_forced(model, cpu, toks)
     prompt = synth.token_ids(9, "prompt", 8, cfg.vocab)
     out, st = model.generate_timed(prompt, 24)
     assert len(out) == 24 and st.decode_tokens == 24 and st.prefill_tokens == 7
-    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 24 and ties <= 1
     assert model.seq_len(0) == 7 + 24
     # generate again: the slot is rewound and the stream repeats exactly
@@ -76,7 +76,7 @@ def test_slots_advance_together(ctx, oracle):
             model.forward(s, 1, [int(t)], False)
     want_logits = []
     for s in range(4):
-        cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+        cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
         for t in seqs[s][:lens[s]]:
             cpu.forward_token(int(t), False)
         rows = []
@@ -157,14 +157,14 @@ def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv)
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=80, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=21, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     assert model.slot_alloc() == 0
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is None      # not built before the first step
     _teacher_forced(model, cpu, synth.token_ids(21, "tf", 70, cfg.vocab))   # crosses several attention split counts
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None  # the persistent kernel did run
     prompt = synth.token_ids(21, "prompt", 8, cfg.vocab)
     out, _ = model.generate_timed(prompt, 24)
-    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 24 and ties <= 1
     out2, _ = model.generate_timed(prompt, 24, max_inflight=0)
     assert out2 == out
@@ -181,7 +181,7 @@ def test_persistent_kernel_long_context(oracle, monkeypatch):
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=320, n_kv=2)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=23, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
     _teacher_forced(model, cpu, synth.token_ids(23, "tf", 300, cfg.vocab))
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
@@ -200,14 +200,110 @@ def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     c = CudaContext(0, flags=1)
     cfg = ksm.ModelConfig(2, 2560, 10240, 8, 2, 256, 4096, 64, 1, sigma_w=0.01, sigma_embd=5e-5)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=24, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
     _teacher_forced(model, cpu, synth.token_ids(24, "tf", 40, cfg.vocab))
     assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
     prompt = synth.token_ids(24, "prompt", 6, cfg.vocab)
     out, _ = model.generate_timed(prompt, 12)
-    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 12 and ties <= 1
+    cpu.close()
+    model.close()
+    c.close()
+
+
+@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+def test_e2b_like_shapes(oracle, monkeypatch, decode_kernel):
+    """Two layers with the E2B row and column counts (hidden 1536, GeGLU 6144, 8 q / 1 kv heads of 256):
+    the shapes of the benchmarked model -- six blocks per row, eight query heads on one KV head, two
+    4-element chunks per thread in the fused norms -- through the persistent kernel and through the
+    launch-per-op path."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
+    c = CudaContext(0, flags=1)
+    cfg = ksm.ModelConfig(2, 1536, 6144, 8, 1, 256, 4096, 320, 1, sigma_w=0.01, sigma_embd=5e-5)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=25, keep=True)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    model.slot_alloc()
+    _teacher_forced(model, cpu, synth.token_ids(25, "tf", 150, cfg.vocab))   # past 128 positions: every split in use
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
+    prompt = synth.token_ids(25, "prompt", 6, cfg.vocab)
+    out, _ = model.generate_timed(prompt, 24)
+    equal, ties = oracle.compare_streams(out, cpu, prompt)
+    assert equal + ties == 24 and ties <= 1
+    cpu.close()
+    model.close()
+    c.close()
+
+
+def _kv_row_bytes(cfg):
+    return cfg.n_kv * (cfg.hd // 32) * 18
+
+
+def _nibble_diffs(a, b, cfg):
+    """(differing 4-bit values, differing fp16 scales) between two packed Q4_0 byte strings."""
+    a = a.reshape(-1, 18)
+    b = b.reshape(-1, 18)
+    qa, qb = a[:, 2:], b[:, 2:]
+    nib = int(((qa & 15) != (qb & 15)).sum() + ((qa >> 4) != (qb >> 4)).sum())
+    sc = int((a[:, :2] != b[:, :2]).any(axis=1).sum())
+    return nib, sc
+
+
+@pytest.mark.parametrize("shape", ["tiny", "e2b_rows"])
+@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+def test_logits_tight_when_kv_bytes_agree(oracle, monkeypatch, shape, decode_kernel):
+    """Why the multi-layer logit bound above is looser than the per-op bound: the only amplifier is a
+    Q4_0 value of a new K/V row that sits on a rounding boundary and rounds the other way (its f32
+    input differs in the last bits).  Shown here by removing that effect: before every step the GPU
+    cache is overwritten with the CPU decoder's bytes, and every step whose own new rows come out
+    byte-identical in every layer must meet the per-op tolerance on the logits,
+    |got - want| <= 1e-4 * scale + 1e-3 * |want|.  The differing values are counted."""
+    from ksearch_b200 import CudaContext
+    monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
+    c = CudaContext(0, flags=1)
+    if shape == "tiny":
+        cfg = ksm.tiny_config(max_seq=48)
+    else:
+        cfg = ksm.ModelConfig(2, 1536, 6144, 8, 1, 256, 4096, 48, 1, sigma_w=0.01, sigma_embd=5e-5)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=26, keep=True)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    model.slot_alloc()
+    rowb = _kv_row_bytes(cfg)
+    toks = synth.token_ids(26, "tf", 40, cfg.vocab)
+    clean = nib_total = sc_total = 0
+    for t, tok in enumerate(toks):
+        if t:
+            for l in range(cfg.n_layers):
+                for which in (0, 1):
+                    model.write_kv(l, which, cpu.kv(l, which)[:t * rowb])
+        model.forward(0, 1, [int(tok)], True)
+        c.synchronize()
+        cpu.forward_token(int(tok), True)
+        nib = sc = 0
+        for l in range(cfg.n_layers):
+            for which in (0, 1):
+                got_row = model.read_kv(l, which, nbytes=(t + 1) * rowb)[t * rowb:]
+                n, s_ = _nibble_diffs(got_row, cpu.kv(l, which)[t * rowb:(t + 1) * rowb], cfg)
+                nib += n
+                sc += s_
+        nib_total += nib
+        sc_total += sc
+        got = model.read_debug(1, 0).astype(np.float64)
+        want = cpu.logits().astype(np.float64)
+        scale = np.abs(want).max()
+        err = np.abs(got - want)
+        if nib == 0 and sc == 0:
+            clean += 1
+            assert np.all(err <= 1e-4 * scale + 1e-3 * np.abs(want)), (t, err.max() / scale)
+        else:
+            assert err.max() <= 2e-2 * scale
+    values = len(toks) * cfg.n_layers * 2 * cfg.n_kv * cfg.hd
+    print(f"[kv parity {shape} kernel={decode_kernel}] steps with identical new rows: {clean}/{len(toks)}; "
+          f"differing 4-bit values {nib_total} of {values}, differing scales {sc_total}")
+    assert clean >= len(toks) // 2
+    assert nib_total <= values // 100
     cpu.close()
     model.close()
     c.close()
@@ -220,7 +316,7 @@ def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
     serve later decode steps (teacher-forced continuation)."""
     cfg = ksm.tiny_config(max_seq=96, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=31, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
     for n_prompt in (1, 7, 8, 9, 21):          # below, at and above the chunk size; ragged last chunk
         toks = synth.token_ids(31, f"p{n_prompt}", n_prompt + 6, cfg.vocab)
@@ -252,13 +348,13 @@ def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=48)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=22, keep=True)
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     assert model.slot_alloc() == 0
     _teacher_forced(model, cpu, synth.token_ids(22, "tf", 20, cfg.vocab))
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is None      # the persistent kernel was never built
     prompt = synth.token_ids(22, "prompt", 8, cfg.vocab)
     out, _ = model.generate_timed(prompt, 24)
-    equal, ties = ksm.compare_streams(out, cpu, prompt)
+    equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 24 and ties <= 1
     cpu.close()
     model.close()
@@ -271,7 +367,7 @@ def test_f16_activation_model_runs_close(ctx, oracle):
     cfg.sigma_w = 0.0005   # keeps every intermediate inside f16 range with random weights
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=11, keep=True)
     model.slot_alloc()
-    cpu = oracle.CpuDecoder(ksm.oracle_cfg(cfg), T)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     toks = synth.token_ids(11, "tf", 6, cfg.vocab)
     for t in toks:
         model.forward(0, 1, [int(t)], True)

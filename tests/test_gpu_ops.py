@@ -249,6 +249,14 @@ def test_sdpa_four_slots_independent_lengths(ctx, oracle, n_q, n_kv):
     _attn_case(ctx, oracle, Eng(F32), 4, n_q, n_kv, 256, 4096, [1024, 4096, 77, 2048], [0, 0, 3, 100], 1.0 / 16.0, 0)
 
 
+@pytest.mark.parametrize("n_q,n_kv", [(8, 1), (8, 2)])
+def test_sdpa_context_16384_and_slot_mix(ctx, oracle, n_q, n_kv):
+    """The attention benchmark shape as written: contexts of 1024 / 4096 / 16384 positions, one slot at the
+    full 16384, and four slots of independent lengths {1024, 4096, 16384, 16384} in one launch."""
+    _attn_case(ctx, oracle, Eng(F32), 1, n_q, n_kv, 256, 16384, [16384], [0], 1.0 / 16.0, 0)
+    _attn_case(ctx, oracle, Eng(F32), 4, n_q, n_kv, 256, 16384, [1024, 4096, 16384, 16384], [0, 0, 0, 0], 1.0 / 16.0, 0)
+
+
 def test_sdpa_f16_and_hd128(ctx, oracle):
     _attn_case(ctx, oracle, Eng(F16), 2, 8, 2, 256, 512, [512, 200], [0, 0], 1.0 / 16.0, 8, act=F16)
     _attn_case(ctx, oracle, Eng(F32), 1, 4, 1, 128, 256, [250], [0], 0.1, 4)
@@ -259,7 +267,7 @@ def test_sdpa_hybrid_and_needle(ctx, oracle):
     'needle' check: K[0]=q, V[0]=1, rest 0 -> output 1 (check_mul_mm.rs:249-294)."""
     e = Eng(F32)
     n_q, hd = 8, 256
-    for tlen in (64, 512, 8192):
+    for tlen in (64, 512, 8192, 16384):
         k = np.zeros((tlen, hd), np.float32)
         v = np.zeros((tlen, hd), np.float32)
         k[0] = 1.0
