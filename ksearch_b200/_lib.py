@@ -94,6 +94,7 @@ SIGNATURES = {
     "ks_model_decode_token": (_i, [_vp, _i, _i, _vp, _vp]),
     "ks_model_generate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp]),
     "ks_model_debug_ptr": (_vp, [_vp, _i, _i]),
+    "ks_model_debug_set": (_i, [_vp, _i, _i, C.c_uint]),
     "ks_model_kv_ptr": (_vp, [_vp, _i, _i, _i]),
     "ks_model_kv_slot_bytes": (_sz, [_vp]),
 }

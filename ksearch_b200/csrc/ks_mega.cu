@@ -1,24 +1,36 @@
 // One persistent kernel for all layers of a decode token (single slot, f32 activations).
 //
 // The op order is forward_token's (crates/ksearch_gemma/src/gemma_prim.rs:923-1197) for dense,
-// KV-owning layers; what changes is WHERE the boundaries between ops are.  On B200 a token is a
-// chain of ~180 dependent steps, each a few hundred kilobytes to ten megabytes of weights, and a
-// kernel boundary costs more than most of those steps take.  Here one block per SM stays resident
-// for the whole token:
-//   * the weight stream never stops: every warp owns a ring of shared-memory stages fed by
-//     cp.async.bulk, and walks ONE item list for the whole token (all its row groups of all phases);
-//     the copies of the next phases are already in flight while the block waits at a barrier;
-//   * phases (qkv | attention | o-proj | gate-up | down, per layer) are separated by a grid barrier
-//     on one global counter; activations cross it through global memory (L2), read with ld.cg;
-//   * the norms are applied while x is staged; their weights are fetched BEFORE the barrier wait,
-//     because the acquire that ends the wait drops the SM's L1 and every later plain load of a
-//     constant would be a full round trip to L2;
-//   * for the same reason nothing on the critical path reads a descriptor from global memory: the
-//     five phase shapes and the per-layer pointers are copied to shared memory once;
-//   * attention: per-head RMS + RoPE + Q4_0 pack of the new K/V row, split-context online softmax
-//     and the merge of the splits (last arriving block) happen inside one phase.
-// Every spin (barrier, mbarrier) is bounded; on expiry the block raises the context's status word,
-// drains its copies and leaves, and the other blocks time out the same way.
+// KV-owning layers; what changes is WHERE the boundaries between ops are and HOW a result reaches
+// its consumers.  A token is a chain of ~175 dependent steps of a few hundred kilobytes to ten
+// megabytes of weights each; neither a kernel boundary nor a grid-wide barrier is affordable
+// between them.  One block per SM (16 warps) stays resident for the whole token:
+//   * Dataflow instead of barriers.  Every activation that crosses blocks (q/k/v, attention
+//     output, o-proj output, GeGLU output, down-proj output, attention split records) is written
+//     as a 64-bit word (f32 value, 32-bit tag) with one relaxed store, tag = token epoch + layer.
+//     A consumer polls the words it needs until their tags match.  Value and tag travel in one
+//     single-copy-atomic word, so no fence, no flag and no second round trip is needed: a hop
+//     between phases costs one store and one load through L2.  Buffers alternate by layer parity.
+//   * Rows are split evenly: block b owns the contiguous rows [b*R/grid, (b+1)*R/grid) (in pairs)
+//     of every matvec phase, so its weights are ONE contiguous byte range per matrix and phase.
+//   * The weight stream never stops: those ranges are cut into pieces that fit a slot of a
+//     block-wide shared-memory ring fed by cp.async.bulk (mbarrier completion).  The pieces of all
+//     phases and layers form one sequence; the last warp to finish with a slot refills it with the
+//     piece n_slots further down the sequence, so the next phases' (and layer's) weights arrive
+//     while the block computes or waits for its inputs.
+//   * Inside a phase an item is 4 rows x one column segment; items go to the 16 warps round-robin,
+//     partial sums meet in shared memory, thread f finishes row f.
+//   * x is staged once per phase and block as 24-bit block fixed point (three byte planes per
+//     32-element sub-block) so weight nibbles x x are exact dp4a integer sums.
+//   * The residual stream never leaves the block: every block applies the same residual-add + norm
+//     to the same inputs in the same order, so each thread keeps its elements in registers.
+//   * Attention: one block per (query head, context split); short contexts use one split (no
+//     merge hop), long ones merge the split records in the head's first block.
+// Every wait (tag poll, mbarrier) is bounded; on expiry the block raises the context's status
+// word and carries on without waiting any more, so the kernel always ends; blocks that see the
+// status word raised stop waiting too.
+#include <cstdlib>
+#include <cstring>
 #include <utility>
 #include <vector>
 
@@ -26,17 +38,22 @@
 
 namespace {
 
-enum { MG_MATVEC = 0, MG_GATE_UP = 1, MG_ATTN = 2 };
-enum { PH_QKV = 0, PH_ATTN = 1, PH_OPROJ = 2, PH_GATEUP = 3, PH_DOWN = 4, PH_PER_LAYER = 5 };
+enum { PH_QKV = 0, PH_OPROJ = 1, PH_GATEUP = 2, PH_DOWN = 3, PH_KINDS = 4 };
+enum { PF_QKV = 0, PF_ATTN = 1, PF_OPROJ = 2, PF_GATEUP = 3, PF_DOWN = 4, PF_PER_LAYER = 5 };
 
-struct MegaShape {          // one of the five phases of a layer; the same for every layer
-  int type;
-  int n_seg;                // matvec: 1 or 3 (q, k, v)
-  unsigned rows[3];
-  unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups (0 for attention)
-  unsigned cols, row_bytes, seg_blocks, n_cseg;
-  int oct;                  // 1: a block owns runs of 8 consecutive groups (32 rows = one sub-block of the next phase's x)
-  int split;                // gate-up only, 1: the gate rows and the up rows of a group are two items (rows too long for one slot)
+constexpr int MG_THREADS = 512, MG_NW = 16;
+constexpr int MG_MAXPIECE = 64;   // pieces of one layer owned by one block
+constexpr int MG_MAXROWS = 96;    // rows of one phase owned by one block
+constexpr int MG_MAXC = 8;        // column segments per row
+constexpr int MG_MAXSLOTS = 16;   // ring slots
+constexpr int MG_MAX_SPLITS = 16; // context splits per head
+
+struct MegaPhase {          // one matvec phase of a layer; the same for every layer
+  unsigned n_seg;           // matrices laid end to end in the phase's row space (qkv: 3, else 1)
+  unsigned mats;            // matrices multiplied per row (gate-up: 2, gate row i and up row i)
+  unsigned seg_start[4];    // first row of each matrix in the row space; [n_seg] = total rows
+  unsigned widx;            // MegaLayer::W index of the first matrix
+  unsigned cols, row_bytes, seg_blocks, n_cseg, piece_rows;
 };
 
 struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
@@ -45,27 +62,40 @@ struct MegaLayer {          // per-layer pointers, copied to shared memory when 
   uint8_t *kv_k, *kv_v;     // this slot's cache rows [max_seq, n_kv, hd] Q4_0
 };
 
+struct Piece {              // a run of consecutive rows of one matrix (two for gate-up): one ring slot
+  uint32_t src_off;         // byte offset of the first row inside its matrix
+  uint32_t out0;            // index of the first row in the phase's output vector
+  uint16_t nrows, row0;     // row0: index of the first row among the block's rows of the phase
+  uint16_t item0, n_items;  // items are numbered through the phase; item j belongs to warp j % 16
+  uint8_t kind, widx, pad[2];
+};
+struct PhInfo {
+  uint16_t p0, np, nrows, nitems;
+};
+
 struct MegaArgs {
-  const void* tables;       // MegaShape[5] then MegaLayer[n_layers], 16-byte aligned; copied to shared memory at start
+  const void* tables;       // MegaPhase[4] then MegaLayer[n_layers], 16-byte aligned; copied to shared memory at start
   unsigned tables_bytes;    // multiple of 16
   int n_layers;
-  int stages;               // ring slots per warp
-  unsigned slot_bytes;      // bytes per ring slot
+  int n_slots;              // ring slots
+  unsigned slot_bytes;      // bytes per ring slot (multiple of 128)
   unsigned x_bytes;         // staging area for x (also the attention scratch)
   unsigned n_q, n_kv, hd, n_splits;
+  unsigned split_from;      // contexts longer than this are split across blocks
   float eps, attn_scale;
   const float* rope;        // [max_seq, hd]
   const int* pos;           // [1]
-  float *x_a, *x_b;         // residual stream: layers read x_a / write x_b at the FFN, the reverse at the next qkv
-  float *yb, *q, *k, *v;
-  unsigned char *ox, *ffx;  // attention output and GeGLU output, written by their producers in the staged fixed-point layout
-  float* att_tmp;           // [n_q * n_splits * (hd + 2)]
-  float4* nsum;             // [grid] per-block sums of the last o-proj / down phase: (sum y^2, sum x*y*wp, sum (y*wp)^2, sum x^2)
-  unsigned* att_cnt;        // [n_q] arrival counters of the attention blocks, per head
-  unsigned* bar;            // [0] running barrier counter, [1] its value when the previous token ended
+  const float* x_in;        // the token's embedding (residual stream on entry)
+  float* resid_out;         // residual stream after the last layer's attention half
+  float* y_out;             // last layer's down-proj output (the head applies the final residual update and norm)
+  // tagged activation vectors, two of each (layer parity)
+  u64 *ll_yd0, *ll_yd1, *ll_yo0, *ll_yo1, *ll_qkv0, *ll_qkv1, *ll_ox0, *ll_ox1, *ll_ff0, *ll_ff1, *ll_rec0, *ll_rec1;
+  unsigned* epoch;          // tag base of this token; advanced by n_layers + 1 when the kernel ends
   unsigned* err;
-  long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released
-                            // (attention rows: 4..7 = q/k/v ready, positions done, folded, arrived)
+  unsigned poll_limit;      // polls of one wait before it gives up
+  unsigned test_stall;      // test hook: added to the tag the gate-up stage waits for (a tag nobody writes)
+  long long* prof;          // optional [2][n_layers][5][4] SM clocks of the first and last block: phase entered, x staged,
+                            // items done, rows stored
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -75,8 +105,8 @@ __device__ __forceinline__ void mb_init(uint32_t bar, unsigned count) {
 __device__ __forceinline__ void mb_expect(uint32_t bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mb_wait(uint32_t bar, unsigned parity) {
-  for (unsigned i = 0; i < (1u << 22); i++) {
+__device__ __forceinline__ bool mb_wait(uint32_t bar, unsigned parity, unsigned limit) {
+  for (unsigned i = 0; i < limit; i++) {
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -94,64 +124,69 @@ __device__ __forceinline__ void bulk_in(uint32_t dst, const void* src, unsigned 
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+
+// ---- tagged words ---------------------------------------------------------------------------------
+__device__ __forceinline__ void ll_store(u64* p, float v, unsigned tag) {
+  const u64 w = ((u64)tag << 32) | (u64)__float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ void ll_load2(const u64* p, u64& a, u64& b) {
+  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ u64 ll_load1(const u64* p) {
+  u64 a;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
   unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ float4 ldcg4(const float* p, unsigned c) { return __ldcg(reinterpret_cast<const float4*>(p) + c); }
+__device__ __forceinline__ unsigned ll_tag(u64 w) { return (unsigned)(w >> 32); }
+__device__ __forceinline__ float ll_val(u64 w) { return __uint_as_float((unsigned)w); }
 
-// Grid-wide barrier on a monotonically increasing counter, in two halves so that loads which do not
-// depend on other blocks can be issued in between.
-// wsum != nullptr: the eight warps left their partial norm sums there; thread 0 folds them (fixed order) into nsum[block].
-__device__ __forceinline__ void grid_arrive(unsigned* counter, const float4* wsum, float4* nsum) {
-  __syncthreads();  // every store of this block is issued
-  if (threadIdx.x == 0) {
-    if (wsum) {
-      float4 t = wsum[0];
-#pragma unroll
-      for (int w = 1; w < 8; w++) {
-        const float4 u = wsum[w];
-        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-      }
-      nsum[blockIdx.x] = t;
-    }
-    // release: everything this block wrote (ordered before by the barrier above) is visible to whoever
-    // acquires the counter; nothing comes back, so the thread does not wait for a round trip
-    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+struct Poll {
+  const unsigned* err;
+  unsigned limit;
+  bool gave_up;  // this thread stopped waiting (its own wait ran out, or it saw the status word raised)
+};
+// After a failed tag check: may the wait go on?
+__device__ __forceinline__ bool poll_again(Poll& pl, unsigned& it) {
+  if (pl.gave_up) return false;
+  if (++it >= pl.limit) {
+    atomicOr(const_cast<unsigned*>(pl.err), 2u);
+    pl.gave_up = true;
+    return false;
   }
+  if ((it & 127u) == 0u && ld_relaxed_u32(pl.err) != 0u) {
+    pl.gave_up = true;
+    return false;
+  }
+  return true;
 }
-// Returns false when the wait gave up.
-// Lane 0 of four warps polls: their loads drift apart in time, so the arrival of the last block is
-// seen sooner than one poller's round trip allows.  sflag: 0 = waiting, 1 = released, 2 = gave up.
-// Two flag words alternate between consecutive barriers, so a word is cleared a whole phase after its last reader.
-__device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, unsigned* err, int* flags, int parity) {
-  int* sflag = flags + parity;
-  if (threadIdx.x == 0) flags[parity ^ 1] = 0;
-  if ((threadIdx.x & 31) == 0 && threadIdx.x < 128) {
-    volatile int* vf = sflag;
-    int state = 0;
-    for (unsigned i = 0; i < (1u << 21); i++) {  // a second or two of polling at most
-      if ((int)(ld_acquire_u32(counter) - target) >= 0) {
-        state = 1;
-        break;
-      }
-      if (*vf == 1) {  // another poller saw it; take the acquire ourselves before reading what other blocks wrote
-        if ((int)(ld_acquire_u32(counter) - target) >= 0) {
-          state = 1;
-          break;
-        }
-      }
+// N chunks of 4 consecutive values (32 bytes, 16-byte aligned): every load is issued before any is checked.
+template <int N>
+__device__ __forceinline__ void ll_wait_chunks(const u64* base, const unsigned (&c)[N], const bool (&live)[N], unsigned tag,
+                                               float4 (&v)[N], Poll& pl) {
+  u64 w[N][4];
+#pragma unroll
+  for (int k = 0; k < N; k++)
+    if (live[k]) {
+      ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
+      ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
     }
-    if (state == 1) {
-      *vf = 1;
-    } else {
-      atomicOr(err, 2u);
-      *vf = 2;
+#pragma unroll
+  for (int k = 0; k < N; k++)
+    if (live[k]) {
+      unsigned it = 0;
+      while (!(ll_tag(w[k][0]) == tag && ll_tag(w[k][1]) == tag && ll_tag(w[k][2]) == tag && ll_tag(w[k][3]) == tag) &&
+             poll_again(pl, it)) {
+        ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
+        ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
+      }
+      v[k] = make_float4(ll_val(w[k][0]), ll_val(w[k][1]), ll_val(w[k][2]), ll_val(w[k][3]));
     }
-  }
-  __syncthreads();
-  return *sflag == 1;
 }
 
 // ---- x as 24-bit block fixed point, weights x x as byte dot products ----------------------------
@@ -165,8 +200,9 @@ __device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, un
 // Shared-memory layout: plane k (k = 0..2) at k * units * 80 bytes, unit u at u * 80 inside it (64
 // used: words 0..7 = elements 0..31 of the low-nibble sub-block, 8..15 = the high-nibble one; the pad
 // keeps the 8 lanes of a row on different banks), then units * 16 bytes of (sum_lo, sum_hi, s_lo, s_hi).
-constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
-constexpr unsigned MG_XU = 80;  // bytes per unit and plane
+constexpr int MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
+constexpr unsigned MG_XU = 80;        // bytes per unit and plane
+// Chunk c = elements 4c..4c+3; the 8 lanes that hold one sub-block's chunks are neighbours, all 32 lanes call.
 __device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, unsigned c, float4 v) {
   const unsigned e = c << 2;
   const unsigned u = e >> 6, hi = (e >> 5) & 1u, l = e & 31u;
@@ -193,47 +229,6 @@ __device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, 
     mt[2 + hi] = sc;
   }
 }
-// The same layout written to GLOBAL memory by a producer: the warp holds the 32 consecutive elements
-// e0 .. e0+31 of one sub-block, one per lane (e0 a multiple of 32).
-__device__ __forceinline__ void fx_store_subblock(unsigned char* dst, unsigned units, unsigned e0, float val, int lane) {
-  float s = val, am = fabsf(val);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    s += __shfl_xor_sync(0xffffffffu, s, o);
-    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-  }
-  const float inv = am > 0.0f ? __fdividef(8.0e6f, am) : 0.0f;
-  const float sc = am > 0.0f ? am * (1.0f / 8.0e6f) : 1.0f;
-  const int X = __float2int_rn(val * inv);
-  const unsigned u = e0 >> 6, hi = (e0 >> 5) & 1u;
-  const size_t plane = (size_t)units * MG_XU;
-  unsigned char* base = dst + (size_t)u * MG_XU + hi * 32u + (unsigned)lane;
-  base[0] = (unsigned char)(X & 0xFF);
-  base[plane] = (unsigned char)((X >> 8) & 0xFF);
-  base[2 * plane] = (unsigned char)((X >> 16) & 0xFF);
-  if (lane == 0) {
-    float* mt = reinterpret_cast<float*>(dst + 3 * plane + (size_t)u * 16u);
-    mt[hi] = s;
-    mt[2 + hi] = sc;
-  }
-}
-// Bring a vector a producer left in that layout into shared memory (units * 256 bytes; the pad words travel too).
-__device__ __forceinline__ void fx_copy_in(unsigned char* xs, const unsigned char* src, unsigned units) {
-  const unsigned n16 = units * 16u;  // 3 planes of 80 bytes + 16 bytes of sums and scales per unit
-  for (unsigned base = 0; base < n16; base += 6u * blockDim.x) {
-    uint4 v[6];
-#pragma unroll
-    for (int k = 0; k < 6; k++) {
-      const unsigned i = base + threadIdx.x + k * blockDim.x;
-      if (i < n16) v[k] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
-    }
-#pragma unroll
-    for (int k = 0; k < 6; k++) {
-      const unsigned i = base + threadIdx.x + k * blockDim.x;
-      if (i < n16) reinterpret_cast<uint4*>(xs)[i] = v[k];
-    }
-  }
-}
 __device__ __forceinline__ unsigned dp4a_uu(unsigned a, unsigned b, unsigned c) {
   unsigned d;
   asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -250,53 +245,77 @@ __device__ __forceinline__ float4 lds_f4o(uint32_t a) {
   asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFF));
   return v;
 }
-// One weight word (8 nibbles: elements j..j+3 of the low and of the high sub-block) against the
-// matching x words of the three planes.
-__device__ __forceinline__ void fx_word(uint32_t w, unsigned xl0, unsigned xl1, unsigned xl2, unsigned xh0, unsigned xh1,
-                                        unsigned xh2, unsigned (&alo)[2], int& alo2, unsigned (&ahi)[2], int& ahi2) {
-  const unsigned lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-  alo[0] = dp4a_uu(lo, xl0, alo[0]);
-  alo[1] = dp4a_uu(lo, xl1, alo[1]);
-  alo2 = dp4a_us(lo, xl2, alo2);
-  ahi[0] = dp4a_uu(hi, xh0, ahi[0]);
-  ahi[1] = dp4a_uu(hi, xh1, ahi[1]);
-  ahi2 = dp4a_us(hi, xh2, ahi2);
+// One byte plane of x for a unit (16 words: [0..7] low sub-block, [8..15] high sub-block) against the
+// masked nibbles of a row's unit: lo[i] / hi[i] hold elements 4i..4i+3 of the low / high sub-block.
+template <bool SIGNED>
+__device__ __forceinline__ void fx_plane(const uint32_t (&lo)[8], const uint32_t (&hi)[8], const uint4 x0, const uint4 x1,
+                                         const uint4 x2, const uint4 x3, int& alo, int& ahi) {
+  if (SIGNED) {
+    alo = dp4a_us(lo[0], x0.x, alo); alo = dp4a_us(lo[1], x0.y, alo); alo = dp4a_us(lo[2], x0.z, alo); alo = dp4a_us(lo[3], x0.w, alo);
+    alo = dp4a_us(lo[4], x1.x, alo); alo = dp4a_us(lo[5], x1.y, alo); alo = dp4a_us(lo[6], x1.z, alo); alo = dp4a_us(lo[7], x1.w, alo);
+    ahi = dp4a_us(hi[0], x2.x, ahi); ahi = dp4a_us(hi[1], x2.y, ahi); ahi = dp4a_us(hi[2], x2.z, ahi); ahi = dp4a_us(hi[3], x2.w, ahi);
+    ahi = dp4a_us(hi[4], x3.x, ahi); ahi = dp4a_us(hi[5], x3.y, ahi); ahi = dp4a_us(hi[6], x3.z, ahi); ahi = dp4a_us(hi[7], x3.w, ahi);
+  } else {
+    unsigned a = (unsigned)alo, h = (unsigned)ahi;
+    a = dp4a_uu(lo[0], x0.x, a); a = dp4a_uu(lo[1], x0.y, a); a = dp4a_uu(lo[2], x0.z, a); a = dp4a_uu(lo[3], x0.w, a);
+    a = dp4a_uu(lo[4], x1.x, a); a = dp4a_uu(lo[5], x1.y, a); a = dp4a_uu(lo[6], x1.z, a); a = dp4a_uu(lo[7], x1.w, a);
+    h = dp4a_uu(hi[0], x2.x, h); h = dp4a_uu(hi[1], x2.y, h); h = dp4a_uu(hi[2], x2.z, h); h = dp4a_uu(hi[3], x2.w, h);
+    h = dp4a_uu(hi[4], x3.x, h); h = dp4a_uu(hi[5], x3.y, h); h = dp4a_uu(hi[6], x3.z, h); h = dp4a_uu(hi[7], x3.w, h);
+    alo = (int)a;
+    ahi = (int)h;
+  }
 }
-// Multiply-accumulate one item against the fixed-point x: MATS row slots per lane.
+// Multiply-accumulate one item against the fixed-point x.  base: shared address of the item's first
+// row at its column segment; rows are row_bytes apart; the second matrix (MATS == 2) sits mat2_off on.
+// The masked nibbles of a unit stay in registers while the three planes of x pass by.
 template <int MATS>
-__device__ __forceinline__ void mg_item_compute_fx(uint32_t slot_addr, uint32_t xs_s, unsigned units, unsigned seg_blocks,
-                                                   unsigned cs, int cl, int rl, float (&yacc)[2]) {
+__device__ __forceinline__ void mg_item_compute_fx(uint32_t base, uint32_t row_bytes, uint32_t mat2_off, uint32_t xs_s,
+                                                   unsigned units, unsigned seg_units, unsigned cs, int cl, int rl,
+                                                   float (&yacc)[2]) {
   const int g = cl & 3;
-  const unsigned seg_bytes = seg_blocks * KS_Q4K_BLOCK_BYTES, seg_units = seg_blocks * 4, upl = seg_units / MG_LPR;
+  const unsigned upl = seg_units / MG_LPR;
   const uint32_t plane = units * MG_XU;
-  uint32_t waddr = slot_addr + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
+  uint32_t waddr = base + (uint32_t)rl * row_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
   uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * MG_XU;
   uint32_t maddr = xs_s + 3u * plane + (cs * seg_units + (unsigned)cl) * 16u;
   for (unsigned it = 0; it < upl; it++) {
-    const float4 mt = lds_f4o<0>(maddr);
-    // 16 words per plane: [0..7] low sub-block, [8..15] high sub-block
-    const uint4 a0 = lds_u4o<0>(xaddr), a1 = lds_u4o<16>(xaddr), a2 = lds_u4o<32>(xaddr), a3 = lds_u4o<48>(xaddr);
-    const uint4 b0 = lds_u4o<0>(xaddr + plane), b1 = lds_u4o<16>(xaddr + plane), b2 = lds_u4o<32>(xaddr + plane),
-                b3 = lds_u4o<48>(xaddr + plane);
-    const uint4 c0 = lds_u4o<0>(xaddr + 2 * plane), c1 = lds_u4o<16>(xaddr + 2 * plane), c2 = lds_u4o<32>(xaddr + 2 * plane),
-                c3 = lds_u4o<48>(xaddr + 2 * plane);
+    uint32_t lo[MATS][8], hi[MATS][8];
+    int a0l[MATS], a0h[MATS], a1l[MATS], a1h[MATS], a2l[MATS], a2h[MATS];
 #pragma unroll
     for (int r = 0; r < MATS; r++) {
-      const uint32_t wa = waddr + (uint32_t)(r * MG_RL) * seg_bytes;
+      const uint32_t wa = waddr + (uint32_t)r * mat2_off;
       const uint4 q0 = lds_u4o<16>(wa), q1 = lds_u4o<32>(wa);
-      const uint4 hdr = lds_u4o<0>(wa - (uint32_t)g * 32u);
-      unsigned alo[2] = {0u, 0u}, ahi[2] = {0u, 0u};
-      int alo2 = 0, ahi2 = 0;
-      fx_word(q0.x, a0.x, b0.x, c0.x, a2.x, b2.x, c2.x, alo, alo2, ahi, ahi2);
-      fx_word(q0.y, a0.y, b0.y, c0.y, a2.y, b2.y, c2.y, alo, alo2, ahi, ahi2);
-      fx_word(q0.z, a0.z, b0.z, c0.z, a2.z, b2.z, c2.z, alo, alo2, ahi, ahi2);
-      fx_word(q0.w, a0.w, b0.w, c0.w, a2.w, b2.w, c2.w, alo, alo2, ahi, ahi2);
-      fx_word(q1.x, a1.x, b1.x, c1.x, a3.x, b3.x, c3.x, alo, alo2, ahi, ahi2);
-      fx_word(q1.y, a1.y, b1.y, c1.y, a3.y, b3.y, c3.y, alo, alo2, ahi, ahi2);
-      fx_word(q1.z, a1.z, b1.z, c1.z, a3.z, b3.z, c3.z, alo, alo2, ahi, ahi2);
-      fx_word(q1.w, a1.w, b1.w, c1.w, a3.w, b3.w, c3.w, alo, alo2, ahi, ahi2);
-      const float flo = fmaf((float)alo2, 65536.0f, fmaf((float)alo[1], 256.0f, (float)alo[0])) * mt.z;
-      const float fhi = fmaf((float)ahi2, 65536.0f, fmaf((float)ahi[1], 256.0f, (float)ahi[0])) * mt.w;
+      const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        lo[r][i] = q[i] & 0x0F0F0F0Fu;
+        hi[r][i] = (q[i] >> 4) & 0x0F0F0F0Fu;
+      }
+      a0l[r] = a0h[r] = a1l[r] = a1h[r] = a2l[r] = a2h[r] = 0;
+    }
+    {
+      const uint4 x0 = lds_u4o<0>(xaddr), x1 = lds_u4o<16>(xaddr), x2 = lds_u4o<32>(xaddr), x3 = lds_u4o<48>(xaddr);
+#pragma unroll
+      for (int r = 0; r < MATS; r++) fx_plane<false>(lo[r], hi[r], x0, x1, x2, x3, a0l[r], a0h[r]);
+    }
+    {
+      const uint32_t xa = xaddr + plane;
+      const uint4 x0 = lds_u4o<0>(xa), x1 = lds_u4o<16>(xa), x2 = lds_u4o<32>(xa), x3 = lds_u4o<48>(xa);
+#pragma unroll
+      for (int r = 0; r < MATS; r++) fx_plane<false>(lo[r], hi[r], x0, x1, x2, x3, a1l[r], a1h[r]);
+    }
+    {
+      const uint32_t xa = xaddr + 2u * plane;
+      const uint4 x0 = lds_u4o<0>(xa), x1 = lds_u4o<16>(xa), x2 = lds_u4o<32>(xa), x3 = lds_u4o<48>(xa);
+#pragma unroll
+      for (int r = 0; r < MATS; r++) fx_plane<true>(lo[r], hi[r], x0, x1, x2, x3, a2l[r], a2h[r]);
+    }
+    const float4 mt = lds_f4o<0>(maddr);
+#pragma unroll
+    for (int r = 0; r < MATS; r++) {
+      const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)r * mat2_off - (uint32_t)g * 32u);
+      const float flo = fmaf((float)a2l[r], 65536.0f, fmaf((float)(unsigned)a1l[r], 256.0f, (float)(unsigned)a0l[r])) * mt.z;
+      const float fhi = fmaf((float)a2h[r], 65536.0f, fmaf((float)(unsigned)a1h[r], 256.0f, (float)(unsigned)a0h[r])) * mt.w;
       yacc[r] = q4k_apply_scales(hdr, g, flo, fhi, mt.x, mt.y, yacc[r]);
     }
     waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
@@ -305,326 +324,173 @@ __device__ __forceinline__ void mg_item_compute_fx(uint32_t slot_addr, uint32_t 
   }
 }
 
-
-// ---- staging of x (with the fused norm prologues), reads through L2 ---------------------------
-// Norm weights of the next matvec phase, fetched into registers before the barrier wait.
-template <int PC>
-struct NormPre {  // PC chunks of 4 elements per thread: cols <= PC * 4 * blockDim
-  float4 w[PC], wp[PC];
-};
-template <int PC>
-__device__ __forceinline__ void mg_prefetch_norm(NormPre<PC>& n, int mode, const float* w, const float* wp, unsigned cols) {
-  const unsigned nchunk = cols >> 2;
-  if (mode == KS_PRO_NONE) return;
-#pragma unroll
-  for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * blockDim.x;
-    if (c < nchunk) {
-      n.w[k] = reinterpret_cast<const float4*>(w)[c];
-      if (mode == KS_PRO_ADD_NORM) n.wp[k] = reinterpret_cast<const float4*>(wp)[c];
-    }
-  }
-}
-
-constexpr int MG_XMAX = 8;  // plain staging keeps up to 8 chunks per thread in flight (cols <= 8192), loops beyond
-
-// mode NONE: x' = x.  NORM: x' = rms(x)*w.  ADD_NORM: r = x + rms(y)*wp (block 0 stores r to out_x); x' = rms(r)*w.
-template <int PC>
-__device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mode, unsigned cols, const float* x,
-                                           const float* y, float* out_x, float eps, const NormPre<PC>& n) {
-  const unsigned units = cols >> 6, nchunk = cols >> 2;
-  if (mode == KS_PRO_NONE) {
-    for (unsigned base = 0; base < nchunk; base += MG_XMAX * blockDim.x) {
-      float4 v[MG_XMAX];
-#pragma unroll
-      for (int k = 0; k < MG_XMAX; k++) {
-        const unsigned c = base + threadIdx.x + k * blockDim.x;
-        if (c < nchunk) v[k] = ldcg4(x, c);
-      }
-#pragma unroll
-      for (int k = 0; k < MG_XMAX; k++) {
-        const unsigned c = base + threadIdx.x + k * blockDim.x;
-        if (c < nchunk) fx_put_chunk(xs, units, c, v[k]);
-      }
-    }
-    return;
-  }
-  const float invn = 1.0f / (float)cols;
-  float4 v[PC], yv[PC];
-  float ss = 0.0f;
-  if (mode == KS_PRO_ADD_NORM) {
-#pragma unroll
-    for (int k = 0; k < PC; k++) {
-      const unsigned c = threadIdx.x + k * blockDim.x;
-      if (c < nchunk) {
-        yv[k] = ldcg4(y, c);
-        v[k] = ldcg4(x, c);
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < PC; k++) {
-      const unsigned c = threadIdx.x + k * blockDim.x;
-      if (c < nchunk) {
-        ss = fmaf(yv[k].x, yv[k].x, ss); ss = fmaf(yv[k].y, yv[k].y, ss);
-        ss = fmaf(yv[k].z, yv[k].z, ss); ss = fmaf(yv[k].w, yv[k].w, ss);
-      }
-    }
-    ss = block_sum_f(ss, red);
-    const float inv = 1.0f / sqrtf(ss * invn + eps);
-    ss = 0.0f;
-#pragma unroll
-    for (int k = 0; k < PC; k++) {
-      const unsigned c = threadIdx.x + k * blockDim.x;
-      if (c < nchunk) {
-        const float4 p4 = n.wp[k];
-        float4 r = v[k];
-        r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
-        r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
-        r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
-        r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
-        if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
-        v[k] = r;
-      }
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < PC; k++) {
-      const unsigned c = threadIdx.x + k * blockDim.x;
-      if (c < nchunk) v[k] = ldcg4(x, c);
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * blockDim.x;
-    if (c < nchunk) {
-      ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
-      ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
-    }
-  }
-  ss = block_sum_f(ss, red);
-  const float inv2 = 1.0f / sqrtf(ss * invn + eps);
-#pragma unroll
-  for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * blockDim.x;
-    if (c < nchunk) {
-      const float4 w4 = n.w[k];
-      float4 r;
-      r.x = __fmul_rn(__fmul_rn(v[k].x, inv2), w4.x);
-      r.y = __fmul_rn(__fmul_rn(v[k].y, inv2), w4.y);
-      r.z = __fmul_rn(__fmul_rn(v[k].z, inv2), w4.z);
-      r.w = __fmul_rn(__fmul_rn(v[k].w, inv2), w4.w);
-      fx_put_chunk(xs, units, c, r);
-    }
-  }
-}
-
-// ADD_NORM without any block-wide reduction: the blocks that produced y left the four sums that both
-// norms need (K:539 expands to  sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2,  r = x + inv y wp).
-template <int PC>
-__device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned cols, const float* x, const float* y, float* out_x,
-                                                 float eps, const NormPre<PC>& n, const float4* nsum, unsigned nblocks) {
-  const unsigned units = cols >> 6, nchunk = cols >> 2;
-  const int lane = threadIdx.x & 31;
-  float4 v[PC], yv[PC], ps[8];
-#pragma unroll
-  for (int j = 0; j < 8; j++) {
-    const unsigned i = (unsigned)lane + 32u * j;
-    ps[j] = i < nblocks ? __ldcg(nsum + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-#pragma unroll
-  for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * blockDim.x;
-    if (c < nchunk) {
-      yv[k] = ldcg4(y, c);
-      v[k] = ldcg4(x, c);
-    }
-  }
-  float4 t = ps[0];
-#pragma unroll
-  for (int j = 1; j < 8; j++) {
-    t.x += ps[j].x; t.y += ps[j].y; t.z += ps[j].z; t.w += ps[j].w;
-  }
+// ---- staging of x ---------------------------------------------------------------------------------
+// Sum four values over the block: every thread gets the same totals (fixed order).  red: 16 float4.
+__device__ __forceinline__ float4 block_sum4(float4 v, float4* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
-    t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
-    t.z += __shfl_xor_sync(0xffffffffu, t.z, o);
-    t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, o);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
+    v.z += __shfl_xor_sync(0xffffffffu, v.z, o);
+    v.w += __shfl_xor_sync(0xffffffffu, v.w, o);
   }
-  const float invn = 1.0f / (float)cols;
-  const float inv = __frsqrt_rn(t.x * invn + eps);
-  const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
-  const float inv2 = __frsqrt_rn(fmaxf(rr, 0.0f) * invn + eps);
+  __syncthreads();  // the previous use of red is over
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float4 t = red[0];
+#pragma unroll
+  for (int w = 1; w < MG_NW; w++) {
+    const float4 u = red[w];
+    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+  }
+  return t;
+}
+
+// The hidden vector of a phase that starts with a norm.  Thread t owns chunks t and t + 512 (4 elements
+// each) of the residual stream in registers (xr), for the whole token.
+//   add == false (first layer):  x' = rms(x) * w
+//   add == true:  r = x + rms(y) * wp (K:539; both RMS factors come from ONE block-wide sum:
+//                 sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2);  x' = rms(r) * w;  xr = r.
+template <int PC>
+__device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, bool add, unsigned cols, float4 (&xr)[PC],
+                                                const u64* ysrc, unsigned tag, const float* w, const float* wp, float eps,
+                                                float* resid_out, Poll& pl) {
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
+  unsigned c[PC];
+  bool live[PC];
+  float4 wv[PC], wpv[PC], yv[PC];
 #pragma unroll
   for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * blockDim.x;
-    if (c < nchunk) {
-      const float4 p4 = n.wp[k], w4 = n.w[k];
-      float4 r = v[k];
-      r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
-      r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
-      r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
-      r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
-      if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
+    c[k] = threadIdx.x + k * MG_THREADS;
+    live[k] = c[k] < nchunk;
+    if (live[k]) {  // constants of the model: in flight while the inputs are awaited
+      wv[k] = reinterpret_cast<const float4*>(w)[c[k]];
+      if (add) wpv[k] = reinterpret_cast<const float4*>(wp)[c[k]];
+    }
+  }
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (add) {
+    ll_wait_chunks<PC>(ysrc, c, live, tag, yv, pl);
+#pragma unroll
+    for (int k = 0; k < PC; k++)
+      if (live[k]) {
+        const float4 x = xr[k], y = yv[k], p = wpv[k];
+        const float t0 = y.x * p.x, t1 = y.y * p.y, t2 = y.z * p.z, t3 = y.w * p.w;
+        s.x = fmaf(y.x, y.x, s.x); s.x = fmaf(y.y, y.y, s.x); s.x = fmaf(y.z, y.z, s.x); s.x = fmaf(y.w, y.w, s.x);
+        s.y = fmaf(x.x, t0, s.y); s.y = fmaf(x.y, t1, s.y); s.y = fmaf(x.z, t2, s.y); s.y = fmaf(x.w, t3, s.y);
+        s.z = fmaf(t0, t0, s.z); s.z = fmaf(t1, t1, s.z); s.z = fmaf(t2, t2, s.z); s.z = fmaf(t3, t3, s.z);
+        s.w = fmaf(x.x, x.x, s.w); s.w = fmaf(x.y, x.y, s.w); s.w = fmaf(x.z, x.z, s.w); s.w = fmaf(x.w, x.w, s.w);
+      }
+  } else {
+#pragma unroll
+    for (int k = 0; k < PC; k++)
+      if (live[k]) {
+        const float4 x = xr[k];
+        s.w = fmaf(x.x, x.x, s.w); s.w = fmaf(x.y, x.y, s.w); s.w = fmaf(x.z, x.z, s.w); s.w = fmaf(x.w, x.w, s.w);
+      }
+  }
+  const float4 t = block_sum4(s, red);
+  const float invn = 1.0f / (float)cols;
+  float inv = 0.0f, inv2;
+  if (add) {
+    inv = __frsqrt_rn(t.x * invn + eps);
+    const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
+    inv2 = __frsqrt_rn(fmaxf(rr, 0.0f) * invn + eps);
+  } else {
+    inv2 = 1.0f / sqrtf(t.w * invn + eps);
+  }
+#pragma unroll
+  for (int k = 0; k < PC; k++)
+    if (live[k]) {  // nchunk is a multiple of 64: whole warps take this branch together
+      float4 r = xr[k];
+      if (add) {
+        const float4 y = yv[k], p = wpv[k];
+        r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(y.x, inv), p.x));
+        r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(y.y, inv), p.y));
+        r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(y.z, inv), p.z));
+        r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(y.w, inv), p.w));
+        xr[k] = r;
+        if (resid_out) reinterpret_cast<float4*>(resid_out)[c[k]] = r;
+      }
+      const float4 w4 = wv[k];
       float4 q;
       q.x = __fmul_rn(__fmul_rn(r.x, inv2), w4.x);
       q.y = __fmul_rn(__fmul_rn(r.y, inv2), w4.y);
       q.z = __fmul_rn(__fmul_rn(r.z, inv2), w4.z);
       q.w = __fmul_rn(__fmul_rn(r.w, inv2), w4.w);
-      fx_put_chunk(xs, units, c, q);
+      fx_put_chunk(xs, units, c[k], q);
     }
-  }
 }
 
-// ---- the per-warp item list of a whole token -----------------------------------------------------
-// Item = (phase, row group, column segment).
-
-// The items of a warp repeat layer after layer (same shapes, other pointers), so the walk over the
-// shapes is done once per kernel: each warp records its items of ONE layer, in phase order, and the
-// issue and consume positions are (layer, entry) pairs.
-constexpr int MG_MAX_ENT = 16;
-struct ItemEnt {
-  uint32_t src_off;  // byte offset of the first copy inside its weight matrix
-  uint32_t pslot;    // index of this item among the block's items of the phase (where its partial sums go)
-  uint16_t seg16;    // bytes of one row segment / 16
-  uint8_t kind, seg, cs, valid;
-  uint8_t widx;      // MegaLayer::W index of the first matrix
-  uint8_t flags;     // bit 0: two matrices (gate, up) in one item; bit 1: whole rows (one copy per matrix);
-                     // bit 2: this item is the second matrix (up) of a split gate-up group
-};
-struct ItemPos {
-  int layer, e;
-};
-__device__ __forceinline__ void pos_next(ItemPos& c, int n_ent) {
-  if (++c.e >= n_ent) {
-    c.e = 0;
-    c.layer++;
-  }
-}
-// Groups of a phase go to blocks round-robin (block c owns groups c, c + grid, ...); the block's items
-// -- its groups x the column segments -- go to its warps round-robin.  A row's column segments may
-// therefore be multiplied by different warps; the partial sums meet in shared memory (slot pslot).
-constexpr int MG_MAX_P = 64;  // items of one block in one phase
-__device__ __forceinline__ unsigned block_groups(const MegaShape& sh) {
-  const unsigned total = sh.type == MG_ATTN ? 0u : sh.grp_start[sh.n_seg];
-  if (sh.oct) {
-    const unsigned octs = (total + 7u) / 8u;
-    return octs > blockIdx.x ? (octs - blockIdx.x + gridDim.x - 1) / gridDim.x * 8u : 0u;
-  }
-  return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-}
-// global group index of this block's k-th group
-__device__ __forceinline__ unsigned block_group_id(const MegaShape& sh, unsigned k) {
-  return sh.oct ? (blockIdx.x + (k >> 3) * gridDim.x) * 8u + (k & 7u) : blockIdx.x + k * gridDim.x;
-}
-// lane 0 of each warp fills its table; returns the entry count (0 when the warp owns nothing, -1 on overflow)
-__device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes, int warp) {
-  int n = 0;
-  for (int kind = 0; kind < PH_PER_LAYER; kind++) {
-    const MegaShape& sh = shapes[kind];
-    const unsigned C = sh.n_cseg, n_slots = block_groups(sh) * C;
-    if (n_slots > (unsigned)MG_MAX_P) return -1;
-    const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
-    const bool split = sh.type == MG_GATE_UP && sh.split;
-    const int mats = (sh.type == MG_GATE_UP && !split) ? 2 : 1;
-    const int w0 = kind == PH_QKV ? 0 : kind == PH_OPROJ ? 3 : kind == PH_GATEUP ? 4 : 6;
-    const unsigned n_items = split ? n_slots * 2u : n_slots;
-    for (unsigned jj = (unsigned)warp; jj < n_items; jj += 8u) {
-      if (n >= MG_MAX_ENT) return -1;
-      const unsigned j = split ? jj >> 1 : jj, second = split ? jj & 1u : 0u;
-      const unsigned k = j / C, cs = j - k * C;
-      const unsigned g = block_group_id(sh, k);
-      if (g >= sh.grp_start[sh.n_seg]) continue;
-      int seg = 0;
-      if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
-      if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
-      const unsigned row0 = (g - sh.grp_start[seg]) * MG_RL;
-      ItemEnt e;
-      e.src_off = row0 * sh.row_bytes + cs * seg_bytes;
-      e.pslot = j;
-      e.seg16 = (uint16_t)(seg_bytes / 16u);
-      e.kind = (uint8_t)kind;
-      e.seg = (uint8_t)seg;
-      e.cs = (uint8_t)cs;
-      e.valid = (uint8_t)min((unsigned)MG_RL, sh.rows[seg] - row0);
-      e.widx = (uint8_t)(w0 + (mats == 2 ? 0 : split ? second : seg));
-      e.flags = (uint8_t)((mats == 2 ? 1 : 0) | (C == 1 ? 2 : 0) | (second ? 4 : 0));
-      ent[n++] = e;
+// A vector other blocks produced (attention output, GeGLU output), staged as it is.
+__device__ __forceinline__ void mg_stage_plain(unsigned char* xs, unsigned cols, const u64* src, unsigned tag, Poll& pl) {
+  constexpr int XC = 4;
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
+  for (unsigned base = 0; base < nchunk; base += XC * MG_THREADS) {
+    unsigned c[XC];
+    bool live[XC];
+    float4 v[XC];
+#pragma unroll
+    for (int k = 0; k < XC; k++) {
+      c[k] = base + threadIdx.x + k * MG_THREADS;
+      live[k] = c[k] < nchunk;
     }
-  }
-  return n;
-}
-
-// Start the copies of one item into a ring slot (all lanes call).
-__device__ __forceinline__ void mg_issue_ent(const ItemEnt& e, const MegaLayer& L, unsigned row_bytes, uint32_t slot_addr,
-                                             uint32_t bar, int lane) {
-  const unsigned seg_bytes = (unsigned)e.seg16 * 16u, valid = e.valid;
-  const int mats = (e.flags & 1) ? 2 : 1;
-  if (lane == 0) mb_expect(bar, valid * mats * seg_bytes);
-  if (e.flags & 2) {
-    if (lane < mats)
-      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, L.W[e.widx + lane] + e.src_off, valid * seg_bytes, bar);
-  } else if (lane < MG_RL * mats) {
-    const int m = lane / MG_RL, rr = lane % MG_RL;
-    if ((unsigned)rr < valid)
-      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, L.W[e.widx + m] + e.src_off + (size_t)rr * row_bytes, seg_bytes, bar);
+    ll_wait_chunks<XC>(src, c, live, tag, v, pl);
+#pragma unroll
+    for (int k = 0; k < XC; k++)
+      if (live[k]) fx_put_chunk(xs, units, c[k], v[k]);
   }
 }
 
-// Multiply-accumulate one item: MATS row slots per lane, units of this lane in the segment.
-template <int MATS>
-__device__ __forceinline__ void mg_item_compute(uint32_t slot_addr, uint32_t xs_s, unsigned units, unsigned seg_blocks,
-                                                unsigned cs, int cl, int rl, float (&yacc)[2]) {
-  const int g = cl & 3;
-  const unsigned seg_bytes = seg_blocks * KS_Q4K_BLOCK_BYTES, seg_units = seg_blocks * 4, upl = seg_units / MG_LPR;
-  uint32_t waddr = slot_addr + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
-  uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * (Q4K_XS * 4u);
-  uint32_t saddr = xs_s + units * (Q4K_XS * 4u) + (cs * seg_units + (unsigned)cl) * 8u;
-  for (unsigned it = 0; it < upl; it++) {
-    const float2 sx = lds_f2a(saddr);
-    u64 acc[MATS][2];
-#pragma unroll
-    for (int r = 0; r < MATS; r++) acc[r][0] = acc[r][1] = 0ull;
-    {
-      u64 xf[16];
-      lds_p2o<0>(xaddr, xf[0], xf[1]);     lds_p2o<16>(xaddr, xf[2], xf[3]);
-      lds_p2o<32>(xaddr, xf[4], xf[5]);    lds_p2o<48>(xaddr, xf[6], xf[7]);
-      lds_p2o<64>(xaddr, xf[8], xf[9]);    lds_p2o<80>(xaddr, xf[10], xf[11]);
-      lds_p2o<96>(xaddr, xf[12], xf[13]);  lds_p2o<112>(xaddr, xf[14], xf[15]);
-#pragma unroll
-      for (int r = 0; r < MATS; r++) {
-        const uint4 q = lds_u4o<16>(waddr + (uint32_t)(r * MG_RL) * seg_bytes);
-        q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
-        q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
-        q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
-        q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
+// ---- pieces -----------------------------------------------------------------------------------------
+// Rows [lo, hi) of a phase's row space owned by this block: an even split in pairs of rows.
+__device__ __forceinline__ void block_rows(const MegaPhase& ph, unsigned& lo, unsigned& hi) {
+  const unsigned half = ph.seg_start[ph.n_seg] >> 1;
+  lo = (unsigned)(((unsigned long long)blockIdx.x * half) / gridDim.x) * 2u;
+  hi = (unsigned)(((unsigned long long)(blockIdx.x + 1) * half) / gridDim.x) * 2u;
+}
+// Thread 0 lists this block's pieces of one layer, in the order they are consumed.  Returns false when a table overflows.
+__device__ __forceinline__ bool build_pieces(Piece* pieces, PhInfo* info, const MegaPhase* phases) {
+  unsigned np = 0;
+  for (int kind = 0; kind < PH_KINDS; kind++) {
+    const MegaPhase& ph = phases[kind];
+    unsigned lo, hi, rows = 0, items = 0;
+    block_rows(ph, lo, hi);
+    info[kind].p0 = (uint16_t)np;
+    for (unsigned s = 0; s < ph.n_seg; s++) {
+      const unsigned a = max(lo, ph.seg_start[s]), b = min(hi, ph.seg_start[s + 1]);
+      for (unsigned r = a; r < b; r += ph.piece_rows) {
+        if (np >= (unsigned)MG_MAXPIECE) return false;
+        const unsigned n = min(ph.piece_rows, b - r);
+        Piece p;
+        p.src_off = (r - ph.seg_start[s]) * ph.row_bytes;
+        p.out0 = r;
+        p.nrows = (uint16_t)n;
+        p.row0 = (uint16_t)rows;
+        p.item0 = (uint16_t)items;
+        p.n_items = (uint16_t)(((n + 3u) / 4u) * ph.n_cseg);
+        p.kind = (uint8_t)kind;
+        p.widx = (uint8_t)(ph.widx + s);
+        p.pad[0] = p.pad[1] = 0;
+        pieces[np++] = p;
+        rows += n;
+        items += p.n_items;
       }
     }
-    {
-      u64 xf[16];
-      lds_p2o<128>(xaddr, xf[0], xf[1]);    lds_p2o<144>(xaddr, xf[2], xf[3]);
-      lds_p2o<160>(xaddr, xf[4], xf[5]);    lds_p2o<176>(xaddr, xf[6], xf[7]);
-      lds_p2o<192>(xaddr, xf[8], xf[9]);    lds_p2o<208>(xaddr, xf[10], xf[11]);
-      lds_p2o<224>(xaddr, xf[12], xf[13]);  lds_p2o<240>(xaddr, xf[14], xf[15]);
-#pragma unroll
-      for (int r = 0; r < MATS; r++) {
-        const uint4 q = lds_u4o<32>(waddr + (uint32_t)(r * MG_RL) * seg_bytes);
-        q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
-        q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
-        q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
-        q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < MATS; r++) {
-      const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)(r * MG_RL) * seg_bytes - (uint32_t)g * 32u);
-      const float2 a01 = unpack2(padd2(acc[r][0], acc[r][1]));
-      yacc[r] = q4k_apply_scales(hdr, g, a01.x, a01.y, sx.x, sx.y, yacc[r]);
-    }
-    waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
-    xaddr += MG_LPR * Q4K_XS * 4u;
-    saddr += MG_LPR * 8u;
+    if (rows > (unsigned)MG_MAXROWS) return false;
+    info[kind].np = (uint16_t)(np - info[kind].p0);
+    info[kind].nrows = (uint16_t)rows;
+    info[kind].nitems = (uint16_t)items;
   }
+  return true;
+}
+// Start the copies of one piece into a ring slot (one thread).
+__device__ __forceinline__ void issue_piece(const Piece& p, const MegaPhase& ph, const MegaLayer& L, uint32_t slot_addr, uint32_t bar) {
+  const unsigned bytes = (unsigned)p.nrows * ph.row_bytes;
+  mb_expect(bar, bytes * ph.mats);
+  bulk_in(slot_addr, L.W[p.widx] + p.src_off, bytes, bar);
+  if (ph.mats == 2) bulk_in(slot_addr + (((unsigned)p.nrows + 3u) & ~3u) * ph.row_bytes, L.W[p.widx + 1] + p.src_off, bytes, bar);
 }
 
 // ---- attention phase ------------------------------------------------------------------------------
@@ -687,32 +553,33 @@ __device__ __forceinline__ int mg_lane_dim(int lane, int j) {
   return j < BPL ? base + j : base + 16 + (j - BPL);
 }
 
-constexpr int MG_MAX_SPLITS = 16;  // context splits per head (the final merge keeps one record per split in registers)
-
 // Shared memory the attention phase needs (it reuses the x staging area).
 __host__ __device__ inline unsigned mg_att_bytes(unsigned hd) {
-  return 8u * (hd + 2u) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 32u;
+  return (unsigned)MG_NW * (hd + 2u) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 8u * MG_MAX_SPLITS + 32u;
 }
 
-// Splits in use for a context of tlen positions: one row per warp (8 per block) until every split is
-// in use, more rows per warp beyond that.
-__host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits) {
-  unsigned ns = (tlen + 7u) / 8u;
+// Splits in use for a context of tlen positions.  A split costs a hop through L2 (records out, merge
+// in the head's first block), which is worth it only once a single block's 16 warps would each walk
+// many positions.
+__host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits, unsigned split_from) {
+  if (tlen <= split_from) return 1u;
+  unsigned ns = (tlen + 31u) / 32u;
   return ns < 1u ? 1u : ns > max_splits ? max_splits : ns;
 }
 
-// One block per (query head, context split): the work of a short context is tiny, so it is spread
-// as widely as the grid allows and every serial step stays short.
-//   1. every warp builds the roped, normed, scaled q of the head in registers (no exchange needed);
-//      in the blocks of the split that holds the newest position, warps 0.. pack the new K row and
-//      warps 4.. the new V row to Q4_0 in shared memory (lower.rs:4231-4702), block pairs (b, b+NB/2)
-//      per warp because RoPE pairs those halves; the block of the KV group's first head stores them;
+// One block per (query head, context split).
+//   1. every warp builds the roped, normed, scaled q of the head in registers (each lane polls the q
+//      values it needs); in the block(s) of the split that holds the newest position, warps 0.. pack
+//      the new K row and warps 8.. the new V row to Q4_0 in shared memory (lower.rs:4231-4702), block
+//      pairs (b, b+NB/2) per warp because RoPE pairs those halves; the block of the KV group's first
+//      head stores them to the cache;
 //   2. warps take the positions of the split round-robin, online softmax per warp;
-//   3. the eight warps' (m, l, O) meet in shared memory, thread d folds dimension d;
-//   4. the block leaves a (m, l, O[hd]) record; the last block of a head to arrive merges the
-//      head's records (lower.rs:5897-6088).
+//   3. the sixteen warps' (m, l, O) meet in shared memory, thread d folds dimension d;
+//   4. one split: thread d stores the head's output; several: the block leaves a tagged (m, l, O[hd])
+//      record and the head's first block merges the records (lower.rs:5897-6088).
 template <int DPL>
-__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, unsigned char* sm, int* sflag, long long* pf) {
+__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, const u64* qkv, u64* ox, u64* rec, unsigned tag,
+                                             unsigned char* sm, Poll& pl) {
   constexpr int HD = DPL * 32, HALF = HD / 2, NB = HD / 32;
   constexpr unsigned ROWB = NB * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -721,43 +588,63 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
   const unsigned head = blockIdx.x / NSMAX, split = blockIdx.x % NSMAX;
   const unsigned G = a.n_q / a.n_kv, kvh = head / G;
   const unsigned pos = (unsigned)a.pos[0], tlen = pos + 1;
-  const unsigned NS = mg_active_splits(tlen, NSMAX);
+  const unsigned NS = mg_active_splits(tlen, NSMAX, a.split_from);
   if (split >= NS) return;
   const unsigned chunk = (tlen + NS - 1) / NS;
   const unsigned p0 = split * chunk, p1 = min(p0 + chunk, tlen);
   const bool owner = pos >= p0 && pos < p1;  // the split that holds the newest position
-  float* part = reinterpret_cast<float*>(sm);     // [8][HD + 2]
-  uint8_t* skrow = reinterpret_cast<uint8_t*>(part + 8 * (HD + 2));
+  float* part = reinterpret_cast<float*>(sm);     // [16][HD + 2]
+  uint8_t* skrow = reinterpret_cast<uint8_t*>(part + MG_NW * (HD + 2));
   uint8_t* svrow = skrow + ROWB + 16u;
   const float* cs = a.rope + (size_t)pos * HD;
+  const unsigned qn = a.n_q * HD, kvn = a.n_kv * HD;
 
   float qr[DPL];
   {
-    const int pb = warp & 3;  // block pair of the K / V job
-    const bool kjob = owner && warp < 4 && pb < NB / 2, vjob = owner && warp >= 4 && pb < NB / 2;
+    const int pb = warp & 7;  // block pair of the K / V job
+    const bool kjob = owner && warp < 8 && pb < NB / 2, vjob = owner && warp >= 8 && pb < NB / 2;
     float qv[DPL], qw[DPL], qc[DPL], qs[DPL], rv[DPL], r_w0 = 0.f, r_w1 = 0.f, r_c = 0.f, r_s = 0.f;
-    const float* qsrc = a.q + (size_t)head * HD;
     const float* qnw = L.norm[1];
 #pragma unroll
     for (int j = 0; j < DPL; j++) {
       const int d = mg_lane_dim<DPL>(lane, j);
-      qv[j] = __ldcg(qsrc + d);
       qw[j] = qnw[d];
       qc[j] = cs[d & (HALF - 1)];
       qs[j] = cs[HALF + (d & (HALF - 1))];
     }
-    if (kjob || vjob) {
-      const float* src = (kjob ? a.k : a.v) + (size_t)kvh * HD;
+    if (kjob) {
+      const float* w = L.norm[2];
+      r_w0 = w[32 * pb + lane];
+      r_w1 = w[HALF + 32 * pb + lane];
+      r_c = cs[32 * pb + lane];
+      r_s = cs[HALF + 32 * pb + lane];
+    }
+    {  // q of this head, then (K / V job) the whole new row: all loads first, then the checks
+      const u64* qsrc = qkv + (size_t)head * HD;
+      const u64* rsrc = qkv + qn + (kjob ? 0u : kvn) + (size_t)kvh * HD;
+      u64 wq[DPL], wr[DPL];
 #pragma unroll
-      for (int j = 0; j < DPL; j++) rv[j] = __ldcg(src + lane + 32 * j);
-      if (kjob) {
-        const float* w = L.norm[2];
-        r_w0 = w[32 * pb + lane];
-        r_w1 = w[HALF + 32 * pb + lane];
-        r_c = cs[32 * pb + lane];
-        r_s = cs[HALF + 32 * pb + lane];
+      for (int j = 0; j < DPL; j++) wq[j] = ll_load1(qsrc + mg_lane_dim<DPL>(lane, j));
+      if (kjob || vjob) {
+#pragma unroll
+        for (int j = 0; j < DPL; j++) wr[j] = ll_load1(rsrc + lane + 32 * j);
+      }
+#pragma unroll
+      for (int j = 0; j < DPL; j++) {
+        unsigned it = 0;
+        while (ll_tag(wq[j]) != tag && poll_again(pl, it)) wq[j] = ll_load1(qsrc + mg_lane_dim<DPL>(lane, j));
+        qv[j] = ll_val(wq[j]);
+      }
+      if (kjob || vjob) {
+#pragma unroll
+        for (int j = 0; j < DPL; j++) {
+          unsigned it = 0;
+          while (ll_tag(wr[j]) != tag && poll_again(pl, it)) wr[j] = ll_load1(rsrc + lane + 32 * j);
+          rv[j] = ll_val(wr[j]);
+        }
       }
     }
+    __syncwarp();
     {
       float ss = 0.0f;
 #pragma unroll
@@ -816,7 +703,6 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
             reinterpret_cast<const unsigned short*>(svrow)[threadIdx.x - n16];
     }
   }
-  if (pf) pf[4] = clock64();
 
   float o[DPL], m = kNegInit, l = 0.0f;
 #pragma unroll
@@ -829,9 +715,9 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
       raw_load<DPL>(t == pos ? svrow : Vc + (size_t)t * rowstride, lane, vn);
     }
 #pragma unroll 1
-    for (; t < p1; t += 8) {
+    for (; t < p1; t += MG_NW) {
       const RawRow<DPL> kr = kn, vr = vn;
-      const unsigned t2 = t + 8;
+      const unsigned t2 = t + MG_NW;
       if (t2 < p1) {
         raw_load<DPL>(t2 == pos ? skrow : Kc + (size_t)t2 * rowstride, lane, kn);
         raw_load<DPL>(t2 == pos ? svrow : Vc + (size_t)t2 * rowstride, lane, vn);
@@ -862,350 +748,315 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
     for (int j = 0; j < DPL; j++) dst[2 + j * 32 + lane] = o[j];
   }
   __syncthreads();
-  if (pf) pf[5] = clock64();
-  // thread d folds head dimension d over the eight warps; it sits in slot j * 32 + lane of the warps' layout
+  // thread d folds head dimension d over the sixteen warps; it sits in slot j * 32 + lane of the warps' layout
   const int d = threadIdx.x;
   int dslot;
   {
     constexpr int BPL = DPL / 2, LPB = 16 / BPL;
     const int within = d & 31, hh = within >> 4, w16 = within & 15;
-    dslot = (hh * BPL + (w16 % BPL)) * 32 + ((d >> 5) * LPB + w16 / BPL);
+    dslot = (hh * BPL + (w16 % BPL)) * 32 + (((d >> 5) & (NB - 1)) * LPB + w16 / BPL);
   }
-  const unsigned ounits = (a.n_q * HD) >> 6;
   float M = kNegInit, Lsum = 0.0f, O = 0.0f;
   if (d < HD) {
-    float mw[8];
+    float mw[MG_NW];
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
+    for (int w = 0; w < MG_NW; w++) {
       mw[w] = part[w * (HD + 2)];
       M = fmaxf(M, mw[w]);
     }
 #pragma unroll
-    for (int w = 0; w < 8; w++) {
+    for (int w = 0; w < MG_NW; w++) {
       const float f = __expf(mw[w] - M);
       Lsum = fmaf(part[w * (HD + 2) + 1], f, Lsum);
       O = fmaf(part[w * (HD + 2) + 2 + dslot], f, O);
     }
   }
-  if (pf) pf[6] = clock64();
   if (NS == 1) {  // one split: this block's result is final
-    if (d < HD) fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), O / Lsum, lane);
-    return;
-  }
-  float* rec = a.att_tmp + ((size_t)head * NSMAX + split) * (HD + 2);
-  if (d < HD) {
-    rec[2 + d] = O;  // records are kept in dimension order
-    if (d == 0) {
-      rec[0] = M;
-      rec[1] = Lsum;
-    }
-    __threadfence();
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) *sflag = (atomicAdd(a.att_cnt + head, 1u) == NS - 1) ? 1 : 0;
-  __syncthreads();
-  if (pf) pf[7] = clock64();
-  if (*sflag) {
-    // last block of this head to arrive: merge the head's records, every load first
-    __threadfence();
-    if (d < HD) {
-      const float* rec0 = a.att_tmp + (size_t)head * NSMAX * (HD + 2);
-      float mp[MG_MAX_SPLITS], lp[MG_MAX_SPLITS], ov[MG_MAX_SPLITS];
-#pragma unroll
-      for (int p = 0; p < MG_MAX_SPLITS; p++) {
-        if ((unsigned)p < NS) {
-          const float* r = rec0 + (size_t)p * (HD + 2);
-          mp[p] = __ldcg(r);
-          lp[p] = __ldcg(r + 1);
-          ov[p] = __ldcg(r + 2 + d);
-        } else {
-          mp[p] = kNegInit;
-          lp[p] = 0.0f;
-          ov[p] = 0.0f;
+    if (d < HD) ll_store(ox + (size_t)head * HD + d, O / Lsum, tag);
+  } else {
+    u64* myrec = rec + ((size_t)head * NSMAX + split) * (HD + 2);
+    if (split != 0) {
+      if (d < HD) {
+        ll_store(myrec + 2 + d, O, tag);  // records are kept in dimension order
+        if (d == 0) {
+          ll_store(myrec, M, tag);
+          ll_store(myrec + 1, Lsum, tag);
         }
       }
-      float MM = kNegInit;
+    } else {
+      // The head's first block merges (lower.rs:5897-6088): its own record is in registers, the others are
+      // awaited.  Thread p fetches (m, l) of split p for everybody; thread d fetches O[d] of every split.
+      float* ml = reinterpret_cast<float*>(svrow + ROWB + 16u);  // [2 * MG_MAX_SPLITS]
+      const u64* rec0 = rec + (size_t)head * NSMAX * (HD + 2);
+      u64 wo[MG_MAX_SPLITS];
+      if (d < HD) {
 #pragma unroll
-      for (int p = 0; p < MG_MAX_SPLITS; p++) MM = fmaxf(MM, mp[p]);
-      float LL = 0.0f, OO = 0.0f;
-#pragma unroll
-      for (int p = 0; p < MG_MAX_SPLITS; p++) {
-        const float f = __expf(mp[p] - MM);
-        LL = fmaf(lp[p], f, LL);
-        OO = fmaf(ov[p], f, OO);
+        for (int p = 1; p < MG_MAX_SPLITS; p++)
+          if ((unsigned)p < NS) wo[p] = ll_load1(rec0 + (size_t)p * (HD + 2) + 2 + d);
       }
-      fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), OO / LL, lane);
+      if (d == 0) {
+        ml[0] = M;
+        ml[1] = Lsum;
+      } else if ((unsigned)d < NS) {
+        const u64* r = rec0 + (size_t)d * (HD + 2);
+        u64 w0 = ll_load1(r), w1 = ll_load1(r + 1);
+        unsigned it = 0;
+        while (!(ll_tag(w0) == tag && ll_tag(w1) == tag) && poll_again(pl, it)) {
+          w0 = ll_load1(r);
+          w1 = ll_load1(r + 1);
+        }
+        ml[2 * d] = ll_val(w0);
+        ml[2 * d + 1] = ll_val(w1);
+      }
+      __syncthreads();
+      if (d < HD) {
+        float MM = kNegInit;
+        for (unsigned p = 0; p < NS; p++) MM = fmaxf(MM, ml[2 * p]);
+        float LL = 0.0f, OO = 0.0f;
+#pragma unroll
+        for (int p = 0; p < MG_MAX_SPLITS; p++)
+          if ((unsigned)p < NS) {
+            float ov = O;
+            if (p > 0) {
+              const u64* r = rec0 + (size_t)p * (HD + 2) + 2 + d;
+              unsigned it = 0;
+              while (ll_tag(wo[p]) != tag && poll_again(pl, it)) wo[p] = ll_load1(r);
+              ov = ll_val(wo[p]);
+            }
+            const float f = __expf(ml[2 * p] - MM);
+            LL = fmaf(ml[2 * p + 1], f, LL);
+            OO = fmaf(ov, f, OO);
+          }
+        ll_store(ox + (size_t)head * HD + d, OO / LL, tag);
+      }
     }
-    if (threadIdx.x == 0) a.att_cnt[head] = 0u;
   }
+  __syncthreads();  // the scratch is the next phase's x staging area
 }
 
 // ---- the kernel -------------------------------------------------------------------------------------
 struct MegaSmem {
-  unsigned ring_off, bar_off, red_off, flag_off, tab_off, ent_off, total;
+  unsigned ring_off, bar_off, done_off, red_off, psum_off, tab_off, piece_off, info_off, total;
 };
-__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int stages, unsigned tables_bytes) {
+__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int n_slots, unsigned tables_bytes) {
   MegaSmem L;
   L.ring_off = (x_bytes + 127u) & ~127u;
-  L.bar_off = L.ring_off + 8u * (unsigned)stages * slot_bytes;
-  L.red_off = (L.bar_off + 8u * 8u * (unsigned)stages + 15u) & ~15u;
-  L.flag_off = L.red_off + 256u + MG_MAX_P * 32u;  // 32 floats for block sums, 8 float4 of per-warp norm sums, partial sums [MG_MAX_P][2][4]
-  L.tab_off = L.flag_off + 48u;  // 4 flag words, then 8 words of per-kind group counts
-  L.ent_off = L.tab_off + tables_bytes;
-  L.total = L.ent_off + 8u * MG_MAX_ENT * (unsigned)sizeof(ItemEnt);
+  L.bar_off = L.ring_off + (unsigned)n_slots * slot_bytes;
+  L.done_off = L.bar_off + MG_MAXSLOTS * 8u;
+  L.red_off = L.done_off + MG_MAXSLOTS * 4u;      // 16 float4 of block sums, then 16 bytes of flags
+  L.psum_off = L.red_off + MG_NW * 16u + 16u;
+  L.tab_off = L.psum_off + 2u * MG_MAXROWS * MG_MAXC * 4u;
+  L.piece_off = L.tab_off + tables_bytes;
+  L.info_off = L.piece_off + MG_MAXPIECE * (unsigned)sizeof(Piece);
+  L.total = L.info_off + PH_KINDS * (unsigned)sizeof(PhInfo) + 16u;
   return L;
 }
 
+struct RingPos {  // where the next piece of the sequence sits (the same in every warp)
+  unsigned slot, par;
+};
+
 template <int DPL, int PC>
-__global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
+__global__ void __launch_bounds__(MG_THREADS, 1) mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cl = lane % MG_LPR, rl = lane / MG_LPR;
-  const int S = a.stages;
-  const MegaSmem SL = mg_smem(a.x_bytes, a.slot_bytes, S, a.tables_bytes);
-  const uint32_t ring_s = sm32(smem + SL.ring_off) + (uint32_t)(warp * S) * a.slot_bytes;
-  const uint32_t bars = sm32(smem + SL.bar_off) + (uint32_t)(warp * S) * 8u;
-  float* red = reinterpret_cast<float*>(smem + SL.red_off);
-  float4* wsum = reinterpret_cast<float4*>(smem + SL.red_off + 128u);
-  float* psum = reinterpret_cast<float*>(smem + SL.red_off + 256u);
-  int* sflag = reinterpret_cast<int*>(smem + SL.flag_off);
-  const MegaShape* shapes = reinterpret_cast<const MegaShape*>(smem + SL.tab_off);
-  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u));
+  const MegaSmem SL = mg_smem(a.x_bytes, a.slot_bytes, a.n_slots, a.tables_bytes);
+  const uint32_t ring_s = sm32(smem + SL.ring_off);
+  const uint32_t bars = sm32(smem + SL.bar_off);
+  int* done = reinterpret_cast<int*>(smem + SL.done_off);
+  float4* red = reinterpret_cast<float4*>(smem + SL.red_off);
+  int* flags = reinterpret_cast<int*>(smem + SL.red_off + MG_NW * 16u);
+  float* psum = reinterpret_cast<float*>(smem + SL.psum_off);
+  const MegaPhase* phases = reinterpret_cast<const MegaPhase*>(smem + SL.tab_off);
+  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u));
+  Piece* pieces = reinterpret_cast<Piece*>(smem + SL.piece_off);
+  PhInfo* info = reinterpret_cast<PhInfo*>(smem + SL.info_off);
   const uint32_t xs_s = sm32(smem);
-  const unsigned bar_base = a.bar[1];
-  const int n_phases = a.n_layers * PH_PER_LAYER;
+  const unsigned n_slots = (unsigned)a.n_slots;
 
   for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
     reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
-  if (threadIdx.x == 0) sflag[2] = sflag[3] = 0;  // barrier flag words ([0] belongs to the attention phase)
-  unsigned* ngrp = reinterpret_cast<unsigned*>(smem + SL.flag_off + 16u);  // this block's group count per phase kind
-  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = 0;
-  if (lane == 0) {
-    for (int s = 0; s < S; s++) mb_init(bars + s * 8u, 1);
+  if (threadIdx.x < MG_MAXSLOTS) done[threadIdx.x] = 0;
+  if (threadIdx.x == 0) {
+    for (unsigned s = 0; s < n_slots; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
-  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = block_groups(shapes[threadIdx.x]);
-  const unsigned H = shapes[PH_QKV].cols;
-
-  ItemEnt* ent = reinterpret_cast<ItemEnt*>(smem + SL.ent_off) + warp * MG_MAX_ENT;
-  int n_ent = 0;
-  if (lane == 0) n_ent = build_items(ent, shapes, warp);
-  n_ent = __shfl_sync(0xffffffffu, n_ent, 0);
-  bool dead = false;  // this warp gave up (a copy never landed, or its item table overflowed): it keeps the block-level steps only
-  if (n_ent < 0) {
-    dead = true;
-    if (lane == 0) atomicOr(a.err, 4u);
-    n_ent = 0;
+  if (threadIdx.x == 0) flags[0] = build_pieces(pieces, info, phases) ? 1 : 0;
+  __syncthreads();
+  if (!flags[0]) {  // a table overflowed: the host's own check of the same arithmetic should have refused this shape
+    if (threadIdx.x == 0) atomicOr(a.err, 4u);
+    return;
   }
-  __syncwarp();
-  ItemPos ic{n_ent > 0 ? 0 : a.n_layers, 0}, cc = ic;
-  unsigned issued = 0, consumed = 0;
-  while (issued < (unsigned)S && ic.layer < a.n_layers) {
-    const ItemEnt e = ent[ic.e];
-    mg_issue_ent(e, layers[ic.layer], shapes[e.kind].row_bytes, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
-    issued++;
-    pos_next(ic, n_ent);
+  const unsigned NP = (unsigned)info[PH_KINDS - 1].p0 + info[PH_KINDS - 1].np;
+  const unsigned total_pieces = NP * (unsigned)a.n_layers;
+  const unsigned epoch = *a.epoch;
+  Poll pl{a.err, a.poll_limit, false};
+  bool dead = false;  // this warp stopped waiting for weight copies (one never landed)
+
+  // fill the ring: piece n goes to slot n
+  if (lane == 0)
+    for (unsigned n = (unsigned)warp; n < n_slots && n < total_pieces; n += MG_NW) {
+      const Piece p = pieces[n % NP];
+      issue_piece(p, phases[p.kind], layers[n / NP], ring_s + n * a.slot_bytes, bars + n * 8u);
+    }
+
+  // the residual stream: this thread's chunks, in registers for the whole token
+  const unsigned H = phases[PH_QKV].cols;
+  float4 xr[PC];
+#pragma unroll
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * MG_THREADS;
+    xr[k] = c < (H >> 2) ? reinterpret_cast<const float4*>(a.x_in)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 
   long long* prof = nullptr;
-  if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * n_phases * 8;
-  int p = 0, layer = 0, kind = 0;
-  for (; p < n_phases; p++) {
+  if (a.prof && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * a.n_layers * PF_PER_LAYER * 4;
+
+  RingPos rp{0u, 0u};
+
+  for (int layer = 0; layer < a.n_layers; layer++) {
     const MegaLayer& L = layers[layer];
-    // constants of this phase, fetched while the other blocks arrive at the barrier before it
-    NormPre<PC> npre;
-    if (kind == PH_QKV)
-      mg_prefetch_norm(npre, layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM, L.norm[0], layers[layer > 0 ? layer - 1 : 0].norm[5], H);
-    else if (kind == PH_GATEUP)
-      mg_prefetch_norm(npre, KS_PRO_ADD_NORM, L.norm[4], L.norm[3], H);
-    if (p > 0) {
-      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x, a.err, sflag + 2, p & 1)) break;
-      if (prof) prof[(p - 1) * 8 + 3] = clock64();
-    }
-    if (prof) prof[p * 8 + 0] = clock64();
-#ifdef KS_MEGA_LATENCY_PROBE
-    if (kind == PH_ATTN && blockIdx.x == gridDim.x - 1) {  // idle block in this phase: time known instruction chains
-      float f = (float)p;
-      const long long c0 = clock64();
-#pragma unroll
-      for (int i = 0; i < 64; i++) f = fmaf(f, 1.0001f, 0.5f);
-      const long long c1 = clock64() + (long long)(f > 1e30f);
-#pragma unroll
-      for (int i = 0; i < 16; i++) f += __shfl_xor_sync(0xffffffffu, f, 1 + (i & 15));
-      const long long c2 = clock64() + (long long)(f > 1e30f);
-      float sacc = f;
-#pragma unroll
-      for (int i = 0; i < 16; i++) sacc += red[(i * 7 + (int)sacc) & 31];
-      const long long c3 = clock64() + (long long)(sacc > 1e30f);
-      if (prof) {
-        prof[p * 8 + 4] = c1 - c0;
-        prof[p * 8 + 5] = c2 - c1;
-        prof[p * 8 + 6] = c3 - c2;
+    const unsigned tag = epoch + (unsigned)layer + 1u;
+    const int b = layer & 1;
+    const bool last = layer + 1 == a.n_layers;
+    // kernel parameters are picked with selects (indexing them would force a local copy)
+    u64* const yd = b ? a.ll_yd1 : a.ll_yd0;
+    const u64* const yd_prev = b ? a.ll_yd0 : a.ll_yd1;
+    u64* const yo = b ? a.ll_yo1 : a.ll_yo0;
+    u64* const qkv = b ? a.ll_qkv1 : a.ll_qkv0;
+    u64* const ox = b ? a.ll_ox1 : a.ll_ox0;
+    u64* const ff = b ? a.ll_ff1 : a.ll_ff0;
+    u64* const rec = b ? a.ll_rec1 : a.ll_rec0;
+
+#pragma unroll 1
+    for (int kind = 0; kind < PH_KINDS; kind++) {
+      // profile rows: qkv, attention, o-proj, gate-up, down
+      long long* pf = prof ? prof + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 4 : nullptr;
+      const MegaPhase& ph = phases[kind];
+      // ---- this phase's input vector, staged in shared memory
+      if (kind == PH_OPROJ) {
+        if (pf) pf[-4] = clock64();
+        mg_attention<DPL>(a, L, qkv, ox, rec, tag, smem, pl);
+        if (pf) pf[-1] = clock64();
       }
-    }
-#endif
-    if (kind == PH_ATTN) {
-      mg_attention<DPL>(a, L, smem, sflag, prof ? prof + p * 8 : nullptr);
-    } else {
-      const MegaShape& sh = shapes[kind];
-      // input, prologue and outputs of this phase
-      int mode = KS_PRO_NONE;
-      const float* x;
-      const float* yin = a.yb;
-      float* out_x = nullptr;
-      if (kind == PH_QKV) {
-        mode = layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM;
-        x = layer == 0 ? a.x_a : a.x_b;
-        out_x = a.x_a;
-      } else if (kind == PH_OPROJ) {
-        x = nullptr;
-      } else if (kind == PH_GATEUP) {
-        mode = KS_PRO_ADD_NORM;
-        x = a.x_a;
-        out_x = a.x_b;
+      if (pf) pf[0] = clock64();
+      if (kind == PH_QKV || kind == PH_GATEUP) {
+        // residual update (from the second phase on) + norm.  q/k/v: the previous layer's down-proj output
+        // and post-FFN norm, then this layer's attention norm; gate/up: the o-proj output and post-attention
+        // norm, then the FFN norm.
+        const bool qk = kind == PH_QKV;
+        mg_stage_hidden<PC>(smem, red, !qk || layer > 0, H, xr, qk ? yd_prev : yo, qk ? tag - 1u : tag + a.test_stall,
+                            qk ? L.norm[0] : L.norm[4], qk ? layers[layer > 0 ? layer - 1 : 0].norm[5] : L.norm[3], a.eps,
+                            (!qk && last && blockIdx.x == 0) ? a.resid_out : nullptr, pl);
       } else {
-        x = nullptr;
+        mg_stage_plain(smem, ph.cols, kind == PH_OPROJ ? ox : ff, tag, pl);
       }
-      if (kind == PH_OPROJ || kind == PH_DOWN)
-        fx_copy_in(smem, kind == PH_OPROJ ? a.ox : a.ffx, sh.cols >> 6);
-      else if (mode == KS_PRO_ADD_NORM)
-        mg_stage_addnorm(smem, sh.cols, x, yin, out_x, a.eps, npre, a.nsum, gridDim.x);
-      else
-        mg_stage_x(smem, red, mode, sh.cols, x, yin, out_x, a.eps, npre);
       __syncthreads();
-      if (prof) prof[p * 8 + 1] = clock64();
-      const unsigned units = sh.cols >> 6;
-      // o-proj and down feed a residual-add + norm: their rows also leave the sums that norm needs
-      const bool sums = kind == PH_OPROJ || kind == PH_DOWN;
-      // Thread f finishes row (f & 3) of this block's group (f >> 2): it adds the column segments'
-      // partial sums in order, applies the epilogue and stores the row.
-      const unsigned n_g = ngrp[kind], C = sh.n_cseg;
-      unsigned frow = 0;
-      int fseg = 0;
-      bool fin = false;
-      float xr = 0.0f, wpr = 0.0f;
-      if ((threadIdx.x >> 2) < n_g) {
-        const unsigned g = block_group_id(sh, threadIdx.x >> 2);
-        if (sh.n_seg > 1 && g >= sh.grp_start[1]) fseg = 1;
-        if (sh.n_seg > 2 && g >= sh.grp_start[2]) fseg = 2;
-        frow = (g - sh.grp_start[fseg]) * MG_RL + (threadIdx.x & 3u);
-        fin = g < sh.grp_start[sh.n_seg] && frow < sh.rows[fseg];
-        if (fin && sums) {  // in flight while the items are multiplied
-          xr = __ldcg((kind == PH_OPROJ ? a.x_a : a.x_b) + frow);
-          wpr = (kind == PH_OPROJ ? L.norm[3] : L.norm[5])[frow];
-        }
-      }
-      while (cc.layer == layer && !dead) {
-        const ItemEnt e = ent[cc.e];
-        if (e.kind != kind) break;
-        const unsigned st = consumed % (unsigned)S;
-        if (!mb_wait(bars + st * 8u, (consumed / (unsigned)S) & 1u)) {
-          dead = true;
-          if (lane == 0) atomicOr(a.err, 1u);
-          break;
-        }
-        const uint32_t slot = ring_s + st * a.slot_bytes;
-        float yacc[2] = {0.0f, 0.0f};
-        if (e.flags & 1)
-          mg_item_compute_fx<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
-        else
-          mg_item_compute_fx<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
-        consumed++;
-        float v0 = yacc[0], v1 = yacc[1];
-#pragma unroll
-        for (int o = MG_LPR / 2; o > 0; o >>= 1) {
-          v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-          v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-        }
-        if (cl == 0) {
-          if (e.flags & 4) {
-            psum[e.pslot * 8u + 4u + (unsigned)rl] = v0;  // the up rows of a split gate-up group
-          } else {
-            psum[e.pslot * 8u + (unsigned)rl] = v0;
-            if (e.flags & 1) psum[e.pslot * 8u + 4u + (unsigned)rl] = v1;
+      if (pf) pf[1] = clock64();
+
+      // ---- this block's items
+      const PhInfo inf = info[kind];
+      const unsigned C = ph.n_cseg, units = ph.cols >> 6, seg_units = ph.seg_blocks * 4u;
+      const unsigned seg_bytes = ph.seg_blocks * KS_Q4K_BLOCK_BYTES;
+      for (unsigned pi = inf.p0; pi < (unsigned)inf.p0 + inf.np; pi++) {
+        const Piece P = pieces[pi];
+        const unsigned first = P.item0 + (((unsigned)warp - P.item0) & (MG_NW - 1u));
+        const unsigned end = (unsigned)P.item0 + P.n_items;
+        if (first < end && !dead) {
+          const bool ok = mb_wait(bars + rp.slot * 8u, rp.par, a.poll_limit);
+          if (!__all_sync(0xffffffffu, ok)) {
+            dead = true;
+            if (lane == 0) atomicOr(a.err, 1u);
           }
         }
-        pos_next(cc, n_ent);
-        // Refill now only when the next item of THIS phase is not in flight yet; everything else is
-        // refilled after the barrier arrival below, off the critical path.
-        if (ic.layer == layer && ent[ic.e].kind == kind) {
-          __syncwarp();
-          if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
-          __syncwarp();
-          const ItemEnt ne = ent[ic.e];
-          mg_issue_ent(ne, layers[ic.layer], sh.row_bytes, slot, bars + st * 8u, lane);
-          issued++;
-          pos_next(ic, n_ent);
+        if (first < end && !dead) {
+          const uint32_t slot_addr = ring_s + rp.slot * a.slot_bytes;
+          const uint32_t mat2 = (((unsigned)P.nrows + 3u) & ~3u) * ph.row_bytes;
+          for (unsigned j = first; j < end; j += MG_NW) {
+            const unsigned local = j - P.item0, gi = local / C, cs = local - gi * C;
+            const uint32_t base = slot_addr + gi * 4u * ph.row_bytes + cs * seg_bytes;
+            float yacc[2] = {0.0f, 0.0f};
+            if (ph.mats == 2)
+              mg_item_compute_fx<2>(base, ph.row_bytes, mat2, xs_s, units, seg_units, cs, cl, rl, yacc);
+            else
+              mg_item_compute_fx<1>(base, ph.row_bytes, 0u, xs_s, units, seg_units, cs, cl, rl, yacc);
+            float v0 = yacc[0], v1 = yacc[1];
+#pragma unroll
+            for (int o = MG_LPR / 2; o > 0; o >>= 1) {
+              v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+              v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+            }
+            const unsigned r = gi * 4u + (unsigned)rl;
+            if (cl == 0 && r < P.nrows) {
+              const unsigned idx = ((unsigned)P.row0 + r) * C + cs;
+              psum[idx] = v0;
+              if (ph.mats == 2) psum[MG_MAXROWS * MG_MAXC + idx] = v1;
+            }
+          }
+        }
+        // this warp is done with the slot; the last of the sixteen refills it with the piece n_slots further on
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          if (atomicAdd(&done[rp.slot], 1) == MG_NW - 1) {
+            done[rp.slot] = 0;
+            __threadfence_block();
+            unsigned npi = pi + n_slots;
+            int nl = layer;
+            while (npi >= NP) {
+              npi -= NP;
+              nl++;
+            }
+            if (nl < a.n_layers) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
+              const Piece np_ = pieces[npi];
+              issue_piece(np_, phases[np_.kind], layers[nl], ring_s + rp.slot * a.slot_bytes, bars + rp.slot * 8u);
+            }
+          }
+        }
+        if (++rp.slot == n_slots) {
+          rp.slot = 0;
+          rp.par ^= 1u;
         }
       }
       __syncthreads();  // the partial sums of every item of this block are in shared memory
-      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f, fval = 0.0f;
-      if (fin) {
-        const float* ps = psum + (size_t)(threadIdx.x >> 2) * C * 8u + (threadIdx.x & 3u);
-        float v0 = 0.0f, v1 = 0.0f;
-        for (unsigned cs = 0; cs < C; cs++) {
-          v0 += ps[cs * 8u];
-          v1 += ps[cs * 8u + 4u];
+      if (pf) pf[2] = clock64();
+
+      // ---- thread f finishes row f of this block: column segments added in order, epilogue, tagged store
+      if (threadIdx.x < inf.nrows) {
+        unsigned pi = inf.p0;
+        while (pi + 1 < (unsigned)inf.p0 + inf.np && pieces[pi + 1].row0 <= threadIdx.x) pi++;
+        const unsigned orow = pieces[pi].out0 + (threadIdx.x - pieces[pi].row0);
+        const float* ps = psum + (size_t)threadIdx.x * C;
+        float v0 = 0.0f;
+        for (unsigned cs = 0; cs < C; cs++) v0 += ps[cs];
+        if (ph.mats == 2) {
+          float v1 = 0.0f;
+          for (unsigned cs = 0; cs < C; cs++) v1 += ps[MG_MAXROWS * MG_MAXC + cs];
+          v0 = gelu_mul(v0, v1);
         }
-        fval = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
-        const float val = fval;
-        if (kind != PH_GATEUP) {
-          float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : a.yb;
-          y[frow] = val;
-        }
-        if (sums) {
-          const float t = val * wpr;
-          ns0 = val * val;
-          ns1 = xr * t;
-          ns2 = t * t;
-          ns3 = xr * xr;
-        }
+        u64* out = kind == PH_QKV ? qkv : kind == PH_OPROJ ? yo : kind == PH_GATEUP ? ff : yd;
+        ll_store(out + orow, v0, tag);
+        if (kind == PH_DOWN && last) a.y_out[orow] = v0;  // the head reads plain floats
       }
-      if (kind == PH_GATEUP && (threadIdx.x >> 2) < n_g) {
-        // this warp's 32 threads hold 32 consecutive rows (a run of 8 groups): one sub-block of the next phase's x
-        const unsigned g0 = block_group_id(sh, (threadIdx.x >> 2) & ~7u);
-        if (g0 < sh.grp_start[1]) fx_store_subblock(a.ffx, sh.rows[0] >> 6, g0 * MG_RL, fval, lane);
-      }
-      if (sums) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          ns0 += __shfl_xor_sync(0xffffffffu, ns0, o);
-          ns1 += __shfl_xor_sync(0xffffffffu, ns1, o);
-          ns2 += __shfl_xor_sync(0xffffffffu, ns2, o);
-          ns3 += __shfl_xor_sync(0xffffffffu, ns3, o);
-        }
-        if (lane == 0) wsum[warp] = make_float4(ns0, ns1, ns2, ns3);
-      }
-    }
-    if (prof) prof[p * 8 + 2] = clock64();
-    if (p + 1 == n_phases) {  // the end of the kernel orders the last phase before whatever follows
-      p++;
-      break;
-    }
-    grid_arrive(a.bar, (kind == PH_OPROJ || kind == PH_DOWN) ? wsum : nullptr, a.nsum);
-    // refill the ring while the other blocks arrive
-    if (!dead && issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
-      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      while (issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
-        const unsigned st = issued % (unsigned)S;
-        const ItemEnt ne = ent[ic.e];
-        mg_issue_ent(ne, layers[ic.layer], shapes[ne.kind].row_bytes, ring_s + st * a.slot_bytes, bars + st * 8u, lane);
-        issued++;
-        pos_next(ic, n_ent);
-      }
-    }
-    if (++kind == PH_PER_LAYER) {
-      kind = 0;
-      layer++;
+      if (pf) pf[3] = clock64();
     }
   }
-  if (p == n_phases && blockIdx.x == 0 && threadIdx.x == 0) a.bar[1] = bar_base + (unsigned)(n_phases - 1) * gridDim.x;
-  // copies still in flight must land before this block's shared memory goes away (bounded)
-  for (unsigned j = consumed; j < issued; j++) mb_wait(bars + (j % (unsigned)S) * 8u, (j / (unsigned)S) & 1u);
+  // The next token's tags must differ from everything this one wrote.  Every block read the epoch before
+  // block 0 can get here (its last phase needed rows from all of them).
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.epoch = epoch + (unsigned)a.n_layers + 1u;
+  // copies still in flight must land before this block's shared memory goes away (bounded; a no-op unless a warp gave up)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (unsigned s = 0; s < n_slots && s < total_pieces; s++) {
+      const unsigned n_last = s + ((total_pieces - 1u - s) / n_slots) * n_slots;
+      mb_wait(bars + s * 8u, (n_last / n_slots) & 1u, a.poll_limit);
+    }
+  }
 }
 
 }  // namespace
@@ -1214,14 +1065,14 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
 struct ks_mega {
   MegaArgs args{};
   void* d_tables = nullptr;
-  unsigned* d_sync = nullptr;  // words 0..1 barrier (a 128-byte line of its own: every block polls it), 64..111 per-head
-                               // attention arrival counters, from byte 512: per-block norm sums
+  unsigned* d_sync = nullptr;     // word 0: the tag epoch
   long long* d_prof = nullptr;
-  unsigned char* d_fx = nullptr;  // attention output and GeGLU output in the staged layout
+  u64* d_ll = nullptr;            // the tagged activation vectors
+  size_t ll_bytes = 0;
   unsigned grid = 0;
   size_t smem = 0;
-  int G = 0, dpl = 0, pc = 4;  // pc: 4-element chunks of the hidden vector per thread (2 up to 2048 columns)
-  float* residual = nullptr;  // buffer that holds the residual stream when the kernel ends
+  int dpl = 0, pc = 1;            // pc: 4-element chunks of the hidden vector per thread
+  float* residual = nullptr;      // buffer that holds the residual stream when the kernel ends
 };
 
 namespace {
@@ -1236,11 +1087,11 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(mg->grid);
-  cfg.blockDim = dim3(256);
+  cfg.blockDim = dim3(MG_THREADS);
   cfg.dynamicSmemBytes = mg->smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;  // every block resident: the grid barrier needs it
+  attr[0].id = cudaLaunchAttributeCooperative;  // every block resident: blocks wait for each other's rows
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -1251,28 +1102,42 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
 }  // namespace
 
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
-  if (mg->dpl == 4) return mg->pc == 2 ? mega_launch_t<4, 2>(ctx, mg) : mega_launch_t<4, 4>(ctx, mg);
-  if (mg->dpl == 8) return mg->pc == 2 ? mega_launch_t<8, 2>(ctx, mg) : mega_launch_t<8, 4>(ctx, mg);
+  if (mg->dpl == 4) return mg->pc == 1 ? mega_launch_t<4, 1>(ctx, mg) : mega_launch_t<4, 2>(ctx, mg);
+  if (mg->dpl == 8) return mg->pc == 1 ? mega_launch_t<8, 1>(ctx, mg) : mega_launch_t<8, 2>(ctx, mg);
   return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size not supported");
 }
 
 float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
 
-// Zero the barrier words and arrival counters (stream-ordered).  They only leave their rest state when
-// a bounded wait gave up; a slot reset puts the kernel back in working order.
+// After a wait gave up the tagged vectors hold a mix of tokens; clearing them (tag 0 is never used)
+// puts the kernel back in working order.  The epoch word keeps counting.  Stream-ordered.
 int ks_mega_reset(ks_ctx* ctx, ks_mega* mg) {
-  cudaError_t e = cudaMemsetAsync(mg->d_sync, 0, 512, ctx->stream);
+  cudaError_t e = cudaMemsetAsync(mg->d_ll, 0, mg->ll_bytes, ctx->stream);
   if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: reset failed: %s", cudaGetErrorString(e));
   return KS_OK;
 }
 const long long* ks_mega_prof(const ks_mega* mg) { return mg->d_prof; }
+
+// Knobs that tests and the profiling reader set: 0 = polls before a wait gives up, 1 = make the gate-up stage
+// of every layer wait for a tag nobody writes (0 = off), 2 = context length from which attention is split
+// across blocks, 3 = record phase clocks (0 / 1).  The caller re-captures its graphs afterwards.
+int ks_mega_set(ks_mega* mg, int what, unsigned value) {
+  if (!mg) return KS_ERR_INVALID;
+  switch (what) {
+    case 0: mg->args.poll_limit = value ? value : 1u; return KS_OK;
+    case 1: mg->args.test_stall = value; return KS_OK;
+    case 2: mg->args.split_from = value; return KS_OK;
+    case 3: mg->args.prof = value ? mg->d_prof : nullptr; return KS_OK;
+    default: return KS_ERR_INVALID;
+  }
+}
 
 void ks_mega_destroy(ks_mega* mg) {
   if (!mg) return;
   if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
   if (mg->d_prof) cudaFree(mg->d_prof);
-  if (mg->d_fx) cudaFree(mg->d_fx);
+  if (mg->d_ll) cudaFree(mg->d_ll);
   delete mg;
 }
 
@@ -1282,114 +1147,109 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   *out = nullptr;
   const unsigned H = d->hidden, F = d->ffn, hd = d->hd, nq = d->n_q, nkv = d->n_kv;
   const unsigned qn = nq * hd, kvn = nkv * hd;
-  const unsigned G = nq / nkv;
   auto even_blocks = [](unsigned cols) { return cols % 512 == 0; };
   if (!even_blocks(H) || !even_blocks(F) || !even_blocks(qn)) return KS_OK;
-  if (H > 16u * 256u) return KS_OK;  // the fused norms hold the vector in registers
-  if (G < 1 || nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
+  if (H > 2u * 4u * MG_THREADS) return KS_OK;  // the residual stream lives in registers: at most two chunks per thread
+  if (nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
+  const unsigned grid = (unsigned)ctx->sm_count;
   // one block per (query head, split): fewer splits than the caller's record layout allows if the grid is small
   unsigned n_splits = (unsigned)d->n_splits;
-  if (n_splits > (unsigned)ctx->sm_count / nq) n_splits = (unsigned)ctx->sm_count / nq;
+  if (n_splits > grid / nq) n_splits = grid / nq;
   if (n_splits > (unsigned)MG_MAX_SPLITS) n_splits = MG_MAX_SPLITS;
-  if (n_splits < 1 || nq > 48) return KS_OK;
+  if (n_splits < 1) return KS_OK;
   if (d->n_layers < 1 || d->n_layers > 128) return KS_OK;
 
-  const int stages = 3;
-  const unsigned shapes_bytes = (unsigned)((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u);
+  const unsigned shapes_bytes = (unsigned)((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u);
   const unsigned tables_bytes = (unsigned)((shapes_bytes + d->n_layers * sizeof(MegaLayer) + 15u) & ~15u);
   unsigned maxcols = H > F ? H : F;
   if (qn > maxcols) maxcols = qn;
-  unsigned x_bytes = (maxcols / 64u) * Q4K_XTOK * 4u;
-  const unsigned att = mg_att_bytes(hd);
-  if (att > x_bytes) x_bytes = att;
-  const unsigned budget = (unsigned)ctx->smem_optin;
-  const MegaSmem fixed = mg_smem(x_bytes, 0, stages, tables_bytes);
-  if (fixed.total + 8u * stages * 4u * KS_Q4K_BLOCK_BYTES * 2u > budget) return KS_OK;
-  unsigned slot_cap = (budget - fixed.total) / (8u * stages);
-  slot_cap &= ~15u;
-  if (slot_cap > 8192u) slot_cap = 8192u;
-  // Blocks per column segment.  A block's items (its groups x column segments) are shared by its 8
-  // warps, so more segments shorten the longest warp until the per-item overhead (measured: a little more
-  // than one unit's worth of time) wins; segments hold an even number of blocks (8 lanes per row) and must fit a ring slot.
-  const unsigned grid = (unsigned)ctx->sm_count;
-  auto pick_seg = [&](unsigned cols, unsigned mats, unsigned total_groups, bool oct = false) {
-    const unsigned nb = cols / 256u;
-    const unsigned n_g = oct ? ((total_groups + 7) / 8 + grid - 1) / grid * 8 : (total_groups + grid - 1) / grid;
-    unsigned best = 0;
-    float best_cost = 0.f;
-    for (unsigned C = 1; C <= nb; C++) {
-      if (nb % C) continue;
-      const unsigned sb = nb / C;
-      if (sb % 2 || 4u * mats * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
-      const float cost = (float)((n_g * C + 7u) / 8u) * ((float)(sb * mats) * 0.5f + 1.2f);
-      if (!best || cost < best_cost) {
-        best = sb;
-        best_cost = cost;
-      }
-    }
-    return best;
-  };
-  const unsigned g_qkv = (qn + 3) / 4 + 2 * ((kvn + 3) / 4), g_h = (H + 3) / 4, g_f = (F + 3) / 4;
-  if (g_qkv > 64u * grid || g_f > 64u * grid || g_h > 64u * grid) return KS_OK;  // a block finishes at most 64 groups per phase
-  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
-  // gate-up: gate and up rows of a group in one item (x read once for both) when they fit a slot, else as two items
-  unsigned sb_h2 = pick_seg(H, 2, g_f, true);
-  bool gu_split = false;
-  if (!sb_h2) {
-    gu_split = true;
-    const unsigned n_g = ((g_f + 7) / 8 + grid - 1) / grid * 8, nb = H / 256u;
-    float best_cost = 0.f;
-    for (unsigned C = 1; C <= nb; C++) {
-      if (nb % C) continue;
-      const unsigned sb = nb / C;
-      if (sb % 2 || 4u * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
-      const float cost = (float)((n_g * C * 2u + 7u) / 8u) * ((float)sb * 0.5f + 1.2f);
-      if (!sb_h2 || cost < best_cost) {
-        sb_h2 = sb;
-        best_cost = cost;
-      }
-    }
-  }
-  if (!sb_h || !sb_h2 || !sb_q || !sb_f) return KS_OK;
-  unsigned slot_bytes = 0;
-  auto upd = [&](unsigned sb, unsigned mats) {
-    const unsigned b = 4u * mats * sb * KS_Q4K_BLOCK_BYTES;
-    if (b > slot_bytes) slot_bytes = b;
-  };
-  upd(sb_h, 1); upd(sb_h2, gu_split ? 1 : 2); upd(sb_q, 1); upd(sb_f, 1);
+  unsigned x_bytes = (maxcols / 64u) * 256u;
+  if (mg_att_bytes(hd) > x_bytes) x_bytes = mg_att_bytes(hd);
 
-  {  // every warp's items of one layer must fit its table
-    auto per_warp = [&](unsigned total_groups, unsigned ncs) { return ((total_groups + grid - 1) / grid * ncs + 7u) / 8u; };
-    const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) +
-                           (((g_f + 7) / 8 + grid - 1) / grid * 8 * (H / 256 / sb_h2) * (gu_split ? 2u : 1u) + 7u) / 8u +
-                           per_warp(g_h, F / 256 / sb_f);
-    if (worst > (unsigned)MG_MAX_ENT) return KS_OK;
-  }
   std::vector<unsigned char> tab(tables_bytes, 0);
-  MegaShape* sh = reinterpret_cast<MegaShape*>(tab.data());
+  MegaPhase* ph = reinterpret_cast<MegaPhase*>(tab.data());
   MegaLayer* ly = reinterpret_cast<MegaLayer*>(tab.data() + shapes_bytes);
-  auto set_rows = [](MegaShape& p, unsigned cols, unsigned sb) {
+  auto set_phase = [&](MegaPhase& p, unsigned n_seg, const unsigned* rows, unsigned mats, unsigned widx, unsigned cols) {
+    p.n_seg = n_seg;
+    p.mats = mats;
+    p.seg_start[0] = 0;
+    for (unsigned s = 0; s < n_seg; s++) p.seg_start[s + 1] = p.seg_start[s] + rows[s];
+    p.widx = widx;
     p.cols = cols;
     p.row_bytes = cols / 256u * KS_Q4K_BLOCK_BYTES;
-    p.seg_blocks = sb;
-    p.n_cseg = cols / 256u / sb;
-    unsigned g0 = 0;
-    for (int s = 0; s < p.n_seg; s++) {
-      p.grp_start[s] = g0;
-      g0 += (p.rows[s] + 3u) / 4u;
-    }
-    p.grp_start[p.n_seg] = g0;
   };
-  sh[PH_QKV].type = MG_MATVEC; sh[PH_QKV].n_seg = 3;
-  sh[PH_QKV].rows[0] = qn; sh[PH_QKV].rows[1] = kvn; sh[PH_QKV].rows[2] = kvn;
-  set_rows(sh[PH_QKV], H, sb_h);
-  sh[PH_ATTN].type = MG_ATTN; sh[PH_ATTN].n_seg = 1; sh[PH_ATTN].n_cseg = 1;
-  sh[PH_OPROJ].type = MG_MATVEC; sh[PH_OPROJ].n_seg = 1; sh[PH_OPROJ].rows[0] = H;
-  set_rows(sh[PH_OPROJ], qn, sb_q);
-  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F; sh[PH_GATEUP].oct = 1; sh[PH_GATEUP].split = gu_split ? 1 : 0;
-  set_rows(sh[PH_GATEUP], H, sb_h2);
-  sh[PH_DOWN].type = MG_MATVEC; sh[PH_DOWN].n_seg = 1; sh[PH_DOWN].rows[0] = H;
-  set_rows(sh[PH_DOWN], F, sb_f);
+  const unsigned r_qkv[3] = {qn, kvn, kvn}, r_h[1] = {H}, r_f[1] = {F};
+  set_phase(ph[PH_QKV], 3, r_qkv, 1, 0, H);
+  set_phase(ph[PH_OPROJ], 1, r_h, 1, 3, qn);
+  set_phase(ph[PH_GATEUP], 1, r_f, 2, 4, H);
+  set_phase(ph[PH_DOWN], 1, r_h, 1, 6, F);
+  for (int k = 0; k < PH_KINDS; k++)
+    if (ph[k].seg_start[ph[k].n_seg] % 4u || ph[k].seg_start[1] % 4u) return KS_OK;
+
+  // ring: as many slots as give every phase room for at least one 4-row group (x 2 matrices for gate-up)
+  const unsigned budget = (unsigned)ctx->smem_optin;
+  unsigned need = 0;
+  for (int k = 0; k < PH_KINDS; k++) need = std::max(need, 4u * ph[k].mats * ph[k].row_bytes);
+  int n_slots = 8;
+  if (const char* e = getenv("KSEARCH_MEGA_SLOTS")) n_slots = atoi(e);
+  if (n_slots > MG_MAXSLOTS) n_slots = MG_MAXSLOTS;
+  unsigned slot_bytes = 0;
+  for (; n_slots >= 2; n_slots--) {
+    const MegaSmem fixed = mg_smem(x_bytes, 0, n_slots, tables_bytes);
+    if (fixed.total >= budget) continue;
+    slot_bytes = ((budget - fixed.total) / (unsigned)n_slots) & ~127u;
+    if (slot_bytes >= need) break;
+  }
+  if (n_slots < 2 || slot_bytes < need) return KS_OK;
+
+  // rows of a phase owned by the fullest block
+  auto max_rows = [&](const MegaPhase& p) {
+    const unsigned half = p.seg_start[p.n_seg] / 2u;
+    unsigned m = 0;
+    for (unsigned b = 0; b < grid; b++) {
+      const unsigned lo = (unsigned)(((unsigned long long)b * half) / grid) * 2u, hi = (unsigned)(((unsigned long long)(b + 1) * half) / grid) * 2u;
+      m = std::max(m, hi - lo);
+    }
+    return m;
+  };
+  // Column segments per phase.  A block's items (4-row groups x column segments) are shared by its 16 warps,
+  // so more segments shorten the longest warp until the per-item overhead (about one 64-weight unit's worth of
+  // time) wins; a segment holds an even number of blocks (8 lanes per row take one unit each per trip).
+  int c_env[PH_KINDS] = {0, 0, 0, 0};
+  if (const char* e = getenv("KSEARCH_MEGA_CSEG")) sscanf(e, "%d,%d,%d,%d", &c_env[0], &c_env[1], &c_env[2], &c_env[3]);
+  unsigned total_pieces = 0;
+  for (int k = 0; k < PH_KINDS; k++) {
+    MegaPhase& p = ph[k];
+    const unsigned R = max_rows(p);
+    if (R > (unsigned)MG_MAXROWS || R == 0) return KS_OK;
+    // pieces: as few as fit the slot, of equal size
+    unsigned cap_rows = (slot_bytes / (p.mats * p.row_bytes)) & ~3u;
+    if (cap_rows > 64u) cap_rows = 64u;
+    const unsigned n_pc = (R + cap_rows - 1u) / cap_rows;
+    p.piece_rows = std::min(cap_rows, (((R + n_pc - 1u) / n_pc) + 3u) & ~3u);
+    unsigned groups = 0;
+    for (unsigned r = 0; r < R; r += p.piece_rows) groups += (std::min(p.piece_rows, R - r) + 3u) / 4u;
+    const unsigned nb = p.cols / 256u;
+    unsigned best = 0;
+    float best_cost = 0.f;
+    for (unsigned C = 1; C <= nb && C <= (unsigned)MG_MAXC; C++) {
+      if (nb % C) continue;
+      const unsigned sb = nb / C;
+      if (sb % 2) continue;
+      if (c_env[k] > 0 && (unsigned)c_env[k] != C) continue;
+      const float cost = (float)((groups * C + MG_NW - 1u) / MG_NW) * ((float)(sb * p.mats) * 0.5f + 1.0f);
+      if (!best || cost < best_cost) {
+        best = C;
+        best_cost = cost;
+      }
+    }
+    if (!best) return KS_OK;
+    p.n_cseg = best;
+    p.seg_blocks = nb / best;
+    total_pieces += p.n_seg + (R + p.piece_rows - 1u) / p.piece_rows + 1u;
+  }
+  if (total_pieces > (unsigned)MG_MAXPIECE) return KS_OK;
+
   for (int l = 0; l < d->n_layers; l++) {
     const ks_mega_layer& L = layers[l];
     MegaLayer& o = ly[l];
@@ -1402,18 +1262,25 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
 
   ks_mega* mg = new ks_mega();
   cudaSetDevice(ctx->device);
-  const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
-  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 512 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess) {
+  const size_t prof_n = (size_t)2 * d->n_layers * PF_PER_LAYER * 4;
+  // tagged vectors, two of each: yd, yo [H], qkv [qn + 2 kvn], ox [qn], ff [F], rec [n_q * n_splits * (hd + 2)]
+  const size_t n_rec = (size_t)nq * n_splits * (hd + 2);
+  auto up2 = [](size_t n) { return (n + 1) & ~size_t(1); };   // keep every vector 16-byte aligned
+  const size_t ll_words = 2 * (up2(H) + up2(H) + up2(qn + 2 * kvn) + up2(qn) + up2(F) + up2(n_rec));
+  mg->ll_bytes = ll_words * sizeof(u64);
+  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_prof, prof_n * sizeof(long long)) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_ll, mg->ll_bytes) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
+  const unsigned epoch0[1] = {1u};
   cudaError_t e = cudaMemcpyAsync(mg->d_tables, tab.data(), tables_bytes, cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 512 + 16 * (size_t)ctx->sm_count, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_fx, 0, ((size_t)qn / 64 + (size_t)F / 64) * 256, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 256, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(mg->d_sync, epoch0, sizeof epoch0, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_ll, 0, mg->ll_bytes, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, prof_n * sizeof(long long), ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab and epoch0 are locals
   if (e != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: table upload failed: %s", cudaGetErrorString(e));
@@ -1422,27 +1289,36 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.tables = mg->d_tables;
   a.tables_bytes = tables_bytes;
   a.n_layers = d->n_layers;
-  a.stages = stages;
+  a.n_slots = n_slots;
   a.slot_bytes = slot_bytes;
   a.x_bytes = x_bytes;
   a.n_q = nq; a.n_kv = nkv; a.hd = hd; a.n_splits = n_splits;
+  a.split_from = 320;
+  if (const char* e2 = getenv("KSEARCH_MEGA_SPLIT_FROM")) a.split_from = (unsigned)atoi(e2);
   a.eps = d->eps; a.attn_scale = d->attn_scale;
   a.rope = d->rope; a.pos = d->pos;
-  a.x_a = d->x_a; a.x_b = d->x_b;
-  a.yb = d->yb; a.q = d->q; a.k = d->k; a.v = d->v;
-  a.ox = mg->d_fx;
-  a.ffx = mg->d_fx + (size_t)qn / 64 * 256;
-  a.att_tmp = d->att_tmp;
-  a.bar = mg->d_sync;
-  a.att_cnt = mg->d_sync + 64;
-  a.nsum = reinterpret_cast<float4*>(mg->d_sync + 128);
+  a.x_in = d->x_a;
+  a.resid_out = d->x_b;
+  a.y_out = d->yb;
+  {
+    u64* p = mg->d_ll;
+    auto take = [&](size_t n) { u64* r = p; p += up2(n); return r; };
+    a.ll_yd0 = take(H); a.ll_yd1 = take(H);
+    a.ll_yo0 = take(H); a.ll_yo1 = take(H);
+    a.ll_qkv0 = take(qn + 2 * kvn); a.ll_qkv1 = take(qn + 2 * kvn);
+    a.ll_ox0 = take(qn); a.ll_ox1 = take(qn);
+    a.ll_ff0 = take(F); a.ll_ff1 = take(F);
+    a.ll_rec0 = take(n_rec); a.ll_rec1 = take(n_rec);
+  }
+  a.epoch = mg->d_sync;
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
-  a.prof = mg->d_prof;
+  a.poll_limit = 1u << 21;  // a second or two of polling at most
+  a.test_stall = 0;
+  a.prof = getenv("KSEARCH_PROFILE") ? mg->d_prof : nullptr;
   mg->grid = grid;
-  mg->smem = mg_smem(x_bytes, slot_bytes, stages, tables_bytes).total;
-  mg->G = (int)G;
+  mg->smem = mg_smem(x_bytes, slot_bytes, n_slots, tables_bytes).total;
   mg->dpl = (int)(hd / 32);
-  mg->pc = H <= 2048 ? 2 : 4;
+  mg->pc = H <= 4u * MG_THREADS ? 1 : 2;
   mg->residual = d->x_b;
   *out = mg;
   return KS_OK;

@@ -912,11 +912,31 @@ const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
   const size_t ab = ks_act_bytes((ks_dtype)m->cfg.act);
   if (which == 0) return (const char*)m->x + (size_t)slot * m->cfg.hidden * ab;
   if (which == 1) return (const char*)m->logits + (size_t)slot * m->cfg.vocab * ab;
-  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][5 * n_layers][4] int64
+  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][n_layers][5][4] int64
     auto it = m->mega.find(slot);
     return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof(it->second);
   }
   return nullptr;
+}
+
+// Knobs of a slot's persistent decode kernel, for tests and for the phase-clock reader: what = 0 polls before
+// a device-side wait gives up, 1 = make one stage of every layer wait for a tag nobody writes (exercises the
+// give-up path; 0 switches it off), 2 = context length from which attention is split across blocks,
+// 3 = record phase clocks (0 / 1).  Builds the kernel if the slot has none yet; drops the captured graphs.
+int ks_model_debug_set(ks_model* m, int slot, int what, unsigned value) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  if (slot < 0 || slot >= m->cfg.n_slots) return ks_fail(c, KS_ERR_STATE, "bad SlotId");
+  ks_mega* mg = nullptr;
+  int rc = get_mega(m, slot, &mg);
+  if (rc) return rc;
+  if (!mg) return ks_fail(c, KS_ERR_UNSUPPORTED, "this model shape does not use the persistent decode kernel");
+  if ((rc = ks_mega_set(mg, what, value))) return ks_fail(c, rc, "debug_set: unknown knob %d", what);
+  cudaStreamSynchronize(c->stream);
+  for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
+  m->graphs.clear();
+  m->graph_nodes.clear();
+  return KS_OK;
 }
 
 // Device address of one slot's rows of a layer's cache ([max_seq, n_kv, hd] Q4_0); which: 0 = K, 1 = V.

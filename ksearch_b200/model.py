@@ -207,6 +207,26 @@ class GemmaCudaModel:
         self.lib.ks_buf_free(self.ctx.h, buf)
         return out.view(np.float32 if self.cfg.act == F32 else np.float16).astype(np.float32)
 
+    POLL_LIMIT, STALL, SPLIT_FROM, PHASE_CLOCKS = 0, 1, 2, 3
+
+    def debug_set(self, what: int, value: int, slot: int = 0):
+        """Knobs of the slot's persistent decode kernel (ks_model_debug_set)."""
+        self.ctx.check(self.lib.ks_model_debug_set(self.h, slot, what, value))
+
+    def phase_clocks(self, slot: int = 0) -> np.ndarray:
+        """SM clock stamps of the last token, int64 [2 (first, last block)][n_layers][5 (qkv, attention, o-proj,
+        gate-up, down)][4 (phase entered, input staged, items done, rows stored)]; recorded only after
+        debug_set(PHASE_CLOCKS, 1) or with KSEARCH_PROFILE set (gemma_prim.rs:885)."""
+        ptr = self.lib.ks_model_debug_ptr(self.h, 2, slot)
+        if not ptr:
+            raise KsError(_lib.ERR_STATE, "the persistent decode kernel has not run for this slot")
+        n = 2 * self.cfg.n_layers * 5 * 4
+        buf = self.lib.ks_buf_wrap(self.ctx.h, ptr, n * 8)
+        out = np.empty(n, np.int64)
+        self.ctx.check(self.lib.ks_buf_download(self.ctx.h, buf, 0, out.ctypes.data, n * 8))
+        self.lib.ks_buf_free(self.ctx.h, buf)
+        return out.reshape(2, self.cfg.n_layers, 5, 4)
+
     def _kv_buf(self, layer: int, which: int, slot: int):
         ptr = self.lib.ks_model_kv_ptr(self.h, layer, which, slot)
         if not ptr:

@@ -19,14 +19,16 @@ def _teacher_forced(model, cpu, tokens, slot=0):
         got = model.read_debug(1, slot).astype(np.float64)
         cpu.forward_token(int(t), True)
         want = cpu.logits().astype(np.float64)
-        # Logits of a 3-layer stack: a KV nibble that sits on a rounding boundary may round the other
-        # way on the GPU (its inputs differ in the last ulp), which moves a few logits by a fraction of
-        # a percent; the bulk must agree far more closely.
+        # The per-op bar carried to the logits: 1e-3 of the logit scale at worst, 1e-4 rms.  (A Q4_0
+        # value of a new K/V row that sits exactly on a rounding boundary could round the other way on
+        # the GPU and move a few logits by more; test_logits_tight_when_kv_bytes_agree counts those
+        # events -- none occur on these seeds.)
         scale = np.abs(want).max()
         err = np.abs(got - want)
         worst = max(worst, err.max() / scale)
-        assert err.max() <= 2e-2 * scale, f"logits differ: {err.max()} on scale {scale}"
-        assert np.sqrt((err ** 2).mean()) <= 2e-3 * scale
+        assert err.max() <= 1e-3 * scale, f"logits differ: {err.max()} on scale {scale}"
+        assert np.sqrt((err ** 2).mean()) <= 1e-4 * scale
+    print(f"[teacher-forced] worst logit error {worst:.2e} of the logit scale over {len(tokens)} tokens")
     return worst
 
 
@@ -91,7 +93,7 @@ def test_slots_advance_together(ctx, oracle):
         for s in range(4):
             got = model.read_debug(1, s).astype(np.float64)
             want = want_logits[s][j]
-            assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max(), (j, s)
+            assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (j, s)
     assert [model.seq_len(s) for s in range(4)] == [l + 5 for l in lens]
     model.slot_free(1)
     assert model.active_batch() == 3 and model.slot_alloc() == 1       # reuses the freed slot (KV:232-249)
@@ -183,8 +185,43 @@ def test_persistent_kernel_long_context(oracle, monkeypatch):
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=23, keep=True)
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
+    model.debug_set(model.SPLIT_FROM, 8)     # split contexts from 9 positions on (the default keeps short ones in one block)
     _teacher_forced(model, cpu, synth.token_ids(23, "tf", 300, cfg.vocab))
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
+    cpu.close()
+    model.close()
+    c.close()
+
+
+def test_device_wait_gives_up_and_recovers(oracle, monkeypatch):
+    """A bounded device-side wait that runs out: one stage of the persistent kernel is told to wait for a
+    value nobody writes, with a limit of 2000 polls.  Nothing faults or hangs: every block stops waiting
+    within microseconds, the kernel ends, the blocking calls report KS_ERR_TIMEOUT and rewind the slot, and
+    after a slot reset the next tokens match the CPU decoder again."""
+    from ksearch_b200 import CudaContext, _lib
+    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    c = CudaContext(0, flags=1)
+    cfg = ksm.tiny_config(max_seq=48)
+    model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=27, keep=True)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    model.slot_alloc()
+    toks = synth.token_ids(27, "tf", 12, cfg.vocab)
+    _teacher_forced(model, cpu, toks[:4])
+    model.debug_set(model.POLL_LIMIT, 2000)
+    model.debug_set(model.STALL, 1)
+    n_before = model.seq_len(0)
+    with pytest.raises(KsError) as ei:                       # blocking step: the status comes back with the token
+        model.decode_token([int(toks[4])])
+    assert ei.value.code == _lib.ERR_TIMEOUT
+    assert model.seq_len(0) == n_before                      # rewound
+    model.forward(0, 1, [int(toks[4])], True)                # enqueue-only step: the status shows at the next synchronize
+    with pytest.raises(KsError) as ei:
+        c.synchronize()
+    assert ei.value.code == _lib.ERR_TIMEOUT
+    c.synchronize()                                          # the status word was cleared
+    model.debug_set(model.STALL, 0)
+    model.debug_set(model.POLL_LIMIT, 1 << 21)
+    _teacher_forced(model, cpu, toks)                        # resets the slot, then matches again
     cpu.close()
     model.close()
     c.close()
@@ -232,6 +269,9 @@ def test_e2b_like_shapes(oracle, monkeypatch, decode_kernel):
     out, _ = model.generate_timed(prompt, 24)
     equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 24 and ties <= 1
+    if decode_kernel == "1":     # the same shapes with the context split across blocks and merged
+        model.debug_set(model.SPLIT_FROM, 8)
+        _teacher_forced(model, cpu, synth.token_ids(25, "tf2", 70, cfg.vocab))
     cpu.close()
     model.close()
     c.close()
@@ -334,7 +374,7 @@ def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
             want = cpu.logits().astype(np.float64)
             scale = np.abs(want).max()
             err = np.abs(got - want)
-            assert err.max() <= 2e-2 * scale and np.sqrt((err ** 2).mean()) <= 2e-3 * scale
+            assert err.max() <= 1e-3 * scale and np.sqrt((err ** 2).mean()) <= 1e-4 * scale
     with pytest.raises(KsError, match="max_seq exceeded"):
         model.prefill(0, [1] * 200)
     cpu.close()
