@@ -276,6 +276,36 @@ int ks_model_debug_set(ks_model* m, int slot, int what, unsigned value);
 void* ks_model_kv_ptr(const ks_model* m, int layer, int which, int slot);
 size_t ks_model_kv_slot_bytes(const ks_model* m);                            /* bytes of one slot in one layer's K (or V) */
 
+/* ---- row-sharded matvec over the GPUs of one box -------------------------------------------------
+ * No counterpart in the reference: crates/ksearch_metal/src/lib.rs:33 takes the system default device and
+ * nothing there spans devices.  One process and one ks_ctx per GPU.  The matrices served are the reference's
+ * largest matvecs, the tied lm_head (GP:1222-1242) and the FFN projections (GP:1130-1157); rank k owns a
+ * contiguous run of rows = a contiguous byte range of the GGUF tensor, x is replicated, ONE exchange follows.
+ * Everything is enqueued on the context's stream (no host synchronisation; capturable in a ks_graph). */
+typedef struct ks_comm ks_comm;
+#define KS_COMM_ID_BYTES 128
+enum { KS_GATHER_NONE = 0, KS_GATHER_NCCL = 1 };
+/* Rank 0 creates the 128-byte rendezvous id and hands it to the other ranks over any host channel. */
+int ks_comm_unique_id(void* id_out);
+/* Collective: every rank calls it with the same id.  n_ranks == 1 needs no id and no NCCL. */
+ks_comm* ks_comm_init(ks_ctx* ctx, int n_ranks, int rank, const void* unique_id);
+void ks_comm_destroy(ks_comm* comm);
+int ks_comm_rank(const ks_comm* comm);
+int ks_comm_size(const ks_comm* comm);
+/* all[all_off + r*count .. ] of every rank <- rank r's slot of the same buffer (in-place all-gather, f32). */
+int ks_comm_all_gather_f32(ks_comm* comm, ks_buf* all, size_t all_off, size_t count);
+/* y_all[y_off + rank*rows_per_rank + i] = W_local[i] . x for this rank's rows_local (<= rows_per_rank) rows,
+ * then (gather == KS_GATHER_NCCL) the in-place all-gather of the slots.  f32 x and y, one token. */
+int ks_matvec_sharded(ks_comm* comm, size_t rows_local, size_t rows_per_rank, size_t cols, ks_dtype wdtype,
+                      const ks_buf* W_local, size_t w_byte_off, const ks_buf* x, size_t x_off, ks_buf* y_all,
+                      size_t y_off, int gather);
+/* Greedy token from row-sharded logits (K:1966 softcap_argmax over the whole vocabulary): arg-max of this
+ * rank's rows_local logits, all-gather of one (value, index) pair per rank, merge with ties to the lower
+ * index (crates/ksearch_codegen/src/render.rs:2355).  row0: global index of this rank's first logit.
+ * Every rank gets the same index, as one f32. */
+int ks_argmax_sharded(ks_comm* comm, size_t rows_local, size_t row0, float cap, const ks_buf* logits_local,
+                      size_t logits_off, ks_buf* out_idx, size_t out_off);
+
 #ifdef __cplusplus
 }
 #endif

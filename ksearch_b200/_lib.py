@@ -95,6 +95,14 @@ SIGNATURES = {
     "ks_model_generate": (_i, [_vp, _i, _vp, _i, _i, _i, _vp, _vp]),
     "ks_model_debug_ptr": (_vp, [_vp, _i, _i]),
     "ks_model_debug_set": (_i, [_vp, _i, _i, C.c_uint]),
+    "ks_comm_unique_id": (_i, [_vp]),
+    "ks_comm_init": (_vp, [_vp, _i, _i, _vp]),
+    "ks_comm_destroy": (None, [_vp]),
+    "ks_comm_rank": (_i, [_vp]),
+    "ks_comm_size": (_i, [_vp]),
+    "ks_comm_all_gather_f32": (_i, [_vp, _vp, _sz, _sz]),
+    "ks_matvec_sharded": (_i, [_vp, _sz, _sz, _sz, _i, _vp, _sz, _vp, _sz, _vp, _sz, _i]),
+    "ks_argmax_sharded": (_i, [_vp, _sz, _sz, _f, _vp, _sz, _vp, _sz]),
     "ks_model_kv_ptr": (_vp, [_vp, _i, _i, _i]),
     "ks_model_kv_slot_bytes": (_sz, [_vp]),
 }

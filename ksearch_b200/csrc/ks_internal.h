@@ -158,7 +158,8 @@ struct ks_mega;
 int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* layers, ks_mega** out);
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg);
 float* ks_mega_residual(const ks_mega* mg);  // where the residual stream is when the kernel ends (yb holds the last down-proj)
-const long long* ks_mega_prof(const ks_mega* mg);  // [2][n_layers][5][4] clock stamps of the last token (first, last block)
+const long long* ks_mega_prof(const ks_mega* mg);  // [2][n_layers][5][8] clock stamps of the last token (first, last block)
+const long long* ks_mega_prof_all(const ks_mega* mg);  // [grid][n_layers][5][8]: every block's stamps (globaltimer ns)
 int ks_mega_reset(ks_ctx* ctx, ks_mega* mg);  // working order again after a timed-out wait
 int ks_mega_set(ks_mega* mg, int what, unsigned value);  // test / profiling knobs, see ks_mega.cu
 void ks_mega_destroy(ks_mega* mg);

@@ -15,11 +15,12 @@
 //     of every matvec phase, so its weights are ONE contiguous byte range per matrix and phase.
 //   * The weight stream never stops: those ranges are cut into pieces that fit a slot of a
 //     block-wide shared-memory ring fed by cp.async.bulk (mbarrier completion).  The pieces of all
-//     phases and layers form one sequence; the last warp to finish with a slot refills it with the
-//     piece n_slots further down the sequence, so the next phases' (and layer's) weights arrive
-//     while the block computes or waits for its inputs.
-//   * Inside a phase an item is 4 rows x one column segment; items go to the 16 warps round-robin,
-//     partial sums meet in shared memory, thread f finishes row f.
+//     phases and layers form one sequence; when the block is done with a slot, a lane of its last warp
+//     refills it with the piece n_slots further down the sequence, so the next phases' (and layer's)
+//     weights arrive while the block computes or waits for its inputs.
+//   * Inside a phase a task is one row x one 32-unit column segment (a lane owns one 64-weight unit
+//     and keeps that unit of x in registers); each warp takes one contiguous run of the block's tasks,
+//     two rows interleaved; row sums meet in shared memory, thread f finishes row f.
 //   * x is staged once per phase and block as 24-bit block fixed point (three byte planes per
 //     32-element sub-block) so weight nibbles x x are exact dp4a integer sums.
 //   * The residual stream never leaves the block: every block applies the same residual-add + norm
@@ -39,9 +40,15 @@
 namespace {
 
 enum { PH_QKV = 0, PH_OPROJ = 1, PH_GATEUP = 2, PH_DOWN = 3, PH_KINDS = 4 };
-enum { PF_QKV = 0, PF_ATTN = 1, PF_OPROJ = 2, PF_GATEUP = 3, PF_DOWN = 4, PF_PER_LAYER = 5 };
+enum { PF_QKV = 0, PF_ATTN = 1, PF_OPROJ = 2, PF_GATEUP = 3, PF_DOWN = 4, PF_PER_LAYER = 5, PF_STAMPS = 8 };
 
-constexpr int MG_THREADS = 512, MG_NW = 16;
+#ifndef MG_NW_CFG
+#define MG_NW_CFG 8
+#endif
+#ifndef MG_FN
+#define MG_FN __forceinline__
+#endif
+constexpr int MG_NW = MG_NW_CFG, MG_THREADS = MG_NW * 32;  // warps per block (at least 8)
 constexpr int MG_MAXPIECE = 64;   // pieces of one layer owned by one block
 constexpr int MG_MAXROWS = 96;    // rows of one phase owned by one block
 constexpr int MG_MAXC = 8;        // column segments per row
@@ -53,7 +60,7 @@ struct MegaPhase {          // one matvec phase of a layer; the same for every l
   unsigned mats;            // matrices multiplied per row (gate-up: 2, gate row i and up row i)
   unsigned seg_start[4];    // first row of each matrix in the row space; [n_seg] = total rows
   unsigned widx;            // MegaLayer::W index of the first matrix
-  unsigned cols, row_bytes, seg_blocks, n_cseg, piece_rows;
+  unsigned cols, row_bytes, seg_units, n_cseg, piece_rows;  // n_cseg column segments of seg_units (<= 32) 64-weight units
 };
 
 struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
@@ -94,8 +101,9 @@ struct MegaArgs {
   unsigned* err;
   unsigned poll_limit;      // polls of one wait before it gives up
   unsigned test_stall;      // test hook: added to the tag the gate-up stage waits for (a tag nobody writes)
-  long long* prof;          // optional [2][n_layers][5][4] SM clocks of the first and last block: phase entered, x staged,
-                            // items done, rows stored
+  long long* prof_all;      // optional [grid][n_layers][5][2]: thread 0 of every block, (phase entered, rows stored)
+  long long* prof;          // optional [2][n_layers][5][8] SM clocks of the first and last block (thread 0): see the PF_* rows;
+                            // matvec phases: entered, inputs arrived, x staged, tasks done, block joined, row stored; attention: entered, q arrived, q/k/v built, positions done, folded, -, stored, left
 };
 
 __device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -143,6 +151,14 @@ __device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ long long gtime() {  // nanoseconds, the same clock on every SM
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ unsigned ll_tag(u64 w) { return (unsigned)(w >> 32); }
 __device__ __forceinline__ float ll_val(u64 w) { return __uint_as_float((unsigned)w); }
 
@@ -152,7 +168,7 @@ struct Poll {
   bool gave_up;  // this thread stopped waiting (its own wait ran out, or it saw the status word raised)
 };
 // After a failed tag check: may the wait go on?
-__device__ __forceinline__ bool poll_again(Poll& pl, unsigned& it) {
+__device__ __noinline__ bool poll_again(Poll& pl, unsigned& it) {
   if (pl.gave_up) return false;
   if (++it >= pl.limit) {
     atomicOr(const_cast<unsigned*>(pl.err), 2u);
@@ -165,7 +181,9 @@ __device__ __forceinline__ bool poll_again(Poll& pl, unsigned& it) {
   }
   return true;
 }
-// N chunks of 4 consecutive values (32 bytes, 16-byte aligned): every load is issued before any is checked.
+// N chunks of 4 consecutive values (32 bytes, 16-byte aligned).  Every load is issued before any is checked,
+// and every chunk that is still stale is re-read in the SAME round: a thread that came early pays one round
+// trip per round, not one per chunk.
 template <int N>
 __device__ __forceinline__ void ll_wait_chunks(const u64* base, const unsigned (&c)[N], const bool (&live)[N], unsigned tag,
                                                float4 (&v)[N], Poll& pl) {
@@ -176,17 +194,25 @@ __device__ __forceinline__ void ll_wait_chunks(const u64* base, const unsigned (
       ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
       ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
     }
+  unsigned it = 0;
+  for (;;) {
+    bool stale[N], any = false;
 #pragma unroll
-  for (int k = 0; k < N; k++)
-    if (live[k]) {
-      unsigned it = 0;
-      while (!(ll_tag(w[k][0]) == tag && ll_tag(w[k][1]) == tag && ll_tag(w[k][2]) == tag && ll_tag(w[k][3]) == tag) &&
-             poll_again(pl, it)) {
+    for (int k = 0; k < N; k++) {
+      stale[k] = live[k] && !(ll_tag(w[k][0]) == tag && ll_tag(w[k][1]) == tag && ll_tag(w[k][2]) == tag && ll_tag(w[k][3]) == tag);
+      any = any || stale[k];
+    }
+    if (!any || !poll_again(pl, it)) break;
+#pragma unroll
+    for (int k = 0; k < N; k++)
+      if (stale[k]) {
         ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
         ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
       }
-      v[k] = make_float4(ll_val(w[k][0]), ll_val(w[k][1]), ll_val(w[k][2]), ll_val(w[k][3]));
-    }
+  }
+#pragma unroll
+  for (int k = 0; k < N; k++)
+    if (live[k]) v[k] = make_float4(ll_val(w[k][0]), ll_val(w[k][1]), ll_val(w[k][2]), ll_val(w[k][3]));
 }
 
 // ---- x as 24-bit block fixed point, weights x x as byte dot products ----------------------------
@@ -203,7 +229,7 @@ __device__ __forceinline__ void ll_wait_chunks(const u64* base, const unsigned (
 constexpr int MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
 constexpr unsigned MG_XU = 80;        // bytes per unit and plane
 // Chunk c = elements 4c..4c+3; the 8 lanes that hold one sub-block's chunks are neighbours, all 32 lanes call.
-__device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, unsigned c, float4 v) {
+__device__ __noinline__ void fx_put_chunk(unsigned char* xs, unsigned units, unsigned c, float4 v) {
   const unsigned e = c << 2;
   const unsigned u = e >> 6, hi = (e >> 5) & 1u, l = e & 31u;
   float s = (v.x + v.y) + (v.z + v.w);
@@ -265,62 +291,53 @@ __device__ __forceinline__ void fx_plane(const uint32_t (&lo)[8], const uint32_t
     ahi = (int)h;
   }
 }
-// Multiply-accumulate one item against the fixed-point x.  base: shared address of the item's first
-// row at its column segment; rows are row_bytes apart; the second matrix (MATS == 2) sits mat2_off on.
-// The masked nibbles of a unit stay in registers while the three planes of x pass by.
-template <int MATS>
-__device__ __forceinline__ void mg_item_compute_fx(uint32_t base, uint32_t row_bytes, uint32_t mat2_off, uint32_t xs_s,
-                                                   unsigned units, unsigned seg_units, unsigned cs, int cl, int rl,
-                                                   float (&yacc)[2]) {
-  const int g = cl & 3;
-  const unsigned upl = seg_units / MG_LPR;
+// This lane's unit of the staged x: three byte planes of 16 words and (sum_lo, sum_hi, s_lo, s_hi).
+struct XUnit {
+  uint4 p[12];
+  float4 mt;
+};
+__device__ __forceinline__ void fx_load_unit(XUnit& x, uint32_t xs_s, unsigned units, unsigned u) {
   const uint32_t plane = units * MG_XU;
-  uint32_t waddr = base + (uint32_t)rl * row_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
-  uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * MG_XU;
-  uint32_t maddr = xs_s + 3u * plane + (cs * seg_units + (unsigned)cl) * 16u;
-  for (unsigned it = 0; it < upl; it++) {
-    uint32_t lo[MATS][8], hi[MATS][8];
-    int a0l[MATS], a0h[MATS], a1l[MATS], a1h[MATS], a2l[MATS], a2h[MATS];
+  const uint32_t xa = xs_s + u * MG_XU;
 #pragma unroll
-    for (int r = 0; r < MATS; r++) {
-      const uint32_t wa = waddr + (uint32_t)r * mat2_off;
-      const uint4 q0 = lds_u4o<16>(wa), q1 = lds_u4o<32>(wa);
-      const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+  for (int k = 0; k < 3; k++) {
+    x.p[4 * k + 0] = lds_u4o<0>(xa + k * plane);
+    x.p[4 * k + 1] = lds_u4o<16>(xa + k * plane);
+    x.p[4 * k + 2] = lds_u4o<32>(xa + k * plane);
+    x.p[4 * k + 3] = lds_u4o<48>(xa + k * plane);
+  }
+  x.mt = lds_f4o<0>(xs_s + 3u * plane + u * 16u);
+}
+// R rows at once against the unit this lane holds: wa[r] is the shared address of row r's unit (its 32
+// nibble bytes sit 16 bytes after the block header at wa[r] - g * 32).  The rows' instruction streams are
+// independent, which is what keeps a warp busy while each row's dp4a chains and loads are in flight.
+template <int R>
+__device__ __forceinline__ void fx_rows(const uint32_t (&wa)[R], int g, const XUnit& x, float (&out)[R]) {
+  uint32_t lo[R][8], hi[R][8];
+  int a0l[R], a0h[R], a1l[R], a1h[R], a2l[R], a2h[R];
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        lo[r][i] = q[i] & 0x0F0F0F0Fu;
-        hi[r][i] = (q[i] >> 4) & 0x0F0F0F0Fu;
-      }
-      a0l[r] = a0h[r] = a1l[r] = a1h[r] = a2l[r] = a2h[r] = 0;
+  for (int r = 0; r < R; r++) {
+    const uint4 q0 = lds_u4o<16>(wa[r]), q1 = lds_u4o<32>(wa[r]);
+    const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      lo[r][i] = q[i] & 0x0F0F0F0Fu;
+      hi[r][i] = (q[i] >> 4) & 0x0F0F0F0Fu;
     }
-    {
-      const uint4 x0 = lds_u4o<0>(xaddr), x1 = lds_u4o<16>(xaddr), x2 = lds_u4o<32>(xaddr), x3 = lds_u4o<48>(xaddr);
+    a0l[r] = a0h[r] = a1l[r] = a1h[r] = a2l[r] = a2h[r] = 0;
+  }
 #pragma unroll
-      for (int r = 0; r < MATS; r++) fx_plane<false>(lo[r], hi[r], x0, x1, x2, x3, a0l[r], a0h[r]);
-    }
-    {
-      const uint32_t xa = xaddr + plane;
-      const uint4 x0 = lds_u4o<0>(xa), x1 = lds_u4o<16>(xa), x2 = lds_u4o<32>(xa), x3 = lds_u4o<48>(xa);
+  for (int r = 0; r < R; r++) fx_plane<false>(lo[r], hi[r], x.p[0], x.p[1], x.p[2], x.p[3], a0l[r], a0h[r]);
 #pragma unroll
-      for (int r = 0; r < MATS; r++) fx_plane<false>(lo[r], hi[r], x0, x1, x2, x3, a1l[r], a1h[r]);
-    }
-    {
-      const uint32_t xa = xaddr + 2u * plane;
-      const uint4 x0 = lds_u4o<0>(xa), x1 = lds_u4o<16>(xa), x2 = lds_u4o<32>(xa), x3 = lds_u4o<48>(xa);
+  for (int r = 0; r < R; r++) fx_plane<false>(lo[r], hi[r], x.p[4], x.p[5], x.p[6], x.p[7], a1l[r], a1h[r]);
 #pragma unroll
-      for (int r = 0; r < MATS; r++) fx_plane<true>(lo[r], hi[r], x0, x1, x2, x3, a2l[r], a2h[r]);
-    }
-    const float4 mt = lds_f4o<0>(maddr);
+  for (int r = 0; r < R; r++) fx_plane<true>(lo[r], hi[r], x.p[8], x.p[9], x.p[10], x.p[11], a2l[r], a2h[r]);
 #pragma unroll
-    for (int r = 0; r < MATS; r++) {
-      const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)r * mat2_off - (uint32_t)g * 32u);
-      const float flo = fmaf((float)a2l[r], 65536.0f, fmaf((float)(unsigned)a1l[r], 256.0f, (float)(unsigned)a0l[r])) * mt.z;
-      const float fhi = fmaf((float)a2h[r], 65536.0f, fmaf((float)(unsigned)a1h[r], 256.0f, (float)(unsigned)a0h[r])) * mt.w;
-      yacc[r] = q4k_apply_scales(hdr, g, flo, fhi, mt.x, mt.y, yacc[r]);
-    }
-    waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
-    xaddr += MG_LPR * MG_XU;
-    maddr += MG_LPR * 16u;
+  for (int r = 0; r < R; r++) {
+    const uint4 hdr = lds_u4o<0>(wa[r] - (uint32_t)g * 32u);
+    const float flo = fmaf((float)a2l[r], 65536.0f, fmaf((float)(unsigned)a1l[r], 256.0f, (float)(unsigned)a0l[r])) * x.mt.z;
+    const float fhi = fmaf((float)a2h[r], 65536.0f, fmaf((float)(unsigned)a1h[r], 256.0f, (float)(unsigned)a0h[r])) * x.mt.w;
+    out[r] = q4k_apply_scales(hdr, g, flo, fhi, x.mt.x, x.mt.y, 0.0f);
   }
 }
 
@@ -339,7 +356,7 @@ __device__ __forceinline__ float4 block_sum4(float4 v, float4* red) {
   if (lane == 0) red[warp] = v;
   __syncthreads();
   float4 t = red[0];
-#pragma unroll
+#pragma unroll 1
   for (int w = 1; w < MG_NW; w++) {
     const float4 u = red[w];
     t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
@@ -347,19 +364,26 @@ __device__ __forceinline__ float4 block_sum4(float4 v, float4* red) {
   return t;
 }
 
+// Per-thread wait state, carried through the phase functions in one word (they are separate,
+// non-inlined functions so that each gets the whole register budget; everything block-wide lives in
+// shared memory): bits 0-7 ring slot of the next piece, bit 8 its mbarrier parity, bit 9 this warp
+// stopped waiting for weight copies, bit 10 this thread stopped waiting for other blocks.
+constexpr unsigned ST_DEAD = 1u << 9, ST_GAVE_UP = 1u << 10;
+
 // The hidden vector of a phase that starts with a norm.  Thread t owns chunks t and t + 512 (4 elements
-// each) of the residual stream in registers (xr), for the whole token.
+// each) of the residual stream; it keeps them in shared memory (xres) between phases.
 //   add == false (first layer):  x' = rms(x) * w
 //   add == true:  r = x + rms(y) * wp (K:539; both RMS factors come from ONE block-wide sum:
-//                 sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2);  x' = rms(r) * w;  xr = r.
+//                 sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2);  x' = rms(r) * w;  xres = r.
 template <int PC>
-__device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, bool add, unsigned cols, float4 (&xr)[PC],
-                                                const u64* ysrc, unsigned tag, const float* w, const float* wp, float eps,
-                                                float* resid_out, Poll& pl) {
+__device__ MG_FN unsigned mg_stage_hidden(unsigned char* xs, float4* red, float* xres, bool add, unsigned cols,
+                                                 const u64* ysrc, unsigned tag, const float* w, const float* wp, float eps,
+                                                 float* resid_out, const unsigned* err, unsigned limit, unsigned st, long long* pf) {
+  Poll pl{err, limit, (st & ST_GAVE_UP) != 0u};
   const unsigned units = cols >> 6, nchunk = cols >> 2;
   unsigned c[PC];
   bool live[PC];
-  float4 wv[PC], wpv[PC], yv[PC];
+  float4 wv[PC], wpv[PC], yv[PC], xr[PC];
 #pragma unroll
   for (int k = 0; k < PC; k++) {
     c[k] = threadIdx.x + k * MG_THREADS;
@@ -367,6 +391,7 @@ __device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, 
     if (live[k]) {  // constants of the model: in flight while the inputs are awaited
       wv[k] = reinterpret_cast<const float4*>(w)[c[k]];
       if (add) wpv[k] = reinterpret_cast<const float4*>(wp)[c[k]];
+      xr[k] = reinterpret_cast<const float4*>(xres)[c[k]];
     }
   }
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -390,6 +415,7 @@ __device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, 
         s.w = fmaf(x.x, x.x, s.w); s.w = fmaf(x.y, x.y, s.w); s.w = fmaf(x.z, x.z, s.w); s.w = fmaf(x.w, x.w, s.w);
       }
   }
+  if (pf) pf[1] = clock64();
   const float4 t = block_sum4(s, red);
   const float invn = 1.0f / (float)cols;
   float inv = 0.0f, inv2;
@@ -410,7 +436,7 @@ __device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, 
         r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(y.y, inv), p.y));
         r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(y.z, inv), p.z));
         r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(y.w, inv), p.w));
-        xr[k] = r;
+        reinterpret_cast<float4*>(xres)[c[k]] = r;
         if (resid_out) reinterpret_cast<float4*>(resid_out)[c[k]] = r;
       }
       const float4 w4 = wv[k];
@@ -421,10 +447,13 @@ __device__ __forceinline__ void mg_stage_hidden(unsigned char* xs, float4* red, 
       q.w = __fmul_rn(__fmul_rn(r.w, inv2), w4.w);
       fx_put_chunk(xs, units, c[k], q);
     }
+  return pl.gave_up ? (st | ST_GAVE_UP) : st;
 }
 
 // A vector other blocks produced (attention output, GeGLU output), staged as it is.
-__device__ __forceinline__ void mg_stage_plain(unsigned char* xs, unsigned cols, const u64* src, unsigned tag, Poll& pl) {
+__device__ MG_FN unsigned mg_stage_plain(unsigned char* xs, unsigned cols, const u64* src, unsigned tag, const unsigned* err,
+                                                unsigned limit, unsigned st, long long* pf) {
+  Poll pl{err, limit, (st & ST_GAVE_UP) != 0u};
   constexpr int XC = 4;
   const unsigned units = cols >> 6, nchunk = cols >> 2;
   for (unsigned base = 0; base < nchunk; base += XC * MG_THREADS) {
@@ -437,10 +466,12 @@ __device__ __forceinline__ void mg_stage_plain(unsigned char* xs, unsigned cols,
       live[k] = c[k] < nchunk;
     }
     ll_wait_chunks<XC>(src, c, live, tag, v, pl);
+    if (pf) pf[1] = clock64();
 #pragma unroll
     for (int k = 0; k < XC; k++)
       if (live[k]) fx_put_chunk(xs, units, c[k], v[k]);
   }
+  return pl.gave_up ? (st | ST_GAVE_UP) : st;
 }
 
 // ---- pieces -----------------------------------------------------------------------------------------
@@ -469,7 +500,7 @@ __device__ __forceinline__ bool build_pieces(Piece* pieces, PhInfo* info, const 
         p.nrows = (uint16_t)n;
         p.row0 = (uint16_t)rows;
         p.item0 = (uint16_t)items;
-        p.n_items = (uint16_t)(((n + 3u) / 4u) * ph.n_cseg);
+        p.n_items = 0;
         p.kind = (uint8_t)kind;
         p.widx = (uint8_t)(ph.widx + s);
         p.pad[0] = p.pad[1] = 0;
@@ -553,148 +584,181 @@ __device__ __forceinline__ int mg_lane_dim(int lane, int j) {
   return j < BPL ? base + j : base + 16 + (j - BPL);
 }
 
+constexpr int MG_AB = 8;  // positions of one warp in flight together
+
 // Shared memory the attention phase needs (it reuses the x staging area).
 __host__ __device__ inline unsigned mg_att_bytes(unsigned hd) {
-  return (unsigned)MG_NW * (hd + 2u) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 8u * MG_MAX_SPLITS + 32u;
+  const unsigned rowb = (hd / 32u) * KS_Q40_BLOCK_BYTES;
+  return (unsigned)MG_NW * (hd + 2u) * 4u + 2u * (rowb + 16u) + 8u * MG_MAX_SPLITS + 12u * hd + 4u * MG_NW +
+         (unsigned)MG_NW * MG_AB * 2u * rowb + 32u;
 }
 
-// Splits in use for a context of tlen positions.  A split costs a hop through L2 (records out, merge
-// in the head's first block), which is worth it only once a single block's 16 warps would each walk
-// many positions.
+// Splits in use for a context of tlen positions: a warp walks at most four positions (one batch of
+// loads in flight) until every split is in use.  A split costs a hop through L2 (records out, merge in
+// the head's first block); contexts of up to split_from positions stay in one block.
 __host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits, unsigned split_from) {
   if (tlen <= split_from) return 1u;
-  unsigned ns = (tlen + 31u) / 32u;
+  unsigned ns = (tlen + 4u * MG_NW - 1u) / (4u * MG_NW);
   return ns < 1u ? 1u : ns > max_splits ? max_splits : ns;
 }
 
-// One block per (query head, context split).
-//   1. every warp builds the roped, normed, scaled q of the head in registers (each lane polls the q
-//      values it needs); in the block(s) of the split that holds the newest position, warps 0.. pack
-//      the new K row and warps 8.. the new V row to Q4_0 in shared memory (lower.rs:4231-4702), block
-//      pairs (b, b+NB/2) per warp because RoPE pairs those halves; the block of the KV group's first
-//      head stores them to the cache;
-//   2. warps take the positions of the split round-robin, online softmax per warp;
-//   3. the sixteen warps' (m, l, O) meet in shared memory, thread d folds dimension d;
+
+// What the attention phase needs, block-wide (read from shared memory).
+struct AttnArgs {
+  unsigned n_q, n_kv, n_splits, split_from;
+  float eps, attn_scale;
+  const float* rope;
+  const int* pos;
+  const unsigned* err;
+  unsigned limit;
+};
+
+// Sum of v over the first nw warps of the block (every thread of those warps calls, every thread gets the
+// total); red: MG_NW floats of scratch.  Fixed order.
+__device__ __forceinline__ float mg_rows_sum(float v, float* red, int nw) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = mg_warp_sum(v);
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.0f;
+  for (int w = 0; w < nw; w++) t += red[w];
+  return t;
+}
+
+// One block per (query head, context split).  The code is kept small on purpose (rolled loops, one
+// value per thread): it runs once per layer, so its instructions are fetched cold every time.
+//   0. each warp starts the loads of its first positions' packed K/V rows (cp.async into the scratch):
+//      they do not depend on this layer's q, so they travel while q is awaited;
+//   1. thread d awaits q[d] of the head (and k[d], v[d] in the block(s) of the split that holds the newest
+//      position), the block norms and ropes them (lower.rs:4231-4702): q stays in shared memory for the
+//      dot products, the new K / V rows are packed to Q4_0 (one warp per 32-value block) and the block of
+//      the KV group's first head stores them to the cache;
+//   2. warps take the positions of the split round-robin, four rows in flight, online softmax per warp;
+//   3. the warps' (m, l, O) meet in shared memory, thread d folds dimension d;
 //   4. one split: thread d stores the head's output; several: the block leaves a tagged (m, l, O[hd])
 //      record and the head's first block merges the records (lower.rs:5897-6088).
 template <int DPL>
-__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, const u64* qkv, u64* ox, u64* rec, unsigned tag,
-                                             unsigned char* sm, Poll& pl) {
+__device__ MG_FN unsigned mg_attention(const AttnArgs* ap, const MegaLayer* Lp, const u64* qkv, u64* ox, u64* rec, unsigned tag,
+                                       unsigned char* sm, unsigned st, long long* pf) {
   constexpr int HD = DPL * 32, HALF = HD / 2, NB = HD / 32;
   constexpr unsigned ROWB = NB * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned NSMAX = a.n_splits;
-  if (blockIdx.x >= a.n_q * NSMAX) return;
+  const unsigned NSMAX = ap->n_splits, n_q = ap->n_q, n_kv = ap->n_kv;
+  if (blockIdx.x >= n_q * NSMAX) return st;
   const unsigned head = blockIdx.x / NSMAX, split = blockIdx.x % NSMAX;
-  const unsigned G = a.n_q / a.n_kv, kvh = head / G;
-  const unsigned pos = (unsigned)a.pos[0], tlen = pos + 1;
-  const unsigned NS = mg_active_splits(tlen, NSMAX, a.split_from);
-  if (split >= NS) return;
+  const unsigned G = n_q / n_kv, kvh = head / G;
+  const unsigned pos = (unsigned)ap->pos[0], tlen = pos + 1;
+  const unsigned NS = mg_active_splits(tlen, NSMAX, ap->split_from);
+  if (split >= NS) return st;
+  Poll pl{ap->err, ap->limit, (st & ST_GAVE_UP) != 0u};
   const unsigned chunk = (tlen + NS - 1) / NS;
   const unsigned p0 = split * chunk, p1 = min(p0 + chunk, tlen);
   const bool owner = pos >= p0 && pos < p1;  // the split that holds the newest position
-  float* part = reinterpret_cast<float*>(sm);     // [16][HD + 2]
+  // scratch: part [NW][HD + 2] | skrow | svrow | ml [2 * MAX_SPLITS] | vec [3][HD] (q, k, v) | red [NW] | kvbuf
+  float* part = reinterpret_cast<float*>(sm);
   uint8_t* skrow = reinterpret_cast<uint8_t*>(part + MG_NW * (HD + 2));
   uint8_t* svrow = skrow + ROWB + 16u;
-  const float* cs = a.rope + (size_t)pos * HD;
-  const unsigned qn = a.n_q * HD, kvn = a.n_kv * HD;
+  float* ml = reinterpret_cast<float*>(svrow + ROWB + 16u);
+  float* vec = ml + 2 * MG_MAX_SPLITS;
+  float* red = vec + 3 * HD;
+  uint8_t* kvbuf = reinterpret_cast<uint8_t*>(red + MG_NW) + (size_t)warp * (MG_AB * 2u * ROWB);  // [MG_AB][K, V][ROWB]
+  const float* cs = ap->rope + (size_t)pos * HD;
+  const unsigned qn = n_q * HD, kvn = n_kv * HD;
+  const size_t rowstride = (size_t)n_kv * ROWB;
+  uint8_t* Kc = Lp->kv_k + (size_t)kvh * ROWB;
+  uint8_t* Vc = Lp->kv_v + (size_t)kvh * ROWB;
 
-  float qr[DPL];
+  // 0. the first batch of cached rows (the newest position's row does not exist yet: it comes from skrow / svrow)
+  auto prefetch_rows = [&](unsigned tb) {
+#pragma unroll 1
+    for (int i = 0; i < MG_AB; i++) {
+      const unsigned t = tb + (unsigned)(MG_NW * i);
+      if (t < p1 && t != pos && lane < (int)(ROWB / 8u)) {
+        cp_async8(sm32(kvbuf + (size_t)(2 * i) * ROWB) + (uint32_t)lane * 8u, Kc + (size_t)t * rowstride + (size_t)lane * 8u);
+        cp_async8(sm32(kvbuf + (size_t)(2 * i + 1) * ROWB) + (uint32_t)lane * 8u, Vc + (size_t)t * rowstride + (size_t)lane * 8u);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  prefetch_rows(p0 + (unsigned)warp);
+
+  // 1. q (and the new k, v): one value per thread
+  const int d = threadIdx.x;
+  const bool has = d < HD;  // whole warps: HD is a multiple of 32
   {
-    const int pb = warp & 7;  // block pair of the K / V job
-    const bool kjob = owner && warp < 8 && pb < NB / 2, vjob = owner && warp >= 8 && pb < NB / 2;
-    float qv[DPL], qw[DPL], qc[DPL], qs[DPL], rv[DPL], r_w0 = 0.f, r_w1 = 0.f, r_c = 0.f, r_s = 0.f;
-    const float* qnw = L.norm[1];
-#pragma unroll
-    for (int j = 0; j < DPL; j++) {
-      const int d = mg_lane_dim<DPL>(lane, j);
-      qw[j] = qnw[d];
-      qc[j] = cs[d & (HALF - 1)];
-      qs[j] = cs[HALF + (d & (HALF - 1))];
-    }
-    if (kjob) {
-      const float* w = L.norm[2];
-      r_w0 = w[32 * pb + lane];
-      r_w1 = w[HALF + 32 * pb + lane];
-      r_c = cs[32 * pb + lane];
-      r_s = cs[HALF + 32 * pb + lane];
-    }
-    {  // q of this head, then (K / V job) the whole new row: all loads first, then the checks
-      const u64* qsrc = qkv + (size_t)head * HD;
-      const u64* rsrc = qkv + qn + (kjob ? 0u : kvn) + (size_t)kvh * HD;
-      u64 wq[DPL], wr[DPL];
-#pragma unroll
-      for (int j = 0; j < DPL; j++) wq[j] = ll_load1(qsrc + mg_lane_dim<DPL>(lane, j));
-      if (kjob || vjob) {
-#pragma unroll
-        for (int j = 0; j < DPL; j++) wr[j] = ll_load1(rsrc + lane + 32 * j);
+    float qv = 0.f, kx = 0.f, vx = 0.f, qw = 0.f, kw = 0.f, c = 0.f, sn = 0.f;
+    if (has) {
+      qw = Lp->norm[1][d];
+      c = cs[d & (HALF - 1)];
+      sn = cs[HALF + (d & (HALF - 1))];
+      if (owner) kw = Lp->norm[2][d];
+      const u64* qp = qkv + (size_t)head * HD + d;
+      const u64* kp = qkv + qn + (size_t)kvh * HD + d;
+      const u64* vp = kp + kvn;
+      u64 wq = ll_load1(qp), wk = 0, wv = 0;
+      if (owner) {
+        wk = ll_load1(kp);
+        wv = ll_load1(vp);
       }
-#pragma unroll
-      for (int j = 0; j < DPL; j++) {
-        unsigned it = 0;
-        while (ll_tag(wq[j]) != tag && poll_again(pl, it)) wq[j] = ll_load1(qsrc + mg_lane_dim<DPL>(lane, j));
-        qv[j] = ll_val(wq[j]);
-      }
-      if (kjob || vjob) {
-#pragma unroll
-        for (int j = 0; j < DPL; j++) {
-          unsigned it = 0;
-          while (ll_tag(wr[j]) != tag && poll_again(pl, it)) wr[j] = ll_load1(rsrc + lane + 32 * j);
-          rv[j] = ll_val(wr[j]);
+      unsigned it = 0;
+      if (owner) {  // every stale word is re-read in the same round
+        while (!(ll_tag(wq) == tag && ll_tag(wk) == tag && ll_tag(wv) == tag) && poll_again(pl, it)) {
+          if (ll_tag(wq) != tag) wq = ll_load1(qp);
+          if (ll_tag(wk) != tag) wk = ll_load1(kp);
+          if (ll_tag(wv) != tag) wv = ll_load1(vp);
         }
-      }
-    }
-    __syncwarp();
-    {
-      float ss = 0.0f;
-#pragma unroll
-      for (int j = 0; j < DPL; j++) ss = fmaf(qv[j], qv[j], ss);
-      ss = mg_warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
-      // lanes 0..15 hold dims of the first half, lanes 16..31 their RoPE partners (dim + HD/2)
-#pragma unroll
-      for (int j = 0; j < DPL; j++) {
-        const float u = __fmul_rn(__fmul_rn(qv[j], inv), qw[j]);
-        const float pu = __shfl_xor_sync(0xffffffffu, u, 16);
-        const float r = lane < 16 ? __fsub_rn(__fmul_rn(u, qc[j]), __fmul_rn(pu, qs[j]))
-                                  : __fadd_rn(__fmul_rn(pu, qs[j]), __fmul_rn(u, qc[j]));
-        qr[j] = r * a.attn_scale;
-      }
-    }
-    if (kjob || vjob) {
-      float ss = 0.0f;
-#pragma unroll
-      for (int j = 0; j < DPL; j++) ss = fmaf(rv[j], rv[j], ss);
-      ss = mg_warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
-      float x0 = 0.f, x1 = 0.f;  // this lane's element of block pb and of block pb + NB/2
-#pragma unroll
-      for (int j = 0; j < DPL / 2; j++)
-        if (j == pb) {
-          x0 = rv[j];
-          x1 = rv[j + DPL / 2];
-        }
-      float lo, hi;
-      if (kjob) {
-        const float u = __fmul_rn(__fmul_rn(x0, inv), r_w0), vv = __fmul_rn(__fmul_rn(x1, inv), r_w1);
-        lo = __fsub_rn(__fmul_rn(u, r_c), __fmul_rn(vv, r_s));
-        hi = __fadd_rn(__fmul_rn(u, r_s), __fmul_rn(vv, r_c));
+        kx = ll_val(wk);
+        vx = ll_val(wv);
       } else {
-        lo = __fmul_rn(x0, inv);
-        hi = __fmul_rn(x1, inv);
+        while (ll_tag(wq) != tag && poll_again(pl, it)) wq = ll_load1(qp);
       }
-      uint8_t* dst = kjob ? skrow : svrow;
-      // values pass through f16 before packing (render.rs:1046)
-      mg_pack_q40(__half2float(__float2half_rn(lo)), dst + pb * KS_Q40_BLOCK_BYTES, lane);
-      mg_pack_q40(__half2float(__float2half_rn(hi)), dst + (pb + NB / 2) * KS_Q40_BLOCK_BYTES, lane);
+      qv = ll_val(wq);
     }
-  }
-  const size_t rowstride = (size_t)a.n_kv * ROWB;
-  uint8_t* Kc = L.kv_k + (size_t)kvh * ROWB;
-  uint8_t* Vc = L.kv_v + (size_t)kvh * ROWB;
-  if (owner) {
-    __syncthreads();
-    if (head == kvh * G) {
+    if (pf) pf[1] = clock64();
+    if (warp < NB) {  // the warps that hold the HD values
+      const float sq = mg_rows_sum(qv * qv, red, NB);
+      const float invq = 1.0f / sqrtf(sq / (float)HD + ap->eps);
+      vec[d] = __fmul_rn(__fmul_rn(qv, invq), qw);
+      if (owner) {
+        __syncthreads();
+        const float sk = mg_rows_sum(kx * kx, red, NB);
+        __syncthreads();
+        const float sv = mg_rows_sum(vx * vx, red, NB);
+        const float invk = 1.0f / sqrtf(sk / (float)HD + ap->eps), invv = 1.0f / sqrtf(sv / (float)HD + ap->eps);
+        vec[HD + d] = __fmul_rn(__fmul_rn(kx, invk), kw);
+        vx = __fmul_rn(vx, invv);
+      }
+    } else {  // the other warps only keep the barriers company
+      __syncthreads();
+      if (owner) {
+        __syncthreads();
+        __syncthreads();
+        __syncthreads();
+        __syncthreads();
+      }
+    }
+    __syncthreads();  // u = normed q (and k) of every dimension is in vec
+    float qrot = 0.f, krot = 0.f;
+    if (has) {
+      // dims of the first half pair with dim + HD/2 (gemma_prim.rs:33-56 cos / sin table)
+      const float u = vec[d], pu = vec[d ^ HALF];
+      qrot = d < HALF ? __fsub_rn(__fmul_rn(u, c), __fmul_rn(pu, sn)) : __fadd_rn(__fmul_rn(pu, sn), __fmul_rn(u, c));
+      if (owner) {
+        const float uk = vec[HD + d], pk = vec[HD + (d ^ HALF)];
+        krot = d < HALF ? __fsub_rn(__fmul_rn(uk, c), __fmul_rn(pk, sn)) : __fadd_rn(__fmul_rn(pk, sn), __fmul_rn(uk, c));
+      }
+    }
+    __syncthreads();  // every partner was read
+    if (has) {
+      vec[d] = qrot * ap->attn_scale;
+      if (owner) {
+        // values pass through f16 before packing (render.rs:1046); warp w holds block w of both rows
+        mg_pack_q40(__half2float(__float2half_rn(krot)), skrow + warp * KS_Q40_BLOCK_BYTES, lane);
+        mg_pack_q40(__half2float(__float2half_rn(vx)), svrow + warp * KS_Q40_BLOCK_BYTES, lane);
+      }
+    }
+    __syncthreads();  // q and the packed rows are in shared memory
+    if (owner && head == kvh * G) {
       const unsigned n16 = ROWB / 2;
       if (threadIdx.x < n16)
         reinterpret_cast<unsigned short*>(Kc + (size_t)pos * rowstride)[threadIdx.x] = reinterpret_cast<const unsigned short*>(skrow)[threadIdx.x];
@@ -703,25 +767,30 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
             reinterpret_cast<const unsigned short*>(svrow)[threadIdx.x - n16];
     }
   }
+  if (pf) pf[2] = clock64();
+  float qr[DPL];
+#pragma unroll
+  for (int j = 0; j < DPL; j++) qr[j] = vec[mg_lane_dim<DPL>(lane, j)];
 
+  // 2. this warp's positions
   float o[DPL], m = kNegInit, l = 0.0f;
 #pragma unroll
   for (int j = 0; j < DPL; j++) o[j] = 0.0f;
-  {
-    RawRow<DPL> kn, vn;  // next row, in flight while the current one is processed
-    unsigned t = p0 + warp;
-    if (t < p1) {
-      raw_load<DPL>(t == pos ? skrow : Kc + (size_t)t * rowstride, lane, kn);
-      raw_load<DPL>(t == pos ? svrow : Vc + (size_t)t * rowstride, lane, vn);
-    }
 #pragma unroll 1
-    for (; t < p1; t += MG_NW) {
-      const RawRow<DPL> kr = kn, vr = vn;
-      const unsigned t2 = t + MG_NW;
-      if (t2 < p1) {
-        raw_load<DPL>(t2 == pos ? skrow : Kc + (size_t)t2 * rowstride, lane, kn);
-        raw_load<DPL>(t2 == pos ? svrow : Vc + (size_t)t2 * rowstride, lane, vn);
-      }
+  for (unsigned tb = p0 + (unsigned)warp; tb < p1; tb += MG_NW * MG_AB) {
+    if (tb != p0 + (unsigned)warp) {  // later batches (long contexts): the buffer is free again
+      __syncwarp();
+      prefetch_rows(tb);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncwarp();
+#pragma unroll 1
+    for (int i = 0; i < MG_AB; i++) {
+      const unsigned t = tb + (unsigned)(MG_NW * i);
+      if (t >= p1) break;
+      RawRow<DPL> kr, vr;
+      raw_load<DPL>(t == pos ? skrow : kvbuf + (size_t)(2 * i) * ROWB, lane, kr);
+      raw_load<DPL>(t == pos ? svrow : kvbuf + (size_t)(2 * i + 1) * ROWB, lane, vr);
       float kv[DPL];
       raw_decode<DPL>(kr, kv);
       float sc = 0.0f;
@@ -738,6 +807,7 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
       for (int j = 0; j < DPL; j++) o[j] = fmaf(e, kv[j], o[j] * alpha);
     }
   }
+  if (pf) pf[3] = clock64();
   {
     float* dst = part + warp * (HD + 2);
     if (lane == 0) {
@@ -748,8 +818,7 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
     for (int j = 0; j < DPL; j++) dst[2 + j * 32 + lane] = o[j];
   }
   __syncthreads();
-  // thread d folds head dimension d over the sixteen warps; it sits in slot j * 32 + lane of the warps' layout
-  const int d = threadIdx.x;
+  // 3. thread d folds head dimension d over the warps; it sits in slot j * 32 + lane of the warps' layout
   int dslot;
   {
     constexpr int BPL = DPL / 2, LPB = 16 / BPL;
@@ -757,26 +826,24 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
     dslot = (hh * BPL + (w16 % BPL)) * 32 + (((d >> 5) & (NB - 1)) * LPB + w16 / BPL);
   }
   float M = kNegInit, Lsum = 0.0f, O = 0.0f;
-  if (d < HD) {
-    float mw[MG_NW];
-#pragma unroll
+  if (has) {
+#pragma unroll 1
+    for (int w = 0; w < MG_NW; w++) M = fmaxf(M, part[w * (HD + 2)]);
+#pragma unroll 1
     for (int w = 0; w < MG_NW; w++) {
-      mw[w] = part[w * (HD + 2)];
-      M = fmaxf(M, mw[w]);
-    }
-#pragma unroll
-    for (int w = 0; w < MG_NW; w++) {
-      const float f = __expf(mw[w] - M);
+      const float f = __expf(part[w * (HD + 2)] - M);
       Lsum = fmaf(part[w * (HD + 2) + 1], f, Lsum);
       O = fmaf(part[w * (HD + 2) + 2 + dslot], f, O);
     }
   }
+  if (pf) pf[4] = clock64();
+  // 4.
   if (NS == 1) {  // one split: this block's result is final
-    if (d < HD) ll_store(ox + (size_t)head * HD + d, O / Lsum, tag);
+    if (has) ll_store(ox + (size_t)head * HD + d, O / Lsum, tag);
   } else {
     u64* myrec = rec + ((size_t)head * NSMAX + split) * (HD + 2);
     if (split != 0) {
-      if (d < HD) {
+      if (has) {
         ll_store(myrec + 2 + d, O, tag);  // records are kept in dimension order
         if (d == 0) {
           ll_store(myrec, M, tag);
@@ -785,15 +852,8 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
       }
     } else {
       // The head's first block merges (lower.rs:5897-6088): its own record is in registers, the others are
-      // awaited.  Thread p fetches (m, l) of split p for everybody; thread d fetches O[d] of every split.
-      float* ml = reinterpret_cast<float*>(svrow + ROWB + 16u);  // [2 * MG_MAX_SPLITS]
+      // awaited.  Thread p fetches (m, l) of split p for everybody; thread d fetches O[d], four splits at a time.
       const u64* rec0 = rec + (size_t)head * NSMAX * (HD + 2);
-      u64 wo[MG_MAX_SPLITS];
-      if (d < HD) {
-#pragma unroll
-        for (int p = 1; p < MG_MAX_SPLITS; p++)
-          if ((unsigned)p < NS) wo[p] = ll_load1(rec0 + (size_t)p * (HD + 2) + 2 + d);
-      }
       if (d == 0) {
         ml[0] = M;
         ml[1] = Lsum;
@@ -809,92 +869,293 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
         ml[2 * d + 1] = ll_val(w1);
       }
       __syncthreads();
-      if (d < HD) {
+      if (has) {
         float MM = kNegInit;
+#pragma unroll 1
         for (unsigned p = 0; p < NS; p++) MM = fmaxf(MM, ml[2 * p]);
-        float LL = 0.0f, OO = 0.0f;
+        float f0 = __expf(ml[0] - MM);
+        float LL = ml[1] * f0, OO = O * f0;
+#pragma unroll 1
+        for (unsigned pb = 1; pb < NS; pb += 4) {
+          u64 w[4];
 #pragma unroll
-        for (int p = 0; p < MG_MAX_SPLITS; p++)
-          if ((unsigned)p < NS) {
-            float ov = O;
-            if (p > 0) {
-              const u64* r = rec0 + (size_t)p * (HD + 2) + 2 + d;
-              unsigned it = 0;
-              while (ll_tag(wo[p]) != tag && poll_again(pl, it)) wo[p] = ll_load1(r);
-              ov = ll_val(wo[p]);
+          for (int k = 0; k < 4; k++)
+            if (pb + k < NS) w[k] = ll_load1(rec0 + (size_t)(pb + k) * (HD + 2) + 2 + d);
+          {
+            unsigned it = 0;
+            for (;;) {
+              bool any = false;
+#pragma unroll
+              for (int k = 0; k < 4; k++) any = any || (pb + k < NS && ll_tag(w[k]) != tag);
+              if (!any || !poll_again(pl, it)) break;
+#pragma unroll
+              for (int k = 0; k < 4; k++)
+                if (pb + k < NS && ll_tag(w[k]) != tag) w[k] = ll_load1(rec0 + (size_t)(pb + k) * (HD + 2) + 2 + d);
             }
-            const float f = __expf(ml[2 * p] - MM);
-            LL = fmaf(ml[2 * p + 1], f, LL);
-            OO = fmaf(ov, f, OO);
           }
+#pragma unroll
+          for (int k = 0; k < 4; k++)
+            if (pb + k < NS) {
+              const float f = __expf(ml[2 * (pb + k)] - MM);
+              LL = fmaf(ml[2 * (pb + k) + 1], f, LL);
+              OO = fmaf(ll_val(w[k]), f, OO);
+            }
+        }
         ll_store(ox + (size_t)head * HD + d, OO / LL, tag);
       }
     }
   }
+  if (pf) pf[6] = clock64();
   __syncthreads();  // the scratch is the next phase's x staging area
+  if (pf) pf[7] = clock64();
+  return pl.gave_up ? (st | ST_GAVE_UP) : st;
 }
 
 // ---- the kernel -------------------------------------------------------------------------------------
 struct MegaSmem {
-  unsigned ring_off, bar_off, done_off, red_off, psum_off, tab_off, piece_off, info_off, total;
+  unsigned xs_off, xres_off, ring_off, bar_off, done_off, red_off, psum_off, rowtab_off, tab_off, piece_off, info_off, total;
 };
-__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int n_slots, unsigned tables_bytes) {
+__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned hidden, unsigned slot_bytes, int n_slots, unsigned tables_bytes) {
   MegaSmem L;
-  L.ring_off = (x_bytes + 127u) & ~127u;
+  L.xs_off = 1024u;  // MegaShared first
+  L.xres_off = L.xs_off + ((x_bytes + 127u) & ~127u);
+  L.ring_off = L.xres_off + ((hidden * 4u + 127u) & ~127u);
   L.bar_off = L.ring_off + (unsigned)n_slots * slot_bytes;
   L.done_off = L.bar_off + MG_MAXSLOTS * 8u;
-  L.red_off = L.done_off + MG_MAXSLOTS * 4u;      // 16 float4 of block sums, then 16 bytes of flags
-  L.psum_off = L.red_off + MG_NW * 16u + 16u;
-  L.tab_off = L.psum_off + 2u * MG_MAXROWS * MG_MAXC * 4u;
+  L.red_off = L.done_off + MG_MAXSLOTS * 4u;      // 16 float4 of block sums
+  L.psum_off = L.red_off + MG_NW * 16u;
+  L.rowtab_off = L.psum_off + 2u * MG_MAXROWS * MG_MAXC * 4u;
+  L.tab_off = L.rowtab_off + 2u * MG_MAXROWS * 4u;
   L.piece_off = L.tab_off + tables_bytes;
   L.info_off = L.piece_off + MG_MAXPIECE * (unsigned)sizeof(Piece);
   L.total = L.info_off + PH_KINDS * (unsigned)sizeof(PhInfo) + 16u;
   return L;
 }
 
-struct RingPos {  // where the next piece of the sequence sits (the same in every warp)
-  unsigned slot, par;
+struct MegaShared {  // block-wide state at the start of dynamic shared memory
+  MegaSmem SL;
+  AttnArgs att;
+  unsigned n_slots, slot_bytes, n_layers, poll_limit;
+  unsigned NP, total_pieces;
+  unsigned* err;
+  int ok;
 };
+static_assert(sizeof(MegaShared) <= 1024, "MegaShared must fit its reserved kilobyte");
+
+// One matvec phase after its input was staged.  A lane owns one 64-weight unit of a 32-unit column
+// segment and keeps that unit of x in registers; a task is (segment, matrix, row); the tasks of a wave
+// (the rows of up to half the ring's slots) are ordered segment-major and cut into one
+// contiguous range per warp, so a warp loads x at most twice per wave and all warps get the same number
+// of tasks (+-1); two tasks run interleaved.  Row sums meet in shared memory; after a block-wide barrier
+// thread f finishes row f of the wave (segments added in order, epilogue, tagged store) while lanes of the
+// last warp refill the wave's slots with the pieces n_slots further down the sequence (one lane per slot:
+// issuing them one after the other from one thread cost 0.3 us each on the critical path).  Begins with
+// the block-wide barrier that ends the staging of x.
+__device__ MG_FN unsigned mg_phase(int kind, int layer, unsigned tag, u64* out, float* plain, long long* pf, unsigned st, long long* pa) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const MegaShared* S = reinterpret_cast<const MegaShared*>(smem);
+  const MegaSmem& SL = S->SL;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t ring_s = sm32(smem + SL.ring_off), bars = sm32(smem + SL.bar_off), xs_s = sm32(smem + SL.xs_off);
+  float* psum = reinterpret_cast<float*>(smem + SL.psum_off);
+  uint32_t* rowaddr = reinterpret_cast<uint32_t*>(smem + SL.rowtab_off);  // shared address of each row of the wave (first matrix)
+  uint32_t* rowmat2 = rowaddr + MG_MAXROWS;                               // distance to the same row of the second matrix
+  const MegaPhase* phases = reinterpret_cast<const MegaPhase*>(smem + SL.tab_off);
+  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u));
+  const Piece* pieces = reinterpret_cast<const Piece*>(smem + SL.piece_off);
+  const PhInfo inf = reinterpret_cast<const PhInfo*>(smem + SL.info_off)[kind];
+  const MegaPhase& ph = phases[kind];
+  const unsigned n_slots = S->n_slots, slot_bytes = S->slot_bytes, NP = S->NP;
+  unsigned slot = st & 0xFFu, par = (st >> 8) & 1u;
+  bool dead = (st & ST_DEAD) != 0u;
+
+  const unsigned NS = ph.n_cseg, units = ph.cols >> 6, seg_units = ph.seg_units;
+  const unsigned row_bytes = ph.row_bytes, mats = ph.mats;
+  const unsigned wave_max = n_slots > 1u ? n_slots / 2u : 1u;
+  const bool active = (unsigned)lane < seg_units;
+  XUnit x;
+  int cur_s = -1;
+  for (unsigned wp0 = inf.p0; wp0 < (unsigned)inf.p0 + inf.np; wp0 += wave_max) {
+    const unsigned wp1 = min(wp0 + wave_max, (unsigned)inf.p0 + inf.np);
+    const unsigned wr0 = pieces[wp0].row0, wr1 = (unsigned)pieces[wp1 - 1].row0 + pieces[wp1 - 1].nrows, rows_w = wr1 - wr0;
+    if (threadIdx.x < rows_w) {
+      const unsigned r = wr0 + threadIdx.x;
+      unsigned pi = wp0;
+      while (pi + 1 < wp1 && pieces[pi + 1].row0 <= r) pi++;
+      unsigned sl = slot + (pi - wp0);
+      if (sl >= n_slots) sl -= n_slots;
+      rowaddr[threadIdx.x] = ring_s + sl * slot_bytes + (r - pieces[pi].row0) * row_bytes;
+      rowmat2[threadIdx.x] = (((unsigned)pieces[pi].nrows + 3u) & ~3u) * row_bytes;
+    }
+    __syncthreads();  // x is staged (first wave), the row table is written
+    if (pf && wp0 == inf.p0) pf[2] = clock64();
+    if (pa && threadIdx.x == 0 && wp0 == inf.p0) pa[3] = gtime();
+    // the wave's weights: one lane per piece asks the piece's mbarrier, the warp votes
+    if (!dead) {
+      bool ok = true;
+      if ((unsigned)lane < wp1 - wp0) {
+        unsigned sl = slot + (unsigned)lane, pr = par;
+        if (sl >= n_slots) {
+          sl -= n_slots;
+          pr ^= 1u;
+        }
+        ok = mb_wait(bars + sl * 8u, pr, S->poll_limit);
+      }
+      if (!__all_sync(0xffffffffu, ok)) {
+        dead = true;
+        if (lane == 0) atomicOr(S->err, 1u);
+      }
+    }
+    if (pa && threadIdx.x == 0 && wp0 == inf.p0) pa[4] = gtime();
+    if (!dead) {
+      const unsigned per_seg = mats * rows_w, T = NS * per_seg;
+      const unsigned t0 = (unsigned)warp * T / MG_NW, t1 = (unsigned)(warp + 1) * T / MG_NW;
+      unsigned t = t0, sg = t0 / per_seg, rem = t0 - sg * per_seg;
+      // task (sg, rem): rem < rows_w is row rem of the first matrix, else row rem - rows_w of the second
+      auto row_of = [&](unsigned q, uint32_t uoff, uint32_t& wa, unsigned& pidx) {
+        const unsigned m = q >= rows_w ? 1u : 0u, r = q - m * rows_w;
+        wa = rowaddr[r] + (m ? rowmat2[r] : 0u) + uoff;
+        pidx = ((wr0 + r) * mats + m) * NS + sg;
+      };
+#pragma unroll 1
+      while (t < t1) {
+        const unsigned u = sg * seg_units + (unsigned)lane;
+        if ((int)sg != cur_s) {
+          if (active) fx_load_unit(x, xs_s, units, u);
+          cur_s = (int)sg;
+        }
+        const uint32_t uoff = (u >> 2) * KS_Q4K_BLOCK_BYTES + (u & 3u) * 32u;
+        unsigned n = min(t1 - t, per_seg - rem);  // my tasks left in this segment
+        t += n;
+#pragma unroll 1
+        for (; n >= 2u; n -= 2u, rem += 2u) {  // two rows at a time: their instruction streams interleave
+          uint32_t wa[2];
+          unsigned pidx[2];
+          row_of(rem, uoff, wa[0], pidx[0]);
+          row_of(rem + 1u, uoff, wa[1], pidx[1]);
+          float v[2] = {0.0f, 0.0f};
+          if (active) fx_rows<2>(wa, (int)(u & 3u), x, v);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+            v[1] += __shfl_xor_sync(0xffffffffu, v[1], o);
+          }
+          if (lane == 0) {
+            psum[pidx[0]] = v[0];
+            psum[pidx[1]] = v[1];
+          }
+        }
+        if (n) {
+          uint32_t wa[1];
+          unsigned pidx;
+          row_of(rem, uoff, wa[0], pidx);
+          float v[1] = {0.0f};
+          if (active) fx_rows<1>(wa, (int)(u & 3u), x, v);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+          if (lane == 0) psum[pidx] = v[0];
+          rem += 1u;
+        }
+        if (rem == per_seg) {
+          rem = 0;
+          sg++;
+        }
+      }
+    }
+    if (pf) pf[3] = clock64();
+    if (pa && threadIdx.x == 0) pa[5] = gtime();
+    __syncthreads();  // the wave's row sums are in shared memory and nobody reads its slots any more
+    if (pf) pf[4] = clock64();
+    if (pa && threadIdx.x == 0) pa[6] = gtime();
+    // the last warp (never a finishing warp) refills the wave's slots with the pieces n_slots further on, one lane per slot
+    if (warp == MG_NW - 1 && (unsigned)lane < wp1 - wp0) {
+      const long long rt0 = pa ? gtime() : 0;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slots were read through the generic proxy
+      unsigned sl = slot + (unsigned)lane;
+      if (sl >= n_slots) sl -= n_slots;
+      unsigned npi = wp0 + (unsigned)lane + n_slots;
+      unsigned nl = (unsigned)layer;
+      while (npi >= NP) {
+        npi -= NP;
+        nl++;
+      }
+      if (nl < S->n_layers) {
+        const Piece np_ = pieces[npi];
+        issue_piece(np_, phases[np_.kind], layers[nl], ring_s + sl * slot_bytes, bars + sl * 8u);
+      }
+      if (pa && lane == 0) pa[7] = gtime() - rt0;
+    }
+    // thread f finishes row wr0 + f of the block: segments added in order, epilogue, tagged store
+    if (threadIdx.x < rows_w) {
+      const unsigned r = wr0 + threadIdx.x;
+      unsigned pi = wp0;
+      while (pi + 1 < wp1 && pieces[pi + 1].row0 <= r) pi++;
+      const unsigned orow = pieces[pi].out0 + (r - pieces[pi].row0);
+      const float* ps = psum + (size_t)r * mats * NS;
+      float v0 = 0.0f;
+      for (unsigned sg = 0; sg < NS; sg++) v0 += ps[sg];
+      if (mats == 2) {
+        float v1 = 0.0f;
+        for (unsigned sg = 0; sg < NS; sg++) v1 += ps[NS + sg];
+        v0 = gelu_mul(v0, v1);
+      }
+      ll_store(out + orow, v0, tag);
+      if (plain) plain[orow] = v0;  // the head reads plain floats
+    }
+    if (pf) pf[5] = clock64();
+    slot += wp1 - wp0;
+    if (slot >= n_slots) {
+      slot -= n_slots;
+      par ^= 1u;
+    }
+  }
+  return (st & ST_GAVE_UP) | slot | (par << 8) | (dead ? ST_DEAD : 0u);
+}
 
 template <int DPL, int PC>
 __global__ void __launch_bounds__(MG_THREADS, 1) mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int cl = lane % MG_LPR, rl = lane / MG_LPR;
-  const MegaSmem SL = mg_smem(a.x_bytes, a.slot_bytes, a.n_slots, a.tables_bytes);
+  MegaShared* S = reinterpret_cast<MegaShared*>(smem);
+  const unsigned H0 = reinterpret_cast<const MegaPhase*>(a.tables)[PH_QKV].cols;  // hidden size (tables are in global memory here)
+  const MegaSmem SL = mg_smem(a.x_bytes, H0, a.slot_bytes, a.n_slots, a.tables_bytes);
   const uint32_t ring_s = sm32(smem + SL.ring_off);
   const uint32_t bars = sm32(smem + SL.bar_off);
-  int* done = reinterpret_cast<int*>(smem + SL.done_off);
   float4* red = reinterpret_cast<float4*>(smem + SL.red_off);
-  int* flags = reinterpret_cast<int*>(smem + SL.red_off + MG_NW * 16u);
-  float* psum = reinterpret_cast<float*>(smem + SL.psum_off);
+  float* xres = reinterpret_cast<float*>(smem + SL.xres_off);
+  unsigned char* xs = smem + SL.xs_off;
   const MegaPhase* phases = reinterpret_cast<const MegaPhase*>(smem + SL.tab_off);
   const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u));
   Piece* pieces = reinterpret_cast<Piece*>(smem + SL.piece_off);
   PhInfo* info = reinterpret_cast<PhInfo*>(smem + SL.info_off);
-  const uint32_t xs_s = sm32(smem);
   const unsigned n_slots = (unsigned)a.n_slots;
 
   for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
     reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
-  if (threadIdx.x < MG_MAXSLOTS) done[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
+    S->SL = SL;
+    S->att.n_q = a.n_q; S->att.n_kv = a.n_kv; S->att.n_splits = a.n_splits; S->att.split_from = a.split_from;
+    S->att.eps = a.eps; S->att.attn_scale = a.attn_scale; S->att.rope = a.rope; S->att.pos = a.pos;
+    S->att.err = a.err; S->att.limit = a.poll_limit;
+    S->n_slots = n_slots; S->slot_bytes = a.slot_bytes; S->n_layers = (unsigned)a.n_layers; S->poll_limit = a.poll_limit;
+    S->err = a.err;
     for (unsigned s = 0; s < n_slots; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
-  if (threadIdx.x == 0) flags[0] = build_pieces(pieces, info, phases) ? 1 : 0;
+  if (threadIdx.x == 0) {
+    S->ok = build_pieces(pieces, info, phases) ? 1 : 0;
+    S->NP = (unsigned)info[PH_KINDS - 1].p0 + info[PH_KINDS - 1].np;
+    S->total_pieces = S->NP * (unsigned)a.n_layers;
+  }
   __syncthreads();
-  if (!flags[0]) {  // a table overflowed: the host's own check of the same arithmetic should have refused this shape
+  if (!S->ok) {  // a table overflowed: the host's own check of the same arithmetic should have refused this shape
     if (threadIdx.x == 0) atomicOr(a.err, 4u);
     return;
   }
-  const unsigned NP = (unsigned)info[PH_KINDS - 1].p0 + info[PH_KINDS - 1].np;
-  const unsigned total_pieces = NP * (unsigned)a.n_layers;
+  const unsigned NP = S->NP, total_pieces = S->total_pieces;
   const unsigned epoch = *a.epoch;
-  Poll pl{a.err, a.poll_limit, false};
-  bool dead = false;  // this warp stopped waiting for weight copies (one never landed)
 
   // fill the ring: piece n goes to slot n
   if (lane == 0)
@@ -903,147 +1164,61 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_kernel(const MegaArgs a) {
       issue_piece(p, phases[p.kind], layers[n / NP], ring_s + n * a.slot_bytes, bars + n * 8u);
     }
 
-  // the residual stream: this thread's chunks, in registers for the whole token
+  // the residual stream: thread t keeps chunks t and t + 512 (only ever touched by the same thread)
   const unsigned H = phases[PH_QKV].cols;
-  float4 xr[PC];
-#pragma unroll
-  for (int k = 0; k < PC; k++) {
-    const unsigned c = threadIdx.x + k * MG_THREADS;
-    xr[k] = c < (H >> 2) ? reinterpret_cast<const float4*>(a.x_in)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
+  for (unsigned c = threadIdx.x; c < (H >> 2); c += MG_THREADS)
+    reinterpret_cast<float4*>(xres)[c] = reinterpret_cast<const float4*>(a.x_in)[c];
 
   long long* prof = nullptr;
   if (a.prof && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * a.n_layers * PF_PER_LAYER * 4;
+    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * a.n_layers * PF_PER_LAYER * PF_STAMPS;
 
-  RingPos rp{0u, 0u};
-
+  long long* pall = (a.prof_all && (threadIdx.x == 0 || threadIdx.x == MG_THREADS - 32)) ? a.prof_all + (size_t)blockIdx.x * a.n_layers * PF_PER_LAYER * 8 : nullptr;
+  unsigned st = 0u;  // ring position, wait state (see ST_*)
+#pragma unroll 1
   for (int layer = 0; layer < a.n_layers; layer++) {
-    const MegaLayer& L = layers[layer];
     const unsigned tag = epoch + (unsigned)layer + 1u;
     const int b = layer & 1;
     const bool last = layer + 1 == a.n_layers;
-    // kernel parameters are picked with selects (indexing them would force a local copy)
-    u64* const yd = b ? a.ll_yd1 : a.ll_yd0;
-    const u64* const yd_prev = b ? a.ll_yd0 : a.ll_yd1;
-    u64* const yo = b ? a.ll_yo1 : a.ll_yo0;
-    u64* const qkv = b ? a.ll_qkv1 : a.ll_qkv0;
-    u64* const ox = b ? a.ll_ox1 : a.ll_ox0;
-    u64* const ff = b ? a.ll_ff1 : a.ll_ff0;
-    u64* const rec = b ? a.ll_rec1 : a.ll_rec0;
-
 #pragma unroll 1
     for (int kind = 0; kind < PH_KINDS; kind++) {
+      // kernel parameters are picked with selects (indexing them would force a local copy)
+      u64* const yd = b ? a.ll_yd1 : a.ll_yd0;
+      u64* const yo = b ? a.ll_yo1 : a.ll_yo0;
+      u64* const qkv = b ? a.ll_qkv1 : a.ll_qkv0;
+      u64* const ox = b ? a.ll_ox1 : a.ll_ox0;
+      u64* const ff = b ? a.ll_ff1 : a.ll_ff0;
       // profile rows: qkv, attention, o-proj, gate-up, down
-      long long* pf = prof ? prof + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 4 : nullptr;
-      const MegaPhase& ph = phases[kind];
-      // ---- this phase's input vector, staged in shared memory
+      long long* pf = prof ? prof + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * PF_STAMPS : nullptr;
+      const MegaLayer& L = layers[layer];
       if (kind == PH_OPROJ) {
-        if (pf) pf[-4] = clock64();
-        mg_attention<DPL>(a, L, qkv, ox, rec, tag, smem, pl);
-        if (pf) pf[-1] = clock64();
+        if (pall && threadIdx.x == 0) pall[((size_t)layer * PF_PER_LAYER + PF_ATTN) * 8] = gtime();
+        if (pf) pf[-PF_STAMPS] = clock64();
+        st = mg_attention<DPL>(&S->att, &L, qkv, ox, b ? a.ll_rec1 : a.ll_rec0, tag, xs, st, pf ? pf - PF_STAMPS : nullptr);
+      }
+      if (pall && threadIdx.x == 0) {
+        if (kind == PH_OPROJ) pall[((size_t)layer * PF_PER_LAYER + PF_ATTN) * 8 + 1] = gtime();
+        pall[((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 8] = gtime();
       }
       if (pf) pf[0] = clock64();
+      // ---- this phase's input vector, staged in shared memory
       if (kind == PH_QKV || kind == PH_GATEUP) {
         // residual update (from the second phase on) + norm.  q/k/v: the previous layer's down-proj output
         // and post-FFN norm, then this layer's attention norm; gate/up: the o-proj output and post-attention
         // norm, then the FFN norm.
         const bool qk = kind == PH_QKV;
-        mg_stage_hidden<PC>(smem, red, !qk || layer > 0, H, xr, qk ? yd_prev : yo, qk ? tag - 1u : tag + a.test_stall,
-                            qk ? L.norm[0] : L.norm[4], qk ? layers[layer > 0 ? layer - 1 : 0].norm[5] : L.norm[3], a.eps,
-                            (!qk && last && blockIdx.x == 0) ? a.resid_out : nullptr, pl);
+        st = mg_stage_hidden<PC>(xs, red, xres, !qk || layer > 0, H, qk ? (b ? a.ll_yd0 : a.ll_yd1) : yo,
+                                 qk ? tag - 1u : tag + a.test_stall, qk ? L.norm[0] : L.norm[4],
+                                 qk ? layers[layer > 0 ? layer - 1 : 0].norm[5] : L.norm[3], a.eps,
+                                 (!qk && last && blockIdx.x == 0) ? a.resid_out : nullptr, a.err, a.poll_limit, st, pf);
       } else {
-        mg_stage_plain(smem, ph.cols, kind == PH_OPROJ ? ox : ff, tag, pl);
+        st = mg_stage_plain(xs, phases[kind].cols, kind == PH_OPROJ ? ox : ff, tag, a.err, a.poll_limit, st, pf);
       }
-      __syncthreads();
-      if (pf) pf[1] = clock64();
-
-      // ---- this block's items
-      const PhInfo inf = info[kind];
-      const unsigned C = ph.n_cseg, units = ph.cols >> 6, seg_units = ph.seg_blocks * 4u;
-      const unsigned seg_bytes = ph.seg_blocks * KS_Q4K_BLOCK_BYTES;
-      for (unsigned pi = inf.p0; pi < (unsigned)inf.p0 + inf.np; pi++) {
-        const Piece P = pieces[pi];
-        const unsigned first = P.item0 + (((unsigned)warp - P.item0) & (MG_NW - 1u));
-        const unsigned end = (unsigned)P.item0 + P.n_items;
-        if (first < end && !dead) {
-          const bool ok = mb_wait(bars + rp.slot * 8u, rp.par, a.poll_limit);
-          if (!__all_sync(0xffffffffu, ok)) {
-            dead = true;
-            if (lane == 0) atomicOr(a.err, 1u);
-          }
-        }
-        if (first < end && !dead) {
-          const uint32_t slot_addr = ring_s + rp.slot * a.slot_bytes;
-          const uint32_t mat2 = (((unsigned)P.nrows + 3u) & ~3u) * ph.row_bytes;
-          for (unsigned j = first; j < end; j += MG_NW) {
-            const unsigned local = j - P.item0, gi = local / C, cs = local - gi * C;
-            const uint32_t base = slot_addr + gi * 4u * ph.row_bytes + cs * seg_bytes;
-            float yacc[2] = {0.0f, 0.0f};
-            if (ph.mats == 2)
-              mg_item_compute_fx<2>(base, ph.row_bytes, mat2, xs_s, units, seg_units, cs, cl, rl, yacc);
-            else
-              mg_item_compute_fx<1>(base, ph.row_bytes, 0u, xs_s, units, seg_units, cs, cl, rl, yacc);
-            float v0 = yacc[0], v1 = yacc[1];
-#pragma unroll
-            for (int o = MG_LPR / 2; o > 0; o >>= 1) {
-              v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-              v1 += __shfl_xor_sync(0xffffffffu, v1, o);
-            }
-            const unsigned r = gi * 4u + (unsigned)rl;
-            if (cl == 0 && r < P.nrows) {
-              const unsigned idx = ((unsigned)P.row0 + r) * C + cs;
-              psum[idx] = v0;
-              if (ph.mats == 2) psum[MG_MAXROWS * MG_MAXC + idx] = v1;
-            }
-          }
-        }
-        // this warp is done with the slot; the last of the sixteen refills it with the piece n_slots further on
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence_block();
-          if (atomicAdd(&done[rp.slot], 1) == MG_NW - 1) {
-            done[rp.slot] = 0;
-            __threadfence_block();
-            unsigned npi = pi + n_slots;
-            int nl = layer;
-            while (npi >= NP) {
-              npi -= NP;
-              nl++;
-            }
-            if (nl < a.n_layers) {
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
-              const Piece np_ = pieces[npi];
-              issue_piece(np_, phases[np_.kind], layers[nl], ring_s + rp.slot * a.slot_bytes, bars + rp.slot * 8u);
-            }
-          }
-        }
-        if (++rp.slot == n_slots) {
-          rp.slot = 0;
-          rp.par ^= 1u;
-        }
-      }
-      __syncthreads();  // the partial sums of every item of this block are in shared memory
-      if (pf) pf[2] = clock64();
-
-      // ---- thread f finishes row f of this block: column segments added in order, epilogue, tagged store
-      if (threadIdx.x < inf.nrows) {
-        unsigned pi = inf.p0;
-        while (pi + 1 < (unsigned)inf.p0 + inf.np && pieces[pi + 1].row0 <= threadIdx.x) pi++;
-        const unsigned orow = pieces[pi].out0 + (threadIdx.x - pieces[pi].row0);
-        const float* ps = psum + (size_t)threadIdx.x * C;
-        float v0 = 0.0f;
-        for (unsigned cs = 0; cs < C; cs++) v0 += ps[cs];
-        if (ph.mats == 2) {
-          float v1 = 0.0f;
-          for (unsigned cs = 0; cs < C; cs++) v1 += ps[MG_MAXROWS * MG_MAXC + cs];
-          v0 = gelu_mul(v0, v1);
-        }
-        u64* out = kind == PH_QKV ? qkv : kind == PH_OPROJ ? yo : kind == PH_GATEUP ? ff : yd;
-        ll_store(out + orow, v0, tag);
-        if (kind == PH_DOWN && last) a.y_out[orow] = v0;  // the head reads plain floats
-      }
-      if (pf) pf[3] = clock64();
+      u64* const out = kind == PH_QKV ? qkv : kind == PH_OPROJ ? yo : kind == PH_GATEUP ? ff : yd;
+      long long* pa = pall ? pall + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 8 : nullptr;
+      if (pa && threadIdx.x == 0) pa[2] = gtime();
+      st = mg_phase(kind, layer, tag, out, (kind == PH_DOWN && last) ? a.y_out : nullptr, pf, st, pa);
+      if (pa && threadIdx.x == 0) pa[1] = gtime();
     }
   }
   // The next token's tags must differ from everything this one wrote.  Every block read the epoch before
@@ -1067,6 +1242,7 @@ struct ks_mega {
   void* d_tables = nullptr;
   unsigned* d_sync = nullptr;     // word 0: the tag epoch
   long long* d_prof = nullptr;
+  long long* d_prof_all = nullptr;
   u64* d_ll = nullptr;            // the tagged activation vectors
   size_t ll_bytes = 0;
   unsigned grid = 0;
@@ -1102,9 +1278,22 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
 }  // namespace
 
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
-  if (mg->dpl == 4) return mg->pc == 1 ? mega_launch_t<4, 1>(ctx, mg) : mega_launch_t<4, 2>(ctx, mg);
-  if (mg->dpl == 8) return mg->pc == 1 ? mega_launch_t<8, 1>(ctx, mg) : mega_launch_t<8, 2>(ctx, mg);
-  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size not supported");
+  if (mg->dpl == 4) {
+    switch (mg->pc) {
+      case 1: return mega_launch_t<4, 1>(ctx, mg);
+      case 2: return mega_launch_t<4, 2>(ctx, mg);
+      case 3: return mega_launch_t<4, 3>(ctx, mg);
+      case 4: return mega_launch_t<4, 4>(ctx, mg);
+    }
+  } else if (mg->dpl == 8) {
+    switch (mg->pc) {
+      case 1: return mega_launch_t<8, 1>(ctx, mg);
+      case 2: return mega_launch_t<8, 2>(ctx, mg);
+      case 3: return mega_launch_t<8, 3>(ctx, mg);
+      case 4: return mega_launch_t<8, 4>(ctx, mg);
+    }
+  }
+  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size or hidden size not supported");
 }
 
 float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
@@ -1117,6 +1306,7 @@ int ks_mega_reset(ks_ctx* ctx, ks_mega* mg) {
   return KS_OK;
 }
 const long long* ks_mega_prof(const ks_mega* mg) { return mg->d_prof; }
+const long long* ks_mega_prof_all(const ks_mega* mg) { return mg->d_prof_all; }
 
 // Knobs that tests and the profiling reader set: 0 = polls before a wait gives up, 1 = make the gate-up stage
 // of every layer wait for a tag nobody writes (0 = off), 2 = context length from which attention is split
@@ -1127,7 +1317,7 @@ int ks_mega_set(ks_mega* mg, int what, unsigned value) {
     case 0: mg->args.poll_limit = value ? value : 1u; return KS_OK;
     case 1: mg->args.test_stall = value; return KS_OK;
     case 2: mg->args.split_from = value; return KS_OK;
-    case 3: mg->args.prof = value ? mg->d_prof : nullptr; return KS_OK;
+    case 3: mg->args.prof = value ? mg->d_prof : nullptr; mg->args.prof_all = value > 1 ? mg->d_prof_all : nullptr; return KS_OK;
     default: return KS_ERR_INVALID;
   }
 }
@@ -1137,6 +1327,7 @@ void ks_mega_destroy(ks_mega* mg) {
   if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
   if (mg->d_prof) cudaFree(mg->d_prof);
+  if (mg->d_prof_all) cudaFree(mg->d_prof_all);
   if (mg->d_ll) cudaFree(mg->d_ll);
   delete mg;
 }
@@ -1147,9 +1338,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   *out = nullptr;
   const unsigned H = d->hidden, F = d->ffn, hd = d->hd, nq = d->n_q, nkv = d->n_kv;
   const unsigned qn = nq * hd, kvn = nkv * hd;
-  auto even_blocks = [](unsigned cols) { return cols % 512 == 0; };
-  if (!even_blocks(H) || !even_blocks(F) || !even_blocks(qn)) return KS_OK;
-  if (H > 2u * 4u * MG_THREADS) return KS_OK;  // the residual stream lives in registers: at most two chunks per thread
+  if (H % 256u || F % 256u || qn % 256u) return KS_OK;
+  if (H > 4u * 4u * MG_THREADS) return KS_OK;  // the norm stages hold at most four 4-element chunks per thread
   if (nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
   const unsigned grid = (unsigned)ctx->sm_count;
   // one block per (query head, split): fewer splits than the caller's record layout allows if the grid is small
@@ -1195,7 +1385,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   if (n_slots > MG_MAXSLOTS) n_slots = MG_MAXSLOTS;
   unsigned slot_bytes = 0;
   for (; n_slots >= 2; n_slots--) {
-    const MegaSmem fixed = mg_smem(x_bytes, 0, n_slots, tables_bytes);
+    const MegaSmem fixed = mg_smem(x_bytes, H, 0, n_slots, tables_bytes);
     if (fixed.total >= budget) continue;
     slot_bytes = ((budget - fixed.total) / (unsigned)n_slots) & ~127u;
     if (slot_bytes >= need) break;
@@ -1212,11 +1402,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
     }
     return m;
   };
-  // Column segments per phase.  A block's items (4-row groups x column segments) are shared by its 16 warps,
-  // so more segments shorten the longest warp until the per-item overhead (about one 64-weight unit's worth of
-  // time) wins; a segment holds an even number of blocks (8 lanes per row take one unit each per trip).
-  int c_env[PH_KINDS] = {0, 0, 0, 0};
-  if (const char* e = getenv("KSEARCH_MEGA_CSEG")) sscanf(e, "%d,%d,%d,%d", &c_env[0], &c_env[1], &c_env[2], &c_env[3]);
+  // Column segments per phase: a lane owns one 64-weight unit of a segment, so a segment has at most 32 units;
+  // the units of a row are split evenly over as few segments as that allows.
   unsigned total_pieces = 0;
   for (int k = 0; k < PH_KINDS; k++) {
     MegaPhase& p = ph[k];
@@ -1227,25 +1414,10 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
     if (cap_rows > 64u) cap_rows = 64u;
     const unsigned n_pc = (R + cap_rows - 1u) / cap_rows;
     p.piece_rows = std::min(cap_rows, (((R + n_pc - 1u) / n_pc) + 3u) & ~3u);
-    unsigned groups = 0;
-    for (unsigned r = 0; r < R; r += p.piece_rows) groups += (std::min(p.piece_rows, R - r) + 3u) / 4u;
-    const unsigned nb = p.cols / 256u;
-    unsigned best = 0;
-    float best_cost = 0.f;
-    for (unsigned C = 1; C <= nb && C <= (unsigned)MG_MAXC; C++) {
-      if (nb % C) continue;
-      const unsigned sb = nb / C;
-      if (sb % 2) continue;
-      if (c_env[k] > 0 && (unsigned)c_env[k] != C) continue;
-      const float cost = (float)((groups * C + MG_NW - 1u) / MG_NW) * ((float)(sb * p.mats) * 0.5f + 1.0f);
-      if (!best || cost < best_cost) {
-        best = C;
-        best_cost = cost;
-      }
-    }
-    if (!best) return KS_OK;
-    p.n_cseg = best;
-    p.seg_blocks = nb / best;
+    const unsigned U = p.cols / 64u;
+    p.n_cseg = (U + 31u) / 32u;
+    if (p.n_cseg > (unsigned)MG_MAXC || U % p.n_cseg) return KS_OK;
+    p.seg_units = U / p.n_cseg;
     total_pieces += p.n_seg + (R + p.piece_rows - 1u) / p.piece_rows + 1u;
   }
   if (total_pieces > (unsigned)MG_MAXPIECE) return KS_OK;
@@ -1262,7 +1434,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
 
   ks_mega* mg = new ks_mega();
   cudaSetDevice(ctx->device);
-  const size_t prof_n = (size_t)2 * d->n_layers * PF_PER_LAYER * 4;
+  const size_t prof_n = (size_t)2 * d->n_layers * PF_PER_LAYER * PF_STAMPS;
   // tagged vectors, two of each: yd, yo [H], qkv [qn + 2 kvn], ox [qn], ff [F], rec [n_q * n_splits * (hd + 2)]
   const size_t n_rec = (size_t)nq * n_splits * (hd + 2);
   auto up2 = [](size_t n) { return (n + 1) & ~size_t(1); };   // keep every vector 16-byte aligned
@@ -1270,6 +1442,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   mg->ll_bytes = ll_words * sizeof(u64);
   if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256) != cudaSuccess ||
       cudaMalloc((void**)&mg->d_prof, prof_n * sizeof(long long)) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_prof_all, (size_t)grid * d->n_layers * PF_PER_LAYER * 8 * sizeof(long long)) != cudaSuccess ||
       cudaMalloc((void**)&mg->d_ll, mg->ll_bytes) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
@@ -1293,7 +1466,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.slot_bytes = slot_bytes;
   a.x_bytes = x_bytes;
   a.n_q = nq; a.n_kv = nkv; a.hd = hd; a.n_splits = n_splits;
-  a.split_from = 320;
+  a.split_from = MG_NW * MG_AB;  // one batch of rows per warp
   if (const char* e2 = getenv("KSEARCH_MEGA_SPLIT_FROM")) a.split_from = (unsigned)atoi(e2);
   a.eps = d->eps; a.attn_scale = d->attn_scale;
   a.rope = d->rope; a.pos = d->pos;
@@ -1316,9 +1489,9 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.test_stall = 0;
   a.prof = getenv("KSEARCH_PROFILE") ? mg->d_prof : nullptr;
   mg->grid = grid;
-  mg->smem = mg_smem(x_bytes, slot_bytes, n_slots, tables_bytes).total;
+  mg->smem = mg_smem(x_bytes, H, slot_bytes, n_slots, tables_bytes).total;
   mg->dpl = (int)(hd / 32);
-  mg->pc = H <= 4u * MG_THREADS ? 1 : 2;
+  mg->pc = (int)((H / 4u + MG_THREADS - 1u) / MG_THREADS);
   mg->residual = d->x_b;
   *out = mg;
   return KS_OK;

@@ -912,9 +912,13 @@ const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
   const size_t ab = ks_act_bytes((ks_dtype)m->cfg.act);
   if (which == 0) return (const char*)m->x + (size_t)slot * m->cfg.hidden * ab;
   if (which == 1) return (const char*)m->logits + (size_t)slot * m->cfg.vocab * ab;
-  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][n_layers][5][4] int64
+  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][n_layers][5][8] int64
     auto it = m->mega.find(slot);
     return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof(it->second);
+  }
+  if (which == 3) {  // the same for every block: [grid][n_layers][5][2] int64 (phase entered, rows stored)
+    auto it = m->mega.find(slot);
+    return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof_all(it->second);
   }
   return nullptr;
 }

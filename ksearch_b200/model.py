@@ -215,17 +215,19 @@ class GemmaCudaModel:
 
     def phase_clocks(self, slot: int = 0) -> np.ndarray:
         """SM clock stamps of the last token, int64 [2 (first, last block)][n_layers][5 (qkv, attention, o-proj,
-        gate-up, down)][4 (phase entered, input staged, items done, rows stored)]; recorded only after
-        debug_set(PHASE_CLOCKS, 1) or with KSEARCH_PROFILE set (gemma_prim.rs:885)."""
+        gate-up, down)][8]; matvec phases: entered, inputs arrived, x staged, tasks done, block joined, row stored
+        (6 used); attention: entered, q arrived, q/k/v built, positions done, folded, -,
+        stored, left.  Recorded only after debug_set(PHASE_CLOCKS, 1) or with KSEARCH_PROFILE set
+        (gemma_prim.rs:885)."""
         ptr = self.lib.ks_model_debug_ptr(self.h, 2, slot)
         if not ptr:
             raise KsError(_lib.ERR_STATE, "the persistent decode kernel has not run for this slot")
-        n = 2 * self.cfg.n_layers * 5 * 4
+        n = 2 * self.cfg.n_layers * 5 * 8
         buf = self.lib.ks_buf_wrap(self.ctx.h, ptr, n * 8)
         out = np.empty(n, np.int64)
         self.ctx.check(self.lib.ks_buf_download(self.ctx.h, buf, 0, out.ctypes.data, n * 8))
         self.lib.ks_buf_free(self.ctx.h, buf)
-        return out.reshape(2, self.cfg.n_layers, 5, 4)
+        return out.reshape(2, self.cfg.n_layers, 5, 8)
 
     def _kv_buf(self, layer: int, which: int, slot: int):
         ptr = self.lib.ks_model_kv_ptr(self.h, layer, which, slot)
