@@ -4,7 +4,7 @@
 // KV-owning layers; what changes is WHERE the boundaries between ops are and HOW a result reaches
 // its consumers.  A token is a chain of ~175 dependent steps of a few hundred kilobytes to ten
 // megabytes of weights each; neither a kernel boundary nor a grid-wide barrier is affordable
-// between them.  One block per SM (16 warps) stays resident for the whole token:
+// between them.  One block per SM (8 warps) stays resident for the whole token:
 //   * Dataflow instead of barriers.  Every activation that crosses blocks (q/k/v, attention
 //     output, o-proj output, GeGLU output, down-proj output, attention split records) is written
 //     as a 64-bit word (f32 value, 32-bit tag) with one relaxed store, tag = token epoch + layer.
@@ -454,7 +454,7 @@ __device__ MG_FN unsigned mg_stage_hidden(unsigned char* xs, float4* red, float*
 __device__ MG_FN unsigned mg_stage_plain(unsigned char* xs, unsigned cols, const u64* src, unsigned tag, const unsigned* err,
                                                 unsigned limit, unsigned st, long long* pf) {
   Poll pl{err, limit, (st & ST_GAVE_UP) != 0u};
-  constexpr int XC = 4;
+  constexpr int XC = 6;
   const unsigned units = cols >> 6, nchunk = cols >> 2;
   for (unsigned base = 0; base < nchunk; base += XC * MG_THREADS) {
     unsigned c[XC];

@@ -40,6 +40,13 @@ __global__ void end_token_kernel(int n, int* pos) {
   const int s = threadIdx.x;
   if (s < n) pos[s] += 1;
 }
+// What a blocking step brings back: the n next-token ids and, behind them, whether a device-side wait gave up.
+__global__ void collect_kernel(int n, const float* tok, const unsigned* err_word, float* ret) {
+  ks_pdl_entry();
+  const int s = threadIdx.x;
+  if (s < n) ret[s] = tok[s];
+  if (s == n) ret[n] = err_word[0] ? 1.0f : 0.0f;
+}
 __global__ void set_state_kernel(int slot, int pos_value, int* pos) { ks_pdl_entry(); pos[slot] = pos_value; }
 // A prompt chunk: row t of the chunk sits at position base + t of ONE slot (causal: it sees base + t + 1 positions).
 __global__ void begin_chunk_kernel(int n, const int* base, int* cpos, float* meta) {
@@ -95,6 +102,7 @@ struct ks_model {
   float* meta = nullptr;  // [n_slots][4]
   float* attn_tmp = nullptr;
   int n_splits = 1;
+  float* ret = nullptr;       // [n_slots][n_slots + 1] per first slot: next ids + status flag of the last blocking step
   float* host_tok = nullptr;  // pinned ring for token read-back
   size_t host_tok_n = 0;
   // graphs keyed by (first slot, n slots, src parity, want_logits)
@@ -135,6 +143,7 @@ struct Lane {
   char *x, *xb, *x2, *xn, *q, *k, *v, *o, *ff, *logits;
   const float* tok_in;
   float* tok_out;
+  float* ret;        // where a blocking step's ids and status flag are collected
   int* pos;          // device, one per row
   float* meta;       // device, (tlen, start, -, -) per row
   float* attn_tmp;
@@ -159,6 +168,7 @@ Lane slot_lane(ks_model* m, int first, int src) {
   L.logits = (char*)m->logits + (size_t)first * g.vocab * ab;
   L.tok_in = m->tok + (size_t)src * g.n_slots + first;
   L.tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  L.ret = m->ret + (size_t)first * (g.n_slots + 1);
   L.pos = m->pos + first;
   L.meta = m->meta + (size_t)first * 4;
   L.attn_tmp = m->attn_tmp;
@@ -249,7 +259,8 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  return KS_OK;
+  KS_LAUNCH(c, (collect_kernel), 1, 32, 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  return ks_after_launch(c, "collect");
 }
 
 // The same token with the norms folded into the matvecs that consume them: five launches per layer
@@ -323,7 +334,8 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, xn, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  return KS_OK;
+  KS_LAUNCH(c, (collect_kernel), 1, 32, 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  return ks_after_launch(c, "collect");
 }
 
 // One slot's token with every layer inside one persistent kernel; embedding before, head after.
@@ -350,7 +362,10 @@ int enqueue_forward_mega(ks_model* m, ks_mega* mg, int first, int src, bool want
     return rc;
   ks_mv_seg sh{(const uint8_t*)m->token_embd.dptr, logits, (unsigned)g.vocab};
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, KS_F32, xn, 1, nullptr))) return rc;
-  return ks_launch_softcap_argmax(c, g.vocab, g.softcap, KS_F32, logits, tok_out);
+  if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, KS_F32, logits, tok_out))) return rc;
+  KS_LAUNCH(c, (collect_kernel), 1, 32, 0, 1, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD,
+            m->ret + (size_t)first * (g.n_slots + 1));
+  return ks_after_launch(c, "collect");
 }
 
 // The persistent kernel of slot `first`, built on first use (outside any stream capture).
@@ -557,6 +572,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
        dev_alloc(m, &m->ff, S * F * ab) == KS_OK && dev_alloc(m, &m->logits, S * (size_t)g.vocab * ab) == KS_OK &&
        dev_alloc(m, (void**)&m->tok, 2 * S * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->pos, S * sizeof(int)) == KS_OK &&
        dev_alloc(m, (void**)&m->meta, S * 4 * sizeof(float)) == KS_OK &&
+       dev_alloc(m, (void**)&m->ret, S * (S + 1) * sizeof(float)) == KS_OK &&
        dev_alloc(m, (void**)&m->rope, (size_t)g.max_seq * g.hd * sizeof(float)) == KS_OK;
   {
     // every token of a chunk keeps its staged input vector in shared memory (280 bytes per 64 columns);
@@ -830,13 +846,15 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   KS_REQUIRE(c, tokens && next, "decode_token: null argument");
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
-  float* back = m->host_tok;
-  unsigned* status = reinterpret_cast<unsigned*>(m->host_tok + m->host_tok_n - 9);  // pinned word next to the id staging
-  KS_CUDA(c, cudaMemcpyAsync(back, m->tok + (size_t)m->tok_src[first] * m->cfg.n_slots + first, n * sizeof(float),
-                             cudaMemcpyDeviceToHost, c->stream));
-  KS_CUDA(c, cudaMemcpyAsync(status, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream));
+  float* back = m->host_tok;  // n ids, then the status flag
+  KS_CUDA(c, cudaMemcpyAsync(back, m->ret + (size_t)first * (m->cfg.n_slots + 1), (n + 1) * sizeof(float), cudaMemcpyDeviceToHost,
+                             c->stream));
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
-  if ((rc = check_device_status(m, status, first, n, 1))) return rc;
+  if (back[n] != 0.0f) {
+    unsigned flag = 0;
+    cudaMemcpy(&flag, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof flag, cudaMemcpyDeviceToHost);
+    if ((rc = check_device_status(m, &flag, first, n, 1))) return rc;
+  }
   for (int s = 0; s < n; s++) next[s] = (int)back[s];
   return KS_OK;
 }

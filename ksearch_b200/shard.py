@@ -7,7 +7,8 @@ NVLink on GPUs, gloo in the CPU tests).  Where only the arg-max of y is wanted (
 greedy decode), each rank reduces its own slice and 8 bytes per rank are gathered instead.
 
 The reference has no multi-device code (crates/ksearch_metal/src/lib.rs:33 uses the system default
-device); this module is new.  torch.distributed is plumbing here: process group, all-gather.
+device); this module is new.  The GPU path goes through the C ABI (ks_comm_*, ks_matvec_sharded,
+ks_argmax_sharded: NCCL on the context's stream); the row arithmetic below is shared with the CPU tests.
 """
 from __future__ import annotations
 
@@ -63,49 +64,77 @@ def merge_argmax(pairs, row0s) -> int:
     return best_i
 
 
-class ShardedMatvec:
-    """One rank's share of y = W x and the exchange that follows.
+class Comm:
+    """ks_comm of include/ksearch_cuda.h: one rank of the NCCL group the sharded ops exchange over."""
 
-    ctx: a CudaContext of this rank's GPU; W_local: the rank's packed rows (uint8).  all_gather runs on
-    torch.distributed's default group (NCCL on GPUs).  The context's stream is synchronised before
-    the collective, which is issued on torch's current stream.
+    ID_BYTES = 128
+
+    def __init__(self, ctx, world: int, rank: int, unique_id: bytes | None):
+        import ctypes as C
+        self.ctx, self.world, self.rank = ctx, world, rank
+        buf = C.create_string_buffer(unique_id, self.ID_BYTES) if unique_id is not None else None
+        self.h = ctx.lib.ks_comm_init(ctx.h, world, rank, buf)
+        if not self.h:
+            from .eng import KsError
+            raise KsError(-2, ctx.lib.ks_last_error(ctx.h).decode())
+
+    @staticmethod
+    def unique_id(lib) -> bytes:
+        """Rank 0 makes the rendezvous id; the other ranks get the bytes over any host channel."""
+        import ctypes as C
+        buf = C.create_string_buffer(Comm.ID_BYTES)
+        rc = lib.ks_comm_unique_id(buf)
+        if rc:
+            from .eng import KsError
+            raise KsError(rc, lib.ks_last_error(None).decode())
+        return buf.raw
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.ks_comm_destroy(self.h)
+            self.h = None
+
+
+class ShardedMatvec:
+    """One rank's share of y = W x and the exchange that follows, through the C ABI: x and the
+    gathered y stay on the device, everything is enqueued on the context's stream.
+
+    ctx: a CudaContext of this rank's GPU; comm: this rank's Comm; W_local: the rank's packed rows (uint8).
     """
 
-    def __init__(self, ctx, dtype: int, rows: int, cols: int, W_local: np.ndarray, world: int, rank: int):
-        import torch  # noqa: F401  (plumbing only)
-        self.ctx, self.dtype, self.rows, self.cols, self.world, self.rank = ctx, dtype, rows, cols, world, rank
-        self.r0, self.n = row_shard(rows, world, rank)
-        self.per = padded_rows(rows, world)
-        off, nb = shard_byte_range(dtype, rows, cols, world, rank)
+    def __init__(self, ctx, comm: Comm, dtype: int, rows: int, cols: int, W_local: np.ndarray):
+        self.ctx, self.comm, self.dtype, self.rows, self.cols = ctx, comm, dtype, rows, cols
+        self.world, self.rank = comm.world, comm.rank
+        self.r0, self.n = row_shard(rows, self.world, self.rank)
+        self.per = padded_rows(rows, self.world)
+        off, nb = shard_byte_range(dtype, rows, cols, self.world, self.rank)
         assert W_local.nbytes == nb, "W_local must be exactly this rank's rows"
-        self.W = ctx.buffer_bytes(W_local) if nb else None
-        self.y_local = ctx.buffer_empty_f32(self.per)
+        self.W = ctx.buffer_bytes(W_local) if nb else ctx.buffer_empty_bytes(16)
+        self.y_all = ctx.buffer_empty_f32(self.world * self.per)
         self.x = ctx.buffer_empty_f32(cols)
+        self.tok = ctx.buffer_empty_f32(1)
 
-    def _as_tensor(self, buf, n):
-        import torch
-
-        class _Arr:
-            __cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (buf.ptr, False), "version": 3}
-        return torch.as_tensor(_Arr(), device=f"cuda:{self.ctx.lib.ks_ctx_device(self.ctx.h)}")
-
-    def local(self, x_host: np.ndarray):
+    def set_x(self, x_host: np.ndarray):
         self.ctx.write_buffer(self.x, np.asarray(x_host, np.float32))
-        if self.n:
-            self.ctx.check(self.ctx.lib.ks_matvec(self.ctx.h, self.n, self.cols, self.dtype, self.W.h, 0, 0,
-                                                  self.x.h, 0, self.y_local.h, 0, 1))
 
-    def all_gather(self):
-        """Returns a torch tensor [world * per] with every rank's slice (padded)."""
-        import torch
-        import torch.distributed as dist
-        self.ctx.synchronize()
-        mine = self._as_tensor(self.y_local, self.per)
-        out = torch.empty(self.world * self.per, dtype=torch.float32, device=mine.device)
-        dist.all_gather_into_tensor(out, mine)
-        return out
+    def enqueue(self, gather: bool = True):
+        """Local rows into this rank's slot of y_all, then (gather) the in-place all-gather."""
+        self.ctx.check(self.ctx.lib.ks_matvec_sharded(self.comm.h, self.n, self.per, self.cols, self.dtype, self.W.h, 0,
+                                                      self.x.h, 0, self.y_all.h, 0, 1 if gather else 0))
+
+    def enqueue_argmax(self, cap: float):
+        """Greedy token from the local logits: one (value, index) pair per rank is gathered instead of the vector."""
+        self.ctx.check(self.ctx.lib.ks_argmax_sharded(self.comm.h, self.n, self.r0, cap, self.y_all.h, self.rank * self.per,
+                                                      self.tok.h, 0))
 
     def forward(self, x_host: np.ndarray) -> np.ndarray:
-        self.local(x_host)
-        g = self.all_gather().cpu().numpy().reshape(self.world, self.per)
+        self.set_x(x_host)
+        self.enqueue(True)
+        g = self.ctx.read_f32(self.y_all, self.world * self.per).reshape(self.world, self.per)
         return gather_rows(list(g), self.rows, self.world)
+
+    def argmax(self, x_host: np.ndarray, cap: float) -> int:
+        self.set_x(x_host)
+        self.enqueue(False)
+        self.enqueue_argmax(cap)
+        return int(self.ctx.read_f32(self.tok, 1)[0])
