@@ -238,6 +238,9 @@ def time_kernels_alone(ctx, model, slot, cfg, peak, steps):
     # The persistent decode kernel: steps without the head are embed + that kernel + a one-thread
     # position update, so their device time is the kernel's (the two small launches add ~2 us).
     n = max(8, min(steps, 32))
+    model.slot_reset(slot)
+    for i in range(PROMPT_LEN):   # the benchmark's context length, then 6 x n more positions
+        model.forward(slot, 1, [1 + i], False)
 
     def layers_only():
         for i in range(n):
@@ -492,7 +495,7 @@ def main():
     from ksearch_b200 import synth
     peak, peak_kind = measured_peak()
     ctx = CudaContext(local, flags=1)  # bit 0: programmatic dependent launch
-    cfg = ksm.e2b_config(max_seq=PROMPT_LEN + args.steps * 2 + args.warmup * 2 + 16 + 64)
+    cfg = ksm.e2b_config(max_seq=PROMPT_LEN + args.steps * 2 + args.warmup * 2 + 16 + 64 + 256)
     want_cpu = world == 1 and not args.no_cpu_baseline
     if want_cpu:
         model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, SEED + rank, keep=True)

@@ -782,7 +782,12 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
     }
     KS_CUDA(c, cudaMemcpyAsync(m->tok + first, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
   }
-  if ((rc = run_forward(m, first, n, src, want_logits != 0))) return rc;
+  // The slots share one pass over the weights as long as their staged input vectors fit the matvec kernels'
+  // shared memory side by side (m->chunk of them); a larger batch takes several passes.
+  for (int s0 = 0; s0 < n; s0 += m->chunk) {
+    const int nn = n - s0 < m->chunk ? n - s0 : m->chunk;
+    if ((rc = run_forward(m, first + s0, nn, src, want_logits != 0))) return rc;
+  }
   for (int s = first; s < first + n; s++) {
     m->seq_len[s] += 1;
     m->tok_src[s] = (char)(want_logits ? (src ^ 1) : src);
@@ -847,8 +852,14 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
   float* back = m->host_tok;  // n ids, then the status flag
-  KS_CUDA(c, cudaMemcpyAsync(back, m->ret + (size_t)first * (m->cfg.n_slots + 1), (n + 1) * sizeof(float), cudaMemcpyDeviceToHost,
-                             c->stream));
+  if (n <= m->chunk) {        // one pass: its last kernel collected ids and flag side by side, one copy brings both
+    KS_CUDA(c, cudaMemcpyAsync(back, m->ret + (size_t)first * (m->cfg.n_slots + 1), (n + 1) * sizeof(float), cudaMemcpyDeviceToHost,
+                               c->stream));
+  } else {                    // several passes: ids from the token buffer, the flag as any non-zero status word
+    KS_CUDA(c, cudaMemcpyAsync(back, m->tok + (size_t)m->tok_src[first] * m->cfg.n_slots + first, n * sizeof(float),
+                               cudaMemcpyDeviceToHost, c->stream));
+    KS_CUDA(c, cudaMemcpyAsync(back + n, (unsigned*)c->ws + KS_WS_ERR_WORD, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream));
+  }
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
   if (back[n] != 0.0f) {
     unsigned flag = 0;

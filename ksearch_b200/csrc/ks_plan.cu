@@ -148,6 +148,8 @@ int ks_plan_candidates(const char* op, ks_plan* out, int max_out) {
         }
   for (int nr : {2, 4})  // the direct-load kernels
     for (int cps : {2, 4}) c.push_back(ks_plan{1, nr, 8, cps, 0.f});
+  if (!q6 && !gu && strncmp(op, "qkv_", 4) != 0)  // Q4_K rows out of a shared-memory ring against a block fixed-point x
+    for (int cps : {1, 2}) c.push_back(ks_plan{3, 0, 8, cps, 0.f});
   if (q6)  // block fixed-point x, byte dot products
     for (int nr : {1, 2})
       for (int nw : {4, 8})

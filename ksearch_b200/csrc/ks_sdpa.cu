@@ -61,27 +61,42 @@ __device__ __forceinline__ int lane_dim(int lane, int j) {
   return j < BPL ? base + j : base + 16 + (j - BPL);
 }
 
-template <int G, int DPL, typename T>
+constexpr int kRing = 8;  // rows of one warp in flight (K and V each)
+
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// ASYNC: the rows of a warp travel through a ring of kRing shared-memory buffers filled by cp.async (8 bytes per
+// lane), so kRing rows of K and V are in flight per warp while one is being multiplied; without it a warp waited
+// out one full memory round trip per row.  Needs 8-byte aligned rows; the plain path takes the rest.
+// G: query heads served by one block (at most 4: more would not leave registers for enough warps per SM); a KV head
+// with a larger group is served by hpk / G blocks (blockIdx.y = kvh * (hpk / G) + group), each reading the rows itself.
+template <int G, int DPL, typename T, bool ASYNC>
 __global__ void __launch_bounds__(kWarps * 32)
 sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uint8_t* K, const uint8_t* V,
                  size_t slot_stride, const float* meta, float* tmp, T* out, int n_splits) {
   ks_pdl_entry();
   constexpr int HD = DPL * 32;
+  constexpr unsigned ROWB = (HD / 32) * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int split = blockIdx.x, kvh = blockIdx.y, slot = blockIdx.z;
+  const unsigned hpk = n_q / n_kv, gpk = hpk / G;  // heads and blocks per KV head
+  const int split = blockIdx.x, kvh = blockIdx.y / gpk, slot = blockIdx.z;
+  const unsigned head0 = (unsigned)kvh * hpk + (blockIdx.y % gpk) * G;  // first query head of this block
   const unsigned tlen = (unsigned)meta[slot * 4 + 0];
   const unsigned start = (unsigned)meta[slot * 4 + 1];
   const unsigned chunk = (tlen + n_splits - 1) / n_splits;
   const unsigned p0 = split * chunk;
   const unsigned p1 = min(p0 + chunk, tlen);
-  const size_t rowb = (size_t)(HD / 32) * KS_Q40_BLOCK_BYTES;
+  const size_t rowb = ROWB;
   const uint8_t* Ks = K + (size_t)slot * slot_stride;
   const uint8_t* Vs = V + (size_t)slot * slot_stride;
+  __shared__ __align__(16) uint8_t ring[ASYNC ? kWarps * kRing * 2 * ROWB : 16];
 
   float qr[G][DPL], o[G][DPL], m[G], l[G];
 #pragma unroll
   for (int g = 0; g < G; g++) {
-    const size_t qb = ((size_t)slot * n_q + (size_t)kvh * G + g) * HD;
+    const size_t qb = ((size_t)slot * n_q + head0 + g) * HD;
 #pragma unroll
     for (int j = 0; j < DPL; j++) {
       qr[g][j] = ld_act<T>(q, qb + lane_dim<DPL>(lane, j)) * scale;
@@ -91,10 +106,10 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
     l[g] = 0.0f;
   }
 
-  for (unsigned t = p0 + warp; t < p1; t += kWarps) {
-    const size_t row = ((size_t)(start + t) * n_kv + kvh) * rowb;
+  // one position: scores of the G heads against the K row, then the online-softmax update with the V row
+  auto step = [&](const uint8_t* krow, const uint8_t* vrow) {
     float kv[DPL];
-    load_row<DPL>(Ks + row, lane, kv);
+    load_row<DPL>(krow, lane, kv);
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
@@ -107,16 +122,53 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
     for (int off = 16; off > 0; off >>= 1)
 #pragma unroll
       for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
-    load_row<DPL>(Vs + row, lane, kv);
+    load_row<DPL>(vrow, lane, kv);
 #pragma unroll
     for (int g = 0; g < G; g++) {
-      const float m2 = fmaxf(m[g], s[g]);
-      const float alpha = __expf(m[g] - m2);
-      const float e = __expf(s[g] - m2);
-      l[g] = l[g] * alpha + e;
-      m[g] = m2;
+      if (s[g] > m[g]) {  // a new maximum (the same in every lane): rescale what was gathered so far
+        const float alpha = __expf(m[g] - s[g]);
+        l[g] *= alpha;
 #pragma unroll
-      for (int j = 0; j < DPL; j++) o[g][j] = fmaf(e, kv[j], o[g][j] * alpha);
+        for (int j = 0; j < DPL; j++) o[g][j] *= alpha;
+        m[g] = s[g];
+      }
+      const float e = __expf(s[g] - m[g]);
+      l[g] += e;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) o[g][j] = fmaf(e, kv[j], o[g][j]);
+    }
+  };
+
+  if (ASYNC) {
+    uint8_t* my = ring + (size_t)warp * (kRing * 2 * ROWB);
+    const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(my);
+    auto fetch = [&](unsigned n) {  // the warp's n-th position into buffer n % kRing (an empty group past the end)
+      const unsigned t = p0 + (unsigned)warp + n * kWarps;
+      if (t < p1 && lane < (int)(ROWB / 8u)) {
+        const size_t row = ((size_t)(start + t) * n_kv + kvh) * rowb + (size_t)lane * 8u;
+        const uint32_t dst = my_s + (n % kRing) * (2u * ROWB) + (uint32_t)lane * 8u;
+        cp_async8(dst, Ks + row);
+        cp_async8(dst + ROWB, Vs + row);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll 1
+    for (unsigned n = 0; n < (unsigned)kRing; n++) fetch(n);
+    unsigned n = 0;
+#pragma unroll 1
+    for (unsigned t = p0 + warp; t < p1; t += kWarps, n++) {
+      asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
+      __syncwarp();
+      const uint8_t* buf = my + (size_t)(n % kRing) * (2u * ROWB);
+      step(buf, buf + ROWB);
+      __syncwarp();  // every lane is done with the buffer before it is refilled
+      fetch(n + kRing);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else {
+    for (unsigned t = p0 + warp; t < p1; t += kWarps) {
+      const size_t row = ((size_t)(start + t) * n_kv + kvh) * rowb;
+      step(Ks + row, Vs + row);
     }
   }
 
@@ -147,7 +199,7 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
 #pragma unroll
       for (int j = 0; j < DPL; j++) o[g][j] = o[g][j] * alpha + sm_o[w][g][j * 32 + lane] * beta;
     }
-    const unsigned head = kvh * G + g;
+    const unsigned head = head0 + g;
     if (n_splits == 1) {
       const float inv_l = 1.0f / l[g];
       const size_t ob = ((size_t)slot * n_q + head) * HD;
@@ -165,32 +217,50 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
   }
 }
 
-// Merge the per-split records of one (slot, head): lower.rs:5897-6088.
+// Merge the per-split records of one (slot, head): lower.rs:5897-6088.  The (m, l) pairs go through shared
+// memory; thread d then adds O[d] of the splits eight at a time, every load of a batch issued before any is used
+// (one after the other they cost a memory round trip per split).
 template <typename T>
 __global__ void sdpa_reduce_kernel(unsigned hd, const float* tmp, T* out, int n_splits) {
   ks_pdl_entry();
+  __shared__ float sm[2 * KS_SDPA_MAX_SPLITS];
   const size_t sh = blockIdx.x;  // slot * n_q + head
   const float* rec0 = tmp + sh * n_splits * (hd + 2);
+  for (int p = threadIdx.x; p < n_splits; p += blockDim.x) {
+    sm[2 * p] = rec0[(size_t)p * (hd + 2)];
+    sm[2 * p + 1] = rec0[(size_t)p * (hd + 2) + 1];
+  }
+  __syncthreads();
+  float M = kNegInit;
+  for (int p = 0; p < n_splits; p++) M = fmaxf(M, sm[2 * p]);
+  float L = 0.0f;
+  for (int p = 0; p < n_splits; p++) L = fmaf(sm[2 * p + 1], __expf(sm[2 * p] - M), L);
+  const float inv_l = 1.0f / L;
   for (unsigned d = threadIdx.x; d < hd; d += blockDim.x) {
-    float m = kNegInit, l = 0.0f, o = 0.0f;
-    for (int p = 0; p < n_splits; p++) {
-      const float* rec = rec0 + (size_t)p * (hd + 2);
-      const float mp = rec[0], lp = rec[1];
-      const float m2 = fmaxf(m, mp);
-      const float alpha = __expf(m - m2), beta = __expf(mp - m2);
-      l = l * alpha + lp * beta;
-      m = m2;
-      o = o * alpha + rec[2 + d] * beta;
+    float o = 0.0f;
+    for (int pb = 0; pb < n_splits; pb += 8) {
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++)
+        if (pb + k < n_splits) v[k] = rec0[(size_t)(pb + k) * (hd + 2) + 2 + d];
+#pragma unroll
+      for (int k = 0; k < 8; k++)
+        if (pb + k < n_splits) o = fmaf(v[k], __expf(sm[2 * (pb + k)] - M), o);
     }
-    st_act<T>(out, sh * hd + d, o * (1.0f / l));
+    st_act<T>(out, sh * hd + d, o * inv_l);
   }
 }
 
 template <int G, int DPL, typename T>
 int launch_part(ks_ctx* ctx, dim3 grid, unsigned n_q, unsigned n_kv, float scale, const void* q, const uint8_t* K,
                 const uint8_t* V, size_t slot_stride, const float* meta, float* tmp, void* out, int n_splits) {
-  KS_LAUNCH(ctx, (sdpa_part_kernel<G, DPL, T>), grid, kWarps * 32, 0, n_q, n_kv, scale, (const T*)q, K, V, slot_stride, meta,
-                                                                   tmp, (T*)out, n_splits);
+  const bool aligned = (((uintptr_t)K | (uintptr_t)V | (uintptr_t)slot_stride) & 7u) == 0;
+  if (aligned)
+    KS_LAUNCH(ctx, (sdpa_part_kernel<G, DPL, T, true>), grid, kWarps * 32, 0, n_q, n_kv, scale, (const T*)q, K, V, slot_stride, meta,
+              tmp, (T*)out, n_splits);
+  else
+    KS_LAUNCH(ctx, (sdpa_part_kernel<G, DPL, T, false>), grid, kWarps * 32, 0, n_q, n_kv, scale, (const T*)q, K, V, slot_stride,
+              meta, tmp, (T*)out, n_splits);
   return ks_after_launch(ctx, "sdpa_part");
 }
 
@@ -201,9 +271,12 @@ int launch_part_g(ks_ctx* ctx, int G, dim3 grid, unsigned n_q, unsigned n_kv, fl
     case 1: return launch_part<1, DPL, T>(ctx, grid, n_q, n_kv, scale, q, K, V, slot_stride, meta, tmp, out, n_splits);
     case 2: return launch_part<2, DPL, T>(ctx, grid, n_q, n_kv, scale, q, K, V, slot_stride, meta, tmp, out, n_splits);
     case 4: return launch_part<4, DPL, T>(ctx, grid, n_q, n_kv, scale, q, K, V, slot_stride, meta, tmp, out, n_splits);
-    case 8: return launch_part<8, DPL, T>(ctx, grid, n_q, n_kv, scale, q, K, V, slot_stride, meta, tmp, out, n_splits);
+    case 8:
+    case 16:  // four heads per block, G / 4 blocks per KV head
+      grid.y *= (unsigned)(G / 4);
+      return launch_part<4, DPL, T>(ctx, grid, n_q, n_kv, scale, q, K, V, slot_stride, meta, tmp, out, n_splits);
   }
-  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "sdpa: n_q/n_kv = %d not supported (1, 2, 4, 8)", G);
+  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "sdpa: n_q/n_kv = %d not supported (1, 2, 4, 8, 16)", G);
 }
 
 }  // namespace
@@ -226,9 +299,9 @@ int ks_launch_sdpa(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t 
   if (rc || n_splits == 1) return rc;
   const unsigned blocks = (unsigned)(n_slots * n_q);
   if (act == KS_F32)
-    KS_LAUNCH(ctx, (sdpa_reduce_kernel<float>), blocks, 128, 0, (unsigned)hd, tmp, (float*)out, n_splits);
+    KS_LAUNCH(ctx, (sdpa_reduce_kernel<float>), blocks, 256, 0, (unsigned)hd, tmp, (float*)out, n_splits);
   else
-    KS_LAUNCH(ctx, (sdpa_reduce_kernel<__half>), blocks, 128, 0, (unsigned)hd, tmp, (__half*)out, n_splits);
+    KS_LAUNCH(ctx, (sdpa_reduce_kernel<__half>), blocks, 256, 0, (unsigned)hd, tmp, (__half*)out, n_splits);
   return ks_after_launch(ctx, "sdpa_reduce");
 }
 

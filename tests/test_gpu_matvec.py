@@ -292,3 +292,26 @@ def test_rmsnorm_fused_into_matvec(ctx, oracle, act):
         e.rmsnorm_matvec_wd(ctx, rows, cols, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y, y_prev=byp)
     with pytest.raises(KsError):   # 6144 columns: no fused norm
         e.rmsnorm_matvec_wd(ctx, 8, 6144, eps, Q4K, bx, bwn, ctx.buffer_bytes(W), y)
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (6144, 1536), (1536, 6144), (2560, 10240), (10240, 2560), (130, 2048), (7, 768), (64, 512)])
+def test_matvec_q4k_fixed_point_variant(ctx, oracle, rows, cols):
+    """Planner variant 3: rows out of a shared-memory ring against a block fixed-point x (exact integer
+    products); the same bounds as the f32 kernels."""
+    from ksearch_b200 import _lib
+    W = _gen(Q4K, 73, f"W{rows}x{cols}", rows, cols)
+    x = synth.normals(73, "x", cols)
+    y = ctx.buffer_empty_f32(rows)
+    bw = ctx.buffer_bytes(W)
+    for cps in (1, 2):
+        ctx.plan_override(_lib.Plan(3, 0, 8, cps, 0.0))
+        try:
+            n0 = ctx.launch_count()
+            Eng().matvec_wd(ctx, rows, cols, Q4K, bw, ctx.buffer_bytes(x), y)
+            got = ctx.read_f32(y, rows)
+        finally:
+            ctx.plan_override(None)
+        assert ctx.launch_count() == n0 + 1
+        y32, y64 = oracle.matvec(Q4K, W, rows, cols, x)
+        _check(got, y32, y64, f"fx {rows}x{cols} cps={cps}")
+    bw.free()
