@@ -138,7 +138,7 @@ def workload_config(n_gpus):
                           "dp4a integer sums, scaled back in f32"}
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank, world, emit):
     """The reference's CPU path (dequant + f32 dot decoder restated in C) on the full model, all host threads:
     the benchmark's prompt, W warm-up tokens, then K timed greedy tokens."""
     if rank != 0:
@@ -172,7 +172,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def cpu_baseline_and_parity(cfg, T, prompt, gpu_tokens):
@@ -467,6 +467,15 @@ def sharded_matvecs(ctx, rank, world, dist, peak):
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) print to stdout; the one JSON line must be alone there, so everything
+    # else goes to stderr and the line is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(out_fd, (json.dumps(obj) + "\n").encode())
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -480,7 +489,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, emit)
         return
 
     dist = None
@@ -601,7 +610,7 @@ def main():
         if rank == 0:
             line["serve_e4b"] = sv
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()

@@ -99,7 +99,7 @@ void ks_graph_free(ks_ctx* ctx, ks_graph* g);
  * crates/ksearch_ir/src/kernel.rs:11-54, retargeted to the knobs of the hand-written matvec
  * kernels.  A zero field means "kernel default". */
 typedef struct {
-  int variant;      /* bits 0-7 kernel family (0 streamed, 1 direct loads, 2 Q6_K fixed point, 3 Q4_K fixed point out of a shared-memory ring), 8-15 pipeline stages, 16-23 blocks per column segment (0 = auto) */
+  int variant;      /* bits 0-7 kernel family (0 streamed, 1 direct loads, 2 Q6_K fixed point, 3 Q4_K fixed point out of a shared-memory ring, 4 Q6_K fixed point out of shared-memory rings), 8-15 pipeline stages, 16-23 blocks per column segment (0 = auto) */
   int nr;           /* rows kept in flight per lane group (nr0) */
   int nwarps;       /* warps per block (nsg) */
   int ctas_per_sm;  /* grid = min(tiles, SMs * ctas_per_sm) */

@@ -117,6 +117,10 @@ int ks_launch_matvec_stream_q6k(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, s
 // variant 2 (Q6_K only): x as block fixed point, byte dot products; returns 1 when the call must use another variant
 int ks_launch_matvec_q6k_fx(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x, int n_tok,
                             const ks_plan* plan);
+// variant 4 (Q6_K): variant 2's arithmetic with the rows streamed through per-warp shared-memory rings; returns 1 when
+// the call must use another variant
+int ks_launch_matvec_q6k_ring(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, size_t cols, ks_dtype act, const void* x, int n_tok,
+                              const ks_plan* plan);
 // variant 3 (Q4_K, one token, f32): rows out of a shared-memory ring against a block fixed-point x (ks_mv_fx.cu);
 // returns 1 when the call must use another variant
 int ks_launch_matvec_q4k_fx(ks_ctx* ctx, const ks_mv_seg* segs, int n_seg, ks_mv_epilogue epi, size_t cols, ks_dtype act,

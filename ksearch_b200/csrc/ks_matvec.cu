@@ -345,7 +345,11 @@ int ks_launch_matvec(ks_ctx* ctx, ks_dtype wdtype, const ks_mv_seg* segs, int n_
   }
   if (wdtype == KS_Q4K && (!plan || (plan->variant & 0xFF) == 0 || (plan->variant & 0xFF) == 3))
     return ks_launch_matvec_stream_q4k(ctx, segs, n_seg, epi, cols, act, x, n_tok, plan, nullptr);
-  if (wdtype == KS_Q6K && (!plan || (plan->variant & 0xFF) == 2)) {  // also the default: single-token calls take it, others fall through
+  if (wdtype == KS_Q6K && plan && (plan->variant & 0xFF) == 4) {
+    const int rc = ks_launch_matvec_q6k_ring(ctx, segs, n_seg, cols, act, x, n_tok, plan);
+    if (rc != 1) return rc;
+  }
+  if (wdtype == KS_Q6K && (!plan || (plan->variant & 0xFF) == 2 || (plan->variant & 0xFF) == 4)) {  // also the default: single-token calls take it, others fall through
     const int rc = ks_launch_matvec_q6k_fx(ctx, segs, n_seg, cols, act, x, n_tok, plan);
     if (rc != 1) return rc;
   }

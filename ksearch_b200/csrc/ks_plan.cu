@@ -154,6 +154,10 @@ int ks_plan_candidates(const char* op, ks_plan* out, int max_out) {
     for (int nr : {1, 2})
       for (int nw : {4, 8})
         for (int cps : {4, 6, 8}) c.push_back(ks_plan{2, nr, nw, cps, 0.f});
+  if (q6)  // the same arithmetic, rows streamed through per-warp shared-memory rings
+    for (int st : {2, 3})
+      for (int nr : {1, 2})
+        for (int nw : {8, 10, 12, 16}) c.push_back(ks_plan{4 | (st << 8), nr, nw, 1, 0.f});
   const int n = std::min<int>((int)c.size(), max_out);
   for (int i = 0; i < n; i++) out[i] = c[i];
   return n;

@@ -315,3 +315,24 @@ def test_matvec_q4k_fixed_point_variant(ctx, oracle, rows, cols):
         y32, y64 = oracle.matvec(Q4K, W, rows, cols, x)
         _check(got, y32, y64, f"fx {rows}x{cols} cps={cps}")
     bw.free()
+
+
+@pytest.mark.parametrize("rows,cols", [(512, 1536), (4096, 1536), (1024, 2560), (8, 256), (264, 768)])
+def test_matvec_q6k_ring_variant(ctx, oracle, rows, cols):
+    """Planner variant 4: the Q6_K rows streamed through per-warp shared-memory rings (one bulk copy per 8 rows),
+    the arithmetic of variant 2; signed scales; two and three stages."""
+    from ksearch_b200 import _lib
+    W = synth.q6k_matrix(74, f"W{rows}x{cols}", rows, cols, signed_scales=True)
+    x = synth.normals(74, "x", cols)
+    y = ctx.buffer_empty_f32(rows)
+    bw = ctx.buffer_bytes(W)
+    y32, y64 = oracle.matvec(Q6K, W, rows, cols, x)
+    for stages, nw in ((2, 8), (3, 6)):
+        ctx.plan_override(_lib.Plan(4 | (stages << 8), 2, nw, 1, 0.0))
+        try:
+            Eng().matvec_wd(ctx, rows, cols, Q6K, bw, ctx.buffer_bytes(x), y)
+            got = ctx.read_f32(y, rows)
+        finally:
+            ctx.plan_override(None)
+        _check(got, y32, y64, f"q6k ring {rows}x{cols} stages={stages}")
+    bw.free()
