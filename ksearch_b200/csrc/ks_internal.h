@@ -161,16 +161,28 @@ struct ks_mega_desc {
   float* att_tmp;     // n_q * n_splits * (hd + 2) floats
   int n_splits;
 };
-struct ks_mega;
+// Two kernels take the same description.  ks_mega_* (ks_mega.cu): phases separated by grid-wide barriers,
+// inputs staged from plain global vectors.  ks_flow_* (ks_flow.cu): no barriers, every value that crosses
+// blocks travels as a tagged 64-bit word and consumers poll for the tags.
 // *out == nullptr with KS_OK: shape not covered, keep the launch-per-op path.
+struct ks_mega;
 int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* layers, ks_mega** out);
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg);
 float* ks_mega_residual(const ks_mega* mg);  // where the residual stream is when the kernel ends (yb holds the last down-proj)
-const long long* ks_mega_prof(const ks_mega* mg);  // [2][n_layers][5][8] clock stamps of the last token (first, last block)
-const long long* ks_mega_prof_all(const ks_mega* mg);  // [grid][n_layers][5][8]: every block's stamps (globaltimer ns)
-int ks_mega_reset(ks_ctx* ctx, ks_mega* mg);  // working order again after a timed-out wait
-int ks_mega_set(ks_mega* mg, int what, unsigned value);  // test / profiling knobs, see ks_mega.cu
+const long long* ks_mega_prof(const ks_mega* mg);  // [2][5 * n_layers][8] clock64 stamps of the last token (first, last block)
+int ks_mega_reset(ks_ctx* ctx, ks_mega* mg);  // barrier words back to their rest state (after a timed-out wait)
+int ks_mega_set(ks_mega* mg, int what, unsigned value);  // test knobs: 0 poll limit, 1 stall one barrier
 void ks_mega_destroy(ks_mega* mg);
+
+struct ks_flow;
+int ks_flow_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* layers, ks_flow** out);
+int ks_flow_launch(ks_ctx* ctx, ks_flow* mg);
+float* ks_flow_residual(const ks_flow* mg);
+const long long* ks_flow_prof(const ks_flow* mg);  // [2][n_layers][5][8] globaltimer stamps of the last token (first, last block)
+const long long* ks_flow_prof_all(const ks_flow* mg);  // [grid][n_layers][5][8]: every block's stamps
+int ks_flow_reset(ks_ctx* ctx, ks_flow* mg);  // working order again after a timed-out wait
+int ks_flow_set(ks_flow* mg, int what, unsigned value);  // test / profiling knobs, see ks_flow.cu
+void ks_flow_destroy(ks_flow* mg);
 
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Every kernel of the library is launched through ks_launch_k.  When the context was created with

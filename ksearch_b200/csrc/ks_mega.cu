@@ -1,66 +1,42 @@
 // One persistent kernel for all layers of a decode token (single slot, f32 activations).
 //
 // The op order is forward_token's (crates/ksearch_gemma/src/gemma_prim.rs:923-1197) for dense,
-// KV-owning layers; what changes is WHERE the boundaries between ops are and HOW a result reaches
-// its consumers.  A token is a chain of ~175 dependent steps of a few hundred kilobytes to ten
-// megabytes of weights each; neither a kernel boundary nor a grid-wide barrier is affordable
-// between them.  One block per SM (8 warps) stays resident for the whole token:
-//   * Dataflow instead of barriers.  Every activation that crosses blocks (q/k/v, attention
-//     output, o-proj output, GeGLU output, down-proj output, attention split records) is written
-//     as a 64-bit word (f32 value, 32-bit tag) with one relaxed store, tag = token epoch + layer.
-//     A consumer polls the words it needs until their tags match.  Value and tag travel in one
-//     single-copy-atomic word, so no fence, no flag and no second round trip is needed: a hop
-//     between phases costs one store and one load through L2.  Buffers alternate by layer parity.
-//   * Rows are split evenly: block b owns the contiguous rows [b*R/grid, (b+1)*R/grid) (in pairs)
-//     of every matvec phase, so its weights are ONE contiguous byte range per matrix and phase.
-//   * The weight stream never stops: those ranges are cut into pieces that fit a slot of a
-//     block-wide shared-memory ring fed by cp.async.bulk (mbarrier completion).  The pieces of all
-//     phases and layers form one sequence; when the block is done with a slot, a lane of its last warp
-//     refills it with the piece n_slots further down the sequence, so the next phases' (and layer's)
-//     weights arrive while the block computes or waits for its inputs.
-//   * Inside a phase a task is one row x one 32-unit column segment (a lane owns one 64-weight unit
-//     and keeps that unit of x in registers); each warp takes one contiguous run of the block's tasks,
-//     two rows interleaved; row sums meet in shared memory, thread f finishes row f.
-//   * x is staged once per phase and block as 24-bit block fixed point (three byte planes per
-//     32-element sub-block) so weight nibbles x x are exact dp4a integer sums.
-//   * The residual stream never leaves the block: every block applies the same residual-add + norm
-//     to the same inputs in the same order, so each thread keeps its elements in registers.
-//   * Attention: one block per (query head, context split); short contexts use one split (no
-//     merge hop), long ones merge the split records in the head's first block.
-// Every wait (tag poll, mbarrier) is bounded; on expiry the block raises the context's status
-// word and carries on without waiting any more, so the kernel always ends; blocks that see the
-// status word raised stop waiting too.
-#include <cstdlib>
-#include <cstring>
+// KV-owning layers; what changes is WHERE the boundaries between ops are.  On B200 a token is a
+// chain of ~180 dependent steps, each a few hundred kilobytes to ten megabytes of weights, and a
+// kernel boundary costs more than most of those steps take.  Here one block per SM stays resident
+// for the whole token:
+//   * the weight stream never stops: every warp owns a ring of shared-memory stages fed by
+//     cp.async.bulk, and walks ONE item list for the whole token (all its row groups of all phases);
+//     the copies of the next phases are already in flight while the block waits at a barrier;
+//   * phases (qkv | attention | o-proj | gate-up | down, per layer) are separated by a grid barrier
+//     on one global counter; activations cross it through global memory (L2), read with ld.cg;
+//   * the norms are applied while x is staged; their weights are fetched BEFORE the barrier wait,
+//     because the acquire that ends the wait drops the SM's L1 and every later plain load of a
+//     constant would be a full round trip to L2;
+//   * for the same reason nothing on the critical path reads a descriptor from global memory: the
+//     five phase shapes and the per-layer pointers are copied to shared memory once;
+//   * attention: per-head RMS + RoPE + Q4_0 pack of the new K/V row, split-context online softmax
+//     and the merge of the splits (last arriving block) happen inside one phase.
+// Every spin (barrier, mbarrier) is bounded; on expiry the block raises the context's status word,
+// drains its copies and leaves, and the other blocks time out the same way.
 #include <utility>
 #include <vector>
 
-#include "ks_fx.cuh"
+#include "ks_mv_common.cuh"
 
 namespace {
 
-enum { PH_QKV = 0, PH_OPROJ = 1, PH_GATEUP = 2, PH_DOWN = 3, PH_KINDS = 4 };
-enum { PF_QKV = 0, PF_ATTN = 1, PF_OPROJ = 2, PF_GATEUP = 3, PF_DOWN = 4, PF_PER_LAYER = 5, PF_STAMPS = 8 };
+enum { MG_MATVEC = 0, MG_GATE_UP = 1, MG_ATTN = 2 };
+enum { PH_QKV = 0, PH_ATTN = 1, PH_OPROJ = 2, PH_GATEUP = 3, PH_DOWN = 4, PH_PER_LAYER = 5 };
 
-#ifndef MG_NW_CFG
-#define MG_NW_CFG 8
-#endif
-#ifndef MG_FN
-#define MG_FN __forceinline__
-#endif
-constexpr int MG_NW = MG_NW_CFG, MG_THREADS = MG_NW * 32;  // warps per block (at least 8)
-constexpr int MG_MAXPIECE = 64;   // pieces of one layer owned by one block
-constexpr int MG_MAXROWS = 96;    // rows of one phase owned by one block
-constexpr int MG_MAXC = 8;        // column segments per row
-constexpr int MG_MAXSLOTS = 16;   // ring slots
-constexpr int MG_MAX_SPLITS = 16; // context splits per head
-
-struct MegaPhase {          // one matvec phase of a layer; the same for every layer
-  unsigned n_seg;           // matrices laid end to end in the phase's row space (qkv: 3, else 1)
-  unsigned mats;            // matrices multiplied per row (gate-up: 2, gate row i and up row i)
-  unsigned seg_start[4];    // first row of each matrix in the row space; [n_seg] = total rows
-  unsigned widx;            // MegaLayer::W index of the first matrix
-  unsigned cols, row_bytes, seg_units, n_cseg, piece_rows;  // n_cseg column segments of seg_units (<= 32) 64-weight units
+struct MegaShape {          // one of the five phases of a layer; the same for every layer
+  int type;
+  int n_seg;                // matvec: 1 or 3 (q, k, v)
+  unsigned rows[3];
+  unsigned grp_start[4];    // first group of each segment, [n_seg] = total groups (0 for attention)
+  unsigned cols, row_bytes, seg_blocks, n_cseg;
+  int oct;                  // 1: a block owns runs of 8 consecutive groups (32 rows = one sub-block of the next phase's x)
+  int split;                // gate-up only, 1: the gate rows and the up rows of a group are two items (rows too long for one slot)
 };
 
 struct MegaLayer {          // per-layer pointers, copied to shared memory when the kernel starts
@@ -69,306 +45,588 @@ struct MegaLayer {          // per-layer pointers, copied to shared memory when 
   uint8_t *kv_k, *kv_v;     // this slot's cache rows [max_seq, n_kv, hd] Q4_0
 };
 
-struct Piece {              // a run of consecutive rows of one matrix (two for gate-up): one ring slot
-  uint32_t src_off;         // byte offset of the first row inside its matrix
-  uint32_t out0;            // index of the first row in the phase's output vector
-  uint16_t nrows, row0;     // row0: index of the first row among the block's rows of the phase
-  uint16_t item0, n_items;  // items are numbered through the phase; item j belongs to warp j % 16
-  uint8_t kind, widx, pad[2];
-};
-struct PhInfo {
-  uint16_t p0, np, nrows, nitems;
-};
-
 struct MegaArgs {
-  const void* tables;       // MegaPhase[4] then MegaLayer[n_layers], 16-byte aligned; copied to shared memory at start
+  const void* tables;       // MegaShape[5] then MegaLayer[n_layers], 16-byte aligned; copied to shared memory at start
   unsigned tables_bytes;    // multiple of 16
   int n_layers;
-  int n_slots;              // ring slots
-  unsigned slot_bytes;      // bytes per ring slot (multiple of 128)
+  int stages;               // ring slots per warp
+  unsigned slot_bytes;      // bytes per ring slot
   unsigned x_bytes;         // staging area for x (also the attention scratch)
   unsigned n_q, n_kv, hd, n_splits;
-  unsigned split_from;      // contexts longer than this are split across blocks
   float eps, attn_scale;
   const float* rope;        // [max_seq, hd]
   const int* pos;           // [1]
-  const float* x_in;        // the token's embedding (residual stream on entry)
-  float* resid_out;         // residual stream after the last layer's attention half
-  float* y_out;             // last layer's down-proj output (the head applies the final residual update and norm)
-  // tagged activation vectors, two of each (layer parity)
-  u64 *ll_yd0, *ll_yd1, *ll_yo0, *ll_yo1, *ll_qkv0, *ll_qkv1, *ll_ox0, *ll_ox1, *ll_ff0, *ll_ff1, *ll_rec0, *ll_rec1;
-  unsigned* epoch;          // tag base of this token; advanced by n_layers + 1 when the kernel ends
+  float *x_a, *x_b;         // residual stream: layers read x_a / write x_b at the FFN, the reverse at the next qkv
+  float *yb, *q, *k, *v;
+  unsigned char *ox, *ffx;  // attention output and GeGLU output, written by their producers in the staged fixed-point layout
+  float* att_tmp;           // [n_q * n_splits * (hd + 2)]
+  float4* nsum;             // [grid] per-block sums of the last o-proj / down phase: (sum y^2, sum x*y*wp, sum (y*wp)^2, sum x^2)
+  unsigned* att_cnt;        // [n_q] arrival counters of the attention blocks, per head
+  unsigned* bar;            // [0] running barrier counter, [1] its value when the previous token ended
   unsigned* err;
-  unsigned poll_limit;      // polls of one wait before it gives up
-  unsigned test_stall;      // test hook: added to the tag the gate-up stage waits for (a tag nobody writes)
-  long long* prof_all;      // optional [grid][n_layers][5][2]: thread 0 of every block, (phase entered, rows stored)
-  long long* prof;          // optional [2][n_layers][5][8] SM clocks of the first and last block (thread 0): see the PF_* rows;
-                            // matvec phases: entered, inputs arrived, x staged, tasks done, block joined, row stored; attention: entered, q arrived, q/k/v built, positions done, folded, -, stored, left
+  unsigned poll_limit;      // polls of the barrier counter before a wait gives up
+  unsigned test_stall;      // test hook: the barrier before phase 1 waits for this many arrivals more than ever come
+  long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released
+                            // (attention rows: 4..7 = q/k/v ready, positions done, folded, arrived)
 };
 
-// ---- tagged words ---------------------------------------------------------------------------------
-__device__ __forceinline__ void ll_store(u64* p, float v, unsigned tag) {
-  const u64 w = ((u64)tag << 32) | (u64)__float_as_uint(v);
-  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+__device__ __forceinline__ uint32_t sm32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mb_init(uint32_t bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-__device__ __forceinline__ void ll_load2(const u64* p, u64& a, u64& b) {
-  asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+__device__ __forceinline__ void mb_expect(uint32_t bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ u64 ll_load1(const u64* p) {
-  u64 a;
-  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
-  return a;
+__device__ __forceinline__ bool mb_wait(uint32_t bar, unsigned parity) {
+  for (unsigned i = 0; i < (1u << 22); i++) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
 }
-__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+__device__ __forceinline__ void bulk_in(uint32_t dst, const void* src, unsigned bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
   unsigned v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ long long gtime() {  // nanoseconds, the same clock on every SM
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ unsigned ll_tag(u64 w) { return (unsigned)(w >> 32); }
-__device__ __forceinline__ float ll_val(u64 w) { return __uint_as_float((unsigned)w); }
+__device__ __forceinline__ float4 ldcg4(const float* p, unsigned c) { return __ldcg(reinterpret_cast<const float4*>(p) + c); }
 
-struct Poll {
-  const unsigned* err;
-  unsigned limit;
-  bool gave_up;  // this thread stopped waiting (its own wait ran out, or it saw the status word raised)
-};
-// After a failed tag check: may the wait go on?
-__device__ __noinline__ bool poll_again(Poll& pl, unsigned& it) {
-  if (pl.gave_up) return false;
-  if (++it >= pl.limit) {
-    atomicOr(const_cast<unsigned*>(pl.err), 2u);
-    pl.gave_up = true;
-    return false;
-  }
-  if ((it & 127u) == 0u && ld_relaxed_u32(pl.err) != 0u) {
-    pl.gave_up = true;
-    return false;
-  }
-  return true;
-}
-// N chunks of 4 consecutive values (32 bytes, 16-byte aligned).  Every load is issued before any is checked,
-// and every chunk that is still stale is re-read in the SAME round: a thread that came early pays one round
-// trip per round, not one per chunk.
-template <int N>
-__device__ __forceinline__ void ll_wait_chunks(const u64* base, const unsigned (&c)[N], const bool (&live)[N], unsigned tag,
-                                               float4 (&v)[N], Poll& pl) {
-  u64 w[N][4];
+// Grid-wide barrier on a monotonically increasing counter, in two halves so that loads which do not
+// depend on other blocks can be issued in between.
+// wsum != nullptr: the eight warps left their partial norm sums there; thread 0 folds them (fixed order) into nsum[block].
+__device__ __forceinline__ void grid_arrive(unsigned* counter, const float4* wsum, float4* nsum) {
+  __syncthreads();  // every store of this block is issued
+  if (threadIdx.x == 0) {
+    if (wsum) {
+      float4 t = wsum[0];
 #pragma unroll
-  for (int k = 0; k < N; k++)
-    if (live[k]) {
-      ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
-      ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
-    }
-  unsigned it = 0;
-  for (;;) {
-    bool stale[N], any = false;
-#pragma unroll
-    for (int k = 0; k < N; k++) {
-      stale[k] = live[k] && !(ll_tag(w[k][0]) == tag && ll_tag(w[k][1]) == tag && ll_tag(w[k][2]) == tag && ll_tag(w[k][3]) == tag);
-      any = any || stale[k];
-    }
-    if (!any || !poll_again(pl, it)) break;
-#pragma unroll
-    for (int k = 0; k < N; k++)
-      if (stale[k]) {
-        ll_load2(base + (size_t)c[k] * 4, w[k][0], w[k][1]);
-        ll_load2(base + (size_t)c[k] * 4 + 2, w[k][2], w[k][3]);
+      for (int w = 1; w < 8; w++) {
+        const float4 u = wsum[w];
+        t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
       }
+      nsum[blockIdx.x] = t;
+    }
+    // release: everything this block wrote (ordered before by the barrier above) is visible to whoever
+    // acquires the counter; nothing comes back, so the thread does not wait for a round trip
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
   }
-#pragma unroll
-  for (int k = 0; k < N; k++)
-    if (live[k]) v[k] = make_float4(ll_val(w[k][0]), ll_val(w[k][1]), ll_val(w[k][2]), ll_val(w[k][3]));
+}
+// Returns false when the wait gave up.
+// Lane 0 of four warps polls: their loads drift apart in time, so the arrival of the last block is
+// seen sooner than one poller's round trip allows.  sflag: 0 = waiting, 1 = released, 2 = gave up.
+// Two flag words alternate between consecutive barriers, so a word is cleared a whole phase after its last reader.
+__device__ __forceinline__ bool grid_wait(unsigned* counter, unsigned target, unsigned* err, int* flags, int parity, unsigned limit) {
+  int* sflag = flags + parity;
+  if (threadIdx.x == 0) flags[parity ^ 1] = 0;
+  if ((threadIdx.x & 31) == 0 && threadIdx.x < 128) {
+    volatile int* vf = sflag;
+    int state = 0;
+    for (unsigned i = 0; i < limit; i++) {  // a second or two of polling at most
+      if ((int)(ld_acquire_u32(counter) - target) >= 0) {
+        state = 1;
+        break;
+      }
+      if (*vf == 1) {  // another poller saw it; take the acquire ourselves before reading what other blocks wrote
+        if ((int)(ld_acquire_u32(counter) - target) >= 0) {
+          state = 1;
+          break;
+        }
+      }
+    }
+    if (state == 1) {
+      *vf = 1;
+    } else {
+      atomicOr(err, 2u);
+      *vf = 2;
+    }
+  }
+  __syncthreads();
+  return *sflag == 1;
 }
 
-// ---- staging of x ---------------------------------------------------------------------------------
-// Sum four values over the block: every thread gets the same totals (fixed order).  red: 16 float4.
-__device__ __forceinline__ float4 block_sum4(float4 v, float4* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// ---- x as 24-bit block fixed point, weights x x as byte dot products ----------------------------
+// Each 32-element sub-block of the staged vector shares a scale s; element i is the integer
+// X_i = round(x_i / s), |X_i| <= 8e6, kept as three byte planes (X = l2*65536 + l1*256 + l0, l2
+// signed).  Four neighbouring nibbles of a weight word, masked in place, are the other operand of a
+// dp4a, so 4 weights cost 3 integer dot-product instructions instead of ~9 f32 instructions, and the
+// shared-memory traffic for x drops from 4 bytes to 3/4 byte per weight.  Integer accumulation is
+// exact; the only approximation is x to 24 bits of its sub-block's largest element (f32 has 24 bits
+// per element), far inside the parity tolerance.
+// Shared-memory layout: plane k (k = 0..2) at k * units * 80 bytes, unit u at u * 80 inside it (64
+// used: words 0..7 = elements 0..31 of the low-nibble sub-block, 8..15 = the high-nibble one; the pad
+// keeps the 8 lanes of a row on different banks), then units * 16 bytes of (sum_lo, sum_hi, s_lo, s_hi).
+constexpr int MG_RL = 4, MG_LPR = 8;  // 8 lanes per row, 4 rows side by side
+constexpr unsigned MG_XU = 80;  // bytes per unit and plane
+__device__ __forceinline__ void fx_put_chunk(unsigned char* xs, unsigned units, unsigned c, float4 v) {
+  const unsigned e = c << 2;
+  const unsigned u = e >> 6, hi = (e >> 5) & 1u, l = e & 31u;
+  float s = (v.x + v.y) + (v.z + v.w);
+  float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+  for (int o = 1; o <= 4; o <<= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+  }
+  const float inv = am > 0.0f ? __fdividef(8.0e6f, am) : 0.0f;
+  const float sc = am > 0.0f ? am * (1.0f / 8.0e6f) : 1.0f;
+  const int X0 = __float2int_rn(v.x * inv), X1 = __float2int_rn(v.y * inv), X2 = __float2int_rn(v.z * inv),
+            X3 = __float2int_rn(v.w * inv);
+  const unsigned wi = hi * 8u + (l >> 2);
+  unsigned char* base = xs + (size_t)u * MG_XU + wi * 4u;
+  const size_t plane = (size_t)units * MG_XU;
+  *reinterpret_cast<uint32_t*>(base) = __byte_perm(__byte_perm(X0, X1, 0x0040), __byte_perm(X2, X3, 0x0040), 0x5410);
+  *reinterpret_cast<uint32_t*>(base + plane) = __byte_perm(__byte_perm(X0, X1, 0x0051), __byte_perm(X2, X3, 0x0051), 0x5410);
+  *reinterpret_cast<uint32_t*>(base + 2 * plane) = __byte_perm(__byte_perm(X0, X1, 0x0062), __byte_perm(X2, X3, 0x0062), 0x5410);
+  if ((threadIdx.x & 7u) == 0) {
+    float* mt = reinterpret_cast<float*>(xs + 3 * plane + (size_t)u * 16u);
+    mt[hi] = s;
+    mt[2 + hi] = sc;
+  }
+}
+// The same layout written to GLOBAL memory by a producer: the warp holds the 32 consecutive elements
+// e0 .. e0+31 of one sub-block, one per lane (e0 a multiple of 32).
+__device__ __forceinline__ void fx_store_subblock(unsigned char* dst, unsigned units, unsigned e0, float val, int lane) {
+  float s = val, am = fabsf(val);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    v.x += __shfl_xor_sync(0xffffffffu, v.x, o);
-    v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
-    v.z += __shfl_xor_sync(0xffffffffu, v.z, o);
-    v.w += __shfl_xor_sync(0xffffffffu, v.w, o);
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
   }
-  __syncthreads();  // the previous use of red is over
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float4 t = red[0];
-#pragma unroll 1
-  for (int w = 1; w < MG_NW; w++) {
-    const float4 u = red[w];
-    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+  const float inv = am > 0.0f ? __fdividef(8.0e6f, am) : 0.0f;
+  const float sc = am > 0.0f ? am * (1.0f / 8.0e6f) : 1.0f;
+  const int X = __float2int_rn(val * inv);
+  const unsigned u = e0 >> 6, hi = (e0 >> 5) & 1u;
+  const size_t plane = (size_t)units * MG_XU;
+  unsigned char* base = dst + (size_t)u * MG_XU + hi * 32u + (unsigned)lane;
+  base[0] = (unsigned char)(X & 0xFF);
+  base[plane] = (unsigned char)((X >> 8) & 0xFF);
+  base[2 * plane] = (unsigned char)((X >> 16) & 0xFF);
+  if (lane == 0) {
+    float* mt = reinterpret_cast<float*>(dst + 3 * plane + (size_t)u * 16u);
+    mt[hi] = s;
+    mt[2 + hi] = sc;
   }
-  return t;
 }
-
-// Per-thread wait state, carried through the phase functions in one word (they are separate,
-// non-inlined functions so that each gets the whole register budget; everything block-wide lives in
-// shared memory): bits 0-7 ring slot of the next piece, bit 8 its mbarrier parity, bit 9 this warp
-// stopped waiting for weight copies, bit 10 this thread stopped waiting for other blocks.
-constexpr unsigned ST_DEAD = 1u << 9, ST_GAVE_UP = 1u << 10;
-
-// The hidden vector of a phase that starts with a norm.  Thread t owns chunks t and t + 512 (4 elements
-// each) of the residual stream; it keeps them in shared memory (xres) between phases.
-//   add == false (first layer):  x' = rms(x) * w
-//   add == true:  r = x + rms(y) * wp (K:539; both RMS factors come from ONE block-wide sum:
-//                 sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2);  x' = rms(r) * w;  xres = r.
-template <int PC>
-__device__ MG_FN unsigned mg_stage_hidden(unsigned char* xs, float4* red, float* xres, bool add, unsigned cols,
-                                                 const u64* ysrc, unsigned tag, const float* w, const float* wp, float eps,
-                                                 float* resid_out, const unsigned* err, unsigned limit, unsigned st, long long* pf) {
-  Poll pl{err, limit, (st & ST_GAVE_UP) != 0u};
-  const unsigned units = cols >> 6, nchunk = cols >> 2;
-  unsigned c[PC];
-  bool live[PC];
-  float4 wv[PC], wpv[PC], yv[PC], xr[PC];
+// Bring a vector a producer left in that layout into shared memory (units * 256 bytes; the pad words travel too).
+__device__ __forceinline__ void fx_copy_in(unsigned char* xs, const unsigned char* src, unsigned units) {
+  const unsigned n16 = units * 16u;  // 3 planes of 80 bytes + 16 bytes of sums and scales per unit
+  for (unsigned base = 0; base < n16; base += 6u * blockDim.x) {
+    uint4 v[6];
 #pragma unroll
-  for (int k = 0; k < PC; k++) {
-    c[k] = threadIdx.x + k * MG_THREADS;
-    live[k] = c[k] < nchunk;
-    if (live[k]) {  // constants of the model: in flight while the inputs are awaited
-      wv[k] = reinterpret_cast<const float4*>(w)[c[k]];
-      if (add) wpv[k] = reinterpret_cast<const float4*>(wp)[c[k]];
-      xr[k] = reinterpret_cast<const float4*>(xres)[c[k]];
+    for (int k = 0; k < 6; k++) {
+      const unsigned i = base + threadIdx.x + k * blockDim.x;
+      if (i < n16) v[k] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
+    }
+#pragma unroll
+    for (int k = 0; k < 6; k++) {
+      const unsigned i = base + threadIdx.x + k * blockDim.x;
+      if (i < n16) reinterpret_cast<uint4*>(xs)[i] = v[k];
     }
   }
-  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (add) {
-    ll_wait_chunks<PC>(ysrc, c, live, tag, yv, pl);
+}
+__device__ __forceinline__ unsigned dp4a_uu(unsigned a, unsigned b, unsigned c) {
+  unsigned d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) {  // a: unsigned bytes, b: signed bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds_f4o(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFF));
+  return v;
+}
+// One weight word (8 nibbles: elements j..j+3 of the low and of the high sub-block) against the
+// matching x words of the three planes.
+__device__ __forceinline__ void fx_word(uint32_t w, unsigned xl0, unsigned xl1, unsigned xl2, unsigned xh0, unsigned xh1,
+                                        unsigned xh2, unsigned (&alo)[2], int& alo2, unsigned (&ahi)[2], int& ahi2) {
+  const unsigned lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+  alo[0] = dp4a_uu(lo, xl0, alo[0]);
+  alo[1] = dp4a_uu(lo, xl1, alo[1]);
+  alo2 = dp4a_us(lo, xl2, alo2);
+  ahi[0] = dp4a_uu(hi, xh0, ahi[0]);
+  ahi[1] = dp4a_uu(hi, xh1, ahi[1]);
+  ahi2 = dp4a_us(hi, xh2, ahi2);
+}
+// Multiply-accumulate one item against the fixed-point x: MATS row slots per lane.
+template <int MATS>
+__device__ __forceinline__ void mg_item_compute_fx(uint32_t slot_addr, uint32_t xs_s, unsigned units, unsigned seg_blocks,
+                                                   unsigned cs, int cl, int rl, float (&yacc)[2]) {
+  const int g = cl & 3;
+  const unsigned seg_bytes = seg_blocks * KS_Q4K_BLOCK_BYTES, seg_units = seg_blocks * 4, upl = seg_units / MG_LPR;
+  const uint32_t plane = units * MG_XU;
+  uint32_t waddr = slot_addr + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
+  uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * MG_XU;
+  uint32_t maddr = xs_s + 3u * plane + (cs * seg_units + (unsigned)cl) * 16u;
+  for (unsigned it = 0; it < upl; it++) {
+    const float4 mt = lds_f4o<0>(maddr);
+    // 16 words per plane: [0..7] low sub-block, [8..15] high sub-block
+    const uint4 a0 = lds_u4o<0>(xaddr), a1 = lds_u4o<16>(xaddr), a2 = lds_u4o<32>(xaddr), a3 = lds_u4o<48>(xaddr);
+    const uint4 b0 = lds_u4o<0>(xaddr + plane), b1 = lds_u4o<16>(xaddr + plane), b2 = lds_u4o<32>(xaddr + plane),
+                b3 = lds_u4o<48>(xaddr + plane);
+    const uint4 c0 = lds_u4o<0>(xaddr + 2 * plane), c1 = lds_u4o<16>(xaddr + 2 * plane), c2 = lds_u4o<32>(xaddr + 2 * plane),
+                c3 = lds_u4o<48>(xaddr + 2 * plane);
 #pragma unroll
-    for (int k = 0; k < PC; k++)
-      if (live[k]) {
-        const float4 x = xr[k], y = yv[k], p = wpv[k];
-        const float t0 = y.x * p.x, t1 = y.y * p.y, t2 = y.z * p.z, t3 = y.w * p.w;
-        s.x = fmaf(y.x, y.x, s.x); s.x = fmaf(y.y, y.y, s.x); s.x = fmaf(y.z, y.z, s.x); s.x = fmaf(y.w, y.w, s.x);
-        s.y = fmaf(x.x, t0, s.y); s.y = fmaf(x.y, t1, s.y); s.y = fmaf(x.z, t2, s.y); s.y = fmaf(x.w, t3, s.y);
-        s.z = fmaf(t0, t0, s.z); s.z = fmaf(t1, t1, s.z); s.z = fmaf(t2, t2, s.z); s.z = fmaf(t3, t3, s.z);
-        s.w = fmaf(x.x, x.x, s.w); s.w = fmaf(x.y, x.y, s.w); s.w = fmaf(x.z, x.z, s.w); s.w = fmaf(x.w, x.w, s.w);
-      }
-  } else {
-#pragma unroll
-    for (int k = 0; k < PC; k++)
-      if (live[k]) {
-        const float4 x = xr[k];
-        s.w = fmaf(x.x, x.x, s.w); s.w = fmaf(x.y, x.y, s.w); s.w = fmaf(x.z, x.z, s.w); s.w = fmaf(x.w, x.w, s.w);
-      }
+    for (int r = 0; r < MATS; r++) {
+      const uint32_t wa = waddr + (uint32_t)(r * MG_RL) * seg_bytes;
+      const uint4 q0 = lds_u4o<16>(wa), q1 = lds_u4o<32>(wa);
+      const uint4 hdr = lds_u4o<0>(wa - (uint32_t)g * 32u);
+      unsigned alo[2] = {0u, 0u}, ahi[2] = {0u, 0u};
+      int alo2 = 0, ahi2 = 0;
+      fx_word(q0.x, a0.x, b0.x, c0.x, a2.x, b2.x, c2.x, alo, alo2, ahi, ahi2);
+      fx_word(q0.y, a0.y, b0.y, c0.y, a2.y, b2.y, c2.y, alo, alo2, ahi, ahi2);
+      fx_word(q0.z, a0.z, b0.z, c0.z, a2.z, b2.z, c2.z, alo, alo2, ahi, ahi2);
+      fx_word(q0.w, a0.w, b0.w, c0.w, a2.w, b2.w, c2.w, alo, alo2, ahi, ahi2);
+      fx_word(q1.x, a1.x, b1.x, c1.x, a3.x, b3.x, c3.x, alo, alo2, ahi, ahi2);
+      fx_word(q1.y, a1.y, b1.y, c1.y, a3.y, b3.y, c3.y, alo, alo2, ahi, ahi2);
+      fx_word(q1.z, a1.z, b1.z, c1.z, a3.z, b3.z, c3.z, alo, alo2, ahi, ahi2);
+      fx_word(q1.w, a1.w, b1.w, c1.w, a3.w, b3.w, c3.w, alo, alo2, ahi, ahi2);
+      const float flo = fmaf((float)alo2, 65536.0f, fmaf((float)alo[1], 256.0f, (float)alo[0])) * mt.z;
+      const float fhi = fmaf((float)ahi2, 65536.0f, fmaf((float)ahi[1], 256.0f, (float)ahi[0])) * mt.w;
+      yacc[r] = q4k_apply_scales(hdr, g, flo, fhi, mt.x, mt.y, yacc[r]);
+    }
+    waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
+    xaddr += MG_LPR * MG_XU;
+    maddr += MG_LPR * 16u;
   }
-  if (pf) pf[1] = clock64();
-  const float4 t = block_sum4(s, red);
+}
+
+
+// ---- staging of x (with the fused norm prologues), reads through L2 ---------------------------
+// Norm weights of the next matvec phase, fetched into registers before the barrier wait.
+template <int PC>
+struct NormPre {  // PC chunks of 4 elements per thread: cols <= PC * 4 * blockDim
+  float4 w[PC], wp[PC];
+};
+template <int PC>
+__device__ __forceinline__ void mg_prefetch_norm(NormPre<PC>& n, int mode, const float* w, const float* wp, unsigned cols) {
+  const unsigned nchunk = cols >> 2;
+  if (mode == KS_PRO_NONE) return;
+#pragma unroll
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      n.w[k] = reinterpret_cast<const float4*>(w)[c];
+      if (mode == KS_PRO_ADD_NORM) n.wp[k] = reinterpret_cast<const float4*>(wp)[c];
+    }
+  }
+}
+
+constexpr int MG_XMAX = 8;  // plain staging keeps up to 8 chunks per thread in flight (cols <= 8192), loops beyond
+
+// mode NONE: x' = x.  NORM: x' = rms(x)*w.  ADD_NORM: r = x + rms(y)*wp (block 0 stores r to out_x); x' = rms(r)*w.
+template <int PC>
+__device__ __forceinline__ void mg_stage_x(unsigned char* xs, float* red, int mode, unsigned cols, const float* x,
+                                           const float* y, float* out_x, float eps, const NormPre<PC>& n) {
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
+  if (mode == KS_PRO_NONE) {
+    for (unsigned base = 0; base < nchunk; base += MG_XMAX * blockDim.x) {
+      float4 v[MG_XMAX];
+#pragma unroll
+      for (int k = 0; k < MG_XMAX; k++) {
+        const unsigned c = base + threadIdx.x + k * blockDim.x;
+        if (c < nchunk) v[k] = ldcg4(x, c);
+      }
+#pragma unroll
+      for (int k = 0; k < MG_XMAX; k++) {
+        const unsigned c = base + threadIdx.x + k * blockDim.x;
+        if (c < nchunk) fx_put_chunk(xs, units, c, v[k]);
+      }
+    }
+    return;
+  }
   const float invn = 1.0f / (float)cols;
-  float inv = 0.0f, inv2;
-  if (add) {
-    inv = __frsqrt_rn(t.x * invn + eps);
-    const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
-    inv2 = __frsqrt_rn(fmaxf(rr, 0.0f) * invn + eps);
+  float4 v[PC], yv[PC];
+  float ss = 0.0f;
+  if (mode == KS_PRO_ADD_NORM) {
+#pragma unroll
+    for (int k = 0; k < PC; k++) {
+      const unsigned c = threadIdx.x + k * blockDim.x;
+      if (c < nchunk) {
+        yv[k] = ldcg4(y, c);
+        v[k] = ldcg4(x, c);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < PC; k++) {
+      const unsigned c = threadIdx.x + k * blockDim.x;
+      if (c < nchunk) {
+        ss = fmaf(yv[k].x, yv[k].x, ss); ss = fmaf(yv[k].y, yv[k].y, ss);
+        ss = fmaf(yv[k].z, yv[k].z, ss); ss = fmaf(yv[k].w, yv[k].w, ss);
+      }
+    }
+    ss = block_sum_f(ss, red);
+    const float inv = 1.0f / sqrtf(ss * invn + eps);
+    ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < PC; k++) {
+      const unsigned c = threadIdx.x + k * blockDim.x;
+      if (c < nchunk) {
+        const float4 p4 = n.wp[k];
+        float4 r = v[k];
+        r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
+        r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
+        r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
+        r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
+        if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
+        v[k] = r;
+      }
+    }
   } else {
-    inv2 = 1.0f / sqrtf(t.w * invn + eps);
+#pragma unroll
+    for (int k = 0; k < PC; k++) {
+      const unsigned c = threadIdx.x + k * blockDim.x;
+      if (c < nchunk) v[k] = ldcg4(x, c);
+    }
   }
 #pragma unroll
-  for (int k = 0; k < PC; k++)
-    if (live[k]) {  // nchunk is a multiple of 64: whole warps take this branch together
-      float4 r = xr[k];
-      if (add) {
-        const float4 y = yv[k], p = wpv[k];
-        r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(y.x, inv), p.x));
-        r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(y.y, inv), p.y));
-        r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(y.z, inv), p.z));
-        r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(y.w, inv), p.w));
-        reinterpret_cast<float4*>(xres)[c[k]] = r;
-        if (resid_out) reinterpret_cast<float4*>(resid_out)[c[k]] = r;
-      }
-      const float4 w4 = wv[k];
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
+      ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+    }
+  }
+  ss = block_sum_f(ss, red);
+  const float inv2 = 1.0f / sqrtf(ss * invn + eps);
+#pragma unroll
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      const float4 w4 = n.w[k];
+      float4 r;
+      r.x = __fmul_rn(__fmul_rn(v[k].x, inv2), w4.x);
+      r.y = __fmul_rn(__fmul_rn(v[k].y, inv2), w4.y);
+      r.z = __fmul_rn(__fmul_rn(v[k].z, inv2), w4.z);
+      r.w = __fmul_rn(__fmul_rn(v[k].w, inv2), w4.w);
+      fx_put_chunk(xs, units, c, r);
+    }
+  }
+}
+
+// ADD_NORM without any block-wide reduction: the blocks that produced y left the four sums that both
+// norms need (K:539 expands to  sum r^2 = sum x^2 + 2 inv sum x y wp + inv^2 sum (y wp)^2,  r = x + inv y wp).
+template <int PC>
+__device__ __forceinline__ void mg_stage_addnorm(unsigned char* xs, unsigned cols, const float* x, const float* y, float* out_x,
+                                                 float eps, const NormPre<PC>& n, const float4* nsum, unsigned nblocks) {
+  const unsigned units = cols >> 6, nchunk = cols >> 2;
+  const int lane = threadIdx.x & 31;
+  float4 v[PC], yv[PC], ps[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const unsigned i = (unsigned)lane + 32u * j;
+    ps[j] = i < nblocks ? __ldcg(nsum + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      yv[k] = ldcg4(y, c);
+      v[k] = ldcg4(x, c);
+    }
+  }
+  float4 t = ps[0];
+#pragma unroll
+  for (int j = 1; j < 8; j++) {
+    t.x += ps[j].x; t.y += ps[j].y; t.z += ps[j].z; t.w += ps[j].w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    t.x += __shfl_xor_sync(0xffffffffu, t.x, o);
+    t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
+    t.z += __shfl_xor_sync(0xffffffffu, t.z, o);
+    t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
+  }
+  const float invn = 1.0f / (float)cols;
+  const float inv = __frsqrt_rn(t.x * invn + eps);
+  const float rr = fmaf(inv * inv, t.z, fmaf(2.0f * inv, t.y, t.w));
+  const float inv2 = __frsqrt_rn(fmaxf(rr, 0.0f) * invn + eps);
+#pragma unroll
+  for (int k = 0; k < PC; k++) {
+    const unsigned c = threadIdx.x + k * blockDim.x;
+    if (c < nchunk) {
+      const float4 p4 = n.wp[k], w4 = n.w[k];
+      float4 r = v[k];
+      r.x = __fadd_rn(r.x, __fmul_rn(__fmul_rn(yv[k].x, inv), p4.x));
+      r.y = __fadd_rn(r.y, __fmul_rn(__fmul_rn(yv[k].y, inv), p4.y));
+      r.z = __fadd_rn(r.z, __fmul_rn(__fmul_rn(yv[k].z, inv), p4.z));
+      r.w = __fadd_rn(r.w, __fmul_rn(__fmul_rn(yv[k].w, inv), p4.w));
+      if (blockIdx.x == 0) reinterpret_cast<float4*>(out_x)[c] = r;
       float4 q;
       q.x = __fmul_rn(__fmul_rn(r.x, inv2), w4.x);
       q.y = __fmul_rn(__fmul_rn(r.y, inv2), w4.y);
       q.z = __fmul_rn(__fmul_rn(r.z, inv2), w4.z);
       q.w = __fmul_rn(__fmul_rn(r.w, inv2), w4.w);
-      fx_put_chunk(xs, units, c[k], q);
+      fx_put_chunk(xs, units, c, q);
     }
-  return pl.gave_up ? (st | ST_GAVE_UP) : st;
-}
-
-// A vector other blocks produced (attention output, GeGLU output), staged as it is.
-__device__ MG_FN unsigned mg_stage_plain(unsigned char* xs, unsigned cols, const u64* src, unsigned tag, const unsigned* err,
-                                                unsigned limit, unsigned st, long long* pf) {
-  Poll pl{err, limit, (st & ST_GAVE_UP) != 0u};
-  constexpr int XC = 6;
-  const unsigned units = cols >> 6, nchunk = cols >> 2;
-  for (unsigned base = 0; base < nchunk; base += XC * MG_THREADS) {
-    unsigned c[XC];
-    bool live[XC];
-    float4 v[XC];
-#pragma unroll
-    for (int k = 0; k < XC; k++) {
-      c[k] = base + threadIdx.x + k * MG_THREADS;
-      live[k] = c[k] < nchunk;
-    }
-    ll_wait_chunks<XC>(src, c, live, tag, v, pl);
-    if (pf) pf[1] = clock64();
-#pragma unroll
-    for (int k = 0; k < XC; k++)
-      if (live[k]) fx_put_chunk(xs, units, c[k], v[k]);
   }
-  return pl.gave_up ? (st | ST_GAVE_UP) : st;
 }
 
-// ---- pieces -----------------------------------------------------------------------------------------
-// Rows [lo, hi) of a phase's row space owned by this block: an even split in pairs of rows.
-__device__ __forceinline__ void block_rows(const MegaPhase& ph, unsigned& lo, unsigned& hi) {
-  const unsigned half = ph.seg_start[ph.n_seg] >> 1;
-  lo = (unsigned)(((unsigned long long)blockIdx.x * half) / gridDim.x) * 2u;
-  hi = (unsigned)(((unsigned long long)(blockIdx.x + 1) * half) / gridDim.x) * 2u;
+// ---- the per-warp item list of a whole token -----------------------------------------------------
+// Item = (phase, row group, column segment).
+
+// The items of a warp repeat layer after layer (same shapes, other pointers), so the walk over the
+// shapes is done once per kernel: each warp records its items of ONE layer, in phase order, and the
+// issue and consume positions are (layer, entry) pairs.
+constexpr int MG_MAX_ENT = 16;
+struct ItemEnt {
+  uint32_t src_off;  // byte offset of the first copy inside its weight matrix
+  uint32_t pslot;    // index of this item among the block's items of the phase (where its partial sums go)
+  uint16_t seg16;    // bytes of one row segment / 16
+  uint8_t kind, seg, cs, valid;
+  uint8_t widx;      // MegaLayer::W index of the first matrix
+  uint8_t flags;     // bit 0: two matrices (gate, up) in one item; bit 1: whole rows (one copy per matrix);
+                     // bit 2: this item is the second matrix (up) of a split gate-up group
+};
+struct ItemPos {
+  int layer, e;
+};
+__device__ __forceinline__ void pos_next(ItemPos& c, int n_ent) {
+  if (++c.e >= n_ent) {
+    c.e = 0;
+    c.layer++;
+  }
 }
-// Thread 0 lists this block's pieces of one layer, in the order they are consumed.  Returns false when a table overflows.
-__device__ __forceinline__ bool build_pieces(Piece* pieces, PhInfo* info, const MegaPhase* phases) {
-  unsigned np = 0;
-  for (int kind = 0; kind < PH_KINDS; kind++) {
-    const MegaPhase& ph = phases[kind];
-    unsigned lo, hi, rows = 0, items = 0;
-    block_rows(ph, lo, hi);
-    info[kind].p0 = (uint16_t)np;
-    for (unsigned s = 0; s < ph.n_seg; s++) {
-      const unsigned a = max(lo, ph.seg_start[s]), b = min(hi, ph.seg_start[s + 1]);
-      for (unsigned r = a; r < b; r += ph.piece_rows) {
-        if (np >= (unsigned)MG_MAXPIECE) return false;
-        const unsigned n = min(ph.piece_rows, b - r);
-        Piece p;
-        p.src_off = (r - ph.seg_start[s]) * ph.row_bytes;
-        p.out0 = r;
-        p.nrows = (uint16_t)n;
-        p.row0 = (uint16_t)rows;
-        p.item0 = (uint16_t)items;
-        p.n_items = 0;
-        p.kind = (uint8_t)kind;
-        p.widx = (uint8_t)(ph.widx + s);
-        p.pad[0] = p.pad[1] = 0;
-        pieces[np++] = p;
-        rows += n;
-        items += p.n_items;
+// Groups of a phase go to blocks round-robin (block c owns groups c, c + grid, ...); the block's items
+// -- its groups x the column segments -- go to its warps round-robin.  A row's column segments may
+// therefore be multiplied by different warps; the partial sums meet in shared memory (slot pslot).
+constexpr int MG_MAX_P = 64;  // items of one block in one phase
+__device__ __forceinline__ unsigned block_groups(const MegaShape& sh) {
+  const unsigned total = sh.type == MG_ATTN ? 0u : sh.grp_start[sh.n_seg];
+  if (sh.oct) {
+    const unsigned octs = (total + 7u) / 8u;
+    return octs > blockIdx.x ? (octs - blockIdx.x + gridDim.x - 1) / gridDim.x * 8u : 0u;
+  }
+  return total > blockIdx.x ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+}
+// global group index of this block's k-th group
+__device__ __forceinline__ unsigned block_group_id(const MegaShape& sh, unsigned k) {
+  return sh.oct ? (blockIdx.x + (k >> 3) * gridDim.x) * 8u + (k & 7u) : blockIdx.x + k * gridDim.x;
+}
+// lane 0 of each warp fills its table; returns the entry count (0 when the warp owns nothing, -1 on overflow)
+__device__ __forceinline__ int build_items(ItemEnt* ent, const MegaShape* shapes, int warp) {
+  int n = 0;
+  for (int kind = 0; kind < PH_PER_LAYER; kind++) {
+    const MegaShape& sh = shapes[kind];
+    const unsigned C = sh.n_cseg, n_slots = block_groups(sh) * C;
+    if (n_slots > (unsigned)MG_MAX_P) return -1;
+    const unsigned seg_bytes = sh.seg_blocks * KS_Q4K_BLOCK_BYTES;
+    const bool split = sh.type == MG_GATE_UP && sh.split;
+    const int mats = (sh.type == MG_GATE_UP && !split) ? 2 : 1;
+    const int w0 = kind == PH_QKV ? 0 : kind == PH_OPROJ ? 3 : kind == PH_GATEUP ? 4 : 6;
+    const unsigned n_items = split ? n_slots * 2u : n_slots;
+    for (unsigned jj = (unsigned)warp; jj < n_items; jj += 8u) {
+      if (n >= MG_MAX_ENT) return -1;
+      const unsigned j = split ? jj >> 1 : jj, second = split ? jj & 1u : 0u;
+      const unsigned k = j / C, cs = j - k * C;
+      const unsigned g = block_group_id(sh, k);
+      if (g >= sh.grp_start[sh.n_seg]) continue;
+      int seg = 0;
+      if (sh.n_seg > 1 && g >= sh.grp_start[1]) seg = 1;
+      if (sh.n_seg > 2 && g >= sh.grp_start[2]) seg = 2;
+      const unsigned row0 = (g - sh.grp_start[seg]) * MG_RL;
+      ItemEnt e;
+      e.src_off = row0 * sh.row_bytes + cs * seg_bytes;
+      e.pslot = j;
+      e.seg16 = (uint16_t)(seg_bytes / 16u);
+      e.kind = (uint8_t)kind;
+      e.seg = (uint8_t)seg;
+      e.cs = (uint8_t)cs;
+      e.valid = (uint8_t)min((unsigned)MG_RL, sh.rows[seg] - row0);
+      e.widx = (uint8_t)(w0 + (mats == 2 ? 0 : split ? second : seg));
+      e.flags = (uint8_t)((mats == 2 ? 1 : 0) | (C == 1 ? 2 : 0) | (second ? 4 : 0));
+      ent[n++] = e;
+    }
+  }
+  return n;
+}
+
+// Start the copies of one item into a ring slot (all lanes call).
+__device__ __forceinline__ void mg_issue_ent(const ItemEnt& e, const MegaLayer& L, unsigned row_bytes, uint32_t slot_addr,
+                                             uint32_t bar, int lane) {
+  const unsigned seg_bytes = (unsigned)e.seg16 * 16u, valid = e.valid;
+  const int mats = (e.flags & 1) ? 2 : 1;
+  if (lane == 0) mb_expect(bar, valid * mats * seg_bytes);
+  if (e.flags & 2) {
+    if (lane < mats)
+      bulk_in(slot_addr + (uint32_t)lane * MG_RL * seg_bytes, L.W[e.widx + lane] + e.src_off, valid * seg_bytes, bar);
+  } else if (lane < MG_RL * mats) {
+    const int m = lane / MG_RL, rr = lane % MG_RL;
+    if ((unsigned)rr < valid)
+      bulk_in(slot_addr + (uint32_t)lane * seg_bytes, L.W[e.widx + m] + e.src_off + (size_t)rr * row_bytes, seg_bytes, bar);
+  }
+}
+
+// Multiply-accumulate one item: MATS row slots per lane, units of this lane in the segment.
+template <int MATS>
+__device__ __forceinline__ void mg_item_compute(uint32_t slot_addr, uint32_t xs_s, unsigned units, unsigned seg_blocks,
+                                                unsigned cs, int cl, int rl, float (&yacc)[2]) {
+  const int g = cl & 3;
+  const unsigned seg_bytes = seg_blocks * KS_Q4K_BLOCK_BYTES, seg_units = seg_blocks * 4, upl = seg_units / MG_LPR;
+  uint32_t waddr = slot_addr + (uint32_t)rl * seg_bytes + (uint32_t)(cl >> 2) * KS_Q4K_BLOCK_BYTES + (uint32_t)g * 32u;
+  uint32_t xaddr = xs_s + (cs * seg_units + (unsigned)cl) * (Q4K_XS * 4u);
+  uint32_t saddr = xs_s + units * (Q4K_XS * 4u) + (cs * seg_units + (unsigned)cl) * 8u;
+  for (unsigned it = 0; it < upl; it++) {
+    const float2 sx = lds_f2a(saddr);
+    u64 acc[MATS][2];
+#pragma unroll
+    for (int r = 0; r < MATS; r++) acc[r][0] = acc[r][1] = 0ull;
+    {
+      u64 xf[16];
+      lds_p2o<0>(xaddr, xf[0], xf[1]);     lds_p2o<16>(xaddr, xf[2], xf[3]);
+      lds_p2o<32>(xaddr, xf[4], xf[5]);    lds_p2o<48>(xaddr, xf[6], xf[7]);
+      lds_p2o<64>(xaddr, xf[8], xf[9]);    lds_p2o<80>(xaddr, xf[10], xf[11]);
+      lds_p2o<96>(xaddr, xf[12], xf[13]);  lds_p2o<112>(xaddr, xf[14], xf[15]);
+#pragma unroll
+      for (int r = 0; r < MATS; r++) {
+        const uint4 q = lds_u4o<16>(waddr + (uint32_t)(r * MG_RL) * seg_bytes);
+        q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
+        q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
+        q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
+        q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
       }
     }
-    if (rows > (unsigned)MG_MAXROWS) return false;
-    info[kind].np = (uint16_t)(np - info[kind].p0);
-    info[kind].nrows = (uint16_t)rows;
-    info[kind].nitems = (uint16_t)items;
+    {
+      u64 xf[16];
+      lds_p2o<128>(xaddr, xf[0], xf[1]);    lds_p2o<144>(xaddr, xf[2], xf[3]);
+      lds_p2o<160>(xaddr, xf[4], xf[5]);    lds_p2o<176>(xaddr, xf[6], xf[7]);
+      lds_p2o<192>(xaddr, xf[8], xf[9]);    lds_p2o<208>(xaddr, xf[10], xf[11]);
+      lds_p2o<224>(xaddr, xf[12], xf[13]);  lds_p2o<240>(xaddr, xf[14], xf[15]);
+#pragma unroll
+      for (int r = 0; r < MATS; r++) {
+        const uint4 q = lds_u4o<32>(waddr + (uint32_t)(r * MG_RL) * seg_bytes);
+        q4_word_p(q.x, xf[0], xf[1], xf[2], xf[3], acc[r][0], acc[r][1]);
+        q4_word_p(q.y, xf[4], xf[5], xf[6], xf[7], acc[r][0], acc[r][1]);
+        q4_word_p(q.z, xf[8], xf[9], xf[10], xf[11], acc[r][0], acc[r][1]);
+        q4_word_p(q.w, xf[12], xf[13], xf[14], xf[15], acc[r][0], acc[r][1]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MATS; r++) {
+      const uint4 hdr = lds_u4o<0>(waddr + (uint32_t)(r * MG_RL) * seg_bytes - (uint32_t)g * 32u);
+      const float2 a01 = unpack2(padd2(acc[r][0], acc[r][1]));
+      yacc[r] = q4k_apply_scales(hdr, g, a01.x, a01.y, sx.x, sx.y, yacc[r]);
+    }
+    waddr += (MG_LPR / 4) * KS_Q4K_BLOCK_BYTES;
+    xaddr += MG_LPR * Q4K_XS * 4u;
+    saddr += MG_LPR * 8u;
   }
-  return true;
-}
-// Start the copies of one piece into a ring slot (one thread).
-__device__ __forceinline__ void issue_piece(const Piece& p, const MegaPhase& ph, const MegaLayer& L, uint32_t slot_addr, uint32_t bar) {
-  const unsigned bytes = (unsigned)p.nrows * ph.row_bytes;
-  mb_expect(bar, bytes * ph.mats);
-  bulk_in(slot_addr, L.W[p.widx] + p.src_off, bytes, bar);
-  if (ph.mats == 2) bulk_in(slot_addr + (((unsigned)p.nrows + 3u) & ~3u) * ph.row_bytes, L.W[p.widx + 1] + p.src_off, bytes, bar);
 }
 
 // ---- attention phase ------------------------------------------------------------------------------
@@ -431,181 +689,127 @@ __device__ __forceinline__ int mg_lane_dim(int lane, int j) {
   return j < BPL ? base + j : base + 16 + (j - BPL);
 }
 
-constexpr int MG_AB = 8;  // positions of one warp in flight together
+constexpr int MG_MAX_SPLITS = 16;  // context splits per head (the final merge keeps one record per split in registers)
 
 // Shared memory the attention phase needs (it reuses the x staging area).
 __host__ __device__ inline unsigned mg_att_bytes(unsigned hd) {
-  const unsigned rowb = (hd / 32u) * KS_Q40_BLOCK_BYTES;
-  return (unsigned)MG_NW * (hd + 2u) * 4u + 2u * (rowb + 16u) + 8u * MG_MAX_SPLITS + 12u * hd + 4u * MG_NW +
-         (unsigned)MG_NW * MG_AB * 2u * rowb + 32u;
+  return 8u * (hd + 2u) * 4u + 2u * ((hd / 32u) * KS_Q40_BLOCK_BYTES + 16u) + 32u;
 }
 
-// Splits in use for a context of tlen positions: a warp walks at most four positions (one batch of
-// loads in flight) until every split is in use.  A split costs a hop through L2 (records out, merge in
-// the head's first block); contexts of up to split_from positions stay in one block.
-__host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits, unsigned split_from) {
-  if (tlen <= split_from) return 1u;
-  unsigned ns = (tlen + 4u * MG_NW - 1u) / (4u * MG_NW);
+// Splits in use for a context of tlen positions: one row per warp (8 per block) until every split is
+// in use, more rows per warp beyond that.
+__host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max_splits) {
+  unsigned ns = (tlen + 7u) / 8u;
   return ns < 1u ? 1u : ns > max_splits ? max_splits : ns;
 }
 
-
-// What the attention phase needs, block-wide (read from shared memory).
-struct AttnArgs {
-  unsigned n_q, n_kv, n_splits, split_from;
-  float eps, attn_scale;
-  const float* rope;
-  const int* pos;
-  const unsigned* err;
-  unsigned limit;
-};
-
-// Sum of v over the first nw warps of the block (every thread of those warps calls, every thread gets the
-// total); red: MG_NW floats of scratch.  Fixed order.
-__device__ __forceinline__ float mg_rows_sum(float v, float* red, int nw) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  v = mg_warp_sum(v);
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = 0.0f;
-  for (int w = 0; w < nw; w++) t += red[w];
-  return t;
-}
-
-// One block per (query head, context split).  The code is kept small on purpose (rolled loops, one
-// value per thread): it runs once per layer, so its instructions are fetched cold every time.
-//   0. each warp starts the loads of its first positions' packed K/V rows (cp.async into the scratch):
-//      they do not depend on this layer's q, so they travel while q is awaited;
-//   1. thread d awaits q[d] of the head (and k[d], v[d] in the block(s) of the split that holds the newest
-//      position), the block norms and ropes them (lower.rs:4231-4702): q stays in shared memory for the
-//      dot products, the new K / V rows are packed to Q4_0 (one warp per 32-value block) and the block of
-//      the KV group's first head stores them to the cache;
-//   2. warps take the positions of the split round-robin, four rows in flight, online softmax per warp;
-//   3. the warps' (m, l, O) meet in shared memory, thread d folds dimension d;
-//   4. one split: thread d stores the head's output; several: the block leaves a tagged (m, l, O[hd])
-//      record and the head's first block merges the records (lower.rs:5897-6088).
+// One block per (query head, context split): the work of a short context is tiny, so it is spread
+// as widely as the grid allows and every serial step stays short.
+//   1. every warp builds the roped, normed, scaled q of the head in registers (no exchange needed);
+//      in the blocks of the split that holds the newest position, warps 0.. pack the new K row and
+//      warps 4.. the new V row to Q4_0 in shared memory (lower.rs:4231-4702), block pairs (b, b+NB/2)
+//      per warp because RoPE pairs those halves; the block of the KV group's first head stores them;
+//   2. warps take the positions of the split round-robin, online softmax per warp;
+//   3. the eight warps' (m, l, O) meet in shared memory, thread d folds dimension d;
+//   4. the block leaves a (m, l, O[hd]) record; the last block of a head to arrive merges the
+//      head's records (lower.rs:5897-6088).
 template <int DPL>
-__device__ MG_FN unsigned mg_attention(const AttnArgs* ap, const MegaLayer* Lp, const u64* qkv, u64* ox, u64* rec, unsigned tag,
-                                       unsigned char* sm, unsigned st, long long* pf) {
+__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, unsigned char* sm, int* sflag, long long* pf) {
   constexpr int HD = DPL * 32, HALF = HD / 2, NB = HD / 32;
   constexpr unsigned ROWB = NB * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned NSMAX = ap->n_splits, n_q = ap->n_q, n_kv = ap->n_kv;
-  if (blockIdx.x >= n_q * NSMAX) return st;
+  const unsigned NSMAX = a.n_splits;
+  if (blockIdx.x >= a.n_q * NSMAX) return;
   const unsigned head = blockIdx.x / NSMAX, split = blockIdx.x % NSMAX;
-  const unsigned G = n_q / n_kv, kvh = head / G;
-  const unsigned pos = (unsigned)ap->pos[0], tlen = pos + 1;
-  const unsigned NS = mg_active_splits(tlen, NSMAX, ap->split_from);
-  if (split >= NS) return st;
-  Poll pl{ap->err, ap->limit, (st & ST_GAVE_UP) != 0u};
+  const unsigned G = a.n_q / a.n_kv, kvh = head / G;
+  const unsigned pos = (unsigned)a.pos[0], tlen = pos + 1;
+  const unsigned NS = mg_active_splits(tlen, NSMAX);
+  if (split >= NS) return;
   const unsigned chunk = (tlen + NS - 1) / NS;
   const unsigned p0 = split * chunk, p1 = min(p0 + chunk, tlen);
   const bool owner = pos >= p0 && pos < p1;  // the split that holds the newest position
-  // scratch: part [NW][HD + 2] | skrow | svrow | ml [2 * MAX_SPLITS] | vec [3][HD] (q, k, v) | red [NW] | kvbuf
-  float* part = reinterpret_cast<float*>(sm);
-  uint8_t* skrow = reinterpret_cast<uint8_t*>(part + MG_NW * (HD + 2));
+  float* part = reinterpret_cast<float*>(sm);     // [8][HD + 2]
+  uint8_t* skrow = reinterpret_cast<uint8_t*>(part + 8 * (HD + 2));
   uint8_t* svrow = skrow + ROWB + 16u;
-  float* ml = reinterpret_cast<float*>(svrow + ROWB + 16u);
-  float* vec = ml + 2 * MG_MAX_SPLITS;
-  float* red = vec + 3 * HD;
-  uint8_t* kvbuf = reinterpret_cast<uint8_t*>(red + MG_NW) + (size_t)warp * (MG_AB * 2u * ROWB);  // [MG_AB][K, V][ROWB]
-  const float* cs = ap->rope + (size_t)pos * HD;
-  const unsigned qn = n_q * HD, kvn = n_kv * HD;
-  const size_t rowstride = (size_t)n_kv * ROWB;
-  uint8_t* Kc = Lp->kv_k + (size_t)kvh * ROWB;
-  uint8_t* Vc = Lp->kv_v + (size_t)kvh * ROWB;
+  const float* cs = a.rope + (size_t)pos * HD;
 
-  // 0. the first batch of cached rows (the newest position's row does not exist yet: it comes from skrow / svrow)
-  auto prefetch_rows = [&](unsigned tb) {
-#pragma unroll 1
-    for (int i = 0; i < MG_AB; i++) {
-      const unsigned t = tb + (unsigned)(MG_NW * i);
-      if (t < p1 && t != pos && lane < (int)(ROWB / 8u)) {
-        cp_async8(sm32(kvbuf + (size_t)(2 * i) * ROWB) + (uint32_t)lane * 8u, Kc + (size_t)t * rowstride + (size_t)lane * 8u);
-        cp_async8(sm32(kvbuf + (size_t)(2 * i + 1) * ROWB) + (uint32_t)lane * 8u, Vc + (size_t)t * rowstride + (size_t)lane * 8u);
-      }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  prefetch_rows(p0 + (unsigned)warp);
-
-  // 1. q (and the new k, v): one value per thread
-  const int d = threadIdx.x;
-  const bool has = d < HD;  // whole warps: HD is a multiple of 32
+  float qr[DPL];
   {
-    float qv = 0.f, kx = 0.f, vx = 0.f, qw = 0.f, kw = 0.f, c = 0.f, sn = 0.f;
-    if (has) {
-      qw = Lp->norm[1][d];
-      c = cs[d & (HALF - 1)];
-      sn = cs[HALF + (d & (HALF - 1))];
-      if (owner) kw = Lp->norm[2][d];
-      const u64* qp = qkv + (size_t)head * HD + d;
-      const u64* kp = qkv + qn + (size_t)kvh * HD + d;
-      const u64* vp = kp + kvn;
-      u64 wq = ll_load1(qp), wk = 0, wv = 0;
-      if (owner) {
-        wk = ll_load1(kp);
-        wv = ll_load1(vp);
+    const int pb = warp & 3;  // block pair of the K / V job
+    const bool kjob = owner && warp < 4 && pb < NB / 2, vjob = owner && warp >= 4 && pb < NB / 2;
+    float qv[DPL], qw[DPL], qc[DPL], qs[DPL], rv[DPL], r_w0 = 0.f, r_w1 = 0.f, r_c = 0.f, r_s = 0.f;
+    const float* qsrc = a.q + (size_t)head * HD;
+    const float* qnw = L.norm[1];
+#pragma unroll
+    for (int j = 0; j < DPL; j++) {
+      const int d = mg_lane_dim<DPL>(lane, j);
+      qv[j] = __ldcg(qsrc + d);
+      qw[j] = qnw[d];
+      qc[j] = cs[d & (HALF - 1)];
+      qs[j] = cs[HALF + (d & (HALF - 1))];
+    }
+    if (kjob || vjob) {
+      const float* src = (kjob ? a.k : a.v) + (size_t)kvh * HD;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) rv[j] = __ldcg(src + lane + 32 * j);
+      if (kjob) {
+        const float* w = L.norm[2];
+        r_w0 = w[32 * pb + lane];
+        r_w1 = w[HALF + 32 * pb + lane];
+        r_c = cs[32 * pb + lane];
+        r_s = cs[HALF + 32 * pb + lane];
       }
-      unsigned it = 0;
-      if (owner) {  // every stale word is re-read in the same round
-        while (!(ll_tag(wq) == tag && ll_tag(wk) == tag && ll_tag(wv) == tag) && poll_again(pl, it)) {
-          if (ll_tag(wq) != tag) wq = ll_load1(qp);
-          if (ll_tag(wk) != tag) wk = ll_load1(kp);
-          if (ll_tag(wv) != tag) wv = ll_load1(vp);
+    }
+    {
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) ss = fmaf(qv[j], qv[j], ss);
+      ss = mg_warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+      // lanes 0..15 hold dims of the first half, lanes 16..31 their RoPE partners (dim + HD/2)
+#pragma unroll
+      for (int j = 0; j < DPL; j++) {
+        const float u = __fmul_rn(__fmul_rn(qv[j], inv), qw[j]);
+        const float pu = __shfl_xor_sync(0xffffffffu, u, 16);
+        const float r = lane < 16 ? __fsub_rn(__fmul_rn(u, qc[j]), __fmul_rn(pu, qs[j]))
+                                  : __fadd_rn(__fmul_rn(pu, qs[j]), __fmul_rn(u, qc[j]));
+        qr[j] = r * a.attn_scale;
+      }
+    }
+    if (kjob || vjob) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < DPL; j++) ss = fmaf(rv[j], rv[j], ss);
+      ss = mg_warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.eps);
+      float x0 = 0.f, x1 = 0.f;  // this lane's element of block pb and of block pb + NB/2
+#pragma unroll
+      for (int j = 0; j < DPL / 2; j++)
+        if (j == pb) {
+          x0 = rv[j];
+          x1 = rv[j + DPL / 2];
         }
-        kx = ll_val(wk);
-        vx = ll_val(wv);
+      float lo, hi;
+      if (kjob) {
+        const float u = __fmul_rn(__fmul_rn(x0, inv), r_w0), vv = __fmul_rn(__fmul_rn(x1, inv), r_w1);
+        lo = __fsub_rn(__fmul_rn(u, r_c), __fmul_rn(vv, r_s));
+        hi = __fadd_rn(__fmul_rn(u, r_s), __fmul_rn(vv, r_c));
       } else {
-        while (ll_tag(wq) != tag && poll_again(pl, it)) wq = ll_load1(qp);
+        lo = __fmul_rn(x0, inv);
+        hi = __fmul_rn(x1, inv);
       }
-      qv = ll_val(wq);
+      uint8_t* dst = kjob ? skrow : svrow;
+      // values pass through f16 before packing (render.rs:1046)
+      mg_pack_q40(__half2float(__float2half_rn(lo)), dst + pb * KS_Q40_BLOCK_BYTES, lane);
+      mg_pack_q40(__half2float(__float2half_rn(hi)), dst + (pb + NB / 2) * KS_Q40_BLOCK_BYTES, lane);
     }
-    if (pf) pf[1] = clock64();
-    if (warp < NB) {  // the warps that hold the HD values
-      const float sq = mg_rows_sum(qv * qv, red, NB);
-      const float invq = 1.0f / sqrtf(sq / (float)HD + ap->eps);
-      vec[d] = __fmul_rn(__fmul_rn(qv, invq), qw);
-      if (owner) {
-        __syncthreads();
-        const float sk = mg_rows_sum(kx * kx, red, NB);
-        __syncthreads();
-        const float sv = mg_rows_sum(vx * vx, red, NB);
-        const float invk = 1.0f / sqrtf(sk / (float)HD + ap->eps), invv = 1.0f / sqrtf(sv / (float)HD + ap->eps);
-        vec[HD + d] = __fmul_rn(__fmul_rn(kx, invk), kw);
-        vx = __fmul_rn(vx, invv);
-      }
-    } else {  // the other warps only keep the barriers company
-      __syncthreads();
-      if (owner) {
-        __syncthreads();
-        __syncthreads();
-        __syncthreads();
-        __syncthreads();
-      }
-    }
-    __syncthreads();  // u = normed q (and k) of every dimension is in vec
-    float qrot = 0.f, krot = 0.f;
-    if (has) {
-      // dims of the first half pair with dim + HD/2 (gemma_prim.rs:33-56 cos / sin table)
-      const float u = vec[d], pu = vec[d ^ HALF];
-      qrot = d < HALF ? __fsub_rn(__fmul_rn(u, c), __fmul_rn(pu, sn)) : __fadd_rn(__fmul_rn(pu, sn), __fmul_rn(u, c));
-      if (owner) {
-        const float uk = vec[HD + d], pk = vec[HD + (d ^ HALF)];
-        krot = d < HALF ? __fsub_rn(__fmul_rn(uk, c), __fmul_rn(pk, sn)) : __fadd_rn(__fmul_rn(pk, sn), __fmul_rn(uk, c));
-      }
-    }
-    __syncthreads();  // every partner was read
-    if (has) {
-      vec[d] = qrot * ap->attn_scale;
-      if (owner) {
-        // values pass through f16 before packing (render.rs:1046); warp w holds block w of both rows
-        mg_pack_q40(__half2float(__float2half_rn(krot)), skrow + warp * KS_Q40_BLOCK_BYTES, lane);
-        mg_pack_q40(__half2float(__float2half_rn(vx)), svrow + warp * KS_Q40_BLOCK_BYTES, lane);
-      }
-    }
-    __syncthreads();  // q and the packed rows are in shared memory
-    if (owner && head == kvh * G) {
+  }
+  const size_t rowstride = (size_t)a.n_kv * ROWB;
+  uint8_t* Kc = L.kv_k + (size_t)kvh * ROWB;
+  uint8_t* Vc = L.kv_v + (size_t)kvh * ROWB;
+  if (owner) {
+    __syncthreads();
+    if (head == kvh * G) {
       const unsigned n16 = ROWB / 2;
       if (threadIdx.x < n16)
         reinterpret_cast<unsigned short*>(Kc + (size_t)pos * rowstride)[threadIdx.x] = reinterpret_cast<const unsigned short*>(skrow)[threadIdx.x];
@@ -614,30 +818,26 @@ __device__ MG_FN unsigned mg_attention(const AttnArgs* ap, const MegaLayer* Lp, 
             reinterpret_cast<const unsigned short*>(svrow)[threadIdx.x - n16];
     }
   }
-  if (pf) pf[2] = clock64();
-  float qr[DPL];
-#pragma unroll
-  for (int j = 0; j < DPL; j++) qr[j] = vec[mg_lane_dim<DPL>(lane, j)];
+  if (pf) pf[4] = clock64();
 
-  // 2. this warp's positions
   float o[DPL], m = kNegInit, l = 0.0f;
 #pragma unroll
   for (int j = 0; j < DPL; j++) o[j] = 0.0f;
-#pragma unroll 1
-  for (unsigned tb = p0 + (unsigned)warp; tb < p1; tb += MG_NW * MG_AB) {
-    if (tb != p0 + (unsigned)warp) {  // later batches (long contexts): the buffer is free again
-      __syncwarp();
-      prefetch_rows(tb);
+  {
+    RawRow<DPL> kn, vn;  // next row, in flight while the current one is processed
+    unsigned t = p0 + warp;
+    if (t < p1) {
+      raw_load<DPL>(t == pos ? skrow : Kc + (size_t)t * rowstride, lane, kn);
+      raw_load<DPL>(t == pos ? svrow : Vc + (size_t)t * rowstride, lane, vn);
     }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncwarp();
 #pragma unroll 1
-    for (int i = 0; i < MG_AB; i++) {
-      const unsigned t = tb + (unsigned)(MG_NW * i);
-      if (t >= p1) break;
-      RawRow<DPL> kr, vr;
-      raw_load<DPL>(t == pos ? skrow : kvbuf + (size_t)(2 * i) * ROWB, lane, kr);
-      raw_load<DPL>(t == pos ? svrow : kvbuf + (size_t)(2 * i + 1) * ROWB, lane, vr);
+    for (; t < p1; t += 8) {
+      const RawRow<DPL> kr = kn, vr = vn;
+      const unsigned t2 = t + 8;
+      if (t2 < p1) {
+        raw_load<DPL>(t2 == pos ? skrow : Kc + (size_t)t2 * rowstride, lane, kn);
+        raw_load<DPL>(t2 == pos ? svrow : Vc + (size_t)t2 * rowstride, lane, vn);
+      }
       float kv[DPL];
       raw_decode<DPL>(kr, kv);
       float sc = 0.0f;
@@ -654,7 +854,6 @@ __device__ MG_FN unsigned mg_attention(const AttnArgs* ap, const MegaLayer* Lp, 
       for (int j = 0; j < DPL; j++) o[j] = fmaf(e, kv[j], o[j] * alpha);
     }
   }
-  if (pf) pf[3] = clock64();
   {
     float* dst = part + warp * (HD + 2);
     if (lane == 0) {
@@ -665,420 +864,329 @@ __device__ MG_FN unsigned mg_attention(const AttnArgs* ap, const MegaLayer* Lp, 
     for (int j = 0; j < DPL; j++) dst[2 + j * 32 + lane] = o[j];
   }
   __syncthreads();
-  // 3. thread d folds head dimension d over the warps; it sits in slot j * 32 + lane of the warps' layout
+  if (pf) pf[5] = clock64();
+  // thread d folds head dimension d over the eight warps; it sits in slot j * 32 + lane of the warps' layout
+  const int d = threadIdx.x;
   int dslot;
   {
     constexpr int BPL = DPL / 2, LPB = 16 / BPL;
     const int within = d & 31, hh = within >> 4, w16 = within & 15;
-    dslot = (hh * BPL + (w16 % BPL)) * 32 + (((d >> 5) & (NB - 1)) * LPB + w16 / BPL);
+    dslot = (hh * BPL + (w16 % BPL)) * 32 + ((d >> 5) * LPB + w16 / BPL);
   }
+  const unsigned ounits = (a.n_q * HD) >> 6;
   float M = kNegInit, Lsum = 0.0f, O = 0.0f;
-  if (has) {
-#pragma unroll 1
-    for (int w = 0; w < MG_NW; w++) M = fmaxf(M, part[w * (HD + 2)]);
-#pragma unroll 1
-    for (int w = 0; w < MG_NW; w++) {
-      const float f = __expf(part[w * (HD + 2)] - M);
+  if (d < HD) {
+    float mw[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      mw[w] = part[w * (HD + 2)];
+      M = fmaxf(M, mw[w]);
+    }
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+      const float f = __expf(mw[w] - M);
       Lsum = fmaf(part[w * (HD + 2) + 1], f, Lsum);
       O = fmaf(part[w * (HD + 2) + 2 + dslot], f, O);
     }
   }
-  if (pf) pf[4] = clock64();
-  // 4.
-  if (NS == 1) {  // one split: this block's result is final
-    if (has) ll_store(ox + (size_t)head * HD + d, O / Lsum, tag);
-  } else {
-    u64* myrec = rec + ((size_t)head * NSMAX + split) * (HD + 2);
-    if (split != 0) {
-      if (has) {
-        ll_store(myrec + 2 + d, O, tag);  // records are kept in dimension order
-        if (d == 0) {
-          ll_store(myrec, M, tag);
-          ll_store(myrec + 1, Lsum, tag);
-        }
-      }
-    } else {
-      // The head's first block merges (lower.rs:5897-6088): its own record is in registers, the others are
-      // awaited.  Thread p fetches (m, l) of split p for everybody; thread d fetches O[d], four splits at a time.
-      const u64* rec0 = rec + (size_t)head * NSMAX * (HD + 2);
-      if (d == 0) {
-        ml[0] = M;
-        ml[1] = Lsum;
-      } else if ((unsigned)d < NS) {
-        const u64* r = rec0 + (size_t)d * (HD + 2);
-        u64 w0 = ll_load1(r), w1 = ll_load1(r + 1);
-        unsigned it = 0;
-        while (!(ll_tag(w0) == tag && ll_tag(w1) == tag) && poll_again(pl, it)) {
-          w0 = ll_load1(r);
-          w1 = ll_load1(r + 1);
-        }
-        ml[2 * d] = ll_val(w0);
-        ml[2 * d + 1] = ll_val(w1);
-      }
-      __syncthreads();
-      if (has) {
-        float MM = kNegInit;
-#pragma unroll 1
-        for (unsigned p = 0; p < NS; p++) MM = fmaxf(MM, ml[2 * p]);
-        float f0 = __expf(ml[0] - MM);
-        float LL = ml[1] * f0, OO = O * f0;
-#pragma unroll 1
-        for (unsigned pb = 1; pb < NS; pb += 4) {
-          u64 w[4];
-#pragma unroll
-          for (int k = 0; k < 4; k++)
-            if (pb + k < NS) w[k] = ll_load1(rec0 + (size_t)(pb + k) * (HD + 2) + 2 + d);
-          {
-            unsigned it = 0;
-            for (;;) {
-              bool any = false;
-#pragma unroll
-              for (int k = 0; k < 4; k++) any = any || (pb + k < NS && ll_tag(w[k]) != tag);
-              if (!any || !poll_again(pl, it)) break;
-#pragma unroll
-              for (int k = 0; k < 4; k++)
-                if (pb + k < NS && ll_tag(w[k]) != tag) w[k] = ll_load1(rec0 + (size_t)(pb + k) * (HD + 2) + 2 + d);
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < 4; k++)
-            if (pb + k < NS) {
-              const float f = __expf(ml[2 * (pb + k)] - MM);
-              LL = fmaf(ml[2 * (pb + k) + 1], f, LL);
-              OO = fmaf(ll_val(w[k]), f, OO);
-            }
-        }
-        ll_store(ox + (size_t)head * HD + d, OO / LL, tag);
-      }
-    }
-  }
   if (pf) pf[6] = clock64();
-  __syncthreads();  // the scratch is the next phase's x staging area
+  if (NS == 1) {  // one split: this block's result is final
+    if (d < HD) fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), O / Lsum, lane);
+    return;
+  }
+  float* rec = a.att_tmp + ((size_t)head * NSMAX + split) * (HD + 2);
+  if (d < HD) {
+    rec[2 + d] = O;  // records are kept in dimension order
+    if (d == 0) {
+      rec[0] = M;
+      rec[1] = Lsum;
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *sflag = (atomicAdd(a.att_cnt + head, 1u) == NS - 1) ? 1 : 0;
+  __syncthreads();
   if (pf) pf[7] = clock64();
-  return pl.gave_up ? (st | ST_GAVE_UP) : st;
+  if (*sflag) {
+    // last block of this head to arrive: merge the head's records, every load first
+    __threadfence();
+    if (d < HD) {
+      const float* rec0 = a.att_tmp + (size_t)head * NSMAX * (HD + 2);
+      float mp[MG_MAX_SPLITS], lp[MG_MAX_SPLITS], ov[MG_MAX_SPLITS];
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) {
+        if ((unsigned)p < NS) {
+          const float* r = rec0 + (size_t)p * (HD + 2);
+          mp[p] = __ldcg(r);
+          lp[p] = __ldcg(r + 1);
+          ov[p] = __ldcg(r + 2 + d);
+        } else {
+          mp[p] = kNegInit;
+          lp[p] = 0.0f;
+          ov[p] = 0.0f;
+        }
+      }
+      float MM = kNegInit;
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) MM = fmaxf(MM, mp[p]);
+      float LL = 0.0f, OO = 0.0f;
+#pragma unroll
+      for (int p = 0; p < MG_MAX_SPLITS; p++) {
+        const float f = __expf(mp[p] - MM);
+        LL = fmaf(lp[p], f, LL);
+        OO = fmaf(ov[p], f, OO);
+      }
+      fx_store_subblock(a.ox, ounits, head * HD + (d & ~31), OO / LL, lane);
+    }
+    if (threadIdx.x == 0) a.att_cnt[head] = 0u;
+  }
 }
 
 // ---- the kernel -------------------------------------------------------------------------------------
 struct MegaSmem {
-  unsigned xs_off, xres_off, ring_off, bar_off, done_off, red_off, psum_off, rowtab_off, tab_off, piece_off, info_off, total;
+  unsigned ring_off, bar_off, red_off, flag_off, tab_off, ent_off, total;
 };
-__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned hidden, unsigned slot_bytes, int n_slots, unsigned tables_bytes) {
+__host__ __device__ inline MegaSmem mg_smem(unsigned x_bytes, unsigned slot_bytes, int stages, unsigned tables_bytes) {
   MegaSmem L;
-  L.xs_off = 1024u;  // MegaShared first
-  L.xres_off = L.xs_off + ((x_bytes + 127u) & ~127u);
-  L.ring_off = L.xres_off + ((hidden * 4u + 127u) & ~127u);
-  L.bar_off = L.ring_off + (unsigned)n_slots * slot_bytes;
-  L.done_off = L.bar_off + MG_MAXSLOTS * 8u;
-  L.red_off = L.done_off + MG_MAXSLOTS * 4u;      // 16 float4 of block sums
-  L.psum_off = L.red_off + MG_NW * 16u;
-  L.rowtab_off = L.psum_off + 2u * MG_MAXROWS * MG_MAXC * 4u;
-  L.tab_off = L.rowtab_off + 2u * MG_MAXROWS * 4u;
-  L.piece_off = L.tab_off + tables_bytes;
-  L.info_off = L.piece_off + MG_MAXPIECE * (unsigned)sizeof(Piece);
-  L.total = L.info_off + PH_KINDS * (unsigned)sizeof(PhInfo) + 16u;
+  L.ring_off = (x_bytes + 127u) & ~127u;
+  L.bar_off = L.ring_off + 8u * (unsigned)stages * slot_bytes;
+  L.red_off = (L.bar_off + 8u * 8u * (unsigned)stages + 15u) & ~15u;
+  L.flag_off = L.red_off + 256u + MG_MAX_P * 32u;  // 32 floats for block sums, 8 float4 of per-warp norm sums, partial sums [MG_MAX_P][2][4]
+  L.tab_off = L.flag_off + 48u;  // 4 flag words, then 8 words of per-kind group counts
+  L.ent_off = L.tab_off + tables_bytes;
+  L.total = L.ent_off + 8u * MG_MAX_ENT * (unsigned)sizeof(ItemEnt);
   return L;
 }
 
-struct MegaShared {  // block-wide state at the start of dynamic shared memory
-  MegaSmem SL;
-  AttnArgs att;
-  unsigned n_slots, slot_bytes, n_layers, poll_limit;
-  unsigned NP, total_pieces;
-  unsigned* err;
-  int ok;
-};
-static_assert(sizeof(MegaShared) <= 1024, "MegaShared must fit its reserved kilobyte");
-
-// One matvec phase after its input was staged.  A lane owns one 64-weight unit of a 32-unit column
-// segment and keeps that unit of x in registers; a task is (segment, matrix, row); the tasks of a wave
-// (the rows of up to half the ring's slots) are ordered segment-major and cut into one
-// contiguous range per warp, so a warp loads x at most twice per wave and all warps get the same number
-// of tasks (+-1); two tasks run interleaved.  Row sums meet in shared memory; after a block-wide barrier
-// thread f finishes row f of the wave (segments added in order, epilogue, tagged store) while lanes of the
-// last warp refill the wave's slots with the pieces n_slots further down the sequence (one lane per slot:
-// issuing them one after the other from one thread cost 0.3 us each on the critical path).  Begins with
-// the block-wide barrier that ends the staging of x.
-__device__ MG_FN unsigned mg_phase(int kind, int layer, unsigned tag, u64* out, float* plain, long long* pf, unsigned st, long long* pa) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  const MegaShared* S = reinterpret_cast<const MegaShared*>(smem);
-  const MegaSmem& SL = S->SL;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t ring_s = sm32(smem + SL.ring_off), bars = sm32(smem + SL.bar_off), xs_s = sm32(smem + SL.xs_off);
-  float* psum = reinterpret_cast<float*>(smem + SL.psum_off);
-  uint32_t* rowaddr = reinterpret_cast<uint32_t*>(smem + SL.rowtab_off);  // shared address of each row of the wave (first matrix)
-  uint32_t* rowmat2 = rowaddr + MG_MAXROWS;                               // distance to the same row of the second matrix
-  const MegaPhase* phases = reinterpret_cast<const MegaPhase*>(smem + SL.tab_off);
-  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u));
-  const Piece* pieces = reinterpret_cast<const Piece*>(smem + SL.piece_off);
-  const PhInfo inf = reinterpret_cast<const PhInfo*>(smem + SL.info_off)[kind];
-  const MegaPhase& ph = phases[kind];
-  const unsigned n_slots = S->n_slots, slot_bytes = S->slot_bytes, NP = S->NP;
-  unsigned slot = st & 0xFFu, par = (st >> 8) & 1u;
-  bool dead = (st & ST_DEAD) != 0u;
-
-  const unsigned NS = ph.n_cseg, units = ph.cols >> 6, seg_units = ph.seg_units;
-  const unsigned row_bytes = ph.row_bytes, mats = ph.mats;
-  const unsigned wave_max = n_slots > 1u ? n_slots / 2u : 1u;
-  const bool active = (unsigned)lane < seg_units;
-  XUnit x;
-  int cur_s = -1;
-  for (unsigned wp0 = inf.p0; wp0 < (unsigned)inf.p0 + inf.np; wp0 += wave_max) {
-    const unsigned wp1 = min(wp0 + wave_max, (unsigned)inf.p0 + inf.np);
-    const unsigned wr0 = pieces[wp0].row0, wr1 = (unsigned)pieces[wp1 - 1].row0 + pieces[wp1 - 1].nrows, rows_w = wr1 - wr0;
-    if (threadIdx.x < rows_w) {
-      const unsigned r = wr0 + threadIdx.x;
-      unsigned pi = wp0;
-      while (pi + 1 < wp1 && pieces[pi + 1].row0 <= r) pi++;
-      unsigned sl = slot + (pi - wp0);
-      if (sl >= n_slots) sl -= n_slots;
-      rowaddr[threadIdx.x] = ring_s + sl * slot_bytes + (r - pieces[pi].row0) * row_bytes;
-      rowmat2[threadIdx.x] = (((unsigned)pieces[pi].nrows + 3u) & ~3u) * row_bytes;
-    }
-    __syncthreads();  // x is staged (first wave), the row table is written
-    if (pf && wp0 == inf.p0) pf[2] = clock64();
-    if (pa && threadIdx.x == 0 && wp0 == inf.p0) pa[3] = gtime();
-    // the wave's weights: one lane per piece asks the piece's mbarrier, the warp votes
-    if (!dead) {
-      bool ok = true;
-      if ((unsigned)lane < wp1 - wp0) {
-        unsigned sl = slot + (unsigned)lane, pr = par;
-        if (sl >= n_slots) {
-          sl -= n_slots;
-          pr ^= 1u;
-        }
-        ok = mb_wait(bars + sl * 8u, pr, S->poll_limit);
-      }
-      if (!__all_sync(0xffffffffu, ok)) {
-        dead = true;
-        if (lane == 0) atomicOr(S->err, 1u);
-      }
-    }
-    if (pa && threadIdx.x == 0 && wp0 == inf.p0) pa[4] = gtime();
-    if (!dead) {
-      const unsigned per_seg = mats * rows_w, T = NS * per_seg;
-      const unsigned t0 = (unsigned)warp * T / MG_NW, t1 = (unsigned)(warp + 1) * T / MG_NW;
-      unsigned t = t0, sg = t0 / per_seg, rem = t0 - sg * per_seg;
-      // task (sg, rem): rem < rows_w is row rem of the first matrix, else row rem - rows_w of the second
-      auto row_of = [&](unsigned q, uint32_t uoff, uint32_t& wa, unsigned& pidx) {
-        const unsigned m = q >= rows_w ? 1u : 0u, r = q - m * rows_w;
-        wa = rowaddr[r] + (m ? rowmat2[r] : 0u) + uoff;
-        pidx = ((wr0 + r) * mats + m) * NS + sg;
-      };
-#pragma unroll 1
-      while (t < t1) {
-        const unsigned u = sg * seg_units + (unsigned)lane;
-        if ((int)sg != cur_s) {
-          if (active) fx_load_unit(x, xs_s, units, u);
-          cur_s = (int)sg;
-        }
-        const uint32_t uoff = (u >> 2) * KS_Q4K_BLOCK_BYTES + (u & 3u) * 32u;
-        unsigned n = min(t1 - t, per_seg - rem);  // my tasks left in this segment
-        t += n;
-#pragma unroll 1
-        for (; n >= 2u; n -= 2u, rem += 2u) {  // two rows at a time: their instruction streams interleave
-          uint32_t wa[2];
-          unsigned pidx[2];
-          row_of(rem, uoff, wa[0], pidx[0]);
-          row_of(rem + 1u, uoff, wa[1], pidx[1]);
-          float v[2] = {0.0f, 0.0f};
-          if (active) fx_rows<2>(wa, (int)(u & 3u), x, v);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
-            v[1] += __shfl_xor_sync(0xffffffffu, v[1], o);
-          }
-          if (lane == 0) {
-            psum[pidx[0]] = v[0];
-            psum[pidx[1]] = v[1];
-          }
-        }
-        if (n) {
-          uint32_t wa[1];
-          unsigned pidx;
-          row_of(rem, uoff, wa[0], pidx);
-          float v[1] = {0.0f};
-          if (active) fx_rows<1>(wa, (int)(u & 3u), x, v);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
-          if (lane == 0) psum[pidx] = v[0];
-          rem += 1u;
-        }
-        if (rem == per_seg) {
-          rem = 0;
-          sg++;
-        }
-      }
-    }
-    if (pf) pf[3] = clock64();
-    if (pa && threadIdx.x == 0) pa[5] = gtime();
-    __syncthreads();  // the wave's row sums are in shared memory and nobody reads its slots any more
-    if (pf) pf[4] = clock64();
-    if (pa && threadIdx.x == 0) pa[6] = gtime();
-    // the last warp (never a finishing warp) refills the wave's slots with the pieces n_slots further on, one lane per slot
-    if (warp == MG_NW - 1 && (unsigned)lane < wp1 - wp0) {
-      const long long rt0 = pa ? gtime() : 0;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slots were read through the generic proxy
-      unsigned sl = slot + (unsigned)lane;
-      if (sl >= n_slots) sl -= n_slots;
-      unsigned npi = wp0 + (unsigned)lane + n_slots;
-      unsigned nl = (unsigned)layer;
-      while (npi >= NP) {
-        npi -= NP;
-        nl++;
-      }
-      if (nl < S->n_layers) {
-        const Piece np_ = pieces[npi];
-        issue_piece(np_, phases[np_.kind], layers[nl], ring_s + sl * slot_bytes, bars + sl * 8u);
-      }
-      if (pa && lane == 0) pa[7] = gtime() - rt0;
-    }
-    // thread f finishes row wr0 + f of the block: segments added in order, epilogue, tagged store
-    if (threadIdx.x < rows_w) {
-      const unsigned r = wr0 + threadIdx.x;
-      unsigned pi = wp0;
-      while (pi + 1 < wp1 && pieces[pi + 1].row0 <= r) pi++;
-      const unsigned orow = pieces[pi].out0 + (r - pieces[pi].row0);
-      const float* ps = psum + (size_t)r * mats * NS;
-      float v0 = 0.0f;
-      for (unsigned sg = 0; sg < NS; sg++) v0 += ps[sg];
-      if (mats == 2) {
-        float v1 = 0.0f;
-        for (unsigned sg = 0; sg < NS; sg++) v1 += ps[NS + sg];
-        v0 = gelu_mul(v0, v1);
-      }
-      ll_store(out + orow, v0, tag);
-      if (plain) plain[orow] = v0;  // the head reads plain floats
-    }
-    if (pf) pf[5] = clock64();
-    slot += wp1 - wp0;
-    if (slot >= n_slots) {
-      slot -= n_slots;
-      par ^= 1u;
-    }
-  }
-  return (st & ST_GAVE_UP) | slot | (par << 8) | (dead ? ST_DEAD : 0u);
-}
-
 template <int DPL, int PC>
-__global__ void __launch_bounds__(MG_THREADS, 1) mega_kernel(const MegaArgs a) {
+__global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  MegaShared* S = reinterpret_cast<MegaShared*>(smem);
-  const unsigned H0 = reinterpret_cast<const MegaPhase*>(a.tables)[PH_QKV].cols;  // hidden size (tables are in global memory here)
-  const MegaSmem SL = mg_smem(a.x_bytes, H0, a.slot_bytes, a.n_slots, a.tables_bytes);
-  const uint32_t ring_s = sm32(smem + SL.ring_off);
-  const uint32_t bars = sm32(smem + SL.bar_off);
-  float4* red = reinterpret_cast<float4*>(smem + SL.red_off);
-  float* xres = reinterpret_cast<float*>(smem + SL.xres_off);
-  unsigned char* xs = smem + SL.xs_off;
-  const MegaPhase* phases = reinterpret_cast<const MegaPhase*>(smem + SL.tab_off);
-  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u));
-  Piece* pieces = reinterpret_cast<Piece*>(smem + SL.piece_off);
-  PhInfo* info = reinterpret_cast<PhInfo*>(smem + SL.info_off);
-  const unsigned n_slots = (unsigned)a.n_slots;
+  const int cl = lane % MG_LPR, rl = lane / MG_LPR;
+  const int S = a.stages;
+  const MegaSmem SL = mg_smem(a.x_bytes, a.slot_bytes, S, a.tables_bytes);
+  const uint32_t ring_s = sm32(smem + SL.ring_off) + (uint32_t)(warp * S) * a.slot_bytes;
+  const uint32_t bars = sm32(smem + SL.bar_off) + (uint32_t)(warp * S) * 8u;
+  float* red = reinterpret_cast<float*>(smem + SL.red_off);
+  float4* wsum = reinterpret_cast<float4*>(smem + SL.red_off + 128u);
+  float* psum = reinterpret_cast<float*>(smem + SL.red_off + 256u);
+  int* sflag = reinterpret_cast<int*>(smem + SL.flag_off);
+  const MegaShape* shapes = reinterpret_cast<const MegaShape*>(smem + SL.tab_off);
+  const MegaLayer* layers = reinterpret_cast<const MegaLayer*>(smem + SL.tab_off + ((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u));
+  const uint32_t xs_s = sm32(smem);
+  const unsigned bar_base = a.bar[1];
+  const int n_phases = a.n_layers * PH_PER_LAYER;
 
   for (unsigned i = threadIdx.x; i < a.tables_bytes / 16u; i += blockDim.x)
     reinterpret_cast<uint4*>(smem + SL.tab_off)[i] = reinterpret_cast<const uint4*>(a.tables)[i];
-  if (threadIdx.x == 0) {
-    S->SL = SL;
-    S->att.n_q = a.n_q; S->att.n_kv = a.n_kv; S->att.n_splits = a.n_splits; S->att.split_from = a.split_from;
-    S->att.eps = a.eps; S->att.attn_scale = a.attn_scale; S->att.rope = a.rope; S->att.pos = a.pos;
-    S->att.err = a.err; S->att.limit = a.poll_limit;
-    S->n_slots = n_slots; S->slot_bytes = a.slot_bytes; S->n_layers = (unsigned)a.n_layers; S->poll_limit = a.poll_limit;
-    S->err = a.err;
-    for (unsigned s = 0; s < n_slots; s++) mb_init(bars + s * 8u, 1);
+  if (threadIdx.x == 0) sflag[2] = sflag[3] = 0;  // barrier flag words ([0] belongs to the attention phase)
+  unsigned* ngrp = reinterpret_cast<unsigned*>(smem + SL.flag_off + 16u);  // this block's group count per phase kind
+  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = 0;
+  if (lane == 0) {
+    for (int s = 0; s < S; s++) mb_init(bars + s * 8u, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    S->ok = build_pieces(pieces, info, phases) ? 1 : 0;
-    S->NP = (unsigned)info[PH_KINDS - 1].p0 + info[PH_KINDS - 1].np;
-    S->total_pieces = S->NP * (unsigned)a.n_layers;
-  }
-  __syncthreads();
-  if (!S->ok) {  // a table overflowed: the host's own check of the same arithmetic should have refused this shape
-    if (threadIdx.x == 0) atomicOr(a.err, 4u);
-    return;
-  }
-  const unsigned NP = S->NP, total_pieces = S->total_pieces;
-  const unsigned epoch = *a.epoch;
+  if (threadIdx.x < PH_PER_LAYER) ngrp[threadIdx.x] = block_groups(shapes[threadIdx.x]);
+  const unsigned H = shapes[PH_QKV].cols;
 
-  // fill the ring: piece n goes to slot n
-  if (lane == 0)
-    for (unsigned n = (unsigned)warp; n < n_slots && n < total_pieces; n += MG_NW) {
-      const Piece p = pieces[n % NP];
-      issue_piece(p, phases[p.kind], layers[n / NP], ring_s + n * a.slot_bytes, bars + n * 8u);
-    }
-
-  // the residual stream: thread t keeps chunks t and t + 512 (only ever touched by the same thread)
-  const unsigned H = phases[PH_QKV].cols;
-  for (unsigned c = threadIdx.x; c < (H >> 2); c += MG_THREADS)
-    reinterpret_cast<float4*>(xres)[c] = reinterpret_cast<const float4*>(a.x_in)[c];
+  ItemEnt* ent = reinterpret_cast<ItemEnt*>(smem + SL.ent_off) + warp * MG_MAX_ENT;
+  int n_ent = 0;
+  if (lane == 0) n_ent = build_items(ent, shapes, warp);
+  n_ent = __shfl_sync(0xffffffffu, n_ent, 0);
+  bool dead = false;  // this warp gave up (a copy never landed, or its item table overflowed): it keeps the block-level steps only
+  if (n_ent < 0) {
+    dead = true;
+    if (lane == 0) atomicOr(a.err, 4u);
+    n_ent = 0;
+  }
+  __syncwarp();
+  ItemPos ic{n_ent > 0 ? 0 : a.n_layers, 0}, cc = ic;
+  unsigned issued = 0, consumed = 0;
+  while (issued < (unsigned)S && ic.layer < a.n_layers) {
+    const ItemEnt e = ent[ic.e];
+    mg_issue_ent(e, layers[ic.layer], shapes[e.kind].row_bytes, ring_s + issued * a.slot_bytes, bars + issued * 8u, lane);
+    issued++;
+    pos_next(ic, n_ent);
+  }
 
   long long* prof = nullptr;
-  if (a.prof && threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
-    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * a.n_layers * PF_PER_LAYER * PF_STAMPS;
-
-  long long* pall = (a.prof_all && (threadIdx.x == 0 || threadIdx.x == MG_THREADS - 32)) ? a.prof_all + (size_t)blockIdx.x * a.n_layers * PF_PER_LAYER * 8 : nullptr;
-  unsigned st = 0u;  // ring position, wait state (see ST_*)
-#pragma unroll 1
-  for (int layer = 0; layer < a.n_layers; layer++) {
-    const unsigned tag = epoch + (unsigned)layer + 1u;
-    const int b = layer & 1;
-    const bool last = layer + 1 == a.n_layers;
-#pragma unroll 1
-    for (int kind = 0; kind < PH_KINDS; kind++) {
-      // kernel parameters are picked with selects (indexing them would force a local copy)
-      u64* const yd = b ? a.ll_yd1 : a.ll_yd0;
-      u64* const yo = b ? a.ll_yo1 : a.ll_yo0;
-      u64* const qkv = b ? a.ll_qkv1 : a.ll_qkv0;
-      u64* const ox = b ? a.ll_ox1 : a.ll_ox0;
-      u64* const ff = b ? a.ll_ff1 : a.ll_ff0;
-      // profile rows: qkv, attention, o-proj, gate-up, down
-      long long* pf = prof ? prof + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * PF_STAMPS : nullptr;
-      const MegaLayer& L = layers[layer];
-      if (kind == PH_OPROJ) {
-        if (pall && threadIdx.x == 0) pall[((size_t)layer * PF_PER_LAYER + PF_ATTN) * 8] = gtime();
-        if (pf) pf[-PF_STAMPS] = clock64();
-        st = mg_attention<DPL>(&S->att, &L, qkv, ox, b ? a.ll_rec1 : a.ll_rec0, tag, xs, st, pf ? pf - PF_STAMPS : nullptr);
-      }
-      if (pall && threadIdx.x == 0) {
-        if (kind == PH_OPROJ) pall[((size_t)layer * PF_PER_LAYER + PF_ATTN) * 8 + 1] = gtime();
-        pall[((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 8] = gtime();
-      }
-      if (pf) pf[0] = clock64();
-      // ---- this phase's input vector, staged in shared memory
-      if (kind == PH_QKV || kind == PH_GATEUP) {
-        // residual update (from the second phase on) + norm.  q/k/v: the previous layer's down-proj output
-        // and post-FFN norm, then this layer's attention norm; gate/up: the o-proj output and post-attention
-        // norm, then the FFN norm.
-        const bool qk = kind == PH_QKV;
-        st = mg_stage_hidden<PC>(xs, red, xres, !qk || layer > 0, H, qk ? (b ? a.ll_yd0 : a.ll_yd1) : yo,
-                                 qk ? tag - 1u : tag + a.test_stall, qk ? L.norm[0] : L.norm[4],
-                                 qk ? layers[layer > 0 ? layer - 1 : 0].norm[5] : L.norm[3], a.eps,
-                                 (!qk && last && blockIdx.x == 0) ? a.resid_out : nullptr, a.err, a.poll_limit, st, pf);
+  if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
+    prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * n_phases * 8;
+  int p = 0, layer = 0, kind = 0;
+  for (; p < n_phases; p++) {
+    const MegaLayer& L = layers[layer];
+    // constants of this phase, fetched while the other blocks arrive at the barrier before it
+    NormPre<PC> npre;
+    if (kind == PH_QKV)
+      mg_prefetch_norm(npre, layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM, L.norm[0], layers[layer > 0 ? layer - 1 : 0].norm[5], H);
+    else if (kind == PH_GATEUP)
+      mg_prefetch_norm(npre, KS_PRO_ADD_NORM, L.norm[4], L.norm[3], H);
+    if (p > 0) {
+      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x + (p == 1 ? a.test_stall : 0u), a.err, sflag + 2, p & 1, a.poll_limit)) break;
+      if (prof) prof[(p - 1) * 8 + 3] = clock64();
+    }
+    if (prof) prof[p * 8 + 0] = clock64();
+    if (kind == PH_ATTN) {
+      mg_attention<DPL>(a, L, smem, sflag, prof ? prof + p * 8 : nullptr);
+    } else {
+      const MegaShape& sh = shapes[kind];
+      // input, prologue and outputs of this phase
+      int mode = KS_PRO_NONE;
+      const float* x;
+      const float* yin = a.yb;
+      float* out_x = nullptr;
+      if (kind == PH_QKV) {
+        mode = layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM;
+        x = layer == 0 ? a.x_a : a.x_b;
+        out_x = a.x_a;
+      } else if (kind == PH_OPROJ) {
+        x = nullptr;
+      } else if (kind == PH_GATEUP) {
+        mode = KS_PRO_ADD_NORM;
+        x = a.x_a;
+        out_x = a.x_b;
       } else {
-        st = mg_stage_plain(xs, phases[kind].cols, kind == PH_OPROJ ? ox : ff, tag, a.err, a.poll_limit, st, pf);
+        x = nullptr;
       }
-      u64* const out = kind == PH_QKV ? qkv : kind == PH_OPROJ ? yo : kind == PH_GATEUP ? ff : yd;
-      long long* pa = pall ? pall + ((size_t)layer * PF_PER_LAYER + (kind == PH_QKV ? PF_QKV : kind + 1)) * 8 : nullptr;
-      if (pa && threadIdx.x == 0) pa[2] = gtime();
-      st = mg_phase(kind, layer, tag, out, (kind == PH_DOWN && last) ? a.y_out : nullptr, pf, st, pa);
-      if (pa && threadIdx.x == 0) pa[1] = gtime();
+      if (kind == PH_OPROJ || kind == PH_DOWN)
+        fx_copy_in(smem, kind == PH_OPROJ ? a.ox : a.ffx, sh.cols >> 6);
+      else if (mode == KS_PRO_ADD_NORM)
+        mg_stage_addnorm(smem, sh.cols, x, yin, out_x, a.eps, npre, a.nsum, gridDim.x);
+      else
+        mg_stage_x(smem, red, mode, sh.cols, x, yin, out_x, a.eps, npre);
+      __syncthreads();
+      if (prof) prof[p * 8 + 1] = clock64();
+      const unsigned units = sh.cols >> 6;
+      // o-proj and down feed a residual-add + norm: their rows also leave the sums that norm needs
+      const bool sums = kind == PH_OPROJ || kind == PH_DOWN;
+      // Thread f finishes row (f & 3) of this block's group (f >> 2): it adds the column segments'
+      // partial sums in order, applies the epilogue and stores the row.
+      const unsigned n_g = ngrp[kind], C = sh.n_cseg;
+      unsigned frow = 0;
+      int fseg = 0;
+      bool fin = false;
+      float xr = 0.0f, wpr = 0.0f;
+      if ((threadIdx.x >> 2) < n_g) {
+        const unsigned g = block_group_id(sh, threadIdx.x >> 2);
+        if (sh.n_seg > 1 && g >= sh.grp_start[1]) fseg = 1;
+        if (sh.n_seg > 2 && g >= sh.grp_start[2]) fseg = 2;
+        frow = (g - sh.grp_start[fseg]) * MG_RL + (threadIdx.x & 3u);
+        fin = g < sh.grp_start[sh.n_seg] && frow < sh.rows[fseg];
+        if (fin && sums) {  // in flight while the items are multiplied
+          xr = __ldcg((kind == PH_OPROJ ? a.x_a : a.x_b) + frow);
+          wpr = (kind == PH_OPROJ ? L.norm[3] : L.norm[5])[frow];
+        }
+      }
+      while (cc.layer == layer && !dead) {
+        const ItemEnt e = ent[cc.e];
+        if (e.kind != kind) break;
+        const unsigned st = consumed % (unsigned)S;
+        if (!mb_wait(bars + st * 8u, (consumed / (unsigned)S) & 1u)) {
+          dead = true;
+          if (lane == 0) atomicOr(a.err, 1u);
+          break;
+        }
+        const uint32_t slot = ring_s + st * a.slot_bytes;
+        float yacc[2] = {0.0f, 0.0f};
+        if (e.flags & 1)
+          mg_item_compute_fx<2>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
+        else
+          mg_item_compute_fx<1>(slot, xs_s, units, sh.seg_blocks, e.cs, cl, rl, yacc);
+        consumed++;
+        float v0 = yacc[0], v1 = yacc[1];
+#pragma unroll
+        for (int o = MG_LPR / 2; o > 0; o >>= 1) {
+          v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+          v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+        }
+        if (cl == 0) {
+          if (e.flags & 4) {
+            psum[e.pslot * 8u + 4u + (unsigned)rl] = v0;  // the up rows of a split gate-up group
+          } else {
+            psum[e.pslot * 8u + (unsigned)rl] = v0;
+            if (e.flags & 1) psum[e.pslot * 8u + 4u + (unsigned)rl] = v1;
+          }
+        }
+        pos_next(cc, n_ent);
+        // Refill now only when the next item of THIS phase is not in flight yet; everything else is
+        // refilled after the barrier arrival below, off the critical path.
+        if (ic.layer == layer && ent[ic.e].kind == kind) {
+          __syncwarp();
+          if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the slot was read through the generic proxy
+          __syncwarp();
+          const ItemEnt ne = ent[ic.e];
+          mg_issue_ent(ne, layers[ic.layer], sh.row_bytes, slot, bars + st * 8u, lane);
+          issued++;
+          pos_next(ic, n_ent);
+        }
+      }
+      __syncthreads();  // the partial sums of every item of this block are in shared memory
+      float ns0 = 0.0f, ns1 = 0.0f, ns2 = 0.0f, ns3 = 0.0f, fval = 0.0f;
+      if (fin) {
+        const float* ps = psum + (size_t)(threadIdx.x >> 2) * C * 8u + (threadIdx.x & 3u);
+        float v0 = 0.0f, v1 = 0.0f;
+        for (unsigned cs = 0; cs < C; cs++) {
+          v0 += ps[cs * 8u];
+          v1 += ps[cs * 8u + 4u];
+        }
+        fval = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
+        const float val = fval;
+        if (kind != PH_GATEUP) {
+          float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : a.yb;
+          y[frow] = val;
+        }
+        if (sums) {
+          const float t = val * wpr;
+          ns0 = val * val;
+          ns1 = xr * t;
+          ns2 = t * t;
+          ns3 = xr * xr;
+        }
+      }
+      if (kind == PH_GATEUP && (threadIdx.x >> 2) < n_g) {
+        // this warp's 32 threads hold 32 consecutive rows (a run of 8 groups): one sub-block of the next phase's x
+        const unsigned g0 = block_group_id(sh, (threadIdx.x >> 2) & ~7u);
+        if (g0 < sh.grp_start[1]) fx_store_subblock(a.ffx, sh.rows[0] >> 6, g0 * MG_RL, fval, lane);
+      }
+      if (sums) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          ns0 += __shfl_xor_sync(0xffffffffu, ns0, o);
+          ns1 += __shfl_xor_sync(0xffffffffu, ns1, o);
+          ns2 += __shfl_xor_sync(0xffffffffu, ns2, o);
+          ns3 += __shfl_xor_sync(0xffffffffu, ns3, o);
+        }
+        if (lane == 0) wsum[warp] = make_float4(ns0, ns1, ns2, ns3);
+      }
+    }
+    if (prof) prof[p * 8 + 2] = clock64();
+    if (p + 1 == n_phases) {  // the end of the kernel orders the last phase before whatever follows
+      p++;
+      break;
+    }
+    grid_arrive(a.bar, (kind == PH_OPROJ || kind == PH_DOWN) ? wsum : nullptr, a.nsum);
+    // refill the ring while the other blocks arrive
+    if (!dead && issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
+      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      while (issued - consumed < (unsigned)S && ic.layer < a.n_layers) {
+        const unsigned st = issued % (unsigned)S;
+        const ItemEnt ne = ent[ic.e];
+        mg_issue_ent(ne, layers[ic.layer], shapes[ne.kind].row_bytes, ring_s + st * a.slot_bytes, bars + st * 8u, lane);
+        issued++;
+        pos_next(ic, n_ent);
+      }
+    }
+    if (++kind == PH_PER_LAYER) {
+      kind = 0;
+      layer++;
     }
   }
-  // The next token's tags must differ from everything this one wrote.  Every block read the epoch before
-  // block 0 can get here (its last phase needed rows from all of them).
-  if (blockIdx.x == 0 && threadIdx.x == 0) *a.epoch = epoch + (unsigned)a.n_layers + 1u;
-  // copies still in flight must land before this block's shared memory goes away (bounded; a no-op unless a warp gave up)
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (unsigned s = 0; s < n_slots && s < total_pieces; s++) {
-      const unsigned n_last = s + ((total_pieces - 1u - s) / n_slots) * n_slots;
-      mb_wait(bars + s * 8u, (n_last / n_slots) & 1u, a.poll_limit);
-    }
-  }
+  if (p == n_phases && blockIdx.x == 0 && threadIdx.x == 0) a.bar[1] = bar_base + (unsigned)(n_phases - 1) * gridDim.x;
+  // copies still in flight must land before this block's shared memory goes away (bounded)
+  for (unsigned j = consumed; j < issued; j++) mb_wait(bars + (j % (unsigned)S) * 8u, (j / (unsigned)S) & 1u);
 }
 
 }  // namespace
@@ -1087,15 +1195,14 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_kernel(const MegaArgs a) {
 struct ks_mega {
   MegaArgs args{};
   void* d_tables = nullptr;
-  unsigned* d_sync = nullptr;     // word 0: the tag epoch
+  unsigned* d_sync = nullptr;  // words 0..1 barrier (a 128-byte line of its own: every block polls it), 64..111 per-head
+                               // attention arrival counters, from byte 512: per-block norm sums
   long long* d_prof = nullptr;
-  long long* d_prof_all = nullptr;
-  u64* d_ll = nullptr;            // the tagged activation vectors
-  size_t ll_bytes = 0;
+  unsigned char* d_fx = nullptr;  // attention output and GeGLU output in the staged layout
   unsigned grid = 0;
   size_t smem = 0;
-  int dpl = 0, pc = 1;            // pc: 4-element chunks of the hidden vector per thread
-  float* residual = nullptr;      // buffer that holds the residual stream when the kernel ends
+  int G = 0, dpl = 0, pc = 4;  // pc: 4-element chunks of the hidden vector per thread (2 up to 2048 columns)
+  float* residual = nullptr;  // buffer that holds the residual stream when the kernel ends
 };
 
 namespace {
@@ -1110,11 +1217,11 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(mg->grid);
-  cfg.blockDim = dim3(MG_THREADS);
+  cfg.blockDim = dim3(256);
   cfg.dynamicSmemBytes = mg->smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;  // every block resident: blocks wait for each other's rows
+  attr[0].id = cudaLaunchAttributeCooperative;  // every block resident: the grid barrier needs it
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -1125,48 +1232,31 @@ int mega_launch_t(ks_ctx* ctx, ks_mega* mg) {
 }  // namespace
 
 int ks_mega_launch(ks_ctx* ctx, ks_mega* mg) {
-  if (mg->dpl == 4) {
-    switch (mg->pc) {
-      case 1: return mega_launch_t<4, 1>(ctx, mg);
-      case 2: return mega_launch_t<4, 2>(ctx, mg);
-      case 3: return mega_launch_t<4, 3>(ctx, mg);
-      case 4: return mega_launch_t<4, 4>(ctx, mg);
-    }
-  } else if (mg->dpl == 8) {
-    switch (mg->pc) {
-      case 1: return mega_launch_t<8, 1>(ctx, mg);
-      case 2: return mega_launch_t<8, 2>(ctx, mg);
-      case 3: return mega_launch_t<8, 3>(ctx, mg);
-      case 4: return mega_launch_t<8, 4>(ctx, mg);
-    }
-  }
-  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size or hidden size not supported");
+  if (mg->dpl == 4) return mg->pc == 2 ? mega_launch_t<4, 2>(ctx, mg) : mega_launch_t<4, 4>(ctx, mg);
+  if (mg->dpl == 8) return mg->pc == 2 ? mega_launch_t<8, 2>(ctx, mg) : mega_launch_t<8, 4>(ctx, mg);
+  return ks_fail(ctx, KS_ERR_UNSUPPORTED, "decode kernel: head size not supported");
 }
 
 float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
 
-// After a wait gave up the tagged vectors hold a mix of tokens; clearing them (tag 0 is never used)
-// puts the kernel back in working order.  The epoch word keeps counting.  Stream-ordered.
+// Zero the barrier words and arrival counters (stream-ordered).  They only leave their rest state when
+// a bounded wait gave up; a slot reset puts the kernel back in working order.
 int ks_mega_reset(ks_ctx* ctx, ks_mega* mg) {
-  cudaError_t e = cudaMemsetAsync(mg->d_ll, 0, mg->ll_bytes, ctx->stream);
+  cudaError_t e = cudaMemsetAsync(mg->d_sync, 0, 512, ctx->stream);
   if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: reset failed: %s", cudaGetErrorString(e));
   return KS_OK;
 }
 const long long* ks_mega_prof(const ks_mega* mg) { return mg->d_prof; }
-const long long* ks_mega_prof_all(const ks_mega* mg) { return mg->d_prof_all; }
 
-// Knobs that tests and the profiling reader set: 0 = polls before a wait gives up, 1 = make the gate-up stage
-// of every layer wait for a tag nobody writes (0 = off), 2 = context length from which attention is split
-// across blocks, 3 = record phase clocks (0 / 1).  The caller re-captures its graphs afterwards.
+// Test knobs (the next launch sees them; graphs captured before must be dropped by the caller):
+// 0 = polls before a barrier wait gives up, 1 = make the first barrier of a token wait for `value`
+// arrivals that never come (exercises the give-up path; 0 switches it off).  2 and 3 belong to the
+// dataflow kernel (attention split point, stamps on or off) and are accepted without effect.
 int ks_mega_set(ks_mega* mg, int what, unsigned value) {
-  if (!mg) return KS_ERR_INVALID;
-  switch (what) {
-    case 0: mg->args.poll_limit = value ? value : 1u; return KS_OK;
-    case 1: mg->args.test_stall = value; return KS_OK;
-    case 2: mg->args.split_from = value; return KS_OK;
-    case 3: mg->args.prof = value ? mg->d_prof : nullptr; mg->args.prof_all = value > 1 ? mg->d_prof_all : nullptr; return KS_OK;
-    default: return KS_ERR_INVALID;
-  }
+  if (what == 0) mg->args.poll_limit = value ? value : 1u;
+  else if (what == 1) mg->args.test_stall = value;
+  else if (what != 2 && what != 3) return KS_ERR_INVALID;
+  return KS_OK;
 }
 
 void ks_mega_destroy(ks_mega* mg) {
@@ -1174,8 +1264,7 @@ void ks_mega_destroy(ks_mega* mg) {
   if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
   if (mg->d_prof) cudaFree(mg->d_prof);
-  if (mg->d_prof_all) cudaFree(mg->d_prof_all);
-  if (mg->d_ll) cudaFree(mg->d_ll);
+  if (mg->d_fx) cudaFree(mg->d_fx);
   delete mg;
 }
 
@@ -1185,90 +1274,114 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   *out = nullptr;
   const unsigned H = d->hidden, F = d->ffn, hd = d->hd, nq = d->n_q, nkv = d->n_kv;
   const unsigned qn = nq * hd, kvn = nkv * hd;
-  if (H % 256u || F % 256u || qn % 256u) return KS_OK;
-  if (H > 4u * 4u * MG_THREADS) return KS_OK;  // the norm stages hold at most four 4-element chunks per thread
-  if (nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
-  const unsigned grid = (unsigned)ctx->sm_count;
+  const unsigned G = nq / nkv;
+  auto even_blocks = [](unsigned cols) { return cols % 512 == 0; };
+  if (!even_blocks(H) || !even_blocks(F) || !even_blocks(qn)) return KS_OK;
+  if (H > 16u * 256u) return KS_OK;  // the fused norms hold the vector in registers
+  if (G < 1 || nq % nkv || !(hd == 128 || hd == 256)) return KS_OK;
   // one block per (query head, split): fewer splits than the caller's record layout allows if the grid is small
   unsigned n_splits = (unsigned)d->n_splits;
-  if (n_splits > grid / nq) n_splits = grid / nq;
+  if (n_splits > (unsigned)ctx->sm_count / nq) n_splits = (unsigned)ctx->sm_count / nq;
   if (n_splits > (unsigned)MG_MAX_SPLITS) n_splits = MG_MAX_SPLITS;
-  if (n_splits < 1) return KS_OK;
+  if (n_splits < 1 || nq > 48) return KS_OK;
   if (d->n_layers < 1 || d->n_layers > 128) return KS_OK;
 
-  const unsigned shapes_bytes = (unsigned)((PH_KINDS * sizeof(MegaPhase) + 15u) & ~15u);
+  const int stages = 3;
+  const unsigned shapes_bytes = (unsigned)((PH_PER_LAYER * sizeof(MegaShape) + 15u) & ~15u);
   const unsigned tables_bytes = (unsigned)((shapes_bytes + d->n_layers * sizeof(MegaLayer) + 15u) & ~15u);
   unsigned maxcols = H > F ? H : F;
   if (qn > maxcols) maxcols = qn;
-  unsigned x_bytes = (maxcols / 64u) * 256u;
-  if (mg_att_bytes(hd) > x_bytes) x_bytes = mg_att_bytes(hd);
+  unsigned x_bytes = (maxcols / 64u) * Q4K_XTOK * 4u;
+  const unsigned att = mg_att_bytes(hd);
+  if (att > x_bytes) x_bytes = att;
+  const unsigned budget = (unsigned)ctx->smem_optin;
+  const MegaSmem fixed = mg_smem(x_bytes, 0, stages, tables_bytes);
+  if (fixed.total + 8u * stages * 4u * KS_Q4K_BLOCK_BYTES * 2u > budget) return KS_OK;
+  unsigned slot_cap = (budget - fixed.total) / (8u * stages);
+  slot_cap &= ~15u;
+  if (slot_cap > 8192u) slot_cap = 8192u;
+  // Blocks per column segment.  A block's items (its groups x column segments) are shared by its 8
+  // warps, so more segments shorten the longest warp until the per-item overhead (measured: a little more
+  // than one unit's worth of time) wins; segments hold an even number of blocks (8 lanes per row) and must fit a ring slot.
+  const unsigned grid = (unsigned)ctx->sm_count;
+  auto pick_seg = [&](unsigned cols, unsigned mats, unsigned total_groups, bool oct = false) {
+    const unsigned nb = cols / 256u;
+    const unsigned n_g = oct ? ((total_groups + 7) / 8 + grid - 1) / grid * 8 : (total_groups + grid - 1) / grid;
+    unsigned best = 0;
+    float best_cost = 0.f;
+    for (unsigned C = 1; C <= nb; C++) {
+      if (nb % C) continue;
+      const unsigned sb = nb / C;
+      if (sb % 2 || 4u * mats * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
+      const float cost = (float)((n_g * C + 7u) / 8u) * ((float)(sb * mats) * 0.5f + 1.2f);
+      if (!best || cost < best_cost) {
+        best = sb;
+        best_cost = cost;
+      }
+    }
+    return best;
+  };
+  const unsigned g_qkv = (qn + 3) / 4 + 2 * ((kvn + 3) / 4), g_h = (H + 3) / 4, g_f = (F + 3) / 4;
+  if (g_qkv > 64u * grid || g_f > 64u * grid || g_h > 64u * grid) return KS_OK;  // a block finishes at most 64 groups per phase
+  const unsigned sb_h = pick_seg(H, 1, g_qkv), sb_q = pick_seg(qn, 1, g_h), sb_f = pick_seg(F, 1, g_h);
+  // gate-up: gate and up rows of a group in one item (x read once for both) when they fit a slot, else as two items
+  unsigned sb_h2 = pick_seg(H, 2, g_f, true);
+  bool gu_split = false;
+  if (!sb_h2) {
+    gu_split = true;
+    const unsigned n_g = ((g_f + 7) / 8 + grid - 1) / grid * 8, nb = H / 256u;
+    float best_cost = 0.f;
+    for (unsigned C = 1; C <= nb; C++) {
+      if (nb % C) continue;
+      const unsigned sb = nb / C;
+      if (sb % 2 || 4u * sb * KS_Q4K_BLOCK_BYTES > slot_cap || n_g * C > (unsigned)MG_MAX_P) continue;
+      const float cost = (float)((n_g * C * 2u + 7u) / 8u) * ((float)sb * 0.5f + 1.2f);
+      if (!sb_h2 || cost < best_cost) {
+        sb_h2 = sb;
+        best_cost = cost;
+      }
+    }
+  }
+  if (!sb_h || !sb_h2 || !sb_q || !sb_f) return KS_OK;
+  unsigned slot_bytes = 0;
+  auto upd = [&](unsigned sb, unsigned mats) {
+    const unsigned b = 4u * mats * sb * KS_Q4K_BLOCK_BYTES;
+    if (b > slot_bytes) slot_bytes = b;
+  };
+  upd(sb_h, 1); upd(sb_h2, gu_split ? 1 : 2); upd(sb_q, 1); upd(sb_f, 1);
 
+  {  // every warp's items of one layer must fit its table
+    auto per_warp = [&](unsigned total_groups, unsigned ncs) { return ((total_groups + grid - 1) / grid * ncs + 7u) / 8u; };
+    const unsigned worst = per_warp(g_qkv, H / 256 / sb_h) + per_warp(g_h, qn / 256 / sb_q) +
+                           (((g_f + 7) / 8 + grid - 1) / grid * 8 * (H / 256 / sb_h2) * (gu_split ? 2u : 1u) + 7u) / 8u +
+                           per_warp(g_h, F / 256 / sb_f);
+    if (worst > (unsigned)MG_MAX_ENT) return KS_OK;
+  }
   std::vector<unsigned char> tab(tables_bytes, 0);
-  MegaPhase* ph = reinterpret_cast<MegaPhase*>(tab.data());
+  MegaShape* sh = reinterpret_cast<MegaShape*>(tab.data());
   MegaLayer* ly = reinterpret_cast<MegaLayer*>(tab.data() + shapes_bytes);
-  auto set_phase = [&](MegaPhase& p, unsigned n_seg, const unsigned* rows, unsigned mats, unsigned widx, unsigned cols) {
-    p.n_seg = n_seg;
-    p.mats = mats;
-    p.seg_start[0] = 0;
-    for (unsigned s = 0; s < n_seg; s++) p.seg_start[s + 1] = p.seg_start[s] + rows[s];
-    p.widx = widx;
+  auto set_rows = [](MegaShape& p, unsigned cols, unsigned sb) {
     p.cols = cols;
     p.row_bytes = cols / 256u * KS_Q4K_BLOCK_BYTES;
-  };
-  const unsigned r_qkv[3] = {qn, kvn, kvn}, r_h[1] = {H}, r_f[1] = {F};
-  set_phase(ph[PH_QKV], 3, r_qkv, 1, 0, H);
-  set_phase(ph[PH_OPROJ], 1, r_h, 1, 3, qn);
-  set_phase(ph[PH_GATEUP], 1, r_f, 2, 4, H);
-  set_phase(ph[PH_DOWN], 1, r_h, 1, 6, F);
-  for (int k = 0; k < PH_KINDS; k++)
-    if (ph[k].seg_start[ph[k].n_seg] % 4u || ph[k].seg_start[1] % 4u) return KS_OK;
-
-  // ring: as many slots as give every phase room for at least one 4-row group (x 2 matrices for gate-up)
-  const unsigned budget = (unsigned)ctx->smem_optin;
-  unsigned need = 0;
-  for (int k = 0; k < PH_KINDS; k++) need = std::max(need, 4u * ph[k].mats * ph[k].row_bytes);
-  int n_slots = 8;
-  if (const char* e = getenv("KSEARCH_MEGA_SLOTS")) n_slots = atoi(e);
-  if (n_slots > MG_MAXSLOTS) n_slots = MG_MAXSLOTS;
-  unsigned slot_bytes = 0;
-  for (; n_slots >= 2; n_slots--) {
-    const MegaSmem fixed = mg_smem(x_bytes, H, 0, n_slots, tables_bytes);
-    if (fixed.total >= budget) continue;
-    slot_bytes = ((budget - fixed.total) / (unsigned)n_slots) & ~127u;
-    if (slot_bytes >= need) break;
-  }
-  if (n_slots < 2 || slot_bytes < need) return KS_OK;
-
-  // rows of a phase owned by the fullest block
-  auto max_rows = [&](const MegaPhase& p) {
-    const unsigned half = p.seg_start[p.n_seg] / 2u;
-    unsigned m = 0;
-    for (unsigned b = 0; b < grid; b++) {
-      const unsigned lo = (unsigned)(((unsigned long long)b * half) / grid) * 2u, hi = (unsigned)(((unsigned long long)(b + 1) * half) / grid) * 2u;
-      m = std::max(m, hi - lo);
+    p.seg_blocks = sb;
+    p.n_cseg = cols / 256u / sb;
+    unsigned g0 = 0;
+    for (int s = 0; s < p.n_seg; s++) {
+      p.grp_start[s] = g0;
+      g0 += (p.rows[s] + 3u) / 4u;
     }
-    return m;
+    p.grp_start[p.n_seg] = g0;
   };
-  // Column segments per phase: a lane owns one 64-weight unit of a segment, so a segment has at most 32 units;
-  // the units of a row are split evenly over as few segments as that allows.
-  unsigned total_pieces = 0;
-  for (int k = 0; k < PH_KINDS; k++) {
-    MegaPhase& p = ph[k];
-    const unsigned R = max_rows(p);
-    if (R > (unsigned)MG_MAXROWS || R == 0) return KS_OK;
-    // pieces: as few as fit the slot, of equal size
-    unsigned cap_rows = (slot_bytes / (p.mats * p.row_bytes)) & ~3u;
-    if (cap_rows > 64u) cap_rows = 64u;
-    const unsigned n_pc = (R + cap_rows - 1u) / cap_rows;
-    p.piece_rows = std::min(cap_rows, (((R + n_pc - 1u) / n_pc) + 3u) & ~3u);
-    const unsigned U = p.cols / 64u;
-    p.n_cseg = (U + 31u) / 32u;
-    if (p.n_cseg > (unsigned)MG_MAXC || U % p.n_cseg) return KS_OK;
-    p.seg_units = U / p.n_cseg;
-    total_pieces += p.n_seg + (R + p.piece_rows - 1u) / p.piece_rows + 1u;
-  }
-  if (total_pieces > (unsigned)MG_MAXPIECE) return KS_OK;
-
+  sh[PH_QKV].type = MG_MATVEC; sh[PH_QKV].n_seg = 3;
+  sh[PH_QKV].rows[0] = qn; sh[PH_QKV].rows[1] = kvn; sh[PH_QKV].rows[2] = kvn;
+  set_rows(sh[PH_QKV], H, sb_h);
+  sh[PH_ATTN].type = MG_ATTN; sh[PH_ATTN].n_seg = 1; sh[PH_ATTN].n_cseg = 1;
+  sh[PH_OPROJ].type = MG_MATVEC; sh[PH_OPROJ].n_seg = 1; sh[PH_OPROJ].rows[0] = H;
+  set_rows(sh[PH_OPROJ], qn, sb_q);
+  sh[PH_GATEUP].type = MG_GATE_UP; sh[PH_GATEUP].n_seg = 1; sh[PH_GATEUP].rows[0] = F; sh[PH_GATEUP].oct = 1; sh[PH_GATEUP].split = gu_split ? 1 : 0;
+  set_rows(sh[PH_GATEUP], H, sb_h2);
+  sh[PH_DOWN].type = MG_MATVEC; sh[PH_DOWN].n_seg = 1; sh[PH_DOWN].rows[0] = H;
+  set_rows(sh[PH_DOWN], F, sb_f);
   for (int l = 0; l < d->n_layers; l++) {
     const ks_mega_layer& L = layers[l];
     MegaLayer& o = ly[l];
@@ -1281,26 +1394,18 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
 
   ks_mega* mg = new ks_mega();
   cudaSetDevice(ctx->device);
-  const size_t prof_n = (size_t)2 * d->n_layers * PF_PER_LAYER * PF_STAMPS;
-  // tagged vectors, two of each: yd, yo [H], qkv [qn + 2 kvn], ox [qn], ff [F], rec [n_q * n_splits * (hd + 2)]
-  const size_t n_rec = (size_t)nq * n_splits * (hd + 2);
-  auto up2 = [](size_t n) { return (n + 1) & ~size_t(1); };   // keep every vector 16-byte aligned
-  const size_t ll_words = 2 * (up2(H) + up2(H) + up2(qn + 2 * kvn) + up2(qn) + up2(F) + up2(n_rec));
-  mg->ll_bytes = ll_words * sizeof(u64);
-  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 256) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_prof, prof_n * sizeof(long long)) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_prof_all, (size_t)grid * d->n_layers * PF_PER_LAYER * 8 * sizeof(long long)) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_ll, mg->ll_bytes) != cudaSuccess) {
+  const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
+  if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 512 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
-  const unsigned epoch0[1] = {1u};
   cudaError_t e = cudaMemcpyAsync(mg->d_tables, tab.data(), tables_bytes, cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 256, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(mg->d_sync, epoch0, sizeof epoch0, cudaMemcpyHostToDevice, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_ll, 0, mg->ll_bytes, ctx->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, prof_n * sizeof(long long), ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab and epoch0 are locals
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 512 + 16 * (size_t)ctx->sm_count, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_fx, 0, ((size_t)qn / 64 + (size_t)F / 64) * 256, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
   if (e != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: table upload failed: %s", cudaGetErrorString(e));
@@ -1309,36 +1414,29 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.tables = mg->d_tables;
   a.tables_bytes = tables_bytes;
   a.n_layers = d->n_layers;
-  a.n_slots = n_slots;
+  a.stages = stages;
   a.slot_bytes = slot_bytes;
   a.x_bytes = x_bytes;
   a.n_q = nq; a.n_kv = nkv; a.hd = hd; a.n_splits = n_splits;
-  a.split_from = MG_NW * MG_AB;  // one batch of rows per warp
-  if (const char* e2 = getenv("KSEARCH_MEGA_SPLIT_FROM")) a.split_from = (unsigned)atoi(e2);
   a.eps = d->eps; a.attn_scale = d->attn_scale;
   a.rope = d->rope; a.pos = d->pos;
-  a.x_in = d->x_a;
-  a.resid_out = d->x_b;
-  a.y_out = d->yb;
-  {
-    u64* p = mg->d_ll;
-    auto take = [&](size_t n) { u64* r = p; p += up2(n); return r; };
-    a.ll_yd0 = take(H); a.ll_yd1 = take(H);
-    a.ll_yo0 = take(H); a.ll_yo1 = take(H);
-    a.ll_qkv0 = take(qn + 2 * kvn); a.ll_qkv1 = take(qn + 2 * kvn);
-    a.ll_ox0 = take(qn); a.ll_ox1 = take(qn);
-    a.ll_ff0 = take(F); a.ll_ff1 = take(F);
-    a.ll_rec0 = take(n_rec); a.ll_rec1 = take(n_rec);
-  }
-  a.epoch = mg->d_sync;
+  a.x_a = d->x_a; a.x_b = d->x_b;
+  a.yb = d->yb; a.q = d->q; a.k = d->k; a.v = d->v;
+  a.ox = mg->d_fx;
+  a.ffx = mg->d_fx + (size_t)qn / 64 * 256;
+  a.att_tmp = d->att_tmp;
+  a.bar = mg->d_sync;
+  a.att_cnt = mg->d_sync + 64;
+  a.nsum = reinterpret_cast<float4*>(mg->d_sync + 128);
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
-  a.poll_limit = 1u << 21;  // a second or two of polling at most
+  a.poll_limit = 1u << 21;
   a.test_stall = 0;
-  a.prof = getenv("KSEARCH_PROFILE") ? mg->d_prof : nullptr;
+  a.prof = mg->d_prof;
   mg->grid = grid;
-  mg->smem = mg_smem(x_bytes, H, slot_bytes, n_slots, tables_bytes).total;
+  mg->smem = mg_smem(x_bytes, slot_bytes, stages, tables_bytes).total;
+  mg->G = (int)G;
   mg->dpl = (int)(hd / 32);
-  mg->pc = (int)((H / 4u + MG_THREADS - 1u) / MG_THREADS);
+  mg->pc = H <= 2048 ? 2 : 4;
   mg->residual = d->x_b;
   *out = mg;
   return KS_OK;

@@ -110,9 +110,16 @@ struct ks_model {
   std::map<uint64_t, size_t> graph_nodes;
   std::vector<void*> owned;
   std::vector<char> tok_src;  // per slot: which half of the ping-pong holds its next input id
-  // one persistent decode kernel per slot (nullptr entry: shape not covered, tried once)
-  std::map<int, ks_mega*> mega;
+  // one persistent decode kernel per slot (both null: shape not covered, tried once); decode_kernel
+  // picks which of the two is built: 1 = grid barriers (ks_mega.cu), 2 = tagged-word dataflow (ks_flow.cu)
+  struct Mega {
+    ks_mega* bar = nullptr;
+    ks_flow* flow = nullptr;
+    explicit operator bool() const { return bar || flow; }
+  };
+  std::map<int, Mega> mega;
   bool use_mega = false;
+  int decode_kernel = 1;
   // prompt chunks (ks_model_prefill): KS_PREFILL_CHUNK rows of activations of their own
   void *cx = nullptr, *cxb = nullptr, *cx2 = nullptr, *cq = nullptr, *ck = nullptr, *cv = nullptr, *co = nullptr, *cff = nullptr;
   float* ctok = nullptr;
@@ -338,8 +345,10 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
   return ks_after_launch(c, "collect");
 }
 
+int mega_reset(ks_ctx* c, const ks_model::Mega& mg) { return mg.bar ? ks_mega_reset(c, mg.bar) : ks_flow_reset(c, mg.flow); }
+
 // One slot's token with every layer inside one persistent kernel; embedding before, head after.
-int enqueue_forward_mega(ks_model* m, ks_mega* mg, int first, int src, bool want_logits) {
+int enqueue_forward_mega(ks_model* m, const ks_model::Mega& mg, int first, int src, bool want_logits) {
   ks_ctx* c = m->ctx;
   const ks_model_config& g = m->cfg;
   const size_t H = g.hidden;
@@ -352,11 +361,11 @@ int enqueue_forward_mega(ks_model* m, ks_mega* mg, int first, int src, bool want
   int* pos = m->pos + first;
   int rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, 1, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, KS_F32, cur))) return rc;
-  if ((rc = ks_mega_launch(c, mg))) return rc;
+  if ((rc = mg.bar ? ks_mega_launch(c, mg.bar) : ks_flow_launch(c, mg.flow))) return rc;
   KS_LAUNCH(c, (end_token_kernel), 1, 32, 0, 1, pos);
   if ((rc = ks_after_launch(c, "end_token"))) return rc;
   if (!want_logits) return KS_OK;
-  float* res = ks_mega_residual(mg);
+  float* res = mg.bar ? ks_mega_residual(mg.bar) : ks_flow_residual(mg.flow);
   if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, 1, g.eps, KS_F32, yb, m->layers[g.n_layers - 1].post_ffw_norm.dptr, res,
                                                m->output_norm.dptr, res, xn)))
     return rc;
@@ -369,8 +378,8 @@ int enqueue_forward_mega(ks_model* m, ks_mega* mg, int first, int src, bool want
 }
 
 // The persistent kernel of slot `first`, built on first use (outside any stream capture).
-int get_mega(ks_model* m, int first, ks_mega** out) {
-  *out = nullptr;
+int get_mega(ks_model* m, int first, ks_model::Mega* out) {
+  *out = ks_model::Mega();
   if (!m->use_mega) return KS_OK;
   auto it = m->mega.find(first);
   if (it != m->mega.end()) {
@@ -406,8 +415,8 @@ int get_mega(ks_model* m, int first, ks_mega** out) {
     o.kv_k = m->kv_k[l] + (size_t)first * m->slot_stride;
     o.kv_v = m->kv_v[l] + (size_t)first * m->slot_stride;
   }
-  ks_mega* mg = nullptr;
-  int rc = ks_mega_create(m->ctx, &d, ls.data(), &mg);
+  ks_model::Mega mg;
+  int rc = m->decode_kernel == 2 ? ks_flow_create(m->ctx, &d, ls.data(), &mg.flow) : ks_mega_create(m->ctx, &d, ls.data(), &mg.bar);
   if (rc) return rc;
   m->mega[first] = mg;
   *out = mg;
@@ -420,7 +429,7 @@ int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
   const uint64_t key = ((uint64_t)first << 32) | ((uint64_t)n << 8) | ((uint64_t)src << 1) | (want_logits ? 1 : 0);
   auto it = m->graphs.find(key);
   if (it == m->graphs.end()) {
-    ks_mega* mg = nullptr;
+    ks_model::Mega mg;
     if (n == 1) {
       int rcm = get_mega(m, first, &mg);
       if (rcm) return rcm;
@@ -561,10 +570,12 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   m->tok_src.assign(g.n_slots, 0);
   const size_t S = g.n_slots;
   m->fused = ks_matvec_can_fuse_pro(KS_Q4K, H) && !getenv("KSEARCH_UNFUSED");
-  // Single-slot steps run all layers inside one persistent kernel; KSEARCH_DECODE_KERNEL=0 keeps one
-  // launch per op (the path every multi-slot step takes anyway).
+  // Single-slot steps run all layers inside one persistent kernel.  KSEARCH_DECODE_KERNEL: 0 keeps one
+  // launch per op (the path every multi-slot step takes anyway), 1 = the kernel whose phases meet at grid
+  // barriers (default), 2 = the kernel whose blocks exchange tagged words instead of meeting.
   const char* dk = getenv("KSEARCH_DECODE_KERNEL");
   m->use_mega = m->fused && g.act == KS_F32 && !(dk && dk[0] == '0');
+  m->decode_kernel = dk && dk[0] == '2' ? 2 : 1;
   ok = ok && dev_alloc(m, &m->xb, S * H * ab) == KS_OK && dev_alloc(m, &m->xn, S * H * ab) == KS_OK;
   ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
        dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&
@@ -650,7 +661,10 @@ void ks_model_destroy(ks_model* m) {
   cudaSetDevice(m->ctx->device);
   cudaStreamSynchronize(m->ctx->stream);
   for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
-  for (auto& kv : m->mega) ks_mega_destroy(kv.second);
+  for (auto& kv : m->mega) {
+    if (kv.second.bar) ks_mega_destroy(kv.second.bar);
+    if (kv.second.flow) ks_flow_destroy(kv.second.flow);
+  }
   for (void* p : m->owned) cudaFree(p);
   if (m->host_tok) cudaFreeHost(m->host_tok);
   delete m;
@@ -735,7 +749,7 @@ int ks_model_slot_reset(ks_model* m, int slot) {
   m->occupied[slot] = 1;
   auto it = m->mega.find(slot);
   if (it != m->mega.end() && it->second) {
-    const int rc = ks_mega_reset(c, it->second);
+    const int rc = mega_reset(c, it->second);
     if (rc) return rc;
   }
   return ks_after_launch(c, "slot_reset");
@@ -809,7 +823,7 @@ static int check_device_status(ks_model* m, const unsigned* status, int first, i
     m->seq_len[s] = m->seq_len[s] >= steps ? m->seq_len[s] - steps : 0;
     KS_LAUNCH(c, (set_state_kernel), 1, 1, 0, s, m->seq_len[s], m->pos);
     auto it = m->mega.find(s);
-    if (it != m->mega.end() && it->second) ks_mega_reset(c, it->second);
+    if (it != m->mega.end() && it->second) mega_reset(c, it->second);
   }
   cudaStreamSynchronize(c->stream);
   return ks_fail(c, KS_ERR_TIMEOUT, "a device-side wait gave up during decode (status word 0x%x); the slots were rewound", flag);
@@ -941,13 +955,14 @@ const void* ks_model_debug_ptr(const ks_model* m, int which, int slot) {
   const size_t ab = ks_act_bytes((ks_dtype)m->cfg.act);
   if (which == 0) return (const char*)m->x + (size_t)slot * m->cfg.hidden * ab;
   if (which == 1) return (const char*)m->logits + (size_t)slot * m->cfg.vocab * ab;
-  if (which == 2) {  // phase clock stamps of the persistent decode kernel: [2][n_layers][5][8] int64
-    auto it = m->mega.find(slot);
-    return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof(it->second);
+  if (which == 2) {  // phase stamps of the persistent decode kernel, first and last block: [2][n_layers][5][8] int64
+    auto it = m->mega.find(slot);  // (clock64 ticks from the barrier kernel, globaltimer ns from the dataflow one)
+    if (it == m->mega.end() || !it->second) return nullptr;
+    return it->second.bar ? (const void*)ks_mega_prof(it->second.bar) : (const void*)ks_flow_prof(it->second.flow);
   }
-  if (which == 3) {  // the same for every block: [grid][n_layers][5][2] int64 (phase entered, rows stored)
+  if (which == 3) {  // every block's stamps [grid][n_layers][5][8] int64; the dataflow kernel only
     auto it = m->mega.find(slot);
-    return it == m->mega.end() || !it->second ? nullptr : (const void*)ks_mega_prof_all(it->second);
+    return it == m->mega.end() || !it->second.flow ? nullptr : (const void*)ks_flow_prof_all(it->second.flow);
   }
   return nullptr;
 }
@@ -960,11 +975,12 @@ int ks_model_debug_set(ks_model* m, int slot, int what, unsigned value) {
   if (!m) return KS_ERR_INVALID;
   ks_ctx* c = m->ctx;
   if (slot < 0 || slot >= m->cfg.n_slots) return ks_fail(c, KS_ERR_STATE, "bad SlotId");
-  ks_mega* mg = nullptr;
+  ks_model::Mega mg;
   int rc = get_mega(m, slot, &mg);
   if (rc) return rc;
   if (!mg) return ks_fail(c, KS_ERR_UNSUPPORTED, "this model shape does not use the persistent decode kernel");
-  if ((rc = ks_mega_set(mg, what, value))) return ks_fail(c, rc, "debug_set: unknown knob %d", what);
+  if ((rc = mg.bar ? ks_mega_set(mg.bar, what, value) : ks_flow_set(mg.flow, what, value)))
+    return ks_fail(c, rc, "debug_set: unknown knob %d", what);
   cudaStreamSynchronize(c->stream);
   for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second);
   m->graphs.clear();

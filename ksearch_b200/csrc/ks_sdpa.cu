@@ -52,6 +52,50 @@ __device__ __forceinline__ void load_row(const uint8_t* row, int lane, float (&o
     out[BPL + 2 * w + 1] = (float)((int)(v >> 12) - 8) * d;
   }
 }
+// The same DPL values as plain nibbles (0..15 as floats) and the block's scale: the -8 offset and the scale are
+// applied once per (row, head) by the caller instead of once per value.
+template <int DPL>
+__device__ __forceinline__ float load_row_raw(const uint8_t* row, int lane, float (&out)[DPL]) {
+  constexpr int BPL = DPL / 2;
+  constexpr int LPB = 16 / BPL;
+  const uint8_t* blk = row + (lane / LPB) * KS_Q40_BLOCK_BYTES;
+  const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(blk)));
+  const unsigned short* qs = reinterpret_cast<const unsigned short*>(blk + 2 + (lane % LPB) * BPL);
+#pragma unroll
+  for (int w = 0; w < BPL / 2; w++) {
+    const unsigned v = qs[w];
+    out[2 * w] = (float)(v & 0xF);
+    out[2 * w + 1] = (float)((v >> 8) & 0xF);
+    out[BPL + 2 * w] = (float)((v >> 4) & 0xF);
+    out[BPL + 2 * w + 1] = (float)(v >> 12);
+  }
+  return d;
+}
+// Sum over the warp of G values per lane; every lane gets all G sums.  G == 4: the lanes first trade halves
+// (each keeps two, then one, of the four values), so 10 shuffles do what 20 would.
+template <int G>
+__device__ __forceinline__ void warp_sum_g(float (&s)[G], int lane) {
+  if (G == 4) {
+    const bool hi = (lane & 16) != 0, h8 = (lane & 8) != 0;
+    float k0 = hi ? s[2] : s[0], k1 = hi ? s[3] : s[1];
+    const float t0 = hi ? s[0] : s[2], t1 = hi ? s[1] : s[3];
+    k0 += __shfl_xor_sync(0xffffffffu, t0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, t1, 16);
+    float k = h8 ? k1 : k0;
+    const float t = h8 ? k0 : k1;
+    k += __shfl_xor_sync(0xffffffffu, t, 8);
+    k += __shfl_xor_sync(0xffffffffu, k, 4);
+    k += __shfl_xor_sync(0xffffffffu, k, 2);
+    k += __shfl_xor_sync(0xffffffffu, k, 1);
+#pragma unroll
+    for (int g = 0; g < G; g++) s[g] = __shfl_sync(0xffffffffu, k, 8 * (g & 1) + 16 * (g >> 1));
+  } else {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+      for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+  }
+}
 // Dimension index (within the head) of this lane's j-th value.
 template <int DPL>
 __device__ __forceinline__ int lane_dim(int lane, int j) {
@@ -93,15 +137,21 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
   const uint8_t* Vs = V + (size_t)slot * slot_stride;
   __shared__ __align__(16) uint8_t ring[ASYNC ? kWarps * kRing * 2 * ROWB : 16];
 
-  float qr[G][DPL], o[G][DPL], m[G], l[G];
+  // qs8[g] = 8 * (sum of this lane's q values): the -8 of Q4_0 leaves the dot product as one term per (row, head);
+  // c[g] gathers sum(e * d) the same way for V, and is taken off o at the end
+  float qr[G][DPL], o[G][DPL], m[G], l[G], qs8[G], c[G];
 #pragma unroll
   for (int g = 0; g < G; g++) {
     const size_t qb = ((size_t)slot * n_q + head0 + g) * HD;
+    float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < DPL; j++) {
       qr[g][j] = ld_act<T>(q, qb + lane_dim<DPL>(lane, j)) * scale;
+      sum += qr[g][j];
       o[g][j] = 0.0f;
     }
+    qs8[g] = 8.0f * sum;
+    c[g] = 0.0f;
     m[g] = kNegInit;
     l[g] = 0.0f;
   }
@@ -109,33 +159,33 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
   // one position: scores of the G heads against the K row, then the online-softmax update with the V row
   auto step = [&](const uint8_t* krow, const uint8_t* vrow) {
     float kv[DPL];
-    load_row<DPL>(krow, lane, kv);
+    const float dk = load_row_raw<DPL>(krow, lane, kv);
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; g++) {
-      float a = 0.0f;
+      float a = -qs8[g];
 #pragma unroll
       for (int j = 0; j < DPL; j++) a = fmaf(qr[g][j], kv[j], a);
-      s[g] = a;
+      s[g] = a * dk;
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-      for (int g = 0; g < G; g++) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
-    load_row<DPL>(vrow, lane, kv);
+    warp_sum_g<G>(s, lane);
+    const float dv = load_row_raw<DPL>(vrow, lane, kv);
 #pragma unroll
     for (int g = 0; g < G; g++) {
       if (s[g] > m[g]) {  // a new maximum (the same in every lane): rescale what was gathered so far
         const float alpha = __expf(m[g] - s[g]);
         l[g] *= alpha;
+        c[g] *= alpha;
 #pragma unroll
         for (int j = 0; j < DPL; j++) o[g][j] *= alpha;
         m[g] = s[g];
       }
       const float e = __expf(s[g] - m[g]);
       l[g] += e;
+      const float ed = e * dv;
+      c[g] += ed;
 #pragma unroll
-      for (int j = 0; j < DPL; j++) o[g][j] = fmaf(e, kv[j], o[g][j]);
+      for (int j = 0; j < DPL; j++) o[g][j] = fmaf(ed, kv[j], o[g][j]);
     }
   };
 
@@ -171,6 +221,11 @@ sdpa_part_kernel(unsigned n_q, unsigned n_kv, float scale, const T* q, const uin
       step(Ks + row, Vs + row);
     }
   }
+
+#pragma unroll
+  for (int g = 0; g < G; g++)
+#pragma unroll
+    for (int j = 0; j < DPL; j++) o[g][j] = fmaf(-8.0f, c[g], o[g][j]);
 
   // merge the warps of this block: warp w leaves (m, l, O) in shared memory, warp 0 folds them in order
   __shared__ float sm_ml[kWarps][G][2];

@@ -29,7 +29,7 @@ def full_model(oracle):
     cpu.close()
 
 
-@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+@pytest.mark.parametrize("decode_kernel", ["1", "2", "0"])
 def test_full_e2b_model_matches_cpu_decoder(full_model, oracle, monkeypatch, decode_kernel):
     monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
     cfg, T, cpu = full_model["cfg"], full_model["T"], full_model["cpu"]
@@ -51,7 +51,7 @@ def test_full_e2b_model_matches_cpu_decoder(full_model, oracle, monkeypatch, dec
     print(f"[config 3, kernel={decode_kernel}] teacher-forced logits over {N_TF} tokens: worst max error "
           f"{worst_max:.2e}, worst rms error {worst_rms:.2e} (relative to the largest logit)")
     assert worst_max <= 1e-3 and worst_rms <= 1e-4
-    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel != "0")
     prompt = synth.token_ids(SEED, "prompt", N_PROMPT, cfg.vocab)
     out, st = model.generate_timed(prompt, N_NEW)
     assert st.prefill_tokens == N_PROMPT - 1 and st.decode_tokens == N_NEW

@@ -150,12 +150,21 @@ def test_model_with_dependent_launch_matches(oracle):
     assert outs[0] == outs[1]
 
 
+def _pick_kernel(monkeypatch, decode_kernel):
+    if decode_kernel is None:
+        monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    else:
+        monkeypatch.setenv("KSEARCH_DECODE_KERNEL", decode_kernel)
+
+
+@pytest.mark.parametrize("decode_kernel", [None, "2"])
 @pytest.mark.parametrize("n_kv", [1, 2])
-def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv):
-    """Every layer of a single-slot step runs inside one persistent kernel (grid barriers between
-    phases) unless KSEARCH_DECODE_KERNEL=0.  Same parity bar as the launch-per-op path."""
+def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv, decode_kernel):
+    """Every layer of a single-slot step runs inside one persistent kernel unless KSEARCH_DECODE_KERNEL=0:
+    by default the one whose phases meet at grid barriers, with =2 the one whose blocks pass tagged words.
+    Same parity bar as the launch-per-op path."""
     from ksearch_b200 import CudaContext
-    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    _pick_kernel(monkeypatch, decode_kernel)
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=80, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=21, keep=True)
@@ -175,17 +184,18 @@ def test_persistent_decode_kernel_matches_cpu_decoder(oracle, monkeypatch, n_kv)
     c.close()
 
 
-def test_persistent_kernel_long_context(oracle, monkeypatch):
+@pytest.mark.parametrize("decode_kernel", [None, "2"])
+def test_persistent_kernel_long_context(oracle, monkeypatch, decode_kernel):
     """300 positions: every attention split in use, several positions per warp, the newest position
     moving through the splits."""
     from ksearch_b200 import CudaContext
-    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    _pick_kernel(monkeypatch, decode_kernel)
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=320, n_kv=2)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=23, keep=True)
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
-    model.debug_set(model.SPLIT_FROM, 8)     # split contexts from 9 positions on (the default keeps short ones in one block)
+    model.debug_set(model.SPLIT_FROM, 8)     # dataflow kernel: split contexts from 9 positions on (its default keeps short ones in one block)
     _teacher_forced(model, cpu, synth.token_ids(23, "tf", 300, cfg.vocab))
     assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None
     cpu.close()
@@ -193,13 +203,15 @@ def test_persistent_kernel_long_context(oracle, monkeypatch):
     c.close()
 
 
-def test_device_wait_gives_up_and_recovers(oracle, monkeypatch):
-    """A bounded device-side wait that runs out: one stage of the persistent kernel is told to wait for a
-    value nobody writes, with a limit of 2000 polls.  Nothing faults or hangs: every block stops waiting
-    within microseconds, the kernel ends, the blocking calls report KS_ERR_TIMEOUT and rewind the slot, and
-    after a slot reset the next tokens match the CPU decoder again."""
+@pytest.mark.parametrize("decode_kernel", [None, "2"])
+def test_device_wait_gives_up_and_recovers(oracle, monkeypatch, decode_kernel):
+    """A bounded device-side wait that runs out: one wait of the persistent kernel (a grid barrier of the
+    default kernel, a tag poll of the dataflow kernel) is told to wait for something nobody writes, with a
+    limit of 2000 polls.  Nothing faults or hangs: every block stops waiting within microseconds, the
+    kernel ends, the blocking calls report KS_ERR_TIMEOUT and rewind the slot, and after a slot reset the
+    next tokens match the CPU decoder again."""
     from ksearch_b200 import CudaContext, _lib
-    monkeypatch.delenv("KSEARCH_DECODE_KERNEL", raising=False)
+    _pick_kernel(monkeypatch, decode_kernel)
     c = CudaContext(0, flags=1)
     cfg = ksm.tiny_config(max_seq=48)
     model, T = ksm.GemmaCudaModel.synthetic(c, cfg, seed=27, keep=True)
@@ -227,7 +239,7 @@ def test_device_wait_gives_up_and_recovers(oracle, monkeypatch):
     c.close()
 
 
-@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+@pytest.mark.parametrize("decode_kernel", ["1", "2", "0"])
 def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     """Two layers with the E4B row and column counts (hidden 2560, GeGLU 10240, 8 q / 2 kv heads of
     256): ten blocks per row, gate and up rows too long for one ring slot, four 4-element chunks per
@@ -240,7 +252,7 @@ def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
     _teacher_forced(model, cpu, synth.token_ids(24, "tf", 40, cfg.vocab))
-    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel != "0")
     prompt = synth.token_ids(24, "prompt", 6, cfg.vocab)
     out, _ = model.generate_timed(prompt, 12)
     equal, ties = oracle.compare_streams(out, cpu, prompt)
@@ -250,7 +262,7 @@ def test_e4b_like_shapes(oracle, monkeypatch, decode_kernel):
     c.close()
 
 
-@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+@pytest.mark.parametrize("decode_kernel", ["1", "2", "0"])
 def test_e2b_like_shapes(oracle, monkeypatch, decode_kernel):
     """Two layers with the E2B row and column counts (hidden 1536, GeGLU 6144, 8 q / 1 kv heads of 256):
     the shapes of the benchmarked model -- six blocks per row, eight query heads on one KV head, two
@@ -264,12 +276,12 @@ def test_e2b_like_shapes(oracle, monkeypatch, decode_kernel):
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
     _teacher_forced(model, cpu, synth.token_ids(25, "tf", 150, cfg.vocab))   # past 128 positions: every split in use
-    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel == "1")
+    assert (model.lib.ks_model_debug_ptr(model.h, 2, 0) is not None) == (decode_kernel != "0")
     prompt = synth.token_ids(25, "prompt", 6, cfg.vocab)
     out, _ = model.generate_timed(prompt, 24)
     equal, ties = oracle.compare_streams(out, cpu, prompt)
     assert equal + ties == 24 and ties <= 1
-    if decode_kernel == "1":     # the same shapes with the context split across blocks and merged
+    if decode_kernel == "2":     # the same shapes with the context split across blocks and merged
         model.debug_set(model.SPLIT_FROM, 8)
         _teacher_forced(model, cpu, synth.token_ids(25, "tf2", 70, cfg.vocab))
     cpu.close()
@@ -292,7 +304,7 @@ def _nibble_diffs(a, b, cfg):
 
 
 @pytest.mark.parametrize("shape", ["tiny", "e2b_rows"])
-@pytest.mark.parametrize("decode_kernel", ["1", "0"])
+@pytest.mark.parametrize("decode_kernel", ["1", "2", "0"])
 def test_logits_tight_when_kv_bytes_agree(oracle, monkeypatch, shape, decode_kernel):
     """Why the multi-layer logit bound above is looser than the per-op bound: the only amplifier is a
     Q4_0 value of a new K/V row that sits on a rounding boundary and rounds the other way (its f32
