@@ -47,10 +47,10 @@ PARITY_TOKENS = 16
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 << 20
 
-# dram__bytes_read.sum + dram__bytes_write.sum per layer of one launch of the persistent decode kernel (E2B layer
-# shape), from an ncu capture of the current kernel on an 8-layer model (its traffic grows with the layer count);
-# None until such a capture exists.
-DECODE_KERNEL_DRAM_TRAFFIC_PER_LAYER = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent decode kernel on the full 35-layer
+# E2B shape, divided by 35 (ncu capture of this bench's own command: 698.5 MB read + 0.9 MB written per launch;
+# profiles/mega_kernel_e2b_decode.md).
+DECODE_KERNEL_DRAM_TRAFFIC_PER_LAYER = 19_982_000
 
 
 def measured_peak():
@@ -249,7 +249,7 @@ def time_kernels_alone(ctx, model, slot, cfg, peak, steps):
     head = cfg.vocab * cfg.hidden // 256 * (210 if cfg.embd_dtype == Q6K else 144)
     nbytes = ksm.weight_bytes_per_token(cfg) - head
     out["decode_layers"] = {"kernel": "mega_kernel (all 35 layers of a token in one persistent launch; q/k/v, attention, o-proj, "
-                                      "gate/up + GELU, down per layer; blocks hand rows to each other as tagged words, no grid barrier)",
+                                      "gate/up + GELU, down per layer, a grid barrier between phases)",
                             "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "launches_per_token": 1}
     x = ctx.buffer_bytes(np.random.default_rng(0).standard_normal(cfg.hidden).astype(np.float32))
     # gate/up: 35 distinct layer pairs, 10.6 MB each
