@@ -49,7 +49,7 @@ L2_BYTES = 126 << 20
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent decode kernel on the full 35-layer
 # E2B shape, divided by 35 (ncu capture of this bench's own command: 698.5 MB read + 0.9 MB written per launch;
-# profiles/mega_kernel_e2b_decode.md).
+# the summary of that capture is kept under profiles/).
 DECODE_KERNEL_DRAM_TRAFFIC_PER_LAYER = 19_982_000
 
 

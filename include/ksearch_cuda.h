@@ -265,11 +265,13 @@ int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens);
 int ks_model_decode_token(ks_model* m, int first_slot, int n_slots, const int* tokens, int* next);    /* GP:1616 decode_token, blocking */
 int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight,
                       int* out, ks_generate_stats* stats);                   /* GP:1658 generate_timed */
-const void* ks_model_debug_ptr(const ks_model* m, int which, int slot);      /* test hook: 0 residual x, 1 logits, 2 phase clocks */
+const void* ks_model_debug_ptr(const ks_model* m, int which, int slot);      /* test hook: 0 residual x, 1 logits, 2 phase stamps (first, last block), 3 every block's stamps */
 /* Knobs of a slot's persistent decode kernel (tests, profiling): what = 0 polls before a device-side wait gives
- * up, 1 = make one stage of every layer wait for a value nobody writes (exercises the KS_ERR_TIMEOUT path; 0 =
- * off), 2 = context length from which attention is split across blocks, 3 = record per-phase SM clocks (the
- * counterpart of KSEARCH_PROFILE, GP:885,924-929,1260-1273; also switched on by that environment variable). */
+ * up, 1 = make one wait of the token (a grid barrier; with KSEARCH_DECODE_KERNEL=2 one stage of every layer) wait
+ * for something nobody writes (exercises the KS_ERR_TIMEOUT path; 0 = off); KSEARCH_DECODE_KERNEL=2 only: 2 =
+ * context length from which attention is split across blocks, 3 = record per-phase time stamps (the counterpart
+ * of KSEARCH_PROFILE, GP:885,924-929,1260-1273; also switched on by that environment variable; the default
+ * kernel always records its stamps). */
 int ks_model_debug_set(ks_model* m, int slot, int what, unsigned value);
 /* One slot's rows of a layer's KV cache on the device, [max_seq, n_kv, hd] in Q4_0 (KV:24-60 holds one such
  * buffer per owning layer); which: 0 = K, 1 = V.  For tests and for hosts that snapshot or restore a slot. */
