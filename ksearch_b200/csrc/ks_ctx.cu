@@ -85,6 +85,7 @@ void ks_ctx_destroy(ks_ctx* c) {
   if (c->stage_x) ks_buf_free(c, c->stage_x);
   if (c->stage_y) ks_buf_free(c, c->stage_y);
   if (c->ws) cudaFree(c->ws);
+  if (c->gemm_ws) cudaFree(c->gemm_ws);
   if (c->t0) cudaEventDestroy(c->t0);
   if (c->t1) cudaEventDestroy(c->t1);
   cudaStreamDestroy(c->stream);
@@ -295,3 +296,21 @@ int ks_has_gpu_work(ks_ctx* c) {
 }
 
 }  // extern "C"
+
+int ks_ctx_gemm_scratch(ks_ctx* c, size_t bytes, void** out) {
+  if (bytes > c->gemm_ws_bytes) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(c->stream, &st);
+    if (st != cudaStreamCaptureStatusNone)
+      return ks_fail(c, KS_ERR_STATE, "gemm: scratch of %zu bytes must exist before the stream is captured", bytes);
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);  // launches that still read the old scratch
+    if (c->gemm_ws) cudaFree(c->gemm_ws);
+    c->gemm_ws = nullptr;
+    c->gemm_ws_bytes = 0;
+    if (cudaMalloc(&c->gemm_ws, bytes) != cudaSuccess) return ks_fail(c, KS_ERR_OOM, "gemm: cudaMalloc(%zu) failed", bytes);
+    c->gemm_ws_bytes = bytes;
+  }
+  *out = c->gemm_ws;
+  return KS_OK;
+}

@@ -1,0 +1,455 @@
+// Q4_K / Q6_K weights x a batch of 9..256 token rows on the 5th-generation tensor cores (tcgen05).
+//
+// The reference routes matvec_batch with more than 8 rows (crates/ksearch_kernels/src/lib.rs:1414) to its
+// mul_mm kernel (crates/ksearch_codegen/src/render.rs:1073-1291: 64x32 tiles, weights dequantised to half in
+// threadgroup memory, simdgroup 8x8 MMA).  Here one CTA owns 128 weight rows and ALL token rows:
+//   D[weight row, token] (f32, in tensor memory)  +=  A[128 rows, 16 k] . B[tokens, 16 k]^T
+// with the weight rows as the M side of the MMA, so 9 tokens cost as little tensor work as the instruction
+// allows (N = 16) and 256 tokens fill it (N = 256).
+//   * B (token rows) is prepared once per call by x_split_kernel: every f32 x is split into two f16 terms
+//     (hi = rn(x), lo = rn(x - hi)) and stored k-step by k-step in exactly the shared-memory image the MMA wants
+//     (8x8 core matrices, K-major, no swizzle), so a k-step of B is ONE cp.async.bulk into the stage.
+//   * A (weights) is dequantised by the CTA's 256 threads, one row half per thread and k-step, bit for bit as
+//     crates/ksearch_gguf/src/gguf_impl.rs:618-633 / 761-791 computes it, scaled by 2^8 (exact; keeps the low
+//     term out of the f16 denormal range), split the same way and stored as core matrices.
+//   * Three MMAs per 16 k: Ahi.Bhi + Ahi.Blo + Alo.Bhi; the dropped lo.lo term is below 2^-22 relative, so the
+//     result matches f32 arithmetic (the reference's single half operands give ~1e-3).
+//   * Two stages: while the tensor core works on one, the threads dequantise the next; tcgen05.commit on an
+//     mbarrier hands a stage back.  The accumulator (128 lanes x N columns) is read back with tcgen05.ld, scaled
+//     by 2^-8 and stored coalesced along the weight-row index.
+// Every wait is bounded; on expiry the CTA raises the context's status word, waits (bounded) for what it has in
+// flight, frees its tensor memory and returns.
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
+#include "ks_fx.cuh"
+
+namespace {
+
+constexpr int GM_ROWS = 128;        // weight rows per CTA (M of the MMA)
+constexpr int GM_KSTEP = 64;        // k per stage: one Q4_K scale pair, half of a Q6_K 128-run
+constexpr int GM_THREADS = 256;
+constexpr unsigned GM_A_BYTES = 2u * 8u * GM_ROWS * 16u;  // hi + lo, 8 k-chunks, 128 rows, 16 bytes: 32 KB
+constexpr unsigned GM_WAIT = 1u << 20;
+
+struct GemmArgs {
+  const uint8_t* W;
+  size_t row_bytes;
+  const __half* xt;   // [k-steps][2][8][NP][8] halves
+  float* y;           // y[token * ldy + row]
+  size_t ldy;
+  unsigned rows, cols, n_tok, np;  // np: token count padded to a multiple of 16 (<= 256)
+  unsigned tmem_cols;              // power of two >= max(32, np)
+  unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
+  size_t part_stride;              // floats between the outputs of consecutive splits
+  unsigned* err;
+};
+
+// x[token, k] (f32, row stride ldx) -> the B image: k-step s, part p (0 hi, 1 lo), chunk c, token t, 8 halves.
+__global__ void x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsigned np, unsigned cols, __half* xt) {
+  ks_pdl_entry();
+  const unsigned chunks = cols / 8u;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)np * chunks) return;
+  const unsigned t = (unsigned)(i % np), ck = (unsigned)(i / np);  // consecutive threads: consecutive tokens of one chunk
+  float v[8];
+  if (t < n_tok) {
+    const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + (size_t)ck * 8u);
+    const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + (size_t)ck * 8u + 4u);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = 0.0f;
+  }
+  __align__(16) __half2 hi[4], lo[4];
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+    const float2 hf = __half22float2(h);
+    hi[e] = h;
+    lo[e] = __floats2half2_rn(v[2 * e] - hf.x, v[2 * e + 1] - hf.y);
+  }
+  const unsigned s = ck >> 3, c = ck & 7u;
+  __half* base = xt + ((size_t)s * 2u * 8u + c) * np * 8u + (size_t)t * 8u;
+  *reinterpret_cast<uint4*>(base) = *reinterpret_cast<const uint4*>(hi);
+  *reinterpret_cast<uint4*>(base + (size_t)8u * np * 8u) = *reinterpret_cast<const uint4*>(lo);
+}
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void tc_alloc(uint32_t slot_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] . B[smem desc]^T, f16 inputs, f32 accumulation; one thread issues.
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 8 consecutive f32 columns of this warp's 32 lanes.
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Shared-memory operand descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` = bytes between the
+// two 8-k chunks of one MMA, `sbo` = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, unsigned lbo, unsigned sbo) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) |
+         (1ull << 46);
+}
+
+__device__ __forceinline__ uint32_t pack_h2(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+// Eight f32 weights (already scaled by 2^8) -> 16 bytes of hi and 16 bytes of lo halves.
+__device__ __forceinline__ void split8(const float (&w)[8], uint4& hi, uint4& lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const __half2 hh = __floats2half2_rn(w[2 * e], w[2 * e + 1]);
+    const float2 hf = __half22float2(hh);
+    h[e] = pack_h2(hh);
+    l[e] = pack_h2(__floats2half2_rn(w[2 * e] - hf.x, w[2 * e + 1] - hf.y));
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// The packed bytes one thread needs for one k-step, fetched a step ahead of their use.
+template <int DT>
+struct Raw;
+template <>
+struct Raw<KS_Q4K> {
+  uint4 hdr, q0, q1;  // d, dmin, 12 scale bytes; the k-step's 32 bytes of nibbles
+};
+template <>
+struct Raw<KS_Q6K> {
+  uint32_t ql[4], qh[4];  // 16 + 16 bytes as 2-byte loads packed in pairs
+  float ds0, ds1;         // 2^8 d sc for the two 16-runs
+};
+
+// Thread (row, half h) of k-step ks: weights [64 ks + 32 h, +32) of its row.
+__device__ __forceinline__ void load_raw(const GemmArgs& a, unsigned row, unsigned h, unsigned ks, Raw<KS_Q4K>& w) {
+  const uint8_t* blk = a.W + (size_t)row * a.row_bytes + (size_t)(ks >> 2) * 144u;
+  const unsigned j = ks & 3u;
+  w.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+  w.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16u + 32u * j));
+  w.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32u + 32u * j));
+}
+// Q6_K: block = ql[128] qh[64] scales[16] d; a 128-run holds four groups g of 32 (gguf_impl.rs:761-791):
+// group g takes nibble g >> 1 of ql[32 (g & 1) + l] and bits 2g, 2g + 1 of qh[l].
+__device__ __forceinline__ void load_raw(const GemmArgs& a, unsigned row, unsigned h, unsigned ks, Raw<KS_Q6K>& w) {
+  const uint8_t* blk = a.W + (size_t)row * a.row_bytes + (size_t)(ks >> 2) * 210u;
+  const unsigned n = (ks >> 1) & 1u, g = 2u * (ks & 1u) + h;
+  const uint16_t* ql = reinterpret_cast<const uint16_t*>(blk + 64u * n + 32u * (g & 1u));  // blocks are 2-byte aligned
+  const uint16_t* qh = reinterpret_cast<const uint16_t*>(blk + 128u + 32u * n);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {  // this thread's 16-run pair: l = 0..31 is words 0..15; half h of the k-step is all of them
+    w.ql[i] = 0;
+    w.qh[i] = 0;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    const uint32_t lo = __ldg(ql + i), hi = __ldg(qh + i);
+    // keep only this group's nibble / bit pair, packed 4 bits and 2 bits per element
+    const uint32_t ln = ((lo >> (4u * (g >> 1))) & 0xFu) | (((lo >> (8u + 4u * (g >> 1))) & 0xFu) << 4);
+    const uint32_t hn = ((hi >> (2u * g)) & 3u) | (((hi >> (8u + 2u * g)) & 3u) << 2);
+    w.ql[i >> 2] |= ln << (8 * (i & 3));
+    w.qh[i >> 2] |= hn << (4 * (i & 3)) ;
+  }
+  const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192u + 8u * n + 2u * g);
+  const float d = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * 256.0f;
+  w.ds0 = d * (float)sc[0];
+  w.ds1 = d * (float)sc[1];
+}
+
+__device__ __forceinline__ void dequant8(const Raw<KS_Q4K>& w, unsigned h, unsigned j, int cc, float dsc, float dm, float (&out)[8]) {
+  const uint32_t wds[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
+#pragma unroll
+  for (int e = 0; e < 8; e++) {
+    const uint32_t wd = wds[2 * cc + (e >> 2)] >> (4u * h);
+    const float q = (float)((wd >> (8 * (e & 3))) & 0xFu);
+    out[e] = __fsub_rn(__fmul_rn(dsc, q), dm);  // d*sc*q - dmin*m as gguf_impl.rs:618-633 rounds it, times 2^8
+  }
+}
+
+// The thread's 32 weights into chunks 4h..4h+3 of the A stage (hi and lo halves).
+template <int DT>
+__device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, unsigned h, unsigned ks, unsigned char* A, unsigned r) {
+  uint4* Ahi = reinterpret_cast<uint4*>(A) + (size_t)(4u * h) * GM_ROWS + r;
+  uint4* Alo = Ahi + (size_t)8u * GM_ROWS;
+  if (!live) {  // rows past the matrix: zeros (their outputs are not stored)
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      Ahi[(size_t)cc * GM_ROWS] = make_uint4(0, 0, 0, 0);
+      Alo[(size_t)cc * GM_ROWS] = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
+  if constexpr (DT == KS_Q4K) {
+    float dsc_lo, dsc_hi, dm_lo, dm_hi;
+    q4k_group_scales(w.hdr, (int)(ks & 3u), dsc_lo, dsc_hi, dm_lo, dm_hi);
+    const float dsc = (h ? dsc_hi : dsc_lo) * 256.0f, dm = (h ? dm_hi : dm_lo) * 256.0f;
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      float v[8];
+      dequant8(w, h, ks & 3u, cc, dsc, dm, v);
+      uint4 hi, lo;
+      split8(v, hi, lo);
+      Ahi[(size_t)cc * GM_ROWS] = hi;
+      Alo[(size_t)cc * GM_ROWS] = lo;
+    }
+  } else {
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) {  // element l = 8 cc + e: pair i = l >> 1, byte b = l & 1
+        const int i = 4 * cc + (e >> 1), b = e & 1;
+        const uint32_t lq = (w.ql[i >> 2] >> (8 * (i & 3) + 4 * b)) & 0xFu;
+        const uint32_t hq = (w.qh[i >> 2] >> (4 * (i & 3) + 2 * b)) & 3u;
+        const int q = (int)(lq | (hq << 4)) - 32;
+        v[e] = (cc < 2 ? w.ds0 : w.ds1) * (float)q;
+      }
+      uint4 hi, lo;
+      split8(v, hi, lo);
+      Ahi[(size_t)cc * GM_ROWS] = hi;
+      Alo[(size_t)cc * GM_ROWS] = lo;
+    }
+  }
+}
+
+// grid = (row tiles, k splits): CTA (bx, by) multiplies rows [128 bx, +128) over k-steps [by * per, (by + 1) * per)
+// and stores its sums at y + by * part_stride (a partial when there is more than one split).
+template <int DT>
+__global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  // [0,64): mbarriers full[2], freed[2], done; [64,68): tensor-memory address; stages from 1024
+  const uint32_t bars = sm32(smem);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 64);
+  const unsigned b_bytes = a.np * 256u;                 // hi + lo, 8 chunks, np tokens, 16 bytes
+  const unsigned stage_bytes = GM_A_BYTES + b_bytes;
+  unsigned char* stage0 = smem + 1024;
+  const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+  const unsigned r = tid & (GM_ROWS - 1), h = tid >> 7;
+  const unsigned row = blockIdx.x * GM_ROWS + r;
+  const bool live = row < a.rows;
+  const unsigned ks0 = blockIdx.y * a.ksteps_per, ks1 = min(ks0 + a.ksteps_per, a.cols / GM_KSTEP);
+  const unsigned ksteps = ks1 - ks0;
+  float* yout = a.y + (size_t)blockIdx.y * a.part_stride;
+
+  Raw<DT> raw;  // weights do not depend on the kernels before this one: fetch the first k-step right away
+  if (live) load_raw(a, row, h, ks0, raw);
+  if (tid == 0) {
+    for (int i = 0; i < 5; i++) mb_init(bars + 8u * i, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tc_alloc(sm32(tslot), a.tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tslot;
+  ks_pdl_entry();  // the B image comes from the kernel before this one
+
+  const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
+  bool ok = true;
+  unsigned issued_b = 0;  // thread 0: bulk copies issued
+  for (unsigned i = 0; i < ksteps; i++) {
+    const unsigned ks = ks0 + i, s = i & 1u, u = i >> 1;
+    unsigned char* A = stage0 + (size_t)s * stage_bytes;
+    unsigned char* B = A + GM_A_BYTES;
+    if (u > 0) {  // the MMAs that read this stage two steps ago are done
+      if (ok && !mb_wait(bars + 8u * (2u + s), (u - 1u) & 1u, GM_WAIT)) ok = false;
+      tc_fence_after();
+    }
+    if (tid == 0 && ok) {
+      mb_expect(bars + 8u * s, b_bytes);
+      bulk_in(sm32(B), a.xt + (size_t)ks * (b_bytes / 2u), b_bytes, bars + 8u * s);
+      issued_b = i + 1;
+    }
+    const Raw<DT> cur = raw;
+    if (live && i + 1 < ksteps) load_raw(a, row, h, ks + 1, raw);  // in flight while this step is converted
+    dequant_to_stage<DT>(cur, live, h, ks, A, r);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    if (tid == 0) {
+      if (!mb_wait(bars + 8u * s, u & 1u, GM_WAIT)) {
+        ok = false;
+      } else {
+        tc_fence_after();
+        const uint32_t a0 = sm32(A), b0 = sm32(B);
+#pragma unroll
+        for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
+          const uint64_t ah = tc_desc(a0 + (2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
+          const uint64_t al = tc_desc(a0 + (8u + 2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
+          const uint64_t bh = tc_desc(b0 + (2u * j) * (a.np * 16u), a.np * 16u, 128u);
+          const uint64_t bl = tc_desc(b0 + (8u + 2u * j) * (a.np * 16u), a.np * 16u, 128u);
+          tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
+          tc_mma_f16(tmem, ah, bl, idesc, 1u);
+          tc_mma_f16(tmem, al, bh, idesc, 1u);
+        }
+        tc_commit(bars + 8u * (2u + s));
+        if (i + 1 == ksteps) tc_commit(bars + 8u * 4u);
+      }
+    }
+  }
+  // all MMAs done (tcgen05.commit tracks every MMA issued before it)
+  ok = __syncthreads_and(ok);
+  if (ok && !mb_wait(bars + 8u * 4u, 0u, GM_WAIT)) ok = false;
+  tc_fence_after();
+  if (ok) {
+    // warp w reads lanes 32 (w % 4) .. +31; warps 0-3 take the even 8-column groups, warps 4-7 the odd ones
+    const unsigned lane_base = (warp & 3u) * 32u;
+    const unsigned out_row = blockIdx.x * GM_ROWS + lane_base + lane;
+    for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 16u) {
+      uint32_t v[8];
+      tc_ld8(tmem + (lane_base << 16) + c0, v);
+      if (out_row < a.rows) {
+#pragma unroll
+        for (unsigned e = 0; e < 8; e++)
+          if (c0 + e < a.n_tok) yout[(size_t)(c0 + e) * a.ldy + out_row] = __uint_as_float(v[e]) * (1.0f / 256.0f);
+      }
+    }
+  } else {
+    if (tid == 0) {
+      atomicOr(a.err, 8u);
+      // what this thread started must finish before shared and tensor memory go away (bounded): the last bulk
+      // copy, and every MMA issued so far (a fresh commit tracks them all)
+      if (issued_b) mb_wait(bars + 8u * ((issued_b - 1u) & 1u), ((issued_b - 1u) >> 1) & 1u, GM_WAIT);
+      tc_commit(bars + 8u * 4u);
+      mb_wait(bars + 8u * 4u, 0u, GM_WAIT);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc_dealloc(tmem, a.tmem_cols);
+}
+
+// Sum of the k-split partials in split order (the result does not depend on how the CTAs were scheduled), then
+// the epilogue: mode 0 y = sum; mode 1 y = gelu(sum of P0) * (sum of P1) (lib.rs:953, the GeGLU of gate and up).
+__global__ void gemm_finish_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok, unsigned rows,
+                                   size_t ldp, float* y, size_t ldy, int mode) {
+  ks_pdl_entry();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tok * rows) return;
+  const unsigned t = (unsigned)(i / rows), r = (unsigned)(i % rows);
+  const size_t at = (size_t)t * ldp + r;
+  float g = 0.0f, u = 0.0f;
+  for (unsigned s = 0; s < splits; s++) g += P0[(size_t)s * part_stride + at];
+  if (mode == 1) {
+    for (unsigned s = 0; s < splits; s++) u += P1[(size_t)s * part_stride + at];
+    g = gelu_mul(g, u);
+  }
+  y[(size_t)t * ldy + r] = g;
+}
+
+}  // namespace
+
+namespace {
+unsigned gemm_np(int n_tok) { return ((unsigned)n_tok + 15u) / 16u * 16u; }
+// k splits: enough CTAs to occupy the chip about one and a half times over, at least four k-steps each.
+unsigned gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols) {
+  const unsigned tiles = (unsigned)((rows + GM_ROWS - 1) / GM_ROWS), ksteps = (unsigned)(cols / GM_KSTEP);
+  unsigned s = ((unsigned)ctx->sm_count * 3u / 2u + tiles - 1) / tiles;
+  if (s > ksteps / 4u) s = ksteps / 4u;
+  if (s > 16u) s = 16u;
+  return s < 1u ? 1u : s;
+}
+bool gemm_covers(ks_dtype wdtype, size_t cols, int n_tok) {
+  return (wdtype == KS_Q4K || wdtype == KS_Q6K) && cols % 256 == 0 && n_tok >= 1 && n_tok <= 256;
+}
+}  // namespace
+
+unsigned ks_gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols) { return gemm_splits(ctx, rows, cols); }
+// Bytes of the B image of n_tok rows of `cols` values (hi + lo halves, token count padded to 16).
+size_t ks_gemm_xt_bytes(size_t cols, int n_tok) { return cols * gemm_np(n_tok) * 4; }
+// Bytes of one set of k-split partials for a rows x cols matrix.
+size_t ks_gemm_part_bytes(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok) {
+  return (size_t)gemm_splits(ctx, rows, cols) * (size_t)n_tok * rows * 4;
+}
+
+// x[t * ldx + k] (f32) -> the B image in xt.
+int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt) {
+  if (cols % 256 || n_tok < 1 || n_tok > 256 || ldx % 4) return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad operand shape");
+  const unsigned np = gemm_np(n_tok);
+  const size_t n_thr = (size_t)np * (cols / 8);
+  KS_LAUNCH(ctx, (x_split_kernel), (unsigned)((n_thr + 255) / 256), 256, 0, x, ldx, (unsigned)n_tok, np, (unsigned)cols, (__half*)xt);
+  return ks_after_launch(ctx, "x_split");
+}
+
+// P[s][t * ldp + r] = sum over k-split s of W[r, k] x[t, k]; *splits_out tells how many partials were written
+// (1: P already holds the result).  `xt` is the image ks_launch_gemm_split made of the same rows.
+int ks_launch_gemm_part(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const void* xt, int n_tok, float* P,
+                        size_t ldp, unsigned max_splits, unsigned* splits_out) {
+  if (!gemm_covers(wdtype, cols, n_tok)) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
+  GemmArgs a{};
+  a.W = W;
+  a.row_bytes = cols / 256 * (wdtype == KS_Q4K ? 144 : 210);
+  a.xt = (const __half*)xt;
+  a.y = P;
+  a.ldy = ldp;
+  a.rows = (unsigned)rows;
+  a.cols = (unsigned)cols;
+  a.n_tok = (unsigned)n_tok;
+  a.np = gemm_np(n_tok);
+  a.tmem_cols = 32;
+  while (a.tmem_cols < a.np) a.tmem_cols <<= 1;
+  unsigned splits = gemm_splits(ctx, rows, cols);
+  if (splits > max_splits) splits = max_splits;
+  const unsigned ksteps = (unsigned)(cols / GM_KSTEP);
+  a.ksteps_per = (ksteps + splits - 1) / splits;
+  splits = (ksteps + a.ksteps_per - 1) / a.ksteps_per;
+  a.part_stride = (size_t)n_tok * ldp;
+  a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
+  const size_t smem = 1024 + 2 * ((size_t)GM_A_BYTES + (size_t)a.np * 256);
+  if (smem > ctx->smem_optin) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: %zu B of shared memory needed", smem);
+  auto kern = wdtype == KS_Q4K ? gemm_kq_tc_kernel<KS_Q4K> : gemm_kq_tc_kernel<KS_Q6K>;
+  static size_t smem_set[2][16] = {{0}};
+  size_t& set = smem_set[wdtype == KS_Q4K ? 0 : 1][ctx->device & 15];
+  if (smem > set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "gemm: cannot set %zu B shared memory: %s", smem, cudaGetErrorString(e));
+    set = smem;
+  }
+  KS_LAUNCH(ctx, kern, dim3((unsigned)((rows + GM_ROWS - 1) / GM_ROWS), splits), GM_THREADS, smem, a);
+  *splits_out = splits;
+  return ks_after_launch(ctx, "gemm_kq_tc");
+}
+
+// y[t * ldy + r] = sum_s P0[s][t * ldp + r]  (mode 0)  or  gelu(sum P0) * sum P1  (mode 1).
+int ks_launch_gemm_finish(ks_ctx* ctx, const float* P0, const float* P1, unsigned splits, int n_tok, size_t rows, size_t ldp, float* y,
+                          size_t ldy, int mode) {
+  const size_t n = (size_t)n_tok * rows;
+  KS_LAUNCH(ctx, (gemm_finish_kernel), (unsigned)((n + 255) / 256), 256, 0, P0, P1, (size_t)n_tok * ldp, splits, (unsigned)n_tok,
+            (unsigned)rows, ldp, y, ldy, mode);
+  return ks_after_launch(ctx, "gemm_finish");
+}
+
+// y[t * ldy + r] = sum_k W[r, k] x[t * ldx + k] for t < n_tok (<= 256), f32 x and y: operand split, GEMM and, when
+// the k range was split, the ordered sum of the partials.  `scratch`: ks_gemm_xt_bytes + ks_gemm_part_bytes.
+int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const float* x, size_t ldx, float* y,
+                      size_t ldy, int n_tok, void* scratch) {
+  if (!gemm_covers(wdtype, cols, n_tok) || ldx % 4) return 1;
+  int rc = ks_launch_gemm_split(ctx, x, ldx, n_tok, cols, scratch);
+  if (rc) return rc;
+  float* P = (float*)((char*)scratch + ks_gemm_xt_bytes(cols, n_tok));
+  const unsigned want = gemm_splits(ctx, rows, cols);
+  unsigned splits = 1;
+  if (want == 1) return ks_launch_gemm_part(ctx, wdtype, rows, cols, W, scratch, n_tok, y, ldy, 1, &splits);
+  if ((rc = ks_launch_gemm_part(ctx, wdtype, rows, cols, W, scratch, n_tok, P, rows, want, &splits))) return rc;
+  return ks_launch_gemm_finish(ctx, P, nullptr, splits, n_tok, rows, rows, y, ldy, 0);
+}

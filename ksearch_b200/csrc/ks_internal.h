@@ -27,6 +27,8 @@ struct ks_ctx {
   ks_plan override_plan{};
   std::map<std::string, ks_plan> plans;  // op_rowsxcols[_bN] -> plan (searched, loaded or set)
   void* ws = nullptr;  // small zero-initialised device workspace (cross-block reductions)
+  void* gemm_ws = nullptr;  // token rows split into f16 terms for the tensor-core GEMM (grown outside stream capture)
+  size_t gemm_ws_bytes = 0;
   // pinned staging for the *_host convenience calls
   void* stage_h = nullptr;
   size_t stage_h_bytes = 0;
@@ -143,6 +145,22 @@ int ks_launch_sdpa(ks_ctx* ctx, size_t n_slots, size_t n_q, size_t n_kv, size_t 
 int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype,
                                  const void* src, const float* idx, ks_dtype act, void* dst);
 int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);
+
+// ---- tensor-core GEMM for batches of more than 8 token rows (ks_gemm.cu) ---------------------------
+size_t ks_gemm_xt_bytes(size_t cols, int n_tok);
+unsigned ks_gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols);  // k splits the GEMM will use for this matrix
+size_t ks_gemm_part_bytes(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok);
+// The context's scratch, grown to `bytes` (fails inside a stream capture when it would have to grow).
+int ks_ctx_gemm_scratch(ks_ctx* ctx, size_t bytes, void** out);
+int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt);
+int ks_launch_gemm_part(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const void* xt, int n_tok, float* P,
+                        size_t ldp, unsigned max_splits, unsigned* splits_out);
+int ks_launch_gemm_finish(ks_ctx* ctx, const float* P0, const float* P1, unsigned splits, int n_tok, size_t rows, size_t ldp, float* y,
+                          size_t ldy, int mode);
+// Split + GEMM (+ ordered sum of the k-split partials).  Returns 1 when the shape is not covered (cols not a
+// multiple of 256, more than 256 rows).  scratch: ks_gemm_xt_bytes + ks_gemm_part_bytes.
+int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const float* x, size_t ldx, float* y,
+                      size_t ldy, int n_tok, void* scratch);
 
 // ---- all layers of one token as ONE persistent kernel (ks_mega.cu) --------------------------------
 struct ks_mega_layer {

@@ -457,10 +457,19 @@ int ks_matvec(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_b
   int rc = check_w(ctx, "matvec", wdtype, W, w_byte_off, rows, cols);
   if (rc) return rc;
   KS_REQUIRE(ctx, ks_is_act(act), "matvec: activation dtype must be F32 or F16");
-  KS_REQUIRE(ctx, n_tok >= 1 && n_tok <= 8, "matvec: n_tok=%d outside 1..8 (larger batches belong to the prefill GEMM)", n_tok);
+  KS_REQUIRE(ctx, n_tok >= 1 && n_tok <= 256, "matvec: n_tok=%d outside 1..256", n_tok);
   const size_t ab = ks_act_bytes(act);
   KS_REQUIRE(ctx, ks_fits(x, x_off * ab, (size_t)n_tok * cols * ab), "matvec: x buffer too small");
   KS_REQUIRE(ctx, ks_fits(y, y_off * ab, (size_t)n_tok * rows * ab), "matvec: y buffer too small");
+  if (n_tok > 8) {  // the reference's mul_mm route (lib.rs:1414): a tensor-core GEMM over all rows at once
+    KS_REQUIRE(ctx, act == KS_F32 && (wdtype == KS_Q4K || wdtype == KS_Q6K) && cols % 256 == 0 && x_off % 4 == 0,
+               "matvec: batches of more than 8 rows need f32 activations, Q4K/Q6K weights, cols %% 256 == 0 and x_off %% 4 == 0");
+    void* scratch = nullptr;
+    if ((rc = ks_ctx_gemm_scratch(ctx, ks_gemm_xt_bytes(cols, n_tok) + ks_gemm_part_bytes(ctx, rows, cols, n_tok), &scratch))) return rc;
+    rc = ks_launch_gemm_kq(ctx, wdtype, rows, cols, (const uint8_t*)W->dptr + w_byte_off, (const float*)x->dptr + x_off, cols,
+                           (float*)y->dptr + y_off, rows, n_tok, scratch);
+    return rc == 1 ? ks_fail(ctx, KS_ERR_UNSUPPORTED, "matvec: %zux%zu with %d rows does not fit the GEMM kernel", rows, cols, n_tok) : rc;
+  }
   ks_mv_seg seg{(const uint8_t*)W->dptr + w_byte_off, (char*)y->dptr + y_off * ab, (unsigned)rows};
   return ks_launch_matvec(ctx, wdtype, &seg, 1, KS_EPI_PLAIN, cols, act, (const char*)x->dptr + x_off * ab, n_tok, nullptr);
 }

@@ -127,6 +127,11 @@ struct ks_model {
   float* cmeta = nullptr;
   float* cattn_tmp = nullptr;
   int chunk = 1;  // tokens per prompt chunk: as many as the matvec kernels can stage side by side (<= KS_PREFILL_CHUNK)
+  // rows per pass through the tensor-core GEMM (0: not available, activations are not f32); its scratch inside the
+  // context's GEMM workspace: the split operand image, two sets of k-split partials
+  int gemm_chunk = 0;
+  void* gemm_xt = nullptr;
+  float *gemm_p0 = nullptr, *gemm_p1 = nullptr;
 };
 
 namespace {
@@ -142,6 +147,8 @@ int dev_alloc(ks_model* m, void** p, size_t bytes) {
 }
 
 constexpr int KS_PREFILL_CHUNK = 8;  // tokens per pass over the weights (the matvec kernels take up to 8)
+constexpr int KS_GEMM_CHUNK = 128;   // rows per pass when the tensor-core GEMM takes the matrices (f32 activations)
+constexpr size_t KS_STAGE_IDS = 256; // pinned words that stage host token ids
 
 // Where a forward pass reads and writes: n rows of activations, their positions, and the KV caches
 // behind them.  Decode steps map row s to slot first + s (one cache per row); a prompt chunk maps
@@ -200,18 +207,20 @@ Lane chunk_lane(ks_model* m, int slot) {
   return L;
 }
 
+unsigned row_threads(int n) { return (unsigned)((n + 1 + 31) / 32 * 32); }  // one thread per row and one more
+
 int lane_begin(ks_model* m, const Lane& L, int n) {
   if (L.chunk_base)
-    KS_LAUNCH(m->ctx, (begin_chunk_kernel), 1, 32, 0, n, (const int*)L.chunk_base, L.pos, L.meta);
+    KS_LAUNCH(m->ctx, (begin_chunk_kernel), 1, row_threads(n), 0, n, (const int*)L.chunk_base, L.pos, L.meta);
   else
-    KS_LAUNCH(m->ctx, (begin_token_kernel), 1, 32, 0, n, (const int*)L.pos, L.meta);
+    KS_LAUNCH(m->ctx, (begin_token_kernel), 1, row_threads(n), 0, n, (const int*)L.pos, L.meta);
   return ks_after_launch(m->ctx, "begin_token");
 }
 int lane_end(ks_model* m, const Lane& L, int n) {
   if (L.chunk_base)
     KS_LAUNCH(m->ctx, (end_chunk_kernel), 1, 32, 0, n, L.chunk_base);
   else
-    KS_LAUNCH(m->ctx, (end_token_kernel), 1, 32, 0, n, L.pos);
+    KS_LAUNCH(m->ctx, (end_token_kernel), 1, row_threads(n), 0, n, L.pos);
   return ks_after_launch(m->ctx, "end_token");
 }
 
@@ -266,7 +275,71 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  KS_LAUNCH(c, (collect_kernel), 1, 32, 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  return ks_after_launch(c, "collect");
+}
+
+// y[t, :] = W x[t, :] for the n rows whose split image is in m->gemm_xt (tensor-core GEMM; k-split partials are
+// summed in order by a second launch).
+int gemm_rows(ks_model* m, ks_dtype dt, const void* W, size_t rows, size_t cols, int n, char* y, size_t ldy) {
+  ks_ctx* c = m->ctx;
+  unsigned splits = 1;
+  if (ks_gemm_splits(c, rows, cols) == 1)  // enough row tiles to fill the chip: results go straight to y
+    return ks_launch_gemm_part(c, dt, rows, cols, (const uint8_t*)W, m->gemm_xt, n, (float*)y, ldy, 1, &splits);
+  int rc = ks_launch_gemm_part(c, dt, rows, cols, (const uint8_t*)W, m->gemm_xt, n, m->gemm_p0, rows, 16, &splits);
+  if (rc) return rc;
+  return ks_launch_gemm_finish(c, m->gemm_p0, nullptr, splits, n, rows, rows, (float*)y, ldy, 0);
+}
+
+// The same op order for 9..KS_GEMM_CHUNK rows (a prompt chunk, or more slots than the batch matvec stages side by
+// side): the matrices go through the tensor-core GEMM, the reference's mul_mm route (forward_prefill_chunk,
+// gemma_prim.rs:1317-1607); norms, RoPE/KV pack, attention and GELU are the row-wise kernels above.  f32 only.
+int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
+  ks_ctx* c = m->ctx;
+  const ks_model_config& g = m->cfg;
+  const ks_dtype act = KS_F32;
+  const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
+  const size_t qn = nq * hd, kvn = nkv * hd;
+  char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff, *logits = L_.logits;
+  float* tok_out = L_.tok_out;
+  int rc;
+  if ((rc = lane_begin(m, L_, n))) return rc;
+  if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, L_.tok_in, act, x))) return rc;
+  if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
+  for (int l = 0; l < g.n_layers; l++) {
+    const Layer& L = m->layers[l];
+    if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
+    if ((rc = gemm_rows(m, KS_Q4K, L.wq.dptr, qn, H, n, q, qn))) return rc;
+    if ((rc = gemm_rows(m, KS_Q4K, L.wk.dptr, kvn, H, n, k, kvn))) return rc;
+    if ((rc = gemm_rows(m, KS_Q4K, L.wv.dptr, kvn, H, n, v, kvn))) return rc;
+    uint8_t* kk = m->kv_k[l] + L_.kv_off;
+    uint8_t* kv = m->kv_v[l] + L_.kv_off;
+    if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
+                                         kk, kv, L_.pos, L_.kv_stride)))
+      return rc;
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, L_.meta, L_.attn_tmp, o, m->n_splits)))
+      return rc;
+    if ((rc = ks_launch_gemm_split(c, (const float*)o, qn, n, qn, m->gemm_xt))) return rc;
+    if ((rc = gemm_rows(m, KS_Q4K, L.wo.dptr, H, qn, n, x2, H))) return rc;
+    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_attn_norm.dptr, x, L.ffn_norm.dptr, x, x2))) return rc;
+    // gate and up share the operand image; their partials meet in the GeGLU epilogue (lib.rs:953)
+    if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
+    unsigned sg = 1, su = 1;
+    if ((rc = ks_launch_gemm_part(c, KS_Q4K, F, H, (const uint8_t*)L.wgate.dptr, m->gemm_xt, n, m->gemm_p0, F, 16, &sg))) return rc;
+    if ((rc = ks_launch_gemm_part(c, KS_Q4K, F, H, (const uint8_t*)L.wup.dptr, m->gemm_xt, n, m->gemm_p1, F, 16, &su))) return rc;
+    if ((rc = ks_launch_gemm_finish(c, m->gemm_p0, m->gemm_p1, sg, n, F, F, (float*)ff, F, 1))) return rc;
+    if ((rc = ks_launch_gemm_split(c, (const float*)ff, F, n, F, m->gemm_xt))) return rc;
+    if ((rc = gemm_rows(m, KS_Q4K, L.wdown.dptr, H, F, n, x2, H))) return rc;
+    const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
+    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_ffw_norm.dptr, x, next_norm, x, x2))) return rc;
+  }
+  if ((rc = lane_end(m, L_, n))) return rc;
+  if (!want_logits) return KS_OK;
+  if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
+  if ((rc = gemm_rows(m, (ks_dtype)g.embd_dtype, m->token_embd.dptr, g.vocab, H, n, logits, g.vocab))) return rc;
+  for (int s = 0; s < n; s++)
+    if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * 4, tok_out + s))) return rc;
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
   return ks_after_launch(c, "collect");
 }
 
@@ -341,11 +414,15 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, xn, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  KS_LAUNCH(c, (collect_kernel), 1, 32, 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
   return ks_after_launch(c, "collect");
 }
 
 int mega_reset(ks_ctx* c, const ks_model::Mega& mg) { return mg.bar ? ks_mega_reset(c, mg.bar) : ks_flow_reset(c, mg.flow); }
+
+// Rows that share one pass over the weights when `left` rows are waiting: what the batch matvec stages side by
+// side, or, for more rows than that, a tensor-core GEMM chunk.
+int pass_rows(const ks_model* m, int left) { return left > m->chunk && m->gemm_chunk ? m->gemm_chunk : m->chunk; }
 
 // One slot's token with every layer inside one persistent kernel; embedding before, head after.
 int enqueue_forward_mega(ks_model* m, const ks_model::Mega& mg, int first, int src, bool want_logits) {
@@ -439,6 +516,7 @@ int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
     const uint64_t before = c->launches;
     const Lane lane = slot_lane(m, first, src);
     int rc = mg ? enqueue_forward_mega(m, mg, first, src, want_logits)
+             : n > m->chunk ? enqueue_forward_gemm(m, lane, n, want_logits)
              : m->fused ? enqueue_forward_fused(m, lane, n, want_logits)
                         : enqueue_forward(m, lane, n, want_logits);
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
@@ -473,7 +551,9 @@ int run_prefill_chunk(ks_model* m, int slot, int n) {
     KS_CUDA(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     const uint64_t before = c->launches;
     const Lane lane = chunk_lane(m, slot);
-    int rc = m->fused ? enqueue_forward_fused(m, lane, n, false) : enqueue_forward(m, lane, n, false);
+    int rc = n > m->chunk ? enqueue_forward_gemm(m, lane, n, false)
+             : m->fused   ? enqueue_forward_fused(m, lane, n, false)
+                          : enqueue_forward(m, lane, n, false);
     cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
     c->launches = before;
     if (rc) {
@@ -512,7 +592,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   if (g.n_q < 1 || g.n_kv < 1 || g.n_q % g.n_kv) return bad("n_q must be a multiple of n_kv");
   if (g.hd != 128 && g.hd != 256) return bad("head_dim must be 128 or 256");
   if ((g.n_q * g.hd) % 256) return bad("n_q*head_dim must be a multiple of 256");
-  if (g.vocab < 1 || g.max_seq < 1 || g.n_slots < 1 || g.n_slots > 8) return bad("vocab, max_seq >= 1 and 1 <= n_slots <= 8 required");
+  if (g.vocab < 1 || g.max_seq < 1 || g.n_slots < 1 || g.n_slots > 64) return bad("vocab, max_seq >= 1 and 1 <= n_slots <= 64 required");
   if (g.embd_dtype != KS_Q4K && g.embd_dtype != KS_Q6K) return bad("token_embd must be Q4K or Q6K");
   if (g.act != KS_F32 && g.act != KS_F16) return bad("activation dtype must be F32 or F16");
   if (!(g.softcap > 0.0f)) return bad("softcap must be > 0");
@@ -592,7 +672,29 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
     if (qn > maxcols) maxcols = qn;
     m->chunk = KS_PREFILL_CHUNK;
     while (m->chunk > 1 && (size_t)m->chunk * (maxcols / 64) * 280 + (64u << 10) > ctx->smem_optin) m->chunk--;
-    const size_t C = KS_PREFILL_CHUNK;
+    // f32 activations and block-aligned columns: larger batches go through the tensor-core GEMM
+    if (g.act == KS_F32 && H % 256 == 0 && F % 256 == 0 && qn % 256 == 0 && !getenv("KSEARCH_NO_GEMM")) {
+      const int G = KS_GEMM_CHUNK;
+      m->gemm_chunk = G;
+      const size_t rows_of[5] = {qn, H, F, H, (size_t)g.vocab}, cols_of[5] = {H, qn, H, F, H};
+      size_t xt = 0, part = 0;
+      for (int i = 0; i < 5; i++) {
+        const size_t a = ks_gemm_xt_bytes(cols_of[i], G), b = ks_gemm_part_bytes(ctx, rows_of[i], cols_of[i], G);
+        xt = a > xt ? a : xt;
+        part = b > part ? b : part;
+      }
+      xt = (xt + 255) & ~(size_t)255;
+      part = (part + 255) & ~(size_t)255;
+      void* ws = nullptr;
+      if (ks_ctx_gemm_scratch(ctx, xt + 2 * part, &ws) != KS_OK) {
+        ok = false;
+      } else {
+        m->gemm_xt = ws;
+        m->gemm_p0 = (float*)((char*)ws + xt);
+        m->gemm_p1 = (float*)((char*)ws + xt + part);
+      }
+    }
+    const size_t C = m->gemm_chunk > KS_PREFILL_CHUNK ? m->gemm_chunk : KS_PREFILL_CHUNK;
     ok = ok && dev_alloc(m, &m->cx, C * H * ab) == KS_OK && dev_alloc(m, &m->cxb, C * H * ab) == KS_OK &&
          dev_alloc(m, &m->cx2, C * H * ab) == KS_OK && dev_alloc(m, &m->cq, C * qn * ab) == KS_OK &&
          dev_alloc(m, &m->ck, C * kvn * ab) == KS_OK && dev_alloc(m, &m->cv, C * kvn * ab) == KS_OK &&
@@ -602,7 +704,8 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   }
   if (ok) {
     m->n_splits = ks_sdpa_pick_splits(ctx, 1, g.n_kv, g.max_seq);
-    ok = dev_alloc(m, (void**)&m->cattn_tmp, ((size_t)KS_PREFILL_CHUNK * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
+    const size_t C = m->gemm_chunk > KS_PREFILL_CHUNK ? m->gemm_chunk : KS_PREFILL_CHUNK;
+    ok = dev_alloc(m, (void**)&m->cattn_tmp, (C * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
   }
   if (ok) {
     ok = dev_alloc(m, (void**)&m->attn_tmp, (S * g.n_q * (size_t)m->n_splits * (g.hd + 2) + 4) * sizeof(float)) == KS_OK;
@@ -622,7 +725,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
          cudaStreamSynchronize(ctx->stream) == cudaSuccess;
     if (!ok) ks_fail(ctx, KS_ERR_CUDA, "model_create: rope upload failed");
   }
-  m->host_tok_n = 4096;
+  m->host_tok_n = 8192;
   if (ok && cudaMallocHost((void**)&m->host_tok, m->host_tok_n * sizeof(float)) != cudaSuccess) {
     ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
     ok = false;
@@ -788,7 +891,8 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
         return ks_fail(c, KS_ERR_STATE, "slots %d..%d hold their device-side token ids in different buffers; pass host ids", first, first + n - 1);
   if (tokens) {
     src = 0;
-    float* stage = m->host_tok + m->host_tok_n - 8;  // last 8 entries of the pinned ring stage the ids
+    KS_REQUIRE(c, (size_t)n <= KS_STAGE_IDS, "forward: more than %zu slots per call", KS_STAGE_IDS);
+    float* stage = m->host_tok + m->host_tok_n - 16 - KS_STAGE_IDS;  // the pinned ring's tail stages the ids
     KS_CUDA(c, cudaStreamSynchronize(c->stream));     // the staging words may still be in flight
     for (int s = 0; s < n; s++) {
       KS_REQUIRE(c, tokens[s] >= 0 && tokens[s] < m->cfg.vocab, "token id %d outside the vocabulary", tokens[s]);
@@ -798,8 +902,9 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
   }
   // The slots share one pass over the weights as long as their staged input vectors fit the matvec kernels'
   // shared memory side by side (m->chunk of them); a larger batch takes several passes.
-  for (int s0 = 0; s0 < n; s0 += m->chunk) {
-    const int nn = n - s0 < m->chunk ? n - s0 : m->chunk;
+  const int per_pass = pass_rows(m, n);
+  for (int s0 = 0; s0 < n; s0 += per_pass) {
+    const int nn = n - s0 < per_pass ? n - s0 : per_pass;
     if ((rc = run_forward(m, first + s0, nn, src, want_logits != 0))) return rc;
   }
   for (int s = first; s < first + n; s++) {
@@ -842,9 +947,10 @@ int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens) {
   int rc;
   if ((rc = check_ready(m)) || (rc = check_slots(m, slot, 1))) return rc;
   if (m->seq_len[slot] + n_tokens > m->cfg.max_seq) return ks_fail(c, KS_ERR_STATE, "max_seq exceeded");
-  float* stage = m->host_tok + m->host_tok_n - 8;
-  for (int t0 = 0; t0 < n_tokens; t0 += m->chunk) {
-    const int n = n_tokens - t0 < m->chunk ? n_tokens - t0 : m->chunk;
+  float* stage = m->host_tok + m->host_tok_n - 16 - KS_STAGE_IDS;
+  for (int t0 = 0; t0 < n_tokens;) {
+    const int per_pass = pass_rows(m, n_tokens - t0);
+    const int n = n_tokens - t0 < per_pass ? n_tokens - t0 : per_pass;
     KS_CUDA(c, cudaStreamSynchronize(c->stream));  // the staging words may still be in flight
     for (int t = 0; t < n; t++) {
       KS_REQUIRE(c, tokens[t0 + t] >= 0 && tokens[t0 + t] < m->cfg.vocab, "token id %d outside the vocabulary", tokens[t0 + t]);
@@ -853,6 +959,7 @@ int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens) {
     KS_CUDA(c, cudaMemcpyAsync(m->ctok, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     if ((rc = run_prefill_chunk(m, slot, n))) return rc;
     m->seq_len[slot] += n;
+    t0 += n;
   }
   return KS_OK;
 }
@@ -866,7 +973,7 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
   float* back = m->host_tok;  // n ids, then the status flag
-  if (n <= m->chunk) {        // one pass: its last kernel collected ids and flag side by side, one copy brings both
+  if (n <= pass_rows(m, n)) {  // one pass: its last kernel collected ids and flag side by side, one copy brings both
     KS_CUDA(c, cudaMemcpyAsync(back, m->ret + (size_t)first * (m->cfg.n_slots + 1), (n + 1) * sizeof(float), cudaMemcpyDeviceToHost,
                                c->stream));
   } else {                    // several passes: ids from the token buffer, the flag as any non-zero status word
@@ -895,7 +1002,7 @@ int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, in
   if (!m) return KS_ERR_INVALID;
   ks_ctx* c = m->ctx;
   KS_REQUIRE(c, prompt && n_prompt >= 1, "empty prompt");
-  KS_REQUIRE(c, n_new >= 0 && (size_t)n_new <= m->host_tok_n - 16, "generate: n_new out of range");
+  KS_REQUIRE(c, n_new >= 0 && (size_t)n_new <= m->host_tok_n - 32 - KS_STAGE_IDS, "generate: n_new out of range");
   KS_REQUIRE(c, out || n_new == 0, "generate: null output");
   int rc;
   if ((rc = ks_model_slot_reset(m, slot))) return rc;

@@ -212,7 +212,7 @@ class Eng:
         ctx.check(ctx.lib.ks_matvec(ctx.h, rows, cols, weight_dtype, a.h, 0, self.act, x.h, x_off_elems, y.h, y_off_elems, 1))
 
     def matvec_batch(self, ctx, rows, cols, batch, weight_dtype, a, x, y):
-        """K:1414 (batch <= 8: token-looped GEMV family)"""
+        """K:1414 (batch <= 8: token-looped GEMV family; 9..256 rows: the tensor-core GEMM, the reference's mul_mm route)"""
         ctx.check(ctx.lib.ks_matvec(ctx.h, rows, cols, weight_dtype, a.h, 0, self.act, x.h, 0, y.h, 0, batch))
 
     def matvec_qkv_wds(self, ctx, q_rows, kv_rows, cols, wq_dtype, wk_dtype, wv_dtype, wq, wk, wv, x, q, k, v):

@@ -230,7 +230,7 @@ def test_matvec_errors(ctx):
     with pytest.raises(KsError, match="not supported"):
         e.matvec_wd(ctx, 8, 512, F16, W, x, y)
     with pytest.raises(KsError, match="n_tok"):
-        e.matvec_batch(ctx, 8, 512, 9, Q4K, W, x, y)
+        e.matvec_batch(ctx, 8, 512, 0, Q4K, W, x, y)
     with pytest.raises(KsError, match="y buffer"):
         e.matvec_wd_at(ctx, 8, 512, Q4K, W, x, 0, y, 4)
     with pytest.raises(KsError):

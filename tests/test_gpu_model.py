@@ -363,14 +363,15 @@ def test_logits_tight_when_kv_bytes_agree(oracle, monkeypatch, shape, decode_ker
 
 @pytest.mark.parametrize("n_kv", [1, 2])
 def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
-    """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk.
+    """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk: up to 8
+    rows through the batch matvec, longer prompts in chunks of up to 128 rows through the tensor-core GEMM.
     After the prompt, the next-token logits must match the CPU decoder, and the KV rows it wrote must
     serve later decode steps (teacher-forced continuation)."""
-    cfg = ksm.tiny_config(max_seq=96, n_kv=n_kv)
+    cfg = ksm.tiny_config(max_seq=192, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=31, keep=True)
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
-    for n_prompt in (1, 7, 8, 9, 21):          # below, at and above the chunk size; ragged last chunk
+    for n_prompt in (1, 7, 8, 9, 21, 128, 150, 137):   # batch matvec; one GEMM chunk; full chunk + ragged rest; rest of 9
         toks = synth.token_ids(31, f"p{n_prompt}", n_prompt + 6, cfg.vocab)
         model.slot_reset(0)
         cpu.reset()
@@ -390,6 +391,44 @@ def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
     with pytest.raises(KsError, match="max_seq exceeded"):
         model.prefill(0, [1] * 200)
     cpu.close()
+    model.close()
+
+
+def test_many_slots_share_a_gemm_pass(ctx, oracle):
+    """Twelve slots, more than the batch matvec stages side by side: one step is one pass through the tensor-core
+    GEMM path.  Each slot matches its own single-slot CPU run, through forward (logits) and through the blocking
+    decode_token (ids)."""
+    n = 12
+    cfg = ksm.tiny_config(max_seq=32, n_slots=n)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=12, keep=True)
+    assert [model.slot_alloc() for _ in range(n)] == list(range(n))
+    lens = [1 + (5 * s) % 11 for s in range(n)]
+    seqs = [synth.token_ids(12, f"s{s}", lens[s] + 4, cfg.vocab) for s in range(n)]
+    for s in range(n):
+        model.prefill(s, seqs[s][:lens[s]])
+    cpus = []
+    for s in range(n):
+        cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+        for t in seqs[s][:lens[s]]:
+            cpu.forward_token(int(t), False)
+        cpus.append(cpu)
+    launches = ctx.launch_count()
+    for j in range(3):
+        model.forward(0, n, [int(seqs[s][lens[s] + j]) for s in range(n)], True)
+        ctx.synchronize()
+        for s in range(n):
+            cpus[s].forward_token(int(seqs[s][lens[s] + j]), True)
+            want = cpus[s].logits().astype(np.float64)
+            got = model.read_debug(1, s).astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (j, s)
+    per_step = (ctx.launch_count() - launches) // 3
+    nxt = model.decode_token([int(seqs[s][lens[s] + 3]) for s in range(n)], 0)
+    for s in range(n):
+        cpus[s].forward_token(int(seqs[s][lens[s] + 3]), True)
+        lg = cpus[s].logits().astype(np.float64)
+        assert nxt[s] == int(np.argmax(lg)) or np.sort(lg)[-1] - lg[nxt[s]] < 2e-3 * np.abs(lg).max()
+        cpus[s].close()
+    print(f"[12 slots] {per_step} launches per step")
     model.close()
 
 
