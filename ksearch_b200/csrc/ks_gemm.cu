@@ -34,15 +34,18 @@ constexpr unsigned GM_A_BYTES = 2u * 8u * GM_ROWS * 16u;  // hi + lo, 8 k-chunks
 constexpr unsigned GM_WAIT = 1u << 20;
 
 struct GemmArgs {
-  const uint8_t* W;
+  // up to three matrices over the same columns and token rows in one launch (q, k, v; gate, up): matrix i owns
+  // the row tiles [tile0[i], tile0[i + 1])
+  const uint8_t* W[3];
+  float* y[3];            // y[i][token * ldy[i] + row]
+  size_t ldy[3];
+  size_t part_stride[3];  // floats between the outputs of consecutive k splits
+  unsigned rows[3], tile0[4];
   size_t row_bytes;
   const __half* xt;   // [k-steps][2][8][NP][8] halves
-  float* y;           // y[token * ldy + row]
-  size_t ldy;
-  unsigned rows, cols, n_tok, np;  // np: token count padded to a multiple of 16 (<= 256)
+  unsigned cols, n_tok, np;        // np: token count padded to a multiple of 16 (<= 256)
   unsigned tmem_cols;              // power of two >= max(32, np)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
-  size_t part_stride;              // floats between the outputs of consecutive splits
   unsigned* err;
 };
 
@@ -142,8 +145,8 @@ struct Raw<KS_Q6K> {
 };
 
 // Thread (row, half h) of k-step ks: weights [64 ks + 32 h, +32) of its row.
-__device__ __forceinline__ void load_raw(const GemmArgs& a, unsigned row, unsigned h, unsigned ks, Raw<KS_Q4K>& w) {
-  const uint8_t* blk = a.W + (size_t)row * a.row_bytes + (size_t)(ks >> 2) * 144u;
+__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned h, unsigned ks, Raw<KS_Q4K>& w) {
+  const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 144u;
   const unsigned j = ks & 3u;
   w.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
   w.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16u + 32u * j));
@@ -151,8 +154,8 @@ __device__ __forceinline__ void load_raw(const GemmArgs& a, unsigned row, unsign
 }
 // Q6_K: block = ql[128] qh[64] scales[16] d; a 128-run holds four groups g of 32 (gguf_impl.rs:761-791):
 // group g takes nibble g >> 1 of ql[32 (g & 1) + l] and bits 2g, 2g + 1 of qh[l].
-__device__ __forceinline__ void load_raw(const GemmArgs& a, unsigned row, unsigned h, unsigned ks, Raw<KS_Q6K>& w) {
-  const uint8_t* blk = a.W + (size_t)row * a.row_bytes + (size_t)(ks >> 2) * 210u;
+__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned h, unsigned ks, Raw<KS_Q6K>& w) {
+  const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 210u;
   const unsigned n = (ks >> 1) & 1u, g = 2u * (ks & 1u) + h;
   const uint16_t* ql = reinterpret_cast<const uint16_t*>(blk + 64u * n + 32u * (g & 1u));  // blocks are 2-byte aligned
   const uint16_t* qh = reinterpret_cast<const uint16_t*>(blk + 128u + 32u * n);
@@ -245,14 +248,22 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   unsigned char* stage0 = smem + 1024;
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const unsigned r = tid & (GM_ROWS - 1), h = tid >> 7;
-  const unsigned row = blockIdx.x * GM_ROWS + r;
-  const bool live = row < a.rows;
+  // which matrix this row tile belongs to (selects, no dynamic indexing of the parameter arrays)
+  const unsigned bx = blockIdx.x;
+  const int seg = (bx >= a.tile0[1]) + (bx >= a.tile0[2]);
+  const uint8_t* W = seg == 0 ? a.W[0] : seg == 1 ? a.W[1] : a.W[2];
+  const unsigned seg_rows = seg == 0 ? a.rows[0] : seg == 1 ? a.rows[1] : a.rows[2];
+  const size_t ldy = seg == 0 ? a.ldy[0] : seg == 1 ? a.ldy[1] : a.ldy[2];
+  const size_t part_stride = seg == 0 ? a.part_stride[0] : seg == 1 ? a.part_stride[1] : a.part_stride[2];
+  const unsigned row_base = (bx - (seg == 0 ? a.tile0[0] : seg == 1 ? a.tile0[1] : a.tile0[2])) * GM_ROWS;
+  const unsigned row = row_base + r;
+  const bool live = row < seg_rows;
   const unsigned ks0 = blockIdx.y * a.ksteps_per, ks1 = min(ks0 + a.ksteps_per, a.cols / GM_KSTEP);
   const unsigned ksteps = ks1 - ks0;
-  float* yout = a.y + (size_t)blockIdx.y * a.part_stride;
+  float* yout = (seg == 0 ? a.y[0] : seg == 1 ? a.y[1] : a.y[2]) + (size_t)blockIdx.y * part_stride;
 
   Raw<DT> raw;  // weights do not depend on the kernels before this one: fetch the first k-step right away
-  if (live) load_raw(a, row, h, ks0, raw);
+  if (live) load_raw(W, a.row_bytes, row, h, ks0, raw);
   if (tid == 0) {
     for (int i = 0; i < 5; i++) mb_init(bars + 8u * i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -281,7 +292,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
       issued_b = i + 1;
     }
     const Raw<DT> cur = raw;
-    if (live && i + 1 < ksteps) load_raw(a, row, h, ks + 1, raw);  // in flight while this step is converted
+    if (live && i + 1 < ksteps) load_raw(W, a.row_bytes, row, h, ks + 1, raw);  // in flight while this step is converted
     dequant_to_stage<DT>(cur, live, h, ks, A, r);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
     ok = __syncthreads_and(ok);
@@ -314,14 +325,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   if (ok) {
     // warp w reads lanes 32 (w % 4) .. +31; warps 0-3 take the even 8-column groups, warps 4-7 the odd ones
     const unsigned lane_base = (warp & 3u) * 32u;
-    const unsigned out_row = blockIdx.x * GM_ROWS + lane_base + lane;
+    const unsigned out_row = row_base + lane_base + lane;
     for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 16u) {
       uint32_t v[8];
       tc_ld8(tmem + (lane_base << 16) + c0, v);
-      if (out_row < a.rows) {
+      if (out_row < seg_rows) {
 #pragma unroll
         for (unsigned e = 0; e < 8; e++)
-          if (c0 + e < a.n_tok) yout[(size_t)(c0 + e) * a.ldy + out_row] = __uint_as_float(v[e]) * (1.0f / 256.0f);
+          if (c0 + e < a.n_tok) yout[(size_t)(c0 + e) * ldy + out_row] = __uint_as_float(v[e]) * (1.0f / 256.0f);
       }
     }
   } else {
@@ -340,21 +351,37 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
 }
 
 // Sum of the k-split partials in split order (the result does not depend on how the CTAs were scheduled), then
-// the epilogue: mode 0 y = sum; mode 1 y = gelu(sum of P0) * (sum of P1) (lib.rs:953, the GeGLU of gate and up).
-__global__ void gemm_finish_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok, unsigned rows,
-                                   size_t ldp, float* y, size_t ldy, int mode) {
+// the epilogue.  mode 0: up to three matrices, y[i] = sum of P[i]; mode 1: y[0] = gelu(sum of P[0]) * (sum of P[1])
+// (lib.rs:953, the GeGLU of gate and up).
+struct FinishArgs {
+  const float* P[3];
+  float* y[3];
+  size_t ldy[3], part_stride[3];
+  unsigned rows[3], n_seg, splits, n_tok;
+  int mode;
+};
+__global__ void gemm_finish_kernel(const FinishArgs f) {
   ks_pdl_entry();
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)n_tok * rows) return;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t n0 = (size_t)f.n_tok * f.rows[0], n1 = f.n_seg > 1 && f.mode == 0 ? (size_t)f.n_tok * f.rows[1] : 0,
+               n2 = f.n_seg > 2 && f.mode == 0 ? (size_t)f.n_tok * f.rows[2] : 0;
+  if (i >= n0 + n1 + n2) return;
+  const int seg = (i >= n0) + (i >= n0 + n1);
+  i -= seg == 0 ? 0 : seg == 1 ? n0 : n0 + n1;
+  const unsigned rows = seg == 0 ? f.rows[0] : seg == 1 ? f.rows[1] : f.rows[2];
+  const float* P = seg == 0 ? f.P[0] : seg == 1 ? f.P[1] : f.P[2];
+  const size_t ps = seg == 0 ? f.part_stride[0] : seg == 1 ? f.part_stride[1] : f.part_stride[2];
   const unsigned t = (unsigned)(i / rows), r = (unsigned)(i % rows);
-  const size_t at = (size_t)t * ldp + r;
-  float g = 0.0f, u = 0.0f;
-  for (unsigned s = 0; s < splits; s++) g += P0[(size_t)s * part_stride + at];
-  if (mode == 1) {
-    for (unsigned s = 0; s < splits; s++) u += P1[(size_t)s * part_stride + at];
+  const size_t at = (size_t)t * rows + r;  // partials are dense [split][token][row]
+  float g = 0.0f;
+  for (unsigned s = 0; s < f.splits; s++) g += P[(size_t)s * ps + at];
+  if (f.mode == 1) {
+    float u = 0.0f;
+    for (unsigned s = 0; s < f.splits; s++) u += f.P[1][(size_t)s * f.part_stride[1] + at];
     g = gelu_mul(g, u);
   }
-  y[(size_t)t * ldy + r] = g;
+  float* y = seg == 0 ? f.y[0] : seg == 1 ? f.y[1] : f.y[2];
+  y[(size_t)t * (seg == 0 ? f.ldy[0] : seg == 1 ? f.ldy[1] : f.ldy[2]) + r] = g;
 }
 
 }  // namespace
@@ -374,13 +401,8 @@ bool gemm_covers(ks_dtype wdtype, size_t cols, int n_tok) {
 }
 }  // namespace
 
-unsigned ks_gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols) { return gemm_splits(ctx, rows, cols); }
 // Bytes of the B image of n_tok rows of `cols` values (hi + lo halves, token count padded to 16).
 size_t ks_gemm_xt_bytes(size_t cols, int n_tok) { return cols * gemm_np(n_tok) * 4; }
-// Bytes of one set of k-split partials for a rows x cols matrix.
-size_t ks_gemm_part_bytes(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok) {
-  return (size_t)gemm_splits(ctx, rows, cols) * (size_t)n_tok * rows * 4;
-}
 
 // x[t * ldx + k] (f32) -> the B image in xt.
 int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt) {
@@ -391,29 +413,58 @@ int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, siz
   return ks_after_launch(ctx, "x_split");
 }
 
-// P[s][t * ldp + r] = sum over k-split s of W[r, k] x[t, k]; *splits_out tells how many partials were written
-// (1: P already holds the result).  `xt` is the image ks_launch_gemm_split made of the same rows.
-int ks_launch_gemm_part(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const void* xt, int n_tok, float* P,
-                        size_t ldp, unsigned max_splits, unsigned* splits_out) {
-  if (!gemm_covers(wdtype, cols, n_tok)) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
+// Up to three matrices over the same columns in one launch.  With one k split matrix i's result goes straight to
+// y[i] (row stride ldy[i]); otherwise the partials go to P (dense [split][token][row] per matrix, matrix after
+// matrix) and a second launch sums them in split order into y.  mode 1 (two matrices, gate and up): y[0] =
+// gelu(gate) * up, always through P.  `xt` is the image ks_launch_gemm_split made of the same token rows.
+int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* const* W, const size_t* rows, size_t cols, const void* xt,
+                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode) {
+  if (!gemm_covers(wdtype, cols, n_tok) || n_seg < 1 || n_seg > 3) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
   GemmArgs a{};
-  a.W = W;
+  FinishArgs f{};
+  unsigned tiles = 0;
+  size_t total_rows = 0;
+  for (int i = 0; i < 3; i++) {
+    a.tile0[i] = tiles;
+    if (i < n_seg) {
+      a.W[i] = W[i];
+      a.rows[i] = (unsigned)rows[i];
+      tiles += (unsigned)((rows[i] + GM_ROWS - 1) / GM_ROWS);
+      total_rows += rows[i];
+    }
+  }
+  a.tile0[3] = tiles;
+  for (int i = n_seg; i < 3; i++) a.tile0[i] = 0xFFFFFFFFu;  // no tile reaches an absent matrix
   a.row_bytes = cols / 256 * (wdtype == KS_Q4K ? 144 : 210);
   a.xt = (const __half*)xt;
-  a.y = P;
-  a.ldy = ldp;
-  a.rows = (unsigned)rows;
   a.cols = (unsigned)cols;
   a.n_tok = (unsigned)n_tok;
   a.np = gemm_np(n_tok);
   a.tmem_cols = 32;
   while (a.tmem_cols < a.np) a.tmem_cols <<= 1;
-  unsigned splits = gemm_splits(ctx, rows, cols);
-  if (splits > max_splits) splits = max_splits;
   const unsigned ksteps = (unsigned)(cols / GM_KSTEP);
+  unsigned splits = gemm_splits(ctx, total_rows, cols);
   a.ksteps_per = (ksteps + splits - 1) / splits;
   splits = (ksteps + a.ksteps_per - 1) / a.ksteps_per;
-  a.part_stride = (size_t)n_tok * ldp;
+  const bool direct = splits == 1 && mode == 0;
+  size_t poff = 0;
+  for (int i = 0; i < n_seg; i++) {
+    if (direct) {
+      a.y[i] = y[i];
+      a.ldy[i] = ldy[i];
+      a.part_stride[i] = 0;
+    } else {
+      a.y[i] = P + poff;
+      a.ldy[i] = rows[i];
+      a.part_stride[i] = (size_t)n_tok * rows[i];
+      f.P[i] = a.y[i];
+      f.part_stride[i] = a.part_stride[i];
+      f.rows[i] = (unsigned)rows[i];
+      f.y[i] = mode == 1 ? y[0] : y[i];
+      f.ldy[i] = mode == 1 ? ldy[0] : ldy[i];
+      poff += (size_t)splits * n_tok * rows[i];
+    }
+  }
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
   const size_t smem = 1024 + 2 * ((size_t)GM_A_BYTES + (size_t)a.np * 256);
   if (smem > ctx->smem_optin) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: %zu B of shared memory needed", smem);
@@ -425,31 +476,30 @@ int ks_launch_gemm_part(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, 
     if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "gemm: cannot set %zu B shared memory: %s", smem, cudaGetErrorString(e));
     set = smem;
   }
-  KS_LAUNCH(ctx, kern, dim3((unsigned)((rows + GM_ROWS - 1) / GM_ROWS), splits), GM_THREADS, smem, a);
-  *splits_out = splits;
-  return ks_after_launch(ctx, "gemm_kq_tc");
-}
-
-// y[t * ldy + r] = sum_s P0[s][t * ldp + r]  (mode 0)  or  gelu(sum P0) * sum P1  (mode 1).
-int ks_launch_gemm_finish(ks_ctx* ctx, const float* P0, const float* P1, unsigned splits, int n_tok, size_t rows, size_t ldp, float* y,
-                          size_t ldy, int mode) {
-  const size_t n = (size_t)n_tok * rows;
-  KS_LAUNCH(ctx, (gemm_finish_kernel), (unsigned)((n + 255) / 256), 256, 0, P0, P1, (size_t)n_tok * ldp, splits, (unsigned)n_tok,
-            (unsigned)rows, ldp, y, ldy, mode);
+  KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS, smem, a);
+  int rc = ks_after_launch(ctx, "gemm_kq_tc");
+  if (rc || direct) return rc;
+  f.n_seg = (unsigned)n_seg;
+  f.splits = splits;
+  f.n_tok = (unsigned)n_tok;
+  f.mode = mode;
+  const size_t n = (size_t)n_tok * (mode == 1 ? rows[0] : total_rows);
+  KS_LAUNCH(ctx, (gemm_finish_kernel), (unsigned)((n + 255) / 256), 256, 0, f);
   return ks_after_launch(ctx, "gemm_finish");
 }
 
+// Floats of partials ks_launch_gemm_segs may write for matrices of `total_rows` rows in all.
+size_t ks_gemm_part_floats(const ks_ctx* ctx, size_t total_rows, size_t cols, int n_tok) {
+  return (size_t)gemm_splits(ctx, total_rows, cols) * (size_t)n_tok * total_rows;
+}
+
 // y[t * ldy + r] = sum_k W[r, k] x[t * ldx + k] for t < n_tok (<= 256), f32 x and y: operand split, GEMM and, when
-// the k range was split, the ordered sum of the partials.  `scratch`: ks_gemm_xt_bytes + ks_gemm_part_bytes.
+// the k range was split, the ordered sum of the partials.  `scratch`: ks_gemm_xt_bytes + 4 * ks_gemm_part_floats.
 int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const float* x, size_t ldx, float* y,
                       size_t ldy, int n_tok, void* scratch) {
   if (!gemm_covers(wdtype, cols, n_tok) || ldx % 4) return 1;
   int rc = ks_launch_gemm_split(ctx, x, ldx, n_tok, cols, scratch);
   if (rc) return rc;
   float* P = (float*)((char*)scratch + ks_gemm_xt_bytes(cols, n_tok));
-  const unsigned want = gemm_splits(ctx, rows, cols);
-  unsigned splits = 1;
-  if (want == 1) return ks_launch_gemm_part(ctx, wdtype, rows, cols, W, scratch, n_tok, y, ldy, 1, &splits);
-  if ((rc = ks_launch_gemm_part(ctx, wdtype, rows, cols, W, scratch, n_tok, P, rows, want, &splits))) return rc;
-  return ks_launch_gemm_finish(ctx, P, nullptr, splits, n_tok, rows, rows, y, ldy, 0);
+  return ks_launch_gemm_segs(ctx, wdtype, 1, &W, &rows, cols, scratch, n_tok, &y, &ldy, P, 0);
 }

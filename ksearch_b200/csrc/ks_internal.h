@@ -147,18 +147,18 @@ int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scal
 int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);
 
 // ---- tensor-core GEMM for batches of more than 8 token rows (ks_gemm.cu) ---------------------------
-size_t ks_gemm_xt_bytes(size_t cols, int n_tok);
-unsigned ks_gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols);  // k splits the GEMM will use for this matrix
-size_t ks_gemm_part_bytes(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok);
+size_t ks_gemm_xt_bytes(size_t cols, int n_tok);  // bytes of the split image of n_tok rows of `cols` values
+size_t ks_gemm_part_floats(const ks_ctx* ctx, size_t total_rows, size_t cols, int n_tok);  // k-split partials, at most
 // The context's scratch, grown to `bytes` (fails inside a stream capture when it would have to grow).
 int ks_ctx_gemm_scratch(ks_ctx* ctx, size_t bytes, void** out);
+// x[t * ldx + k] (f32) -> the image the GEMM reads its token rows from.
 int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt);
-int ks_launch_gemm_part(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const void* xt, int n_tok, float* P,
-                        size_t ldp, unsigned max_splits, unsigned* splits_out);
-int ks_launch_gemm_finish(ks_ctx* ctx, const float* P0, const float* P1, unsigned splits, int n_tok, size_t rows, size_t ldp, float* y,
-                          size_t ldy, int mode);
-// Split + GEMM (+ ordered sum of the k-split partials).  Returns 1 when the shape is not covered (cols not a
-// multiple of 256, more than 256 rows).  scratch: ks_gemm_xt_bytes + ks_gemm_part_bytes.
+// Up to three matrices over the same columns and token rows (q, k, v; gate, up) in one launch; mode 1: two
+// matrices, y[0] = gelu(W[0] x) * (W[1] x).  P: ks_gemm_part_floats(sum of rows) floats.
+int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* const* W, const size_t* rows, size_t cols, const void* xt,
+                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode);
+// Split + GEMM for one matrix.  Returns 1 when the shape is not covered (cols not a multiple of 256, more than
+// 256 rows).  scratch: ks_gemm_xt_bytes + 4 * ks_gemm_part_floats bytes.
 int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const float* x, size_t ldx, float* y,
                       size_t ldy, int n_tok, void* scratch);
 

@@ -465,7 +465,7 @@ int ks_matvec(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_b
     KS_REQUIRE(ctx, act == KS_F32 && (wdtype == KS_Q4K || wdtype == KS_Q6K) && cols % 256 == 0 && x_off % 4 == 0,
                "matvec: batches of more than 8 rows need f32 activations, Q4K/Q6K weights, cols %% 256 == 0 and x_off %% 4 == 0");
     void* scratch = nullptr;
-    if ((rc = ks_ctx_gemm_scratch(ctx, ks_gemm_xt_bytes(cols, n_tok) + ks_gemm_part_bytes(ctx, rows, cols, n_tok), &scratch))) return rc;
+    if ((rc = ks_ctx_gemm_scratch(ctx, ks_gemm_xt_bytes(cols, n_tok) + 4 * ks_gemm_part_floats(ctx, rows, cols, n_tok), &scratch))) return rc;
     rc = ks_launch_gemm_kq(ctx, wdtype, rows, cols, (const uint8_t*)W->dptr + w_byte_off, (const float*)x->dptr + x_off, cols,
                            (float*)y->dptr + y_off, rows, n_tok, scratch);
     return rc == 1 ? ks_fail(ctx, KS_ERR_UNSUPPORTED, "matvec: %zux%zu with %d rows does not fit the GEMM kernel", rows, cols, n_tok) : rc;

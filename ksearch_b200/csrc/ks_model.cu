@@ -131,7 +131,7 @@ struct ks_model {
   // context's GEMM workspace: the split operand image, two sets of k-split partials
   int gemm_chunk = 0;
   void* gemm_xt = nullptr;
-  float *gemm_p0 = nullptr, *gemm_p1 = nullptr;
+  float* gemm_p0 = nullptr;
 };
 
 namespace {
@@ -283,12 +283,9 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
 // summed in order by a second launch).
 int gemm_rows(ks_model* m, ks_dtype dt, const void* W, size_t rows, size_t cols, int n, char* y, size_t ldy) {
   ks_ctx* c = m->ctx;
-  unsigned splits = 1;
-  if (ks_gemm_splits(c, rows, cols) == 1)  // enough row tiles to fill the chip: results go straight to y
-    return ks_launch_gemm_part(c, dt, rows, cols, (const uint8_t*)W, m->gemm_xt, n, (float*)y, ldy, 1, &splits);
-  int rc = ks_launch_gemm_part(c, dt, rows, cols, (const uint8_t*)W, m->gemm_xt, n, m->gemm_p0, rows, 16, &splits);
-  if (rc) return rc;
-  return ks_launch_gemm_finish(c, m->gemm_p0, nullptr, splits, n, rows, rows, (float*)y, ldy, 0);
+  const uint8_t* Ws[1] = {(const uint8_t*)W};
+  float* ys[1] = {(float*)y};
+  return ks_launch_gemm_segs(c, dt, 1, Ws, &rows, cols, m->gemm_xt, n, ys, &ldy, m->gemm_p0, 0);
 }
 
 // The same op order for 9..KS_GEMM_CHUNK rows (a prompt chunk, or more slots than the batch matvec stages side by
@@ -303,31 +300,40 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
   char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff, *logits = L_.logits;
   float* tok_out = L_.tok_out;
   int rc;
+  // the rows themselves spread attention over the chip: split each row's context only as far as needed to give
+  // every SM two blocks
+  int att_splits = (int)((2 * (size_t)c->sm_count + n * nkv - 1) / (n * nkv));
+  att_splits = att_splits < 1 ? 1 : att_splits > m->n_splits ? m->n_splits : att_splits;
   if ((rc = lane_begin(m, L_, n))) return rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, L_.tok_in, act, x))) return rc;
   if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
   for (int l = 0; l < g.n_layers; l++) {
     const Layer& L = m->layers[l];
     if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
-    if ((rc = gemm_rows(m, KS_Q4K, L.wq.dptr, qn, H, n, q, qn))) return rc;
-    if ((rc = gemm_rows(m, KS_Q4K, L.wk.dptr, kvn, H, n, k, kvn))) return rc;
-    if ((rc = gemm_rows(m, KS_Q4K, L.wv.dptr, kvn, H, n, v, kvn))) return rc;
+    {  // q, k and v rows in one launch (lib.rs:227)
+      const uint8_t* Ws[3] = {(const uint8_t*)L.wq.dptr, (const uint8_t*)L.wk.dptr, (const uint8_t*)L.wv.dptr};
+      float* ys[3] = {(float*)q, (float*)k, (float*)v};
+      const size_t rs[3] = {qn, kvn, kvn};
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 3, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, 0))) return rc;
+    }
     uint8_t* kk = m->kv_k[l] + L_.kv_off;
     uint8_t* kv = m->kv_v[l] + L_.kv_off;
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, L_.pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, L_.meta, L_.attn_tmp, o, m->n_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, L_.meta, L_.attn_tmp, o, att_splits)))
       return rc;
     if ((rc = ks_launch_gemm_split(c, (const float*)o, qn, n, qn, m->gemm_xt))) return rc;
     if ((rc = gemm_rows(m, KS_Q4K, L.wo.dptr, H, qn, n, x2, H))) return rc;
     if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_attn_norm.dptr, x, L.ffn_norm.dptr, x, x2))) return rc;
     // gate and up share the operand image; their partials meet in the GeGLU epilogue (lib.rs:953)
     if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
-    unsigned sg = 1, su = 1;
-    if ((rc = ks_launch_gemm_part(c, KS_Q4K, F, H, (const uint8_t*)L.wgate.dptr, m->gemm_xt, n, m->gemm_p0, F, 16, &sg))) return rc;
-    if ((rc = ks_launch_gemm_part(c, KS_Q4K, F, H, (const uint8_t*)L.wup.dptr, m->gemm_xt, n, m->gemm_p1, F, 16, &su))) return rc;
-    if ((rc = ks_launch_gemm_finish(c, m->gemm_p0, m->gemm_p1, sg, n, F, F, (float*)ff, F, 1))) return rc;
+    {
+      const uint8_t* Ws[2] = {(const uint8_t*)L.wgate.dptr, (const uint8_t*)L.wup.dptr};
+      float* ys[2] = {(float*)ff, (float*)ff};
+      const size_t rs[2] = {F, F};
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 2, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, 1))) return rc;
+    }
     if ((rc = ks_launch_gemm_split(c, (const float*)ff, F, n, F, m->gemm_xt))) return rc;
     if ((rc = gemm_rows(m, KS_Q4K, L.wdown.dptr, H, F, n, x2, H))) return rc;
     const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
@@ -676,22 +682,21 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
     if (g.act == KS_F32 && H % 256 == 0 && F % 256 == 0 && qn % 256 == 0 && !getenv("KSEARCH_NO_GEMM")) {
       const int G = KS_GEMM_CHUNK;
       m->gemm_chunk = G;
-      const size_t rows_of[5] = {qn, H, F, H, (size_t)g.vocab}, cols_of[5] = {H, qn, H, F, H};
+      // one launch each: q|k|v, o, gate|up, down, head
+      const size_t rows_of[5] = {qn + 2 * kvn, H, 2 * F, H, (size_t)g.vocab}, cols_of[5] = {H, qn, H, F, H};
       size_t xt = 0, part = 0;
       for (int i = 0; i < 5; i++) {
-        const size_t a = ks_gemm_xt_bytes(cols_of[i], G), b = ks_gemm_part_bytes(ctx, rows_of[i], cols_of[i], G);
+        const size_t a = ks_gemm_xt_bytes(cols_of[i], G), b = 4 * ks_gemm_part_floats(ctx, rows_of[i], cols_of[i], G);
         xt = a > xt ? a : xt;
         part = b > part ? b : part;
       }
       xt = (xt + 255) & ~(size_t)255;
-      part = (part + 255) & ~(size_t)255;
       void* ws = nullptr;
-      if (ks_ctx_gemm_scratch(ctx, xt + 2 * part, &ws) != KS_OK) {
+      if (ks_ctx_gemm_scratch(ctx, xt + part, &ws) != KS_OK) {
         ok = false;
       } else {
         m->gemm_xt = ws;
         m->gemm_p0 = (float*)((char*)ws + xt);
-        m->gemm_p1 = (float*)((char*)ws + xt + part);
       }
     }
     const size_t C = m->gemm_chunk > KS_PREFILL_CHUNK ? m->gemm_chunk : KS_PREFILL_CHUNK;
