@@ -9,13 +9,14 @@
 //   * B (token rows) is prepared once per call by x_split_kernel: every f32 x is split into two f16 terms
 //     (hi = rn(x), lo = rn(x - hi)) and stored k-step by k-step in exactly the shared-memory image the MMA wants
 //     (8x8 core matrices, K-major, no swizzle), so a k-step of B is ONE cp.async.bulk into the stage.
-//   * A (weights) is dequantised by the CTA's 256 threads, one row half per thread and k-step, bit for bit as
+//   * A (weights) is dequantised by the CTA's 512 threads, a quarter of a row's k-step (16 weights) each, bit for bit as
 //     crates/ksearch_gguf/src/gguf_impl.rs:618-633 / 761-791 computes it, scaled by 2^8 (exact; keeps the low
 //     term out of the f16 denormal range), split the same way and stored as core matrices.
 //   * Three MMAs per 16 k: Ahi.Bhi + Ahi.Blo + Alo.Bhi; the dropped lo.lo term is below 2^-22 relative, so the
 //     result matches f32 arithmetic (the reference's single half operands give ~1e-3).
-//   * Two stages: while the tensor core works on one, the threads dequantise the next; tcgen05.commit on an
-//     mbarrier hands a stage back.  The accumulator (128 lanes x N columns) is read back with tcgen05.ld, scaled
+//   * Two A stages: while the tensor core works on one, the threads dequantise the next; tcgen05.commit on an
+//     mbarrier hands a stage back.  The B copies run up to two k-steps ahead in a ring of up to four stages, the
+//     packed weights two k-steps ahead in registers.  The accumulator (128 lanes x N columns) is read back with tcgen05.ld, scaled
 //     by 2^-8 and stored coalesced along the weight-row index.
 // Every wait is bounded; on expiry the CTA raises the context's status word, waits (bounded) for what it has in
 // flight, frees its tensor memory and returns.
@@ -29,7 +30,7 @@ namespace {
 
 constexpr int GM_ROWS = 128;        // weight rows per CTA (M of the MMA)
 constexpr int GM_KSTEP = 64;        // k per stage: one Q4_K scale pair, half of a Q6_K 128-run
-constexpr int GM_THREADS = 256;
+constexpr int GM_THREADS = 512;     // four threads per weight row and k-step
 constexpr unsigned GM_A_BYTES = 2u * 8u * GM_ROWS * 16u;  // hi + lo, 8 k-chunks, 128 rows, 16 bytes: 32 KB
 constexpr unsigned GM_WAIT = 1u << 20;
 
@@ -46,6 +47,7 @@ struct GemmArgs {
   unsigned cols, n_tok, np;        // np: token count padded to a multiple of 16 (<= 256)
   unsigned tmem_cols;              // power of two >= max(32, np)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
+  unsigned nb;                     // B stages (2..4): token rows are requested nb - 2 k-steps ahead
   unsigned* err;
 };
 
@@ -131,107 +133,89 @@ __device__ __forceinline__ void split8(const float (&w)[8], uint4& hi, uint4& lo
   lo = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
-// The packed bytes one thread needs for one k-step, fetched a step ahead of their use.
+// The packed bytes one thread needs for one k-step, fetched a step ahead of their use.  Thread (row, quarter qd)
+// owns weights [64 ks + 16 qd, +16) of its row: chunks 2 qd and 2 qd + 1 of the stage.
 template <int DT>
 struct Raw;
 template <>
 struct Raw<KS_Q4K> {
-  uint4 hdr, q0, q1;  // d, dmin, 12 scale bytes; the k-step's 32 bytes of nibbles
+  uint4 hdr, q;  // d, dmin, 12 scale bytes; 16 bytes that hold the quarter's nibbles
 };
 template <>
 struct Raw<KS_Q6K> {
-  uint32_t ql[4], qh[4];  // 16 + 16 bytes as 2-byte loads packed in pairs
-  float ds0, ds1;         // 2^8 d sc for the two 16-runs
+  uint32_t ql[2], qh;  // 16 nibbles, 16 bit pairs
+  float ds;            // 2^8 d sc of the quarter's 16-run
 };
 
-// Thread (row, half h) of k-step ks: weights [64 ks + 32 h, +32) of its row.
-__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned h, unsigned ks, Raw<KS_Q4K>& w) {
+__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned qd, unsigned ks, Raw<KS_Q4K>& w) {
   const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 144u;
-  const unsigned j = ks & 3u;
   w.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-  w.q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16u + 32u * j));
-  w.q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32u + 32u * j));
+  w.q = __ldg(reinterpret_cast<const uint4*>(blk + 16u + 32u * (ks & 3u) + 16u * (qd & 1u)));
 }
 // Q6_K: block = ql[128] qh[64] scales[16] d; a 128-run holds four groups g of 32 (gguf_impl.rs:761-791):
-// group g takes nibble g >> 1 of ql[32 (g & 1) + l] and bits 2g, 2g + 1 of qh[l].
-__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned h, unsigned ks, Raw<KS_Q6K>& w) {
+// group g takes nibble g >> 1 of ql[32 (g & 1) + l] and bits 2g, 2g + 1 of qh[l]; scale index 2g + (l >> 4).
+__device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned qd, unsigned ks, Raw<KS_Q6K>& w) {
   const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 210u;
-  const unsigned n = (ks >> 1) & 1u, g = 2u * (ks & 1u) + h;
-  const uint16_t* ql = reinterpret_cast<const uint16_t*>(blk + 64u * n + 32u * (g & 1u));  // blocks are 2-byte aligned
-  const uint16_t* qh = reinterpret_cast<const uint16_t*>(blk + 128u + 32u * n);
+  const unsigned n = (ks >> 1) & 1u, g = 2u * (ks & 1u) + (qd >> 1), sub = qd & 1u;
+  const uint16_t* ql = reinterpret_cast<const uint16_t*>(blk + 64u * n + 32u * (g & 1u) + 16u * sub);  // blocks are 2-byte aligned
+  const uint16_t* qh = reinterpret_cast<const uint16_t*>(blk + 128u + 32u * n + 16u * sub);
+  w.ql[0] = w.ql[1] = w.qh = 0;
 #pragma unroll
-  for (int i = 0; i < 4; i++) {  // this thread's 16-run pair: l = 0..31 is words 0..15; half h of the k-step is all of them
-    w.ql[i] = 0;
-    w.qh[i] = 0;
-  }
-#pragma unroll
-  for (int i = 0; i < 16; i++) {
+  for (int i = 0; i < 8; i++) {  // pair i: elements l = 2i, 2i + 1 of the 16-run
     const uint32_t lo = __ldg(ql + i), hi = __ldg(qh + i);
-    // keep only this group's nibble / bit pair, packed 4 bits and 2 bits per element
     const uint32_t ln = ((lo >> (4u * (g >> 1))) & 0xFu) | (((lo >> (8u + 4u * (g >> 1))) & 0xFu) << 4);
     const uint32_t hn = ((hi >> (2u * g)) & 3u) | (((hi >> (8u + 2u * g)) & 3u) << 2);
     w.ql[i >> 2] |= ln << (8 * (i & 3));
-    w.qh[i >> 2] |= hn << (4 * (i & 3)) ;
+    w.qh |= hn << (4 * i);
   }
-  const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192u + 8u * n + 2u * g);
-  const float d = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * 256.0f;
-  w.ds0 = d * (float)sc[0];
-  w.ds1 = d * (float)sc[1];
+  const int8_t sc = *reinterpret_cast<const int8_t*>(blk + 192u + 8u * n + 2u * g + sub);
+  w.ds = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * 256.0f * (float)sc;
 }
 
-__device__ __forceinline__ void dequant8(const Raw<KS_Q4K>& w, unsigned h, unsigned j, int cc, float dsc, float dm, float (&out)[8]) {
-  const uint32_t wds[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
-#pragma unroll
-  for (int e = 0; e < 8; e++) {
-    const uint32_t wd = wds[2 * cc + (e >> 2)] >> (4u * h);
-    const float q = (float)((wd >> (8 * (e & 3))) & 0xFu);
-    out[e] = __fsub_rn(__fmul_rn(dsc, q), dm);  // d*sc*q - dmin*m as gguf_impl.rs:618-633 rounds it, times 2^8
-  }
-}
-
-// The thread's 32 weights into chunks 4h..4h+3 of the A stage (hi and lo halves).
+// The thread's 16 weights into chunks 2 qd, 2 qd + 1 of the A stage (hi and lo halves).
 template <int DT>
-__device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, unsigned h, unsigned ks, unsigned char* A, unsigned r) {
-  uint4* Ahi = reinterpret_cast<uint4*>(A) + (size_t)(4u * h) * GM_ROWS + r;
+__device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, unsigned qd, unsigned ks, unsigned char* A, unsigned r) {
+  uint4* Ahi = reinterpret_cast<uint4*>(A) + (size_t)(2u * qd) * GM_ROWS + r;
   uint4* Alo = Ahi + (size_t)8u * GM_ROWS;
   if (!live) {  // rows past the matrix: zeros (their outputs are not stored)
 #pragma unroll
-    for (int cc = 0; cc < 4; cc++) {
+    for (int cc = 0; cc < 2; cc++) {
       Ahi[(size_t)cc * GM_ROWS] = make_uint4(0, 0, 0, 0);
       Alo[(size_t)cc * GM_ROWS] = make_uint4(0, 0, 0, 0);
     }
     return;
   }
+  const unsigned h = qd >> 1;
+  float dsc = 0.0f, dm = 0.0f;
   if constexpr (DT == KS_Q4K) {
     float dsc_lo, dsc_hi, dm_lo, dm_hi;
     q4k_group_scales(w.hdr, (int)(ks & 3u), dsc_lo, dsc_hi, dm_lo, dm_hi);
-    const float dsc = (h ? dsc_hi : dsc_lo) * 256.0f, dm = (h ? dm_hi : dm_lo) * 256.0f;
+    dsc = (h ? dsc_hi : dsc_lo) * 256.0f;
+    dm = (h ? dm_hi : dm_lo) * 256.0f;
+  }
 #pragma unroll
-    for (int cc = 0; cc < 4; cc++) {
-      float v[8];
-      dequant8(w, h, ks & 3u, cc, dsc, dm, v);
-      uint4 hi, lo;
-      split8(v, hi, lo);
-      Ahi[(size_t)cc * GM_ROWS] = hi;
-      Alo[(size_t)cc * GM_ROWS] = lo;
-    }
-  } else {
+  for (int cc = 0; cc < 2; cc++) {
+    float v[8];
+    if constexpr (DT == KS_Q4K) {
+      const uint32_t wds[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
 #pragma unroll
-    for (int cc = 0; cc < 4; cc++) {
-      float v[8];
-#pragma unroll
-      for (int e = 0; e < 8; e++) {  // element l = 8 cc + e: pair i = l >> 1, byte b = l & 1
-        const int i = 4 * cc + (e >> 1), b = e & 1;
-        const uint32_t lq = (w.ql[i >> 2] >> (8 * (i & 3) + 4 * b)) & 0xFu;
-        const uint32_t hq = (w.qh[i >> 2] >> (4 * (i & 3) + 2 * b)) & 3u;
-        const int q = (int)(lq | (hq << 4)) - 32;
-        v[e] = (cc < 2 ? w.ds0 : w.ds1) * (float)q;
+      for (int e = 0; e < 8; e++) {
+        const uint32_t wd = wds[2 * cc + (e >> 2)] >> (4u * h);
+        const float q = (float)((wd >> (8 * (e & 3))) & 0xFu);
+        v[e] = __fsub_rn(__fmul_rn(dsc, q), dm);  // d*sc*q - dmin*m as gguf_impl.rs:618-633 rounds it, times 2^8
       }
-      uint4 hi, lo;
-      split8(v, hi, lo);
-      Ahi[(size_t)cc * GM_ROWS] = hi;
-      Alo[(size_t)cc * GM_ROWS] = lo;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) {  // element l = 8 cc + e of the 16-run
+        const uint32_t lq = (w.ql[cc] >> (4 * e)) & 0xFu;
+        const uint32_t hq = (w.qh >> (16 * cc + 2 * e)) & 3u;
+        v[e] = w.ds * (float)((int)(lq | (hq << 4)) - 32);
+      }
     }
+    uint4 hi, lo;
+    split8(v, hi, lo);
+    Ahi[(size_t)cc * GM_ROWS] = hi;
+    Alo[(size_t)cc * GM_ROWS] = lo;
   }
 }
 
@@ -240,14 +224,17 @@ __device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, un
 template <int DT>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  // [0,64): mbarriers full[2], freed[2], done; [64,68): tensor-memory address; stages from 1024
+  // [0,32): mbarriers fullB[4]; [32,48): freed[2]; [48,56): done; [64,68): tensor-memory address;
+  // from 1024: two A stages, then the ring of B stages
   const uint32_t bars = sm32(smem);
+  const uint32_t bar_freed = bars + 32u, bar_done = bars + 48u;
   uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 64);
   const unsigned b_bytes = a.np * 256u;                 // hi + lo, 8 chunks, np tokens, 16 bytes
-  const unsigned stage_bytes = GM_A_BYTES + b_bytes;
-  unsigned char* stage0 = smem + 1024;
+  unsigned char* A0 = smem + 1024;
+  unsigned char* B0 = A0 + 2u * GM_A_BYTES;
+  const unsigned nb = a.nb, ahead = nb - 2u;            // B(i + ahead) is requested at step i
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-  const unsigned r = tid & (GM_ROWS - 1), h = tid >> 7;
+  const unsigned r = tid & (GM_ROWS - 1), qd = tid >> 7;
   // which matrix this row tile belongs to (selects, no dynamic indexing of the parameter arrays)
   const unsigned bx = blockIdx.x;
   const int seg = (bx >= a.tile0[1]) + (bx >= a.tile0[2]);
@@ -262,10 +249,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   const unsigned ksteps = ks1 - ks0;
   float* yout = (seg == 0 ? a.y[0] : seg == 1 ? a.y[1] : a.y[2]) + (size_t)blockIdx.y * part_stride;
 
-  Raw<DT> raw;  // weights do not depend on the kernels before this one: fetch the first k-step right away
-  if (live) load_raw(W, a.row_bytes, row, h, ks0, raw);
+  // weights do not depend on the kernels before this one: the first two k-steps are fetched right away
+  Raw<DT> raw0, raw1;
+  if (live) {
+    load_raw(W, a.row_bytes, row, qd, ks0, raw0);
+    if (ksteps > 1) load_raw(W, a.row_bytes, row, qd, ks0 + 1, raw1);
+  }
   if (tid == 0) {
-    for (int i = 0; i < 5; i++) mb_init(bars + 8u * i, 1);
+    for (int i = 0; i < 7; i++) mb_init(bars + 8u * i, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) tc_alloc(sm32(tslot), a.tmem_cols);
@@ -278,31 +269,39 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
   bool ok = true;
   unsigned issued_b = 0;  // thread 0: bulk copies issued
+  if (tid == 0)
+    for (; issued_b < ahead && issued_b < ksteps; issued_b++) {
+      const uint32_t fb = bars + 8u * (issued_b % nb);
+      mb_expect(fb, b_bytes);
+      bulk_in(sm32(B0 + (size_t)(issued_b % nb) * b_bytes), a.xt + (size_t)(ks0 + issued_b) * (b_bytes / 2u), b_bytes, fb);
+    }
   for (unsigned i = 0; i < ksteps; i++) {
     const unsigned ks = ks0 + i, s = i & 1u, u = i >> 1;
-    unsigned char* A = stage0 + (size_t)s * stage_bytes;
-    unsigned char* B = A + GM_A_BYTES;
-    if (u > 0) {  // the MMAs that read this stage two steps ago are done
-      if (ok && !mb_wait(bars + 8u * (2u + s), (u - 1u) & 1u, GM_WAIT)) ok = false;
+    unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
+    if (u > 0) {  // the MMAs of step i - 2 are done: A stage s and B stage (i - 2) % nb are free
+      if (ok && !mb_wait(bar_freed + 8u * s, (u - 1u) & 1u, GM_WAIT)) ok = false;
       tc_fence_after();
     }
-    if (tid == 0 && ok) {
-      mb_expect(bars + 8u * s, b_bytes);
-      bulk_in(sm32(B), a.xt + (size_t)ks * (b_bytes / 2u), b_bytes, bars + 8u * s);
-      issued_b = i + 1;
+    if (tid == 0 && ok && issued_b < ksteps) {  // issued_b == i + ahead here
+      const uint32_t fb = bars + 8u * (issued_b % nb);
+      mb_expect(fb, b_bytes);
+      bulk_in(sm32(B0 + (size_t)(issued_b % nb) * b_bytes), a.xt + (size_t)(ks0 + issued_b) * (b_bytes / 2u), b_bytes, fb);
+      issued_b++;
     }
-    const Raw<DT> cur = raw;
-    if (live && i + 1 < ksteps) load_raw(W, a.row_bytes, row, h, ks + 1, raw);  // in flight while this step is converted
-    dequant_to_stage<DT>(cur, live, h, ks, A, r);
+    const Raw<DT> cur = raw0;
+    raw0 = raw1;
+    if (live && i + 2 < ksteps) load_raw(W, a.row_bytes, row, qd, ks + 2, raw1);  // in flight while two steps are converted
+    dequant_to_stage<DT>(cur, live, qd, ks, A, r);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
     ok = __syncthreads_and(ok);
     if (!ok) break;
     if (tid == 0) {
-      if (!mb_wait(bars + 8u * s, u & 1u, GM_WAIT)) {
+      const unsigned t = i % nb;
+      if (!mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT)) {
         ok = false;
       } else {
         tc_fence_after();
-        const uint32_t a0 = sm32(A), b0 = sm32(B);
+        const uint32_t a0 = sm32(A), b0 = sm32(B0 + (size_t)t * b_bytes);
 #pragma unroll
         for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
           const uint64_t ah = tc_desc(a0 + (2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
@@ -313,20 +312,20 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
           tc_mma_f16(tmem, ah, bl, idesc, 1u);
           tc_mma_f16(tmem, al, bh, idesc, 1u);
         }
-        tc_commit(bars + 8u * (2u + s));
-        if (i + 1 == ksteps) tc_commit(bars + 8u * 4u);
+        tc_commit(bar_freed + 8u * s);
+        if (i + 1 == ksteps) tc_commit(bar_done);
       }
     }
   }
   // all MMAs done (tcgen05.commit tracks every MMA issued before it)
   ok = __syncthreads_and(ok);
-  if (ok && !mb_wait(bars + 8u * 4u, 0u, GM_WAIT)) ok = false;
+  if (ok && !mb_wait(bar_done, 0u, GM_WAIT)) ok = false;
   tc_fence_after();
   if (ok) {
-    // warp w reads lanes 32 (w % 4) .. +31; warps 0-3 take the even 8-column groups, warps 4-7 the odd ones
+    // warp w reads lanes 32 (w % 4) .. +31; the four warps of a lane quarter take every fourth 8-column group
     const unsigned lane_base = (warp & 3u) * 32u;
     const unsigned out_row = row_base + lane_base + lane;
-    for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 16u) {
+    for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 32u) {
       uint32_t v[8];
       tc_ld8(tmem + (lane_base << 16) + c0, v);
       if (out_row < seg_rows) {
@@ -340,9 +339,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
       atomicOr(a.err, 8u);
       // what this thread started must finish before shared and tensor memory go away (bounded): the last bulk
       // copy, and every MMA issued so far (a fresh commit tracks them all)
-      if (issued_b) mb_wait(bars + 8u * ((issued_b - 1u) & 1u), ((issued_b - 1u) >> 1) & 1u, GM_WAIT);
-      tc_commit(bars + 8u * 4u);
-      mb_wait(bars + 8u * 4u, 0u, GM_WAIT);
+      for (unsigned j = issued_b > nb ? issued_b - nb : 0u; j < issued_b; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
+      tc_commit(bar_done);
+      mb_wait(bar_done, 0u, GM_WAIT);
     }
   }
   tc_fence_before();
@@ -388,13 +387,35 @@ __global__ void gemm_finish_kernel(const FinishArgs f) {
 
 namespace {
 unsigned gemm_np(int n_tok) { return ((unsigned)n_tok + 15u) / 16u * 16u; }
-// k splits: enough CTAs to occupy the chip about one and a half times over, at least four k-steps each.
-unsigned gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols) {
+// Shared memory of one CTA and the B stages it gets: the two A stages, then as many B stages as fit, at most four.
+size_t gemm_smem(const ks_ctx* ctx, unsigned np, unsigned* nb_out) {
+  const size_t fixed = 1024 + 2 * (size_t)GM_A_BYTES, bb = (size_t)np * 256;
+  if (fixed + 2 * bb > ctx->smem_optin) return 0;
+  size_t nb = (ctx->smem_optin - fixed) / bb;
+  nb = nb > 4 ? 4 : nb;
+  if (nb_out) *nb_out = (unsigned)nb;
+  return fixed + nb * bb;
+}
+// k splits of a launch over `tiles` row tiles: the count that minimises rounds x (k-steps per CTA + a fixed
+// start-up and epilogue cost of about three k-steps); two CTAs that share an SM cost each other about a fifth.
+unsigned gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok) {
   const unsigned tiles = (unsigned)((rows + GM_ROWS - 1) / GM_ROWS), ksteps = (unsigned)(cols / GM_KSTEP);
-  unsigned s = ((unsigned)ctx->sm_count * 3u / 2u + tiles - 1) / tiles;
-  if (s > ksteps / 4u) s = ksteps / 4u;
-  if (s > 16u) s = 16u;
-  return s < 1u ? 1u : s;
+  const size_t smem = gemm_smem(ctx, gemm_np(n_tok), nullptr);
+  const unsigned cps = smem && 2 * (smem + 1024) <= ctx->smem_optin ? 2u : 1u;
+  const unsigned sms = (unsigned)ctx->sm_count, slots = sms * cps;
+  unsigned best = 1;
+  double best_cost = 1e30;
+  for (unsigned s = 1; s <= 16 && s * 2 <= (ksteps < 2 ? 2 : ksteps); s++) {
+    const unsigned per = (ksteps + s - 1) / s, real = (ksteps + per - 1) / per;
+    if (real != s) continue;  // this count leaves a split empty
+    const unsigned ctas = tiles * s, rounds = (ctas + slots - 1) / slots;
+    const double cost = (double)rounds * (per + 3) * (cps == 2 && ctas > sms ? 1.2 : 1.0);
+    if (cost < best_cost * 0.97) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 bool gemm_covers(ks_dtype wdtype, size_t cols, int n_tok) {
   return (wdtype == KS_Q4K || wdtype == KS_Q6K) && cols % 256 == 0 && n_tok >= 1 && n_tok <= 256;
@@ -443,7 +464,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
   a.tmem_cols = 32;
   while (a.tmem_cols < a.np) a.tmem_cols <<= 1;
   const unsigned ksteps = (unsigned)(cols / GM_KSTEP);
-  unsigned splits = gemm_splits(ctx, total_rows, cols);
+  unsigned splits = gemm_splits(ctx, total_rows, cols, n_tok);
   a.ksteps_per = (ksteps + splits - 1) / splits;
   splits = (ksteps + a.ksteps_per - 1) / a.ksteps_per;
   const bool direct = splits == 1 && mode == 0;
@@ -466,8 +487,8 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     }
   }
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
-  const size_t smem = 1024 + 2 * ((size_t)GM_A_BYTES + (size_t)a.np * 256);
-  if (smem > ctx->smem_optin) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: %zu B of shared memory needed", smem);
+  const size_t smem = gemm_smem(ctx, a.np, &a.nb);
+  if (!smem) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: %u token rows do not fit the shared memory", a.np);
   auto kern = wdtype == KS_Q4K ? gemm_kq_tc_kernel<KS_Q4K> : gemm_kq_tc_kernel<KS_Q6K>;
   static size_t smem_set[2][16] = {{0}};
   size_t& set = smem_set[wdtype == KS_Q4K ? 0 : 1][ctx->device & 15];
@@ -490,7 +511,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
 
 // Floats of partials ks_launch_gemm_segs may write for matrices of `total_rows` rows in all.
 size_t ks_gemm_part_floats(const ks_ctx* ctx, size_t total_rows, size_t cols, int n_tok) {
-  return (size_t)gemm_splits(ctx, total_rows, cols) * (size_t)n_tok * total_rows;
+  return (size_t)gemm_splits(ctx, total_rows, cols, n_tok) * (size_t)n_tok * total_rows;
 }
 
 // y[t * ldy + r] = sum_k W[r, k] x[t * ldx + k] for t < n_tok (<= 256), f32 x and y: operand split, GEMM and, when

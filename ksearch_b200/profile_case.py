@@ -3,6 +3,7 @@ profiler captures are taken on.
 
     python -m ksearch_b200.profile_case matvec --dtype q4k --rows 4096 --cols 4096 --copies 16 --iters 2
     python -m ksearch_b200.profile_case gate_up --rows 6144 --cols 1536 --copies 16 --iters 2
+    python -m ksearch_b200.profile_case matvec --dtype q4k --rows 20480 --cols 2560 --copies 6 --iters 2 --batch 128
     python -m ksearch_b200.profile_case decode --layers 4 --tokens 4
 
 `--copies` distinct weight copies are cycled so that a launch never finds its weights in L2
@@ -29,6 +30,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--tokens", type=int, default=4)
     ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=1, help="token rows per matvec call (more than 8: the tensor-core GEMM)")
     args = ap.parse_args()
     ctx = CudaContext(0, flags=args.pdl)
     eng = Eng()
@@ -53,8 +55,8 @@ def main():
     big = ctx.buffer_empty_bytes(one.nbytes * args.copies * n_mat)
     for c in range(args.copies * n_mat):
         ctx.write_buffer(big, one, c * one.nbytes)
-    x = ctx.buffer_bytes(synth.normals(1, "x", args.cols))
-    y = ctx.buffer_empty_f32(args.rows)
+    x = ctx.buffer_bytes(synth.normals(1, "x", args.cols * args.batch))
+    y = ctx.buffer_empty_f32(args.rows * args.batch)
     lib = ctx.lib
     bufs = [lib.ks_buf_wrap(ctx.h, big.ptr + c * one.nbytes, one.nbytes) for c in range(args.copies * n_mat)]
 
@@ -62,7 +64,7 @@ def main():
         if args.op == "gate_up":
             ctx.check(lib.ks_matvec_gate_up_gelu(ctx.h, args.rows, args.cols, dt, bufs[2 * c], bufs[2 * c + 1], 0, x.h, y.h))
         else:
-            ctx.check(lib.ks_matvec(ctx.h, args.rows, args.cols, dt, bufs[c], 0, 0, x.h, 0, y.h, 0, 1))
+            ctx.check(lib.ks_matvec(ctx.h, args.rows, args.cols, dt, bufs[c], 0, 0, x.h, 0, y.h, 0, args.batch))
 
     for c in range(args.copies):   # first touch
         launch(c)
