@@ -309,6 +309,32 @@ def matvec_shape(ctx, peak, dtype, rows, cols, tag):
             "launches_timed": 5 * ncopy, "cold_l2": f"{ncopy} rotating weight copies ({ncopy * one.nbytes / 1e6:.0f} MB)"}
 
 
+def gemm_shape(ctx, dtype, rows, cols, n_tok, tag):
+    """The tensor-core GEMM behind batches of more than 8 rows (prompt chunks, many slots): rows x cols weights
+    against n_tok token rows, over rotating weight copies larger than L2, one CUDA graph; median of 5.  Each call is
+    the operand split, the GEMM and (when the k range was split) the ordered sum of the partials."""
+    from ksearch_b200 import Q4K, synth
+    lib = ctx.lib
+    one = (synth.q4k_matrix if dtype == Q4K else synth.q6k_matrix)(SEED, tag, rows, cols)
+    ncopy = int(max(3, -(-2 * L2_BYTES // one.nbytes) + 1))
+    big = ctx.buffer_empty_bytes(one.nbytes * ncopy)
+    for c in range(ncopy):
+        ctx.write_buffer(big, one, c * one.nbytes)
+    x = ctx.buffer_bytes(synth.normals(SEED, tag + "/x", cols * n_tok))
+    y = ctx.buffer_empty_f32(rows * n_tok)
+    ctx.check(lib.ks_matvec(ctx.h, rows, cols, dtype, big.h, 0, 0, x.h, 0, y.h, 0, n_tok))   # sizes the scratch, untimed
+    g = graph_of(ctx, [lambda c=c: ctx.check(lib.ks_matvec(ctx.h, rows, cols, dtype, big.h, c * one.nbytes, 0, x.h, 0, y.h, 0, n_tok))
+                       for c in range(ncopy)])
+    ms = median_ms(ctx, lambda: ctx.graph_launch(g), warm=2) / ncopy
+    ctx.graph_free(g)
+    big.free()
+    flops = 2.0 * rows * cols * n_tok
+    return {"shape": f"{'Q4_K' if dtype == Q4K else 'Q6_K'} {rows}x{cols} x {n_tok} rows, fp32 x/y", "us": ms * 1e3,
+            "weight_gbs": one.nbytes / ms / 1e6, "tflops_useful": flops / ms / 1e9,
+            "tflops_issued": 3.0 * flops / ms / 1e9,
+            "note": "three f16 MMAs per product (hi.hi + hi.lo + lo.hi) keep f32 accuracy; bound by the CUDA-core dequantisation"}
+
+
 def attention_shapes(ctx, peak):
     """Decode attention over a Q4_0 cache: 8 query heads on 1 (MQA) and 2 (GQA) KV heads of 256, 4 slots, contexts
     1024 / 4096 / 16384 and the mixed batch; caches rotated so every launch reads its rows from HBM."""
@@ -394,7 +420,8 @@ def serve_e4b(ctx, rank, world, dist, peak, prompt_len=512, n_new=256):
            "prefill_tok_s_total": n_local * world * (prompt_len - 1) / prefill_s,
            "bytes_required_per_round_per_gpu": per_step, "gbs_per_gpu": per_step / (ms / steps) / 1e6,
            "frac_of_measured_peak": per_step / (ms / steps) / 1e6 / peak,
-           "path": "persistent decode kernel" if n_local == 1 else "one launch per op, the slots share each pass over the weights"}
+           "path": "persistent decode kernel" if n_local == 1 else "one launch per op; more slots than the batch matvec stages share one pass through the tensor-core GEMM, "
+                                                                   "prompts run in 128-row GEMM chunks"}
     model.close()
     return res
 
@@ -597,6 +624,9 @@ def main():
             line["matvec_shapes"] = [matvec_shape(ctx, peak, Q4K, r, c, f"cfg1/{r}x{c}")
                                      for r, c in ((1536, 6144), (6144, 1536), (2560, 10240), (10240, 2560))]
             line["attention"] = attention_shapes(ctx, peak)
+            # the reference's own mul_mm check shapes (check_mul_mm.rs:300-304) and one E4B FFN shape at a full chunk
+            line["gemm_shapes"] = [gemm_shape(ctx, Q4K, r, c, t, f"gemm/{r}x{c}x{t}")
+                                   for r, c, t in ((2048, 1536, 256), (4096, 1536, 256), (4096, 1536, 55), (20480, 2560, 128))]
     model.close()
     if want_cpu:
         line["cpu_baseline"], line["parity"] = cpu_baseline_and_parity(cfg, T, prompt, gpu_first)
