@@ -451,6 +451,9 @@ def sharded_matvecs(ctx, rank, world, dist, peak):
         sm = shard.ShardedMatvec(ctx, comm, dtype, rows, cols, W[off:off + nb])
         sm.set_x(x)
         reps = 20
+        # load-time plan search for the local and the whole shape (untimed), as a model's warm_plans does
+        for r_ in (sm.n, rows):
+            lib.ks_plan_search(ctx.h, b"mv_q4k" if dtype == Q4K else b"mv_q6k", r_, 0, cols, 1, None)
 
         def t(fn):
             g = graph_of(ctx, [fn] * reps)

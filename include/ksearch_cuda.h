@@ -49,7 +49,7 @@ typedef enum {
 #define KS_Q4K_BLOCK_BYTES 144
 #define KS_Q6K_BLOCK_BYTES 210
 #define KS_Q40_BLOCK_BYTES 18
-#define KS_SDPA_MAX_SPLITS 64
+#define KS_SDPA_MAX_SPLITS 128
 
 /* ---- runtime: MetalContext (M:16-218) ----------------------------------- */
 ks_ctx* ks_ctx_create(int device, uint64_t flags);          /* M:31-41  MetalContext::new */

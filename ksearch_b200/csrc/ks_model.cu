@@ -207,6 +207,13 @@ Lane chunk_lane(ks_model* m, int slot) {
   return L;
 }
 
+// Context splits of an attention launch over n rows: the rows themselves spread the work over the chip, so each
+// row's context is split only as far as about 256 blocks in all need (never beyond what the scratch was sized for).
+int att_splits_for(const ks_model* m, int n) {
+  int s = ks_sdpa_pick_splits(m->ctx, (size_t)n, (size_t)m->cfg.n_kv, (size_t)m->cfg.max_seq);
+  return s > m->n_splits ? m->n_splits : s;
+}
+
 unsigned row_threads(int n) { return (unsigned)((n + 1 + 31) / 32 * 32); }  // one thread per row and one more
 
 int lane_begin(ks_model* m, const Lane& L, int n) {
@@ -255,7 +262,7 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, m->n_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, att_splits_for(m, n))))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, x2, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
@@ -300,10 +307,7 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
   char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff, *logits = L_.logits;
   float* tok_out = L_.tok_out;
   int rc;
-  // the rows themselves spread attention over the chip: split each row's context only as far as needed to give
-  // every SM two blocks
-  int att_splits = (int)((2 * (size_t)c->sm_count + n * nkv - 1) / (n * nkv));
-  att_splits = att_splits < 1 ? 1 : att_splits > m->n_splits ? m->n_splits : att_splits;
+  const int att_splits = att_splits_for(m, n);
   if ((rc = lane_begin(m, L_, n))) return rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, L_.tok_in, act, x))) return rc;
   if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
@@ -393,7 +397,7 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, m->n_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, att_splits_for(m, n))))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, yb, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;

@@ -234,7 +234,7 @@ def _attn_case(ctx, oracle, e, n_slots, n_q, n_kv, hd, max_t, tlens, starts, sca
 
 
 @pytest.mark.parametrize("n_q,n_kv", [(8, 1), (8, 2)])
-@pytest.mark.parametrize("tlen,n_splits", [(1, 1), (1, 16), (17, 16), (127, 1), (128, 16), (1024, 0), (1000, 64)])
+@pytest.mark.parametrize("tlen,n_splits", [(1, 1), (1, 16), (17, 16), (127, 1), (128, 16), (1024, 0), (1000, 64), (1000, 128), (300, 2)])
 def test_sdpa_single_slot(ctx, oracle, n_q, n_kv, tlen, n_splits):
     _attn_case(ctx, oracle, Eng(F32), 1, n_q, n_kv, 256, 1024, [tlen], [0], 1.0 / 16.0, n_splits)
 
