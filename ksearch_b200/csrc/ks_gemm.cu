@@ -386,6 +386,110 @@ __global__ void gemm_finish_kernel(const FinishArgs f) {
 }  // namespace
 
 namespace {
+// Eight f32 values -> 16 bytes of hi and 16 bytes of lo halves at token t, chunk ck of the B image.
+__device__ __forceinline__ void put_split8(__half* xt, unsigned np, unsigned t, unsigned ck, const float (&v)[8]) {
+  uint4 hi, lo;
+  split8(v, hi, lo);
+  __half* base = xt + ((size_t)(ck >> 3) * 16u + (ck & 7u)) * np * 8u + (size_t)t * 8u;
+  *reinterpret_cast<uint4*>(base) = hi;
+  *reinterpret_cast<uint4*>(base + (size_t)8u * np * 8u) = lo;
+}
+
+// The sum of a matrix's k-split partials straight into what consumes it, one block per token row:
+//   y = sum of partials;  x = res + rms(y) * w_post (lower.rs:3926-4077, the residual update of lib.rs:539);
+//   the image of rms(x) * w_norm for the next GEMM.
+// The f32 normed vector is not stored: on this path only a GEMM reads it.  Rows past n_tok become zeros.
+struct EpiNormArgs {
+  const float* P;
+  size_t part_stride;
+  unsigned splits, n_tok, np, rows;
+  const float *res, *w_post, *w_norm;
+  float eps;
+  float* out_x;
+  __half* xt;
+};
+__global__ void gemm_finish_norm_split_kernel(const EpiNormArgs e) {
+  ks_pdl_entry();
+  __shared__ float red[32];
+  const unsigned t = blockIdx.x, ck = threadIdx.x, chunks = e.rows / 8u;
+  const bool live = ck < chunks && t < e.n_tok;
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) y[i] = 0.0f;
+  const size_t at = (size_t)t * e.rows + 8u * ck;
+  if (live)
+    for (unsigned s = 0; s < e.splits; s++) {
+      const float4 a = *reinterpret_cast<const float4*>(e.P + (size_t)s * e.part_stride + at);
+      const float4 b = *reinterpret_cast<const float4*>(e.P + (size_t)s * e.part_stride + at + 4);
+      y[0] += a.x; y[1] += a.y; y[2] += a.z; y[3] += a.w; y[4] += b.x; y[5] += b.y; y[6] += b.z; y[7] += b.w;
+    }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) ss = fmaf(y[i], y[i], ss);
+  ss = block_sum_f(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)e.rows + e.eps);
+  float v[8], ss2 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) v[i] = 0.0f;
+  if (live) {
+    const float4 r0 = *reinterpret_cast<const float4*>(e.res + at), r1 = *reinterpret_cast<const float4*>(e.res + at + 4);
+    const float4 p0 = *reinterpret_cast<const float4*>(e.w_post + 8u * ck), p1 = *reinterpret_cast<const float4*>(e.w_post + 8u * ck + 4);
+    const float rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w}, pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __fadd_rn(rr[i], __fmul_rn(__fmul_rn(y[i], inv), pp[i]));
+    *reinterpret_cast<float4*>(e.out_x + at) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(e.out_x + at + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) ss2 = fmaf(v[i], v[i], ss2);
+  ss2 = block_sum_f(ss2, red);
+  const float inv2 = 1.0f / sqrtf(ss2 / (float)e.rows + e.eps);
+  if (ck < chunks) {
+    float xn[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) xn[i] = 0.0f;
+    if (live) {
+      const float4 n0 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck), n1 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck + 4);
+      const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++) xn[i] = __fmul_rn(__fmul_rn(v[i], inv2), nn[i]);
+    }
+    put_split8(e.xt, e.np, t, ck, xn);
+  }
+}
+
+// gelu(sum of gate partials) * (sum of up partials) (lib.rs:953) straight into the image the down GEMM reads.
+__global__ void gemm_finish_gelu_split_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok,
+                                              unsigned np, unsigned rows, __half* xt) {
+  ks_pdl_entry();
+  const unsigned chunks = rows / 8u;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)np * chunks) return;
+  const unsigned t = (unsigned)(i / chunks), ck = (unsigned)(i % chunks);
+  float v[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) v[k] = 0.0f;
+  if (t < n_tok) {
+    float g[8], u[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) g[k] = u[k] = 0.0f;
+    const size_t at = (size_t)t * rows + 8u * ck;
+    for (unsigned s = 0; s < splits; s++) {
+      const float4 a = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at);
+      const float4 b = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at + 4);
+      const float4 c = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at);
+      const float4 d = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at + 4);
+      g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+      u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w; u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = gelu_mul(g[k], u[k]);
+  }
+  put_split8(xt, np, t, ck, v);
+}
+}  // namespace
+
+namespace {
 unsigned gemm_np(int n_tok) { return ((unsigned)n_tok + 15u) / 16u * 16u; }
 // Shared memory of one CTA and the B stages it gets: the two A stages, then as many B stages as fit, at most four.
 size_t gemm_smem(const ks_ctx* ctx, unsigned np, unsigned* nb_out) {
@@ -439,8 +543,11 @@ int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, siz
 // matrix) and a second launch sums them in split order into y.  mode 1 (two matrices, gate and up): y[0] =
 // gelu(gate) * up, always through P.  `xt` is the image ks_launch_gemm_split made of the same token rows.
 int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* const* W, const size_t* rows, size_t cols, const void* xt,
-                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode) {
+                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode, const ks_gemm_epi* epi) {
   if (!gemm_covers(wdtype, cols, n_tok) || n_seg < 1 || n_seg > 3) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
+  if ((mode == KS_GEMM_NORM_SPLIT && (n_seg != 1 || !epi || rows[0] % 8 || rows[0] > 8192)) ||
+      (mode == KS_GEMM_GELU_SPLIT && (n_seg != 2 || !epi || rows[0] != rows[1] || rows[0] % 8)))
+    return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad epilogue arguments");
   GemmArgs a{};
   FinishArgs f{};
   unsigned tiles = 0;
@@ -467,7 +574,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
   unsigned splits = gemm_splits(ctx, total_rows, cols, n_tok);
   a.ksteps_per = (ksteps + splits - 1) / splits;
   splits = (ksteps + a.ksteps_per - 1) / a.ksteps_per;
-  const bool direct = splits == 1 && mode == 0;
+  const bool direct = splits == 1 && mode == KS_GEMM_PLAIN;
   size_t poff = 0;
   for (int i = 0; i < n_seg; i++) {
     if (direct) {
@@ -481,8 +588,10 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
       f.P[i] = a.y[i];
       f.part_stride[i] = a.part_stride[i];
       f.rows[i] = (unsigned)rows[i];
-      f.y[i] = mode == 1 ? y[0] : y[i];
-      f.ldy[i] = mode == 1 ? ldy[0] : ldy[i];
+      if (mode == KS_GEMM_PLAIN || mode == KS_GEMM_GELU) {
+        f.y[i] = mode == KS_GEMM_GELU ? y[0] : y[i];
+        f.ldy[i] = mode == KS_GEMM_GELU ? ldy[0] : ldy[i];
+      }
       poff += (size_t)splits * n_tok * rows[i];
     }
   }
@@ -500,11 +609,34 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
   KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS, smem, a);
   int rc = ks_after_launch(ctx, "gemm_kq_tc");
   if (rc || direct) return rc;
+  if (mode == KS_GEMM_NORM_SPLIT) {
+    EpiNormArgs e{};
+    e.P = a.y[0];
+    e.part_stride = a.part_stride[0];
+    e.splits = splits;
+    e.n_tok = (unsigned)n_tok;
+    e.np = a.np;
+    e.rows = (unsigned)rows[0];
+    e.res = epi->res;
+    e.w_post = epi->w_post;
+    e.w_norm = epi->w_norm;
+    e.eps = epi->eps;
+    e.out_x = epi->out_x;
+    e.xt = (__half*)epi->xt_out;
+    KS_LAUNCH(ctx, (gemm_finish_norm_split_kernel), a.np, (unsigned)((rows[0] / 8 + 31) / 32 * 32), 0, e);
+    return ks_after_launch(ctx, "gemm_finish_norm_split");
+  }
+  if (mode == KS_GEMM_GELU_SPLIT) {
+    const size_t n = (size_t)a.np * (rows[0] / 8);
+    KS_LAUNCH(ctx, (gemm_finish_gelu_split_kernel), (unsigned)((n + 255) / 256), 256, 0, (const float*)a.y[0], (const float*)a.y[1],
+              a.part_stride[0], splits, (unsigned)n_tok, a.np, (unsigned)rows[0], (__half*)epi->xt_out);
+    return ks_after_launch(ctx, "gemm_finish_gelu_split");
+  }
   f.n_seg = (unsigned)n_seg;
   f.splits = splits;
   f.n_tok = (unsigned)n_tok;
   f.mode = mode;
-  const size_t n = (size_t)n_tok * (mode == 1 ? rows[0] : total_rows);
+  const size_t n = (size_t)n_tok * (mode == KS_GEMM_GELU ? rows[0] : total_rows);
   KS_LAUNCH(ctx, (gemm_finish_kernel), (unsigned)((n + 255) / 256), 256, 0, f);
   return ks_after_launch(ctx, "gemm_finish");
 }
@@ -522,5 +654,5 @@ int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, co
   int rc = ks_launch_gemm_split(ctx, x, ldx, n_tok, cols, scratch);
   if (rc) return rc;
   float* P = (float*)((char*)scratch + ks_gemm_xt_bytes(cols, n_tok));
-  return ks_launch_gemm_segs(ctx, wdtype, 1, &W, &rows, cols, scratch, n_tok, &y, &ldy, P, 0);
+  return ks_launch_gemm_segs(ctx, wdtype, 1, &W, &rows, cols, scratch, n_tok, &y, &ldy, P, KS_GEMM_PLAIN, nullptr);
 }

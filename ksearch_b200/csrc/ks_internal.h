@@ -153,10 +153,19 @@ size_t ks_gemm_part_floats(const ks_ctx* ctx, size_t total_rows, size_t cols, in
 int ks_ctx_gemm_scratch(ks_ctx* ctx, size_t bytes, void** out);
 // x[t * ldx + k] (f32) -> the image the GEMM reads its token rows from.
 int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt);
-// Up to three matrices over the same columns and token rows (q, k, v; gate, up) in one launch; mode 1: two
-// matrices, y[0] = gelu(W[0] x) * (W[1] x).  P: ks_gemm_part_floats(sum of rows) floats.
+// Up to three matrices over the same columns and token rows (q, k, v; gate, up) in one launch.  What becomes of
+// the sums: PLAIN y[i] = W[i] x; GELU (two matrices) y[0] = gelu(W[0] x) * (W[1] x); NORM_SPLIT (one matrix)
+// out_x = res + rms(W x) * w_post and the image of rms(out_x) * w_norm for the next GEMM in xt_out; GELU_SPLIT
+// (two matrices) the image of gelu(W[0] x) * (W[1] x) in xt_out.  P: ks_gemm_part_floats(sum of rows) floats.
+enum { KS_GEMM_PLAIN = 0, KS_GEMM_GELU = 1, KS_GEMM_NORM_SPLIT = 2, KS_GEMM_GELU_SPLIT = 3 };
+struct ks_gemm_epi {
+  const float *res, *w_post, *w_norm;  // NORM_SPLIT: residual rows [n_tok, rows], the two norm weights
+  float eps;
+  float* out_x;                        // NORM_SPLIT: the updated residual rows
+  void* xt_out;                        // the image written for the next GEMM (may be the image this GEMM read)
+};
 int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* const* W, const size_t* rows, size_t cols, const void* xt,
-                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode);
+                        int n_tok, float* const* y, const size_t* ldy, float* P, int mode, const ks_gemm_epi* epi);
 // Split + GEMM for one matrix.  Returns 1 when the shape is not covered (cols not a multiple of 256, more than
 // 256 rows).  scratch: ks_gemm_xt_bytes + 4 * ks_gemm_part_floats bytes.
 int ks_launch_gemm_kq(ks_ctx* ctx, ks_dtype wdtype, size_t rows, size_t cols, const uint8_t* W, const float* x, size_t ldx, float* y,

@@ -286,15 +286,6 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   return ks_after_launch(c, "collect");
 }
 
-// y[t, :] = W x[t, :] for the n rows whose split image is in m->gemm_xt (tensor-core GEMM; k-split partials are
-// summed in order by a second launch).
-int gemm_rows(ks_model* m, ks_dtype dt, const void* W, size_t rows, size_t cols, int n, char* y, size_t ldy) {
-  ks_ctx* c = m->ctx;
-  const uint8_t* Ws[1] = {(const uint8_t*)W};
-  float* ys[1] = {(float*)y};
-  return ks_launch_gemm_segs(c, dt, 1, Ws, &rows, cols, m->gemm_xt, n, ys, &ldy, m->gemm_p0, 0);
-}
-
 // The same op order for 9..KS_GEMM_CHUNK rows (a prompt chunk, or more slots than the batch matvec stages side by
 // side): the matrices go through the tensor-core GEMM, the reference's mul_mm route (forward_prefill_chunk,
 // gemma_prim.rs:1317-1607); norms, RoPE/KV pack, attention and GELU are the row-wise kernels above.  f32 only.
@@ -304,21 +295,28 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
   const ks_dtype act = KS_F32;
   const size_t H = g.hidden, F = g.ffn, hd = g.hd, nq = g.n_q, nkv = g.n_kv;
   const size_t qn = nq * hd, kvn = nkv * hd;
-  char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *ff = L_.ff, *logits = L_.logits;
+  char *x = L_.x, *x2 = L_.x2, *q = L_.q, *k = L_.k, *v = L_.v, *o = L_.o, *logits = L_.logits;
   float* tok_out = L_.tok_out;
   int rc;
   const int att_splits = att_splits_for(m, n);
   if ((rc = lane_begin(m, L_, n))) return rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, n, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, L_.tok_in, act, x))) return rc;
   if ((rc = ks_launch_rmsnorm(c, H, n, g.eps, act, x, m->layers[0].attn_norm.dptr, nullptr, 0, 0.f, x2))) return rc;
+  if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
+  // From here on the normed rows exist only as the image the next GEMM reads: the sums of the o-proj and
+  // down-proj partials go straight through the residual update and the next norm into that image.
+  ks_gemm_epi epi{};
+  epi.eps = g.eps;
+  epi.res = (const float*)x;
+  epi.out_x = (float*)x;
+  epi.xt_out = m->gemm_xt;
   for (int l = 0; l < g.n_layers; l++) {
     const Layer& L = m->layers[l];
-    if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
     {  // q, k and v rows in one launch (lib.rs:227)
       const uint8_t* Ws[3] = {(const uint8_t*)L.wq.dptr, (const uint8_t*)L.wk.dptr, (const uint8_t*)L.wv.dptr};
       float* ys[3] = {(float*)q, (float*)k, (float*)v};
       const size_t rs[3] = {qn, kvn, kvn};
-      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 3, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, 0))) return rc;
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 3, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, KS_GEMM_PLAIN, nullptr))) return rc;
     }
     uint8_t* kk = m->kv_k[l] + L_.kv_off;
     uint8_t* kv = m->kv_v[l] + L_.kv_off;
@@ -328,25 +326,35 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
     if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, L_.meta, L_.attn_tmp, o, att_splits)))
       return rc;
     if ((rc = ks_launch_gemm_split(c, (const float*)o, qn, n, qn, m->gemm_xt))) return rc;
-    if ((rc = gemm_rows(m, KS_Q4K, L.wo.dptr, H, qn, n, x2, H))) return rc;
-    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_attn_norm.dptr, x, L.ffn_norm.dptr, x, x2))) return rc;
-    // gate and up share the operand image; their partials meet in the GeGLU epilogue (lib.rs:953)
-    if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
-    {
-      const uint8_t* Ws[2] = {(const uint8_t*)L.wgate.dptr, (const uint8_t*)L.wup.dptr};
-      float* ys[2] = {(float*)ff, (float*)ff};
-      const size_t rs[2] = {F, F};
-      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 2, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, 1))) return rc;
+    {  // o-proj, x += rms(.) * w_post_attn, image of rms(x) * w_ffn_norm (lib.rs:539)
+      const uint8_t* Ws[1] = {(const uint8_t*)L.wo.dptr};
+      float* ys[1] = {nullptr};
+      epi.w_post = (const float*)L.post_attn_norm.dptr;
+      epi.w_norm = (const float*)L.ffn_norm.dptr;
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 1, Ws, &H, qn, m->gemm_xt, n, ys, &H, m->gemm_p0, KS_GEMM_NORM_SPLIT, &epi))) return rc;
     }
-    if ((rc = ks_launch_gemm_split(c, (const float*)ff, F, n, F, m->gemm_xt))) return rc;
-    if ((rc = gemm_rows(m, KS_Q4K, L.wdown.dptr, H, F, n, x2, H))) return rc;
-    const void* next_norm = (l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr;
-    if ((rc = ks_launch_rmsnorm_add_then_rmsnorm(c, H, n, g.eps, act, x2, L.post_ffw_norm.dptr, x, next_norm, x, x2))) return rc;
+    {  // gate and up share the operand image; their partials meet in the GeGLU epilogue (lib.rs:953)
+      const uint8_t* Ws[2] = {(const uint8_t*)L.wgate.dptr, (const uint8_t*)L.wup.dptr};
+      float* ys[2] = {nullptr, nullptr};
+      const size_t rs[2] = {F, F};
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 2, Ws, rs, H, m->gemm_xt, n, ys, rs, m->gemm_p0, KS_GEMM_GELU_SPLIT, &epi))) return rc;
+    }
+    {  // down-proj, x += rms(.) * w_post_ffw, image of the NEXT norm (next layer's attn norm, or the output norm)
+      const uint8_t* Ws[1] = {(const uint8_t*)L.wdown.dptr};
+      float* ys[1] = {nullptr};
+      epi.w_post = (const float*)L.post_ffw_norm.dptr;
+      epi.w_norm = (const float*)((l + 1 < g.n_layers) ? m->layers[l + 1].attn_norm.dptr : m->output_norm.dptr);
+      if ((rc = ks_launch_gemm_segs(c, KS_Q4K, 1, Ws, &H, F, m->gemm_xt, n, ys, &H, m->gemm_p0, KS_GEMM_NORM_SPLIT, &epi))) return rc;
+    }
   }
   if ((rc = lane_end(m, L_, n))) return rc;
   if (!want_logits) return KS_OK;
-  if ((rc = ks_launch_gemm_split(c, (const float*)x2, H, n, H, m->gemm_xt))) return rc;
-  if ((rc = gemm_rows(m, (ks_dtype)g.embd_dtype, m->token_embd.dptr, g.vocab, H, n, logits, g.vocab))) return rc;
+  {
+    const uint8_t* Ws[1] = {(const uint8_t*)m->token_embd.dptr};
+    float* ys[1] = {(float*)logits};
+    const size_t V = (size_t)g.vocab;
+    if ((rc = ks_launch_gemm_segs(c, (ks_dtype)g.embd_dtype, 1, Ws, &V, H, m->gemm_xt, n, ys, &V, m->gemm_p0, KS_GEMM_PLAIN, nullptr))) return rc;
+  }
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * 4, tok_out + s))) return rc;
   KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
