@@ -128,10 +128,12 @@ int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_o
                ks_buf* dst_f32, size_t dst_off);
 
 /* ---- matvec family ------------------------------------------------------- */
-/* y[t, r] = sum_c deq(W)[r, c] * x[t, c], t < n_tok (1..8).  x is [n_tok, cols],
+/* y[t, r] = sum_c deq(W)[r, c] * x[t, c], t < n_tok (1..256).  x is [n_tok, cols],
  * y is [n_tok, rows].  K:137 matvec_wd, K:1446 matvec_wd_at (offsets),
- * K:1414 matvec_batch for 2 <= n_tok <= 8.  The weight matrix is streamed once
- * for all n_tok tokens. */
+ * K:1414 matvec_batch: up to 8 rows share one GEMV pass over the weights; 9..256 rows take the route the
+ * reference gives to mul_mm (crates/ksearch_codegen/src/render.rs:1073-1291), here a tensor-core GEMM
+ * (f32 activations, Q4K / Q6K weights, cols a multiple of 256, x_off a multiple of 4).  The first such call
+ * grows a scratch buffer inside the context: make it outside any ks_graph capture. */
 int ks_matvec(ks_ctx* ctx, size_t rows, size_t cols, ks_dtype wdtype, const ks_buf* W, size_t w_byte_off,
               ks_dtype act, const ks_buf* x, size_t x_off, ks_buf* y, size_t y_off, int n_tok);
 /* K:227 matvec_qkv_wds: three outputs in one launch. */
@@ -231,7 +233,7 @@ int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_b
 typedef struct ks_model ks_model;
 typedef struct {              /* the GemmaConfig fields the dense path uses (crates/ksearch_gemma/src/lib.rs:14-36) */
   int n_layers, hidden, ffn, n_q, n_kv, hd, vocab, max_seq;
-  int n_slots;                /* KvPool max_batch (1..8): slots that can advance in one weight pass */
+  int n_slots;                /* KvPool max_batch (1..64): slots that can advance together */
   float eps, rope_theta, softcap, attn_scale;   /* attn_scale: the reference uses 1 */
   int embd_dtype;             /* ks_dtype of the tied token_embd / lm_head: KS_Q4K or KS_Q6K */
   int act;                    /* ks_dtype of activations and norm weights: KS_F32 or KS_F16 */
@@ -257,10 +259,11 @@ int ks_model_slot_reset(ks_model* m, int slot);                              /* 
 int ks_model_slot_seq_len(const ks_model* m, int slot);                      /* KV:161 seq_len */
 int ks_model_slot_active(const ks_model* m);                                 /* KV:179 active_batch().len() */
 int ks_model_forward(ks_model* m, int first_slot, int n_slots, const int* tokens, int want_logits);   /* GP:881 forward_token, enqueue only */
-/* Prompt tokens of one slot without logits, eight per pass over the weights (the rows of a chunk attend
- * causally inside the chunk).  Stands in for GemmaPrimModel::prefill_chunk
- * (crates/ksearch_gemma/src/gemma_prim.rs:1305-1315) with the batch GEMV (crates/ksearch_kernels/src/lib.rs:1414)
- * in place of the mul_mm GEMM.  The slot advances by n_tokens; enqueues only. */
+/* Prompt tokens of one slot without logits, up to 128 per pass over the weights (the rows of a chunk attend
+ * causally inside the chunk).  GemmaPrimModel::prefill_chunk (crates/ksearch_gemma/src/gemma_prim.rs:1305-1315):
+ * chunks of more than 8 rows run every matrix through the tensor-core GEMM (the reference's mul_mm), shorter
+ * ones through the batch GEMV (crates/ksearch_kernels/src/lib.rs:1414).  The slot advances by n_tokens;
+ * enqueues only, apart from the wait for the pinned staging words between chunks. */
 int ks_model_prefill(ks_model* m, int slot, const int* tokens, int n_tokens);
 int ks_model_decode_token(ks_model* m, int first_slot, int n_slots, const int* tokens, int* next);    /* GP:1616 decode_token, blocking */
 int ks_model_generate(ks_model* m, int slot, const int* prompt, int n_prompt, int n_new, int max_inflight,
