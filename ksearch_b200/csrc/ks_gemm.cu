@@ -14,8 +14,9 @@
 //     term out of the f16 denormal range), split the same way and stored as core matrices.
 //   * Three MMAs per 16 k: Ahi.Bhi + Ahi.Blo + Alo.Bhi; the dropped lo.lo term is below 2^-22 relative, so the
 //     result matches f32 arithmetic (the reference's single half operands give ~1e-3).
-//   * Two A stages: while the tensor core works on one, the threads dequantise the next; tcgen05.commit on an
-//     mbarrier hands a stage back.  The B copies run up to two k-steps ahead in a ring of up to four stages, the
+//   * Warp-specialised: 16 warps dequantise into two A stages and signal each one full on an mbarrier (one arrival
+//     per warp); a 17th warp's first lane requests the B copies, waits for both operands of a step, issues the MMAs
+//     and lets tcgen05.commit hand the stage back on another mbarrier.  No block-wide barrier inside the k loop.  The B copies run up to two k-steps ahead in a ring of up to four stages, the
 //     packed weights two k-steps ahead in registers.  The accumulator (128 lanes x N columns) is read back with tcgen05.ld, scaled
 //     by 2^-8 and stored coalesced along the weight-row index.
 // Every wait is bounded; on expiry the CTA raises the context's status word, waits (bounded) for what it has in
@@ -30,7 +31,7 @@ namespace {
 
 constexpr int GM_ROWS = 128;        // weight rows per CTA (M of the MMA)
 constexpr int GM_KSTEP = 64;        // k per stage: one Q4_K scale pair, half of a Q6_K 128-run
-constexpr int GM_THREADS = 512;     // four threads per weight row and k-step
+constexpr int GM_THREADS = 512;     // dequantising threads: four per weight row and k-step (one more warp issues the MMAs)
 constexpr unsigned GM_A_BYTES = 2u * 8u * GM_ROWS * 16u;  // hi + lo, 8 k-chunks, 128 rows, 16 bytes: 32 KB
 constexpr unsigned GM_WAIT = 1u << 20;
 
@@ -47,7 +48,7 @@ struct GemmArgs {
   unsigned cols, n_tok, np;        // np: token count padded to a multiple of 16 (<= 256)
   unsigned tmem_cols;              // power of two >= max(32, np)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
-  unsigned nb;                     // B stages (2..4): token rows are requested nb - 2 k-steps ahead
+  unsigned nb;                     // B stages (2..4): token rows are requested up to nb - 2 k-steps ahead
   unsigned* err;
 };
 
@@ -222,17 +223,18 @@ __device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, un
 // grid = (row tiles, k splits): CTA (bx, by) multiplies rows [128 bx, +128) over k-steps [by * per, (by + 1) * per)
 // and stores its sums at y + by * part_stride (a partial when there is more than one split).
 template <int DT>
-__global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArgs a) {
+__global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  // [0,32): mbarriers fullB[4]; [32,48): freed[2]; [48,56): done; [64,68): tensor-memory address;
+  // [0,32): mbarriers fullB[4]; [32,48): freed[2]; [48,56): done; [64,80): fullA[2]; [96,100): tensor-memory address;
   // from 1024: two A stages, then the ring of B stages
   const uint32_t bars = sm32(smem);
-  const uint32_t bar_freed = bars + 32u, bar_done = bars + 48u;
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 64);
+  const uint32_t bar_freed = bars + 32u, bar_done = bars + 48u, bar_fullA = bars + 64u;
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 96);
+  volatile unsigned* fail = reinterpret_cast<volatile unsigned*>(smem + 100);  // a bounded wait gave up somewhere in the CTA
   const unsigned b_bytes = a.np * 256u;                 // hi + lo, 8 chunks, np tokens, 16 bytes
   unsigned char* A0 = smem + 1024;
   unsigned char* B0 = A0 + 2u * GM_A_BYTES;
-  const unsigned nb = a.nb, ahead = nb - 2u;            // B(i + ahead) is requested at step i
+  const unsigned nb = a.nb;                             // B stages: the copies run up to nb - 1 steps ahead
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   const unsigned r = tid & (GM_ROWS - 1), qd = tid >> 7;
   // which matrix this row tile belongs to (selects, no dynamic indexing of the parameter arrays)
@@ -250,13 +252,16 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   float* yout = (seg == 0 ? a.y[0] : seg == 1 ? a.y[1] : a.y[2]) + (size_t)blockIdx.y * part_stride;
 
   // weights do not depend on the kernels before this one: the first two k-steps are fetched right away
+  const bool producer = warp < GM_THREADS / 32;  // warps 0..15 dequantise, warp 16 feeds the tensor core
   Raw<DT> raw0, raw1;
-  if (live) {
+  if (producer && live) {
     load_raw(W, a.row_bytes, row, qd, ks0, raw0);
     if (ksteps > 1) load_raw(W, a.row_bytes, row, qd, ks0 + 1, raw1);
   }
   if (tid == 0) {
-    for (int i = 0; i < 7; i++) mb_init(bars + 8u * i, 1);
+    for (int i = 0; i < 7; i++) mb_init(bars + 8u * i, 1);                 // fullB[4], freed[2], done: one arrival each
+    for (int i = 0; i < 2; i++) mb_init(bar_fullA + 8u * i, GM_THREADS / 32);  // fullA[2]: one arrival per producer warp
+    *fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) tc_alloc(sm32(tslot), a.tmem_cols);
@@ -266,62 +271,80 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
   const uint32_t tmem = *tslot;
   ks_pdl_entry();  // the B image comes from the kernel before this one
 
-  const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
-  bool ok = true;
-  unsigned issued_b = 0;  // thread 0: bulk copies issued
-  if (tid == 0)
-    for (; issued_b < ahead && issued_b < ksteps; issued_b++) {
-      const uint32_t fb = bars + 8u * (issued_b % nb);
-      mb_expect(fb, b_bytes);
-      bulk_in(sm32(B0 + (size_t)(issued_b % nb) * b_bytes), a.xt + (size_t)(ks0 + issued_b) * (b_bytes / 2u), b_bytes, fb);
-    }
-  for (unsigned i = 0; i < ksteps; i++) {
-    const unsigned ks = ks0 + i, s = i & 1u, u = i >> 1;
-    unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
-    if (u > 0) {  // the MMAs of step i - 2 are done: A stage s and B stage (i - 2) % nb are free
-      if (ok && !mb_wait(bar_freed + 8u * s, (u - 1u) & 1u, GM_WAIT)) ok = false;
-      tc_fence_after();
-    }
-    if (tid == 0 && ok && issued_b < ksteps) {  // issued_b == i + ahead here
-      const uint32_t fb = bars + 8u * (issued_b % nb);
-      mb_expect(fb, b_bytes);
-      bulk_in(sm32(B0 + (size_t)(issued_b % nb) * b_bytes), a.xt + (size_t)(ks0 + issued_b) * (b_bytes / 2u), b_bytes, fb);
-      issued_b++;
-    }
-    const Raw<DT> cur = raw0;
-    raw0 = raw1;
-    if (live && i + 2 < ksteps) load_raw(W, a.row_bytes, row, qd, ks + 2, raw1);  // in flight while two steps are converted
-    dequant_to_stage<DT>(cur, live, qd, ks, A, r);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    if (tid == 0) {
-      const unsigned t = i % nb;
-      if (!mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT)) {
-        ok = false;
-      } else {
-        tc_fence_after();
-        const uint32_t a0 = sm32(A), b0 = sm32(B0 + (size_t)t * b_bytes);
-#pragma unroll
-        for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
-          const uint64_t ah = tc_desc(a0 + (2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
-          const uint64_t al = tc_desc(a0 + (8u + 2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
-          const uint64_t bh = tc_desc(b0 + (2u * j) * (a.np * 16u), a.np * 16u, 128u);
-          const uint64_t bl = tc_desc(b0 + (8u + 2u * j) * (a.np * 16u), a.np * 16u, 128u);
-          tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
-          tc_mma_f16(tmem, ah, bl, idesc, 1u);
-          tc_mma_f16(tmem, al, bh, idesc, 1u);
-        }
-        tc_commit(bar_freed + 8u * s);
-        if (i + 1 == ksteps) tc_commit(bar_done);
+  if (producer) {
+    // ---- 16 warps: packed weights -> two f16 terms -> A stage; no block-wide barrier inside the loop
+    for (unsigned i = 0; i < ksteps; i++) {
+      const unsigned ks = ks0 + i, s = i & 1u, u = i >> 1;
+      unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
+      if (u > 0 && !mb_wait(bar_freed + 8u * s, (u - 1u) & 1u, GM_WAIT)) {  // the MMAs of step i - 2 still read this stage
+        *fail = 1;
+        break;
       }
+      const Raw<DT> cur = raw0;
+      raw0 = raw1;
+      if (live && i + 2 < ksteps) load_raw(W, a.row_bytes, row, qd, ks + 2, raw1);  // in flight while two steps are converted
+      dequant_to_stage<DT>(cur, live, qd, ks, A, r);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_fullA + 8u * s) : "memory");
+    }
+  } else if (lane == 0) {
+    // ---- one thread: token-row copies ahead, MMAs as soon as both operands of a step are there
+    const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
+    unsigned issued_b = 0;
+    bool ok = true;
+    for (unsigned i = 0; i < ksteps && ok; i++) {
+      const unsigned s = i & 1u, u = i >> 1, t = i % nb;
+      // B(j) goes into stage j % nb, last read by the MMAs of step j - nb; copies run up to nb - 2 steps ahead, so
+      // the stage they overwrite belongs to a step whose MMAs ended long ago (never the one just issued)
+      while (ok && issued_b < ksteps && issued_b < i + nb - 1u) {
+        const unsigned j = issued_b;
+        if (j >= nb) {  // wait for the MMAs of step j - nb (they committed to freed[(j - nb) & 1])
+          const unsigned k = j - nb;
+          if (!mb_wait(bar_freed + 8u * (k & 1u), (k >> 1) & 1u, GM_WAIT)) {
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t fb = bars + 8u * (j % nb);
+        mb_expect(fb, b_bytes);
+        bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
+        issued_b++;
+      }
+      if (!ok || !mb_wait(bar_fullA + 8u * s, u & 1u, GM_WAIT) || !mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t a0 = sm32(A0 + (size_t)s * GM_A_BYTES), b0 = sm32(B0 + (size_t)t * b_bytes);
+#pragma unroll
+      for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
+        const uint64_t ah = tc_desc(a0 + (2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
+        const uint64_t al = tc_desc(a0 + (8u + 2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
+        const uint64_t bh = tc_desc(b0 + (2u * j) * (a.np * 16u), a.np * 16u, 128u);
+        const uint64_t bl = tc_desc(b0 + (8u + 2u * j) * (a.np * 16u), a.np * 16u, 128u);
+        tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
+        tc_mma_f16(tmem, ah, bl, idesc, 1u);
+        tc_mma_f16(tmem, al, bh, idesc, 1u);
+      }
+      tc_commit(bar_freed + 8u * s);
+      if (i + 1 == ksteps) tc_commit(bar_done);
+    }
+    if (!ok) {
+      *fail = 1;
+      // what this thread started must finish before shared and tensor memory go away (bounded): the copies still in
+      // flight, and every MMA issued so far (a fresh commit tracks them all)
+      for (unsigned j = issued_b > nb ? issued_b - nb : 0u; j < issued_b; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
+      tc_commit(bar_done);
+      mb_wait(bar_done, 0u, GM_WAIT);
     }
   }
+  __syncthreads();
+  bool ok = *fail == 0;
   // all MMAs done (tcgen05.commit tracks every MMA issued before it)
-  ok = __syncthreads_and(ok);
   if (ok && !mb_wait(bar_done, 0u, GM_WAIT)) ok = false;
   tc_fence_after();
-  if (ok) {
+  if (ok && producer) {
     // warp w reads lanes 32 (w % 4) .. +31; the four warps of a lane quarter take every fourth 8-column group
     const unsigned lane_base = (warp & 3u) * 32u;
     const unsigned out_row = row_base + lane_base + lane;
@@ -334,15 +357,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_kq_tc_kernel(const GemmArg
           if (c0 + e < a.n_tok) yout[(size_t)(c0 + e) * ldy + out_row] = __uint_as_float(v[e]) * (1.0f / 256.0f);
       }
     }
-  } else {
-    if (tid == 0) {
-      atomicOr(a.err, 8u);
-      // what this thread started must finish before shared and tensor memory go away (bounded): the last bulk
-      // copy, and every MMA issued so far (a fresh commit tracks them all)
-      for (unsigned j = issued_b > nb ? issued_b - nb : 0u; j < issued_b; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
-      tc_commit(bar_done);
-      mb_wait(bar_done, 0u, GM_WAIT);
-    }
+  } else if (!ok && tid == 0) {
+    atomicOr(a.err, 8u);
   }
   tc_fence_before();
   __syncthreads();
@@ -507,6 +523,10 @@ unsigned gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok) {
   const size_t smem = gemm_smem(ctx, gemm_np(n_tok), nullptr);
   const unsigned cps = smem && 2 * (smem + 1024) <= ctx->smem_optin ? 2u : 1u;
   const unsigned sms = (unsigned)ctx->sm_count, slots = sms * cps;
+  if (const char* f = getenv("KSEARCH_GEMM_SPLITS")) {  // measurement override
+    const unsigned s = (unsigned)atoi(f);
+    if (s >= 1 && s <= 16 && s * 2 <= (ksteps < 2 ? 2 : ksteps)) return s;
+  }
   unsigned best = 1;
   double best_cost = 1e30;
   for (unsigned s = 1; s <= 16 && s * 2 <= (ksteps < 2 ? 2 : ksteps); s++) {
@@ -606,7 +626,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "gemm: cannot set %zu B shared memory: %s", smem, cudaGetErrorString(e));
     set = smem;
   }
-  KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS, smem, a);
+  KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS + 32, smem, a);
   int rc = ks_after_launch(ctx, "gemm_kq_tc");
   if (rc || direct) return rc;
   if (mode == KS_GEMM_NORM_SPLIT) {
