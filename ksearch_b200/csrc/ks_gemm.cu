@@ -173,9 +173,34 @@ __device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, uns
   w.ds = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * 256.0f * (float)sc;
 }
 
+// 2^8 d sc and 2^8 dmin m of the four sub-blocks 2j + h (j = 0..3) of a Q4_K super-block: get_scale_min_k4
+// (gguf_impl.rs:563-573) for the half h this thread always works on, decoded once per super-block instead of once
+// per k-step.
+struct Q4Scales {
+  float dsc[4], dm[4];
+};
+__device__ __forceinline__ void q4k_half_scales(const uint4 hdr, unsigned h, Q4Scales& o) {
+  const __half2 dd = *reinterpret_cast<const __half2*>(&hdr.x);
+  const float d = __low2float(dd) * 256.0f, dmin = __high2float(dd) * 256.0f;
+  const unsigned sh = 8u * h;
+  // bytes q[h], q[2+h] | q[4+h], q[6+h] | q[8+h], q[10+h] of the 12 scale bytes
+  const unsigned a0 = (hdr.y >> sh) & 0xFFu, a2 = (hdr.y >> (16u + sh)) & 0xFFu;
+  const unsigned b0 = (hdr.z >> sh) & 0xFFu, b2 = (hdr.z >> (16u + sh)) & 0xFFu;
+  const unsigned c0 = (hdr.w >> sh) & 0xFFu, c2 = (hdr.w >> (16u + sh)) & 0xFFu;
+  o.dsc[0] = d * (float)(a0 & 63u);
+  o.dm[0] = dmin * (float)(b0 & 63u);
+  o.dsc[1] = d * (float)(a2 & 63u);
+  o.dm[1] = dmin * (float)(b2 & 63u);
+  o.dsc[2] = d * (float)((c0 & 0xFu) | ((a0 >> 6) << 4));
+  o.dm[2] = dmin * (float)((c0 >> 4) | ((b0 >> 6) << 4));
+  o.dsc[3] = d * (float)((c2 & 0xFu) | ((a2 >> 6) << 4));
+  o.dm[3] = dmin * (float)((c2 >> 4) | ((b2 >> 6) << 4));
+}
+
 // The thread's 16 weights into chunks 2 qd, 2 qd + 1 of the A stage (hi and lo halves).
 template <int DT>
-__device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, unsigned qd, unsigned ks, unsigned char* A, unsigned r) {
+__device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, const Q4Scales& sc4, bool live, unsigned qd, unsigned ks,
+                                                 unsigned char* A, unsigned r) {
   uint4* Ahi = reinterpret_cast<uint4*>(A) + (size_t)(2u * qd) * GM_ROWS + r;
   uint4* Alo = Ahi + (size_t)8u * GM_ROWS;
   if (!live) {  // rows past the matrix: zeros (their outputs are not stored)
@@ -188,21 +213,25 @@ __device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, bool live, un
   }
   const unsigned h = qd >> 1;
   float dsc = 0.0f, dm = 0.0f;
+  uint32_t nib[4] = {0, 0, 0, 0};
   if constexpr (DT == KS_Q4K) {
-    float dsc_lo, dsc_hi, dm_lo, dm_hi;
-    q4k_group_scales(w.hdr, (int)(ks & 3u), dsc_lo, dsc_hi, dm_lo, dm_hi);
-    dsc = (h ? dsc_hi : dsc_lo) * 256.0f;
-    dm = (h ? dm_hi : dm_lo) * 256.0f;
+    const unsigned j = ks & 3u;  // selects, no dynamic indexing
+    dsc = j == 0 ? sc4.dsc[0] : j == 1 ? sc4.dsc[1] : j == 2 ? sc4.dsc[2] : sc4.dsc[3];
+    dm = j == 0 ? sc4.dm[0] : j == 1 ? sc4.dm[1] : j == 2 ? sc4.dm[2] : sc4.dm[3];
+    const unsigned sh = 4u * h;
+    nib[0] = (w.q.x >> sh) & 0x0F0F0F0Fu;
+    nib[1] = (w.q.y >> sh) & 0x0F0F0F0Fu;
+    nib[2] = (w.q.z >> sh) & 0x0F0F0F0Fu;
+    nib[3] = (w.q.w >> sh) & 0x0F0F0F0Fu;
   }
 #pragma unroll
   for (int cc = 0; cc < 2; cc++) {
     float v[8];
     if constexpr (DT == KS_Q4K) {
-      const uint32_t wds[4] = {w.q.x, w.q.y, w.q.z, w.q.w};
 #pragma unroll
       for (int e = 0; e < 8; e++) {
-        const uint32_t wd = wds[2 * cc + (e >> 2)] >> (4u * h);
-        const float q = (float)((wd >> (8 * (e & 3))) & 0xFu);
+        // one byte permute puts nibble byte e under the exponent of 2^23: the float 2^23 + q, then an exact subtract
+        const float q = __uint_as_float(__byte_perm(nib[2 * cc + (e >> 2)], 0x4B000000u, 0x7440u | (unsigned)(e & 3))) - 8388608.0f;
         v[e] = __fsub_rn(__fmul_rn(dsc, q), dm);  // d*sc*q - dmin*m as gguf_impl.rs:618-633 rounds it, times 2^8
       }
     } else {
@@ -254,6 +283,7 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
   // weights do not depend on the kernels before this one: the first two k-steps are fetched right away
   const bool producer = warp < GM_THREADS / 32;  // warps 0..15 dequantise, warp 16 feeds the tensor core
   Raw<DT> raw0, raw1;
+  Q4Scales sc4{};
   if (producer && live) {
     load_raw(W, a.row_bytes, row, qd, ks0, raw0);
     if (ksteps > 1) load_raw(W, a.row_bytes, row, qd, ks0 + 1, raw1);
@@ -283,7 +313,9 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
       const Raw<DT> cur = raw0;
       raw0 = raw1;
       if (live && i + 2 < ksteps) load_raw(W, a.row_bytes, row, qd, ks + 2, raw1);  // in flight while two steps are converted
-      dequant_to_stage<DT>(cur, live, qd, ks, A, r);
+      if constexpr (DT == KS_Q4K)
+        if (i == 0 || (ks & 3u) == 0) q4k_half_scales(cur.hdr, qd >> 1, sc4);  // a new super-block
+      dequant_to_stage<DT>(cur, sc4, live, qd, ks, A, r);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_fullA + 8u * s) : "memory");
