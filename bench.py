@@ -439,6 +439,11 @@ def sharded_matvecs(ctx, rank, world, dist, peak):
         uid = torch.frombuffer(bytearray(shard.Comm.unique_id(lib)), dtype=torch.uint8).cuda()
     dist.broadcast(uid, 0)
     comm = shard.Comm(ctx, world, rank, uid.cpu().numpy().tobytes())
+    # mailboxes for the arg-max exchange over peer memory: every rank's 64-byte handle to every rank
+    mine = torch.frombuffer(bytearray(comm.p2p_handle()), dtype=torch.uint8).cuda()
+    allh = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    comm.p2p_open(b"".join(h.cpu().numpy().tobytes() for h in allh))
     out = {}
     cfg = ksm.e2b_config()
     for name, dtype, rows, cols in (("q6k_lm_head_262144x1536", Q6K, 262144, 1536), ("q4k_gate_up_20480x2560", Q4K, 20480, 2560)):
@@ -467,8 +472,12 @@ def sharded_matvecs(ctx, rank, world, dist, peak):
         both_us = t(lambda: sm.enqueue(True))
         res = {"rows": rows, "cols": cols, "local_matvec_us": local_us, "all_gather_us": gather_us, "sharded_us": both_us,
                "all_gather_bytes": 4 * sm.per * world}
-        if dtype == Q6K:
+        if dtype == Q6K:   # local rows + arg-max + exchange of one (value, index) word per rank: peer memory, then NCCL
             res["sharded_argmax_us"] = t(lambda: (sm.enqueue(False), sm.enqueue_argmax(30.0)))
+            comm.set(comm.USE_P2P, 0)
+            res["sharded_argmax_nccl_us"] = t(lambda: (sm.enqueue(False), sm.enqueue_argmax(30.0)))
+            comm.set(comm.USE_P2P, 1)
+            res["argmax_exchange"] = "one kernel: 8-byte stores into the peers' mailboxes over NVLink, bounded poll, merge"
         # parity and the 1-GPU time, on rank 0 (it holds the whole matrix for this)
         y = sm.forward(x)
         tok = sm.argmax(x, 30.0) if dtype == Q6K else None

@@ -295,6 +295,16 @@ int ks_comm_unique_id(void* id_out);
 /* Collective: every rank calls it with the same id.  n_ranks == 1 needs no id and no NCCL. */
 ks_comm* ks_comm_init(ks_ctx* ctx, int n_ranks, int rank, const void* unique_id);
 void ks_comm_destroy(ks_comm* comm);
+/* Optional: the arg-max exchange over peer memory (NVLink) instead of NCCL.  Every rank creates its mailbox and
+ * gets a 64-byte handle; the host gathers the handles of all ranks (rank r's at r * 64) and every rank opens them.
+ * From then on ks_argmax_sharded is one kernel that stores this rank's (value, index) word into every peer's
+ * mailbox, waits (bounded; KS_ERR_TIMEOUT through the status word) for the peers' words and merges them.
+ * ks_comm_set: what 0 = use peer memory (1, default once open) or NCCL (0); 1 = poll limit of the peer wait;
+ * 2 = zero this rank's mailbox and step counter (all ranks, nothing in flight). */
+#define KS_COMM_P2P_HANDLE_BYTES 64
+int ks_comm_p2p_handle(ks_comm* comm, void* handle_out);
+int ks_comm_p2p_open(ks_comm* comm, const void* all_handles);
+int ks_comm_set(ks_comm* comm, int what, unsigned value);
 int ks_comm_rank(const ks_comm* comm);
 int ks_comm_size(const ks_comm* comm);
 /* all[all_off + r*count .. ] of every rank <- rank r's slot of the same buffer (in-place all-gather, f32). */

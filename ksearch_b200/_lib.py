@@ -98,6 +98,9 @@ SIGNATURES = {
     "ks_comm_unique_id": (_i, [_vp]),
     "ks_comm_init": (_vp, [_vp, _i, _i, _vp]),
     "ks_comm_destroy": (None, [_vp]),
+    "ks_comm_p2p_handle": (_i, [_vp, _vp]),
+    "ks_comm_p2p_open": (_i, [_vp, _vp]),
+    "ks_comm_set": (_i, [_vp, _i, C.c_uint]),
     "ks_comm_rank": (_i, [_vp]),
     "ks_comm_size": (_i, [_vp]),
     "ks_comm_all_gather_f32": (_i, [_vp, _vp, _sz, _sz]),

@@ -77,6 +77,79 @@ __global__ void argmax_merge_kernel(const float* pairs, int n_ranks, float* out_
   }
 }
 
+// ---- the same exchange over peer memory (NVLink), fused with the merge -----------------------------------------
+// Every rank owns a mailbox of 2 x n_ranks 64-bit words that its peers can write (cudaIpc mapping).  One kernel per
+// call: lane r stores this rank's (value, index, step) word into rank r's mailbox with one 8-byte system-scope store
+// -- value and tag travel in one single-copy-atomic word, so no fence and no flag -- then lane r polls its own
+// mailbox word r until the tag shows this step, and the warp merges the n_ranks candidates (largest value, ties to
+// the lower index).  No NCCL launch: the exchange costs one store and one poll across NVLink instead of the
+// ~20 us latency of a tiny all-gather.  The word: value bits << 32 | index << 8 | step & 0xFF; mailboxes alternate
+// by step parity, so a rank that is one step ahead never overwrites a word a slower rank still waits for.  The
+// poll is bounded: on expiry the context's status word is raised and the rank's own candidate is written.
+constexpr int KS_P2P_MAX_RANKS = 32;
+struct P2pArgs {
+  unsigned long long* box[KS_P2P_MAX_RANKS];  // box[r]: rank r's mailbox as mapped into this process (own: local)
+  unsigned* step;                             // this rank's step counter (device)
+  unsigned n_ranks, rank, row0, poll_limit;
+  float cap;
+  const float* logits;
+  const float* local_idx;
+  float* out_idx;
+  unsigned* err;
+};
+__global__ void argmax_p2p_kernel(const P2pArgs a) {
+  ks_pdl_entry();
+  const unsigned lane = threadIdx.x;
+  unsigned step = 0;
+  if (lane == 0) step = a.step[0] + 1u;
+  step = __shfl_sync(0xffffffffu, step, 0);
+  const unsigned i = (unsigned)a.local_idx[0];
+  const float v = a.cap * tanhf(a.logits[i] / a.cap);
+  const unsigned long long word =
+      ((unsigned long long)__float_as_uint(v) << 32) | ((unsigned long long)(a.row0 + i) << 8) | (unsigned long long)(step & 0xFFu);
+  const unsigned slot = (step & 1u) * a.n_ranks;
+  unsigned long long* peer_box = nullptr;
+#pragma unroll
+  for (int r = 0; r < KS_P2P_MAX_RANKS; r++)
+    if (lane == (unsigned)r) peer_box = a.box[r];  // selects: no dynamic indexing of the parameter array
+  if (lane < a.n_ranks)
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(peer_box + slot + a.rank), "l"(word) : "memory");
+  // own mailbox: word `lane` comes from rank `lane`
+  unsigned long long got = word;
+  bool ok = true;
+  if (lane < a.n_ranks) {
+    const unsigned long long* mine = a.box[0];
+#pragma unroll
+    for (int r = 1; r < KS_P2P_MAX_RANKS; r++)
+      if (a.rank == (unsigned)r) mine = a.box[r];
+    ok = false;
+    for (unsigned n = 0; n < a.poll_limit; n++) {
+      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(got) : "l"(mine + slot + lane) : "memory");
+      if ((unsigned)(got & 0xFFull) == (step & 0xFFu)) {
+        ok = true;
+        break;
+      }
+    }
+    if (!ok) got = word;  // gave up: fall back to the local candidate, the status word tells the host
+  }
+  if (__any_sync(0xffffffffu, !ok) && lane == 0) atomicOr(a.err, 16u);
+  float bv = lane < a.n_ranks ? __uint_as_float((unsigned)(got >> 32)) : -3.0e38f;
+  unsigned bi = lane < a.n_ranks ? (unsigned)((got >> 8) & 0xFFFFFFu) : 0xFFFFFFFFu;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    a.out_idx[0] = (float)bi;
+    a.step[0] = step;
+  }
+}
+
 }  // namespace
 
 struct ks_comm {
@@ -85,6 +158,12 @@ struct ks_comm {
   int n_ranks = 1, rank = 0;
   float* pair_local = nullptr;  // [2] this rank's (value, index), then [2 * n_ranks] gathered
   float* idx_local = nullptr;   // [1]
+  // peer-memory exchange: this rank's mailbox (2 x n_ranks words) + step counter, and the peers' mailboxes as mapped here
+  unsigned long long* box_local = nullptr;
+  unsigned* step = nullptr;
+  unsigned long long* box[KS_P2P_MAX_RANKS] = {nullptr};
+  bool p2p = false, use_p2p = true;
+  unsigned poll_limit = 1u << 23;  // several seconds of polling: the peers are other processes
 };
 
 extern "C" {
@@ -148,9 +227,67 @@ void ks_comm_destroy(ks_comm* c) {
   if (!c) return;
   cudaSetDevice(c->ctx->device);
   cudaStreamSynchronize(c->ctx->stream);
+  for (int r = 0; r < c->n_ranks && r < KS_P2P_MAX_RANKS; r++)
+    if (r != c->rank && c->box[r]) cudaIpcCloseMemHandle(c->box[r]);
+  if (c->box_local) cudaFree(c->box_local);
   if (c->comm) nccl_api().CommDestroy(c->comm);
   if (c->pair_local) cudaFree(c->pair_local);
   delete c;
+}
+
+// This rank's mailbox, created on first use, as a 64-byte handle the other ranks open (any host channel carries it).
+int ks_comm_p2p_handle(ks_comm* c, void* handle_out) {
+  if (!c || !handle_out) return KS_ERR_INVALID;
+  ks_ctx* ctx = c->ctx;
+  static_assert(sizeof(cudaIpcMemHandle_t) == KS_COMM_P2P_HANDLE_BYTES, "IPC handle size");
+  KS_REQUIRE(ctx, c->n_ranks <= KS_P2P_MAX_RANKS, "comm_p2p: at most %d ranks", KS_P2P_MAX_RANKS);
+  cudaSetDevice(ctx->device);
+  if (!c->box_local) {
+    const size_t bytes = 256 + 2 * (size_t)c->n_ranks * sizeof(unsigned long long);
+    KS_CUDA(ctx, cudaMalloc((void**)&c->box_local, bytes));
+    KS_CUDA(ctx, cudaMemset(c->box_local, 0, bytes));
+    c->step = reinterpret_cast<unsigned*>(c->box_local + 2 * (size_t)c->n_ranks);
+  }
+  cudaIpcMemHandle_t h;
+  KS_CUDA(ctx, cudaIpcGetMemHandle(&h, c->box_local));
+  memcpy(handle_out, &h, sizeof h);
+  return KS_OK;
+}
+// all_handles: n_ranks x 64 bytes, rank r's handle at r * 64 (this rank's own entry is ignored).  Collective in the
+// sense that every rank must have created its mailbox first.  From then on ks_argmax_sharded exchanges over peer memory.
+int ks_comm_p2p_open(ks_comm* c, const void* all_handles) {
+  if (!c || !all_handles) return KS_ERR_INVALID;
+  ks_ctx* ctx = c->ctx;
+  KS_REQUIRE(ctx, c->box_local, "comm_p2p_open: call ks_comm_p2p_handle first");
+  cudaSetDevice(ctx->device);
+  for (int r = 0; r < c->n_ranks; r++) {
+    if (r == c->rank) {
+      c->box[r] = c->box_local;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char*)all_handles + (size_t)r * sizeof h, sizeof h);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "comm_p2p_open: rank %d's mailbox cannot be mapped: %s", r, cudaGetErrorString(e));
+    c->box[r] = (unsigned long long*)p;
+  }
+  c->p2p = true;
+  return KS_OK;
+}
+// what = 0: 1 exchanges over peer memory when the mailboxes are open (default), 0 always NCCL; what = 1: polls before
+// the peer wait gives up; what = 2: zero this rank's mailbox and step counter (every rank, with no step in flight,
+// after a wait gave up).
+int ks_comm_set(ks_comm* c, int what, unsigned value) {
+  if (!c) return KS_ERR_INVALID;
+  if (what == 0) c->use_p2p = value != 0;
+  else if (what == 1) c->poll_limit = value ? value : 1u;
+  else if (what == 2 && c->box_local) {
+    cudaSetDevice(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->stream);
+    cudaMemset(c->box_local, 0, 256 + 2 * (size_t)c->n_ranks * sizeof(unsigned long long));
+  } else if (what != 2) return KS_ERR_INVALID;
+  return KS_OK;
 }
 
 int ks_comm_rank(const ks_comm* c) { return c ? c->rank : -1; }
@@ -196,6 +333,22 @@ int ks_argmax_sharded(ks_comm* c, size_t rows_local, size_t row0, float cap, con
   const float* lg = (const float*)logits_local->dptr + logits_off;
   int rc = ks_launch_softcap_argmax(ctx, rows_local, cap, KS_F32, lg, c->idx_local);
   if (rc) return rc;
+  if (c->p2p && c->use_p2p && c->n_ranks > 1) {  // one kernel: store to every peer, poll the own mailbox, merge
+    P2pArgs a{};
+    for (int r = 0; r < c->n_ranks; r++) a.box[r] = c->box[r];
+    a.step = c->step;
+    a.n_ranks = (unsigned)c->n_ranks;
+    a.rank = (unsigned)c->rank;
+    a.row0 = (unsigned)row0;
+    a.poll_limit = c->poll_limit;
+    a.cap = cap;
+    a.logits = lg;
+    a.local_idx = c->idx_local;
+    a.out_idx = (float*)out_idx->dptr + out_off;
+    a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
+    KS_LAUNCH(ctx, (argmax_p2p_kernel), 1, 32, 0, a);
+    return ks_after_launch(ctx, "argmax_p2p");
+  }
   float* pairs = c->pair_local + 2;  // gathered pairs; this rank's own pair is written in place
   KS_LAUNCH(ctx, (argmax_pair_kernel), 1, 32, 0, lg, (const float*)c->idx_local, cap, (unsigned)row0, pairs + 2 * (size_t)c->rank);
   if ((rc = ks_after_launch(ctx, "argmax_pair"))) return rc;

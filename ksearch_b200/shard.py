@@ -89,6 +89,25 @@ class Comm:
             raise KsError(rc, lib.ks_last_error(None).decode())
         return buf.raw
 
+    P2P_HANDLE_BYTES = 64
+    USE_P2P, POLL_LIMIT, RESET = 0, 1, 2
+
+    def p2p_handle(self) -> bytes:
+        """This rank's mailbox for the peer-memory exchange, as the 64 bytes the other ranks open."""
+        import ctypes as C
+        buf = C.create_string_buffer(self.P2P_HANDLE_BYTES)
+        self.ctx.check(self.ctx.lib.ks_comm_p2p_handle(self.h, buf))
+        return buf.raw
+
+    def p2p_open(self, all_handles: bytes):
+        """all_handles: the handles of every rank, rank r's at r * 64 (gathered over any host channel)."""
+        import ctypes as C
+        assert len(all_handles) == self.world * self.P2P_HANDLE_BYTES
+        self.ctx.check(self.ctx.lib.ks_comm_p2p_open(self.h, C.create_string_buffer(all_handles, len(all_handles))))
+
+    def set(self, what: int, value: int):
+        self.ctx.check(self.ctx.lib.ks_comm_set(self.h, what, value))
+
     def close(self):
         if self.h:
             self.ctx.lib.ks_comm_destroy(self.h)
