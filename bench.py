@@ -499,6 +499,8 @@ def sharded_matvecs(ctx, rank, world, dist, peak):
         res["parity_ok"] = bool(ok[0] > 0)
         if rank == 0:
             res["speedup_over_one_gpu"] = res["one_gpu_us"] / both_us
+            if "sharded_argmax_us" in res:   # the one-GPU figure is the matvec alone, without its arg-max
+                res["argmax_speedup_over_one_gpu_matvec"] = res["one_gpu_us"] / res["sharded_argmax_us"]
             res["bound_by"] = "the all-gather" if gather_us > local_us else "the local rows"
         out[name] = res
     comm.close()
