@@ -584,8 +584,13 @@ def main():
     launches = ctx.launch_count() - n0
     barrier()
 
-    # ---- end to end: host token ids in and out of every step through the blocking C-ABI call
-    tok = 1
+    # ---- end to end: host token ids in and out of every step through the blocking C-ABI call, over the SAME
+    # positions as the device-resident leg (the slot is rewound and the prompt replayed, untimed; decode time grows
+    # with the context, so timing this leg further down the sequence would measure a different workload)
+    model.slot_reset(slot)
+    for t in prompt[:-1]:
+        model.forward(slot, 1, [int(t)], False)
+    tok = int(prompt[-1])
     for _ in range(args.warmup):
         tok = model.decode_token([tok], slot)[0]
     barrier()

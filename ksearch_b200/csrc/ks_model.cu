@@ -110,6 +110,9 @@ struct ks_model {
   std::map<uint64_t, size_t> graph_nodes;
   std::vector<void*> owned;
   std::vector<char> tok_src;  // per slot: which half of the ping-pong holds its next input id
+  // ids that come from the host are read by the embedding kernel straight out of this pinned, device-visible array
+  // (one word per slot; source index 2): no staging copy in front of the step
+  float* host_ids = nullptr;
   // one persistent decode kernel per slot (both null: shape not covered, tried once); decode_kernel
   // picks which of the two is built: 1 = grid barriers (ks_mega.cu), 2 = tagged-word dataflow (ks_flow.cu)
   struct Mega {
@@ -180,8 +183,8 @@ Lane slot_lane(ks_model* m, int first, int src) {
   L.o = (char*)m->o + (size_t)first * qn * ab;
   L.ff = (char*)m->ff + (size_t)first * F * ab;
   L.logits = (char*)m->logits + (size_t)first * g.vocab * ab;
-  L.tok_in = m->tok + (size_t)src * g.n_slots + first;
-  L.tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  L.tok_in = src == 2 ? m->host_ids + first : m->tok + (size_t)src * g.n_slots + first;
+  L.tok_out = m->tok + (size_t)(src == 2 ? 1 : src ^ 1) * g.n_slots + first;
   L.ret = m->ret + (size_t)first * (g.n_slots + 1);
   L.pos = m->pos + first;
   L.meta = m->meta + (size_t)first * 4;
@@ -451,8 +454,8 @@ int enqueue_forward_mega(ks_model* m, const ks_model::Mega& mg, int first, int s
   float* yb = (float*)m->x2 + (size_t)first * H;
   float* xn = (float*)m->xn + (size_t)first * H;
   float* logits = (float*)m->logits + (size_t)first * g.vocab;
-  const float* tok_in = m->tok + (size_t)src * g.n_slots + first;
-  float* tok_out = m->tok + (size_t)(src ^ 1) * g.n_slots + first;
+  const float* tok_in = src == 2 ? m->host_ids + first : m->tok + (size_t)src * g.n_slots + first;
+  float* tok_out = m->tok + (size_t)(src == 2 ? 1 : src ^ 1) * g.n_slots + first;
   int* pos = m->pos + first;
   int rc;
   if ((rc = ks_launch_copy_scale_indexed(c, H, 1, sqrtf((float)H), (ks_dtype)g.embd_dtype, m->token_embd.dptr, tok_in, KS_F32, cur))) return rc;
@@ -742,6 +745,11 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
          cudaStreamSynchronize(ctx->stream) == cudaSuccess;
     if (!ok) ks_fail(ctx, KS_ERR_CUDA, "model_create: rope upload failed");
   }
+  if (ok && cudaMallocHost((void**)&m->host_ids, (size_t)g.n_slots * sizeof(float)) != cudaSuccess) {
+    ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
+    m->host_ids = nullptr;
+    ok = false;
+  }
   m->host_tok_n = 8192;
   if (ok && cudaMallocHost((void**)&m->host_tok, m->host_tok_n * sizeof(float)) != cudaSuccess) {
     ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
@@ -787,6 +795,7 @@ void ks_model_destroy(ks_model* m) {
   }
   for (void* p : m->owned) cudaFree(p);
   if (m->host_tok) cudaFreeHost(m->host_tok);
+  if (m->host_ids) cudaFreeHost(m->host_ids);
   delete m;
 }
 
@@ -907,15 +916,11 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
       if (m->tok_src[s] != src)
         return ks_fail(c, KS_ERR_STATE, "slots %d..%d hold their device-side token ids in different buffers; pass host ids", first, first + n - 1);
   if (tokens) {
-    src = 0;
-    KS_REQUIRE(c, (size_t)n <= KS_STAGE_IDS, "forward: more than %zu slots per call", KS_STAGE_IDS);
-    float* stage = m->host_tok + m->host_tok_n - 16 - KS_STAGE_IDS;  // the pinned ring's tail stages the ids
-    KS_CUDA(c, cudaStreamSynchronize(c->stream));     // the staging words may still be in flight
-    for (int s = 0; s < n; s++) {
+    src = 2;  // the step's embedding kernel reads the ids from pinned host memory
+    for (int s = 0; s < n; s++)
       KS_REQUIRE(c, tokens[s] >= 0 && tokens[s] < m->cfg.vocab, "token id %d outside the vocabulary", tokens[s]);
-      stage[s] = (float)tokens[s];
-    }
-    KS_CUDA(c, cudaMemcpyAsync(m->tok + first, stage, n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    KS_CUDA(c, cudaStreamSynchronize(c->stream));     // an earlier step may not have read its ids yet
+    for (int s = 0; s < n; s++) m->host_ids[first + s] = (float)tokens[s];
   }
   // The slots share one pass over the weights as long as their staged input vectors fit the matvec kernels'
   // shared memory side by side (m->chunk of them); a larger batch takes several passes.
@@ -926,7 +931,7 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
   }
   for (int s = first; s < first + n; s++) {
     m->seq_len[s] += 1;
-    m->tok_src[s] = (char)(want_logits ? (src ^ 1) : src);
+    m->tok_src[s] = (char)(want_logits ? (src == 2 ? 1 : src ^ 1) : (src == 2 ? 0 : src));
   }
   return KS_OK;
 }
