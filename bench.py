@@ -133,6 +133,8 @@ def workload_config(n_gpus):
             "weight_bytes_per_token": 1027031040, "prompt_len": PROMPT_LEN, "slots_per_gpu": 1,
             "parallelism": f"replicas x{n_gpus}, no collective on the decode path",
             "l2": "weights (1.03 GB/token) are 8x the 126 MB L2, so every step streams them from HBM",
+            "positions": "value and e2e are timed over the same positions: prompt, W warm-up tokens, then K tokens "
+                         "(the slot is rewound and the prompt replayed before the e2e leg)",
             "arithmetic": "f32 activations and accumulation; inside the persistent decode kernel and the lm_head the input vector "
                           "is 24-bit block fixed point (three int8 planes per 32 elements) and weight x input products are exact "
                           "dp4a integer sums, scaled back in f32"}
