@@ -10,6 +10,8 @@
 //     the copies of the next phases are already in flight while the block waits at a barrier;
 //   * phases (qkv | attention | o-proj | gate-up | down, per layer) are separated by a grid barrier
 //     on one global counter; activations cross it through global memory (L2), read with ld.cg;
+//     one hop has no barrier: q/k/v go to the attention blocks as 64-bit (value, tag) words written
+//     with relaxed stores and polled by their consumers (a hop of ~1 us instead of ~2 us);
 //   * the norms are applied while x is staged; their weights are fetched BEFORE the barrier wait,
 //     because the acquire that ends the wait drops the SM's L1 and every later plain load of a
 //     constant would be a full round trip to L2;
@@ -17,7 +19,7 @@
 //     five phase shapes and the per-layer pointers are copied to shared memory once;
 //   * attention: per-head RMS + RoPE + Q4_0 pack of the new K/V row, split-context online softmax
 //     and the merge of the splits (last arriving block) happen inside one phase.
-// Every spin (barrier, mbarrier) is bounded; on expiry the block raises the context's status word,
+// Every spin (barrier, tagged word, mbarrier) is bounded; on expiry the block raises the context's status word,
 // drains its copies and leaves, and the other blocks time out the same way.
 #include <utility>
 #include <vector>
@@ -64,7 +66,9 @@ struct MegaArgs {
   unsigned* att_cnt;        // [n_q] arrival counters of the attention blocks, per head
   unsigned* bar;            // [0] running barrier counter, [1] its value when the previous token ended
   unsigned* err;
-  unsigned poll_limit;      // polls of the barrier counter before a wait gives up
+  unsigned long long* qkv_t;  // q | k | v rows of the current layer as (tag << 32 | f32 bits) words: the q/k/v phase hands
+                              // them to the attention blocks without a grid barrier, consumers poll for the tag
+  unsigned poll_limit;      // polls of the barrier counter (or of a tagged word) before a wait gives up
   unsigned test_stall;      // test hook: the barrier before phase 1 waits for this many arrivals more than ever come
   long long* prof;          // [2][phases][8] SM clocks of the first and last block: start, staged, computed, released
                             // (attention rows: 4..7 = q/k/v ready, positions done, folded, arrived)
@@ -102,6 +106,32 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
   return v;
 }
 __device__ __forceinline__ float4 ldcg4(const float* p, unsigned c) { return __ldcg(reinterpret_cast<const float4*>(p) + c); }
+// A value and its tag in one 64-bit word: single-copy atomic, so a consumer that sees the tag sees the value; no fence.
+__device__ __forceinline__ void tag_store(unsigned long long* p, float v, unsigned tag) {
+  const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long tag_load(const unsigned long long* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+// Four tagged words per lane until every tag matches; false when the limit ran out.
+__device__ __forceinline__ bool tag_wait4(const unsigned long long* base, int i0, int i1, int i2, int i3, unsigned tag, unsigned limit,
+                                          float& o0, float& o1, float& o2, float& o3) {
+  for (unsigned it = 0; it < limit; it++) {
+    const unsigned long long w0 = tag_load(base + i0), w1 = tag_load(base + i1), w2 = tag_load(base + i2), w3 = tag_load(base + i3);
+    if ((unsigned)(w0 >> 32) == tag && (unsigned)(w1 >> 32) == tag && (unsigned)(w2 >> 32) == tag && (unsigned)(w3 >> 32) == tag) {
+      o0 = __uint_as_float((unsigned)w0);
+      o1 = __uint_as_float((unsigned)w1);
+      o2 = __uint_as_float((unsigned)w2);
+      o3 = __uint_as_float((unsigned)w3);
+      return true;
+    }
+  }
+  o0 = o1 = o2 = o3 = 0.0f;
+  return false;
+}
 
 // Grid-wide barrier on a monotonically increasing counter, in two halves so that loads which do not
 // depend on other blocks can be issued in between.
@@ -714,7 +744,8 @@ __host__ __device__ inline unsigned mg_active_splits(unsigned tlen, unsigned max
 //   4. the block leaves a (m, l, O[hd]) record; the last block of a head to arrive merges the
 //      head's records (lower.rs:5897-6088).
 template <int DPL>
-__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, unsigned char* sm, int* sflag, long long* pf) {
+__device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer& L, unsigned char* sm, int* sflag, long long* pf,
+                                             unsigned tag) {
   constexpr int HD = DPL * 32, HALF = HD / 2, NB = HD / 32;
   constexpr unsigned ROWB = NB * KS_Q40_BLOCK_BYTES;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -738,20 +769,29 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
     const int pb = warp & 3;  // block pair of the K / V job
     const bool kjob = owner && warp < 4 && pb < NB / 2, vjob = owner && warp >= 4 && pb < NB / 2;
     float qv[DPL], qw[DPL], qc[DPL], qs[DPL], rv[DPL], r_w0 = 0.f, r_w1 = 0.f, r_c = 0.f, r_s = 0.f;
-    const float* qsrc = a.q + (size_t)head * HD;
     const float* qnw = L.norm[1];
 #pragma unroll
-    for (int j = 0; j < DPL; j++) {
+    for (int j = 0; j < DPL; j++) {  // constants first: they are on their way while the tagged words are polled
       const int d = mg_lane_dim<DPL>(lane, j);
-      qv[j] = __ldcg(qsrc + d);
       qw[j] = qnw[d];
       qc[j] = cs[d & (HALF - 1)];
       qs[j] = cs[HALF + (d & (HALF - 1))];
     }
-    if (kjob || vjob) {
-      const float* src = (kjob ? a.k : a.v) + (size_t)kvh * HD;
+    // q (and, in the owner split, k / v) arrive as tagged words straight from the blocks that computed them
+    bool got = true;
+    {
+      const unsigned long long* qsrc = a.qkv_t + (size_t)head * HD;
 #pragma unroll
-      for (int j = 0; j < DPL; j++) rv[j] = __ldcg(src + lane + 32 * j);
+      for (int j = 0; j < DPL; j += 4)
+        got = tag_wait4(qsrc, mg_lane_dim<DPL>(lane, j), mg_lane_dim<DPL>(lane, j + 1), mg_lane_dim<DPL>(lane, j + 2),
+                        mg_lane_dim<DPL>(lane, j + 3), tag, a.poll_limit, qv[j], qv[j + 1], qv[j + 2], qv[j + 3]) && got;
+    }
+    if (kjob || vjob) {
+      const unsigned long long* src = a.qkv_t + (size_t)a.n_q * HD + (kjob ? 0u : (size_t)a.n_kv * HD) + (size_t)kvh * HD;
+#pragma unroll
+      for (int j = 0; j < DPL; j += 4)
+        got = tag_wait4(src, lane + 32 * j, lane + 32 * (j + 1), lane + 32 * (j + 2), lane + 32 * (j + 3), tag, a.poll_limit, rv[j],
+                        rv[j + 1], rv[j + 2], rv[j + 3]) && got;
       if (kjob) {
         const float* w = L.norm[2];
         r_w0 = w[32 * pb + lane];
@@ -760,6 +800,7 @@ __device__ __forceinline__ void mg_attention(const MegaArgs& a, const MegaLayer&
         r_s = cs[HALF + 32 * pb + lane];
       }
     }
+    if (!got) atomicOr(a.err, 2u);  // a tagged word never came: the values are zeros, the status word tells the host
     {
       float ss = 0.0f;
 #pragma unroll
@@ -1015,6 +1056,9 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
   if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
     prof = a.prof + (size_t)(blockIdx.x == 0 ? 0 : 1) * n_phases * 8;
   int p = 0, layer = 0, kind = 0;
+  // tag of this token's words: position and layer; a slot reset clears the words, so a replayed position never
+  // meets its own old tags
+  const unsigned tag_base = (((unsigned)a.pos[0] + 1u) << 8) + 1u;
   for (; p < n_phases; p++) {
     const MegaLayer& L = layers[layer];
     // constants of this phase, fetched while the other blocks arrive at the barrier before it
@@ -1023,13 +1067,19 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
       mg_prefetch_norm(npre, layer == 0 ? KS_PRO_NORM : KS_PRO_ADD_NORM, L.norm[0], layers[layer > 0 ? layer - 1 : 0].norm[5], H);
     else if (kind == PH_GATEUP)
       mg_prefetch_norm(npre, KS_PRO_ADD_NORM, L.norm[4], L.norm[3], H);
-    if (p > 0) {
-      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x + (p == 1 ? a.test_stall : 0u), a.err, sflag + 2, p & 1, a.poll_limit)) break;
+    // No barrier in front of attention: its inputs are tagged words.  Every block still ARRIVES after every phase,
+    // so the targets of the barriers that remain are unchanged; the flag word this wait would have cleared is
+    // cleared all the same.  (The parity stays `p & 1`: written as a separate counter the same logic compiles into
+    // a kernel that is 40 % slower.)
+    if (p > 0 && kind == PH_ATTN) {
+      if (threadIdx.x == 0) sflag[2 + ((p & 1) ^ 1)] = 0;
+    } else if (p > 0) {
+      if (!grid_wait(a.bar, bar_base + (unsigned)p * gridDim.x + (p == 2 ? a.test_stall : 0u), a.err, sflag + 2, p & 1, a.poll_limit)) break;
       if (prof) prof[(p - 1) * 8 + 3] = clock64();
     }
     if (prof) prof[p * 8 + 0] = clock64();
     if (kind == PH_ATTN) {
-      mg_attention<DPL>(a, L, smem, sflag, prof ? prof + p * 8 : nullptr);
+      mg_attention<DPL>(a, L, smem, sflag, prof ? prof + p * 8 : nullptr, tag_base + (unsigned)layer);
     } else {
       const MegaShape& sh = shapes[kind];
       // input, prologue and outputs of this phase
@@ -1133,9 +1183,11 @@ __global__ void __launch_bounds__(256, 1) mega_kernel(const MegaArgs a) {
         }
         fval = sh.type == MG_GATE_UP ? gelu_mul(v0, v1) : v0;
         const float val = fval;
-        if (kind != PH_GATEUP) {
-          float* y = kind == PH_QKV ? (fseg == 0 ? a.q : fseg == 1 ? a.k : a.v) : a.yb;
-          y[frow] = val;
+        if (kind == PH_QKV) {  // handed to the attention blocks as tagged words (no barrier follows this phase)
+          const size_t at = fseg == 0 ? 0u : fseg == 1 ? (size_t)a.n_q * a.hd : (size_t)(a.n_q + a.n_kv) * a.hd;
+          tag_store(a.qkv_t + at + frow, val, tag_base + (unsigned)layer);
+        } else if (kind != PH_GATEUP) {
+          a.yb[frow] = val;
         }
         if (sums) {
           const float t = val * wpr;
@@ -1198,6 +1250,8 @@ struct ks_mega {
   unsigned* d_sync = nullptr;  // words 0..1 barrier (a 128-byte line of its own: every block polls it), 64..111 per-head
                                // attention arrival counters, from byte 512: per-block norm sums
   long long* d_prof = nullptr;
+  unsigned long long* d_qkv = nullptr;  // tagged q | k | v words
+  size_t qkv_words = 0;
   unsigned char* d_fx = nullptr;  // attention output and GeGLU output in the staged layout
   unsigned grid = 0;
   size_t smem = 0;
@@ -1243,6 +1297,7 @@ float* ks_mega_residual(const ks_mega* mg) { return mg->residual; }
 // a bounded wait gave up; a slot reset puts the kernel back in working order.
 int ks_mega_reset(ks_ctx* ctx, ks_mega* mg) {
   cudaError_t e = cudaMemsetAsync(mg->d_sync, 0, 512, ctx->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_qkv, 0, mg->qkv_words * sizeof(unsigned long long), ctx->stream);  // no stale tags
   if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "decode kernel: reset failed: %s", cudaGetErrorString(e));
   return KS_OK;
 }
@@ -1263,6 +1318,7 @@ void ks_mega_destroy(ks_mega* mg) {
   if (!mg) return;
   if (mg->d_tables) cudaFree(mg->d_tables);
   if (mg->d_sync) cudaFree(mg->d_sync);
+  if (mg->d_qkv) cudaFree(mg->d_qkv);
   if (mg->d_prof) cudaFree(mg->d_prof);
   if (mg->d_fx) cudaFree(mg->d_fx);
   delete mg;
@@ -1397,7 +1453,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   const size_t n_phases = (size_t)d->n_layers * PH_PER_LAYER;
   if (cudaMalloc(&mg->d_tables, tables_bytes) != cudaSuccess || cudaMalloc((void**)&mg->d_sync, 512 + 16 * (size_t)ctx->sm_count) != cudaSuccess ||
       cudaMalloc((void**)&mg->d_prof, n_phases * 16 * sizeof(long long)) != cudaSuccess ||
-      cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess) {
+      cudaMalloc((void**)&mg->d_fx, ((size_t)qn / 64 + (size_t)F / 64) * 256) != cudaSuccess ||
+      cudaMalloc((void**)&mg->d_qkv, ((size_t)qn + 2 * (size_t)kvn) * sizeof(unsigned long long)) != cudaSuccess) {
     ks_mega_destroy(mg);
     return ks_fail(ctx, KS_ERR_OOM, "decode kernel: cannot allocate its tables");
   }
@@ -1405,6 +1462,8 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_sync, 0, 512 + 16 * (size_t)ctx->sm_count, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_fx, 0, ((size_t)qn / 64 + (size_t)F / 64) * 256, ctx->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_prof, 0, n_phases * 16 * sizeof(long long), ctx->stream);
+  mg->qkv_words = (size_t)qn + 2 * (size_t)kvn;
+  if (e == cudaSuccess) e = cudaMemsetAsync(mg->d_qkv, 0, mg->qkv_words * sizeof(unsigned long long), ctx->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // tab is a local
   if (e != cudaSuccess) {
     ks_mega_destroy(mg);
@@ -1426,6 +1485,7 @@ int ks_mega_create(ks_ctx* ctx, const ks_mega_desc* d, const ks_mega_layer* laye
   a.ffx = mg->d_fx + (size_t)qn / 64 * 256;
   a.att_tmp = d->att_tmp;
   a.bar = mg->d_sync;
+  a.qkv_t = mg->d_qkv;
   a.att_cnt = mg->d_sync + 64;
   a.nsum = reinterpret_cast<float4*>(mg->d_sync + 128);
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
