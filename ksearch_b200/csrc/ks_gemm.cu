@@ -8,17 +8,23 @@
 // allows (N = 16) and 256 tokens fill it (N = 256).
 //   * B (token rows) is prepared once per call by x_split_kernel: every f32 x is split into two f16 terms
 //     (hi = rn(x), lo = rn(x - hi)) and stored k-step by k-step in exactly the shared-memory image the MMA wants
-//     (8x8 core matrices, K-major, no swizzle), so a k-step of B is ONE cp.async.bulk into the stage.
-//   * A (weights) is dequantised by the CTA's 512 threads, a quarter of a row's k-step (16 weights) each, bit for bit as
-//     crates/ksearch_gguf/src/gguf_impl.rs:618-633 / 761-791 computes it, scaled by 2^8 (exact; keeps the low
-//     term out of the f16 denormal range), split the same way and stored as core matrices.
-//   * Three MMAs per 16 k: Ahi.Bhi + Ahi.Blo + Alo.Bhi; the dropped lo.lo term is below 2^-22 relative, so the
-//     result matches f32 arithmetic (the reference's single half operands give ~1e-3).
+//     (8x8 core matrices, K-major, no swizzle; per 8-k chunk the hi rows of all tokens, then the lo rows), so a
+//     k-step of B is ONE cp.async.bulk into the stage.
+//   * A (weights) is dequantised by the CTA's 512 threads, a quarter of a row's k-step (16 weights) each.  Q4_K:
+//     bit for bit as crates/ksearch_gguf/src/gguf_impl.rs:690-721 computes it in f32, scaled by 2^6 (exact; keeps
+//     the low term out of the f16 denormal range), then split like x.  Q6_K (gguf_impl.rs:761-791): in half2
+//     arithmetic straight from the packed bytes (see dequant_to_stage), two f16 terms that add up to the f32 weight
+//     to 2^-17.  Both are stored as core matrices.
+//   * Products: Ahi.Bhi + Ahi.Blo + Alo.Bhi; the dropped lo.lo term is below 2^-22 relative, so the result matches
+//     f32 arithmetic (the reference's single half operands give ~1e-3).  Up to 128 token rows the first two are ONE
+//     MMA over 2 NP rows of B (the hi and lo rows of a chunk are neighbours): the accumulator has 2 NP columns, the
+//     epilogue adds the halves, and the tensor core fetches the A tile twice per 16 k instead of three times.
 //   * Warp-specialised: 16 warps dequantise into two A stages and signal each one full on an mbarrier (one arrival
-//     per warp); a 17th warp's first lane requests the B copies, waits for both operands of a step, issues the MMAs
-//     and lets tcgen05.commit hand the stage back on another mbarrier.  No block-wide barrier inside the k loop.  The B copies run up to two k-steps ahead in a ring of up to four stages, the
-//     packed weights two k-steps ahead in registers.  The accumulator (128 lanes x N columns) is read back with tcgen05.ld, scaled
-//     by 2^-8 and stored coalesced along the weight-row index.
+//     per warp); the first lane of a 17th warp waits for both operands of a step, issues its MMAs and lets
+//     tcgen05.commit release the step's A and B stage on one mbarrier; the first lane of an 18th warp requests the
+//     token rows (ring of two or four stages) as those mbarriers complete.  No block-wide barrier inside the k
+//     loop; the packed weights are fetched two k-steps ahead into registers.  The accumulator is read back with
+//     tcgen05.ld, scaled by 2^-6 and stored coalesced along the weight-row index.
 // Every wait is bounded; on expiry the CTA raises the context's status word, waits (bounded) for what it has in
 // flight, frees its tensor memory and returns.
 #include <cuda_fp16.h>
@@ -31,9 +37,11 @@ namespace {
 
 constexpr int GM_ROWS = 128;        // weight rows per CTA (M of the MMA)
 constexpr int GM_KSTEP = 64;        // k per stage: one Q4_K scale pair, half of a Q6_K 128-run
-constexpr int GM_THREADS = 512;     // dequantising threads: four per weight row and k-step (one more warp issues the MMAs)
+constexpr int GM_THREADS = 512;     // dequantising threads: four per weight row and k-step (two more warps: MMAs, copies)
 constexpr unsigned GM_A_BYTES = 2u * 8u * GM_ROWS * 16u;  // hi + lo, 8 k-chunks, 128 rows, 16 bytes: 32 KB
 constexpr unsigned GM_WAIT = 1u << 20;
+constexpr float GM_SCALE = 64.0f;   // weights carry 2^6: keeps the low f16 term of small weights out of the denormal
+                                    // range and the high term finite up to |w| = 1000
 
 struct GemmArgs {
   // up to three matrices over the same columns and token rows in one launch (q, k, v; gate, up): matrix i owns
@@ -44,15 +52,40 @@ struct GemmArgs {
   size_t part_stride[3];  // floats between the outputs of consecutive k splits
   unsigned rows[3], tile0[4];
   size_t row_bytes;
-  const __half* xt;   // [k-steps][2][8][NP][8] halves
+  const __half* xt;   // [chunks of 8 k][2][NP][8] halves
   unsigned cols, n_tok, np;        // np: token count padded to a multiple of 16 (<= 256)
-  unsigned tmem_cols;              // power of two >= max(32, np)
+  unsigned tmem_cols;              // power of two >= max(32, accumulator columns)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
-  unsigned nb;                     // B stages (2..4): token rows are requested up to nb - 2 k-steps ahead
+  unsigned nb;                     // B stages (2 or 4): token rows are requested up to nb - 1 k-steps ahead
   unsigned* err;
 };
 
-// x[token, k] (f32, row stride ldx) -> the B image: k-step s, part p (0 hi, 1 lo), chunk c, token t, 8 halves.
+__device__ __forceinline__ uint32_t pack_h2(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+// Eight f32 values -> 16 bytes of hi and 16 bytes of lo halves (hi = rn(v), lo = rn(v - hi)).
+__device__ __forceinline__ void split8(const float (&w)[8], uint4& hi, uint4& lo) {
+  uint32_t h[4], l[4];
+#pragma unroll
+  for (int e = 0; e < 4; e++) {
+    const __half2 hh = __floats2half2_rn(w[2 * e], w[2 * e + 1]);
+    const float2 hf = __half22float2(hh);
+    h[e] = pack_h2(hh);
+    l[e] = pack_h2(__floats2half2_rn(w[2 * e] - hf.x, w[2 * e + 1] - hf.y));
+  }
+  hi = make_uint4(h[0], h[1], h[2], h[3]);
+  lo = make_uint4(l[0], l[1], l[2], l[3]);
+}
+// Eight f32 values -> token t, chunk ck of the B image: chunk c (8 k), part p (0 hi, 1 lo), token t, 8 halves.  A
+// chunk's hi and lo rows are neighbours, so one MMA can take both as 2 NP rows of B.
+__device__ __forceinline__ void put_split8(__half* xt, unsigned np, unsigned t, unsigned ck, const float (&v)[8]) {
+  uint4 hi, lo;
+  split8(v, hi, lo);
+  __half* base = xt + (size_t)ck * 2u * np * 8u + (size_t)t * 8u;
+  *reinterpret_cast<uint4*>(base) = hi;
+  *reinterpret_cast<uint4*>(base + (size_t)np * 8u) = lo;
+}
+
+// x[token, k] (f32, row stride ldx) -> the B image.  Rows past n_tok become zeros.
 __global__ void x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsigned np, unsigned cols, __half* xt) {
   ks_pdl_entry();
   const unsigned chunks = cols / 8u;
@@ -68,18 +101,7 @@ __global__ void x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsig
 #pragma unroll
     for (int e = 0; e < 8; e++) v[e] = 0.0f;
   }
-  __align__(16) __half2 hi[4], lo[4];
-#pragma unroll
-  for (int e = 0; e < 4; e++) {
-    const __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-    const float2 hf = __half22float2(h);
-    hi[e] = h;
-    lo[e] = __floats2half2_rn(v[2 * e] - hf.x, v[2 * e + 1] - hf.y);
-  }
-  const unsigned s = ck >> 3, c = ck & 7u;
-  __half* base = xt + ((size_t)s * 2u * 8u + c) * np * 8u + (size_t)t * 8u;
-  *reinterpret_cast<uint4*>(base) = *reinterpret_cast<const uint4*>(hi);
-  *reinterpret_cast<uint4*>(base + (size_t)8u * np * 8u) = *reinterpret_cast<const uint4*>(lo);
+  put_split8(xt, np, t, ck, v);
 }
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -119,22 +141,7 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, unsigned lbo, un
          (1ull << 46);
 }
 
-__device__ __forceinline__ uint32_t pack_h2(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-// Eight f32 weights (already scaled by 2^8) -> 16 bytes of hi and 16 bytes of lo halves.
-__device__ __forceinline__ void split8(const float (&w)[8], uint4& hi, uint4& lo) {
-  uint32_t h[4], l[4];
-#pragma unroll
-  for (int e = 0; e < 4; e++) {
-    const __half2 hh = __floats2half2_rn(w[2 * e], w[2 * e + 1]);
-    const float2 hf = __half22float2(hh);
-    h[e] = pack_h2(hh);
-    l[e] = pack_h2(__floats2half2_rn(w[2 * e] - hf.x, w[2 * e + 1] - hf.y));
-  }
-  hi = make_uint4(h[0], h[1], h[2], h[3]);
-  lo = make_uint4(l[0], l[1], l[2], l[3]);
-}
-
-// The packed bytes one thread needs for one k-step, fetched a step ahead of their use.  Thread (row, quarter qd)
+// The packed bytes one thread needs for one k-step, fetched two steps ahead of their use.  Thread (row, quarter qd)
 // owns weights [64 ks + 16 qd, +16) of its row: chunks 2 qd and 2 qd + 1 of the stage.
 template <int DT>
 struct Raw;
@@ -144,36 +151,50 @@ struct Raw<KS_Q4K> {
 };
 template <>
 struct Raw<KS_Q6K> {
-  uint32_t ql[2], qh;  // 16 nibbles, 16 bit pairs
-  float ds;            // 2^8 d sc of the quarter's 16-run
+  uint32_t ql[4], qh[4];  // the 16 bytes that hold the quarter's nibbles, the 16 bytes that hold its bit pairs
+  float ds;               // 2^6 d sc of the quarter's 16-run
 };
 
+// A read-only load the compiler must issue where it is written (it may not sink it towards the first use, which is
+// two k-steps later): the weights have to be in flight while the steps before them are converted.
+__device__ __forceinline__ uint4 ldg_now(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_now32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned qd, unsigned ks, Raw<KS_Q4K>& w) {
   const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 144u;
-  w.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-  w.q = __ldg(reinterpret_cast<const uint4*>(blk + 16u + 32u * (ks & 3u) + 16u * (qd & 1u)));
+  w.hdr = ldg_now(blk);
+  w.q = ldg_now(blk + 16u + 32u * (ks & 3u) + 16u * (qd & 1u));
+}
+// 16 bytes from a 2-byte-aligned address: five aligned words, shifted into place (the fifth lies inside the same
+// 210-byte block wherever this is used).
+__device__ __forceinline__ void load16_a2(const uint8_t* p, uint32_t (&o)[4]) {
+  const unsigned sh = 8u * (unsigned)((uintptr_t)p & 3u);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - (sh >> 3));
+  const uint32_t x0 = ldg_now32(q), x1 = ldg_now32(q + 1), x2 = ldg_now32(q + 2), x3 = ldg_now32(q + 3), x4 = ldg_now32(q + 4);
+  o[0] = __funnelshift_r(x0, x1, sh);
+  o[1] = __funnelshift_r(x1, x2, sh);
+  o[2] = __funnelshift_r(x2, x3, sh);
+  o[3] = __funnelshift_r(x3, x4, sh);
 }
 // Q6_K: block = ql[128] qh[64] scales[16] d; a 128-run holds four groups g of 32 (gguf_impl.rs:761-791):
 // group g takes nibble g >> 1 of ql[32 (g & 1) + l] and bits 2g, 2g + 1 of qh[l]; scale index 2g + (l >> 4).
 __device__ __forceinline__ void load_raw(const uint8_t* W, size_t row_bytes, unsigned row, unsigned qd, unsigned ks, Raw<KS_Q6K>& w) {
-  const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 210u;
+  const uint8_t* blk = W + (size_t)row * row_bytes + (size_t)(ks >> 2) * 210u;  // blocks are 2-byte aligned
   const unsigned n = (ks >> 1) & 1u, g = 2u * (ks & 1u) + (qd >> 1), sub = qd & 1u;
-  const uint16_t* ql = reinterpret_cast<const uint16_t*>(blk + 64u * n + 32u * (g & 1u) + 16u * sub);  // blocks are 2-byte aligned
-  const uint16_t* qh = reinterpret_cast<const uint16_t*>(blk + 128u + 32u * n + 16u * sub);
-  w.ql[0] = w.ql[1] = w.qh = 0;
-#pragma unroll
-  for (int i = 0; i < 8; i++) {  // pair i: elements l = 2i, 2i + 1 of the 16-run
-    const uint32_t lo = __ldg(ql + i), hi = __ldg(qh + i);
-    const uint32_t ln = ((lo >> (4u * (g >> 1))) & 0xFu) | (((lo >> (8u + 4u * (g >> 1))) & 0xFu) << 4);
-    const uint32_t hn = ((hi >> (2u * g)) & 3u) | (((hi >> (8u + 2u * g)) & 3u) << 2);
-    w.ql[i >> 2] |= ln << (8 * (i & 3));
-    w.qh |= hn << (4 * i);
-  }
+  load16_a2(blk + 64u * n + 32u * (g & 1u) + 16u * sub, w.ql);
+  load16_a2(blk + 128u + 32u * n + 16u * sub, w.qh);
   const int8_t sc = *reinterpret_cast<const int8_t*>(blk + 192u + 8u * n + 2u * g + sub);
-  w.ds = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * 256.0f * (float)sc;
+  w.ds = __half2float(*reinterpret_cast<const __half*>(blk + 208u)) * GM_SCALE * (float)sc;
 }
 
-// 2^8 d sc and 2^8 dmin m of the four sub-blocks 2j + h (j = 0..3) of a Q4_K super-block: get_scale_min_k4
+// 2^6 d sc and 2^6 dmin m of the four sub-blocks 2j + h (j = 0..3) of a Q4_K super-block: get_scale_min_k4
 // (gguf_impl.rs:563-573) for the half h this thread always works on, decoded once per super-block instead of once
 // per k-step.
 struct Q4Scales {
@@ -181,7 +202,7 @@ struct Q4Scales {
 };
 __device__ __forceinline__ void q4k_half_scales(const uint4 hdr, unsigned h, Q4Scales& o) {
   const __half2 dd = *reinterpret_cast<const __half2*>(&hdr.x);
-  const float d = __low2float(dd) * 256.0f, dmin = __high2float(dd) * 256.0f;
+  const float d = __low2float(dd) * GM_SCALE, dmin = __high2float(dd) * GM_SCALE;
   const unsigned sh = 8u * h;
   // bytes q[h], q[2+h] | q[4+h], q[6+h] | q[8+h], q[10+h] of the 12 scale bytes
   const unsigned a0 = (hdr.y >> sh) & 0xFFu, a2 = (hdr.y >> (16u + sh)) & 0xFFu;
@@ -211,61 +232,78 @@ __device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, const Q4Scale
     }
     return;
   }
-  const unsigned h = qd >> 1;
-  float dsc = 0.0f, dm = 0.0f;
-  uint32_t nib[4] = {0, 0, 0, 0};
   if constexpr (DT == KS_Q4K) {
-    const unsigned j = ks & 3u;  // selects, no dynamic indexing
-    dsc = j == 0 ? sc4.dsc[0] : j == 1 ? sc4.dsc[1] : j == 2 ? sc4.dsc[2] : sc4.dsc[3];
-    dm = j == 0 ? sc4.dm[0] : j == 1 ? sc4.dm[1] : j == 2 ? sc4.dm[2] : sc4.dm[3];
+    // d*sc*q - dmin*m as gguf_impl.rs:690-721 rounds it (times 2^6), then the two f16 terms
+    const unsigned h = qd >> 1, j = ks & 3u;  // selects, no dynamic indexing
+    const float dsc = j == 0 ? sc4.dsc[0] : j == 1 ? sc4.dsc[1] : j == 2 ? sc4.dsc[2] : sc4.dsc[3];
+    const float dm = j == 0 ? sc4.dm[0] : j == 1 ? sc4.dm[1] : j == 2 ? sc4.dm[2] : sc4.dm[3];
     const unsigned sh = 4u * h;
-    nib[0] = (w.q.x >> sh) & 0x0F0F0F0Fu;
-    nib[1] = (w.q.y >> sh) & 0x0F0F0F0Fu;
-    nib[2] = (w.q.z >> sh) & 0x0F0F0F0Fu;
-    nib[3] = (w.q.w >> sh) & 0x0F0F0F0Fu;
-  }
+    const uint32_t nib[4] = {(w.q.x >> sh) & 0x0F0F0F0Fu, (w.q.y >> sh) & 0x0F0F0F0Fu, (w.q.z >> sh) & 0x0F0F0F0Fu, (w.q.w >> sh) & 0x0F0F0F0Fu};
 #pragma unroll
-  for (int cc = 0; cc < 2; cc++) {
-    float v[8];
-    if constexpr (DT == KS_Q4K) {
+    for (int cc = 0; cc < 2; cc++) {
+      float v[8];
 #pragma unroll
       for (int e = 0; e < 8; e++) {
         // one byte permute puts nibble byte e under the exponent of 2^23: the float 2^23 + q, then an exact subtract
         const float q = __uint_as_float(__byte_perm(nib[2 * cc + (e >> 2)], 0x4B000000u, 0x7440u | (unsigned)(e & 3))) - 8388608.0f;
-        v[e] = __fsub_rn(__fmul_rn(dsc, q), dm);  // d*sc*q - dmin*m as gguf_impl.rs:618-633 rounds it, times 2^8
+        v[e] = __fsub_rn(__fmul_rn(dsc, q), dm);
       }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; e++) {  // element l = 8 cc + e of the 16-run
-        const uint32_t lq = (w.ql[cc] >> (4 * e)) & 0xFu;
-        const uint32_t hq = (w.qh >> (16 * cc + 2 * e)) & 3u;
-        v[e] = w.ds * (float)((int)(lq | (hq << 4)) - 32);
-      }
+      uint4 hi, lo;
+      split8(v, hi, lo);
+      Ahi[(size_t)cc * GM_ROWS] = hi;
+      Alo[(size_t)cc * GM_ROWS] = lo;
     }
-    uint4 hi, lo;
-    split8(v, hi, lo);
-    Ahi[(size_t)cc * GM_ROWS] = hi;
-    Alo[(size_t)cc * GM_ROWS] = lo;
+  } else {
+    // (2^6 d sc) q in half2 arithmetic: the f32 scale A is cut into A1 = A rounded to 6 significant bits (A1 q is
+    // exact in f16 for q in -32..31) and A2 = A - A1 (at most 11 significant bits: exact in f16); q + 32 comes out of
+    // the packed bytes as the half 0x5400 | (q + 32) << 4 = 64 + (q + 32) by one byte permute and one OR; one exact
+    // add makes it q, and two multiplies give hi = A1 q (exact) and lo = rn(A2 q): hi + lo is A q to 2^-17.
+    const unsigned g = 2u * (ks & 1u) + (qd >> 1);
+    const __half a1 = __float2half_rn(__uint_as_float((__float_as_uint(w.ds) + 0x00020000u) & 0xFFFC0000u));
+    const __half2 s1 = __half2half2(a1), s2 = __half2half2(__float2half_rn(w.ds - __half2float(a1)));
+    const __half2 bias = __float2half2_rn(-96.0f);
+    const unsigned shl = 4u * (1u - (g >> 1)), shh = 2u * g;
+    uint32_t hi[8], lo[8];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const uint32_t tl = (w.ql[k] << shl) & 0xF0F0F0F0u;   // the nibble at bits 4..7 of its byte
+      const uint32_t th = (w.qh[k] >> shh) & 0x03030303u;   // the bit pair at bits 0..1: bits 8..9 of the half
+      const __half2 p0 = __hadd2(as_h2(__byte_perm(tl, th, 0x5140u) | 0x54005400u), bias);
+      const __half2 p1 = __hadd2(as_h2(__byte_perm(tl, th, 0x7362u) | 0x54005400u), bias);
+      hi[2 * k] = pack_h2(__hmul2(p0, s1));
+      hi[2 * k + 1] = pack_h2(__hmul2(p1, s1));
+      lo[2 * k] = pack_h2(__hmul2(p0, s2));
+      lo[2 * k + 1] = pack_h2(__hmul2(p1, s2));
+    }
+#pragma unroll
+    for (int cc = 0; cc < 2; cc++) {
+      Ahi[(size_t)cc * GM_ROWS] = make_uint4(hi[4 * cc], hi[4 * cc + 1], hi[4 * cc + 2], hi[4 * cc + 3]);
+      Alo[(size_t)cc * GM_ROWS] = make_uint4(lo[4 * cc], lo[4 * cc + 1], lo[4 * cc + 2], lo[4 * cc + 3]);
+    }
   }
 }
 
 // grid = (row tiles, k splits): CTA (bx, by) multiplies rows [128 bx, +128) over k-steps [by * per, (by + 1) * per)
 // and stores its sums at y + by * part_stride (a partial when there is more than one split).
+// Warps 0..15 dequantise; lane 0 of warp 16 issues the MMAs; lane 0 of warp 17 requests the token rows.  Step i uses
+// A stage i % 2 and B stage i % nb (nb = 2 or 4); its MMAs commit to free[i % nb], which releases both.
 template <int DT>
-__global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const GemmArgs a) {
+__global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  // [0,32): mbarriers fullB[4]; [32,48): freed[2]; [48,56): done; [64,80): fullA[2]; [96,100): tensor-memory address;
-  // from 1024: two A stages, then the ring of B stages
+  // [0,32): mbarriers fullB[4]; [32,64): free[4]; [64,72): done; [72,88): fullA[2]; [96,100): tensor-memory address;
+  // [100,104): failure flag; from 1024: two A stages, then the ring of B stages
   const uint32_t bars = sm32(smem);
-  const uint32_t bar_freed = bars + 32u, bar_done = bars + 48u, bar_fullA = bars + 64u;
+  const uint32_t bar_free = bars + 32u, bar_done = bars + 64u, bar_fullA = bars + 72u;
   uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 96);
   volatile unsigned* fail = reinterpret_cast<volatile unsigned*>(smem + 100);  // a bounded wait gave up somewhere in the CTA
-  const unsigned b_bytes = a.np * 256u;                 // hi + lo, 8 chunks, np tokens, 16 bytes
+  const unsigned b_bytes = a.np * 256u;                 // 8 chunks, hi + lo, np tokens, 16 bytes
   unsigned char* A0 = smem + 1024;
   unsigned char* B0 = A0 + 2u * GM_A_BYTES;
-  const unsigned nb = a.nb;                             // B stages: the copies run up to nb - 1 steps ahead
+  const unsigned nb = a.nb;
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-  const unsigned r = tid & (GM_ROWS - 1), qd = tid >> 7;
+  // a producer warp takes 8 rows x 4 quarters: its 32 loads of a k-step fall into 8 runs of contiguous bytes, and the
+  // 8 lanes that store together (same quarter) write 128 contiguous bytes
+  const unsigned r = ((warp << 3) | (tid & 7u)) & (GM_ROWS - 1), qd = (tid >> 3) & 3u;
   // which matrix this row tile belongs to (selects, no dynamic indexing of the parameter arrays)
   const unsigned bx = blockIdx.x;
   const int seg = (bx >= a.tile0[1]) + (bx >= a.tile0[2]);
@@ -281,7 +319,7 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
   float* yout = (seg == 0 ? a.y[0] : seg == 1 ? a.y[1] : a.y[2]) + (size_t)blockIdx.y * part_stride;
 
   // weights do not depend on the kernels before this one: the first two k-steps are fetched right away
-  const bool producer = warp < GM_THREADS / 32;  // warps 0..15 dequantise, warp 16 feeds the tensor core
+  const bool producer = warp < GM_THREADS / 32;
   Raw<DT> raw0, raw1;
   Q4Scales sc4{};
   if (producer && live) {
@@ -289,7 +327,7 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
     if (ksteps > 1) load_raw(W, a.row_bytes, row, qd, ks0 + 1, raw1);
   }
   if (tid == 0) {
-    for (int i = 0; i < 7; i++) mb_init(bars + 8u * i, 1);                 // fullB[4], freed[2], done: one arrival each
+    for (int i = 0; i < 9; i++) mb_init(bars + 8u * i, 1);                    // fullB[4], free[4], done: one arrival each
     for (int i = 0; i < 2; i++) mb_init(bar_fullA + 8u * i, GM_THREADS / 32);  // fullA[2]: one arrival per producer warp
     *fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -304,9 +342,9 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
   if (producer) {
     // ---- 16 warps: packed weights -> two f16 terms -> A stage; no block-wide barrier inside the loop
     for (unsigned i = 0; i < ksteps; i++) {
-      const unsigned ks = ks0 + i, s = i & 1u, u = i >> 1;
+      const unsigned ks = ks0 + i, s = i & 1u;
       unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
-      if (u > 0 && !mb_wait(bar_freed + 8u * s, (u - 1u) & 1u, GM_WAIT)) {  // the MMAs of step i - 2 still read this stage
+      if (i >= 2u && !mb_wait(bar_free + 8u * ((i - 2u) % nb), ((i - 2u) / nb) & 1u, GM_WAIT)) {  // the MMAs of step i - 2 still read this stage
         *fail = 1;
         break;
       }
@@ -316,60 +354,68 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
       if constexpr (DT == KS_Q4K)
         if (i == 0 || (ks & 3u) == 0) q4k_half_scales(cur.hdr, qd >> 1, sc4);  // a new super-block
       dequant_to_stage<DT>(cur, sc4, live, qd, ks, A, r);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores of A, then the tensor core's reads
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_fullA + 8u * s) : "memory");
-    }
-  } else if (lane == 0) {
-    // ---- one thread: token-row copies ahead, MMAs as soon as both operands of a step are there
-    const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
-    unsigned issued_b = 0;
-    bool ok = true;
-    for (unsigned i = 0; i < ksteps && ok; i++) {
-      const unsigned s = i & 1u, u = i >> 1, t = i % nb;
-      // B(j) goes into stage j % nb, last read by the MMAs of step j - nb; copies run up to nb - 2 steps ahead, so
-      // the stage they overwrite belongs to a step whose MMAs ended long ago (never the one just issued)
-      while (ok && issued_b < ksteps && issued_b < i + nb - 1u) {
-        const unsigned j = issued_b;
-        if (j >= nb) {  // wait for the MMAs of step j - nb (they committed to freed[(j - nb) & 1])
-          const unsigned k = j - nb;
-          if (!mb_wait(bar_freed + 8u * (k & 1u), (k >> 1) & 1u, GM_WAIT)) {
-            ok = false;
-            break;
-          }
-        }
-        const uint32_t fb = bars + 8u * (j % nb);
-        mb_expect(fb, b_bytes);
-        bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
-        issued_b++;
+      if (lane == 0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the warp's generic-proxy stores of A, then the tensor core's reads
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_fullA + 8u * s) : "memory");
       }
-      if (!ok || !mb_wait(bar_fullA + 8u * s, u & 1u, GM_WAIT) || !mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT)) {
+    }
+  } else if (warp == GM_THREADS / 32 && lane == 0) {
+    // ---- one thread: the MMAs of a step as soon as both operands are there
+    const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
+    // up to 128 token rows: the hi and lo rows of B go through ONE instruction as 2 NP rows (columns [0, NP) take
+    // Ahi.Bhi, columns [NP, 2 NP) Ahi.Blo), so the tensor core fetches the A tile twice per 16 k instead of three times
+    const bool cat = a.np <= 128u;
+    const uint32_t idesc2 = (1u << 4) | ((a.np >> 2) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);
+    // descriptors of the first chunk pair of stage 0; the address field counts 16-byte units and shared memory ends
+    // below its 14 bits, so the other stages and chunks are plain additions
+    const uint64_t a_desc0 = tc_desc(sm32(A0), GM_ROWS * 16u, 128u), b_desc0 = tc_desc(sm32(B0), 2u * a.np * 16u, 128u);
+    bool ok = true;
+    for (unsigned i = 0; i < ksteps; i++) {
+      const unsigned s = i & 1u, t = i % nb;
+      if (!mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT) || !mb_wait(bar_fullA + 8u * s, (i >> 1) & 1u, GM_WAIT)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t a0 = sm32(A0 + (size_t)s * GM_A_BYTES), b0 = sm32(B0 + (size_t)t * b_bytes);
+      const uint64_t a_hi = a_desc0 + (uint64_t)(s * (GM_A_BYTES >> 4)), b_hi = b_desc0 + (uint64_t)(t * (b_bytes >> 4));
 #pragma unroll
       for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
-        const uint64_t ah = tc_desc(a0 + (2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
-        const uint64_t al = tc_desc(a0 + (8u + 2u * j) * (GM_ROWS * 16u), GM_ROWS * 16u, 128u);
-        const uint64_t bh = tc_desc(b0 + (2u * j) * (a.np * 16u), a.np * 16u, 128u);
-        const uint64_t bl = tc_desc(b0 + (8u + 2u * j) * (a.np * 16u), a.np * 16u, 128u);
-        tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
-        tc_mma_f16(tmem, ah, bl, idesc, 1u);
+        const uint64_t ah = a_hi + (uint64_t)(2u * j * GM_ROWS);
+        const uint64_t al = ah + (uint64_t)(8u * GM_ROWS);
+        const uint64_t bh = b_hi + (uint64_t)(4u * j * a.np);  // chunk 2j: 2 NP rows of 16 bytes each
+        if (cat) {
+          tc_mma_f16(tmem, ah, bh, idesc2, (i | j) ? 1u : 0u);
+        } else {
+          tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
+          tc_mma_f16(tmem, ah, bh + (uint64_t)a.np, idesc, 1u);
+        }
         tc_mma_f16(tmem, al, bh, idesc, 1u);
       }
-      tc_commit(bar_freed + 8u * s);
+      tc_commit(bar_free + 8u * t);
       if (i + 1 == ksteps) tc_commit(bar_done);
     }
     if (!ok) {
       *fail = 1;
-      // what this thread started must finish before shared and tensor memory go away (bounded): the copies still in
-      // flight, and every MMA issued so far (a fresh commit tracks them all)
-      for (unsigned j = issued_b > nb ? issued_b - nb : 0u; j < issued_b; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
+      // every MMA issued so far must finish before shared and tensor memory go away (bounded): a fresh commit tracks them all
       tc_commit(bar_done);
       mb_wait(bar_done, 0u, GM_WAIT);
     }
+  } else if (warp == GM_THREADS / 32 + 1 && lane == 0) {
+    // ---- one thread: token rows of step j into B stage j % nb, as soon as the MMAs of step j - nb are done
+    unsigned issued = 0;
+    for (unsigned j = 0; j < ksteps; j++) {
+      if (j >= nb && !mb_wait(bar_free + 8u * (j % nb), (j / nb - 1u) & 1u, GM_WAIT)) {
+        *fail = 1;
+        break;
+      }
+      const uint32_t fb = bars + 8u * (j % nb);
+      mb_expect(fb, b_bytes);
+      bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
+      issued++;
+    }
+    // the copies must have landed before this CTA's shared memory goes away (bounded; all done already unless a wait gave up)
+    for (unsigned j = issued > nb ? issued - nb : 0u; j < issued; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
   }
   __syncthreads();
   bool ok = *fail == 0;
@@ -381,12 +427,19 @@ __global__ void __launch_bounds__(GM_THREADS + 32, 2) gemm_kq_tc_kernel(const Ge
     const unsigned lane_base = (warp & 3u) * 32u;
     const unsigned out_row = row_base + lane_base + lane;
     for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 32u) {
-      uint32_t v[8];
+      uint32_t v[8], v2[8];
       tc_ld8(tmem + (lane_base << 16) + c0, v);
+      if (a.np <= 128u) {
+        tc_ld8(tmem + (lane_base << 16) + a.np + c0, v2);  // the columns that took Ahi.Blo
+      } else {
+#pragma unroll
+        for (unsigned e = 0; e < 8; e++) v2[e] = 0u;
+      }
       if (out_row < seg_rows) {
 #pragma unroll
         for (unsigned e = 0; e < 8; e++)
-          if (c0 + e < a.n_tok) yout[(size_t)(c0 + e) * ldy + out_row] = __uint_as_float(v[e]) * (1.0f / 256.0f);
+          if (c0 + e < a.n_tok)
+            yout[(size_t)(c0 + e) * ldy + out_row] = (__uint_as_float(v[e]) + __uint_as_float(v2[e])) * (1.0f / GM_SCALE);
       }
     }
   } else if (!ok && tid == 0) {
@@ -434,15 +487,6 @@ __global__ void gemm_finish_kernel(const FinishArgs f) {
 }  // namespace
 
 namespace {
-// Eight f32 values -> 16 bytes of hi and 16 bytes of lo halves at token t, chunk ck of the B image.
-__device__ __forceinline__ void put_split8(__half* xt, unsigned np, unsigned t, unsigned ck, const float (&v)[8]) {
-  uint4 hi, lo;
-  split8(v, hi, lo);
-  __half* base = xt + ((size_t)(ck >> 3) * 16u + (ck & 7u)) * np * 8u + (size_t)t * 8u;
-  *reinterpret_cast<uint4*>(base) = hi;
-  *reinterpret_cast<uint4*>(base + (size_t)8u * np * 8u) = lo;
-}
-
 // The sum of a matrix's k-split partials straight into what consumes it, one block per token row:
 //   y = sum of partials;  x = res + rms(y) * w_post (lower.rs:3926-4077, the residual update of lib.rs:539);
 //   the image of rms(x) * w_norm for the next GEMM.
@@ -539,12 +583,11 @@ __global__ void gemm_finish_gelu_split_kernel(const float* P0, const float* P1, 
 
 namespace {
 unsigned gemm_np(int n_tok) { return ((unsigned)n_tok + 15u) / 16u * 16u; }
-// Shared memory of one CTA and the B stages it gets: the two A stages, then as many B stages as fit, at most four.
+// Shared memory of one CTA and the B stages it gets: the two A stages, then four B stages if they fit, else two.
 size_t gemm_smem(const ks_ctx* ctx, unsigned np, unsigned* nb_out) {
   const size_t fixed = 1024 + 2 * (size_t)GM_A_BYTES, bb = (size_t)np * 256;
   if (fixed + 2 * bb > ctx->smem_optin) return 0;
-  size_t nb = (ctx->smem_optin - fixed) / bb;
-  nb = nb > 4 ? 4 : nb;
+  const size_t nb = fixed + 4 * bb <= ctx->smem_optin ? 4 : 2;  // even: step i's MMAs release A stage i % 2 and B stage i % nb together
   if (nb_out) *nb_out = (unsigned)nb;
   return fixed + nb * bb;
 }
@@ -620,8 +663,8 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
   a.cols = (unsigned)cols;
   a.n_tok = (unsigned)n_tok;
   a.np = gemm_np(n_tok);
-  a.tmem_cols = 32;
-  while (a.tmem_cols < a.np) a.tmem_cols <<= 1;
+  a.tmem_cols = 32;  // the accumulator: 2 NP columns up to 128 token rows (hi and lo products side by side), NP beyond
+  while (a.tmem_cols < (a.np <= 128 ? 2 * a.np : a.np)) a.tmem_cols <<= 1;
   const unsigned ksteps = (unsigned)(cols / GM_KSTEP);
   unsigned splits = gemm_splits(ctx, total_rows, cols, n_tok);
   a.ksteps_per = (ksteps + splits - 1) / splits;
@@ -658,7 +701,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     if (e != cudaSuccess) return ks_fail(ctx, KS_ERR_CUDA, "gemm: cannot set %zu B shared memory: %s", smem, cudaGetErrorString(e));
     set = smem;
   }
-  KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS + 32, smem, a);
+  KS_LAUNCH(ctx, kern, dim3(tiles, splits), GM_THREADS + 64, smem, a);
   int rc = ks_after_launch(ctx, "gemm_kq_tc");
   if (rc || direct) return rc;
   if (mode == KS_GEMM_NORM_SPLIT) {
