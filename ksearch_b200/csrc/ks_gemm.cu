@@ -56,10 +56,16 @@ struct GemmArgs {
   unsigned cols, n_tok, np;        // np: token count padded to a multiple of 16 (<= 256)
   unsigned tmem_cols;              // power of two >= max(32, accumulator columns)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
-  unsigned nb;                     // B stages (2 or 4): token rows are requested up to nb - 1 k-steps ahead
+  unsigned nb;                     // stages (2..4) of the A ring and of the B ring
   unsigned* err;
 };
 
+// 1 in exactly one lane of a converged warp.
+__device__ __forceinline__ unsigned elect_one() {
+  unsigned pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred;
+}
 __device__ __forceinline__ uint32_t pack_h2(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 // Eight f32 values -> 16 bytes of hi and 16 bytes of lo halves (hi = rn(v), lo = rn(v - hi)).
@@ -285,21 +291,21 @@ __device__ __forceinline__ void dequant_to_stage(const Raw<DT>& w, const Q4Scale
 
 // grid = (row tiles, k splits): CTA (bx, by) multiplies rows [128 bx, +128) over k-steps [by * per, (by + 1) * per)
 // and stores its sums at y + by * part_stride (a partial when there is more than one split).
-// Warps 0..15 dequantise; lane 0 of warp 16 issues the MMAs; lane 0 of warp 17 requests the token rows.  Step i uses
-// A stage i % 2 and B stage i % nb (nb = 2 or 4); its MMAs commit to free[i % nb], which releases both.
+// Warps 0..15 dequantise; an elected lane of warp 16 issues the MMAs; an elected lane of warp 17 requests the token rows.  Step i uses
+// stage i % nb of the A ring and of the B ring (nb = 2..4); its MMAs commit to free[i % nb], which releases both.
 template <int DT>
 __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const GemmArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  // [0,32): mbarriers fullB[4]; [32,64): free[4]; [64,72): done; [72,88): fullA[2]; [96,100): tensor-memory address;
-  // [100,104): failure flag; from 1024: two A stages, then the ring of B stages
+  // [0,32): mbarriers fullB[4]; [32,64): free[4]; [64,72): done; [72,104): fullA[4]; [104,108): tensor-memory address;
+  // [108,112): failure flag; from 1024: the A stages, then the B stages
   const uint32_t bars = sm32(smem);
   const uint32_t bar_free = bars + 32u, bar_done = bars + 64u, bar_fullA = bars + 72u;
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 96);
-  volatile unsigned* fail = reinterpret_cast<volatile unsigned*>(smem + 100);  // a bounded wait gave up somewhere in the CTA
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + 104);
+  volatile unsigned* fail = reinterpret_cast<volatile unsigned*>(smem + 108);  // a bounded wait gave up somewhere in the CTA
   const unsigned b_bytes = a.np * 256u;                 // 8 chunks, hi + lo, np tokens, 16 bytes
   unsigned char* A0 = smem + 1024;
-  unsigned char* B0 = A0 + 2u * GM_A_BYTES;
   const unsigned nb = a.nb;
+  unsigned char* B0 = A0 + (size_t)nb * GM_A_BYTES;
   const unsigned tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
   // a producer warp takes 8 rows x 4 quarters: its 32 loads of a k-step fall into 8 runs of contiguous bytes, and the
   // 8 lanes that store together (same quarter) write 128 contiguous bytes
@@ -328,7 +334,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
   }
   if (tid == 0) {
     for (int i = 0; i < 9; i++) mb_init(bars + 8u * i, 1);                    // fullB[4], free[4], done: one arrival each
-    for (int i = 0; i < 2; i++) mb_init(bar_fullA + 8u * i, GM_THREADS / 32);  // fullA[2]: one arrival per producer warp
+    for (int i = 0; i < 4; i++) mb_init(bar_fullA + 8u * i, GM_THREADS / 32);  // fullA[4]: one arrival per producer warp
     *fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -342,9 +348,9 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
   if (producer) {
     // ---- 16 warps: packed weights -> two f16 terms -> A stage; no block-wide barrier inside the loop
     for (unsigned i = 0; i < ksteps; i++) {
-      const unsigned ks = ks0 + i, s = i & 1u;
+      const unsigned ks = ks0 + i, s = i % nb;
       unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
-      if (i >= 2u && !mb_wait(bar_free + 8u * ((i - 2u) % nb), ((i - 2u) / nb) & 1u, GM_WAIT)) {  // the MMAs of step i - 2 still read this stage
+      if (i >= nb && !mb_wait(bar_free + 8u * s, (i / nb - 1u) & 1u, GM_WAIT)) {  // the MMAs of step i - nb still read this stage
         *fail = 1;
         break;
       }
@@ -360,8 +366,11 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_fullA + 8u * s) : "memory");
       }
     }
-  } else if (warp == GM_THREADS / 32 && lane == 0) {
-    // ---- one thread: the MMAs of a step as soon as both operands are there
+  } else if (warp == GM_THREADS / 32) {
+    // ---- the MMAs of a step as soon as both operands are there.  The whole warp runs the loop, converged, and one
+    // elected lane issues: the loop state and the 64-bit descriptors then live in uniform registers, which is where
+    // tcgen05.mma reads them (computed inside a one-lane branch they are moved there one by one, ~150 cycles per MMA).
+    const unsigned leader = elect_one();
     const uint32_t idesc = (1u << 4) | ((a.np >> 3) << 17) | ((unsigned)(GM_ROWS >> 4) << 24);  // f32 accumulate, f16 x f16, K-major both
     // up to 128 token rows: the hi and lo rows of B go through ONE instruction as 2 NP rows (columns [0, NP) take
     // Ahi.Bhi, columns [NP, 2 NP) Ahi.Blo), so the tensor core fetches the A tile twice per 16 k instead of three times
@@ -372,47 +381,60 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
     const uint64_t a_desc0 = tc_desc(sm32(A0), GM_ROWS * 16u, 128u), b_desc0 = tc_desc(sm32(B0), 2u * a.np * 16u, 128u);
     bool ok = true;
     for (unsigned i = 0; i < ksteps; i++) {
-      const unsigned s = i & 1u, t = i % nb;
-      if (!mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT) || !mb_wait(bar_fullA + 8u * s, (i >> 1) & 1u, GM_WAIT)) {
+      const unsigned t = i % nb, s = t;
+      const bool got = mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT) && mb_wait(bar_fullA + 8u * s, (i / nb) & 1u, GM_WAIT);
+      if (!__all_sync(0xffffffffu, got)) {
         ok = false;
         break;
       }
       tc_fence_after();
       const uint64_t a_hi = a_desc0 + (uint64_t)(s * (GM_A_BYTES >> 4)), b_hi = b_desc0 + (uint64_t)(t * (b_bytes >> 4));
+      if (leader) {
 #pragma unroll
-      for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
-        const uint64_t ah = a_hi + (uint64_t)(2u * j * GM_ROWS);
-        const uint64_t al = ah + (uint64_t)(8u * GM_ROWS);
-        const uint64_t bh = b_hi + (uint64_t)(4u * j * a.np);  // chunk 2j: 2 NP rows of 16 bytes each
-        if (cat) {
-          tc_mma_f16(tmem, ah, bh, idesc2, (i | j) ? 1u : 0u);
-        } else {
-          tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
-          tc_mma_f16(tmem, ah, bh + (uint64_t)a.np, idesc, 1u);
+        for (unsigned j = 0; j < 4; j++) {  // 16 k each: chunks 2j, 2j+1
+          const uint64_t ah = a_hi + (uint64_t)(2u * j * GM_ROWS);
+          const uint64_t al = ah + (uint64_t)(8u * GM_ROWS);
+          const uint64_t bh = b_hi + (uint64_t)(4u * j * a.np);  // chunk 2j: 2 NP rows of 16 bytes each
+          if (cat) {
+            tc_mma_f16(tmem, ah, bh, idesc2, (i | j) ? 1u : 0u);
+          } else {
+            tc_mma_f16(tmem, ah, bh, idesc, (i | j) ? 1u : 0u);
+            tc_mma_f16(tmem, ah, bh + (uint64_t)a.np, idesc, 1u);
+          }
+          tc_mma_f16(tmem, al, bh, idesc, 1u);
         }
-        tc_mma_f16(tmem, al, bh, idesc, 1u);
+        tc_commit(bar_free + 8u * t);
+        if (i + 1 == ksteps) tc_commit(bar_done);
       }
-      tc_commit(bar_free + 8u * t);
-      if (i + 1 == ksteps) tc_commit(bar_done);
+      __syncwarp();
     }
     if (!ok) {
-      *fail = 1;
       // every MMA issued so far must finish before shared and tensor memory go away (bounded): a fresh commit tracks them all
-      tc_commit(bar_done);
+      if (leader) {
+        *fail = 1;
+        tc_commit(bar_done);
+      }
+      __syncwarp();
       mb_wait(bar_done, 0u, GM_WAIT);
     }
-  } else if (warp == GM_THREADS / 32 + 1 && lane == 0) {
-    // ---- one thread: token rows of step j into B stage j % nb, as soon as the MMAs of step j - nb are done
+  } else if (warp == GM_THREADS / 32 + 1) {
+    // ---- token rows of step j into B stage j % nb, as soon as the MMAs of step j - nb are done (whole warp in the
+    // loop, one elected lane issues)
+    const unsigned leader = elect_one();
     unsigned issued = 0;
     for (unsigned j = 0; j < ksteps; j++) {
-      if (j >= nb && !mb_wait(bar_free + 8u * (j % nb), (j / nb - 1u) & 1u, GM_WAIT)) {
-        *fail = 1;
+      const bool got = j < nb || mb_wait(bar_free + 8u * (j % nb), (j / nb - 1u) & 1u, GM_WAIT);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (leader) *fail = 1;
         break;
       }
-      const uint32_t fb = bars + 8u * (j % nb);
-      mb_expect(fb, b_bytes);
-      bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
+      if (leader) {
+        const uint32_t fb = bars + 8u * (j % nb);
+        mb_expect(fb, b_bytes);
+        bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
+      }
       issued++;
+      __syncwarp();
     }
     // the copies must have landed before this CTA's shared memory goes away (bounded; all done already unless a wait gave up)
     for (unsigned j = issued > nb ? issued - nb : 0u; j < issued; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
@@ -583,20 +605,25 @@ __global__ void gemm_finish_gelu_split_kernel(const float* P0, const float* P1, 
 
 namespace {
 unsigned gemm_np(int n_tok) { return ((unsigned)n_tok + 15u) / 16u * 16u; }
-// Shared memory of one CTA and the B stages it gets: the two A stages, then four B stages if they fit, else two.
+// Shared memory of one CTA and its stage count (A and B rings have the same depth): two stages when that lets two
+// CTAs share an SM (measured: a third stage that still lets them does not pay), else as many (up to four) as one CTA fits.
 size_t gemm_smem(const ks_ctx* ctx, unsigned np, unsigned* nb_out) {
-  const size_t fixed = 1024 + 2 * (size_t)GM_A_BYTES, bb = (size_t)np * 256;
-  if (fixed + 2 * bb > ctx->smem_optin) return 0;
-  const size_t nb = fixed + 4 * bb <= ctx->smem_optin ? 4 : 2;  // even: step i's MMAs release A stage i % 2 and B stage i % nb together
+  const size_t stage = (size_t)GM_A_BYTES + (size_t)np * 256, per_sm = ctx->smem_optin + 1024;  // the SM holds 1 KB more than a CTA may ask for
+  auto bytes = [&](size_t n) { return 1024 + n * stage; };
+  auto two_fit = [&](size_t n) { return 2 * (bytes(n) + 1024) <= per_sm; };  // each resident CTA costs 1 KB on top
+  if (bytes(2) > ctx->smem_optin) return 0;
+  size_t nb = 2;
+  if (!two_fit(2))
+    while (nb < 4 && bytes(nb + 1) <= ctx->smem_optin) nb++;
   if (nb_out) *nb_out = (unsigned)nb;
-  return fixed + nb * bb;
+  return bytes(nb);
 }
 // k splits of a launch over `tiles` row tiles: the count that minimises rounds x (k-steps per CTA + a fixed
 // start-up and epilogue cost of about three k-steps); two CTAs that share an SM cost each other about a fifth.
 unsigned gemm_splits(const ks_ctx* ctx, size_t rows, size_t cols, int n_tok) {
   const unsigned tiles = (unsigned)((rows + GM_ROWS - 1) / GM_ROWS), ksteps = (unsigned)(cols / GM_KSTEP);
   const size_t smem = gemm_smem(ctx, gemm_np(n_tok), nullptr);
-  const unsigned cps = smem && 2 * (smem + 1024) <= ctx->smem_optin ? 2u : 1u;
+  const unsigned cps = smem && 2 * (smem + 1024) <= ctx->smem_optin + 1024 ? 2u : 1u;
   const unsigned sms = (unsigned)ctx->sm_count, slots = sms * cps;
   if (const char* f = getenv("KSEARCH_GEMM_SPLITS")) {  // measurement override
     const unsigned s = (unsigned)atoi(f);
