@@ -334,7 +334,7 @@ def gemm_shape(ctx, dtype, rows, cols, n_tok, tag):
     return {"shape": f"{'Q4_K' if dtype == Q4K else 'Q6_K'} {rows}x{cols} x {n_tok} rows, fp32 x/y", "us": ms * 1e3,
             "weight_gbs": one.nbytes / ms / 1e6, "tflops_useful": flops / ms / 1e9,
             "tflops_issued": 3.0 * flops / ms / 1e9,
-            "note": "three f16 MMAs per product (hi.hi + hi.lo + lo.hi) keep f32 accuracy; bound by the CUDA-core dequantisation"}
+            "note": "three f16 products per weight and x (hi.hi + hi.lo + lo.hi) keep f32 accuracy; bound by the CUDA-core dequantisation and instruction issue"}
 
 
 def attention_shapes(ctx, peak):
