@@ -19,6 +19,8 @@
 #include <cstring>
 #include <map>
 #include <string>
+#include <atomic>
+#include <chrono>
 #include <vector>
 
 #include "ks_internal.h"
@@ -41,11 +43,29 @@ __global__ void end_token_kernel(int n, int* pos) {
   if (s < n) pos[s] += 1;
 }
 // What a blocking step brings back: the n next-token ids and, behind them, whether a device-side wait gave up.
-__global__ void collect_kernel(int n, const float* tok, const unsigned* err_word, float* ret) {
+// `host` (pinned host memory, may be null): the same values where the host can see them without a copy — ids at
+// [0, n), the flag at [n_slots], and last, behind a system-wide fence, the request word the host left at
+// [n_slots + 2] echoed to [n_slots + 1]: a host that spins on the echo needs neither a copy nor a stream wait.
+__global__ void collect_kernel(int n, const float* tok, const unsigned* err_word, float* ret, float* host, int n_slots) {
   ks_pdl_entry();
   const int s = threadIdx.x;
-  if (s < n) ret[s] = tok[s];
-  if (s == n) ret[n] = err_word[0] ? 1.0f : 0.0f;
+  if (s < n) {
+    ret[s] = tok[s];
+    if (host) host[s] = tok[s];
+  }
+  if (s == n) {
+    const float f = err_word[0] ? 1.0f : 0.0f;
+    ret[n] = f;
+    if (host) host[n_slots] = f;
+  }
+  if (host) {
+    __threadfence_system();
+    __syncthreads();
+    if (s == 0) {
+      volatile unsigned* w = reinterpret_cast<volatile unsigned*>(host);
+      w[n_slots + 1] = w[n_slots + 2];
+    }
+  }
 }
 __global__ void set_state_kernel(int slot, int pos_value, int* pos) { ks_pdl_entry(); pos[slot] = pos_value; }
 // A prompt chunk: row t of the chunk sits at position base + t of ONE slot (causal: it sees base + t + 1 positions).
@@ -104,6 +124,8 @@ struct ks_model {
   int n_splits = 1;
   float* ret = nullptr;       // [n_slots][n_slots + 1] per first slot: next ids + status flag of the last blocking step
   float* host_tok = nullptr;  // pinned ring for token read-back
+  float* host_ret = nullptr;  // pinned: what collect_kernel leaves for a blocking step (ids, flag, echo, request word)
+  unsigned req_id = 0;        // the last request word handed to collect_kernel
   size_t host_tok_n = 0;
   // graphs keyed by (first slot, n slots, src parity, want_logits)
   std::map<uint64_t, cudaGraphExec_t> graphs;
@@ -285,7 +307,7 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, x2, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret, (float*)m->host_ret, (int)g.n_slots);
   return ks_after_launch(c, "collect");
 }
 
@@ -360,7 +382,7 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
   }
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * 4, tok_out + s))) return rc;
-  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret, (float*)m->host_ret, (int)g.n_slots);
   return ks_after_launch(c, "collect");
 }
 
@@ -435,7 +457,7 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, act, xn, n, nullptr))) return rc;
   for (int s = 0; s < n; s++)
     if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, act, logits + (size_t)s * g.vocab * ab, tok_out + s))) return rc;
-  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret);
+  KS_LAUNCH(c, (collect_kernel), 1, row_threads(n), 0, n, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD, L_.ret, (float*)m->host_ret, (int)g.n_slots);
   return ks_after_launch(c, "collect");
 }
 
@@ -471,7 +493,7 @@ int enqueue_forward_mega(ks_model* m, const ks_model::Mega& mg, int first, int s
   if ((rc = ks_launch_matvec(c, (ks_dtype)g.embd_dtype, &sh, 1, KS_EPI_PLAIN, H, KS_F32, xn, 1, nullptr))) return rc;
   if ((rc = ks_launch_softcap_argmax(c, g.vocab, g.softcap, KS_F32, logits, tok_out))) return rc;
   KS_LAUNCH(c, (collect_kernel), 1, 32, 0, 1, (const float*)tok_out, (const unsigned*)c->ws + KS_WS_ERR_WORD,
-            m->ret + (size_t)first * (g.n_slots + 1));
+            m->ret + (size_t)first * (g.n_slots + 1), (float*)m->host_ret, (int)g.n_slots);
   return ks_after_launch(c, "collect");
 }
 
@@ -750,6 +772,12 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
     m->host_ids = nullptr;
     ok = false;
   }
+  if (ok && cudaMallocHost((void**)&m->host_ret, ((size_t)g.n_slots + 4) * sizeof(float)) != cudaSuccess) {
+    ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
+    m->host_ret = nullptr;
+    ok = false;
+  }
+  if (m->host_ret) memset(m->host_ret, 0, ((size_t)g.n_slots + 4) * sizeof(float));
   m->host_tok_n = 8192;
   if (ok && cudaMallocHost((void**)&m->host_tok, m->host_tok_n * sizeof(float)) != cudaSuccess) {
     ks_fail(ctx, KS_ERR_OOM, "model_create: pinned allocation failed");
@@ -795,6 +823,7 @@ void ks_model_destroy(ks_model* m) {
   }
   for (void* p : m->owned) cudaFree(p);
   if (m->host_tok) cudaFreeHost(m->host_tok);
+  if (m->host_ret) cudaFreeHost(m->host_ret);
   if (m->host_ids) cudaFreeHost(m->host_ids);
   delete m;
 }
@@ -992,10 +1021,37 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   if (!m) return KS_ERR_INVALID;
   ks_ctx* c = m->ctx;
   KS_REQUIRE(c, tokens && next, "decode_token: null argument");
+  // the request word the step's last kernel echoes into pinned memory once ids and flag are there
+  volatile unsigned* hw = reinterpret_cast<volatile unsigned*>(m->host_ret);
+  const int ns = m->cfg.n_slots;
+  const unsigned req = ++m->req_id ? m->req_id : ++m->req_id;
+  hw[ns + 2] = req;
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
   float* back = m->host_tok;  // n ids, then the status flag
-  if (n <= pass_rows(m, n)) {  // one pass: its last kernel collected ids and flag side by side, one copy brings both
+  if (n <= pass_rows(m, n)) {  // one pass: its last kernel left ids and flag in pinned memory; wait for its echo
+    const auto t0 = std::chrono::steady_clock::now();
+    bool seen = false;
+    for (unsigned spin = 0;; spin++) {
+      if (hw[ns + 1] == req) {
+        seen = true;
+        break;
+      }
+      if ((spin & 0xFFFu) == 0xFFFu) {  // a look at the clock and at the stream now and then: an error must not spin forever
+        if (cudaStreamQuery(c->stream) != cudaErrorNotReady) break;
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(10)) break;
+      }
+    }
+    if (seen) {
+      std::atomic_thread_fence(std::memory_order_acquire);
+      for (int s = 0; s < n; s++) back[s] = m->host_ret[s];
+      back[n] = m->host_ret[ns];
+      if (back[n] == 0.0f) {
+        for (int s = 0; s < n; s++) next[s] = (int)back[s];
+        return KS_OK;
+      }
+    }
+    // not seen (the stream ended or failed first) or a wait gave up on the device: the plain route below
     KS_CUDA(c, cudaMemcpyAsync(back, m->ret + (size_t)first * (m->cfg.n_slots + 1), (n + 1) * sizeof(float), cudaMemcpyDeviceToHost,
                                c->stream));
   } else {                    // several passes: ids from the token buffer, the flag as any non-zero status word
