@@ -48,9 +48,9 @@ FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 << 20
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent decode kernel on the full 35-layer
-# E2B shape, divided by 35 (ncu capture of this bench's own command: 698.5 MB read + 0.9 MB written per launch;
-# the summary of that capture is kept under profiles/).
-DECODE_KERNEL_DRAM_TRAFFIC_PER_LAYER = 19_982_000
+# E2B shape, divided by 35 (ncu capture of this bench's own command at the last change of ks_mega.cu, commit bf56ad6:
+# 698.50 MB read + 0.54 MB written per launch, median of three launches).
+DECODE_KERNEL_DRAM_TRAFFIC_PER_LAYER = 19_973_000
 
 
 def measured_peak():
