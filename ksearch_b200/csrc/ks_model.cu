@@ -126,6 +126,7 @@ struct ks_model {
   float* host_tok = nullptr;  // pinned ring for token read-back
   float* host_ret = nullptr;  // pinned: what collect_kernel leaves for a blocking step (ids, flag, echo, request word)
   unsigned req_id = 0;        // the last request word handed to collect_kernel
+  int solo_max = 2;           // up to this many slots step as one persistent-kernel pass each
   size_t host_tok_n = 0;
   // graphs keyed by (first slot, n slots, src parity, want_logits)
   std::map<uint64_t, cudaGraphExec_t> graphs;
@@ -699,6 +700,10 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   const char* dk = getenv("KSEARCH_DECODE_KERNEL");
   m->use_mega = m->fused && g.act == KS_F32 && !(dk && dk[0] == '0');
   m->decode_kernel = dk && dk[0] == '2' ? 2 : 1;
+  // Two slots step faster as two persistent-kernel passes than side by side through one launch per op (same
+  // measurement: E2B 938 against 1074 us, E4B 1157 against 1378); from three slots on the GEMM path wins.
+  m->solo_max = 2;
+  if (const char* sm = getenv("KSEARCH_SOLO_SLOTS")) m->solo_max = atoi(sm) < 1 ? 1 : atoi(sm);
   ok = ok && dev_alloc(m, &m->xb, S * H * ab) == KS_OK && dev_alloc(m, &m->xn, S * H * ab) == KS_OK;
   ok = ok && dev_alloc(m, &m->x, S * H * ab) == KS_OK && dev_alloc(m, &m->x2, S * H * ab) == KS_OK &&
        dev_alloc(m, &m->q, S * qn * ab) == KS_OK && dev_alloc(m, &m->k, S * kvn * ab) == KS_OK &&
@@ -734,6 +739,13 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
       } else {
         m->gemm_xt = ws;
         m->gemm_p0 = (float*)((char*)ws + xt);
+        // Measured on both model shapes (12 layers + head, one round of n slots): the GEMM path costs about the same
+        // for 3 rows as for 16 and beats the batch matvec from 3 rows on (E2B 3 / 4 / 6 rows: 1264 / 1232 / 1307 us
+        // against 1485 / 1748 / 2348; E4B 3 rows: 1501 against 1787), so only pairs still share a batch-matvec pass.
+        // KSEARCH_BATCH_ROWS moves the limit (measurement).
+        int limit = 2;
+        if (const char* br = getenv("KSEARCH_BATCH_ROWS")) limit = atoi(br) < 1 ? 1 : atoi(br);
+        if (limit < m->chunk) m->chunk = limit;
       }
     }
     const size_t C = m->gemm_chunk > KS_PREFILL_CHUNK ? m->gemm_chunk : KS_PREFILL_CHUNK;
@@ -929,6 +941,20 @@ static int check_slots(ks_model* m, int first, int n) {
   return KS_OK;
 }
 
+// Rows per pass of a decode step over slots [first, first + n).  A few slots are faster as one persistent-kernel
+// pass each (all layers in one launch, section "one slot" above) than side by side through one launch per op.
+int step_rows(ks_model* m, int first, int n) {
+  if (n > 1 && n <= m->solo_max) {
+    bool all = true;
+    for (int s = first; s < first + n && all; s++) {
+      ks_model::Mega mg;
+      all = get_mega(m, s, &mg) == 0 && mg;
+    }
+    if (all) return 1;
+  }
+  return pass_rows(m, n);
+}
+
 // Enqueue one token for slots first..first+n-1.  tokens != NULL: ids are written from the host
 // first (decode_token_sampled, gemma_prim.rs:1622-1634); NULL: ids already on the device from the
 // previous step's argmax.  Nothing is read back and nothing waits.
@@ -953,7 +979,7 @@ int ks_model_forward(ks_model* m, int first, int n, const int* tokens, int want_
   }
   // The slots share one pass over the weights as long as their staged input vectors fit the matvec kernels'
   // shared memory side by side (m->chunk of them); a larger batch takes several passes.
-  const int per_pass = pass_rows(m, n);
+  const int per_pass = step_rows(m, first, n);
   for (int s0 = 0; s0 < n; s0 += per_pass) {
     const int nn = n - s0 < per_pass ? n - s0 : per_pass;
     if ((rc = run_forward(m, first + s0, nn, src, want_logits != 0))) return rc;
@@ -1029,7 +1055,7 @@ int ks_model_decode_token(ks_model* m, int first, int n, const int* tokens, int*
   int rc = ks_model_forward(m, first, n, tokens, 1);
   if (rc) return rc;
   float* back = m->host_tok;  // n ids, then the status flag
-  if (n <= pass_rows(m, n)) {  // one pass: its last kernel left ids and flag in pinned memory; wait for its echo
+  if (n <= step_rows(m, first, n)) {  // one pass: its last kernel left ids and flag in pinned memory; wait for its echo
     const auto t0 = std::chrono::steady_clock::now();
     bool seen = false;
     for (unsigned spin = 0;; spin++) {

@@ -361,17 +361,23 @@ def test_logits_tight_when_kv_bytes_agree(oracle, monkeypatch, shape, decode_ker
     c.close()
 
 
+@pytest.mark.parametrize("batch_rows", [None, "8"])
 @pytest.mark.parametrize("n_kv", [1, 2])
-def test_prefill_chunks_match_token_by_token(ctx, oracle, n_kv):
-    """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk: up to 8
-    rows through the batch matvec, longer prompts in chunks of up to 128 rows through the tensor-core GEMM.
+def test_prefill_chunks_match_token_by_token(ctx, oracle, monkeypatch, n_kv, batch_rows):
+    """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk: up to 2
+    rows through the batch matvec (up to 8 with KSEARCH_BATCH_ROWS=8, the limit before the GEMM path proved faster
+    from 3 rows on), longer prompts in chunks of up to 128 rows through the tensor-core GEMM.
     After the prompt, the next-token logits must match the CPU decoder, and the KV rows it wrote must
     serve later decode steps (teacher-forced continuation)."""
+    if batch_rows is None:
+        monkeypatch.delenv("KSEARCH_BATCH_ROWS", raising=False)
+    else:
+        monkeypatch.setenv("KSEARCH_BATCH_ROWS", batch_rows)
     cfg = ksm.tiny_config(max_seq=192, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=31, keep=True)
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
-    for n_prompt in (1, 7, 8, 9, 21, 128, 150, 137):   # batch matvec; one GEMM chunk; full chunk + ragged rest; rest of 9
+    for n_prompt in (1, 2, 3, 7, 8, 9, 21, 128, 150, 137):   # batch matvec; one GEMM chunk; full chunk + ragged rest; rest of 9
         toks = synth.token_ids(31, f"p{n_prompt}", n_prompt + 6, cfg.vocab)
         model.slot_reset(0)
         cpu.reset()
@@ -429,6 +435,45 @@ def test_many_slots_share_a_gemm_pass(ctx, oracle):
         assert nxt[s] == int(np.argmax(lg)) or np.sort(lg)[-1] - lg[nxt[s]] < 2e-3 * np.abs(lg).max()
         cpus[s].close()
     print(f"[12 slots] {per_step} launches per step")
+    model.close()
+
+
+@pytest.mark.parametrize("n", [2, 3])
+def test_few_slots_step_together(ctx, oracle, n):
+    """Two slots step as two persistent-kernel passes, three as one pass through the GEMM path (both measured
+    faster than the batch matvec at those counts).  Each slot matches its own single-slot CPU run, through
+    forward (logits, ids chained on the device) and through the blocking decode_token."""
+    cfg = ksm.tiny_config(max_seq=48, n_slots=n)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=14, keep=True)
+    assert [model.slot_alloc() for _ in range(n)] == list(range(n))
+    lens = [4 + 3 * s for s in range(n)]
+    seqs = [synth.token_ids(14, f"s{s}", lens[s] + 6, cfg.vocab) for s in range(n)]
+    cpus = []
+    for s in range(n):
+        model.prefill(s, seqs[s][:lens[s]])
+        cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+        for t in seqs[s][:lens[s]]:
+            cpu.forward_token(int(t), False)
+        cpus.append(cpu)
+    for j in range(4):
+        model.forward(0, n, [int(seqs[s][lens[s] + j]) for s in range(n)], True)
+        ctx.synchronize()
+        for s in range(n):
+            cpus[s].forward_token(int(seqs[s][lens[s] + j]), True)
+            want = cpus[s].logits().astype(np.float64)
+            got = model.read_debug(1, s).astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (j, s)
+    for j in (4, 5):
+        nxt = model.decode_token([int(seqs[s][lens[s] + j]) for s in range(n)], 0)
+        for s in range(n):
+            cpus[s].forward_token(int(seqs[s][lens[s] + j]), True)
+            lg = cpus[s].logits().astype(np.float64)
+            assert nxt[s] == int(np.argmax(lg)) or np.sort(lg)[-1] - lg[nxt[s]] < 2e-3 * np.abs(lg).max()
+    assert [model.seq_len(s) for s in range(n)] == [l + 6 for l in lens]
+    if n == 2:
+        assert model.lib.ks_model_debug_ptr(model.h, 2, 1) is not None  # slot 1 got its own persistent kernel
+    for cpu in cpus:
+        cpu.close()
     model.close()
 
 
