@@ -423,7 +423,7 @@ def serve_e4b(ctx, rank, world, dist, peak, prompt_len=512, n_new=256):
            "bytes_required_per_round_per_gpu": per_step, "gbs_per_gpu": per_step / (ms / steps) / 1e6,
            "frac_of_measured_peak": per_step / (ms / steps) / 1e6 / peak,
            "path": "persistent decode kernel" if n_local == 1 else "one launch per op; more slots than the batch matvec stages share one pass through the tensor-core GEMM, "
-                                                                   "prompts run in 128-row GEMM chunks"}
+                                                                   "prompts run in 256-row GEMM chunks"}
     model.close()
     return res
 

@@ -173,7 +173,7 @@ int dev_alloc(ks_model* m, void** p, size_t bytes) {
 }
 
 constexpr int KS_PREFILL_CHUNK = 8;  // tokens per pass over the weights (the matvec kernels take up to 8)
-constexpr int KS_GEMM_CHUNK = 128;   // rows per pass when the tensor-core GEMM takes the matrices (f32 activations)
+constexpr int KS_GEMM_CHUNK = 256;   // rows per pass when the tensor-core GEMM takes the matrices (f32 activations)
 constexpr size_t KS_STAGE_IDS = 256; // pinned words that stage host token ids
 
 // Where a forward pass reads and writes: n rows of activations, their positions, and the KV caches

@@ -366,18 +366,19 @@ def test_logits_tight_when_kv_bytes_agree(oracle, monkeypatch, shape, decode_ker
 def test_prefill_chunks_match_token_by_token(ctx, oracle, monkeypatch, n_kv, batch_rows):
     """ks_model_prefill: prompt rows share a pass over the weights and attend causally inside a chunk: up to 2
     rows through the batch matvec (up to 8 with KSEARCH_BATCH_ROWS=8, the limit before the GEMM path proved faster
-    from 3 rows on), longer prompts in chunks of up to 128 rows through the tensor-core GEMM.
+    from 3 rows on), longer prompts in chunks of up to 256 rows through the tensor-core GEMM.
     After the prompt, the next-token logits must match the CPU decoder, and the KV rows it wrote must
     serve later decode steps (teacher-forced continuation)."""
     if batch_rows is None:
         monkeypatch.delenv("KSEARCH_BATCH_ROWS", raising=False)
     else:
         monkeypatch.setenv("KSEARCH_BATCH_ROWS", batch_rows)
-    cfg = ksm.tiny_config(max_seq=192, n_kv=n_kv)
+    cfg = ksm.tiny_config(max_seq=560, n_kv=n_kv)
     model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=31, keep=True)
     cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
     model.slot_alloc()
-    for n_prompt in (1, 2, 3, 7, 8, 9, 21, 128, 150, 137):   # batch matvec; one GEMM chunk; full chunk + ragged rest; rest of 9
+    # batch matvec; GEMM chunks of 16..256 rows (up to 128: hi|lo rows in one MMA); full chunks + ragged rest
+    for n_prompt in (1, 2, 3, 7, 8, 9, 21, 128, 150, 137, 256, 300, 530):
         toks = synth.token_ids(31, f"p{n_prompt}", n_prompt + 6, cfg.vocab)
         model.slot_reset(0)
         cpu.reset()
@@ -395,7 +396,7 @@ def test_prefill_chunks_match_token_by_token(ctx, oracle, monkeypatch, n_kv, bat
             err = np.abs(got - want)
             assert err.max() <= 1e-3 * scale and np.sqrt((err ** 2).mean()) <= 1e-4 * scale
     with pytest.raises(KsError, match="max_seq exceeded"):
-        model.prefill(0, [1] * 200)
+        model.prefill(0, [1] * 600)
     cpu.close()
     model.close()
 
