@@ -127,6 +127,14 @@ int ks_plan_file_load(const char* dir, const char* key, const char* chip, ks_pla
 int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_off, size_t nelem,
                ks_buf* dst_f32, size_t dst_off);
 
+/* ---- load-time requantisation to Q4_K: GG:803-1016 make_qkx2_quants + quantize_f32_to_q4k ----
+ * The reference's loader turns Q6_K ffn_down / attn_v tensors, and f32 / bf16 ones, into Q4_K on the host before
+ * upload (GP:415-440 ensure_weight: dequant_to_f32, then quantize_f32_to_q4k).  The same arithmetic on the GPU,
+ * byte for byte: nelem source elements (a multiple of 256; Q6K, Q4K, F16 or F32) -> nelem / 256 blocks of 144
+ * bytes.  Byte offsets are multiples of 4. */
+int ks_quantize_q4k(ks_ctx* ctx, ks_dtype src_dtype, const ks_buf* src, size_t src_byte_off, size_t nelem,
+                    ks_buf* dst_q4k, size_t dst_byte_off);
+
 /* ---- matvec family ------------------------------------------------------- */
 /* y[t, r] = sum_c deq(W)[r, c] * x[t, c], t < n_tok (1..256).  x is [n_tok, cols],
  * y is [n_tok, rows].  K:137 matvec_wd, K:1446 matvec_wd_at (offsets),
@@ -251,6 +259,9 @@ int ks_model_warm_plans(ks_model* m, int n_tok);                             /* 
  * blk.N.{attn_norm,attn_q_norm,attn_k_norm,post_attention_norm,ffn_norm,post_ffw_norm}.weight (act dtype). */
 size_t ks_model_tensor_bytes(const ks_model* m, const char* name);           /* 0 if unknown */
 int ks_model_upload_tensor(ks_model* m, const char* name, const void* host, size_t bytes);  /* GP:415-451 ensure_weight */
+/* The same with the file's tensor type: bytes of the resident type are copied; a Q6K, F16 or F32 matrix whose resident
+ * form is Q4_K is requantised on the device as the reference's loader does on the host (GP:422-440, GG:803-1016). */
+int ks_model_upload_tensor_as(ks_model* m, const char* name, ks_dtype src_dtype, const void* host, size_t bytes);
 const void* ks_model_tensor_ptr(const ks_model* m, const char* name);      /* device address of a resident tensor, NULL if unknown */
 size_t ks_model_weight_bytes(const ks_model* m);
 int ks_model_slot_alloc(ks_model* m);                                        /* KV:136 alloc -> slot id, or KS_ERR_STATE "KvPool full" */

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ks_plan_file_save": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _vp]),
     "ks_plan_file_load": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _vp]),
     "ks_dequant": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _sz]),
+    "ks_quantize_q4k": (_i, [_vp, _i, _vp, _sz, _sz, _vp, _sz]),
     "ks_matvec": (_i, [_vp, _sz, _sz, _i, _vp, _sz, _i, _vp, _sz, _vp, _sz, _i]),
     "ks_matvec_qkv": (_i, [_vp, _sz, _sz, _sz, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp]),
     "ks_matvec_gate_up_gelu": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _vp, _vp]),
@@ -82,6 +83,7 @@ SIGNATURES = {
     "ks_model_warm_plans": (_i, [_vp, _i]),
     "ks_model_tensor_bytes": (_sz, [_vp, C.c_char_p]),
     "ks_model_upload_tensor": (_i, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_model_upload_tensor_as": (_i, [_vp, C.c_char_p, _i, _vp, _sz]),
     "ks_model_tensor_ptr": (_vp, [_vp, C.c_char_p]),
     "ks_model_weight_bytes": (_sz, [_vp]),
     "ks_model_slot_alloc": (_i, [_vp]),

@@ -147,6 +147,8 @@ int ks_launch_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scal
 int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, const void* logits, float* out_idx);
 
 // ---- tensor-core GEMM for batches of more than 8 token rows (ks_gemm.cu) ---------------------------
+// nelem (a multiple of 256) elements of src (Q6K, Q4K, F16, F32) -> Q4_K blocks, as the reference's load-time quantizer.
+int ks_launch_quantize_q4k(ks_ctx* ctx, ks_dtype src_dtype, const void* src, size_t nelem, void* dst);
 size_t ks_gemm_xt_bytes(size_t cols, int n_tok);  // bytes of the split image of n_tok rows of `cols` values
 size_t ks_gemm_part_floats(const ks_ctx* ctx, size_t total_rows, size_t cols, int n_tok);  // k-split partials, at most
 // The context's scratch, grown to `bytes` (fails inside a stream capture when it would have to grow).

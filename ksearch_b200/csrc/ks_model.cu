@@ -89,6 +89,7 @@ struct Tensor {
   void* dptr = nullptr;
   size_t bytes = 0;
   bool set = false;
+  int dtype = KS_F32;  // what the resident bytes are
 };
 
 struct Layer {
@@ -654,6 +655,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
     off = (off + 255) & ~size_t(255);
     t.dptr = (void*)off;  // offset for now
     t.bytes = bytes;
+    t.dtype = name == "token_embd.weight" ? g.embd_dtype : name.find("norm") != std::string::npos ? g.act : (int)KS_Q4K;
     off += bytes;
     m->by_name[name] = &t;
   };
@@ -856,6 +858,33 @@ int ks_model_upload_tensor(ks_model* m, const char* name, const void* host, size
   KS_CUDA(c, cudaMemcpyAsync(it->second->dptr, host, bytes, cudaMemcpyHostToDevice, c->stream));
   KS_CUDA(c, cudaStreamSynchronize(c->stream));
   it->second->set = true;
+  return KS_OK;
+}
+
+// ensure_weight (gemma_prim.rs:415-451) with the file's tensor type: a tensor stored as it is resident is copied; a
+// Q6_K, F16 or F32 tensor whose resident form is Q4_K (the reference requantises Q6_K ffn_down / attn_v and every
+// f32 / bf16 matrix on the host) is staged on the device and requantised there by the same arithmetic.
+int ks_model_upload_tensor_as(ks_model* m, const char* name, ks_dtype src_dtype, const void* host, size_t bytes) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, name && host, "model_upload_tensor: null argument");
+  auto it = m->by_name.find(name);
+  KS_REQUIRE(c, it != m->by_name.end(), "missing tensor %s", name);
+  Tensor& t = *it->second;
+  if ((int)src_dtype == t.dtype) return ks_model_upload_tensor(m, name, host, bytes);
+  KS_REQUIRE(c, t.dtype == KS_Q4K && (src_dtype == KS_Q6K || src_dtype == KS_F16 || src_dtype == KS_F32),
+             "tensor %s: no conversion from ggml type %d to the resident type %d", name, (int)src_dtype, t.dtype);
+  const size_t nelem = t.bytes / KS_Q4K_BLOCK_BYTES * 256;
+  KS_REQUIRE(c, bytes == ks_nbytes(src_dtype, nelem), "tensor %s: got %zu bytes, expected %zu", name, bytes, ks_nbytes(src_dtype, nelem));
+  void* stage = nullptr;
+  if (cudaMalloc(&stage, bytes) != cudaSuccess) return ks_fail(c, KS_ERR_OOM, "tensor %s: cannot stage %zu bytes", name, bytes);
+  cudaError_t e = cudaMemcpyAsync(stage, host, bytes, cudaMemcpyHostToDevice, c->stream);
+  int rc = e == cudaSuccess ? ks_launch_quantize_q4k(c, src_dtype, stage, nelem, t.dptr) : KS_ERR_CUDA;
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  cudaFree(stage);
+  if (e != cudaSuccess) return ks_fail(c, KS_ERR_CUDA, "tensor %s: upload failed: %s", name, cudaGetErrorString(e));
+  if (rc) return rc;
+  t.set = true;
   return KS_OK;
 }
 

@@ -87,6 +87,174 @@ __global__ void dequant_kernel(int dtype, const uint8_t* src, size_t n, float* d
     dst[i] = deq_any(dtype, src, i);
 }
 
+// ---- f32 / packed -> Q4_K: the reference's load-time quantizer (gguf_impl.rs:803-1016) -----------------
+// The model loader requantises Q6_K ffn_down / attn_v tensors (and f32 / bf16 ones) to Q4_K on the host
+// (gemma_prim.rs:415-440); here the same arithmetic runs on the GPU, byte for byte: every float operation is an
+// explicit round-to-nearest intrinsic in the reference's order (no fused multiply-add), sums run sequentially.
+// One thread per 32-element sub-block; the 8 threads of a super-block are neighbouring lanes.
+__device__ __forceinline__ int q4k_nearest_int(float f) {
+  return (int)(__float_as_uint(__fadd_rn(f, 12582912.0f)) & 0x007fffffu) - 0x00400000;
+}
+__device__ __forceinline__ int q4k_clampi(int v, int lo, int hi) { return v < lo ? lo : v > hi ? hi : v; }
+// f32 -> f16 as the reference's own converter rounds (lib.rs:39-75: half UP in magnitude, not ties-to-even).
+__device__ __forceinline__ unsigned f32_to_f16_half_up(float v) {
+  const unsigned bits = __float_as_uint(v), sign = (bits >> 16) & 0x8000u;
+  int e = (int)((bits >> 23) & 0xFFu);
+  unsigned mant = bits & 0x7FFFFFu;
+  if (e == 255) return mant == 0 ? (sign | 0x7C00u) : (sign | 0x7C00u | (mant >> 13));
+  e -= 127;
+  if (e > 15) return sign | 0x7C00u;
+  if (e < -14) {
+    if (e < -24) return sign;
+    mant |= 0x800000u;
+    const unsigned shift = (unsigned)(-14 - e) + 13u;
+    return sign | ((mant + (1u << (shift - 1u))) >> shift);
+  }
+  const unsigned he = (unsigned)(e + 15), hm = mant + 0x1000u;
+  if (hm & 0x800000u) return sign | ((he + 1u) << 10);
+  return sign | (he << 10) | (hm >> 13);
+}
+// make_qkx2_quants (gguf_impl.rs:803-905) for n = 32, nmax = 15, rmin = -1, rdelta = 0.1, nstep = 20.
+__device__ float q4k_search(const float (&x)[32], const float (&w)[32], unsigned char (&L)[32], float* the_min) {
+  float mn = x[0], mx = x[0];
+  float sum_w = w[0], sum_x = __fmul_rn(sum_w, x[0]);
+  for (int i = 1; i < 32; i++) {
+    if (x[i] < mn) mn = x[i];
+    if (x[i] > mx) mx = x[i];
+    sum_w = __fadd_rn(sum_w, w[i]);
+    sum_x = __fadd_rn(sum_x, __fmul_rn(w[i], x[i]));
+  }
+  if (mn > 0.0f) mn = 0.0f;
+  if (mx == mn) {
+    for (int i = 0; i < 32; i++) L[i] = 0;
+    *the_min = -mn;
+    return 0.0f;
+  }
+  float iscale = __fdiv_rn(15.0f, __fsub_rn(mx, mn));
+  float scale = __fdiv_rn(1.0f, iscale);
+  float best = 0.0f;
+  for (int i = 0; i < 32; i++) {
+    const int l = q4k_clampi(q4k_nearest_int(__fmul_rn(iscale, __fsub_rn(x[i], mn))), 0, 15);
+    L[i] = (unsigned char)l;
+    const float diff = __fsub_rn(__fadd_rn(__fmul_rn(scale, (float)l), mn), x[i]);
+    best = __fadd_rn(best, __fmul_rn(w[i], __fmul_rn(diff, diff)));
+  }
+  unsigned char Laux[32];
+  for (int is = 0; is <= 20; is++) {
+    // mn is the best minimum found so far: the candidate grid moves with it, as in the reference
+    iscale = __fdiv_rn(__fadd_rn(__fadd_rn(-1.0f, __fmul_rn(0.1f, (float)is)), 15.0f), __fsub_rn(mx, mn));
+    float sl = 0.0f, sl2 = 0.0f, sxl = 0.0f;
+    for (int i = 0; i < 32; i++) {
+      const int l = q4k_clampi(q4k_nearest_int(__fmul_rn(iscale, __fsub_rn(x[i], mn))), 0, 15);
+      Laux[i] = (unsigned char)l;
+      const float lf = (float)l;
+      sl = __fadd_rn(sl, __fmul_rn(w[i], lf));
+      sl2 = __fadd_rn(sl2, __fmul_rn(__fmul_rn(w[i], lf), lf));
+      sxl = __fadd_rn(sxl, __fmul_rn(__fmul_rn(w[i], lf), x[i]));
+    }
+    const float D = __fsub_rn(__fmul_rn(sum_w, sl2), __fmul_rn(sl, sl));
+    if (D > 0.0f) {
+      float ts = __fdiv_rn(__fsub_rn(__fmul_rn(sum_w, sxl), __fmul_rn(sum_x, sl)), D);
+      float tm = __fdiv_rn(__fsub_rn(__fmul_rn(sl2, sum_x), __fmul_rn(sl, sxl)), D);
+      if (tm > 0.0f) {
+        tm = 0.0f;
+        ts = __fdiv_rn(sxl, sl2);
+      }
+      float err = 0.0f;
+      for (int i = 0; i < 32; i++) {
+        const float diff = __fsub_rn(__fadd_rn(__fmul_rn(ts, (float)Laux[i]), tm), x[i]);
+        err = __fadd_rn(err, __fmul_rn(w[i], __fmul_rn(diff, diff)));
+      }
+      if (err < best) {
+        for (int i = 0; i < 32; i++) L[i] = Laux[i];
+        best = err;
+        scale = ts;
+        mn = tm;
+      }
+    }
+  }
+  *the_min = -mn;
+  return scale;
+}
+// quantize_f32_to_q4k (gguf_impl.rs:907-1016): n_sb super-blocks of 256 source elements -> 144 bytes each.
+__global__ void quantize_q4k_kernel(int dtype, const uint8_t* src, size_t n_sb, uint8_t* dst) {
+  ks_pdl_entry();
+  const size_t gt = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t sb = gt >> 3;
+  const unsigned j = (unsigned)(gt & 7u);
+  const bool live = sb < n_sb;  // whole groups of 8 lanes are live or not; dead lanes still take part in the shuffles
+  float x[32], w[32];
+  unsigned char L[32];
+  float scale = 0.0f, mnv = 0.0f;
+  if (live) {
+    float s2 = 0.0f;
+    for (int t = 0; t < 32; t++) {
+      x[t] = deq_any(dtype, src, sb * 256 + 32 * j + t);
+      s2 = __fadd_rn(s2, __fmul_rn(x[t], x[t]));
+    }
+    const float av = __fsqrt_rn(__fdiv_rn(s2, 32.0f));
+    for (int t = 0; t < 32; t++) w[t] = __fadd_rn(av, fabsf(x[t]));
+    scale = q4k_search(x, w, L, &mnv);
+  } else {
+    for (int t = 0; t < 32; t++) L[t] = 0;
+  }
+  // the largest scale and minimum of the super-block (the reference starts both at 0 and keeps what compares greater)
+  float max_scale = fmaxf(scale, 0.0f), max_min = fmaxf(mnv, 0.0f);
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    max_scale = fmaxf(max_scale, __shfl_xor_sync(0xffffffffu, max_scale, o));
+    max_min = fmaxf(max_min, __shfl_xor_sync(0xffffffffu, max_min, o));
+  }
+  const float inv_scale = max_scale > 0.0f ? __fdiv_rn(63.0f, max_scale) : 0.0f;
+  const float inv_min = max_min > 0.0f ? __fdiv_rn(63.0f, max_min) : 0.0f;
+  const unsigned db = f32_to_f16_half_up(__fdiv_rn(max_scale, 63.0f)), mb = f32_to_f16_half_up(__fdiv_rn(max_min, 63.0f));
+  unsigned ls = (unsigned)q4k_nearest_int(__fmul_rn(inv_scale, scale)) & 0xFFu;  // the reference casts to u8, then clamps
+  unsigned lm = (unsigned)q4k_nearest_int(__fmul_rn(inv_min, mnv)) & 0xFFu;
+  if (ls > 63u) ls = 63u;
+  if (lm > 63u) lm = 63u;
+  // the 12 scale bytes (gguf_impl.rs:976-983), built by every lane from its neighbours' values
+  const unsigned lane = threadIdx.x & 31u, base = lane & ~7u;
+  unsigned sc[12];
+#pragma unroll
+  for (int i = 0; i < 12; i++) sc[i] = 0;
+#pragma unroll
+  for (unsigned jj = 0; jj < 8; jj++) {
+    const unsigned s_ = __shfl_sync(0xffffffffu, ls, base + jj), m_ = __shfl_sync(0xffffffffu, lm, base + jj);
+    if (jj < 4) {
+      sc[jj] |= s_;
+      sc[jj + 4] |= m_;
+    } else {
+      sc[jj + 4] |= (s_ & 0x0Fu) | ((m_ & 0x0Fu) << 4);
+      sc[jj - 4] |= (s_ >> 4) << 6;
+      sc[jj] |= (m_ >> 4) << 6;
+    }
+  }
+  uint8_t* blk = dst + sb * KS_Q4K_BLOCK_BYTES;
+  if (live && j == 0) {
+    uint32_t* h = reinterpret_cast<uint32_t*>(blk);
+    h[0] = db | (mb << 16);
+    h[1] = sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24);
+    h[2] = sc[4] | (sc[5] << 8) | (sc[6] << 16) | (sc[7] << 24);
+    h[3] = sc[8] | (sc[9] << 8) | (sc[10] << 16) | (sc[11] << 24);
+  }
+  // final levels against the stored 6-bit scale and minimum (unpacking the bytes gives ls and lm back)
+  if (live) {
+    const float dj = __fmul_rn(half_bits_to_float((unsigned short)db), (float)ls);
+    if (dj != 0.0f) {
+      const float dm = __fmul_rn(half_bits_to_float((unsigned short)mb), (float)lm);
+      for (int t = 0; t < 32; t++) L[t] = (unsigned char)q4k_clampi(q4k_nearest_int(__fdiv_rn(__fadd_rn(x[t], dm), dj)), 0, 15);
+    }
+  }
+  // byte t of a 64-element group holds sub-block 2g's level in the low nibble and sub-block 2g + 1's in the high one
+  uint32_t* qs = reinterpret_cast<uint32_t*>(blk + 16 + 32 * (j >> 1));
+#pragma unroll
+  for (int wd = 0; wd < 8; wd++) {
+    const uint32_t mine = (uint32_t)L[4 * wd] | ((uint32_t)L[4 * wd + 1] << 8) | ((uint32_t)L[4 * wd + 2] << 16) | ((uint32_t)L[4 * wd + 3] << 24);
+    const uint32_t next = __shfl_down_sync(0xffffffffu, mine, 1);
+    if (live && !(j & 1u)) qs[wd] = mine | (next << 4);
+  }
+}
+
 // ---- block reductions -----------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -414,6 +582,14 @@ int ks_launch_softcap_argmax(ks_ctx* ctx, size_t n, float cap, ks_dtype act, con
 }
 
 // ---- C ABI --------------------------------------------------------------------------------------
+int ks_launch_quantize_q4k(ks_ctx* ctx, ks_dtype src_dtype, const void* src, size_t nelem, void* dst) {
+  const size_t n_sb = nelem / 256, threads = n_sb * 8;
+  if (nelem % 256 || (threads + 127) / 128 >= (1ull << 31)) return ks_fail(ctx, KS_ERR_INVALID, "quantize_q4k: bad element count %zu", nelem);
+  if (n_sb == 0) return KS_OK;
+  KS_LAUNCH(ctx, (quantize_q4k_kernel), (unsigned)((threads + 127) / 128), 128, 0, (int)src_dtype, (const uint8_t*)src, n_sb, (uint8_t*)dst);
+  return ks_after_launch(ctx, "quantize_q4k");
+}
+
 extern "C" {
 
 int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_off, size_t nelem, ks_buf* dst,
@@ -430,6 +606,18 @@ int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_o
   KS_LAUNCH(ctx, (dequant_kernel), (unsigned)blocks, 256, 0, (int)dtype, (const uint8_t*)src->dptr + src_byte_off, nelem,
                                                             (float*)dst->dptr + dst_off);
   return ks_after_launch(ctx, "dequant");
+}
+
+int ks_quantize_q4k(ks_ctx* ctx, ks_dtype src_dtype, const ks_buf* src, size_t src_byte_off, size_t nelem, ks_buf* dst,
+                    size_t dst_byte_off) {
+  if (!ctx) return KS_ERR_INVALID;
+  KS_REQUIRE(ctx, src_dtype == KS_Q6K || src_dtype == KS_Q4K || src_dtype == KS_F16 || src_dtype == KS_F32,
+             "quantize_q4k: unsupported source type %d", (int)src_dtype);
+  KS_REQUIRE(ctx, nelem % 256 == 0, "quantize_q4k: nelem=%zu is not a multiple of 256", nelem);
+  KS_REQUIRE(ctx, src_byte_off % 4 == 0 && dst_byte_off % 4 == 0, "quantize_q4k: byte offsets must be multiples of 4");
+  KS_REQUIRE(ctx, ks_fits(src, src_byte_off, ks_nbytes(src_dtype, nelem)), "quantize_q4k: source buffer too small");
+  KS_REQUIRE(ctx, ks_fits(dst, dst_byte_off, nelem / 256 * KS_Q4K_BLOCK_BYTES), "quantize_q4k: destination buffer too small");
+  return ks_launch_quantize_q4k(ctx, src_dtype, (const uint8_t*)src->dptr + src_byte_off, nelem, (uint8_t*)dst->dptr + dst_byte_off);
 }
 
 int ks_rmsnorm(ks_ctx* ctx, size_t n, size_t rows, float eps, ks_dtype act, const ks_buf* x, size_t x_off,

@@ -353,6 +353,13 @@ class Eng:
         ctx.check(ctx.lib.ks_dequant(ctx.h, dtype, src.h, src_byte_off, nelem, dst.h, dst_off))
 
 
+    # ---- load-time requantisation ---------------------------------------------
+    def quantize_q4k(self, ctx, src_dtype, src, nelem, dst, src_byte_off=0, dst_byte_off=0):
+        """crates/ksearch_gguf/src/gguf_impl.rs:803-1016 quantize_f32_to_q4k over the dequantised source, as
+        crates/ksearch_gemma/src/gemma_prim.rs:415-440 applies it to Q6_K ffn_down / attn_v tensors at load."""
+        ctx.check(ctx.lib.ks_quantize_q4k(ctx.h, src_dtype, src.h, src_byte_off, nelem, dst.h, dst_byte_off))
+
+
 def write_meta(ctx: CudaContext, meta: Buffer, tlen: int, start: int = 0, win: int = 0, slot: int = 0):
     """Host write of (tlen, start, win) as f32 (crates/ksearch_gemma/src/gemma_prim.rs:636-644)."""
     ctx.write_buffer(meta, np.array([tlen, start, win, 0], np.float32), slot * 16)

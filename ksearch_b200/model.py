@@ -137,11 +137,16 @@ class GemmaCudaModel:
                 kept[name] = t
         return (m, kept) if keep else m
 
-    def upload_tensor(self, name: str, data: np.ndarray):
+    def upload_tensor(self, name: str, data: np.ndarray, dtype: int | None = None):
+        """ensure_weight (crates/ksearch_gemma/src/gemma_prim.rs:415-451).  dtype: the tensor's type in the file when
+        it differs from the resident one (Q6_K / F16 / F32 matrices are requantised to Q4_K on the device)."""
         a = np.ascontiguousarray(data)
         if a.dtype == np.float32 and self.cfg.act == F16 and "norm" in name:
             a = a.astype(np.float16)
-        self.ctx.check(self.lib.ks_model_upload_tensor(self.h, name.encode(), a.ctypes.data, a.nbytes))
+        if dtype is None:
+            self.ctx.check(self.lib.ks_model_upload_tensor(self.h, name.encode(), a.ctypes.data, a.nbytes))
+        else:
+            self.ctx.check(self.lib.ks_model_upload_tensor_as(self.h, name.encode(), dtype, a.ctypes.data, a.nbytes))
 
     def warm_plans(self, n_tok: int = 1) -> int:
         """Load-time BEAM warm (gemma_prim.rs:254-290): search or load the launch plan of every matvec shape."""
@@ -206,6 +211,18 @@ class GemmaCudaModel:
         self.ctx.check(self.lib.ks_buf_download(self.ctx.h, buf, 0, out.ctypes.data, nb))
         self.lib.ks_buf_free(self.ctx.h, buf)
         return out.view(np.float32 if self.cfg.act == F32 else np.float16).astype(np.float32)
+
+    def read_tensor(self, name: str) -> np.ndarray:
+        """The resident bytes of a tensor (after any load-time requantisation)."""
+        nb = self.lib.ks_model_tensor_bytes(self.h, name.encode())
+        ptr = self.lib.ks_model_tensor_ptr(self.h, name.encode())
+        if not ptr or not nb:
+            raise KsError(-1, f"missing tensor {name}")
+        buf = self.lib.ks_buf_wrap(self.ctx.h, ptr, nb)
+        out = np.empty(nb, np.uint8)
+        self.ctx.check(self.lib.ks_buf_download(self.ctx.h, buf, 0, out.ctypes.data, nb))
+        self.lib.ks_buf_free(self.ctx.h, buf)
+        return out
 
     POLL_LIMIT, STALL, SPLIT_FROM, PHASE_CLOCKS = 0, 1, 2, 3
 

@@ -478,6 +478,32 @@ def test_few_slots_step_together(ctx, oracle, n):
     model.close()
 
 
+def test_q6k_tensors_are_requantised_at_load(ctx, oracle):
+    """The reference's loader turns Q6_K ffn_down and attn_v tensors into Q4_K before upload (ensure_weight,
+    gemma_prim.rs:422-433: dequant_to_f32 + quantize_f32_to_q4k).  upload_tensor(..., dtype=Q6K) does the same on
+    the device: the resident bytes equal the CPU quantizer's, and the model decodes like the CPU decoder that was
+    given those bytes."""
+    from ksearch_b200 import Q6K
+    cfg = ksm.tiny_config(max_seq=48)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=33, keep=True)
+    for name, kind, rows, cols in ksm.tensor_specs(cfg):
+        if name.endswith("ffn_down.weight") or name.endswith("attn_v.weight"):
+            q6 = synth.q6k_matrix(33, name + "/q6", rows, cols, cfg.sigma_w, signed_scales=True)
+            model.upload_tensor(name, q6, dtype=Q6K)
+            want = oracle.quantize_q4k(oracle.dequant(Q6K, q6, rows * cols))
+            assert np.array_equal(model.read_tensor(name), want), name
+            T[name] = want
+    with pytest.raises(KsError, match="no conversion"):
+        model.upload_tensor("blk.0.attn_norm.weight", np.zeros(cfg.hidden // 256 * 210, np.uint8), dtype=Q6K)
+    with pytest.raises(KsError, match="expected"):
+        model.upload_tensor("blk.0.ffn_down.weight", np.zeros(210, np.uint8), dtype=Q6K)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    _teacher_forced(model, cpu, synth.token_ids(33, "tf", 24, cfg.vocab))
+    cpu.close()
+    model.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext

@@ -37,6 +37,55 @@ def test_dequant_edge_cases(ctx):
         e.dequant(ctx, 17, src, 256, dst)         # unsupported ggml type
 
 
+def _q4k_sources(n):
+    """Source tensors for the load-time requantisation: the reference applies it to Q6_K tensors (signed scales as
+    real files have them) and to f32 ones; the f32 case carries the shapes a quantizer trips over."""
+    q6 = synth.q6k_matrix(51, "down", n // 1024, 1024, signed_scales=True)
+    f = (synth.normals(52, "w", n) * 0.05).astype(np.float32)
+    f[:256] = 0.0                                   # an all-zero super-block: zero scales, zero levels
+    f[256:288] = 0.37                               # a constant positive sub-block (its minimum clamps to 0)
+    f[288:320] = -0.37                              # a constant negative sub-block (max == min)
+    f[512:768] = np.abs(f[512:768])                 # a super-block without negative values: every minimum is 0
+    f[768:1024] *= 1e-6                             # tiny values: scales near the f16 subnormal range
+    f[1024:1280] *= 300.0                           # large values
+    return [(Q6K, q6), (F32, f), (F16, f.astype(np.float16))]
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_quantize_q4k_matches_reference_quantizer(ctx, oracle, which):
+    """ks_quantize_q4k: gguf_impl.rs:803-1016 on the GPU, byte for byte against the CPU restatement fed with the
+    dequantised source (gemma_prim.rs:415-440: dequant_to_f32, then quantize_f32_to_q4k)."""
+    n = 96 * 1024
+    dtype, data = _q4k_sources(n)[which]
+    src = ctx.buffer_bytes(data)
+    dst = ctx.buffer_empty_bytes(n // 256 * 144)
+    Eng().quantize_q4k(ctx, dtype, src, n, dst)
+    got = ctx.read_bytes(dst, n // 256 * 144)
+    flat = oracle.dequant(dtype, data, n) if dtype == Q6K else np.asarray(data, np.float32)
+    want = oracle.quantize_q4k(flat)
+    bad = np.flatnonzero(got != want)
+    assert bad.size == 0, f"{bad.size} differing bytes, first at {bad[:8]} (block {bad[0] // 144}, byte {bad[0] % 144})"
+    # and the result is a usable Q4_K tensor: it dequantises close to the source
+    back = oracle.dequant(Q4K, got, n)
+    scale = np.abs(flat).reshape(-1, 256).max(axis=1).repeat(256) + 1e-30
+    assert np.abs(back - flat).max() <= 0.12 * scale.max() and np.median(np.abs(back - flat) / scale) < 0.03
+
+
+def test_quantize_q4k_edge_cases(ctx):
+    e = Eng()
+    src = ctx.buffer_bytes(np.zeros(256, np.float32))
+    dst = ctx.buffer_empty_bytes(144)
+    e.quantize_q4k(ctx, F32, src, 0, dst)            # empty input is a no-op
+    e.quantize_q4k(ctx, F32, src, 256, dst)
+    assert not ctx.read_bytes(dst, 144).any()        # zeros quantise to an all-zero block
+    with pytest.raises(KsError):
+        e.quantize_q4k(ctx, F32, src, 100, dst)      # ragged
+    with pytest.raises(KsError):
+        e.quantize_q4k(ctx, F32, src, 512, dst)      # source too small
+    with pytest.raises(KsError):
+        e.quantize_q4k(ctx, Q40, src, 256, dst)      # unsupported source type
+
+
 @pytest.mark.parametrize("act", [F32, F16])
 @pytest.mark.parametrize("n,rows", [(1536, 1), (2560, 1), (256, 5), (4096, 3), (100, 2)])
 def test_rmsnorm_family(ctx, oracle, act, n, rows):
