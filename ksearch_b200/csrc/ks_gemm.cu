@@ -57,6 +57,8 @@ struct GemmArgs {
   unsigned tmem_cols;              // power of two >= max(32, accumulator columns)
   unsigned ksteps_per;             // k-steps per CTA (grid.y splits the k range)
   unsigned nb;                     // stages (2..4) of the A ring and of the B ring
+  unsigned wait_limit;             // polls before a wait inside the kernel gives up
+  unsigned test_stall;             // test hook: the token rows of k-step test_stall - 1 of every CTA are never requested
   unsigned* err;
 };
 
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
     for (unsigned i = 0; i < ksteps; i++) {
       const unsigned ks = ks0 + i, s = i % nb;
       unsigned char* A = A0 + (size_t)s * GM_A_BYTES;
-      if (i >= nb && !mb_wait(bar_free + 8u * s, (i / nb - 1u) & 1u, GM_WAIT)) {  // the MMAs of step i - nb still read this stage
+      if (i >= nb && !mb_wait(bar_free + 8u * s, (i / nb - 1u) & 1u, a.wait_limit)) {  // the MMAs of step i - nb still read this stage
         *fail = 1;
         break;
       }
@@ -382,7 +384,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
     bool ok = true;
     for (unsigned i = 0; i < ksteps; i++) {
       const unsigned t = i % nb, s = t;
-      const bool got = mb_wait(bars + 8u * t, (i / nb) & 1u, GM_WAIT) && mb_wait(bar_fullA + 8u * s, (i / nb) & 1u, GM_WAIT);
+      const bool got = mb_wait(bars + 8u * t, (i / nb) & 1u, a.wait_limit) && mb_wait(bar_fullA + 8u * s, (i / nb) & 1u, a.wait_limit);
       if (!__all_sync(0xffffffffu, got)) {
         ok = false;
         break;
@@ -415,7 +417,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
         tc_commit(bar_done);
       }
       __syncwarp();
-      mb_wait(bar_done, 0u, GM_WAIT);
+      mb_wait(bar_done, 0u, a.wait_limit);
     }
   } else if (warp == GM_THREADS / 32 + 1) {
     // ---- token rows of step j into B stage j % nb, as soon as the MMAs of step j - nb are done (whole warp in the
@@ -423,26 +425,28 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
     const unsigned leader = elect_one();
     unsigned issued = 0;
     for (unsigned j = 0; j < ksteps; j++) {
-      const bool got = j < nb || mb_wait(bar_free + 8u * (j % nb), (j / nb - 1u) & 1u, GM_WAIT);
+      const bool got = j < nb || mb_wait(bar_free + 8u * (j % nb), (j / nb - 1u) & 1u, a.wait_limit);
       if (!__all_sync(0xffffffffu, got)) {
         if (leader) *fail = 1;
         break;
       }
+      const bool withheld = a.test_stall && j + 1 == a.test_stall;  // test hook: this step's token rows never arrive
       if (leader) {
         const uint32_t fb = bars + 8u * (j % nb);
         mb_expect(fb, b_bytes);
-        bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
+        if (!withheld) bulk_in(sm32(B0 + (size_t)(j % nb) * b_bytes), a.xt + (size_t)(ks0 + j) * (b_bytes / 2u), b_bytes, fb);
       }
+      if (withheld) break;  // nothing to wait for at the end either
       issued++;
       __syncwarp();
     }
     // the copies must have landed before this CTA's shared memory goes away (bounded; all done already unless a wait gave up)
-    for (unsigned j = issued > nb ? issued - nb : 0u; j < issued; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, GM_WAIT);
+    for (unsigned j = issued > nb ? issued - nb : 0u; j < issued; j++) mb_wait(bars + 8u * (j % nb), (j / nb) & 1u, a.wait_limit);
   }
   __syncthreads();
   bool ok = *fail == 0;
   // all MMAs done (tcgen05.commit tracks every MMA issued before it)
-  if (ok && !mb_wait(bar_done, 0u, GM_WAIT)) ok = false;
+  if (ok && !mb_wait(bar_done, 0u, a.wait_limit)) ok = false;
   tc_fence_after();
   if (ok && producer) {
     // warp w reads lanes 32 (w % 4) .. +31; the four warps of a lane quarter take every fourth 8-column group
@@ -718,6 +722,11 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     }
   }
   a.err = (unsigned*)ctx->ws + KS_WS_ERR_WORD;
+  a.wait_limit = GM_WAIT;
+  if (const char* t = getenv("KSEARCH_GEMM_TEST_STALL")) {  // exercises the give-up path: short waits, one operand withheld
+    a.test_stall = (unsigned)atoi(t);
+    if (a.test_stall) a.wait_limit = 4000;
+  }
   const size_t smem = gemm_smem(ctx, a.np, &a.nb);
   if (!smem) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: %u token rows do not fit the shared memory", a.np);
   auto kern = wdtype == KS_Q4K ? gemm_kq_tc_kernel<KS_Q4K> : gemm_kq_tc_kernel<KS_Q6K>;

@@ -83,3 +83,30 @@ def test_gemm_errors(ctx):
         e.matvec_batch(ctx, 8, 512, 257, Q4K, W, x, y)
     with pytest.raises(KsError, match="x buffer"):
         e.matvec_batch(ctx, 8, 512, 16, Q4K, W, ctx.buffer_empty_f32(512 * 15), y)
+
+
+@pytest.mark.parametrize("batch,stall", [(16, 1), (128, 1), (200, 1)])
+def test_gemm_wait_gives_up_and_recovers(oracle, monkeypatch, batch, stall):
+    """A bounded wait of the GEMM kernel that runs out, without a fault or a hang: with KSEARCH_GEMM_TEST_STALL=k the
+    warp that requests the token rows withholds the copy of k-step k - 1 in every CTA and every wait gives up after
+    4000 polls.  The MMA warp stops waiting for the operand, the dequantising warps for their stage, the CTA awaits
+    what it has in flight, frees its tensor memory and leaves; the next synchronize reports KS_ERR_TIMEOUT, and
+    the same call without the hook is correct again."""
+    from ksearch_b200 import CudaContext, _lib
+    c = CudaContext(0, flags=1)
+    rows, cols = 512, 1536
+    W = _gen(Q4K, 91, "Wstall", rows, cols)
+    x = synth.normals(91, "xstall", batch * cols).reshape(batch, cols)
+    bw, bx, y = c.buffer_bytes(W), c.buffer_bytes(x), c.buffer_empty_f32(batch * rows)
+    monkeypatch.setenv("KSEARCH_GEMM_TEST_STALL", str(stall))
+    c.check(c.lib.ks_matvec(c.h, rows, cols, Q4K, bw.h, 0, 0, bx.h, 0, y.h, 0, batch))   # enqueues fine
+    with pytest.raises(KsError) as ei:
+        c.synchronize()
+    assert ei.value.code == _lib.ERR_TIMEOUT
+    c.synchronize()                                                                       # the status word was cleared
+    monkeypatch.delenv("KSEARCH_GEMM_TEST_STALL")
+    c.check(c.lib.ks_matvec(c.h, rows, cols, Q4K, bw.h, 0, 0, bx.h, 0, y.h, 0, batch))
+    c.synchronize()
+    y32, y64 = oracle.matvec(Q4K, W, rows, cols, x)
+    _check(c.read_f32(y, batch * rows).reshape(batch, rows), np.atleast_2d(y32), np.atleast_2d(y64), "gemm after a give-up")
+    c.close()
