@@ -239,6 +239,37 @@ int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_b
 /* ---- decode driver: GemmaPrimModel (GP:76-132, 881-1275, 1616-1768) + KvPool (KV:24-230) ----
  * Dense layers that own their KV cache; no per-layer embeddings, sliding window or shared KV. */
 typedef struct ks_model ks_model;
+
+/* ---- GGUF container (GG:130-417 Gguf::open and accessors); host code, no GPU needed -------------------------
+ * ks_gguf_open maps the file and parses header, key/value metadata and tensor infos; NULL on failure with the
+ * reason in err ("not a GGUF file (bad magic)", "unsupported GGUF version N", "truncated GGUF file", ... — where the
+ * reference panics).  ggml type ids as in the file (GG:20-31: F32 0, F16 1, Q4_0 2, Q4_K 12, Q5_K 13, Q6_K 14, BF16 30). */
+typedef struct ks_gguf ks_gguf;
+ks_gguf* ks_gguf_open(const char* path, char* err, size_t err_len);
+void ks_gguf_close(ks_gguf* g);
+int ks_gguf_version(const ks_gguf* g);
+size_t ks_gguf_n_tensors(const ks_gguf* g);
+size_t ks_gguf_n_kv(const ks_gguf* g);
+uint64_t ks_gguf_data_offset(const ks_gguf* g);                       /* first byte of tensor data: aligned to general.alignment (default 32) */
+const char* ks_gguf_tensor_name(const ks_gguf* g, size_t i);          /* file order; NULL past the end */
+/* GG:262-324 tensor / tensor_type / tensor_file_offset: up to 4 dims (ne0 first), absolute file offset, byte length.
+ * KS_ERR_INVALID when the tensor is not in the file. */
+int ks_gguf_tensor(const ks_gguf* g, const char* name, uint32_t* ggml_type, uint32_t* n_dims, uint64_t* dims4,
+                   uint64_t* file_offset, uint64_t* nbytes);
+const void* ks_gguf_tensor_raw(const ks_gguf* g, const char* name);   /* GG:277 tensor_raw: bytes inside the mapping; NULL if unknown */
+/* GG:326-417 metadata accessors with the reference's coercions; 1 = found, 0 = absent or of another type */
+int ks_gguf_has_key(const ks_gguf* g, const char* key);
+int ks_gguf_get_u32(const ks_gguf* g, const char* key, uint32_t* out);   /* U32, I32, U64, U16 */
+int ks_gguf_get_u64(const ks_gguf* g, const char* key, uint64_t* out);   /* U64, U32, I32 */
+int ks_gguf_get_f32(const ks_gguf* g, const char* key, float* out);      /* F32, F64 */
+int ks_gguf_get_bool(const ks_gguf* g, const char* key, int* out);
+const char* ks_gguf_get_str(const ks_gguf* g, const char* key);          /* NULL if absent */
+long long ks_gguf_arr_len(const ks_gguf* g, const char* key, uint32_t* elem_type);   /* -1: absent or not an array */
+long long ks_gguf_get_arr_u32(const ks_gguf* g, const char* key, uint32_t* out, size_t max);  /* element count, -1: other type */
+long long ks_gguf_get_arr_i32(const ks_gguf* g, const char* key, int32_t* out, size_t max);
+long long ks_gguf_get_arr_f32(const ks_gguf* g, const char* key, float* out, size_t max);
+long long ks_gguf_get_arr_bool(const ks_gguf* g, const char* key, uint8_t* out, size_t max);
+const char* ks_gguf_get_arr_str(const ks_gguf* g, const char* key, size_t i);
 typedef struct {              /* the GemmaConfig fields the dense path uses (crates/ksearch_gemma/src/lib.rs:14-36) */
   int n_layers, hidden, ffn, n_q, n_kv, hd, vocab, max_seq;
   int n_slots;                /* KvPool max_batch (1..64): slots that can advance together */
@@ -262,6 +293,11 @@ int ks_model_upload_tensor(ks_model* m, const char* name, const void* host, size
 /* The same with the file's tensor type: bytes of the resident type are copied; a Q6K, F16 or F32 matrix whose resident
  * form is Q4_K is requantised on the device as the reference's loader does on the host (GP:422-440, GG:803-1016). */
 int ks_model_upload_tensor_as(ks_model* m, const char* name, ks_dtype src_dtype, const void* host, size_t bytes);
+/* Every tensor the model holds, by its GGUF name, out of an open file (GP:149-183, 356-357, 415-451): element counts
+ * are checked against the model's shapes, F32 / F16 / Q4_K / Q6_K tensors are uploaded or requantised as
+ * ks_model_upload_tensor_as does, F32 norm weights are narrowed with the reference's own f32 -> f16 (GGL:39-75)
+ * when the model keeps f16 activations.  KS_ERR_INVALID "tensor not found: NAME" when one is missing. */
+int ks_model_load_gguf(ks_model* m, const ks_gguf* g);
 const void* ks_model_tensor_ptr(const ks_model* m, const char* name);      /* device address of a resident tensor, NULL if unknown */
 size_t ks_model_weight_bytes(const ks_model* m);
 int ks_model_slot_alloc(ks_model* m);                                        /* KV:136 alloc -> slot id, or KS_ERR_STATE "KvPool full" */

@@ -84,6 +84,28 @@ SIGNATURES = {
     "ks_model_tensor_bytes": (_sz, [_vp, C.c_char_p]),
     "ks_model_upload_tensor": (_i, [_vp, C.c_char_p, _vp, _sz]),
     "ks_model_upload_tensor_as": (_i, [_vp, C.c_char_p, _i, _vp, _sz]),
+    "ks_model_load_gguf": (_i, [_vp, _vp]),
+    "ks_gguf_open": (_vp, [C.c_char_p, C.c_char_p, _sz]),
+    "ks_gguf_close": (None, [_vp]),
+    "ks_gguf_version": (_i, [_vp]),
+    "ks_gguf_n_tensors": (_sz, [_vp]),
+    "ks_gguf_n_kv": (_sz, [_vp]),
+    "ks_gguf_data_offset": (C.c_uint64, [_vp]),
+    "ks_gguf_tensor_name": (C.c_char_p, [_vp, _sz]),
+    "ks_gguf_tensor": (_i, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _vp]),
+    "ks_gguf_tensor_raw": (_vp, [_vp, C.c_char_p]),
+    "ks_gguf_has_key": (_i, [_vp, C.c_char_p]),
+    "ks_gguf_get_u32": (_i, [_vp, C.c_char_p, _vp]),
+    "ks_gguf_get_u64": (_i, [_vp, C.c_char_p, _vp]),
+    "ks_gguf_get_f32": (_i, [_vp, C.c_char_p, _vp]),
+    "ks_gguf_get_bool": (_i, [_vp, C.c_char_p, _vp]),
+    "ks_gguf_get_str": (C.c_char_p, [_vp, C.c_char_p]),
+    "ks_gguf_arr_len": (C.c_longlong, [_vp, C.c_char_p, _vp]),
+    "ks_gguf_get_arr_u32": (C.c_longlong, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_gguf_get_arr_i32": (C.c_longlong, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_gguf_get_arr_f32": (C.c_longlong, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_gguf_get_arr_bool": (C.c_longlong, [_vp, C.c_char_p, _vp, _sz]),
+    "ks_gguf_get_arr_str": (C.c_char_p, [_vp, C.c_char_p, _sz]),
     "ks_model_tensor_ptr": (_vp, [_vp, C.c_char_p]),
     "ks_model_weight_bytes": (_sz, [_vp]),
     "ks_model_slot_alloc": (_i, [_vp]),

@@ -888,6 +888,66 @@ int ks_model_upload_tensor_as(ks_model* m, const char* name, ks_dtype src_dtype,
   return KS_OK;
 }
 
+// f32 -> f16 as the reference's converter rounds (crates/ksearch_gguf/src/lib.rs:39-75: half UP in magnitude).
+static uint16_t f32_to_f16_half_up(float v) {
+  uint32_t bits;
+  memcpy(&bits, &v, 4);
+  const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000u);
+  int e = (int)((bits >> 23) & 0xFFu);
+  uint32_t mant = bits & 0x7FFFFFu;
+  if (e == 255) return mant == 0 ? (uint16_t)(sign | 0x7C00u) : (uint16_t)(sign | 0x7C00u | (mant >> 13));
+  e -= 127;
+  if (e > 15) return (uint16_t)(sign | 0x7C00u);
+  if (e < -14) {
+    if (e < -24) return sign;
+    mant |= 0x800000u;
+    const uint32_t shift = (uint32_t)(-14 - e) + 13u;
+    return (uint16_t)(sign | ((mant + (1u << (shift - 1u))) >> shift));
+  }
+  const uint32_t he = (uint32_t)(e + 15), hm = mant + 0x1000u;
+  if (hm & 0x800000u) return (uint16_t)(sign | ((he + 1u) << 10));
+  return (uint16_t)(sign | (he << 10) | (hm >> 13));
+}
+
+int ks_model_load_gguf(ks_model* m, const ks_gguf* g) {
+  if (!m) return KS_ERR_INVALID;
+  ks_ctx* c = m->ctx;
+  KS_REQUIRE(c, g, "model_load_gguf: null file");
+  for (auto& kv : m->by_name) {
+    const char* name = kv.first.c_str();
+    const Tensor& t = *kv.second;
+    uint32_t type = 0, n_dims = 0;
+    uint64_t dims[4], off = 0, nbytes = 0;
+    if (ks_gguf_tensor(g, name, &type, &n_dims, dims, &off, &nbytes)) return ks_fail(c, KS_ERR_INVALID, "tensor not found: %s", name);
+    ks_dtype src;
+    switch (type) {  // gguf_impl.rs:20-31
+      case 0: src = KS_F32; break;
+      case 1: src = KS_F16; break;
+      case 12: src = KS_Q4K; break;
+      case 14: src = KS_Q6K; break;
+      default: return ks_fail(c, KS_ERR_UNSUPPORTED, "tensor %s: ggml type %u is not supported", name, type);
+    }
+    const size_t nelem = t.dtype == KS_F32 ? t.bytes / 4 : t.dtype == KS_F16 ? t.bytes / 2 : t.bytes / ks_block_bytes((ks_dtype)t.dtype) * 256;
+    uint64_t have = 1;
+    for (uint32_t d = 0; d < n_dims && d < 4; d++) have *= dims[d];
+    KS_REQUIRE(c, n_dims <= 4 && have == nelem, "tensor %s: the file holds %llu elements, the model expects %zu", name,
+               (unsigned long long)have, nelem);
+    const void* raw = ks_gguf_tensor_raw(g, name);
+    KS_REQUIRE(c, raw, "tensor %s: no data", name);
+    int rc;
+    if (src == KS_F32 && t.dtype == KS_F16) {  // norm weights of an f16 model
+      std::vector<uint16_t> h(nelem);
+      const float* f = static_cast<const float*>(raw);
+      for (size_t i = 0; i < nelem; i++) h[i] = f32_to_f16_half_up(f[i]);
+      rc = ks_model_upload_tensor(m, name, h.data(), nelem * 2);
+    } else {
+      rc = ks_model_upload_tensor_as(m, name, src, raw, (size_t)nbytes);
+    }
+    if (rc) return rc;
+  }
+  return KS_OK;
+}
+
 const void* ks_model_tensor_ptr(const ks_model* m, const char* name) {
   if (!m || !name) return nullptr;
   auto it = m->by_name.find(name);

@@ -212,6 +212,11 @@ class GemmaCudaModel:
         self.lib.ks_buf_free(self.ctx.h, buf)
         return out.view(np.float32 if self.cfg.act == F32 else np.float16).astype(np.float32)
 
+    def load_gguf(self, g):
+        """Every tensor of the model out of an open Gguf (ks_model_load_gguf): uploads by GGUF name, requantises
+        Q6_K / F16 / F32 matrices to Q4_K on the device as the reference's loader does on the host."""
+        self.ctx.check(self.lib.ks_model_load_gguf(self.h, g.h))
+
     def read_tensor(self, name: str) -> np.ndarray:
         """The resident bytes of a tensor (after any load-time requantisation)."""
         nb = self.lib.ks_model_tensor_bytes(self.h, name.encode())

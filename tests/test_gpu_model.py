@@ -504,6 +504,70 @@ def test_q6k_tensors_are_requantised_at_load(ctx, oracle):
     model.close()
 
 
+@pytest.mark.parametrize("act_f16", [False, True])
+def test_model_loads_from_a_gguf_file(ctx, oracle, tmp_path, act_f16):
+    """A model file as the reference loads it: Q4_K matrices, Q6_K ffn_down / attn_v (requantised at load), F32
+    norm weights, the embedding table in its own type.  ks_model_load_gguf finds every tensor by name; the model
+    then decodes like the CPU decoder that was given the same (requantised) tensors.  Missing tensors, wrong
+    shapes and unsupported types are refused."""
+    from ksearch_b200 import F16, Q6K
+    from ksearch_b200.gguf import GGML_F32, GGML_Q4_K, GGML_Q5_K, GGML_Q6_K, Gguf
+    from tests import gguf_writer as W
+    cfg = ksm.tiny_config(max_seq=40, act=F16 if act_f16 else F32)
+    if act_f16:
+        cfg.sigma_w = 0.0005   # keeps every intermediate inside f16 range with random weights
+    _, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=35, keep=True)
+    tensors = []
+    for name, kind, rows, cols in ksm.tensor_specs(cfg):
+        if name.endswith("ffn_down.weight") or name.endswith("attn_v.weight"):
+            q6 = synth.q6k_matrix(35, name + "/q6", rows, cols, cfg.sigma_w, signed_scales=True)
+            tensors.append((name, GGML_Q6_K, (cols, rows), q6))
+            T[name] = oracle.quantize_q4k(oracle.dequant(Q6K, q6, rows * cols))
+        elif kind == "norm":
+            tensors.append((name, GGML_F32, (cols,), np.asarray(T[name], np.float32)))
+        else:
+            gt = GGML_Q6_K if (kind == "embd" and cfg.embd_dtype == Q6K) else GGML_Q4_K
+            tensors.append((name, gt, (cols, rows), T[name]))
+    path = tmp_path / "tiny.gguf"
+    W.write_gguf(path, [("general.architecture", W.STR, "gemma4"), ("gemma4.block_count", W.U32, cfg.n_layers)], tensors)
+    model = ksm.GemmaCudaModel(ctx, cfg)
+    with Gguf(path) as g:
+        model.load_gguf(g)
+    for name in T:
+        if name.endswith("ffn_down.weight"):
+            assert np.array_equal(model.read_tensor(name), T[name]), name
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    if act_f16:   # f16 activations (norm weights narrowed at load): the bar of test_f16_activation_model_runs_close
+        for t in synth.token_ids(35, "tf", 6, cfg.vocab):
+            model.forward(0, 1, [int(t)], True)
+            cpu.forward_token(int(t), True)
+        ctx.synchronize()
+        got, want = model.read_debug(1, 0).astype(np.float64), cpu.logits().astype(np.float64)
+        assert np.abs(got - want).max() <= 0.05 * np.abs(want).max()
+    else:
+        _teacher_forced(model, cpu, synth.token_ids(35, "tf", 20, cfg.vocab))
+    cpu.close()
+    model.close()
+    # refusals
+    m2 = ksm.GemmaCudaModel(ctx, cfg)
+    W.write_gguf(path, [], tensors[:-1])
+    with Gguf(path) as g, pytest.raises(KsError, match="tensor not found"):
+        m2.load_gguf(g)
+    bad = list(tensors)
+    n0, g0, d0, b0 = bad[2]
+    bad[2] = (n0, g0, (d0[0], d0[1] * 2), np.concatenate([np.asarray(b0).ravel()] * 2))
+    W.write_gguf(path, [], bad)
+    with Gguf(path) as g, pytest.raises(KsError, match="the model expects"):
+        m2.load_gguf(g)
+    bad = list(tensors)
+    bad[2] = (n0, GGML_Q5_K, d0, np.zeros(int(np.prod(d0)) // 256 * 176, np.uint8))
+    W.write_gguf(path, [], bad)
+    with Gguf(path) as g, pytest.raises(KsError, match="not supported"):
+        m2.load_gguf(g)
+    m2.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
