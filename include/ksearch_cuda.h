@@ -276,6 +276,8 @@ typedef struct {              /* the GemmaConfig fields the dense path uses (cra
   float eps, rope_theta, softcap, attn_scale;   /* attn_scale: the reference uses 1 */
   int embd_dtype;             /* ks_dtype of the tied token_embd / lm_head: KS_Q4K or KS_Q6K */
   int act;                    /* ks_dtype of activations and norm weights: KS_F32 or KS_F16 */
+  int sliding_window;         /* GemmaConfig.sliding_window: positions a sliding-window layer attends to; 0 = every layer is full */
+  unsigned long long swa_layers;  /* bit l set: layer l is a sliding-window layer (GemmaConfig.swa_pattern, lib.rs:137-147; <= 64 layers) */
 } ks_model_config;
 typedef struct {              /* GenerateStats (crates/ksearch_gemma/src/lib.rs:189-205), device-timed */
   int prefill_tokens, decode_tokens;

@@ -93,23 +93,67 @@ __device__ __forceinline__ void put_split8(__half* xt, unsigned np, unsigned t, 
   *reinterpret_cast<uint4*>(base + (size_t)np * 8u) = lo;
 }
 
-// x[token, k] (f32, row stride ldx) -> the B image.  Rows past n_tok become zeros.
+// Range.  f16 ends at 65504 and loses its low term below ~1e-3 (the low half of a small value is a denormal);
+// activations do neither.  Every token row is therefore stored as x * 2^-e with e = exponent(largest magnitude) - 14,
+// so the scaled row peaks in [2^14, 2^15), and the GEMM multiplies that token's outputs by 2^e (both exact).
+// The factors 2^e sit behind the image, one float per (padded) token row; an all-zero row keeps e = 0.
+__device__ __host__ __forceinline__ size_t xt_scale_off(unsigned cols, unsigned np) { return (size_t)cols * np * 2u; }  // in halves
+__device__ __forceinline__ float row_scale_down(float row_max, float* scale_up) {
+  int e = 0;
+  if (row_max > 0.0f && row_max < 3.0e38f) {
+    e = (int)((__float_as_uint(row_max) >> 23) & 0xFFu) - 127 - 14;
+    e = e < -100 ? -100 : e;  // 2^-e must stay a float
+  }
+  *scale_up = __uint_as_float((unsigned)(127 + e) << 23);
+  return __uint_as_float((unsigned)(127 - e) << 23);
+}
+__device__ __forceinline__ float block_max_f(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+  return t;
+}
+__device__ __forceinline__ float absmax8(const float (&v)[8]) {
+  return fmaxf(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))),
+               fmaxf(fmaxf(fabsf(v[4]), fabsf(v[5])), fmaxf(fabsf(v[6]), fabsf(v[7]))));
+}
+
+// x[token, k] (f32, row stride ldx) -> the B image.  One block per (padded) token row; rows past n_tok become zeros.
 __global__ void x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsigned np, unsigned cols, __half* xt) {
   ks_pdl_entry();
-  const unsigned chunks = cols / 8u;
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)np * chunks) return;
-  const unsigned t = (unsigned)(i % np), ck = (unsigned)(i / np);  // consecutive threads: consecutive tokens of one chunk
-  float v[8];
-  if (t < n_tok) {
-    const float4 a = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + (size_t)ck * 8u);
-    const float4 b = *reinterpret_cast<const float4*>(x + (size_t)t * ldx + (size_t)ck * 8u + 4u);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
+  __shared__ float red[32];
+  const unsigned t = blockIdx.x, chunks = cols / 8u;
+  const bool live = t < n_tok;
+  const float* row = x + (size_t)t * ldx;
+  float m = 0.0f;
+  if (live)
+    for (unsigned ck = threadIdx.x; ck < chunks; ck += blockDim.x) {
+      const float4 a = *reinterpret_cast<const float4*>(row + (size_t)ck * 8u), b = *reinterpret_cast<const float4*>(row + (size_t)ck * 8u + 4u);
+      const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      m = fmaxf(m, absmax8(v));
+    }
+  m = block_max_f(m, red);
+  float up;
+  const float down = row_scale_down(m, &up);
+  if (threadIdx.x == 0) reinterpret_cast<float*>(xt + xt_scale_off(cols, np))[t] = up;
+  for (unsigned ck = threadIdx.x; ck < chunks; ck += blockDim.x) {
+    float v[8];
+    if (live) {
+      const float4 a = *reinterpret_cast<const float4*>(row + (size_t)ck * 8u), b = *reinterpret_cast<const float4*>(row + (size_t)ck * 8u + 4u);
+      v[0] = a.x * down; v[1] = a.y * down; v[2] = a.z * down; v[3] = a.w * down;
+      v[4] = b.x * down; v[5] = b.y * down; v[6] = b.z * down; v[7] = b.w * down;
+    } else {
 #pragma unroll
-    for (int e = 0; e < 8; e++) v[e] = 0.0f;
+      for (int e = 0; e < 8; e++) v[e] = 0.0f;
+    }
+    put_split8(xt, np, t, ck, v);
   }
-  put_split8(xt, np, t, ck, v);
 }
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
@@ -452,6 +496,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
     // warp w reads lanes 32 (w % 4) .. +31; the four warps of a lane quarter take every fourth 8-column group
     const unsigned lane_base = (warp & 3u) * 32u;
     const unsigned out_row = row_base + lane_base + lane;
+    const float* up = reinterpret_cast<const float*>(a.xt + xt_scale_off(a.cols, a.np));  // 2^e of every token row
     for (unsigned c0 = (warp >> 2) * 8u; c0 < a.np; c0 += 32u) {
       uint32_t v[8], v2[8];
       tc_ld8(tmem + (lane_base << 16) + c0, v);
@@ -465,7 +510,7 @@ __global__ void __launch_bounds__(GM_THREADS + 64, 2) gemm_kq_tc_kernel(const Ge
 #pragma unroll
         for (unsigned e = 0; e < 8; e++)
           if (c0 + e < a.n_tok)
-            yout[(size_t)(c0 + e) * ldy + out_row] = (__uint_as_float(v[e]) + __uint_as_float(v2[e])) * (1.0f / GM_SCALE);
+            yout[(size_t)(c0 + e) * ldy + out_row] = (__uint_as_float(v[e]) + __uint_as_float(v2[e])) * ((1.0f / GM_SCALE) * up[c0 + e]);
       }
     }
   } else if (!ok && tid == 0) {
@@ -562,48 +607,70 @@ __global__ void gemm_finish_norm_split_kernel(const EpiNormArgs e) {
   for (int i = 0; i < 8; i++) ss2 = fmaf(v[i], v[i], ss2);
   ss2 = block_sum_f(ss2, red);
   const float inv2 = 1.0f / sqrtf(ss2 / (float)e.rows + e.eps);
+  float xn[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) xn[i] = 0.0f;
+  if (live) {
+    const float4 n0 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck), n1 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck + 4);
+    const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) xn[i] = __fmul_rn(__fmul_rn(v[i], inv2), nn[i]);
+  }
+  float up;
+  const float down = row_scale_down(block_max_f(absmax8(xn), red), &up);
+  if (threadIdx.x == 0) reinterpret_cast<float*>(e.xt + xt_scale_off(e.rows, e.np))[t] = up;
   if (ck < chunks) {
-    float xn[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) xn[i] = 0.0f;
-    if (live) {
-      const float4 n0 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck), n1 = *reinterpret_cast<const float4*>(e.w_norm + 8u * ck + 4);
-      const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
-#pragma unroll
-      for (int i = 0; i < 8; i++) xn[i] = __fmul_rn(__fmul_rn(v[i], inv2), nn[i]);
-    }
+    for (int i = 0; i < 8; i++) xn[i] *= down;
     put_split8(e.xt, e.np, t, ck, xn);
   }
 }
 
 // gelu(sum of gate partials) * (sum of up partials) (lib.rs:953) straight into the image the down GEMM reads.
+constexpr int GM_GELU_CHUNKS = 8;  // 8-value chunks per thread: rows up to 8 * 8 * 256 = 16384
 __global__ void gemm_finish_gelu_split_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok,
                                               unsigned np, unsigned rows, __half* xt) {
   ks_pdl_entry();
-  const unsigned chunks = rows / 8u;
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)np * chunks) return;
-  const unsigned t = (unsigned)(i / chunks), ck = (unsigned)(i % chunks);
-  float v[8];
+  __shared__ float red[32];
+  const unsigned t = blockIdx.x, chunks = rows / 8u;  // one block per (padded) token row
+  float v[GM_GELU_CHUNKS][8];
+  float m = 0.0f;
 #pragma unroll
-  for (int k = 0; k < 8; k++) v[k] = 0.0f;
-  if (t < n_tok) {
-    float g[8], u[8];
+  for (int kk = 0; kk < GM_GELU_CHUNKS; kk++) {
+    const unsigned ck = threadIdx.x + (unsigned)kk * blockDim.x;
 #pragma unroll
-    for (int k = 0; k < 8; k++) g[k] = u[k] = 0.0f;
-    const size_t at = (size_t)t * rows + 8u * ck;
-    for (unsigned s = 0; s < splits; s++) {
-      const float4 a = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at);
-      const float4 b = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at + 4);
-      const float4 c = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at);
-      const float4 d = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at + 4);
-      g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
-      u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w; u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+    for (int k = 0; k < 8; k++) v[kk][k] = 0.0f;
+    if (t < n_tok && ck < chunks) {
+      float g[8], u[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) g[k] = u[k] = 0.0f;
+      const size_t at = (size_t)t * rows + 8u * ck;
+      for (unsigned s = 0; s < splits; s++) {
+        const float4 a = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at);
+        const float4 b = *reinterpret_cast<const float4*>(P0 + (size_t)s * part_stride + at + 4);
+        const float4 c = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at);
+        const float4 d = *reinterpret_cast<const float4*>(P1 + (size_t)s * part_stride + at + 4);
+        g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w; g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        u[0] += c.x; u[1] += c.y; u[2] += c.z; u[3] += c.w; u[4] += d.x; u[5] += d.y; u[6] += d.z; u[7] += d.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; k++) v[kk][k] = gelu_mul(g[k], u[k]);
+      m = fmaxf(m, absmax8(v[kk]));
     }
-#pragma unroll
-    for (int k = 0; k < 8; k++) v[k] = gelu_mul(g[k], u[k]);
   }
-  put_split8(xt, np, t, ck, v);
+  // gelu(gate) * up is where a random-weight model leaves the f16 range
+  float up;
+  const float down = row_scale_down(block_max_f(m, red), &up);
+  if (threadIdx.x == 0) reinterpret_cast<float*>(xt + xt_scale_off(rows, np))[t] = up;
+#pragma unroll
+  for (int kk = 0; kk < GM_GELU_CHUNKS; kk++) {
+    const unsigned ck = threadIdx.x + (unsigned)kk * blockDim.x;
+    if (ck < chunks) {
+#pragma unroll
+      for (int k = 0; k < 8; k++) v[kk][k] *= down;
+      put_split8(xt, np, t, ck, v[kk]);
+    }
+  }
 }
 }  // namespace
 
@@ -653,14 +720,13 @@ bool gemm_covers(ks_dtype wdtype, size_t cols, int n_tok) {
 }  // namespace
 
 // Bytes of the B image of n_tok rows of `cols` values (hi + lo halves, token count padded to 16).
-size_t ks_gemm_xt_bytes(size_t cols, int n_tok) { return cols * gemm_np(n_tok) * 4; }
+size_t ks_gemm_xt_bytes(size_t cols, int n_tok) { return cols * gemm_np(n_tok) * 4 + (size_t)gemm_np(n_tok) * 4; }  // image + one factor per row
 
 // x[t * ldx + k] (f32) -> the B image in xt.
 int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt) {
   if (cols % 256 || n_tok < 1 || n_tok > 256 || ldx % 4) return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad operand shape");
   const unsigned np = gemm_np(n_tok);
-  const size_t n_thr = (size_t)np * (cols / 8);
-  KS_LAUNCH(ctx, (x_split_kernel), (unsigned)((n_thr + 255) / 256), 256, 0, x, ldx, (unsigned)n_tok, np, (unsigned)cols, (__half*)xt);
+  KS_LAUNCH(ctx, (x_split_kernel), np, 256, 0, x, ldx, (unsigned)n_tok, np, (unsigned)cols, (__half*)xt);
   return ks_after_launch(ctx, "x_split");
 }
 
@@ -672,7 +738,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
                         int n_tok, float* const* y, const size_t* ldy, float* P, int mode, const ks_gemm_epi* epi) {
   if (!gemm_covers(wdtype, cols, n_tok) || n_seg < 1 || n_seg > 3) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
   if ((mode == KS_GEMM_NORM_SPLIT && (n_seg != 1 || !epi || rows[0] % 8 || rows[0] > 8192)) ||
-      (mode == KS_GEMM_GELU_SPLIT && (n_seg != 2 || !epi || rows[0] != rows[1] || rows[0] % 8)))
+      (mode == KS_GEMM_GELU_SPLIT && (n_seg != 2 || !epi || rows[0] != rows[1] || rows[0] % 8 || rows[0] > 8u * GM_GELU_CHUNKS * 256u)))
     return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad epilogue arguments");
   GemmArgs a{};
   FinishArgs f{};
@@ -758,8 +824,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     return ks_after_launch(ctx, "gemm_finish_norm_split");
   }
   if (mode == KS_GEMM_GELU_SPLIT) {
-    const size_t n = (size_t)a.np * (rows[0] / 8);
-    KS_LAUNCH(ctx, (gemm_finish_gelu_split_kernel), (unsigned)((n + 255) / 256), 256, 0, (const float*)a.y[0], (const float*)a.y[1],
+    KS_LAUNCH(ctx, (gemm_finish_gelu_split_kernel), a.np, 256, 0, (const float*)a.y[0], (const float*)a.y[1],
               a.part_stride[0], splits, (unsigned)n_tok, a.np, (unsigned)rows[0], (__half*)epi->xt_out);
     return ks_after_launch(ctx, "gemm_finish_gelu_split");
   }

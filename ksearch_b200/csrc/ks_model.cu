@@ -27,15 +27,25 @@
 
 namespace {
 
-__global__ void begin_token_kernel(int n, const int* pos, float* meta) {
+// (tlen, start) of a row with kv_len cached positions: everything for a full-attention layer, the last `window`
+// positions for a sliding-window layer (gemma_prim.rs:1009-1016).  meta_swa may be null (no such layers).
+__device__ __forceinline__ void write_meta_pair(float* meta, float* meta_swa, int row, int kv_len, int window) {
+  meta[row * 4 + 0] = (float)kv_len;
+  meta[row * 4 + 1] = 0.0f;
+  meta[row * 4 + 2] = 0.0f;
+  meta[row * 4 + 3] = 0.0f;
+  if (meta_swa) {
+    const int start = kv_len > window ? kv_len - window : 0;
+    meta_swa[row * 4 + 0] = (float)(kv_len - start);
+    meta_swa[row * 4 + 1] = (float)start;
+    meta_swa[row * 4 + 2] = 0.0f;
+    meta_swa[row * 4 + 3] = 0.0f;
+  }
+}
+__global__ void begin_token_kernel(int n, const int* pos, float* meta, float* meta_swa, int window) {
   ks_pdl_entry();
   const int s = threadIdx.x;
-  if (s < n) {
-    meta[s * 4 + 0] = (float)(pos[s] + 1);  // tlen = kv_len (gemma_prim.rs:1009-1016, full attention)
-    meta[s * 4 + 1] = 0.0f;                 // start
-    meta[s * 4 + 2] = 0.0f;
-    meta[s * 4 + 3] = 0.0f;
-  }
+  if (s < n) write_meta_pair(meta, meta_swa, s, pos[s] + 1, window);
 }
 __global__ void end_token_kernel(int n, int* pos) {
   ks_pdl_entry();
@@ -69,15 +79,12 @@ __global__ void collect_kernel(int n, const float* tok, const unsigned* err_word
 }
 __global__ void set_state_kernel(int slot, int pos_value, int* pos) { ks_pdl_entry(); pos[slot] = pos_value; }
 // A prompt chunk: row t of the chunk sits at position base + t of ONE slot (causal: it sees base + t + 1 positions).
-__global__ void begin_chunk_kernel(int n, const int* base, int* cpos, float* meta) {
+__global__ void begin_chunk_kernel(int n, const int* base, int* cpos, float* meta, float* meta_swa, int window) {
   ks_pdl_entry();
   const int t = threadIdx.x;
   if (t < n) {
     cpos[t] = base[0] + t;
-    meta[t * 4 + 0] = (float)(base[0] + t + 1);
-    meta[t * 4 + 1] = 0.0f;
-    meta[t * 4 + 2] = 0.0f;
-    meta[t * 4 + 3] = 0.0f;
+    write_meta_pair(meta, meta_swa, t, base[0] + t + 1, window);
   }
 }
 __global__ void end_chunk_kernel(int n, int* base) {
@@ -121,6 +128,7 @@ struct ks_model {
   float* tok = nullptr;   // [2][n_slots] f32 token ids, ping-pong (gemma_prim.rs:98-99)
   int* pos = nullptr;     // [n_slots]
   float* meta = nullptr;  // [n_slots][4]
+  float* meta_swa = nullptr;  // the same for sliding-window layers; null when the model has none
   float* attn_tmp = nullptr;
   int n_splits = 1;
   float* ret = nullptr;       // [n_slots][n_slots + 1] per first slot: next ids + status flag of the last blocking step
@@ -152,6 +160,7 @@ struct ks_model {
   float* ctok = nullptr;
   int* cpos = nullptr;
   float* cmeta = nullptr;
+  float* cmeta_swa = nullptr;
   float* cattn_tmp = nullptr;
   int chunk = 1;  // tokens per prompt chunk: as many as the matvec kernels can stage side by side (<= KS_PREFILL_CHUNK)
   // rows per pass through the tensor-core GEMM (0: not available, activations are not f32); its scratch inside the
@@ -187,6 +196,7 @@ struct Lane {
   float* ret;        // where a blocking step's ids and status flag are collected
   int* pos;          // device, one per row
   float* meta;       // device, (tlen, start, -, -) per row
+  float* meta_swa;   // the same for sliding-window layers (null: none)
   float* attn_tmp;
   size_t kv_off;     // byte offset of row 0's cache inside every layer's K / V allocation
   size_t kv_stride;  // bytes between the caches of consecutive rows
@@ -212,6 +222,7 @@ Lane slot_lane(ks_model* m, int first, int src) {
   L.ret = m->ret + (size_t)first * (g.n_slots + 1);
   L.pos = m->pos + first;
   L.meta = m->meta + (size_t)first * 4;
+  L.meta_swa = m->meta_swa ? m->meta_swa + (size_t)first * 4 : nullptr;
   L.attn_tmp = m->attn_tmp;
   L.kv_off = (size_t)first * m->slot_stride;
   L.kv_stride = m->slot_stride;
@@ -227,6 +238,7 @@ Lane chunk_lane(ks_model* m, int slot) {
   L.tok_out = nullptr;
   L.pos = m->cpos;
   L.meta = m->cmeta;
+  L.meta_swa = m->cmeta_swa;
   L.attn_tmp = m->cattn_tmp;
   L.kv_off = (size_t)slot * m->slot_stride;
   L.kv_stride = 0;
@@ -245,9 +257,9 @@ unsigned row_threads(int n) { return (unsigned)((n + 1 + 31) / 32 * 32); }  // o
 
 int lane_begin(ks_model* m, const Lane& L, int n) {
   if (L.chunk_base)
-    KS_LAUNCH(m->ctx, (begin_chunk_kernel), 1, row_threads(n), 0, n, (const int*)L.chunk_base, L.pos, L.meta);
+    KS_LAUNCH(m->ctx, (begin_chunk_kernel), 1, row_threads(n), 0, n, (const int*)L.chunk_base, L.pos, L.meta, L.meta_swa, (int)m->cfg.sliding_window);
   else
-    KS_LAUNCH(m->ctx, (begin_token_kernel), 1, row_threads(n), 0, n, (const int*)L.pos, L.meta);
+    KS_LAUNCH(m->ctx, (begin_token_kernel), 1, row_threads(n), 0, n, (const int*)L.pos, L.meta, L.meta_swa, (int)m->cfg.sliding_window);
   return ks_after_launch(m->ctx, "begin_token");
 }
 int lane_end(ks_model* m, const Lane& L, int n) {
@@ -256,6 +268,14 @@ int lane_end(ks_model* m, const Lane& L, int n) {
   else
     KS_LAUNCH(m->ctx, (end_token_kernel), 1, row_threads(n), 0, n, L.pos);
   return ks_after_launch(m->ctx, "end_token");
+}
+
+// Does any layer attend to a window shorter than the cache?
+bool has_window(const ks_model_config& g) { return g.sliding_window > 0 && g.sliding_window < g.max_seq && g.swa_layers != 0; }
+
+// The (tlen, start) rows layer l's attention reads: the sliding-window ones for a sliding-window layer.
+const float* layer_meta(const ks_model* m, const Lane& L, int l) {
+  return L.meta_swa && ((m->cfg.swa_layers >> l) & 1ull) ? L.meta_swa : L.meta;
 }
 
 // One token per row through every layer.
@@ -270,7 +290,6 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
   const float* tok_in = L_.tok_in;
   float* tok_out = L_.tok_out;
   int* pos = L_.pos;
-  float* meta = L_.meta;
   int rc;
 
   if ((rc = lane_begin(m, L_, n))) return rc;
@@ -289,7 +308,7 @@ int enqueue_forward(ks_model* m, const Lane& L_, int n, bool want_logits) {
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, att_splits_for(m, n))))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, layer_meta(m, L_, l), L_.attn_tmp, o, att_splits_for(m, n))))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, x2, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
@@ -350,7 +369,7 @@ int enqueue_forward_gemm(ks_model* m, const Lane& L_, int n, bool want_logits) {
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, L_.pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, L_.meta, L_.attn_tmp, o, att_splits)))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, layer_meta(m, L_, l), L_.attn_tmp, o, att_splits)))
       return rc;
     if ((rc = ks_launch_gemm_split(c, (const float*)o, qn, n, qn, m->gemm_xt))) return rc;
     {  // o-proj, x += rms(.) * w_post_attn, image of rms(x) * w_ffn_norm (lib.rs:539)
@@ -404,7 +423,6 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
   const float* tok_in = L_.tok_in;
   float* tok_out = L_.tok_out;
   int* pos = L_.pos;
-  float* meta = L_.meta;
   int rc;
 
   if ((rc = lane_begin(m, L_, n))) return rc;
@@ -432,7 +450,7 @@ int enqueue_forward_fused(ks_model* m, const Lane& L_, int n, bool want_logits) 
     if ((rc = ks_launch_per_head_qkv_q40(c, nq, nkv, hd, n, g.eps, act, q, L.q_norm.dptr, m->rope, k, L.k_norm.dptr, v, q,
                                          kk, kv, pos, L_.kv_stride)))
       return rc;
-    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, meta, L_.attn_tmp, o, att_splits_for(m, n))))
+    if ((rc = ks_launch_sdpa(c, n, nq, nkv, hd, g.attn_scale, act, q, kk, kv, L_.kv_stride, layer_meta(m, L_, l), L_.attn_tmp, o, att_splits_for(m, n))))
       return rc;
     ks_mv_seg so{(const uint8_t*)L.wo.dptr, yb, (unsigned)H};
     if ((rc = ks_launch_matvec(c, KS_Q4K, &so, 1, KS_EPI_PLAIN, qn, act, o, n, nullptr))) return rc;
@@ -552,7 +570,7 @@ int run_forward(ks_model* m, int first, int n, int src, bool want_logits) {
   auto it = m->graphs.find(key);
   if (it == m->graphs.end()) {
     ks_model::Mega mg;
-    if (n == 1) {
+    if (n == 1) {  // (with sliding-window layers get_mega leaves mg empty: the launch-per-op path runs)
       int rcm = get_mega(m, first, &mg);
       if (rcm) return rcm;
     }
@@ -641,6 +659,8 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   if (g.embd_dtype != KS_Q4K && g.embd_dtype != KS_Q6K) return bad("token_embd must be Q4K or Q6K");
   if (g.act != KS_F32 && g.act != KS_F16) return bad("activation dtype must be F32 or F16");
   if (!(g.softcap > 0.0f)) return bad("softcap must be > 0");
+  if (g.sliding_window < 0) return bad("sliding_window must be >= 0");
+  if (g.n_layers > 64 && g.sliding_window > 0 && g.swa_layers) return bad("sliding-window layers are flagged in a 64-bit mask: at most 64 layers");
   cudaSetDevice(ctx->device);
 
   ks_model* m = new ks_model();
@@ -700,7 +720,8 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
   // launch per op (the path every multi-slot step takes anyway), 1 = the kernel whose phases meet at grid
   // barriers (default), 2 = the kernel whose blocks exchange tagged words instead of meeting.
   const char* dk = getenv("KSEARCH_DECODE_KERNEL");
-  m->use_mega = m->fused && g.act == KS_F32 && !(dk && dk[0] == '0');
+  // (the persistent kernels attend to the whole context: a model with sliding-window layers takes one launch per op)
+  m->use_mega = m->fused && g.act == KS_F32 && !(dk && dk[0] == '0') && !has_window(g);
   m->decode_kernel = dk && dk[0] == '2' ? 2 : 1;
   // Two slots step faster as two persistent-kernel passes than side by side through one launch per op (same
   // measurement: E2B 938 against 1074 us, E4B 1157 against 1378); from three slots on the GEMM path wins.
@@ -713,6 +734,7 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
        dev_alloc(m, &m->ff, S * F * ab) == KS_OK && dev_alloc(m, &m->logits, S * (size_t)g.vocab * ab) == KS_OK &&
        dev_alloc(m, (void**)&m->tok, 2 * S * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->pos, S * sizeof(int)) == KS_OK &&
        dev_alloc(m, (void**)&m->meta, S * 4 * sizeof(float)) == KS_OK &&
+       (!has_window(g) || dev_alloc(m, (void**)&m->meta_swa, S * 4 * sizeof(float)) == KS_OK) &&
        dev_alloc(m, (void**)&m->ret, S * (S + 1) * sizeof(float)) == KS_OK &&
        dev_alloc(m, (void**)&m->rope, (size_t)g.max_seq * g.hd * sizeof(float)) == KS_OK;
   {
@@ -756,7 +778,8 @@ ks_model* ks_model_create(ks_ctx* ctx, const ks_model_config* cfg) {
          dev_alloc(m, &m->ck, C * kvn * ab) == KS_OK && dev_alloc(m, &m->cv, C * kvn * ab) == KS_OK &&
          dev_alloc(m, &m->co, C * qn * ab) == KS_OK && dev_alloc(m, &m->cff, C * F * ab) == KS_OK &&
          dev_alloc(m, (void**)&m->ctok, C * sizeof(float)) == KS_OK && dev_alloc(m, (void**)&m->cpos, C * sizeof(int)) == KS_OK &&
-         dev_alloc(m, (void**)&m->cmeta, C * 4 * sizeof(float)) == KS_OK;
+         dev_alloc(m, (void**)&m->cmeta, C * 4 * sizeof(float)) == KS_OK &&
+         (!has_window(g) || dev_alloc(m, (void**)&m->cmeta_swa, C * 4 * sizeof(float)) == KS_OK);
   }
   if (ok) {
     m->n_splits = ks_sdpa_pick_splits(ctx, 1, g.n_kv, g.max_seq);

@@ -35,6 +35,8 @@ class ModelConfig:
     attn_scale: float = 1.0 / 16.0
     embd_dtype: int = Q6K
     act: int = F32
+    sliding_window: int = 0       # positions a sliding-window layer attends to (0: every layer is full attention)
+    swa_layers: int = 0           # bit l set: layer l is a sliding-window layer
     # synthetic-weight scales: fp16 |N(0, sigma)| super-block scales
     sigma_w: float = 0.01
     sigma_embd: float = 1e-4
@@ -107,7 +109,7 @@ def weight_bytes_per_token(cfg: ModelConfig) -> int:
 class _Cfg(C.Structure):
     _fields_ = [(k, C.c_int) for k in ("n_layers", "hidden", "ffn", "n_q", "n_kv", "hd", "vocab", "max_seq", "n_slots")] + \
                [(k, C.c_float) for k in ("eps", "rope_theta", "softcap", "attn_scale")] + \
-               [("embd_dtype", C.c_int), ("act", C.c_int)]
+               [("embd_dtype", C.c_int), ("act", C.c_int), ("sliding_window", C.c_int), ("swa_layers", C.c_ulonglong)]
 
 
 class GenStats(C.Structure):

@@ -647,6 +647,10 @@ typedef struct {
   const uint8_t** wgate; const uint8_t** wup; const uint8_t** wdown;
   const float** attn_norm; const float** q_norm; const float** k_norm;
   const float** post_attn_norm; const float** ffn_norm; const float** post_ffw_norm;
+  /* sliding-window layers (gemma_prim.rs:1009-1016): layer l with bit l of swa_layers set attends to the last
+   * sliding_window positions only; 0 = every layer is full attention */
+  int sliding_window;
+  unsigned long long swa_layers;
 } kso_model;
 
 typedef struct {
@@ -715,8 +719,13 @@ int kso_forward_token(kso_state* s, int token, int want_logits) {
     kso_rmsnorm_per_head_qkv_q40(nq, nkv, hd, 1, m->eps, s->q, m->q_norm[l],
                                  s->rope + (size_t)s->pos * hd, s->k, m->k_norm[l], s->v, s->q,
                                  s->kv_k[l], s->kv_v[l], (size_t)s->pos * nkv * rowb);
-    kso_sdpa_decode(nq, nkv, hd, s->q, s->kv_k[l], s->kv_v[l], (size_t)s->pos + 1, 0,
-                    m->attn_scale, 0, s->o);
+    {
+      /* kv_len = pos + 1; a sliding-window layer starts at kv_len - window (gemma_prim.rs:1009-1016) */
+      size_t kv_len = (size_t)s->pos + 1, start = 0;
+      if (m->sliding_window > 0 && ((m->swa_layers >> l) & 1ull) && kv_len > (size_t)m->sliding_window)
+        start = kv_len - (size_t)m->sliding_window;
+      kso_sdpa_decode(nq, nkv, hd, s->q, s->kv_k[l], s->kv_v[l], kv_len - start, start, m->attn_scale, 0, s->o);
+    }
     kso_matvec(KS_Q4K, m->wo[l], H, nq * hd, s->o, 1, NULL, acc);
     for (size_t i = 0; i < H; i++) s->x2[i] = (float)acc[i];
     kso_rmsnorm_add_then_rmsnorm(s->x2, m->post_attn_norm[l], s->x, m->ffn_norm[l], H, 1, m->eps,

@@ -277,6 +277,7 @@ class _Model(C.Structure):
         ("wgate", C.c_void_p), ("wup", C.c_void_p), ("wdown", C.c_void_p),
         ("attn_norm", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
         ("post_attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("post_ffw_norm", C.c_void_p),
+        ("sliding_window", C.c_int), ("swa_layers", C.c_ulonglong),
     ]
 
 
@@ -305,6 +306,8 @@ class CpuDecoder:
             setattr(m, k, int(cfg[k]))
         for k in ("eps", "rope_theta", "softcap", "attn_scale"):
             setattr(m, k, float(cfg[k]))
+        m.sliding_window = int(cfg.get("sliding_window", 0))
+        m.swa_layers = int(cfg.get("swa_layers", 0))
 
         def hold(a, dt):
             a = np.ascontiguousarray(a, dtype=dt)
@@ -373,7 +376,10 @@ _CFG_KEYS = ("n_layers", "hidden", "ffn", "n_q", "n_kv", "hd", "vocab", "max_seq
 
 def decoder_cfg(cfg) -> dict:
     """The CpuDecoder's config dict from a model-config object (attributes of the same names)."""
-    return {k: getattr(cfg, k) for k in _CFG_KEYS}
+    d = {k: getattr(cfg, k) for k in _CFG_KEYS}
+    d["sliding_window"] = int(getattr(cfg, "sliding_window", 0))
+    d["swa_layers"] = int(getattr(cfg, "swa_layers", 0))
+    return d
 
 
 def compare_streams(cuda_tokens, cpu_decoder, prompt, logit_tol: float = 2e-3):

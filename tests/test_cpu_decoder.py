@@ -40,7 +40,9 @@ def _np_forward(cfg, T, oracle, tokens):
             vq = oracle.dequant(synth.Q40, oracle.pack_q40(vh.astype(np.float32), True), nkv * hd).reshape(nkv, hd)
             Ks[l].append(kq)
             Vs[l].append(vq)
-            o = np_ref.attention(qh, np.stack(Ks[l]), np.stack(Vs[l]), nq, nkv, hd, cfg.attn_scale)
+            # a sliding-window layer attends to the last `sliding_window` positions (gemma_prim.rs:1009-1016)
+            lo = max(0, len(Ks[l]) - cfg.sliding_window) if cfg.sliding_window and (cfg.swa_layers >> l) & 1 else 0
+            o = np_ref.attention(qh, np.stack(Ks[l][lo:]), np.stack(Vs[l][lo:]), nq, nkv, hd, cfg.attn_scale)
             a = deq(p + "attn_output.weight", synth.Q4K, H, nq * hd) @ o
             x = x + np_ref.rmsnorm(a, T[p + "post_attention_norm.weight"], cfg.eps)
             h2 = np_ref.rmsnorm(x, T[p + "ffn_norm.weight"], cfg.eps)
@@ -72,6 +74,34 @@ def test_cpu_decoder_matches_numpy_and_is_deterministic(oracle):
     b = dec.generate([1, 2, 3], 4)
     assert a == b and len(a) == 4
     dec.close()
+
+
+def test_cpu_decoder_sliding_window_layers(oracle):
+    """Layers flagged in swa_layers attend to the last sliding_window positions only (gemma_prim.rs:1009-1016):
+    against the NumPy restatement, and against the full-attention decoder (equal while the context fits the
+    window, different beyond)."""
+    cfg = ksm.tiny_config(max_seq=12)
+    cfg.n_layers = 2
+    T = ksm.synth_tensors(cfg, 6)
+    toks = [9, 300, 41, 1500, 7, 7, 88, 1023]
+    full = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    cfg.sliding_window, cfg.swa_layers = 3, 0b01          # layer 0 slides, layer 1 is full
+    win = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    for i, t in enumerate(toks):
+        full.forward_token(t, True)
+        win.forward_token(t, True)
+        same = np.array_equal(full.logits(), win.logits())
+        assert same == (i < 3), i
+    got = win.logits().astype(np.float64)
+    want = _np_forward(cfg, T, oracle, toks)
+    assert np.abs(got - want).max() < 2e-2 * np.abs(want).max()
+    cfg.sliding_window = 64                                # a window longer than the cache changes nothing
+    wide = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    for t in toks:
+        wide.forward_token(t, True)
+    assert np.array_equal(wide.logits(), full.logits())
+    for d in (full, win, wide):
+        d.close()
 
 
 def test_cpu_decoder_max_seq(oracle):

@@ -110,3 +110,29 @@ def test_gemm_wait_gives_up_and_recovers(oracle, monkeypatch, batch, stall):
     y32, y64 = oracle.matvec(Q4K, W, rows, cols, x)
     _check(c.read_f32(y, batch * rows).reshape(batch, rows), np.atleast_2d(y32), np.atleast_2d(y64), "gemm after a give-up")
     c.close()
+
+
+@pytest.mark.parametrize("dtype", [Q4K, Q6K])
+def test_gemm_token_rows_beyond_the_f16_range(ctx, oracle, dtype):
+    """Token rows whose values leave the f16 range (65504): the operand image stores such a row scaled by a power
+    of two and the kernel scales its outputs back, so the result still matches the f64 CPU result.  Rows of small,
+    ordinary and huge magnitude side by side in one batch."""
+    rows, cols, batch = 256, 1024, 12
+    W = _gen(dtype, 83, "Wrange", rows, cols)
+    x = synth.normals(83, "xrange", batch * cols).reshape(batch, cols).astype(np.float32)
+    x[1] *= 1e-4
+    x[2] *= 3.0e4        # peaks near 1e5: past the f16 range
+    x[5] *= 1.0e9
+    x[7, 100] = 7.0e5    # one outlier in an ordinary row
+    x[9] *= 2.5e30
+    y = ctx.buffer_empty_f32(batch * rows)
+    bw, bx = ctx.buffer_bytes(W), ctx.buffer_bytes(x)
+    ctx.check(ctx.lib.ks_matvec(ctx.h, rows, cols, dtype, bw.h, 0, 0, bx.h, 0, y.h, 0, batch))
+    got = ctx.read_f32(y, batch * rows).reshape(batch, rows).astype(np.float64)
+    assert np.isfinite(got).all()
+    _, y64 = oracle.matvec(dtype, W, rows, cols, x)
+    y64 = np.atleast_2d(y64).astype(np.float64)
+    for t in range(batch):                     # each row against its own scale
+        scale = np.abs(y64[t]).max()
+        err = np.abs(got[t] - y64[t])
+        assert (err <= 1e-3 * np.abs(y64[t]) + 1e-5 * scale).all(), (t, err.max() / scale)

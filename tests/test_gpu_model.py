@@ -568,6 +568,57 @@ def test_model_loads_from_a_gguf_file(ctx, oracle, tmp_path, act_f16):
     m2.close()
 
 
+@pytest.mark.parametrize("n_kv", [1, 2])
+def test_sliding_window_layers(ctx, oracle, n_kv):
+    """Sliding-window layers (GemmaConfig.swa_pattern / sliding_window, gemma_prim.rs:1009-1016): flagged layers
+    attend to the last `sliding_window` cached positions, the others to all of them.  Single-slot decode (one
+    launch per op: the persistent kernels attend to the whole context and are bypassed), prompt chunks through the
+    batch matvec and the GEMM path, and several slots at once, all against the CPU decoder."""
+    cfg = ksm.tiny_config(max_seq=120, n_slots=3, n_kv=n_kv)
+    cfg.sliding_window, cfg.swa_layers = 16, 0b101          # layers 0 and 2 slide, layer 1 is full
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=37, keep=True)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    assert model.slot_alloc() == 0
+    _teacher_forced(model, cpu, synth.token_ids(37, "tf", 40, cfg.vocab))       # crosses the window at 16
+    assert model.lib.ks_model_debug_ptr(model.h, 2, 0) is None                  # no persistent kernel was built
+    for n_prompt in (2, 9, 30, 70):                                             # batch matvec; GEMM chunks inside and beyond the window
+        toks = synth.token_ids(37, f"p{n_prompt}", n_prompt + 4, cfg.vocab)
+        model.slot_reset(0)
+        cpu.reset()
+        model.prefill(0, toks[:n_prompt])
+        for t in toks[:n_prompt]:
+            cpu.forward_token(int(t), False)
+        for t in toks[n_prompt:]:
+            model.forward(0, 1, [int(t)], True)
+            ctx.synchronize()
+            cpu.forward_token(int(t), True)
+            got, want = model.read_debug(1, 0).astype(np.float64), cpu.logits().astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (n_prompt, t)
+    # three slots with different histories step together (GEMM path), each against its own CPU run
+    assert [model.slot_alloc() for _ in range(2)] == [1, 2]
+    lens = [20, 5, 33]
+    seqs = [synth.token_ids(37, f"s{s}", lens[s] + 3, cfg.vocab) for s in range(3)]
+    cpus = []
+    for s in range(3):
+        model.slot_reset(s)
+        model.prefill(s, seqs[s][:lens[s]])
+        c2 = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+        for t in seqs[s][:lens[s]]:
+            c2.forward_token(int(t), False)
+        cpus.append(c2)
+    for j in range(3):
+        model.forward(0, 3, [int(seqs[s][lens[s] + j]) for s in range(3)], True)
+        ctx.synchronize()
+        for s in range(3):
+            cpus[s].forward_token(int(seqs[s][lens[s] + j]), True)
+            got, want = model.read_debug(1, s).astype(np.float64), cpus[s].logits().astype(np.float64)
+            assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max(), (j, s)
+    for c2 in cpus:
+        c2.close()
+    cpu.close()
+    model.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
