@@ -240,6 +240,13 @@ int ks_gelu_mul(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* g, const ks_b
  * Dense layers that own their KV cache; no per-layer embeddings, sliding window or shared KV. */
 typedef struct ks_model ks_model;
 
+/* ---- CPU sampling of the serve surface (crates/ksearch_gemma/src/sample.rs:9-81); host code, no GPU needed ----
+ * cap * tanh(x / cap) when cap > 0, then: temperature < 1e-6 -> greedy arg-max (first of equal values, the device
+ * kernel's choice); otherwise softmax at that temperature, tokens below min_p * p_max dropped, one multinomial draw
+ * from splitmix32(seed | 1).  Returns the token id. */
+uint32_t ks_sample_softcap_min_p(const uint16_t* logits_f16, size_t n, float cap, float temperature, float min_p, uint32_t seed);
+uint32_t ks_sample_softcap_min_p_f32(const float* logits, size_t n, float cap, float temperature, float min_p, uint32_t seed);
+
 /* ---- GGUF container (GG:130-417 Gguf::open and accessors); host code, no GPU needed -------------------------
  * ks_gguf_open maps the file and parses header, key/value metadata and tensor infos; NULL on failure with the
  * reason in err ("not a GGUF file (bad magic)", "unsupported GGUF version N", "truncated GGUF file", ... — where the

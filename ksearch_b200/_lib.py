@@ -85,6 +85,8 @@ SIGNATURES = {
     "ks_model_upload_tensor": (_i, [_vp, C.c_char_p, _vp, _sz]),
     "ks_model_upload_tensor_as": (_i, [_vp, C.c_char_p, _i, _vp, _sz]),
     "ks_model_load_gguf": (_i, [_vp, _vp]),
+    "ks_sample_softcap_min_p": (C.c_uint32, [_vp, _sz, _f, _f, _f, C.c_uint32]),
+    "ks_sample_softcap_min_p_f32": (C.c_uint32, [_vp, _sz, _f, _f, _f, C.c_uint32]),
     "ks_gguf_open": (_vp, [C.c_char_p, C.c_char_p, _sz]),
     "ks_gguf_close": (None, [_vp]),
     "ks_gguf_version": (_i, [_vp]),
