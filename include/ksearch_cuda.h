@@ -34,7 +34,7 @@ typedef struct ks_ctx ks_ctx;
 typedef struct ks_buf ks_buf;
 
 /* crates/ksearch_ir/src/lib.rs:17-74 (DType and packed byte sizes) */
-typedef enum { KS_F32 = 0, KS_F16 = 1, KS_Q4K = 2, KS_Q6K = 3, KS_Q40 = 4 } ks_dtype;
+typedef enum { KS_F32 = 0, KS_F16 = 1, KS_Q4K = 2, KS_Q6K = 3, KS_Q40 = 4, KS_Q5K = 5 } ks_dtype;  /* Q5K: dequant, row gather and load-time requantisation only */
 
 typedef enum {
   KS_OK = 0,
@@ -49,6 +49,7 @@ typedef enum {
 #define KS_Q4K_BLOCK_BYTES 144
 #define KS_Q6K_BLOCK_BYTES 210
 #define KS_Q40_BLOCK_BYTES 18
+#define KS_Q5K_BLOCK_BYTES 176
 #define KS_SDPA_MAX_SPLITS 128
 
 /* ---- runtime: MetalContext (M:16-218) ----------------------------------- */

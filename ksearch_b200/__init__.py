@@ -5,8 +5,8 @@ package holds its sources, its build recipe and a thin host-side mirror of the
 reference's op interface.  Importing the package does not load the library;
 creating a ``CudaContext`` does, and fails loudly without an sm_100 GPU.
 """
-from ._lib import F16, F32, Q4K, Q6K, Q40  # noqa: F401
+from ._lib import F16, F32, Q4K, Q5K, Q6K, Q40  # noqa: F401
 from .eng import Buffer, CudaContext, Eng, KsError, q40_nbytes, q40_row_bytes, q4k_nbytes, q6k_nbytes, write_meta  # noqa: F401
 
-__all__ = ["Buffer", "CudaContext", "Eng", "KsError", "F32", "F16", "Q4K", "Q6K", "Q40",
+__all__ = ["Buffer", "CudaContext", "Eng", "KsError", "F32", "F16", "Q4K", "Q5K", "Q6K", "Q40",
            "q40_nbytes", "q40_row_bytes", "q4k_nbytes", "q6k_nbytes", "write_meta"]

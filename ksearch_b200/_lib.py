@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libksearch_cuda.so")
 HEADER = os.path.join(os.path.dirname(PKG), "include", "ksearch_cuda.h")
 
-F32, F16, Q4K, Q6K, Q40 = 0, 1, 2, 3, 4
+F32, F16, Q4K, Q6K, Q40, Q5K = 0, 1, 2, 3, 4, 5
 OK, ERR_INVALID, ERR_CUDA, ERR_OOM, ERR_UNSUPPORTED, ERR_STATE, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
 
 _sz, _i, _f, _vp, _u64 = C.c_size_t, C.c_int, C.c_float, C.c_void_p, C.c_uint64

@@ -63,7 +63,7 @@ int ks_after_launch(ks_ctx* ctx, const char* what);
 static inline size_t ks_act_bytes(ks_dtype a) { return a == KS_F16 ? 2 : 4; }
 static inline bool ks_is_act(ks_dtype a) { return a == KS_F32 || a == KS_F16; }
 static inline size_t ks_block_bytes(ks_dtype d) {
-  return d == KS_Q4K ? KS_Q4K_BLOCK_BYTES : d == KS_Q6K ? KS_Q6K_BLOCK_BYTES : d == KS_Q40 ? KS_Q40_BLOCK_BYTES : 0;
+  return d == KS_Q4K ? KS_Q4K_BLOCK_BYTES : d == KS_Q6K ? KS_Q6K_BLOCK_BYTES : d == KS_Q40 ? KS_Q40_BLOCK_BYTES : d == KS_Q5K ? KS_Q5K_BLOCK_BYTES : 0;
 }
 static inline size_t ks_block_elems(ks_dtype d) { return d == KS_Q40 ? 32 : 256; }
 // bytes of n elements of dtype d (n a multiple of the block size for packed types)

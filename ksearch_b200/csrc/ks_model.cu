@@ -895,7 +895,7 @@ int ks_model_upload_tensor_as(ks_model* m, const char* name, ks_dtype src_dtype,
   KS_REQUIRE(c, it != m->by_name.end(), "missing tensor %s", name);
   Tensor& t = *it->second;
   if ((int)src_dtype == t.dtype) return ks_model_upload_tensor(m, name, host, bytes);
-  KS_REQUIRE(c, t.dtype == KS_Q4K && (src_dtype == KS_Q6K || src_dtype == KS_F16 || src_dtype == KS_F32),
+  KS_REQUIRE(c, t.dtype == KS_Q4K && (src_dtype == KS_Q6K || src_dtype == KS_Q5K || src_dtype == KS_F16 || src_dtype == KS_F32),
              "tensor %s: no conversion from ggml type %d to the resident type %d", name, (int)src_dtype, t.dtype);
   const size_t nelem = t.bytes / KS_Q4K_BLOCK_BYTES * 256;
   KS_REQUIRE(c, bytes == ks_nbytes(src_dtype, nelem), "tensor %s: got %zu bytes, expected %zu", name, bytes, ks_nbytes(src_dtype, nelem));
@@ -947,6 +947,7 @@ int ks_model_load_gguf(ks_model* m, const ks_gguf* g) {
       case 0: src = KS_F32; break;
       case 1: src = KS_F16; break;
       case 12: src = KS_Q4K; break;
+      case 13: src = KS_Q5K; break;
       case 14: src = KS_Q6K; break;
       default: return ks_fail(c, KS_ERR_UNSUPPORTED, "tensor %s: ggml type %u is not supported", name, type);
     }

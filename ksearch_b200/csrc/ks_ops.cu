@@ -63,6 +63,26 @@ __device__ __forceinline__ float deq_q6k(const uint8_t* base, size_t idx) {
   const int s = sc[(l >> 4) + 2 * k];
   return __fmul_rn(__fmul_rn(d, (float)s), (float)qv);
 }
+// Q5_K (gguf_impl.rs:722-760): d, dmin, 12 scale bytes, qh[32] (bit 2g / 2g + 1 of byte l: the fifth bit of element l
+// of the low / high sub-block of 64-group g), qs[128] nibbles laid out as in Q4_K.
+__device__ __forceinline__ float deq_q5k(const uint8_t* base, size_t idx) {
+  const uint8_t* blk = base + (idx >> 8) * KS_Q5K_BLOCK_BYTES;
+  const unsigned e = (unsigned)(idx & 255), grp = e >> 6, hi = (e >> 5) & 1u, l = e & 31u, j = 2u * grp + hi;
+  const float d = half_bits_to_float(rd16(blk)), dmin = half_bits_to_float(rd16(blk + 2));
+  const uint8_t* q = blk + 4;
+  unsigned sc, m;
+  if (j < 4) {
+    sc = q[j] & 63;
+    m = q[j + 4] & 63;
+  } else {
+    sc = (q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4);
+    m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+  }
+  const unsigned byte = blk[48 + grp * 32 + l];
+  const unsigned nib = hi ? (byte >> 4) : (byte & 0x0F);
+  const float fifth = (blk[16 + l] >> j) & 1u ? 16.0f : 0.0f;
+  return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), __fadd_rn((float)nib, fifth)), __fmul_rn(dmin, (float)m));
+}
 __device__ __forceinline__ float deq_q40(const uint8_t* base, size_t idx) {
   const uint8_t* blk = base + (idx >> 5) * KS_Q40_BLOCK_BYTES;
   const unsigned j = (unsigned)(idx & 31);
@@ -76,6 +96,7 @@ __device__ __forceinline__ float deq_any(int dtype, const void* base, size_t idx
     case KS_Q4K: return deq_q4k((const uint8_t*)base, idx);
     case KS_Q6K: return deq_q6k((const uint8_t*)base, idx);
     case KS_Q40: return deq_q40((const uint8_t*)base, idx);
+    case KS_Q5K: return deq_q5k((const uint8_t*)base, idx);
     case KS_F16: return __half2float(((const __half*)base)[idx]);
     default: return ((const float*)base)[idx];
   }
@@ -595,7 +616,7 @@ extern "C" {
 int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_off, size_t nelem, ks_buf* dst,
                size_t dst_off) {
   if (!ctx) return KS_ERR_INVALID;
-  KS_REQUIRE(ctx, dtype == KS_Q4K || dtype == KS_Q6K || dtype == KS_Q40 || dtype == KS_F16,
+  KS_REQUIRE(ctx, dtype == KS_Q4K || dtype == KS_Q6K || dtype == KS_Q40 || dtype == KS_Q5K || dtype == KS_F16,
              "dequant: unsupported ggml type %d", (int)dtype);
   if (dtype != KS_F16) KS_REQUIRE(ctx, nelem % ks_block_elems(dtype) == 0, "dequant: nelem=%zu is not a whole number of blocks", nelem);
   KS_REQUIRE(ctx, ks_fits(src, src_byte_off, ks_nbytes(dtype, nelem)), "dequant: source buffer too small");
@@ -611,7 +632,7 @@ int ks_dequant(ks_ctx* ctx, ks_dtype dtype, const ks_buf* src, size_t src_byte_o
 int ks_quantize_q4k(ks_ctx* ctx, ks_dtype src_dtype, const ks_buf* src, size_t src_byte_off, size_t nelem, ks_buf* dst,
                     size_t dst_byte_off) {
   if (!ctx) return KS_ERR_INVALID;
-  KS_REQUIRE(ctx, src_dtype == KS_Q6K || src_dtype == KS_Q4K || src_dtype == KS_F16 || src_dtype == KS_F32,
+  KS_REQUIRE(ctx, src_dtype == KS_Q6K || src_dtype == KS_Q5K || src_dtype == KS_Q4K || src_dtype == KS_F16 || src_dtype == KS_F32,
              "quantize_q4k: unsupported source type %d", (int)src_dtype);
   KS_REQUIRE(ctx, nelem % 256 == 0, "quantize_q4k: nelem=%zu is not a multiple of 256", nelem);
   KS_REQUIRE(ctx, src_byte_off % 4 == 0 && dst_byte_off % 4 == 0, "quantize_q4k: byte offsets must be multiples of 4");
@@ -699,11 +720,11 @@ int ks_quantize_q40(ks_ctx* ctx, size_t n, ks_dtype act, const ks_buf* src, size
 int ks_copy_scale_indexed(ks_ctx* ctx, size_t n, size_t batch, float scale, ks_dtype src_dtype, const ks_buf* src,
                           const ks_buf* idx, size_t idx_off, ks_dtype act, ks_buf* dst) {
   if (!ctx) return KS_ERR_INVALID;
-  KS_REQUIRE(ctx, src_dtype == KS_F32 || src_dtype == KS_F16 || src_dtype == KS_Q4K || src_dtype == KS_Q6K,
+  KS_REQUIRE(ctx, src_dtype == KS_F32 || src_dtype == KS_F16 || src_dtype == KS_Q4K || src_dtype == KS_Q5K || src_dtype == KS_Q6K,
              "copy_scale_indexed: source dtype %d not wired", (int)src_dtype);
   KS_REQUIRE(ctx, ks_is_act(act), "copy_scale_indexed: destination dtype must be F32 or F16");
   KS_REQUIRE(ctx, n > 0 && batch > 0 && batch < 65536, "copy_scale_indexed: n=%zu batch=%zu out of range", n, batch);
-  if (src_dtype == KS_Q4K || src_dtype == KS_Q6K) KS_REQUIRE(ctx, n % 256 == 0, "copy_scale_indexed: n=%zu must be a multiple of 256 for packed rows", n);
+  if (src_dtype == KS_Q4K || src_dtype == KS_Q5K || src_dtype == KS_Q6K) KS_REQUIRE(ctx, n % 256 == 0, "copy_scale_indexed: n=%zu must be a multiple of 256 for packed rows", n);
   KS_REQUIRE(ctx, src && src->dptr, "copy_scale_indexed: null source");
   KS_REQUIRE(ctx, ks_fits(idx, idx_off * 4, batch * 4), "copy_scale_indexed: index buffer too small");
   KS_REQUIRE(ctx, ks_fits(dst, 0, batch * n * ks_act_bytes(act)), "copy_scale_indexed: destination buffer too small");

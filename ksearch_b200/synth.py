@@ -78,6 +78,17 @@ def q4k_matrix(seed: int, name: str, rows: int, cols: int, sigma: float = 0.01) 
     return buf.reshape(-1)
 
 
+def q5k_matrix(seed: int, name: str, rows: int, cols: int, sigma: float = 0.01) -> np.ndarray:
+    """[rows, cols] in Q5_K (176 bytes per 256): qs nibbles and qh bits uniform, 6-bit scales / mins uniform,
+    d and dmin = fp16(|N(0, sigma)|)."""
+    assert cols % 256 == 0
+    nb = rows * cols // 256
+    buf = rand_bytes(seed, name, nb * 176).reshape(nb, 176)
+    dd = _abs_half_bits(seed, name + "/d", nb * 2, sigma).reshape(nb, 2)
+    buf[:, 0:4] = dd.view(np.uint8).reshape(nb, 4)
+    return buf.reshape(-1)
+
+
 def q6k_matrix(seed: int, name: str, rows: int, cols: int, sigma: float = 0.01,
                signed_scales: bool = False) -> np.ndarray:
     """[rows, cols] in Q6_K: ql/qh bytes uniform, 16 int8 scales uniform 0..63

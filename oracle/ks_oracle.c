@@ -158,6 +158,36 @@ static void deq_q4k_block(const uint8_t* blk, float* out) {
   }
 }
 
+/* gguf_impl.rs:722-760 */
+static void deq_q5k_block(const uint8_t* blk, float* out) {
+  float d = kso_f16_to_f32(rd16(blk));
+  float dmin = kso_f16_to_f32(rd16(blk + 2));
+  const uint8_t* scales = blk + 4;
+  const uint8_t* qh = blk + 16;
+  const uint8_t* qs = blk + 48;
+  int is = 0, qoff = 0;
+  uint8_t u1 = 1, u2 = 2;
+  for (int y = 0; y < QK_K; y += 64) {
+    uint8_t sc1, m1, sc2, m2;
+    scale_min_k4(is, scales, &sc1, &m1);
+    scale_min_k4(is + 1, scales, &sc2, &m2);
+    float d1 = d * (float)sc1, mn1 = dmin * (float)m1;
+    float d2 = d * (float)sc2, mn2 = dmin * (float)m2;
+    for (int l = 0; l < 32; l++) {
+      float hi = (qh[l] & u1) ? 16.0f : 0.0f;
+      out[y + l] = d1 * ((float)(qs[qoff + l] & 0x0F) + hi) - mn1;
+    }
+    for (int l = 0; l < 32; l++) {
+      float hi = (qh[l] & u2) ? 16.0f : 0.0f;
+      out[y + 32 + l] = d2 * ((float)(qs[qoff + l] >> 4) + hi) - mn2;
+    }
+    qoff += 32;
+    is += 2;
+    u1 = (uint8_t)(u1 << 2);
+    u2 = (uint8_t)(u2 << 2);
+  }
+}
+
 static void deq_q6k_block(const uint8_t* blk, float* out) {
   const uint8_t* ql0 = blk;
   const uint8_t* qh0 = blk + 128;
@@ -183,10 +213,10 @@ static void deq_q6k_block(const uint8_t* blk, float* out) {
 }
 
 /* dtype codes shared with the CUDA library's public header */
-enum { KS_F32 = 0, KS_F16 = 1, KS_Q4K = 2, KS_Q6K = 3, KS_Q40 = 4 };
+enum { KS_F32 = 0, KS_F16 = 1, KS_Q4K = 2, KS_Q6K = 3, KS_Q40 = 4, KS_Q5K = 5 };
 
 size_t kso_block_bytes(int dtype) {
-  return dtype == KS_Q4K ? Q4K_BS : dtype == KS_Q6K ? Q6K_BS : dtype == KS_Q40 ? Q40_BS : 0;
+  return dtype == KS_Q4K ? Q4K_BS : dtype == KS_Q6K ? Q6K_BS : dtype == KS_Q40 ? Q40_BS : dtype == KS_Q5K ? 176 : 0;
 }
 size_t kso_block_elems(int dtype) { return dtype == KS_Q40 ? 32 : QK_K; }
 
@@ -198,6 +228,9 @@ int kso_dequant(int dtype, const uint8_t* src, size_t nelem, float* dst) {
   } else if (dtype == KS_Q6K) {
     if (nelem % QK_K) return -1;
     for (size_t b = 0; b < nelem / QK_K; b++) deq_q6k_block(src + b * Q6K_BS, dst + b * QK_K);
+  } else if (dtype == KS_Q5K) {
+    if (nelem % QK_K) return -1;
+    for (size_t b = 0; b < nelem / QK_K; b++) deq_q5k_block(src + b * 176, dst + b * QK_K);
   } else if (dtype == KS_Q40) {
     if (nelem % 32) return -1;
     for (size_t b = 0; b < nelem / 32; b++) deq_q40_block(src + b * Q40_BS, dst + b * 32);

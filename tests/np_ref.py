@@ -43,6 +43,27 @@ def dequant_q4k(data, nelem):
     return out.reshape(-1)
 
 
+def dequant_q5k(data, nelem):
+    """crates/ksearch_gguf/src/gguf_impl.rs:722-760, vectorised over blocks."""
+    nb = nelem // 256
+    blk = np.asarray(data, np.uint8)[: nb * 176].reshape(nb, 176)
+    d = half_to_f32(blk[:, 0:2].copy().view(np.uint16)[:, 0])
+    dmin = half_to_f32(blk[:, 2:4].copy().view(np.uint16)[:, 0])
+    sc, m = scale_min_k4(blk[:, 4:16])
+    qh = blk[:, 16:48]
+    qs = blk[:, 48:176].reshape(nb, 4, 32)
+    out = np.empty((nb, 4, 2, 32), np.float32)
+    for g in range(4):
+        for hi in range(2):
+            j = 2 * g + hi
+            dj = (d * sc[:, j].astype(np.float32)).astype(np.float32)
+            mj = (dmin * m[:, j].astype(np.float32)).astype(np.float32)
+            nib = (qs[:, g, :] >> 4) if hi else (qs[:, g, :] & 0x0F)
+            q = nib.astype(np.float32) + np.where((qh >> j) & 1, np.float32(16.0), np.float32(0.0))
+            out[:, g, hi, :] = ((dj[:, None] * q).astype(np.float32) - mj[:, None]).astype(np.float32)
+    return out.reshape(-1)
+
+
 def dequant_q6k(data, nelem):
     nb = nelem // 256
     blk = np.asarray(data, np.uint8)[: nb * 210].reshape(nb, 210)

@@ -519,7 +519,11 @@ def test_model_loads_from_a_gguf_file(ctx, oracle, tmp_path, act_f16):
     _, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=35, keep=True)
     tensors = []
     for name, kind, rows, cols in ksm.tensor_specs(cfg):
-        if name.endswith("ffn_down.weight") or name.endswith("attn_v.weight"):
+        if name == "blk.0.attn_v.weight" and not act_f16:   # a Q5_K matrix: requantised like the Q6_K ones
+            q5 = synth.q5k_matrix(35, name + "/q5", rows, cols, cfg.sigma_w)
+            tensors.append((name, GGML_Q5_K, (cols, rows), q5))
+            T[name] = oracle.quantize_q4k(oracle.dequant(5, q5, rows * cols))
+        elif name.endswith("ffn_down.weight") or name.endswith("attn_v.weight"):
             q6 = synth.q6k_matrix(35, name + "/q6", rows, cols, cfg.sigma_w, signed_scales=True)
             tensors.append((name, GGML_Q6_K, (cols, rows), q6))
             T[name] = oracle.quantize_q4k(oracle.dequant(Q6K, q6, rows * cols))
@@ -561,7 +565,7 @@ def test_model_loads_from_a_gguf_file(ctx, oracle, tmp_path, act_f16):
     with Gguf(path) as g, pytest.raises(KsError, match="the model expects"):
         m2.load_gguf(g)
     bad = list(tensors)
-    bad[2] = (n0, GGML_Q5_K, d0, np.zeros(int(np.prod(d0)) // 256 * 176, np.uint8))
+    bad[2] = (n0, 8, d0, np.zeros(int(np.prod(d0)) // 32 * 34, np.uint8))        # Q8_0: a type the loader does not convert
     W.write_gguf(path, [], bad)
     with Gguf(path) as g, pytest.raises(KsError, match="not supported"):
         m2.load_gguf(g)

@@ -13,6 +13,7 @@ pytestmark = pytest.mark.gpu
     (Q6K, lambda n: synth.q6k_matrix(31, "w", n // 1024, 1024, signed_scales=True), 64 * 1024),
     (Q40, lambda n: synth.q40_rows(31, "kv", n), 64 * 1024),
     (Q4K, lambda n: synth.q4k_matrix(32, "w", 1, 256), 256),
+    (5, lambda n: synth.q5k_matrix(31, "w5", n // 1024, 1024), 64 * 1024),      # Q5_K
 ])
 def test_dequant_bit_exact(ctx, oracle, dtype, gen, n):
     data = gen(n)
@@ -48,10 +49,10 @@ def _q4k_sources(n):
     f[512:768] = np.abs(f[512:768])                 # a super-block without negative values: every minimum is 0
     f[768:1024] *= 1e-6                             # tiny values: scales near the f16 subnormal range
     f[1024:1280] *= 300.0                           # large values
-    return [(Q6K, q6), (F32, f), (F16, f.astype(np.float16))]
+    return [(Q6K, q6), (F32, f), (F16, f.astype(np.float16)), (5, synth.q5k_matrix(53, "ple", n // 1024, 1024))]
 
 
-@pytest.mark.parametrize("which", [0, 1, 2])
+@pytest.mark.parametrize("which", [0, 1, 2, 3])
 def test_quantize_q4k_matches_reference_quantizer(ctx, oracle, which):
     """ks_quantize_q4k: gguf_impl.rs:803-1016 on the GPU, byte for byte against the CPU restatement fed with the
     dequantised source (gemma_prim.rs:415-440: dequant_to_f32, then quantize_f32_to_q4k)."""
@@ -61,7 +62,7 @@ def test_quantize_q4k_matches_reference_quantizer(ctx, oracle, which):
     dst = ctx.buffer_empty_bytes(n // 256 * 144)
     Eng().quantize_q4k(ctx, dtype, src, n, dst)
     got = ctx.read_bytes(dst, n // 256 * 144)
-    flat = oracle.dequant(dtype, data, n) if dtype == Q6K else np.asarray(data, np.float32)
+    flat = oracle.dequant(dtype, data, n) if dtype in (Q6K, 5) else np.asarray(data, np.float32)
     want = oracle.quantize_q4k(flat)
     bad = np.flatnonzero(got != want)
     assert bad.size == 0, f"{bad.size} differing bytes, first at {bad[:8]} (block {bad[0] // 144}, byte {bad[0] % 144})"
@@ -198,11 +199,13 @@ def test_per_head_qkv_q40(ctx, oracle, act, n_q, n_kv, hd, n_tok):
         e.rmsnorm_per_head_qkv_q40_off(ctx, n_q, n_kv, 48, eps, bq, bqw, brope, 0, bk, bkw, bv, bq, kvk, kvv, 0)
 
 
-@pytest.mark.parametrize("dtype", [Q6K, Q4K, F16, F32])
+@pytest.mark.parametrize("dtype", [Q6K, Q4K, 5, F16, F32])     # 5: Q5_K, the per-layer-embedding table's type (render.rs:695-724)
 def test_copy_scale_indexed(ctx, oracle, dtype):
     e = Eng(F32)
     n, vocab = 1536, 64
-    if dtype == Q6K:
+    if dtype == 5:
+        src = synth.q5k_matrix(45, "e", vocab, n)
+    elif dtype == Q6K:
         src = synth.q6k_matrix(45, "e", vocab, n, signed_scales=True)
     elif dtype == Q4K:
         src = synth.q4k_matrix(45, "e", vocab, n)

@@ -78,6 +78,7 @@ def test_scale_min_k4_matches_numpy(oracle):
     (Q6K, np_ref.dequant_q6k, lambda: synth.q6k_matrix(7, "w", 8, 1024)),
     (Q6K, np_ref.dequant_q6k, lambda: synth.q6k_matrix(7, "ws", 8, 1024, signed_scales=True)),
     (Q40, np_ref.dequant_q40, lambda: synth.q40_rows(7, "kv", 8 * 1024)),
+    (5, np_ref.dequant_q5k, lambda: synth.q5k_matrix(7, "w5", 8, 1024)),
 ])
 def test_dequant_bit_exact_vs_numpy(oracle, dtype, fn, gen):
     data = gen()
