@@ -623,6 +623,45 @@ def test_sliding_window_layers(ctx, oracle, n_kv):
     model.close()
 
 
+def test_scheduler_serves_requests_like_separate_cpu_runs(ctx, oracle):
+    """The serve loop (scheduler.rs:78-353 mirrored in ksearch_b200/scheduler.py) over the real model: more requests
+    than slots, prompts of different lengths prefilled in chunks beside decoding neighbours, slots reused.  Every
+    greedy request receives exactly the tokens a CPU decoder produces for its prompt alone (up to an end-of-sequence
+    id); a sampled request is reproducible from its seed."""
+    from ksearch_b200.scheduler import EOS_IDS, InferenceRequest, Scheduler, SchedulerConfig
+    cfg = ksm.tiny_config(max_seq=96, n_slots=3)
+    model, T = ksm.GemmaCudaModel.synthetic(ctx, cfg, seed=39, keep=True)
+    sched = Scheduler(model, SchedulerConfig(slots=3, prefill_chunk=8, prefill_tokens_per_tick=24))
+    shapes = [(5, 6), (40, 5), (1, 8), (17, 4), (2, 7)]                      # (prompt length, max_tokens)
+    reqs = [InferenceRequest([int(t) for t in synth.token_ids(39, f"r{i}", n, cfg.vocab)], max_tokens=k)
+            for i, (n, k) in enumerate(shapes)]
+    for r in reqs[:4]:
+        sched.submit(r)
+    for _ in range(3):
+        sched.tick()
+    sched.submit(reqs[4])                                                    # arrives while others decode
+    sched.run(400)
+    for r, (n, k) in zip(reqs, shapes):
+        cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+        want = cpu.generate(r.prompt_ids, k)
+        cpu.close()
+        if any(t in EOS_IDS for t in want):
+            want = want[:min(i for i, t in enumerate(want) if t in EOS_IDS)]
+        got = [e[1] for e in r.events if e[0] == "token"]
+        assert got == want, (n, k)
+        assert r.events[-1][0] == "done" and r.events[-1][2:] == (n, len(want))
+    assert model.active_batch() == 0
+    outs = []
+    for _ in range(2):                                                       # temperature sampling on the host: same seed, same tokens
+        r = InferenceRequest(reqs[0].prompt_ids, max_tokens=6, temperature=0.8, min_p=0.05, seed=1234)
+        sched.submit(r)
+        sched.run(100)
+        outs.append([e[1] for e in r.events if e[0] == "token"])
+        assert all(0 <= t < cfg.vocab for t in outs[-1])
+    assert outs[0] == outs[1] and len(outs[0]) >= 1
+    model.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
