@@ -1055,7 +1055,7 @@ static int check_slots(ks_model* m, int first, int n) {
 }
 
 // Rows per pass of a decode step over slots [first, first + n).  A few slots are faster as one persistent-kernel
-// pass each (all layers in one launch, section "one slot" above) than side by side through one launch per op.
+// pass each (all layers of a slot's token in one launch) than side by side through one launch per op.
 int step_rows(ks_model* m, int first, int n) {
   if (n > 1 && n <= m->solo_max) {
     bool all = true;
