@@ -125,7 +125,7 @@ __device__ __forceinline__ float absmax8(const float (&v)[8]) {
 }
 
 // x[token, k] (f32, row stride ldx) -> the B image.  One block per (padded) token row; rows past n_tok become zeros.
-__global__ void x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsigned np, unsigned cols, __half* xt) {
+__global__ void __launch_bounds__(1024) x_split_kernel(const float* x, size_t ldx, unsigned n_tok, unsigned np, unsigned cols, __half* xt) {
   ks_pdl_entry();
   __shared__ float red[32];
   const unsigned t = blockIdx.x, chunks = cols / 8u;
@@ -627,8 +627,9 @@ __global__ void gemm_finish_norm_split_kernel(const EpiNormArgs e) {
 }
 
 // gelu(sum of gate partials) * (sum of up partials) (lib.rs:953) straight into the image the down GEMM reads.
-constexpr int GM_GELU_CHUNKS = 8;  // 8-value chunks per thread: rows up to 8 * 8 * 256 = 16384
-__global__ void gemm_finish_gelu_split_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok,
+constexpr int GM_GELU_CHUNKS = 2;     // 8-value chunks per thread
+constexpr int GM_ROW_THREADS = 1024;  // threads of a block that writes one token row of an image: rows up to 2 * 8 * 1024 = 16384
+__global__ void __launch_bounds__(GM_ROW_THREADS) gemm_finish_gelu_split_kernel(const float* P0, const float* P1, size_t part_stride, unsigned splits, unsigned n_tok,
                                               unsigned np, unsigned rows, __half* xt) {
   ks_pdl_entry();
   __shared__ float red[32];
@@ -726,7 +727,7 @@ size_t ks_gemm_xt_bytes(size_t cols, int n_tok) { return cols * gemm_np(n_tok) *
 int ks_launch_gemm_split(ks_ctx* ctx, const float* x, size_t ldx, int n_tok, size_t cols, void* xt) {
   if (cols % 256 || n_tok < 1 || n_tok > 256 || ldx % 4) return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad operand shape");
   const unsigned np = gemm_np(n_tok);
-  KS_LAUNCH(ctx, (x_split_kernel), np, 256, 0, x, ldx, (unsigned)n_tok, np, (unsigned)cols, (__half*)xt);
+  KS_LAUNCH(ctx, (x_split_kernel), np, GM_ROW_THREADS, 0, x, ldx, (unsigned)n_tok, np, (unsigned)cols, (__half*)xt);
   return ks_after_launch(ctx, "x_split");
 }
 
@@ -738,7 +739,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
                         int n_tok, float* const* y, const size_t* ldy, float* P, int mode, const ks_gemm_epi* epi) {
   if (!gemm_covers(wdtype, cols, n_tok) || n_seg < 1 || n_seg > 3) return ks_fail(ctx, KS_ERR_UNSUPPORTED, "gemm: shape not covered");
   if ((mode == KS_GEMM_NORM_SPLIT && (n_seg != 1 || !epi || rows[0] % 8 || rows[0] > 8192)) ||
-      (mode == KS_GEMM_GELU_SPLIT && (n_seg != 2 || !epi || rows[0] != rows[1] || rows[0] % 8 || rows[0] > 8u * GM_GELU_CHUNKS * 256u)))
+      (mode == KS_GEMM_GELU_SPLIT && (n_seg != 2 || !epi || rows[0] != rows[1] || rows[0] % 8 || rows[0] > 8u * GM_GELU_CHUNKS * GM_ROW_THREADS)))
     return ks_fail(ctx, KS_ERR_INVALID, "gemm: bad epilogue arguments");
   GemmArgs a{};
   FinishArgs f{};
@@ -824,7 +825,7 @@ int ks_launch_gemm_segs(ks_ctx* ctx, ks_dtype wdtype, int n_seg, const uint8_t* 
     return ks_after_launch(ctx, "gemm_finish_norm_split");
   }
   if (mode == KS_GEMM_GELU_SPLIT) {
-    KS_LAUNCH(ctx, (gemm_finish_gelu_split_kernel), a.np, 256, 0, (const float*)a.y[0], (const float*)a.y[1],
+    KS_LAUNCH(ctx, (gemm_finish_gelu_split_kernel), a.np, GM_ROW_THREADS, 0, (const float*)a.y[0], (const float*)a.y[1],
               a.part_stride[0], splits, (unsigned)n_tok, a.np, (unsigned)rows[0], (__half*)epi->xt_out);
     return ks_after_launch(ctx, "gemm_finish_gelu_split");
   }
