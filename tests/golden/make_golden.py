@@ -73,6 +73,12 @@ def compute(oracle):
     g["pack.q40"] = _d(oracle.pack_q40(synth.normals(SEED, "pack", 512, sigma=0.7)))
     g["pack.q40.through_half"] = _d(oracle.pack_q40(synth.normals(SEED, "pack", 512, sigma=0.7), through_half=True))
     g["f32_to_f16_ref"] = _d(oracle.f32_to_f16_ref(synth.normals(SEED, "h", 4096, sigma=3.0)))
+    W5 = synth.q5k_matrix(SEED, "w5", 16, 1024)
+    g["synth.q5k"] = _d(synth.q5k_matrix(SEED, "e", 4, 512))
+    g["dequant.q5k"] = _d(oracle.dequant(5, W5, 16 * 1024))
+    # the load-time requantisation of the reference's loader: dequantise, then quantize_f32_to_q4k
+    g["requant.q6k_to_q4k"] = _d(oracle.quantize_q4k(oracle.dequant(Q6K, W6, 16 * 1024)))
+    g["requant.q5k_to_q4k"] = _d(oracle.quantize_q4k(oracle.dequant(5, W5, 16 * 1024)))
     return g
 
 
