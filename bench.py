@@ -422,7 +422,7 @@ def serve_e4b(ctx, rank, world, dist, peak, prompt_len=512, n_new=256):
            "prefill_tok_s_total": n_local * world * (prompt_len - 1) / prefill_s,
            "bytes_required_per_round_per_gpu": per_step, "gbs_per_gpu": per_step / (ms / steps) / 1e6,
            "frac_of_measured_peak": per_step / (ms / steps) / 1e6 / peak,
-           "path": "persistent decode kernel" if n_local == 1 else "one launch per op; more slots than the batch matvec stages share one pass through the tensor-core GEMM, "
+           "path": "persistent decode kernel" if n_local == 1 else "two persistent-kernel passes per round" if n_local == 2 else "one launch per op; the slots share one pass through the tensor-core GEMM, "
                                                                    "prompts run in 256-row GEMM chunks"}
     model.close()
     return res
