@@ -662,6 +662,64 @@ def test_scheduler_serves_requests_like_separate_cpu_runs(ctx, oracle):
     model.close()
 
 
+def test_from_a_gguf_file_to_served_text(ctx, oracle, tmp_path):
+    """The whole load and request path over one file: GGUF reader, GemmaConfig, dense model config, device model,
+    tokenizer from the file's vocabulary, chat template, scheduler.  The served tokens are the CPU decoder's greedy
+    tokens for the same prompt ids, cut where the scheduler's stop rules cut them."""
+    from ksearch_b200.chat import gemma4_chat_from_messages
+    from ksearch_b200.gguf import GGML_F32, GGML_Q4_K, GGML_Q6_K
+    from ksearch_b200.scheduler import BUILTIN_STOPS, EOS_IDS
+    from ksearch_b200.serve import Server
+    from ksearch_b200 import Q6K
+    from tests import gguf_writer as W
+    from tests.test_tokenizer import _vocab
+    cfg = ksm.tiny_config(max_seq=64, n_slots=2)
+    T = ksm.synth_tensors(cfg, 41)
+    toks, types, merges = _vocab()
+    toks += [f"t{i}" for i in range(len(toks), cfg.vocab)]
+    types += [1] * (cfg.vocab - len(types))
+    md = [("general.architecture", W.STR, "gemma4"), ("gemma4.block_count", W.U32, cfg.n_layers),
+          ("gemma4.embedding_length", W.U32, cfg.hidden), ("gemma4.attention.head_count", W.U32, cfg.n_q),
+          ("gemma4.attention.head_count_kv", W.U32, cfg.n_kv), ("gemma4.attention.key_length", W.U32, cfg.hd),
+          ("gemma4.attention.key_length_swa", W.U32, cfg.hd), ("gemma4.feed_forward_length", W.U32, cfg.ffn),
+          ("gemma4.attention.sliding_window", W.U32, 512), ("gemma4.context_length", W.U32, 256),
+          ("gemma4.rope.freq_base_swa", W.F32, cfg.rope_theta), ("gemma4.rope.freq_base", W.F32, cfg.rope_theta),
+          ("gemma4.attention.layer_norm_rms_epsilon", W.F32, cfg.eps), ("gemma4.final_logit_softcapping", W.F32, cfg.softcap),
+          ("tokenizer.ggml.model", W.STR, "gemma4"), ("tokenizer.ggml.tokens", W.ARR, (W.STR, toks)),
+          ("tokenizer.ggml.merges", W.ARR, (W.STR, merges)), ("tokenizer.ggml.token_type", W.ARR, (W.I32, types)),
+          ("tokenizer.ggml.unknown_token_id", W.U32, 3), ("tokenizer.ggml.bos_token_id", W.U32, 2)]
+    tensors = []
+    for name, kind, rows, cols in ksm.tensor_specs(cfg):
+        if kind == "norm":
+            tensors.append((name, GGML_F32, (cols,), np.asarray(T[name], np.float32)))
+        else:
+            tensors.append((name, GGML_Q6_K if (kind == "embd" and cfg.embd_dtype == Q6K) else GGML_Q4_K, (cols, rows), T[name]))
+    path = tmp_path / "served.gguf"
+    W.write_gguf(path, md, tensors)
+    srv = Server(str(path), ctx, max_seq=cfg.max_seq, slots=2, attn_scale=cfg.attn_scale)
+    assert (srv.cfg.n_layers, srv.cfg.hidden, srv.cfg.ffn, srv.cfg.hd, srv.cfg.vocab, srv.cfg.sliding_window) == (3, 512, 1024, 128, 2048, 0)
+    messages = [("user", "hello world")]
+    req = srv.submit(messages, max_tokens=8)
+    srv.scheduler.run()
+    got = [e[1] for e in req.events if e[0] == "token"]
+    ids = srv.tokenizer.encode(gemma4_chat_from_messages(messages)).ids
+    assert req.events[-1][0] == "done" and req.events[-1][2] == len(ids)
+    cpu = oracle.CpuDecoder(oracle.decoder_cfg(cfg), T)
+    raw = cpu.generate(ids, 8)
+    cpu.close()
+    want, text = [], ""
+    for t in raw:                                   # the scheduler's stop rules over the CPU tokens
+        if t in EOS_IDS:
+            break
+        text += srv.tokenizer.decode([t], skip_special_tokens=False)
+        if any(s in text for s in BUILTIN_STOPS):
+            break
+        want.append(t)
+    assert got == want
+    assert srv.complete(messages, max_tokens=8) == srv.tokenizer.decode(want, skip_special_tokens=True)
+    srv.close()
+
+
 def test_launch_per_op_path_matches_cpu_decoder(oracle, monkeypatch):
     """KSEARCH_DECODE_KERNEL=0: the single-slot step as one launch per op (fused norm prologues)."""
     from ksearch_b200 import CudaContext
