@@ -175,3 +175,59 @@ def test_more_requests_than_slots_wait_their_turn():
     s.submit(b)
     s.run(50)
     assert _done(a) == ("length", 1, 2) and b.events[0][0] == "error" and "admit failed" in b.events[0][1]
+
+
+def test_sampled_requests_read_logits_and_use_the_reference_sampler():
+    """temperature > 0: the step runs with logits, each request's row goes through sample_softcap_min_p with the
+    request's own rng state (seed | 1, advanced by 0x9E3779B9 per step, scheduler.rs:181-182)."""
+    import numpy as np
+    from ksearch_b200.sample import sample_softcap_min_p
+
+    class LogitModel(FakeModel):
+        class _Ctx:
+            def synchronize(self):
+                pass
+        ctx = _Ctx()
+
+        def forward(self, first, n, toks, want_logits):
+            assert want_logits
+            self.steps.append((first, n))
+            self.rows = {}
+            for i, t in enumerate(toks):
+                s = first + i
+                rng = np.random.default_rng(1000 * t + self.len[s])
+                self.rows[s] = (rng.standard_normal(self.cfg.vocab) * 3).astype(np.float32)
+                self.rows[s][[1, 106]] = -50.0            # never an end-of-sequence id
+                self.len[s] += 1
+
+        def read_debug(self, which, slot):
+            assert which == 1
+            return self.rows[slot]
+
+    m = LogitModel(n_slots=2)
+    s = Scheduler(m, SchedulerConfig(slots=2))
+    a = InferenceRequest([300, 301], max_tokens=4, temperature=0.9, min_p=0.05, seed=10)
+    b = InferenceRequest([400], max_tokens=4, temperature=0.0)          # greedy beside it: the mixed step samples both on the host
+    s.submit(a)
+    s.submit(b)
+    s.run(50)
+    assert _done(a) == ("length", 2, 4) and _done(b) == ("length", 1, 4)
+    # replay request a alone with the documented rng sequence
+    m2 = LogitModel(n_slots=1)
+    m2.slot_alloc()
+    m2.prefill(0, [300])
+    tok, rng, want = 301, (10 | 1), []
+    for _ in range(4):
+        rng = (rng + 0x9E3779B9) & 0xFFFFFFFF
+        m2.forward(0, 1, [tok], True)
+        tok = sample_softcap_min_p(m2.read_debug(1, 0), 30.0, 0.9, 0.05, rng)
+        want.append(tok)
+    assert _tokens(a) == want
+    # the greedy request got the arg-max of its rows
+    m3 = LogitModel(n_slots=2)
+    m3.slot_alloc(); m3.slot_alloc()
+    tok, got = 400, _tokens(b)
+    for step in range(4):
+        m3.forward(1, 1, [tok], True)
+        tok = int(np.argmax(30.0 * np.tanh(m3.read_debug(1, 1) / 30.0)))
+        assert got[step] == tok
