@@ -82,12 +82,12 @@ class CudaContext:
         self.lib = _lib.load()
         self.h = self.lib.ks_ctx_create(device, flags)
         if not self.h:
-            raise KsError(_lib.ERR_UNSUPPORTED, self.lib.ks_last_error(None).decode())
+            raise KsError(_lib.ERR_UNSUPPORTED, self.lib.ks_last_error(None).decode(errors="replace"))
 
     # -- errors
     def check(self, rc: int):
         if rc != 0:
-            raise KsError(rc, self.lib.ks_last_error(self.h).decode())
+            raise KsError(rc, self.lib.ks_last_error(self.h).decode(errors="replace"))
 
     def device_name(self) -> str:
         return self.lib.ks_chip_name(self.h).decode()
@@ -107,7 +107,7 @@ class CudaContext:
     def buffer_empty_bytes(self, nbytes: int) -> Buffer:
         h = self.lib.ks_buf_alloc(self.h, nbytes)
         if not h:
-            raise KsError(_lib.ERR_OOM, self.lib.ks_last_error(self.h).decode())
+            raise KsError(_lib.ERR_OOM, self.lib.ks_last_error(self.h).decode(errors="replace"))
         return Buffer(self, h, nbytes)
 
     def buffer_empty_f32(self, n: int) -> Buffer:
@@ -176,7 +176,7 @@ class CudaContext:
     def graph_end(self) -> int:
         g = self.lib.ks_graph_end(self.h)
         if not g:
-            raise KsError(_lib.ERR_CUDA, self.lib.ks_last_error(self.h).decode())
+            raise KsError(_lib.ERR_CUDA, self.lib.ks_last_error(self.h).decode(errors="replace"))
         return g
 
     def graph_launch(self, g: int):

@@ -36,7 +36,7 @@ class Gguf:
         err = C.create_string_buffer(256)
         self.h = self.lib.ks_gguf_open(str(path).encode(), err, 256)
         if not self.h:
-            raise KsError(_lib.ERR_INVALID, err.value.decode())
+            raise KsError(_lib.ERR_INVALID, err.value.decode(errors="replace"))
 
     def close(self):
         if self.h:
@@ -61,7 +61,7 @@ class Gguf:
         return self.lib.ks_gguf_n_kv(self.h)
 
     def tensor_names(self) -> list:
-        return [self.lib.ks_gguf_tensor_name(self.h, i).decode() for i in range(self.lib.ks_gguf_n_tensors(self.h))]
+        return [self.lib.ks_gguf_tensor_name(self.h, i).decode(errors="replace") for i in range(self.lib.ks_gguf_n_tensors(self.h))]
 
     def has_tensor(self, name: str) -> bool:
         return self.lib.ks_gguf_tensor(self.h, name.encode(), None, None, None, None, None) == 0

@@ -125,7 +125,7 @@ class GemmaCudaModel:
         c = _Cfg(**{k: getattr(cfg, k) for k, _ in _Cfg._fields_})
         self.h = self.lib.ks_model_create(ctx.h, C.byref(c))
         if not self.h:
-            raise KsError(_lib.ERR_INVALID, self.lib.ks_last_error(ctx.h).decode())
+            raise KsError(_lib.ERR_INVALID, self.lib.ks_last_error(ctx.h).decode(errors="replace"))
 
     @classmethod
     def synthetic(cls, ctx: CudaContext, cfg: ModelConfig, seed: int, keep: bool = False):
@@ -161,7 +161,7 @@ class GemmaCudaModel:
     def slot_alloc(self) -> int:
         s = self.lib.ks_model_slot_alloc(self.h)
         if s < 0:
-            raise KsError(s, self.lib.ks_last_error(self.ctx.h).decode())
+            raise KsError(s, self.lib.ks_last_error(self.ctx.h).decode(errors="replace"))
         return s
 
     def slot_free(self, slot: int):

@@ -76,7 +76,7 @@ class Comm:
         self.h = ctx.lib.ks_comm_init(ctx.h, world, rank, buf)
         if not self.h:
             from .eng import KsError
-            raise KsError(-2, ctx.lib.ks_last_error(ctx.h).decode())
+            raise KsError(-2, ctx.lib.ks_last_error(ctx.h).decode(errors="replace"))
 
     @staticmethod
     def unique_id(lib) -> bytes:
@@ -86,7 +86,7 @@ class Comm:
         rc = lib.ks_comm_unique_id(buf)
         if rc:
             from .eng import KsError
-            raise KsError(rc, lib.ks_last_error(None).decode())
+            raise KsError(rc, lib.ks_last_error(None).decode(errors="replace"))
         return buf.raw
 
     P2P_HANDLE_BYTES = 64

@@ -144,3 +144,44 @@ def test_open_errors(tmp_path):
     p.write_bytes(head)
     with pytest.raises(KsError, match="unexpected scalar value type 77"):
         Gguf(p)
+
+
+def test_damaged_headers_are_refused_or_read_never_trusted(tmp_path):
+    """Every truncation of the header and a few hundred random byte changes in it: the reader either refuses the file
+    with an error or opens it and answers every query from inside the mapping (counts, lengths and offsets in the
+    file are bounds-checked before use).  Strings that are no longer UTF-8 come back with replacement characters,
+    as the reference's lossy conversion gives them (gguf_impl.rs:172)."""
+    path, _, _ = _file(tmp_path)
+    whole = path.read_bytes()
+    with Gguf(path) as g:
+        data_off = g.data_offset
+    p = tmp_path / "d.gguf"
+    for cut in range(0, data_off + 1, 5):
+        p.write_bytes(whole[:cut])
+        with pytest.raises(KsError):
+            Gguf(p)
+    rng = np.random.default_rng(7)
+    opened = 0
+    for _ in range(300):
+        b = bytearray(whole)
+        for _ in range(int(rng.integers(1, 4))):
+            b[int(rng.integers(0, data_off))] = int(rng.integers(0, 256))
+        p.write_bytes(bytes(b))
+        try:
+            g = Gguf(p)
+        except KsError:
+            continue
+        with g:
+            opened += 1
+            for name in g.tensor_names():
+                info = g.tensor(name) if g.has_tensor(name) else None
+                if info is not None and info.nbytes:
+                    assert info.file_offset + info.nbytes <= len(whole)
+                    assert g.tensor_raw(name).size == info.nbytes
+            for key in ("tokenizer.ggml.tokens", "gemma4.feed_forward_length", "general.architecture"):
+                g.get_arr_str(key), g.get_usize_list(key), g.get_str(key)
+            try:
+                GemmaConfig.from_gguf(g)
+            except KsError:
+                pass
+    assert 0 < opened < 300
